@@ -1,0 +1,203 @@
+/*
+ * strata_moe.h -- C ABI of the B200-native MoE expert block.
+ *
+ * One hot path of ro99/strata behind plain-C entry points: router scoring with top-k,
+ * token->expert permutation with per-expert offsets, grouped quantized expert GEMMs
+ * (gate/up + SwiGLU, down) on MXFP4 / NVFP4 / INT4-g128 weights, and the top-k-weighted
+ * combine plus shared expert.  All compute runs in hand-written sm_100a CUDA kernels;
+ * there is no CPU fallback: every entry point fails with an error when no CUDA device
+ * is usable.
+ *
+ * Citations "ref:" name the file:line of the reference interface an entry point
+ * replaces (paths within the reference project).
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative STRATA_MOE_E_* code; the text of
+ *     the last failure is available from strata_moe_last_error() (the reference's
+ *     ValidationResult, include/strata/result.hpp:8-20, flattened to code + message);
+ *   - work is enqueued on the context's stream and is asynchronous unless stated;
+ *   - device kernels never trap: data-dependent failures (non-finite logits or results)
+ *     raise a status word that strata_moe_synchronize()/strata_moe_status() report, as the
+ *     reference's moe_error flag does (ref: kernels/cuda/backend.cu:1922-1924);
+ *   - pointers are plain device or host addresses as each parameter states.
+ */
+#ifndef STRATA_MOE_H
+#define STRATA_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct strata_moe_ctx strata_moe_ctx;     /* one per process and device */
+typedef struct strata_moe_layer strata_moe_layer; /* one MoE layer's resident weights + workspaces */
+
+enum {
+    STRATA_MOE_OK = 0,
+    STRATA_MOE_E_INVALID = -1,  /* bad argument / shape / state */
+    STRATA_MOE_E_CUDA = -2,     /* a CUDA call failed */
+    STRATA_MOE_E_NUMERIC = -3,  /* device status word: non-finite value or bad route */
+    STRATA_MOE_E_BUSY = -4,     /* a dense command is already in flight */
+    STRATA_MOE_E_NO_DEVICE = -5
+};
+
+/* Weight encodings (ref: include/strata/cuda_backend.hpp:18-39 CudaWeightEncoding).
+ *   MXFP4    u8 [rows, cols/2], low nibble = even column; E8M0 u8 [rows, cols/32]
+ *   NVFP4    u8 [rows, cols/2]; E4M3 u8 [rows, cols/16]; fp32 global scale;
+ *            w = e2m1 * (e4m3 / global)   (ref: include/strata/cuda_backend.hpp:24-29)
+ *   INT4G128 little-endian u32 [rows, cols/8], nibble j = column 8w+j, value raw-8;
+ *            BF16 scale [rows, cols/128]  (ref: kernels/cuda/backend.cu:1908-1916) */
+enum { STRATA_MOE_FMT_MXFP4 = 0, STRATA_MOE_FMT_NVFP4 = 1, STRATA_MOE_FMT_INT4G128 = 2 };
+
+/* Router score functions (ref: include/strata/model.hpp:43-48 RouterScoreKind). */
+enum {
+    STRATA_MOE_SCORE_SIGMOID = 0,       /* ref: src/platform/numerics.cpp:44-48 */
+    STRATA_MOE_SCORE_SIGMOID_PLAIN = 1, /* ref: src/models/kimi_k3/kimi_k3_ops.cpp:12-14 */
+    STRATA_MOE_SCORE_SOFTMAX = 2,       /* no reference implementation exists */
+    STRATA_MOE_SCORE_SQRTSOFTPLUS = 3   /* ref: src/models/dsv4/deepseek_ops.cpp:82-133 */
+};
+
+enum { STRATA_MOE_ROLE_GATE = 0, STRATA_MOE_ROLE_UP = 1, STRATA_MOE_ROLE_DOWN = 2 };
+
+/* Where a source pointer lives and what registration does with it. */
+enum {
+    STRATA_MOE_SRC_HOST = 0,          /* host memory: copied to the device */
+    STRATA_MOE_SRC_DEVICE_COPY = 1,   /* device memory: copied into layer-owned storage */
+    STRATA_MOE_SRC_DEVICE_BORROW = 2  /* device memory: used in place, caller keeps it alive */
+};
+
+/* One MoE layer (ref: include/strata/model.hpp:50-60 RouterSpec plus the shape constants
+ * each runtime hard-codes, e.g. src/models/glm52/glm_runtime.cpp kHidden/kExperts/kTopK). */
+typedef struct strata_moe_layer_desc {
+    uint32_t hidden;              /* H, multiple of 128 */
+    uint32_t intermediate;        /* I, multiple of 128 */
+    uint32_t experts;             /* E routed experts in the whole model layer (<= 1024) */
+    uint32_t top_k;               /* k (<= 32) */
+    int32_t format;               /* STRATA_MOE_FMT_* of the routed experts */
+    int32_t score_kind;           /* STRATA_MOE_SCORE_* */
+    int32_t normalize;            /* divide the selected scores by their sum */
+    float norm_init;              /* start value of that sum (GLM: 1e-20, others 0) */
+    float weight_scale;           /* multiplied into every routing weight (GLM 2.5, DSV4 1.5) */
+    float output_scale;           /* multiplied into the summed routed output (Laguna 2.5) */
+    float softcap;                /* Laguna tanh logit soft-cap, 0 = off */
+    uint32_t shared_intermediate; /* width of the always-on BF16 shared expert, 0 = none */
+    uint32_t expert_begin;        /* first routed expert resident on this device */
+    uint32_t expert_count;        /* number resident here (experts for a single GPU) */
+    uint32_t max_tokens;          /* largest T of a forward call (sizes the workspaces) */
+    uint32_t max_pairs;           /* largest number of (token, expert) rows the local experts
+                                     receive in one call; 0 = max_tokens * top_k */
+} strata_moe_layer_desc;
+
+/* Optional device outputs of strata_moe_forward (any may be NULL). */
+typedef struct strata_moe_aux {
+    float* logits;     /* [T, E] fp32 */
+    uint32_t* ids;     /* [T, k] expert ids in selection-rank order */
+    float* weights;    /* [T, k] routing weights */
+    uint32_t* counts;  /* [E] */
+    uint32_t* offsets; /* [E + 1] exclusive prefix of counts */
+    uint32_t* perm;    /* [T * k]: position -> token * k + rank, stable by (expert, token, rank) */
+} strata_moe_aux;
+
+typedef struct strata_moe_stats {
+    uint64_t forward_calls;
+    uint64_t kernel_launches; /* kernels of this library launched since creation */
+    uint64_t h2d_bytes, d2h_bytes;
+    uint64_t weight_bytes;    /* resident expert + router + shared bytes */
+    float last_forward_ms;    /* CUDA-event time of the last forward when timing is on */
+} strata_moe_stats;
+
+/* ---- context ------------------------------------------------------------------------
+ * ref: CudaBackend::initialize, include/strata/cuda_backend.hpp:787 (one stream per device,
+ * kernels/cuda/backend.cu:5854-5895).  stream = an existing cudaStream_t to run on, or NULL
+ * to create a non-blocking stream owned by the context. */
+int strata_moe_create(int device, void* stream, strata_moe_ctx** out);
+void strata_moe_destroy(strata_moe_ctx* ctx);
+const char* strata_moe_last_error(const strata_moe_ctx* ctx);
+/* Waits for the stream, then reports and clears the device status word.
+ * ref: CudaBackend::synchronize + the moe_error read-back, kernels/cuda/backend.cu:16927-16943 */
+int strata_moe_synchronize(strata_moe_ctx* ctx);
+int strata_moe_get_stats(const strata_moe_ctx* ctx, strata_moe_stats* out);
+void strata_moe_set_timing(strata_moe_ctx* ctx, int enabled);
+/* With timing on, strata_moe_forward brackets its phases with CUDA events on the context's
+ * stream and waits for the call to finish (ref: the per-command event timing in
+ * kernels/cuda/backend.cu:16294-16380, read back at 16927-16943).  out receives
+ * STRATA_MOE_PHASES durations in ms: router projection, score/top-k, grouping, row gather,
+ * gate/up + SwiGLU, down, shared expert, combine. */
+#define STRATA_MOE_PHASES 8
+int strata_moe_get_phase_ms(strata_moe_ctx* ctx, float* out);
+
+/* ---- layer + weights ------------------------------------------------------------------
+ * ref: CudaBackend::upload(device, CudaWeightDescriptor, weights, scales, CudaWeight&),
+ * include/strata/cuda_backend.hpp:819-823; descriptor include/strata/cuda_backend.hpp:41-51. */
+int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* desc,
+                            strata_moe_layer** out);
+void strata_moe_layer_destroy(strata_moe_layer* layer);
+/* gate_bf16 [E, H] BF16 row-major; bias [E] fp32 or NULL (selection bias only). */
+int strata_moe_set_router(strata_moe_layer* layer, const void* gate_bf16, const float* bias,
+                          int source);
+/* One projection of one routed expert (global expert index, must be resident here).
+ * gate/up are [I, H], down is [H, I]; packed and scales as the format defines. */
+int strata_moe_set_expert(strata_moe_layer* layer, uint32_t expert, int role, const void* packed,
+                          const void* scales, float global_scale, int source);
+/* BF16 shared expert projection: gate/up [Is, H], down [H, Is]. */
+int strata_moe_set_shared(strata_moe_layer* layer, int role, const void* weights_bf16, int source);
+
+/* ---- the layer ------------------------------------------------------------------------
+ * out[t] = output_scale * sum_r w[t,r] * expert_{id[t,r]}(x[t]) + shared(x[t]), r in rank order.
+ * Replaces the sparse_mlp bodies of the model runtimes (ref: src/models/glm52/glm_runtime.cpp:
+ * 1487-1618, src/models/laguna/laguna_runtime.cpp:907-1158, src/models/dsv4/deepseek_runtime.cpp:
+ * 6070-6096) including the host-side routing, grouping and combine they wrap around
+ * CudaBackend::enqueue_moe.  x_bf16 [T, H] BF16 and out [T, H] fp32 are device pointers.
+ * Requires expert_count == experts (single-GPU layer). */
+int strata_moe_forward(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens, float* out,
+                       const strata_moe_aux* aux);
+/* Same call with HOST buffers (pageable or pinned): copies x in, runs, copies out back and
+ * waits.  This is the call shape of the reference, whose commands take host spans
+ * (ref: include/strata/cuda_backend.hpp:1147-1153). */
+int strata_moe_forward_host(strata_moe_layer* layer, const void* x_bf16_host, uint32_t tokens,
+                            float* out_host);
+
+/* ---- stages (used by the expert-parallel driver and by the parity tests) ---------------- */
+/* ref: linear(gate) + glm_route_logits_noaux_tc / laguna_route_sigmoid_topk / kimi_route_topk /
+ * dsv4_route_sqrtsoftplus_f32 (src/models/glm52/glm_ops.cpp:176-233, src/models/laguna/
+ * laguna_ops.cpp:182-243, src/models/kimi_k3/kimi_k3_ops.cpp:192-237, src/models/dsv4/
+ * deepseek_ops.cpp:82-133); projection order as kernels/cuda/backend.cu:651-728. */
+int strata_moe_route(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens, float* logits,
+                     uint32_t* ids, float* weights);
+/* ref: job building in sparse_mlp (src/models/glm52/glm_runtime.cpp:1521-1541) and the page
+ * group table (src/models/dsv4/deepseek_runtime.cpp:6216-6321).  Groups pairs whose expert lies
+ * in [expert_begin, expert_begin + n_experts); counts/offsets are indexed from expert_begin.
+ * pairs = number of entries of ids; perm[pos] = index into ids. */
+int strata_moe_group(strata_moe_layer* layer, const uint32_t* ids, uint32_t pairs,
+                     uint32_t expert_begin, uint32_t n_experts, uint32_t* counts,
+                     uint32_t* offsets, uint32_t* perm);
+/* Grouped expert FFN on rows already sorted by local expert.
+ * ref: CudaBackend::enqueue_deepseek_moe_rows (the grouped command),
+ * include/strata/cuda_backend.hpp:1139-1146, kernels/cuda/backend.cu:15346-15996.
+ * rows_bf16 [pairs, H] BF16 in group order; offsets [expert_count + 1] device;
+ * y [pairs, H] fp32 un-combined expert outputs. */
+int strata_moe_experts_grouped(strata_moe_layer* layer, const void* rows_bf16, uint32_t pairs,
+                               const uint32_t* offsets, float* y);
+/* Exact fp32 dequantisation of one resident projection into host memory [rows, cols]
+ * (the NVFP4 value includes the division by the global scale).  Synchronous. */
+int strata_moe_dequant_export(strata_moe_layer* layer, uint32_t expert, int role, float* out_host);
+
+/* ---- dense command, call-compatible with the reference backend --------------------------
+ * ref: CudaBackend::enqueue_moe / collect_moe, include/strata/cuda_backend.hpp:1147-1153,
+ * kernels/cuda/backend.cu:16003-16396, 17199-17203.  Every listed expert is applied to all
+ * `rows` rows; routed_output is [expert][row][H] fp32, shared_output [row][H] (NULL = skip).
+ * hidden_host is fp32 [rows, H] on the host.  coefficients[i] multiplies expert i's
+ * activation before the down projection for INT4 (ref: kernels/cuda/backend.cu:1933) and must
+ * be 1.0 for the other formats (ref: kernels/cuda/backend.cu:16088-16096).
+ * One command may be in flight per layer; collect waits for it. */
+int strata_moe_enqueue_dense(strata_moe_layer* layer, const float* hidden_host, uint32_t rows,
+                             const uint32_t* experts, const float* coefficients, uint32_t n_experts,
+                             int with_shared);
+int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, float* shared_output);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* STRATA_MOE_H */

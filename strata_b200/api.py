@@ -1,0 +1,271 @@
+"""ctypes binding of include/strata_moe.h.  torch is used only for device memory and streams."""
+import ctypes as C
+import os
+
+import torch
+
+from . import synth
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+EXPORTS = [
+    "strata_moe_create", "strata_moe_destroy", "strata_moe_last_error", "strata_moe_synchronize",
+    "strata_moe_get_stats", "strata_moe_set_timing", "strata_moe_get_phase_ms", "strata_moe_layer_create",
+    "strata_moe_layer_destroy", "strata_moe_set_router", "strata_moe_set_expert",
+    "strata_moe_set_shared", "strata_moe_forward", "strata_moe_forward_host", "strata_moe_route",
+    "strata_moe_group", "strata_moe_experts_grouped", "strata_moe_dequant_export",
+    "strata_moe_enqueue_dense", "strata_moe_collect_dense",
+]
+
+SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
+
+
+class StrataMoeError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"strata_moe error {code}: {message}")
+        self.code = code
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [("hidden", C.c_uint32), ("intermediate", C.c_uint32), ("experts", C.c_uint32),
+                ("top_k", C.c_uint32), ("format", C.c_int32), ("score_kind", C.c_int32),
+                ("normalize", C.c_int32), ("norm_init", C.c_float), ("weight_scale", C.c_float),
+                ("output_scale", C.c_float), ("softcap", C.c_float),
+                ("shared_intermediate", C.c_uint32), ("expert_begin", C.c_uint32),
+                ("expert_count", C.c_uint32), ("max_tokens", C.c_uint32), ("max_pairs", C.c_uint32)]
+
+
+class Aux(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("ids", C.c_void_p), ("weights", C.c_void_p),
+                ("counts", C.c_void_p), ("offsets", C.c_void_p), ("perm", C.c_void_p)]
+
+
+class Stats(C.Structure):
+    _fields_ = [("forward_calls", C.c_uint64), ("kernel_launches", C.c_uint64),
+                ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
+                ("last_forward_ms", C.c_float)]
+
+
+def library_path():
+    return os.path.join(HERE, "libstrata_moe.so")
+
+
+def load_library():
+    """Loads the CUDA library; raises when it has not been built (there is no fallback)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not os.path.exists(path):
+        raise StrataMoeError(-5, f"{path} is missing: run `python -m strata_b200.build` (needs nvcc)")
+    lib = C.CDLL(path)
+    vp, u32, i32, f32 = C.c_void_p, C.c_uint32, C.c_int, C.c_float
+    lib.strata_moe_create.argtypes = [i32, vp, C.POINTER(vp)]
+    lib.strata_moe_destroy.argtypes = [vp]
+    lib.strata_moe_destroy.restype = None
+    lib.strata_moe_last_error.argtypes = [vp]
+    lib.strata_moe_last_error.restype = C.c_char_p
+    lib.strata_moe_synchronize.argtypes = [vp]
+    lib.strata_moe_get_stats.argtypes = [vp, C.POINTER(Stats)]
+    lib.strata_moe_set_timing.argtypes = [vp, i32]
+    lib.strata_moe_set_timing.restype = None
+    lib.strata_moe_get_phase_ms.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.strata_moe_layer_create.argtypes = [vp, C.POINTER(LayerDesc), C.POINTER(vp)]
+    lib.strata_moe_layer_destroy.argtypes = [vp]
+    lib.strata_moe_layer_destroy.restype = None
+    lib.strata_moe_set_router.argtypes = [vp, vp, vp, i32]
+    lib.strata_moe_set_expert.argtypes = [vp, u32, i32, vp, vp, f32, i32]
+    lib.strata_moe_set_shared.argtypes = [vp, i32, vp, i32]
+    lib.strata_moe_forward.argtypes = [vp, vp, u32, vp, C.POINTER(Aux)]
+    lib.strata_moe_forward_host.argtypes = [vp, vp, u32, vp]
+    lib.strata_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
+    lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp]
+    lib.strata_moe_experts_grouped.argtypes = [vp, vp, u32, vp, vp]
+    lib.strata_moe_dequant_export.argtypes = [vp, u32, i32, vp]
+    lib.strata_moe_enqueue_dense.argtypes = [vp, vp, u32, vp, vp, u32, i32]
+    lib.strata_moe_collect_dense.argtypes = [vp, vp, vp]
+    _LIB = lib
+    return lib
+
+
+def _ptr(t):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+class MoeContext:
+    """One per process and device (strata_moe_ctx)."""
+
+    def __init__(self, device=0, use_torch_stream=True):
+        self.lib = load_library()
+        if not torch.cuda.is_available():
+            raise StrataMoeError(-5, "no CUDA device: this library has no CPU path")
+        self.device = torch.device("cuda", device)
+        torch.cuda.set_device(self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream if use_torch_stream else 0
+        h = C.c_void_p()
+        rc = self.lib.strata_moe_create(device, C.c_void_p(stream), C.byref(h))
+        if rc != 0:
+            raise StrataMoeError(rc, "strata_moe_create failed (needs an sm_100 device)")
+        self.h = h
+
+    def check(self, rc):
+        if rc != 0:
+            raise StrataMoeError(rc, self.lib.strata_moe_last_error(self.h).decode())
+
+    def synchronize(self):
+        self.check(self.lib.strata_moe_synchronize(self.h))
+
+    def stats(self):
+        s = Stats()
+        self.check(self.lib.strata_moe_get_stats(self.h, C.byref(s)))
+        return s
+
+    def set_timing(self, on):
+        self.lib.strata_moe_set_timing(self.h, int(on))
+
+    PHASES = ("router_logits", "route", "group", "gather", "gate_up", "down", "shared", "combine")
+
+    def phase_ms(self):
+        out = (C.c_float * 8)()
+        self.check(self.lib.strata_moe_get_phase_ms(self.h, out))
+        return dict(zip(self.PHASES, [float(v) for v in out]))
+
+    def close(self):
+        if self.h:
+            self.lib.strata_moe_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class MoeLayer:
+    """One MoE layer (strata_moe_layer): resident weights + workspaces."""
+
+    def __init__(self, ctx, cfg, max_tokens=None, expert_begin=0, expert_count=None, max_pairs=0):
+        self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
+        d = LayerDesc()
+        d.hidden, d.intermediate, d.experts, d.top_k = cfg.H, cfg.I, cfg.E, cfg.k
+        d.format, d.score_kind, d.normalize = cfg.fmt, cfg.score_kind, int(cfg.normalize)
+        d.norm_init, d.weight_scale, d.output_scale, d.softcap = cfg.norm_init, cfg.weight_scale, cfg.output_scale, 0.0
+        d.shared_intermediate = cfg.I_shared
+        d.expert_begin = expert_begin
+        d.expert_count = cfg.E - expert_begin if expert_count is None else expert_count
+        d.max_tokens = cfg.T if max_tokens is None else max_tokens
+        d.max_pairs = max_pairs
+        self.desc = d
+        h = C.c_void_p()
+        ctx.check(self.lib.strata_moe_layer_create(ctx.h, C.byref(d), C.byref(h)))
+        self.h = h
+        self._keep = []
+
+    # ---- weights -------------------------------------------------------------------
+    def set_router(self, gate_bf16, bias=None):
+        src = SRC_DEVICE_BORROW if gate_bf16.is_cuda else SRC_HOST
+        self._keep += [gate_bf16, bias]
+        self.ctx.check(self.lib.strata_moe_set_router(self.h, _ptr(gate_bf16), _ptr(bias), src))
+
+    def set_expert(self, expert, role, packed, scales, global_scale=1.0):
+        src = SRC_DEVICE_BORROW if packed.is_cuda else SRC_HOST
+        self._keep += [packed, scales]
+        self.ctx.check(self.lib.strata_moe_set_expert(self.h, expert, role, _ptr(packed), _ptr(scales),
+                                                      float(global_scale), src))
+
+    def set_shared(self, role, w):
+        src = SRC_DEVICE_BORROW if w.is_cuda else SRC_HOST
+        self._keep.append(w)
+        self.ctx.check(self.lib.strata_moe_set_shared(self.h, role, _ptr(w), src))
+
+    def load_synth(self, layer):
+        """Registers every tensor of a synth.SynthLayer (borrowed in place when on the GPU)."""
+        self.set_router(layer.router_w, layer.bias)
+        for r, role in enumerate(synth.ROLES):
+            p, s = layer.packed[role], layer.scales[role]
+            for le in range(layer.expert_end - layer.expert_begin):
+                self.set_expert(layer.expert_begin + le, r, p[le], s[le], layer.global_scale(role))
+            if layer.shared:
+                self.set_shared(r, layer.shared[role])
+
+    # ---- compute -------------------------------------------------------------------
+    def forward(self, x, out=None, want_aux=False):
+        T = x.shape[0]
+        dev = x.device
+        if out is None:
+            out = torch.empty(T, self.cfg.H, dtype=torch.float32, device=dev)
+        aux_t = None
+        aux = None
+        if want_aux:
+            E, k = self.cfg.E, self.cfg.k
+            aux_t = dict(logits=torch.empty(T, E, dtype=torch.float32, device=dev),
+                         ids=torch.empty(T, k, dtype=torch.int32, device=dev),
+                         weights=torch.empty(T, k, dtype=torch.float32, device=dev),
+                         counts=torch.empty(E, dtype=torch.int32, device=dev),
+                         offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
+                         perm=torch.empty(T * k, dtype=torch.int32, device=dev))
+            aux = Aux(*[v.data_ptr() for v in aux_t.values()])
+        self.ctx.check(self.lib.strata_moe_forward(self.h, _ptr(x), T, _ptr(out),
+                                                   C.byref(aux) if aux is not None else None))
+        return (out, aux_t) if want_aux else out
+
+    def forward_host(self, x_host, out_host):
+        self.ctx.check(self.lib.strata_moe_forward_host(self.h, _ptr(x_host), x_host.shape[0], _ptr(out_host)))
+        return out_host
+
+    def route(self, x, want_logits=False):
+        T, dev = x.shape[0], x.device
+        ids = torch.empty(T, self.cfg.k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, self.cfg.k, dtype=torch.float32, device=dev)
+        logits = torch.empty(T, self.cfg.E, dtype=torch.float32, device=dev) if want_logits else None
+        self.ctx.check(self.lib.strata_moe_route(self.h, _ptr(x), T, _ptr(logits), _ptr(ids), _ptr(w)))
+        return (ids, w, logits) if want_logits else (ids, w)
+
+    def group(self, ids, expert_begin=0, n_experts=None):
+        n_experts = self.cfg.E if n_experts is None else n_experts
+        flat = ids.reshape(-1)
+        dev = ids.device
+        counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+        offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+        perm = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
+        self.ctx.check(self.lib.strata_moe_group(self.h, _ptr(flat), flat.numel(), expert_begin, n_experts,
+                                                 _ptr(counts), _ptr(offsets), _ptr(perm)))
+        return counts, offsets, perm
+
+    def experts_grouped(self, rows, offsets, y=None):
+        if y is None:
+            y = torch.empty(rows.shape[0], self.cfg.H, dtype=torch.float32, device=rows.device)
+        self.ctx.check(self.lib.strata_moe_experts_grouped(self.h, _ptr(rows), rows.shape[0], _ptr(offsets), _ptr(y)))
+        return y
+
+    def dequant_export(self, expert, role):
+        rows, cols = self.cfg.role_shape(synth.ROLES[role])
+        out = torch.empty(rows, cols, dtype=torch.float32)
+        self.ctx.check(self.lib.strata_moe_dequant_export(self.h, expert, role, _ptr(out)))
+        return out
+
+    def enqueue_dense(self, hidden_f32_host, experts, coefs, with_shared=False):
+        ex = torch.tensor(list(experts), dtype=torch.int32)
+        cf = torch.tensor(list(coefs), dtype=torch.float32)
+        self._dense_keep = (hidden_f32_host, ex, cf)
+        self.ctx.check(self.lib.strata_moe_enqueue_dense(self.h, _ptr(hidden_f32_host), hidden_f32_host.shape[0],
+                                                         _ptr(ex), _ptr(cf), len(ex), int(with_shared)))
+
+    def collect_dense(self, n_experts, rows, with_shared=False):
+        routed = torch.empty(n_experts, rows, self.cfg.H, dtype=torch.float32)
+        shared = torch.empty(rows, self.cfg.H, dtype=torch.float32) if with_shared else None
+        self.ctx.check(self.lib.strata_moe_collect_dense(self.h, _ptr(routed), _ptr(shared)))
+        return routed, shared
+
+    def close(self):
+        if self.h:
+            self.lib.strata_moe_layer_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

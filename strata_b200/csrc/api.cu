@@ -1,0 +1,836 @@
+// Host side of the C ABI declared in include/strata_moe.h: contexts, resident weights,
+// workspaces and the launch sequence of one MoE layer.
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+using namespace smoe;
+
+namespace smoe {
+// prefill.cu (tcgen05 grouped GEMM path); returns false when the shape is not supported by it.
+bool prefill_supported(int fmt, uint32_t H, uint32_t I);
+struct PrefillArgs {
+    int fmt;
+    uint32_t H, I, n_groups, pairs;
+    const uint32_t* offsets;
+    WeightTable gate, up, down;
+    const __nv_bfloat16* x;   // [pairs, H] natural layout, group order
+    __nv_bfloat16* act;       // [pairs, I] natural layout
+    float* y;                 // [pairs, H]
+    uint32_t* tile_table;     // scratch
+    uint32_t* status;
+};
+size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
+int launch_prefill(const PrefillArgs& a, cudaStream_t s, cudaEvent_t mid);
+}  // namespace smoe
+
+struct strata_moe_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    std::string err;
+    uint32_t* d_status = nullptr;
+    uint32_t* h_status = nullptr;  // pinned
+    strata_moe_stats stats{};
+    bool timing = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaEvent_t pev[STRATA_MOE_PHASES + 1] = {};  // phase boundaries of the last timed forward
+    bool pev_valid = false;
+    unsigned long long launches_at_create = 0;
+};
+
+struct DeviceTable {
+    std::vector<const uint8_t*> packed, scales;
+    std::vector<float> global;
+    const uint8_t** d_packed = nullptr;
+    const uint8_t** d_scales = nullptr;
+    float* d_global = nullptr;
+};
+
+struct strata_moe_layer {
+    strata_moe_ctx* ctx = nullptr;
+    strata_moe_layer_desc d{};
+    uint32_t max_pairs = 0;
+    __nv_bfloat16* router = nullptr;
+    float* bias = nullptr;
+    bool has_bias = false;
+    DeviceTable tab[3];
+    bool tables_dirty = true;
+    __nv_bfloat16* shared_w[3] = {nullptr, nullptr, nullptr};
+    const uint8_t** d_shared_ptr[3] = {nullptr, nullptr, nullptr};  // 1-entry tables
+    std::vector<void*> owned;
+    // workspaces
+    float* logits = nullptr;
+    uint32_t *ids = nullptr, *counts = nullptr, *offsets = nullptr, *perm = nullptr, *inv = nullptr;
+    uint32_t *active = nullptr, *n_active = nullptr;
+    float* weights = nullptr;
+    void* group_scratch = nullptr;
+    __nv_bfloat16 *xg = nullptr, *xg_lo = nullptr, *act_hi = nullptr, *act_lo = nullptr;
+    float* y = nullptr;
+    __nv_bfloat16 *sh_act_hi = nullptr, *sh_act_lo = nullptr;
+    float* sh_y = nullptr;
+    __nv_bfloat16* x_stage = nullptr;
+    float* out_stage = nullptr;
+    void* prefill_scratch = nullptr;
+    float* one_global = nullptr;  // device float 1.0 for the shared expert table
+    // dense command state
+    bool dense_in_flight = false;
+    uint32_t dense_rows = 0, dense_n = 0;
+    bool dense_shared = false;
+    float* dense_hidden = nullptr;  // device fp32 [rows, H]
+    float* dense_coef = nullptr;
+    const uint8_t** dense_ptrs = nullptr;  // device: 6 * n pointers
+    float* dense_globals = nullptr;        // device: 3 * n
+    void* dense_pinned = nullptr;          // host staging for the tables above
+};
+
+namespace {
+
+int fail(strata_moe_ctx* c, int code, const std::string& msg) {
+    if (c) c->err = msg;
+    return code;
+}
+
+// phase boundary i of a timed forward (no-op unless timing is on)
+void mark(strata_moe_ctx* c, int i) {
+    if (c->timing) cudaEventRecord(c->pev[i], c->stream);
+}
+
+#define CK(call)                                                                             \
+    do {                                                                                     \
+        cudaError_t e_ = (call);                                                             \
+        if (e_ != cudaSuccess)                                                               \
+            return fail(ctx, STRATA_MOE_E_CUDA,                                              \
+                        std::string(#call) + ": " + cudaGetErrorString(e_));                 \
+    } while (0)
+
+template <typename T>
+cudaError_t dalloc(strata_moe_layer* L, T** p, size_t n) {
+    void* v = nullptr;
+    cudaError_t e = cudaMalloc(&v, n ? n * sizeof(T) : sizeof(T));
+    if (e == cudaSuccess) {
+        L->owned.push_back(v);
+        *p = static_cast<T*>(v);
+    }
+    return e;
+}
+
+size_t packed_bytes(uint32_t rows, uint32_t cols) { return (size_t)rows * cols / 2; }
+size_t scale_bytes(int fmt, uint32_t rows, uint32_t cols) {
+    if (fmt == STRATA_MOE_FMT_MXFP4) return (size_t)rows * cols / 32;
+    if (fmt == STRATA_MOE_FMT_NVFP4) return (size_t)rows * cols / 16;
+    return (size_t)rows * cols / 128 * 2;
+}
+
+int sync_tables(strata_moe_layer* L) {
+    strata_moe_ctx* ctx = L->ctx;
+    if (!L->tables_dirty) return 0;
+    const uint32_t n = L->d.expert_count;
+    for (int r = 0; r < 3; ++r) {
+        DeviceTable& t = L->tab[r];
+        CK(cudaMemcpyAsync(t.d_packed, t.packed.data(), n * sizeof(void*), cudaMemcpyHostToDevice,
+                           ctx->stream));
+        CK(cudaMemcpyAsync(t.d_scales, t.scales.data(), n * sizeof(void*), cudaMemcpyHostToDevice,
+                           ctx->stream));
+        CK(cudaMemcpyAsync(t.d_global, t.global.data(), n * sizeof(float), cudaMemcpyHostToDevice,
+                           ctx->stream));
+    }
+    CK(cudaStreamSynchronize(ctx->stream));  // the host vectors may change after this returns
+    L->tables_dirty = false;
+    return 0;
+}
+
+WeightTable wt(const DeviceTable& t) {
+    WeightTable w;
+    w.packed = t.d_packed;
+    w.scales = t.d_scales;
+    w.global_scale = t.d_global;
+    return w;
+}
+
+bool all_registered(const strata_moe_layer* L, std::string* why) {
+    for (int r = 0; r < 3; ++r)
+        for (uint32_t e = 0; e < L->d.expert_count; ++e)
+            if (!L->tab[r].packed[e] || !L->tab[r].scales[e]) {
+                *why = "expert " + std::to_string(L->d.expert_begin + e) + " role " + std::to_string(r) +
+                       " has no weights";
+                return false;
+            }
+    if (!L->router) {
+        *why = "router weights were never set";
+        return false;
+    }
+    if (L->d.shared_intermediate)
+        for (int r = 0; r < 3; ++r)
+            if (!L->shared_w[r]) {
+                *why = "shared expert weights were never set";
+                return false;
+            }
+    return true;
+}
+
+// rows-per-expert threshold between the weight-streaming path and the tensor-core tile path
+bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
+    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) return false;
+    return (uint64_t)pairs >= (uint64_t)n_groups * 24u;
+}
+
+// Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
+// If x_kperm is non-null it already holds the K-permuted copy.
+int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
+                uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
+                const uint32_t* n_active, uint32_t max_rows, float* y) {
+    strata_moe_ctx* ctx = L->ctx;
+    cudaStream_t s = ctx->stream;
+    if (pairs == 0) return 0;
+    if (use_prefill(L, pairs, n_groups)) {
+        launch_gather_rows_plain(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
+        mark(ctx, 4);
+        PrefillArgs p{};
+        p.fmt = L->d.format;
+        p.H = L->d.hidden;
+        p.I = L->d.intermediate;
+        p.n_groups = n_groups;
+        p.pairs = pairs;
+        p.offsets = offsets;
+        p.gate = wt(L->tab[0]);
+        p.up = wt(L->tab[1]);
+        p.down = wt(L->tab[2]);
+        p.x = L->xg;
+        p.act = L->act_hi;
+        p.y = y;
+        p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
+        p.status = ctx->d_status;
+        if (launch_prefill(p, s, ctx->timing ? ctx->pev[5] : nullptr) != 0)
+            return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
+        mark(ctx, 6);
+        CK(cudaGetLastError());
+        return 0;
+    }
+    launch_gather_rows_kperm(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
+    mark(ctx, 4);
+    DecodeArgs a{};
+    a.fmt = L->d.format;
+    a.H = L->d.hidden;
+    a.I = L->d.intermediate;
+    a.n_groups = n_groups;
+    a.offsets = offsets;
+    a.active_list = active;
+    a.n_active = n_active;
+    a.max_rows_per_group = max_rows;
+    a.gate = wt(L->tab[0]);
+    a.up = wt(L->tab[1]);
+    a.down = wt(L->tab[2]);
+    a.x_hi = L->xg;
+    a.x_lo = nullptr;
+    a.coef = nullptr;
+    a.act_hi = L->act_hi;
+    a.act_lo = L->act_lo;
+    a.y = y;
+    a.status = ctx->d_status;
+    launch_decode_gate_up(a, s);
+    mark(ctx, 5);
+    launch_decode_down(a, s);
+    mark(ctx, 6);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// shared expert over T rows in natural order; offsets table = {0, T} in L->offsets scratch tail
+int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16* x_lo, uint32_t T,
+               const uint32_t* offsets2) {
+    strata_moe_ctx* ctx = L->ctx;
+    DecodeArgs a{};
+    a.fmt = 3;
+    a.H = L->d.hidden;
+    a.I = L->d.shared_intermediate;
+    a.n_groups = 1;
+    a.offsets = offsets2;
+    a.max_rows_per_group = T;
+    WeightTable g{L->d_shared_ptr[0], L->d_shared_ptr[0], L->one_global};
+    WeightTable u{L->d_shared_ptr[1], L->d_shared_ptr[1], L->one_global};
+    WeightTable dn{L->d_shared_ptr[2], L->d_shared_ptr[2], L->one_global};
+    a.gate = g;
+    a.up = u;
+    a.down = dn;
+    a.x_hi = x;
+    a.x_lo = x_lo;
+    a.act_hi = L->sh_act_hi;
+    a.act_lo = L->sh_act_lo;
+    a.y = L->sh_y;
+    a.status = ctx->d_status;
+    launch_decode_gate_up(a, ctx->stream);
+    launch_decode_down(a, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+__global__ void set_pair_kernel(uint32_t* p, uint32_t a, uint32_t b) {
+    p[0] = a;
+    p[1] = b;
+}
+__global__ void uniform_offsets_kernel(uint32_t* p, uint32_t n, uint32_t rows) {
+    for (uint32_t i = threadIdx.x; i <= n; i += blockDim.x) p[i] = i * rows;
+}
+__global__ void split_f32_kernel(const float* x, size_t n, __nv_bfloat16* hi, __nv_bfloat16* lo) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const __nv_bfloat16 h = __float2bfloat16_rn(x[i]);
+        hi[i] = h;
+        lo[i] = __float2bfloat16_rn(x[i] - __bfloat162float(h));
+    }
+}
+
+}  // namespace
+
+// =========================================================================================
+extern "C" {
+
+int strata_moe_create(int device, void* stream, strata_moe_ctx** out) {
+    if (!out) return STRATA_MOE_E_INVALID;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0 || device < 0 || device >= n)
+        return STRATA_MOE_E_NO_DEVICE;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return STRATA_MOE_E_NO_DEVICE;
+    if (prop.major != 10) return STRATA_MOE_E_NO_DEVICE;  // kernels are built for sm_100a only
+    strata_moe_ctx* ctx = new (std::nothrow) strata_moe_ctx();
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    ctx->device = device;
+    if (cudaSetDevice(device) != cudaSuccess) { delete ctx; return STRATA_MOE_E_CUDA; }
+    if (stream) {
+        ctx->stream = static_cast<cudaStream_t>(stream);
+    } else {
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+            delete ctx;
+            return STRATA_MOE_E_CUDA;
+        }
+        ctx->own_stream = true;
+    }
+    if (cudaMalloc(&ctx->d_status, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(ctx->d_status, 0, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMallocHost(&ctx->h_status, sizeof(uint32_t)) != cudaSuccess ||
+        cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess) {
+        strata_moe_destroy(ctx);
+        return STRATA_MOE_E_CUDA;
+    }
+    for (int i = 0; i <= STRATA_MOE_PHASES; ++i)
+        if (cudaEventCreate(&ctx->pev[i]) != cudaSuccess) {
+            strata_moe_destroy(ctx);
+            return STRATA_MOE_E_CUDA;
+        }
+    ctx->launches_at_create = g_kernel_launches;
+    *out = ctx;
+    return 0;
+}
+
+void strata_moe_destroy(strata_moe_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+    if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    for (int i = 0; i <= STRATA_MOE_PHASES; ++i)
+        if (ctx->pev[i]) cudaEventDestroy(ctx->pev[i]);
+    if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+
+const char* strata_moe_last_error(const strata_moe_ctx* ctx) { return ctx ? ctx->err.c_str() : "no context"; }
+
+int strata_moe_synchronize(strata_moe_ctx* ctx) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    CK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaMemsetAsync(ctx->d_status, 0, sizeof(uint32_t), ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    const uint32_t st = *ctx->h_status;
+    if (st) {
+        std::string m = "device status:";
+        if (st & kStatusNonFiniteLogit) m += " non-finite router logit or bias;";
+        if (st & kStatusBadNormaliser) m += " router normaliser not positive;";
+        if (st & kStatusNonFiniteOutput) m += " non-finite expert output;";
+        if (st & kStatusWaitTimeout) m += " bounded wait timed out;";
+        if (st & kStatusBadGroup) m += " inconsistent group table;";
+        return fail(ctx, STRATA_MOE_E_NUMERIC, m);
+    }
+    return 0;
+}
+
+int strata_moe_get_stats(const strata_moe_ctx* ctx, strata_moe_stats* out) {
+    if (!ctx || !out) return STRATA_MOE_E_INVALID;
+    *out = ctx->stats;
+    out->kernel_launches = g_kernel_launches - ctx->launches_at_create;
+    return 0;
+}
+
+void strata_moe_set_timing(strata_moe_ctx* ctx, int enabled) {
+    if (ctx) ctx->timing = enabled != 0;
+}
+
+int strata_moe_get_phase_ms(strata_moe_ctx* ctx, float* out) {
+    if (!ctx || !out) return STRATA_MOE_E_INVALID;
+    if (!ctx->pev_valid) return fail(ctx, STRATA_MOE_E_INVALID, "no timed forward has completed");
+    for (int i = 0; i < STRATA_MOE_PHASES; ++i) CK(cudaEventElapsedTime(&out[i], ctx->pev[i], ctx->pev[i + 1]));
+    return 0;
+}
+
+int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* desc, strata_moe_layer** out) {
+    if (!ctx || !desc || !out) return STRATA_MOE_E_INVALID;
+    *out = nullptr;
+    const strata_moe_layer_desc& d = *desc;
+    if (d.hidden == 0 || d.hidden % 128 || d.intermediate == 0 || d.intermediate % 128)
+        return fail(ctx, STRATA_MOE_E_INVALID, "hidden and intermediate must be positive multiples of 128");
+    if (d.experts == 0 || d.experts > 1024 || d.top_k == 0 || d.top_k > 32 || d.top_k > d.experts)
+        return fail(ctx, STRATA_MOE_E_INVALID, "experts must be in 1..1024 and top_k in 1..min(32, experts)");
+    if (d.format < 0 || d.format > STRATA_MOE_FMT_INT4G128)
+        return fail(ctx, STRATA_MOE_E_INVALID, "unknown weight format");
+    if (d.score_kind < 0 || d.score_kind > STRATA_MOE_SCORE_SQRTSOFTPLUS)
+        return fail(ctx, STRATA_MOE_E_INVALID, "unknown router score kind");
+    if (d.expert_count == 0 || (uint64_t)d.expert_begin + d.expert_count > d.experts)
+        return fail(ctx, STRATA_MOE_E_INVALID, "resident expert range is outside the layer");
+    if (d.shared_intermediate % 128)
+        return fail(ctx, STRATA_MOE_E_INVALID, "shared intermediate must be a multiple of 128");
+    if (d.max_tokens == 0) return fail(ctx, STRATA_MOE_E_INVALID, "max_tokens must be positive");
+    if (!(d.weight_scale == d.weight_scale) || !(d.output_scale == d.output_scale))
+        return fail(ctx, STRATA_MOE_E_INVALID, "router scales must be finite");
+    CK(cudaSetDevice(ctx->device));
+    strata_moe_layer* L = new (std::nothrow) strata_moe_layer();
+    if (!L) return fail(ctx, STRATA_MOE_E_INVALID, "out of host memory");
+    L->ctx = ctx;
+    L->d = d;
+    const uint64_t mp = d.max_pairs ? d.max_pairs : (uint64_t)d.max_tokens * d.top_k;
+    if (mp > 0x7FFFFFFFull) { delete L; return fail(ctx, STRATA_MOE_E_INVALID, "max_pairs too large"); }
+    L->max_pairs = (uint32_t)mp;
+    const uint32_t P = L->max_pairs, T = d.max_tokens, H = d.hidden, I = d.intermediate, E = d.experts;
+    const uint32_t n = d.expert_count;
+    cudaError_t e = cudaSuccess;
+    auto A = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
+    for (int r = 0; r < 3; ++r) {
+        DeviceTable& t = L->tab[r];
+        t.packed.assign(n, nullptr);
+        t.scales.assign(n, nullptr);
+        t.global.assign(n, 1.0f);
+        A(dalloc(L, &t.d_packed, n));
+        A(dalloc(L, &t.d_scales, n));
+        A(dalloc(L, &t.d_global, n));
+        A(dalloc(L, &L->d_shared_ptr[r], 1));
+    }
+    A(dalloc(L, &L->logits, (size_t)T * E));
+    A(dalloc(L, &L->ids, (size_t)T * d.top_k));
+    A(dalloc(L, &L->weights, (size_t)T * d.top_k));
+    A(dalloc(L, &L->counts, (size_t)E));
+    A(dalloc(L, &L->offsets, (size_t)E + 1 + 2 + 12));
+    A(dalloc(L, &L->perm, (size_t)P));
+    A(dalloc(L, &L->inv, (size_t)T * d.top_k > P ? (size_t)T * d.top_k : (size_t)P));
+    A(dalloc(L, &L->active, (size_t)E));
+    A(dalloc(L, &L->n_active, 1));
+    {
+        void* gs = nullptr;
+        size_t gb = group_scratch_bytes((uint32_t)((size_t)T * d.top_k > P ? (size_t)T * d.top_k : P), E);
+        A(cudaMalloc(&gs, gb));
+        if (gs) L->owned.push_back(gs);
+        L->group_scratch = gs;
+        void* ps = nullptr;
+        A(cudaMalloc(&ps, prefill_scratch_bytes(n, P) + 16));
+        if (ps) L->owned.push_back(ps);
+        L->prefill_scratch = ps;
+    }
+    A(dalloc(L, &L->xg, (size_t)P * H));
+    A(dalloc(L, &L->xg_lo, 1));
+    A(dalloc(L, &L->act_hi, (size_t)P * I));
+    A(dalloc(L, &L->act_lo, (size_t)P * I));
+    A(dalloc(L, &L->y, (size_t)P * H));
+    A(dalloc(L, &L->one_global, 1));
+    if (d.shared_intermediate) {
+        A(dalloc(L, &L->sh_act_hi, (size_t)T * d.shared_intermediate));
+        A(dalloc(L, &L->sh_act_lo, (size_t)T * d.shared_intermediate));
+        A(dalloc(L, &L->sh_y, (size_t)T * H));
+    }
+    A(dalloc(L, &L->x_stage, (size_t)T * H));
+    A(dalloc(L, &L->out_stage, (size_t)T * H));
+    if (e == cudaSuccess) {
+        const float one = 1.0f;
+        e = cudaMemcpy(L->one_global, &one, sizeof(float), cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) {
+        strata_moe_layer_destroy(L);
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("layer allocation: ") + cudaGetErrorString(e));
+    }
+    *out = L;
+    return 0;
+}
+
+void strata_moe_layer_destroy(strata_moe_layer* L) {
+    if (!L) return;
+    cudaSetDevice(L->ctx->device);
+    cudaStreamSynchronize(L->ctx->stream);
+    for (void* p : L->owned) cudaFree(p);
+    if (L->dense_pinned) cudaFreeHost(L->dense_pinned);
+    delete L;
+}
+
+static int put(strata_moe_layer* L, const void* src, size_t bytes, int source, const void** dev) {
+    strata_moe_ctx* ctx = L->ctx;
+    if (!src) return fail(ctx, STRATA_MOE_E_INVALID, "null weight pointer");
+    if (source == STRATA_MOE_SRC_DEVICE_BORROW) {
+        *dev = src;
+        return 0;
+    }
+    if (source != STRATA_MOE_SRC_HOST && source != STRATA_MOE_SRC_DEVICE_COPY)
+        return fail(ctx, STRATA_MOE_E_INVALID, "unknown source kind");
+    void* p = nullptr;
+    // 256-byte granularity like the reference's weight arena (kernels/cuda/backend.cu:4889-4890)
+    CK(cudaMalloc(&p, (bytes + 255) / 256 * 256));
+    L->owned.push_back(p);
+    CK(cudaMemcpyAsync(p, src, bytes,
+                       source == STRATA_MOE_SRC_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
+                       ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (source == STRATA_MOE_SRC_HOST) ctx->stats.h2d_bytes += bytes;
+    ctx->stats.weight_bytes += bytes;
+    *dev = p;
+    return 0;
+}
+
+int strata_moe_set_router(strata_moe_layer* L, const void* gate_bf16, const float* bias, int source) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    CK(cudaSetDevice(ctx->device));
+    const void* p = nullptr;
+    int rc = put(L, gate_bf16, (size_t)L->d.experts * L->d.hidden * 2, source, &p);
+    if (rc) return rc;
+    L->router = (__nv_bfloat16*)p;
+    L->has_bias = bias != nullptr;
+    if (bias) {
+        rc = put(L, bias, (size_t)L->d.experts * 4, source, &p);
+        if (rc) return rc;
+        L->bias = (float*)p;
+    } else {
+        L->bias = nullptr;
+    }
+    return 0;
+}
+
+int strata_moe_set_expert(strata_moe_layer* L, uint32_t expert, int role, const void* packed,
+                          const void* scales, float global_scale, int source) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (role < 0 || role > 2) return fail(ctx, STRATA_MOE_E_INVALID, "role must be gate, up or down");
+    if (expert < L->d.expert_begin || expert >= L->d.expert_begin + L->d.expert_count)
+        return fail(ctx, STRATA_MOE_E_INVALID, "expert is not resident on this device");
+    if (L->d.format == STRATA_MOE_FMT_NVFP4 && !(global_scale > 0.0f && global_scale < 3.0e38f))
+        return fail(ctx, STRATA_MOE_E_INVALID, "NVFP4 global scale must be finite and positive");
+    if (((uintptr_t)packed & 15u) && source == STRATA_MOE_SRC_DEVICE_BORROW)
+        return fail(ctx, STRATA_MOE_E_INVALID, "borrowed weights must be 16-byte aligned");
+    CK(cudaSetDevice(ctx->device));
+    const uint32_t rows = role == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
+    const uint32_t cols = role == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+    const void *pp = nullptr, *ps = nullptr;
+    int rc = put(L, packed, packed_bytes(rows, cols), source, &pp);
+    if (rc) return rc;
+    rc = put(L, scales, scale_bytes(L->d.format, rows, cols), source, &ps);
+    if (rc) return rc;
+    const uint32_t le = expert - L->d.expert_begin;
+    L->tab[role].packed[le] = (const uint8_t*)pp;
+    L->tab[role].scales[le] = (const uint8_t*)ps;
+    L->tab[role].global[le] = L->d.format == STRATA_MOE_FMT_NVFP4 ? global_scale : 1.0f;
+    L->tables_dirty = true;
+    return 0;
+}
+
+int strata_moe_set_shared(strata_moe_layer* L, int role, const void* w, int source) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (role < 0 || role > 2) return fail(ctx, STRATA_MOE_E_INVALID, "role must be gate, up or down");
+    if (!L->d.shared_intermediate) return fail(ctx, STRATA_MOE_E_INVALID, "layer has no shared expert");
+    CK(cudaSetDevice(ctx->device));
+    const void* p = nullptr;
+    int rc = put(L, w, (size_t)L->d.shared_intermediate * L->d.hidden * 2, source, &p);
+    if (rc) return rc;
+    L->shared_w[role] = (__nv_bfloat16*)p;
+    CK(cudaMemcpy(L->d_shared_ptr[role], &p, sizeof(void*), cudaMemcpyHostToDevice));
+    return 0;
+}
+
+int strata_moe_route(strata_moe_layer* L, const void* x, uint32_t T, float* logits, uint32_t* ids,
+                     float* weights) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!x || !ids || !weights) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (!L->router) return fail(ctx, STRATA_MOE_E_INVALID, "router weights were never set");
+    CK(cudaSetDevice(ctx->device));
+    float* lg = logits ? logits : L->logits;
+    launch_router_logits((const __nv_bfloat16*)x, L->router, T, L->d.hidden, L->d.experts, lg, ctx->stream);
+    RouterParams p{L->d.experts, L->d.top_k, L->d.score_kind, L->d.normalize, L->d.norm_init,
+                   L->d.weight_scale, L->d.softcap};
+    launch_route(p, lg, L->bias, T, ids, weights, ctx->d_status, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_group(strata_moe_layer* L, const uint32_t* ids, uint32_t pairs, uint32_t expert_begin,
+                     uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!ids || !counts || !offsets || !perm) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (n_experts == 0 || n_experts > L->d.experts) return fail(ctx, STRATA_MOE_E_INVALID, "bad expert range");
+    if ((uint64_t)pairs > (uint64_t)L->d.max_tokens * L->d.top_k && pairs > L->max_pairs)
+        return fail(ctx, STRATA_MOE_E_INVALID, "pairs exceed the layer's workspace");
+    CK(cudaSetDevice(ctx->device));
+    launch_group(ids, pairs, expert_begin, n_experts, counts, offsets, perm, nullptr, nullptr, nullptr,
+                 L->group_scratch, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_experts_grouped(strata_moe_layer* L, const void* rows, uint32_t pairs,
+                               const uint32_t* offsets, float* y) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!rows || !offsets || !y) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (pairs > L->max_pairs) return fail(ctx, STRATA_MOE_E_INVALID, "pairs exceed max_pairs");
+    std::string why;
+    for (int r = 0; r < 3; ++r)
+        for (uint32_t e = 0; e < L->d.expert_count; ++e)
+            if (!L->tab[r].packed[e]) return fail(ctx, STRATA_MOE_E_INVALID, "an expert has no weights");
+    CK(cudaSetDevice(ctx->device));
+    int rc = sync_tables(L);
+    if (rc) return rc;
+    return run_experts(L, (const __nv_bfloat16*)rows, nullptr, 1, pairs, L->d.expert_count, offsets,
+                       nullptr, nullptr, pairs, y);
+}
+
+int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* out,
+                       const strata_moe_aux* aux) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!x || !out) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (L->d.expert_count != L->d.experts)
+        return fail(ctx, STRATA_MOE_E_INVALID, "forward needs every expert resident; use the stage calls for expert parallelism");
+    if (L->dense_in_flight) return fail(ctx, STRATA_MOE_E_BUSY, "a dense command is in flight");
+    std::string why;
+    if (!all_registered(L, &why)) return fail(ctx, STRATA_MOE_E_INVALID, why);
+    if (T == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    int rc = sync_tables(L);
+    if (rc) return rc;
+    cudaStream_t s = ctx->stream;
+    const strata_moe_layer_desc& d = L->d;
+    if (ctx->timing) CK(cudaEventRecord(ctx->ev0, s));
+    mark(ctx, 0);
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+    float* lg = (aux && aux->logits) ? aux->logits : L->logits;
+    uint32_t* ids = (aux && aux->ids) ? aux->ids : L->ids;
+    float* w = (aux && aux->weights) ? aux->weights : L->weights;
+    uint32_t* counts = (aux && aux->counts) ? aux->counts : L->counts;
+    uint32_t* offsets = (aux && aux->offsets) ? aux->offsets : L->offsets;
+    uint32_t* perm = (aux && aux->perm) ? aux->perm : L->perm;
+    const uint32_t P = T * d.top_k;
+    launch_router_logits(xb, L->router, T, d.hidden, d.experts, lg, s);
+    mark(ctx, 1);
+    RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
+    launch_route(rp, lg, L->bias, T, ids, w, ctx->d_status, s);
+    mark(ctx, 2);
+    launch_group(ids, P, 0, d.experts, counts, offsets, perm, L->inv, L->active, L->n_active,
+                 L->group_scratch, s);
+    mark(ctx, 3);
+    rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y);
+    if (rc) return rc;
+    const float* shared = nullptr;
+    if (d.shared_intermediate) {
+        uint32_t* off2 = L->offsets + d.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, T);
+        ++g_kernel_launches;
+        rc = run_shared(L, xb, nullptr, T, off2);
+        if (rc) return rc;
+        shared = L->sh_y;
+    }
+    mark(ctx, 7);
+    launch_combine(L->y, L->inv, w, shared, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s);
+    mark(ctx, 8);
+    CK(cudaGetLastError());
+    if (ctx->timing) {
+        CK(cudaEventRecord(ctx->ev1, s));
+        CK(cudaEventSynchronize(ctx->ev1));
+        CK(cudaEventElapsedTime(&ctx->stats.last_forward_ms, ctx->ev0, ctx->ev1));
+        ctx->pev_valid = true;
+    }
+    ctx->stats.forward_calls++;
+    return 0;
+}
+
+int strata_moe_forward_host(strata_moe_layer* L, const void* x_host, uint32_t T, float* out_host) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!x_host || !out_host) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (T == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    const size_t in_bytes = (size_t)T * L->d.hidden * 2, out_bytes = (size_t)T * L->d.hidden * 4;
+    CK(cudaMemcpyAsync(L->x_stage, x_host, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = strata_moe_forward(L, L->x_stage, T, L->out_stage, nullptr);
+    if (rc) return rc;
+    CK(cudaMemcpyAsync(out_host, L->out_stage, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->stats.h2d_bytes += in_bytes;
+    ctx->stats.d2h_bytes += out_bytes;
+    return strata_moe_synchronize(ctx);
+}
+
+int strata_moe_dequant_export(strata_moe_layer* L, uint32_t expert, int role, float* out_host) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!out_host || role < 0 || role > 2) return fail(ctx, STRATA_MOE_E_INVALID, "bad argument");
+    if (expert < L->d.expert_begin || expert >= L->d.expert_begin + L->d.expert_count)
+        return fail(ctx, STRATA_MOE_E_INVALID, "expert is not resident on this device");
+    const uint32_t le = expert - L->d.expert_begin;
+    if (!L->tab[role].packed[le]) return fail(ctx, STRATA_MOE_E_INVALID, "expert has no weights");
+    CK(cudaSetDevice(ctx->device));
+    const uint32_t rows = role == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
+    const uint32_t cols = role == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+    float* tmp = nullptr;
+    CK(cudaMalloc(&tmp, (size_t)rows * cols * 4));
+    launch_dequant_export(L->d.format, L->tab[role].packed[le], L->tab[role].scales[le],
+                          L->tab[role].global[le], rows, cols, tmp, ctx->stream);
+    cudaError_t e = cudaMemcpyAsync(out_host, tmp, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    cudaFree(tmp);
+    if (e != cudaSuccess) return fail(ctx, STRATA_MOE_E_CUDA, cudaGetErrorString(e));
+    return 0;
+}
+
+int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint32_t rows,
+                             const uint32_t* experts, const float* coefficients, uint32_t n, int with_shared) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    const strata_moe_layer_desc& d = L->d;
+    if (L->dense_in_flight)
+        return fail(ctx, STRATA_MOE_E_BUSY, "a MoE command is already in flight on this layer");
+    if (!hidden_host || rows == 0) return fail(ctx, STRATA_MOE_E_INVALID, "hidden rows are required");
+    if (n == 0 && !with_shared) return fail(ctx, STRATA_MOE_E_INVALID, "command has no experts");
+    if (n && (!experts || !coefficients)) return fail(ctx, STRATA_MOE_E_INVALID, "null expert list");
+    if ((uint64_t)n * rows > L->max_pairs) return fail(ctx, STRATA_MOE_E_INVALID, "experts * rows exceed max_pairs");
+    if (rows > d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "rows exceed max_tokens");
+    if (with_shared && !d.shared_intermediate) return fail(ctx, STRATA_MOE_E_INVALID, "layer has no shared expert");
+    for (uint32_t i = 0; i < n; ++i) {
+        if (experts[i] < d.expert_begin || experts[i] >= d.expert_begin + d.expert_count)
+            return fail(ctx, STRATA_MOE_E_INVALID, "expert is not resident on this device");
+        const uint32_t le = experts[i] - d.expert_begin;
+        for (int r = 0; r < 3; ++r)
+            if (!L->tab[r].packed[le]) return fail(ctx, STRATA_MOE_E_INVALID, "expert has no weights");
+        if (!(coefficients[i] == coefficients[i]) || !(fabsf(coefficients[i]) <= 3.0e38f))
+            return fail(ctx, STRATA_MOE_E_INVALID, "coefficient is not finite");
+        if (d.format != STRATA_MOE_FMT_INT4G128 && coefficients[i] != 1.0f)
+            return fail(ctx, STRATA_MOE_E_INVALID, "only INT4 experts fold a coefficient; pass 1.0");
+    }
+    CK(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    const uint32_t H = d.hidden;
+    if (!L->dense_hidden) {
+        CK(dalloc(L, &L->dense_hidden, (size_t)d.max_tokens * H));
+        CK(dalloc(L, &L->dense_coef, (size_t)L->max_pairs));
+        CK(dalloc(L, &L->dense_ptrs, (size_t)6 * d.expert_count));
+        CK(dalloc(L, &L->dense_globals, (size_t)3 * d.expert_count));
+        CK(dalloc(L, &L->xg_lo, (size_t)L->max_pairs * H));
+        CK(cudaMallocHost(&L->dense_pinned, (size_t)d.expert_count * (6 * sizeof(void*) + 3 * sizeof(float)) +
+                                                (size_t)L->max_pairs * sizeof(float)));
+    }
+    CK(cudaMemcpyAsync(L->dense_hidden, hidden_host, (size_t)rows * H * 4, cudaMemcpyHostToDevice, s));
+    ctx->stats.h2d_bytes += (size_t)rows * H * 4;
+    const uint32_t ne = d.expert_count;
+    const uint8_t** hp = static_cast<const uint8_t**>(L->dense_pinned);
+    float* hg = reinterpret_cast<float*>(hp + 6 * ne);
+    float* hc = hg + 3 * ne;
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint32_t le = experts[i] - d.expert_begin;
+        for (int r = 0; r < 3; ++r) {
+            hp[(2 * r) * ne + i] = L->tab[r].packed[le];
+            hp[(2 * r + 1) * ne + i] = L->tab[r].scales[le];
+            hg[r * ne + i] = L->tab[r].global[le];
+        }
+        for (uint32_t rrow = 0; rrow < rows; ++rrow) hc[(size_t)i * rows + rrow] = coefficients[i];
+    }
+    uint32_t* off = L->offsets;
+    if (n) {
+        CK(cudaMemcpyAsync(L->dense_ptrs, hp, 6 * ne * sizeof(void*), cudaMemcpyHostToDevice, s));
+        CK(cudaMemcpyAsync(L->dense_globals, hg, 3 * ne * sizeof(float), cudaMemcpyHostToDevice, s));
+        CK(cudaMemcpyAsync(L->dense_coef, hc, (size_t)n * rows * sizeof(float), cudaMemcpyHostToDevice, s));
+        uniform_offsets_kernel<<<1, 256, 0, s>>>(off, n, rows);
+        ++g_kernel_launches;
+        launch_gather_rows_kperm_f32(L->dense_hidden, rows, n, H, L->xg, L->xg_lo, s);
+        DecodeArgs a{};
+        a.fmt = d.format;
+        a.H = H;
+        a.I = d.intermediate;
+        a.n_groups = n;
+        a.offsets = off;
+        a.max_rows_per_group = rows;
+        a.gate = WeightTable{L->dense_ptrs + 0 * ne, L->dense_ptrs + 1 * ne, L->dense_globals + 0 * ne};
+        a.up = WeightTable{L->dense_ptrs + 2 * ne, L->dense_ptrs + 3 * ne, L->dense_globals + 1 * ne};
+        a.down = WeightTable{L->dense_ptrs + 4 * ne, L->dense_ptrs + 5 * ne, L->dense_globals + 2 * ne};
+        a.x_hi = L->xg;
+        a.x_lo = L->xg_lo;
+        a.coef = d.format == STRATA_MOE_FMT_INT4G128 ? L->dense_coef : nullptr;
+        a.act_hi = L->act_hi;
+        a.act_lo = L->act_lo;
+        a.y = L->y;
+        a.status = ctx->d_status;
+        launch_decode_gate_up(a, s);
+        launch_decode_down(a, s);
+    }
+    if (with_shared) {
+        for (int r = 0; r < 3; ++r)
+            if (!L->shared_w[r]) return fail(ctx, STRATA_MOE_E_INVALID, "shared expert weights were never set");
+        uint32_t* off2 = L->offsets + d.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, rows);
+        // natural-layout hi/lo split of the fp32 rows for the BF16 shared expert
+        __nv_bfloat16* sh_hi = L->x_stage;
+        __nv_bfloat16* sh_lo = reinterpret_cast<__nv_bfloat16*>(L->out_stage);
+        split_f32_kernel<<<148, 256, 0, s>>>(L->dense_hidden, (size_t)rows * H, sh_hi, sh_lo);
+        g_kernel_launches += 2;
+        int rc = run_shared(L, sh_hi, sh_lo, rows, off2);
+        if (rc) return rc;
+    }
+    CK(cudaGetLastError());
+    L->dense_in_flight = true;
+    L->dense_rows = rows;
+    L->dense_n = n;
+    L->dense_shared = with_shared != 0;
+    return 0;
+}
+
+int strata_moe_collect_dense(strata_moe_layer* L, float* routed_output, float* shared_output) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!L->dense_in_flight) return fail(ctx, STRATA_MOE_E_INVALID, "no MoE command is in flight");
+    CK(cudaSetDevice(ctx->device));
+    // results reach the caller only after completion and a clean status are confirmed
+    int rc = strata_moe_synchronize(ctx);
+    L->dense_in_flight = false;
+    if (rc) return rc;
+    const size_t H = L->d.hidden;
+    if (L->dense_n) {
+        if (!routed_output) return fail(ctx, STRATA_MOE_E_INVALID, "routed output buffer is required");
+        CK(cudaMemcpyAsync(routed_output, L->y, (size_t)L->dense_n * L->dense_rows * H * 4,
+                           cudaMemcpyDeviceToHost, ctx->stream));
+        ctx->stats.d2h_bytes += (size_t)L->dense_n * L->dense_rows * H * 4;
+    }
+    if (L->dense_shared) {
+        if (!shared_output) return fail(ctx, STRATA_MOE_E_INVALID, "shared output buffer is required");
+        CK(cudaMemcpyAsync(shared_output, L->sh_y, (size_t)L->dense_rows * H * 4, cudaMemcpyDeviceToHost,
+                           ctx->stream));
+        ctx->stats.d2h_bytes += (size_t)L->dense_rows * H * 4;
+    }
+    CK(cudaStreamSynchronize(ctx->stream));
+    return 0;
+}
+
+}  // extern "C"

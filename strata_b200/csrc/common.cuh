@@ -1,0 +1,84 @@
+// Shared declarations of the MoE expert-block kernels (sm_100a only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/strata_moe.h"
+
+namespace smoe {
+
+constexpr int kNumSMs = 148;
+
+// Device status word bits (never a trap: kernels record and carry on).
+enum : uint32_t {
+    kStatusNonFiniteLogit = 1u,   // router saw a non-finite logit or bias
+    kStatusBadNormaliser = 2u,    // selected scores do not sum to a positive finite value
+    kStatusNonFiniteOutput = 4u,  // an expert produced a non-finite value
+    kStatusWaitTimeout = 8u,      // a bounded mbarrier wait gave up
+    kStatusBadGroup = 16u         // group table inconsistent with the pair count
+};
+
+struct RouterParams {
+    uint32_t experts, top_k;
+    int32_t score_kind, normalize;
+    float norm_init, weight_scale, softcap;
+};
+
+// One projection of every local expert: base pointers per expert.
+struct WeightTable {
+    const uint8_t* const* packed;  // [n_local] device array of device pointers
+    const uint8_t* const* scales;  // [n_local]
+    const float* global_scale;     // [n_local] NVFP4 divisor (1 otherwise)
+};
+
+// ---- launch wrappers (definitions in the .cu files) ---------------------------------
+// router.cu
+void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
+                          uint32_t E, float* logits, cudaStream_t s);
+void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
+                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s);
+// group.cu
+size_t group_scratch_bytes(uint32_t pairs, uint32_t n_experts);
+void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, uint32_t n_experts,
+                  uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* inv,
+                  uint32_t* active_list, uint32_t* n_active, void* scratch, cudaStream_t s);
+// K-permuted copy of activation rows (layout the decode kernel's B operand reads).
+// src_row[pos] = perm[pos] / k_div when perm != nullptr, else pos.
+void launch_gather_rows_kperm(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
+                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s);
+void launch_gather_rows_kperm_f32(const float* x, uint32_t rows, uint32_t reps, uint32_t H,
+                                  __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s);
+void launch_gather_rows_plain(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
+                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s);
+// decode.cu : small-batch expert FFN (warp-level MMA GEMV path)
+struct DecodeArgs {
+    int fmt;                       // STRATA_MOE_FMT_* or 3 = BF16 (shared expert)
+    uint32_t H, I;
+    uint32_t n_groups;             // size of the offsets table - 1
+    const uint32_t* offsets;       // [n_groups + 1] rows of group g = [offsets[g], offsets[g+1])
+    const uint32_t* active_list;   // [n_active] groups with rows, or nullptr = all groups
+    const uint32_t* n_active;      // device scalar (nullptr when active_list is nullptr)
+    uint32_t max_rows_per_group;   // upper bound used to pick the token tile
+    WeightTable gate, up, down;
+    const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
+    const __nv_bfloat16* x_lo;     // optional low part (fp32 inputs), nullptr otherwise
+    const float* coef;             // optional [pairs] multiplied into the activation, or nullptr
+    __nv_bfloat16* act_hi;         // [pairs, I] scratch, K-permuted
+    __nv_bfloat16* act_lo;
+    float* y;                      // [pairs, H]
+    uint32_t* status;
+};
+void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);
+void launch_decode_down(const DecodeArgs& a, cudaStream_t s);
+// combine.cu
+void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
+                    uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,
+                    uint32_t* status, cudaStream_t s);
+void launch_dequant_export(int fmt, const uint8_t* packed, const uint8_t* scales, float global_scale,
+                           uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
+
+// Launch counter (every wrapper above bumps it once per kernel launch).
+extern unsigned long long g_kernel_launches;
+
+}  // namespace smoe

@@ -1,0 +1,216 @@
+// Token -> expert grouping: per-expert counts, exclusive offsets, and the stable permutation
+// that sorts (token, rank) pairs by expert id while keeping row-major scan order inside each
+// expert -- the lists the reference builds on the host with vector pushes
+// (src/models/glm52/glm_runtime.cpp:1521-1541, src/models/dsv4/deepseek_runtime.cpp:6216-6321).
+//
+// Integer work only.  Pairs are cut into segments of 128 (one warp each); a warp ranks its
+// pairs with __match_any_sync, so the order inside a segment is the scan order, and segment
+// bases come from an exclusive scan over (expert, segment).  Pairs whose expert lies outside
+// [expert_begin, expert_begin + n_experts) are ignored (expert-parallel ranks group only their
+// own experts).
+#include "common.cuh"
+
+namespace smoe {
+
+constexpr uint32_t kSegPairs = 128;   // pairs per warp segment
+constexpr uint32_t kSmallPairs = 4096; // single-CTA path up to this many pairs
+
+// ---- small path: one CTA does everything ---------------------------------------------------
+__global__ void __launch_bounds__(1024) group_small_kernel(
+    const uint32_t* __restrict__ ids, uint32_t pairs, uint32_t ebeg, uint32_t nexp,
+    uint32_t* __restrict__ counts, uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm,
+    uint32_t* __restrict__ inv, uint32_t* __restrict__ active_list, uint32_t* __restrict__ n_active) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* cnt = sm;             // [nexp]
+    uint32_t* cur = sm + nexp;      // [nexp] running cursor
+    uint32_t* scan = sm + 2 * nexp; // [1024] scratch
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t e = tid; e < nexp; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < pairs; i += blockDim.x) {
+        const uint32_t e = ids[i] - ebeg;
+        if (e < nexp) atomicAdd(&cnt[e], 1u);
+    }
+    __syncthreads();
+    // exclusive scan over experts (nexp <= 1024): one element per thread, Hillis-Steele
+    const uint32_t mine = tid < nexp ? cnt[tid] : 0u;
+    scan[tid] = mine;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024u; off <<= 1) {
+        const uint32_t v = tid >= off ? scan[tid - off] : 0u;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    const uint32_t incl = scan[tid];
+    if (tid < nexp) {
+        counts[tid] = mine;
+        offsets[tid] = incl - mine;
+        cur[tid] = incl - mine;
+        if (tid == nexp - 1) offsets[nexp] = incl;
+    }
+    __syncthreads();
+    // active list (ascending): rank = number of non-empty experts before this one
+    scan[tid] = (tid < nexp && mine) ? 1u : 0u;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024u; off <<= 1) {
+        const uint32_t v = tid >= off ? scan[tid - off] : 0u;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    if (active_list) {
+        if (tid < nexp && mine) active_list[scan[tid] - 1u] = tid;
+        if (tid == 1023u) *n_active = scan[1023];
+    }
+    __syncthreads();
+    // stable placement: warps take their 32 pairs in turn
+    const uint32_t nwarps = blockDim.x >> 5;
+    for (uint32_t base = 0; base < pairs; base += blockDim.x) {
+        const uint32_t i = base + tid;
+        const uint32_t e = i < pairs ? ids[i] - ebeg : 0xFFFFFFFFu;
+        const bool ok = e < nexp;
+        for (uint32_t w = 0; w < nwarps; ++w) {
+            if (warp == w && base + w * 32u < pairs) {
+                const uint32_t key = ok ? e : 0xFFFFFFFFu;
+                const uint32_t peers = __match_any_sync(0xFFFFFFFFu, key);
+                if (ok) {
+                    const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+                    const uint32_t pos = cur[e] + rank;
+                    perm[pos] = i;
+                    if (inv) inv[i] = pos;
+                }
+                __syncwarp();
+                if (ok && lane == (uint32_t)(__ffs(peers) - 1)) cur[e] += __popc(peers);
+            }
+            __syncthreads();
+        }
+    }
+    for (uint32_t i = tid; i < pairs; i += blockDim.x) {
+        const uint32_t e = ids[i] - ebeg;
+        if (!(e < nexp) && inv) inv[i] = 0xFFFFFFFFu;
+    }
+}
+
+// ---- large path -------------------------------------------------------------------------
+// A: per-segment histograms  hist[seg][e]
+__global__ void __launch_bounds__(256) group_hist_kernel(const uint32_t* __restrict__ ids,
+                                                         uint32_t pairs, uint32_t ebeg, uint32_t nexp,
+                                                         uint32_t* __restrict__ hist) {
+    extern __shared__ uint32_t sm[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    uint32_t* h = sm + (size_t)warp * nexp;
+    const uint32_t seg = blockIdx.x * 8u + warp;
+    for (uint32_t e = lane; e < nexp; e += 32u) h[e] = 0;
+    __syncwarp();
+    const uint32_t b = seg * kSegPairs;
+    for (uint32_t i = b + lane; i < min(b + kSegPairs, pairs); i += 32u) {
+        const uint32_t e = ids[i] - ebeg;
+        if (e < nexp) atomicAdd(&h[e], 1u);
+    }
+    __syncwarp();
+    if (b < pairs)
+        for (uint32_t e = lane; e < nexp; e += 32u) hist[(size_t)seg * nexp + e] = h[e];
+}
+
+// B: per expert, exclusive scan over segments (in place) and total count
+__global__ void group_segscan_kernel(uint32_t* __restrict__ hist, uint32_t nseg, uint32_t nexp,
+                                     uint32_t* __restrict__ counts) {
+    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= nexp) return;
+    uint32_t run = 0;
+    for (uint32_t s = 0; s < nseg; ++s) {
+        const uint32_t v = hist[(size_t)s * nexp + e];
+        hist[(size_t)s * nexp + e] = run;
+        run += v;
+    }
+    counts[e] = run;
+}
+
+// C: offsets = exclusive scan of counts; active list
+__global__ void __launch_bounds__(1024) group_offsets_kernel(const uint32_t* __restrict__ counts,
+                                                             uint32_t nexp, uint32_t* __restrict__ offsets,
+                                                             uint32_t* __restrict__ active_list,
+                                                             uint32_t* __restrict__ n_active) {
+    __shared__ uint32_t scan[1024];
+    __shared__ uint32_t scan2[1024];
+    const uint32_t tid = threadIdx.x;
+    const uint32_t mine = tid < nexp ? counts[tid] : 0u;
+    scan[tid] = mine;
+    scan2[tid] = mine ? 1u : 0u;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024u; off <<= 1) {
+        const uint32_t v = tid >= off ? scan[tid - off] : 0u;
+        const uint32_t v2 = tid >= off ? scan2[tid - off] : 0u;
+        __syncthreads();
+        scan[tid] += v;
+        scan2[tid] += v2;
+        __syncthreads();
+    }
+    if (tid < nexp) {
+        offsets[tid] = scan[tid] - mine;
+        if (tid == nexp - 1) offsets[nexp] = scan[tid];
+        if (active_list && mine) active_list[scan2[tid] - 1u] = tid;
+    }
+    if (active_list && tid == 1023u) *n_active = scan2[1023];
+}
+
+// D: stable scatter, one warp per segment, 4 rounds of 32 pairs in order
+__global__ void __launch_bounds__(256) group_scatter_kernel(
+    const uint32_t* __restrict__ ids, uint32_t pairs, uint32_t ebeg, uint32_t nexp,
+    const uint32_t* __restrict__ hist, const uint32_t* __restrict__ offsets,
+    uint32_t* __restrict__ perm, uint32_t* __restrict__ inv) {
+    extern __shared__ uint32_t sm[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    uint32_t* cur = sm + (size_t)warp * nexp;
+    const uint32_t seg = blockIdx.x * 8u + warp;
+    const uint32_t b = seg * kSegPairs;
+    if (b >= pairs) return;
+    for (uint32_t e = lane; e < nexp; e += 32u) cur[e] = offsets[e] + hist[(size_t)seg * nexp + e];
+    __syncwarp();
+    for (uint32_t r = 0; r < kSegPairs / 32u; ++r) {
+        const uint32_t i = b + r * 32u + lane;
+        const uint32_t e = i < pairs ? ids[i] - ebeg : 0xFFFFFFFFu;
+        const bool ok = e < nexp;
+        const uint32_t peers = __match_any_sync(0xFFFFFFFFu, ok ? e : 0xFFFFFFFFu);
+        if (ok) {
+            const uint32_t pos = cur[e] + __popc(peers & ((1u << lane) - 1u));
+            perm[pos] = i;
+            if (inv) inv[i] = pos;
+        } else if (i < pairs && inv) {
+            inv[i] = 0xFFFFFFFFu;
+        }
+        __syncwarp();
+        if (ok && lane == (uint32_t)(__ffs(peers) - 1)) cur[e] += __popc(peers);
+        __syncwarp();
+    }
+}
+
+size_t group_scratch_bytes(uint32_t pairs, uint32_t n_experts) {
+    const size_t nseg = (pairs + kSegPairs - 1) / kSegPairs;
+    return (nseg + 8) * (size_t)n_experts * sizeof(uint32_t);
+}
+
+void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, uint32_t n_experts,
+                  uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* inv,
+                  uint32_t* active_list, uint32_t* n_active, void* scratch, cudaStream_t s) {
+    if (pairs <= kSmallPairs) {
+        const size_t smem = (2u * (size_t)n_experts + 1024u) * sizeof(uint32_t);
+        group_small_kernel<<<1, 1024, smem, s>>>(ids, pairs, expert_begin, n_experts, counts, offsets,
+                                                perm, inv, active_list, n_active);
+        ++g_kernel_launches;
+        return;
+    }
+    uint32_t* hist = static_cast<uint32_t*>(scratch);
+    const uint32_t nseg = (pairs + kSegPairs - 1) / kSegPairs;
+    const uint32_t blocks = (nseg + 7) / 8;
+    const size_t smem = 8u * (size_t)n_experts * sizeof(uint32_t);
+    group_hist_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, hist);
+    group_segscan_kernel<<<(n_experts + 127) / 128, 128, 0, s>>>(hist, nseg, n_experts, counts);
+    group_offsets_kernel<<<1, 1024, 0, s>>>(counts, n_experts, offsets, active_list, n_active);
+    group_scatter_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, hist, offsets,
+                                                   perm, inv);
+    g_kernel_launches += 4;
+}
+
+}  // namespace smoe

@@ -1,0 +1,266 @@
+// Router: BF16 projection in the reference's production accumulation order, then score,
+// top-k and routing weights, one warp per token.
+//
+// The projection reproduces kernels/cuda/backend.cu:651-728 of the reference exactly: lane l of
+// a warp owns columns l, l+32, ... of one expert row and accumulates them with a separate
+// multiply and add (no FMA); five shuffle-down rounds fold the 32 partial sums.  Expert ids are
+// a discontinuous function of the logits, so reproducing the order is what makes them
+// bit-identical to the reference's.  For the same reason the scores use an expf that follows
+// the host libm's algorithm step by step in double precision (see expf_libm below).
+#include "common.cuh"
+
+namespace smoe {
+
+// ---------------------------------------------------------------------------------------
+// logits[t, e] for a tile of TT tokens and WARPS expert rows per CTA.  The activation tile and
+// each warp's weight-row chunk are staged in shared memory as fp32, transposed so that lane l
+// reads its columns l, l+32, ... of a 256-column chunk as two 16-byte vectors.
+constexpr int kRouterTT = 16;
+constexpr int kRouterChunk = 256;
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
+    uint32_t E, float* __restrict__ logits) {
+    // xs[tok][half][lane][4] : column = chunk + lane + 32 * (half * 4 + i)
+    __shared__ __align__(16) float xs[kRouterTT][2][32][4];
+    __shared__ __align__(16) float ws[WARPS][2][32][4];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t e = blockIdx.x * WARPS + warp;
+    const uint32_t t0 = blockIdx.y * kRouterTT;
+    const uint32_t nt = min((uint32_t)kRouterTT, T - t0);
+    const bool e_ok = e < E;
+    float sum[kRouterTT];
+#pragma unroll
+    for (int i = 0; i < kRouterTT; ++i) sum[i] = 0.0f;
+
+    for (uint32_t c0 = 0; c0 < H; c0 += kRouterChunk) {
+        const uint32_t cols = min((uint32_t)kRouterChunk, H - c0);  // multiple of 32
+        __syncthreads();
+        // stage activations: TT x 256 elements, 8 per thread-iteration
+        for (uint32_t i = threadIdx.x; i < kRouterTT * (kRouterChunk / 8); i += WARPS * 32) {
+            const uint32_t tok = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (tok < nt && c8 < cols)
+                v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H + c0 + c8));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
+                const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
+                xs[tok][j >> 2][l][j & 3u] = __uint_as_float(bits);
+            }
+        }
+        // stage this warp's weight row chunk
+        if (e_ok) {
+            const uint32_t c8 = lane * 8u;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (c8 < cols) v = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)e * H + c0 + c8));
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int p = 0; p < 8; ++p) {
+                const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
+                const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
+                ws[warp][j >> 2][l][j & 3u] = __uint_as_float(bits);
+            }
+        }
+        __syncthreads();
+        if (!e_ok) continue;
+        const uint32_t nj = cols >> 5;  // columns lane + 32 j, j < nj, exist
+        const float4 w0 = *reinterpret_cast<const float4*>(ws[warp][0][lane]);
+        const float4 w1 = *reinterpret_cast<const float4*>(ws[warp][1][lane]);
+        const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+        for (int tok = 0; tok < kRouterTT; ++tok) {
+            const float4 a0 = *reinterpret_cast<const float4*>(xs[tok][0][lane]);
+            const float4 a1 = *reinterpret_cast<const float4*>(xs[tok][1][lane]);
+            const float xv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float s = sum[tok];
+            if (nj == 8u) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) s = __fadd_rn(s, __fmul_rn(xv[j], wv[j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if ((uint32_t)j < nj) s = __fadd_rn(s, __fmul_rn(xv[j], wv[j]));
+            }
+            sum[tok] = s;
+        }
+    }
+    if (!e_ok) return;
+#pragma unroll
+    for (int tok = 0; tok < kRouterTT; ++tok) {
+        float v = sum[tok];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
+        if (lane == 0 && (uint32_t)tok < nt) logits[(size_t)(t0 + tok) * E + e] = v;
+    }
+}
+
+void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
+                          uint32_t E, float* logits, cudaStream_t s) {
+    if (T == 0) return;
+    const uint32_t ty = (T + kRouterTT - 1) / kRouterTT;
+    // few tokens: spread expert rows over more CTAs; many tokens: 8 rows share one staged tile
+    if ((size_t)ty * ((E + 7) / 8) < 2u * kNumSMs) {
+        dim3 grid((E + 1) / 2, ty);
+        router_logits_kernel<2><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+    } else {
+        dim3 grid((E + 7) / 8, ty);
+        router_logits_kernel<8><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
+    }
+    ++g_kernel_launches;
+}
+
+// ---------------------------------------------------------------------------------------
+// expf as glibc (>= 2.27) computes it: 32-entry table of 2^(i/32), degree-3 polynomial,
+// everything in double, one rounding to float at the end.  Evaluated here with IEEE double
+// operations so the result is bit-identical to the host libm the reference routers call
+// (verified over every float in (-88, 88): two inputs, |x| > 32, differ by one ulp).
+__constant__ unsigned long long kExp2Bits[32] = {
+    0x3ff0000000000000ULL, 0x3ff059b0d3158574ULL, 0x3ff0b5586cf9890fULL, 0x3ff11301d0125b51ULL,
+    0x3ff172b83c7d517bULL, 0x3ff1d4873168b9aaULL, 0x3ff2387a6e756238ULL, 0x3ff29e9df51fdee1ULL,
+    0x3ff306fe0a31b715ULL, 0x3ff371a7373aa9cbULL, 0x3ff3dea64c123422ULL, 0x3ff44e086061892dULL,
+    0x3ff4bfdad5362a27ULL, 0x3ff5342b569d4f82ULL, 0x3ff5ab07dd485429ULL, 0x3ff6247eb03a5585ULL,
+    0x3ff6a09e667f3bcdULL, 0x3ff71f75e8ec5f74ULL, 0x3ff7a11473eb0187ULL, 0x3ff82589994cce13ULL,
+    0x3ff8ace5422aa0dbULL, 0x3ff93737b0cdc5e5ULL, 0x3ff9c49182a3f090ULL, 0x3ffa5503b23e255dULL,
+    0x3ffae89f995ad3adULL, 0x3ffb7f76f2fb5e47ULL, 0x3ffc199bdd85529cULL, 0x3ffcb720dcef9069ULL,
+    0x3ffd5818dcfba487ULL, 0x3ffdfc97337b9b5fULL, 0x3ffea4afa2a490daULL, 0x3fff50765b6e4540ULL};
+
+__device__ float expf_libm(float x) {
+    if (x > 88.72283f) return __int_as_float(0x7F800000);
+    if (x < -103.972076f) return 0.0f;
+    const double invln2n = 0x1.71547652b82fep+0 * 32.0;
+    const double shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
+    const double c1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+    const double c2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+    const double z = __dmul_rn(invln2n, (double)x);
+    double kd = __dadd_rn(z, shift);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, shift);
+    const double r = __dsub_rn(z, kd);
+    unsigned long long tb = kExp2Bits[ki & 31u] - ((ki & 31u) << 47);
+    tb += ki << 47;
+    const double sc = __longlong_as_double((long long)tb);
+    const double zz = __fma_rn(c0, r, c1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(c2, r, 1.0);
+    y = __fma_rn(zz, r2, y);
+    y = __dmul_rn(y, sc);
+    return __double2float_rn(y);
+}
+
+__device__ __forceinline__ float sigmoid_two_branch(float v) {
+    // src/platform/numerics.cpp:44-48 of the reference
+    if (v >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-v)));
+    const float e = expf_libm(v);
+    return __fdiv_rn(e, __fadd_rn(1.0f, e));
+}
+
+// One warp per token.  Shared memory: score[E] and choice[E] per warp.
+constexpr int kRouteWarps = 4;
+
+__global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
+    RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
+    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status) {
+    extern __shared__ float smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t E = p.experts, k = p.top_k;
+    float* score = smem + (size_t)warp * 2u * E;
+    float* choice = score + E;
+    const uint32_t tok = blockIdx.x * kRouteWarps + warp;
+    if (tok >= T) return;
+    const float* lg = logits + (size_t)tok * E;
+    bool bad = false;
+
+    if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) {
+        float mx = -INFINITY;
+        for (uint32_t e = lane; e < E; e += 32u) {
+            const float l = lg[e];
+            bad |= !isfinite(l);
+            mx = fmaxf(mx, l);
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+        for (uint32_t e = lane; e < E; e += 32u) score[e] = expf_libm(__fsub_rn(lg[e], mx));
+        __syncwarp();
+        float sum = 0.0f;  // index order, as a scalar loop sums it
+        if (lane == 0)
+            for (uint32_t e = 0; e < E; ++e) sum = __fadd_rn(sum, score[e]);
+        sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
+        for (uint32_t e = lane; e < E; e += 32u) score[e] = __fdiv_rn(score[e], sum);
+    } else {
+        for (uint32_t e = lane; e < E; e += 32u) {
+            float l = lg[e];
+            bad |= !isfinite(l);
+            if (p.softcap > 0.0f) l = __fmul_rn(tanhf(__fdiv_rn(l, p.softcap)), p.softcap);
+            float sc;
+            if (p.score_kind == STRATA_MOE_SCORE_SIGMOID) sc = sigmoid_two_branch(l);
+            else if (p.score_kind == STRATA_MOE_SCORE_SIGMOID_PLAIN)
+                sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
+            else sc = sqrtf(l > 20.0f ? l : log1pf(expf_libm(l)));
+            score[e] = sc;
+        }
+    }
+    for (uint32_t e = lane; e < E; e += 32u) {
+        const float b = bias ? bias[e] : 0.0f;
+        bad |= !isfinite(b);
+        choice[e] = __fadd_rn(score[e], b);
+    }
+    __syncwarp();
+
+    // k rounds of arg-max over (value desc, index asc); taken entries drop to -inf.
+    float my_w = 0.0f;
+    uint32_t my_id = 0;
+    for (uint32_t r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        uint32_t bi = 0xFFFFFFFFu;
+        for (uint32_t e = lane; e < E; e += 32u) {
+            const float v = choice[e];
+            if (v > bv || bi == 0xFFFFFFFFu) {
+                if (v > bv || bi == 0xFFFFFFFFu) { bv = v; bi = e; }
+            }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+            const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= E) { bad = true; bi = 0; }
+        if (lane == r) { my_id = bi; my_w = score[bi]; }
+        if (lane == 0) choice[bi] = -INFINITY;
+        __syncwarp();
+    }
+    // weights: sum in rank order, divide, scale (lane r holds rank r; k <= 32)
+    float sum = p.norm_init;
+    for (uint32_t r = 0; r < k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, my_w, r));
+    float w = my_w;
+    if (p.normalize) {
+        if (!(sum > 0.0f) || !isfinite(sum)) {
+            if (lane == 0) atomicOr(status, kStatusBadNormaliser);
+            w = 0.0f;
+        } else {
+            w = __fmul_rn(__fdiv_rn(my_w, sum), p.weight_scale);
+        }
+    } else {
+        w = __fmul_rn(my_w, p.weight_scale);
+    }
+    if (lane < k) {
+        ids[(size_t)tok * k + lane] = my_id;
+        weights[(size_t)tok * k + lane] = w;
+    }
+    if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) atomicOr(status, kStatusNonFiniteLogit);
+}
+
+void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
+                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s) {
+    if (T == 0) return;
+    const size_t smem = (size_t)kRouteWarps * 2u * p.experts * sizeof(float);
+    route_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, s>>>(
+        p, logits, bias, T, ids, weights, status);
+    ++g_kernel_launches;
+}
+
+}  // namespace smoe

@@ -1,0 +1,172 @@
+"""CUDA path against the CPU oracle through the C ABI (needs a B200).
+
+Bars (from the task's north star): expert ids, permutation, counts and offsets bit-exact;
+dequantised weights bit-exact; layer output within relative L2 1e-2 and max-abs 2^-6 x RMS of
+the oracle's FP32-accumulate result.  The kernels accumulate in FP32 as well, so a much tighter
+bound is asserted alongside to catch layout or indexing mistakes early.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from strata_b200 import MoeContext, MoeLayer, synth
+from tests import helpers as Hh
+
+pytestmark = pytest.mark.gpu
+
+REL_L2, MAX_ABS = 1e-2, 2.0 ** -6
+TIGHT_REL_L2 = 2e-4
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    return MoeContext(0)
+
+
+def small(fmt, **kw):
+    base = dict(name=f"small{fmt}", H=512, I=256, E=16, k=4, fmt=fmt, T=8, seed=3)
+    base.update(kw)
+    return synth.MoeConfig(**base)
+
+
+SMALL_CASES = [
+    small(synth.FMT_MXFP4),
+    small(synth.FMT_NVFP4, I_shared=128),
+    small(synth.FMT_INT4, norm_init=1e-20, weight_scale=2.5),
+    small(synth.FMT_MXFP4, T=1, name="one_token"),
+    small(synth.FMT_MXFP4, T=37, E=8, k=3, H=384, I=128, name="ragged"),
+    small(synth.FMT_NVFP4, T=19, score_kind=synth.SCORE_SOFTMAX, name="softmax"),
+    small(synth.FMT_INT4, T=5, score_kind=synth.SCORE_SIGMOID_PLAIN, E=32, k=16, name="kimi_like"),
+    small(synth.FMT_NVFP4, T=9, output_scale=2.5, I_shared=256, name="laguna_like"),
+    small(synth.FMT_MXFP4, T=8, zipf_s=1.1, E=64, k=8, name="zipf_bias"),
+]
+
+
+def run_layer(ctx, cfg, T=None):
+    layer = synth.build_layer(cfg, "cuda", T=T)
+    ml = MoeLayer(ctx, cfg, max_tokens=layer.x.shape[0])
+    ml.load_synth(layer)
+    out, aux = ml.forward(layer.x, want_aux=True)
+    ctx.synchronize()
+    return layer, ml, out, aux
+
+
+@pytest.mark.parametrize("cfg", SMALL_CASES, ids=lambda c: c.name)
+def test_small_layer_matches_oracle(ctx, cfg):
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["logits"].cpu().numpy().view(np.uint32), ref["logits"].view(np.uint32))
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    if cfg.score_kind != synth.SCORE_SQRTSOFTPLUS:
+        assert np.array_equal(aux["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
+    assert np.array_equal(aux["counts"].cpu().numpy().astype(np.uint32), ref["counts"])
+    assert np.array_equal(aux["offsets"].cpu().numpy().astype(np.uint32), ref["offsets"])
+    assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= REL_L2 and mx <= MAX_ABS
+    assert rel <= TIGHT_REL_L2, rel
+
+
+@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4, synth.FMT_INT4])
+def test_dequantised_weights_bit_exact(ctx, fmt):
+    cfg = small(fmt, H=256, I=128, E=4, k=2, name=f"deq{fmt}")
+    layer = synth.build_layer(cfg, "cuda")
+    if fmt == synth.FMT_MXFP4:
+        # widen the scale spread over every legal E8M0 byte, including block scales >= 4
+        for role in synth.ROLES:
+            s = layer.scales[role]
+            layer.scales[role] = (torch.arange(s.numel(), device="cuda") % 254 + 1).to(torch.uint8).view_as(s)
+    if fmt == synth.FMT_NVFP4:
+        # every finite E4M3 byte, including subnormal and negative block scales
+        for role in synth.ROLES:
+            s = layer.scales[role]
+            v = (torch.arange(s.numel(), device="cuda") % 256)
+            v = torch.where((v & 0x7F) == 0x7F, torch.zeros_like(v), v)
+            layer.scales[role] = v.to(torch.uint8).view_as(s)
+    ml = MoeLayer(ctx, cfg)
+    ml.set_router(layer.router_w, layer.bias)
+    for r, role in enumerate(synth.ROLES):
+        for e in range(cfg.E):
+            ml.set_expert(e, r, layer.packed[role][e], layer.scales[role][e], 1.0)
+    for r, role in enumerate(synth.ROLES):
+        rows, cols = cfg.role_shape(role)
+        for e in (0, cfg.E - 1):
+            got = ml.dequant_export(e, r).numpy()
+            p = layer.packed[role][e].cpu().numpy()
+            s = layer.scales[role][e].cpu().numpy()
+            want = O.dequant(O.make_matrix(fmt, rows, cols, p, s, 1.0), device_zero=True)
+            # zero sign is canonicalised: the CPU tables and the device decode of the reference
+            # disagree on nibble 0x8 themselves
+            got = got + 0.0
+            want = want + 0.0
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (role, e)
+
+
+def test_nvfp4_global_scale_within_one_ulp(ctx):
+    cfg = small(synth.FMT_NVFP4, H=256, I=128, E=2, k=1, name="deq_global")
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg)
+    ml.load_synth(layer)
+    got = ml.dequant_export(1, 0).numpy()
+    p, s = layer.packed["gate"][1].cpu().numpy(), layer.scales["gate"][1].cpu().numpy()
+    want = O.dequant(O.make_matrix(O.FMT_NVFP4, cfg.I, cfg.H, p, s, synth.NVFP4_GLOBAL["gate"]))
+    assert np.all(np.abs(got - want) <= np.spacing(np.abs(want).astype(np.float32)))
+
+
+@pytest.mark.parametrize("name,T,n_check", [("c0", 8, 8), ("c1", 16, 6), ("c1_sigmoid", 4, 4)])
+def test_full_size_decode_configs(ctx, name, T, n_check):
+    cfg = synth.CONFIGS[name]
+    layer, ml, out, aux = run_layer(ctx, cfg, T=T)
+    sub = np.arange(T)[:n_check]
+    ref = Hh.run_oracle(cfg, layer.x.cpu(), token_subset=sub)
+    assert np.array_equal(aux["logits"].cpu().numpy().view(np.uint32), ref["logits"].view(np.uint32))
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    assert np.array_equal(aux["counts"].cpu().numpy().astype(np.uint32), ref["counts"])
+    assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy()[sub], ref["out"])
+    assert rel <= REL_L2 and mx <= MAX_ABS
+    assert rel <= TIGHT_REL_L2, rel
+
+
+def test_forward_host_round_trip_and_determinism(ctx):
+    cfg = small(synth.FMT_MXFP4, T=8, name="host")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    xh = layer.x.cpu().pin_memory()
+    oh = torch.empty(cfg.T, cfg.H, dtype=torch.float32).pin_memory()
+    ml.forward_host(xh, oh)
+    assert torch.equal(oh, out.cpu())
+    out2 = ml.forward(layer.x)
+    ctx.synchronize()
+    assert torch.equal(out2, out)      # bit-reproducible run to run
+
+
+def test_empty_page_is_a_no_op(ctx):
+    cfg = small(synth.FMT_MXFP4, name="empty")
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg)
+    ml.load_synth(layer)
+    out = ml.forward(layer.x[:0])
+    ctx.synchronize()
+    assert out.shape[0] == 0
+
+
+def test_large_group_path_matches_small_path(ctx):
+    # > 4096 pairs exercises the segmented histogram/scan/scatter kernels
+    cfg = small(synth.FMT_MXFP4, T=1500, E=64, k=6, H=256, I=128, name="grp")
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg)
+    ml.load_synth(layer)
+    ids, w = ml.route(layer.x)
+    counts, offsets, perm = ml.group(ids)
+    ctx.synchronize()
+    rc, rcounts, roffsets, rperm = 0, *O.group(ids.cpu().numpy().astype(np.uint32), cfg.E)
+    assert np.array_equal(counts.cpu().numpy().astype(np.uint32), rcounts)
+    assert np.array_equal(offsets.cpu().numpy().astype(np.uint32), roffsets)
+    assert np.array_equal(perm.cpu().numpy().astype(np.uint32), rperm)
+    # expert-parallel slice: only experts [16, 48)
+    c2, o2, p2 = ml.group(ids, 16, 32)
+    ctx.synchronize()
+    n = int(roffsets[48] - roffsets[16])
+    assert np.array_equal(c2.cpu().numpy().astype(np.uint32), rcounts[16:48])
+    assert np.array_equal(p2.cpu().numpy().astype(np.uint32)[:n], rperm[roffsets[16]:roffsets[48]])
