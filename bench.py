@@ -179,6 +179,7 @@ def run_gpu(args, cfg, T, rank, world):
         return ep.bench(args, cfg, T, rank, world, device, peaks, ClockSampler)
 
     ctx = MoeContext(device.index)
+    torch.cuda.set_stream(ctx.stream)   # flushes, events and the library share one stream
     layer = synth.build_layer(cfg, device, T=T)
     ml = MoeLayer(ctx, cfg, max_tokens=T)
     ml.load_synth(layer)

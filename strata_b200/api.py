@@ -96,18 +96,32 @@ def _ptr(t):
 class MoeContext:
     """One per process and device (strata_moe_ctx)."""
 
-    def __init__(self, device=0, use_torch_stream=True):
+    def __init__(self, device=0, stream=None):
         self.lib = load_library()
         if not torch.cuda.is_available():
             raise StrataMoeError(-5, "no CUDA device: this library has no CPU path")
         self.device = torch.device("cuda", device)
         torch.cuda.set_device(self.device)
-        stream = torch.cuda.current_stream(self.device).cuda_stream if use_torch_stream else 0
+        # the library runs on this torch stream; callers on another stream are ordered against it
+        # by MoeLayer (wait_stream on both sides of every call)
+        self.stream = stream if stream is not None else torch.cuda.Stream(self.device)
         h = C.c_void_p()
-        rc = self.lib.strata_moe_create(device, C.c_void_p(stream), C.byref(h))
+        rc = self.lib.strata_moe_create(device, C.c_void_p(self.stream.cuda_stream), C.byref(h))
         if rc != 0:
             raise StrataMoeError(rc, "strata_moe_create failed (needs an sm_100 device)")
         self.h = h
+
+    def enter(self):
+        """Orders the library's stream after the caller's current stream."""
+        cur = torch.cuda.current_stream(self.device)
+        if cur.cuda_stream != self.stream.cuda_stream:
+            self.stream.wait_stream(cur)
+
+    def leave(self):
+        """Orders the caller's current stream after the library's stream."""
+        cur = torch.cuda.current_stream(self.device)
+        if cur.cuda_stream != self.stream.cuda_stream:
+            cur.wait_stream(self.stream)
 
     def check(self, rc):
         if rc != 0:
@@ -182,6 +196,7 @@ class MoeLayer:
 
     def load_synth(self, layer):
         """Registers every tensor of a synth.SynthLayer (borrowed in place when on the GPU)."""
+        self.ctx.enter()
         self.set_router(layer.router_w, layer.bias)
         for r, role in enumerate(synth.ROLES):
             p, s = layer.packed[role], layer.scales[role]
@@ -196,6 +211,8 @@ class MoeLayer:
         dev = x.device
         if out is None:
             out = torch.empty(T, self.cfg.H, dtype=torch.float32, device=dev)
+        if T == 0:
+            return (out, None) if want_aux else out
         aux_t = None
         aux = None
         if want_aux:
@@ -207,8 +224,10 @@ class MoeLayer:
                          offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
                          perm=torch.empty(T * k, dtype=torch.int32, device=dev))
             aux = Aux(*[v.data_ptr() for v in aux_t.values()])
+        self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_forward(self.h, _ptr(x), T, _ptr(out),
                                                    C.byref(aux) if aux is not None else None))
+        self.ctx.leave()
         return (out, aux_t) if want_aux else out
 
     def forward_host(self, x_host, out_host):
@@ -220,7 +239,9 @@ class MoeLayer:
         ids = torch.empty(T, self.cfg.k, dtype=torch.int32, device=dev)
         w = torch.empty(T, self.cfg.k, dtype=torch.float32, device=dev)
         logits = torch.empty(T, self.cfg.E, dtype=torch.float32, device=dev) if want_logits else None
+        self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_route(self.h, _ptr(x), T, _ptr(logits), _ptr(ids), _ptr(w)))
+        self.ctx.leave()
         return (ids, w, logits) if want_logits else (ids, w)
 
     def group(self, ids, expert_begin=0, n_experts=None):
@@ -230,14 +251,18 @@ class MoeLayer:
         counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
         offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
         perm = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
+        self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_group(self.h, _ptr(flat), flat.numel(), expert_begin, n_experts,
                                                  _ptr(counts), _ptr(offsets), _ptr(perm)))
+        self.ctx.leave()
         return counts, offsets, perm
 
     def experts_grouped(self, rows, offsets, y=None):
         if y is None:
             y = torch.empty(rows.shape[0], self.cfg.H, dtype=torch.float32, device=rows.device)
+        self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_experts_grouped(self.h, _ptr(rows), rows.shape[0], _ptr(offsets), _ptr(y)))
+        self.ctx.leave()
         return y
 
     def dequant_export(self, expert, role):

@@ -12,6 +12,8 @@
 //
 // Replaces, for small row counts, the reference's one-CTA-per-output-row GEMV kernels
 // (kernels/cuda/backend.cu:1886-2069, 2308-2413), which re-read the weights for every row.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "dequant.cuh"
 
@@ -236,15 +238,19 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return g * sig * u;
 }
 
-// DUAL = true : gate + up projections with fused SwiGLU, writes act (hi/lo BF16, K-permuted for
-//               the down kernel unless the down weights are BF16).
-// DUAL = false: one projection (down), writes y fp32 [pairs, rows].
+// Every warp streams TWO 16-row tiles at once against the same activation fragments:
+// DUAL = true : the gate tile and the up tile of the same output rows, fused SwiGLU epilogue,
+//               writes act (hi/lo BF16, K-permuted for the down kernel unless the down weights
+//               are BF16).
+// DUAL = false: two adjacent row tiles of the down projection, writes y fp32 [pairs, rows].
+// The K loop runs in super-steps of two steps (256 columns: each quad reads one full 128-byte
+// line per row) and keeps the next super-step's loads in flight while decoding the current one.
 template <int FMT, int NT, bool SPLIT, bool DUAL>
-__global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
+__global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(DecodeArgs a) {
     const uint32_t lane = threadIdx.x & 31u, gid = lane >> 2, t = lane & 3u;
     const uint32_t K = DUAL ? a.H : a.I;
     const uint32_t R = DUAL ? a.I : a.H;  // output rows of this projection
-    const uint32_t tiles_per_group = R / 16u;
+    const uint32_t tiles_per_group = DUAL ? R / 16u : R / 32u;
     const uint32_t n_act = a.active_list ? *a.n_active : a.n_groups;
     const uint32_t total = n_act * tiles_per_group;
     if (total == 0u) return;
@@ -254,7 +260,9 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
     const uint32_t wid = blockIdx.x * 4u + (threadIdx.x >> 5);
     if (wid >= W_eff) return;
     constexpr uint32_t KSTEP = FMT == kFmtBf16 ? 32u : 128u;
+    constexpr int U = 2;
     const uint32_t steps = K / KSTEP;
+    const uint32_t nsuper = (steps + U - 1u) / U;
     bool bad = false;
 
     for (uint32_t tile = wid; tile < total; tile += W_eff) {
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
         const uint32_t rt = tile - slot * tiles_per_group;
         const uint32_t row0 = a.offsets[g], cnt = a.offsets[g + 1] - row0;
         if (cnt == 0u) continue;
-        const uint32_t row = rt * 16u + gid;
+        const uint32_t row = (DUAL ? rt * 16u : rt * 32u) + gid;  // first stream's row gid
 
         Projection<FMT, NT, SPLIT> pg, pu;
         float gs = 1.0f, us = 1.0f;
@@ -276,7 +284,8 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
             }
         } else {
             pg.init(a.down.packed[g], a.down.scales[g], row, K, t);
-            if (FMT == STRATA_MOE_FMT_NVFP4) gs = kNvfp4AccScale / a.down.global_scale[g];
+            pu.init(a.down.packed[g], a.down.scales[g], row + 16u, K, t);
+            if (FMT == STRATA_MOE_FMT_NVFP4) gs = us = kNvfp4AccScale / a.down.global_scale[g];
         }
 
         for (uint32_t tb = 0; tb < cnt; tb += 8u * NT) {
@@ -299,17 +308,33 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) accg[nt][j] = accu[nt][j] = 0.0f;
 
-            StepLoad<FMT> Lg, Lu, Ng, Nu;
-            step_load(pg, 0, Lg);
-            if (DUAL) step_load(pu, 0, Lu);
-            for (uint32_t kb = 0; kb < steps; ++kb) {
-                // prefetch the next step's weights before decoding this one
-                const uint32_t kn = kb + 1u < steps ? kb + 1u : kb;
-                step_load(pg, kn, Ng);
-                if (DUAL) step_load(pu, kn, Nu);
-                step_compute<FMT, NT, SPLIT, DUAL>(Lg, Lu, xh, xl, valid, kb, t, accg, accu);
-                Lg = Ng;
-                if (DUAL) Lu = Nu;
+            StepLoad<FMT> Lg[U], Lu[U], Ng[U], Nu[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t kb = min((uint32_t)u, steps - 1u);
+                step_load(pg, kb, Lg[u]);
+                step_load(pu, kb, Lu[u]);
+            }
+            for (uint32_t sb = 0; sb < nsuper; ++sb) {
+                // next super-step's weights are requested before this one is decoded
+                const uint32_t sn = sb + 1u < nsuper ? sb + 1u : sb;
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t kb = min(sn * U + u, steps - 1u);
+                    step_load(pg, kb, Ng[u]);
+                    step_load(pu, kb, Nu[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const uint32_t kb = sb * U + u;
+                    if (kb < steps)
+                        step_compute<FMT, NT, SPLIT, true>(Lg[u], Lu[u], xh, xl, valid, kb, t, accg, accu);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    Lg[u] = Ng[u];
+                    Lu[u] = Nu[u];
+                }
             }
 
             // epilogue: c0,c1 = (row gid, tokens 2t, 2t+1); c2,c3 = (row gid + 8, same tokens)
@@ -331,9 +356,10 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
                         a.act_hi[pos * R + col] = hi;
                         a.act_lo[pos * R + col] = lo;
                     } else {
-                        const float v = accg[nt][j] * gs;
-                        if (!(fabsf(v) <= 3.0e38f)) bad = true;
-                        a.y[pos * R + orow] = v;
+                        const float v0 = accg[nt][j] * gs, v1 = accu[nt][j] * us;
+                        if (!(fabsf(v0) <= 3.0e38f) || !(fabsf(v1) <= 3.0e38f)) bad = true;
+                        a.y[pos * R + orow] = v0;
+                        a.y[pos * R + orow + 16u] = v1;
                     }
                 }
             }
@@ -342,14 +368,23 @@ __global__ void __launch_bounds__(128) decode_ffn_kernel(DecodeArgs a) {
     if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
 }
 
+static uint32_t decode_ctas_per_sm() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("STRATA_MOE_DECODE_CTAS_PER_SM");
+        v = e ? atoi(e) : 4;
+        if (v < 1 || v > 16) v = 4;
+    }
+    return (uint32_t)v;
+}
+
 template <int FMT, bool SPLIT, bool DUAL>
 static void launch_nt(const DecodeArgs& a, cudaStream_t s) {
     const uint32_t R = DUAL ? a.I : a.H;
-    const uint32_t total = a.n_groups * (R / 16u);
+    const uint32_t total = a.n_groups * (DUAL ? R / 16u : R / 32u);
     if (total == 0u) return;
-    // 128 registers / thread budget -> 4 CTAs of 4 warps per SM
     uint32_t grid = (total + 3u) / 4u;
-    const uint32_t cap = kNumSMs * 4u;
+    const uint32_t cap = kNumSMs * decode_ctas_per_sm();
     if (grid > cap) grid = cap;
     const uint32_t m = a.max_rows_per_group;
     if (m <= 8u) decode_ffn_kernel<FMT, 1, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);

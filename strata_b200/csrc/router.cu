@@ -15,63 +15,71 @@ namespace smoe {
 // logits[t, e] for a tile of TT tokens and WARPS expert rows per CTA.  The activation tile and
 // each warp's weight-row chunk are staged in shared memory as fp32, transposed so that lane l
 // reads its columns l, l+32, ... of a 256-column chunk as two 16-byte vectors.
-constexpr int kRouterTT = 16;
 constexpr int kRouterChunk = 256;
 
-template <int WARPS>
+__device__ __forceinline__ void router_stage8(float (*dst)[32][4], uint32_t c8, const uint4& v) {
+    // 8 consecutive columns c8..c8+7 -> dst[j >> 2][lane][j & 3] with column = lane + 32 j
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
+        const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
+        dst[j >> 2][l][j & 3u] = __uint_as_float(bits);
+    }
+}
+
+template <int WARPS, int TT>
 __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
     uint32_t E, float* __restrict__ logits) {
     // xs[tok][half][lane][4] : column = chunk + lane + 32 * (half * 4 + i)
-    __shared__ __align__(16) float xs[kRouterTT][2][32][4];
+    __shared__ __align__(16) float xs[TT][2][32][4];
     __shared__ __align__(16) float ws[WARPS][2][32][4];
+    constexpr int THREADS = WARPS * 32;
+    constexpr int XV = (TT * (kRouterChunk / 8) + THREADS - 1) / THREADS;  // uint4 per thread
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t e = blockIdx.x * WARPS + warp;
-    const uint32_t t0 = blockIdx.y * kRouterTT;
-    const uint32_t nt = min((uint32_t)kRouterTT, T - t0);
+    const uint32_t t0 = blockIdx.y * TT;
+    const uint32_t nt = min((uint32_t)TT, T - t0);
     const bool e_ok = e < E;
-    float sum[kRouterTT];
+    float sum[TT];
 #pragma unroll
-    for (int i = 0; i < kRouterTT; ++i) sum[i] = 0.0f;
+    for (int i = 0; i < TT; ++i) sum[i] = 0.0f;
 
+    uint4 xr[XV], wr;
+    auto fetch = [&](uint32_t c0) {
+        const uint32_t cols = min((uint32_t)kRouterChunk, H - c0);
+#pragma unroll
+        for (int q = 0; q < XV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            const uint32_t tok = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
+            xr[q] = make_uint4(0, 0, 0, 0);
+            if (i < TT * (kRouterChunk / 8) && tok < nt && c8 < cols)
+                xr[q] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H + c0 + c8));
+        }
+        wr = make_uint4(0, 0, 0, 0);
+        if (e_ok && lane * 8u < cols)
+            wr = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)e * H + c0 + lane * 8u));
+    };
+    fetch(0);
     for (uint32_t c0 = 0; c0 < H; c0 += kRouterChunk) {
         const uint32_t cols = min((uint32_t)kRouterChunk, H - c0);  // multiple of 32
-        __syncthreads();
-        // stage activations: TT x 256 elements, 8 per thread-iteration
-        for (uint32_t i = threadIdx.x; i < kRouterTT * (kRouterChunk / 8); i += WARPS * 32) {
-            const uint32_t tok = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (tok < nt && c8 < cols)
-                v = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H + c0 + c8));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        __syncthreads();  // everyone is done reading the previous chunk
 #pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
-                const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
-                xs[tok][j >> 2][l][j & 3u] = __uint_as_float(bits);
-            }
+        for (int q = 0; q < XV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            if (i < TT * (kRouterChunk / 8))
+                router_stage8(xs[i / (kRouterChunk / 8)], (i % (kRouterChunk / 8)) * 8u, xr[q]);
         }
-        // stage this warp's weight row chunk
-        if (e_ok) {
-            const uint32_t c8 = lane * 8u;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (c8 < cols) v = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)e * H + c0 + c8));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int p = 0; p < 8; ++p) {
-                const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
-                const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
-                ws[warp][j >> 2][l][j & 3u] = __uint_as_float(bits);
-            }
-        }
+        router_stage8(ws[warp], lane * 8u, wr);
         __syncthreads();
-        if (!e_ok) continue;
+        if (c0 + kRouterChunk < H) fetch(c0 + kRouterChunk);  // overlaps the arithmetic below
         const uint32_t nj = cols >> 5;  // columns lane + 32 j, j < nj, exist
         const float4 w0 = *reinterpret_cast<const float4*>(ws[warp][0][lane]);
         const float4 w1 = *reinterpret_cast<const float4*>(ws[warp][1][lane]);
         const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int tok = 0; tok < kRouterTT; ++tok) {
+        for (int tok = 0; tok < TT; ++tok) {
             const float4 a0 = *reinterpret_cast<const float4*>(xs[tok][0][lane]);
             const float4 a1 = *reinterpret_cast<const float4*>(xs[tok][1][lane]);
             const float xv[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
@@ -89,7 +97,7 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     }
     if (!e_ok) return;
 #pragma unroll
-    for (int tok = 0; tok < kRouterTT; ++tok) {
+    for (int tok = 0; tok < TT; ++tok) {
         float v = sum[tok];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
@@ -100,14 +108,17 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
 void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
                           uint32_t E, float* logits, cudaStream_t s) {
     if (T == 0) return;
-    const uint32_t ty = (T + kRouterTT - 1) / kRouterTT;
-    // few tokens: spread expert rows over more CTAs; many tokens: 8 rows share one staged tile
-    if ((size_t)ty * ((E + 7) / 8) < 2u * kNumSMs) {
-        dim3 grid((E + 1) / 2, ty);
-        router_logits_kernel<2><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+    // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
+    // many tokens: 8 rows share one staged 16-token tile
+    if (T <= 8) {
+        dim3 grid((E + 1) / 2, 1);
+        router_logits_kernel<2, 8><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+    } else if ((size_t)((T + 15) / 16) * ((E + 7) / 8) < 2u * kNumSMs) {
+        dim3 grid((E + 1) / 2, (T + 15) / 16);
+        router_logits_kernel<2, 16><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
     } else {
-        dim3 grid((E + 7) / 8, ty);
-        router_logits_kernel<8><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
+        dim3 grid((E + 7) / 8, (T + 15) / 16);
+        router_logits_kernel<8, 16><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
     }
     ++g_kernel_launches;
 }
