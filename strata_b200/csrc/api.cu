@@ -1,6 +1,7 @@
 // Host side of the C ABI declared in include/strata_moe.h: contexts, resident weights,
 // workspaces and the launch sequence of one MoE layer.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -49,6 +50,8 @@ struct DeviceTable {
     const uint8_t** d_packed = nullptr;
     const uint8_t** d_scales = nullptr;
     float* d_global = nullptr;
+    uint32_t* d_emin = nullptr;   // f16 path tables
+    float* d_post = nullptr;
 };
 
 struct strata_moe_layer {
@@ -77,6 +80,10 @@ struct strata_moe_layer {
     float* out_stage = nullptr;
     void* prefill_scratch = nullptr;
     float* one_global = nullptr;  // device float 1.0 for the shared expert table
+    // f16 decode path for the FP4 formats
+    bool f16_ok = false;
+    uint32_t* d_not_ok = nullptr;
+    float *act_f32 = nullptr, *x_rowscale = nullptr, *act_rowscale = nullptr;
     // dense command state
     bool dense_in_flight = false;
     uint32_t dense_rows = 0, dense_n = 0;
@@ -140,6 +147,35 @@ int sync_tables(strata_moe_layer* L) {
                            ctx->stream));
     }
     CK(cudaStreamSynchronize(ctx->stream));  // the host vectors may change after this returns
+    // f16 weight-streaming path: NVFP4 always qualifies; MXFP4 when every projection's scale
+    // bytes fit one exponent window
+    L->f16_ok = false;
+    if (L->d.format == STRATA_MOE_FMT_NVFP4) {
+        for (int r = 0; r < 3; ++r) {
+            std::vector<float> post(n);
+            for (uint32_t e = 0; e < n; ++e) post[e] = 1.0f / L->tab[r].global[e];
+            CK(cudaMemcpy(L->tab[r].d_post, post.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+        }
+        L->f16_ok = true;
+    } else if (L->d.format == STRATA_MOE_FMT_MXFP4) {
+        bool complete = true;
+        for (int r = 0; r < 3; ++r)
+            for (uint32_t e = 0; e < n; ++e) complete &= L->tab[r].scales[e] != nullptr;
+        if (complete) {
+            CK(cudaMemsetAsync(L->d_not_ok, 0, sizeof(uint32_t), ctx->stream));
+            for (int r = 0; r < 3; ++r) {
+                const uint32_t rows = r == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
+                const uint32_t cols = r == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+                launch_mx_scale_range(L->tab[r].d_scales, n, scale_bytes(L->d.format, rows, cols),
+                                      L->tab[r].d_emin, L->tab[r].d_post, L->d_not_ok, ctx->stream);
+            }
+            uint32_t not_ok = 1;
+            CK(cudaMemcpyAsync(&not_ok, L->d_not_ok, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+            CK(cudaStreamSynchronize(ctx->stream));
+            L->f16_ok = not_ok == 0;
+        }
+    }
+    if (getenv("STRATA_MOE_NO_F16_PATH")) L->f16_ok = false;
     L->tables_dirty = false;
     return 0;
 }
@@ -149,6 +185,8 @@ WeightTable wt(const DeviceTable& t) {
     w.packed = t.d_packed;
     w.scales = t.d_scales;
     w.global_scale = t.d_global;
+    w.emin = t.d_emin;
+    w.post_scale = t.d_post;
     return w;
 }
 
@@ -211,8 +249,6 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         CK(cudaGetLastError());
         return 0;
     }
-    launch_gather_rows_kperm(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
-    mark(ctx, 4);
     DecodeArgs a{};
     a.fmt = L->d.format;
     a.H = L->d.hidden;
@@ -232,6 +268,23 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     a.act_lo = L->act_lo;
     a.y = y;
     a.status = ctx->d_status;
+    if (L->f16_ok) {
+        a.x_rowscale = L->x_rowscale;
+        a.act_f32 = L->act_f32;
+        a.act_rowscale = L->act_rowscale;
+        launch_rows_to_f16_bf16(x_src, perm, k_div, pairs, L->d.hidden, L->xg, L->x_rowscale, s);
+        mark(ctx, 4);
+        launch_decode_fp4_gate_up(a, s);
+        mark(ctx, 5);
+        launch_rows_to_f16_f32(L->act_f32, 0, pairs, L->d.intermediate, L->act_hi, L->act_lo,
+                               L->act_rowscale, s);
+        launch_decode_fp4_down(a, s);
+        mark(ctx, 6);
+        CK(cudaGetLastError());
+        return 0;
+    }
+    launch_gather_rows_kperm(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
+    mark(ctx, 4);
     launch_decode_gate_up(a, s);
     mark(ctx, 5);
     launch_decode_down(a, s);
@@ -420,6 +473,8 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         A(dalloc(L, &t.d_packed, n));
         A(dalloc(L, &t.d_scales, n));
         A(dalloc(L, &t.d_global, n));
+        A(dalloc(L, &t.d_emin, n));
+        A(dalloc(L, &t.d_post, n));
         A(dalloc(L, &L->d_shared_ptr[r], 1));
     }
     A(dalloc(L, &L->logits, (size_t)T * E));
@@ -448,6 +503,10 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
     A(dalloc(L, &L->act_lo, (size_t)P * I));
     A(dalloc(L, &L->y, (size_t)P * H));
     A(dalloc(L, &L->one_global, 1));
+    A(dalloc(L, &L->d_not_ok, 1));
+    A(dalloc(L, &L->act_f32, (size_t)P * I));
+    A(dalloc(L, &L->x_rowscale, (size_t)P));
+    A(dalloc(L, &L->act_rowscale, (size_t)P));
     if (d.shared_intermediate) {
         A(dalloc(L, &L->sh_act_hi, (size_t)T * d.shared_intermediate));
         A(dalloc(L, &L->sh_act_lo, (size_t)T * d.shared_intermediate));
@@ -696,10 +755,22 @@ int strata_moe_dequant_export(strata_moe_layer* L, uint32_t expert, int role, fl
     CK(cudaSetDevice(ctx->device));
     const uint32_t rows = role == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
     const uint32_t cols = role == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+    int rc0 = sync_tables(L);
+    if (rc0) return rc0;
     float* tmp = nullptr;
     CK(cudaMalloc(&tmp, (size_t)rows * cols * 4));
-    launch_dequant_export(L->d.format, L->tab[role].packed[le], L->tab[role].scales[le],
-                          L->tab[role].global[le], rows, cols, tmp, ctx->stream);
+    if (L->f16_ok) {
+        // export what the f16 weight-streaming kernels consume
+        uint32_t emin = 0;
+        float post = 1.0f;
+        CK(cudaMemcpy(&emin, L->tab[role].d_emin + le, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+        CK(cudaMemcpy(&post, L->tab[role].d_post + le, sizeof(float), cudaMemcpyDeviceToHost));
+        launch_dequant_export_f16(L->d.format, L->tab[role].packed[le], L->tab[role].scales[le], emin, post,
+                                  rows, cols, tmp, ctx->stream);
+    } else {
+        launch_dequant_export(L->d.format, L->tab[role].packed[le], L->tab[role].scales[le],
+                              L->tab[role].global[le], rows, cols, tmp, ctx->stream);
+    }
     cudaError_t e = cudaMemcpyAsync(out_host, tmp, (size_t)rows * cols * 4, cudaMemcpyDeviceToHost, ctx->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
     cudaFree(tmp);

@@ -30,6 +30,8 @@ struct WeightTable {
     const uint8_t* const* packed;  // [n_local] device array of device pointers
     const uint8_t* const* scales;  // [n_local]
     const float* global_scale;     // [n_local] NVFP4 divisor (1 otherwise)
+    const uint32_t* emin;          // [n_local] MXFP4 f16 path: smallest E8M0 byte of the projection
+    const float* post_scale;       // [n_local] f16 path: factor applied to the fp32 accumulator
 };
 
 // ---- launch wrappers (definitions in the .cu files) ---------------------------------
@@ -68,7 +70,21 @@ struct DecodeArgs {
     __nv_bfloat16* act_lo;
     float* y;                      // [pairs, H]
     uint32_t* status;
+    // f16 path (decode_fp4.cu): activations as f16 with a per-row power-of-two pre-scale
+    const float* x_rowscale;       // [pairs] factor that undoes the pre-scale of x
+    float* act_f32;                // [pairs, I] SwiGLU output before its f16 split
+    const float* act_rowscale;     // [pairs]
 };
+void launch_decode_fp4_gate_up(const DecodeArgs& a, cudaStream_t s);
+void launch_decode_fp4_down(const DecodeArgs& a, cudaStream_t s);
+void launch_rows_to_f16_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows,
+                             uint32_t C, void* hi, float* rowscale, cudaStream_t s);
+void launch_rows_to_f16_f32(const float* x, uint32_t src_rows, uint32_t rows, uint32_t C, void* hi, void* lo,
+                            float* rowscale, cudaStream_t s);
+void launch_mx_scale_range(const uint8_t* const* scales, uint32_t n, size_t bytes, uint32_t* emin,
+                           float* post_scale, uint32_t* not_ok, cudaStream_t s);
+void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* scales, uint32_t emin,
+                               float post_scale, uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
 void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_down(const DecodeArgs& a, cudaStream_t s);
 // combine.cu

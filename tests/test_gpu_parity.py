@@ -68,11 +68,17 @@ def test_small_layer_matches_oracle(ctx, cfg):
     assert rel <= TIGHT_REL_L2, rel
 
 
-@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4, synth.FMT_INT4])
-def test_dequantised_weights_bit_exact(ctx, fmt):
+@pytest.mark.parametrize("fmt,wide", [(synth.FMT_MXFP4, True), (synth.FMT_MXFP4, False),
+                                      (synth.FMT_NVFP4, True), (synth.FMT_INT4, False)])
+def test_dequantised_weights_bit_exact(ctx, fmt, wide):
+    # wide MXFP4 scales force the general BF16 decoders; narrow ones take the f16 path
     cfg = small(fmt, H=256, I=128, E=4, k=2, name=f"deq{fmt}")
     layer = synth.build_layer(cfg, "cuda")
-    if fmt == synth.FMT_MXFP4:
+    if fmt == synth.FMT_MXFP4 and not wide:
+        for role in synth.ROLES:
+            s = layer.scales[role]
+            layer.scales[role] = (torch.arange(s.numel(), device="cuda") % 27 + 100).to(torch.uint8).view_as(s)
+    if fmt == synth.FMT_MXFP4 and wide:
         # widen the scale spread over every legal E8M0 byte, including block scales >= 4
         for role in synth.ROLES:
             s = layer.scales[role]
@@ -170,3 +176,16 @@ def test_large_group_path_matches_small_path(ctx):
     n = int(roffsets[48] - roffsets[16])
     assert np.array_equal(c2.cpu().numpy().astype(np.uint32), rcounts[16:48])
     assert np.array_equal(p2.cpu().numpy().astype(np.uint32)[:n], rperm[roffsets[16]:roffsets[48]])
+
+
+@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4])
+def test_general_bf16_decoder_path(ctx, fmt, monkeypatch):
+    # the FP4 formats normally take the f16 weight-streaming kernels; an expert whose MXFP4
+    # scales span more than 26 octaves falls back to the general BF16 decoders, forced here
+    monkeypatch.setenv("STRATA_MOE_NO_F16_PATH", "1")
+    cfg = small(fmt, T=11, name=f"general{fmt}")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= TIGHT_REL_L2 and mx <= MAX_ABS
