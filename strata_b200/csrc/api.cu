@@ -11,24 +11,6 @@
 
 using namespace smoe;
 
-namespace smoe {
-// prefill.cu (tcgen05 grouped GEMM path); returns false when the shape is not supported by it.
-bool prefill_supported(int fmt, uint32_t H, uint32_t I);
-struct PrefillArgs {
-    int fmt;
-    uint32_t H, I, n_groups, pairs;
-    const uint32_t* offsets;
-    WeightTable gate, up, down;
-    const __nv_bfloat16* x;   // [pairs, H] natural layout, group order
-    __nv_bfloat16* act;       // [pairs, I] natural layout
-    float* y;                 // [pairs, H]
-    uint32_t* tile_table;     // scratch
-    uint32_t* status;
-};
-size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
-int launch_prefill(const PrefillArgs& a, cudaStream_t s, cudaEvent_t mid);
-}  // namespace smoe
-
 struct strata_moe_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -214,7 +196,10 @@ bool all_registered(const strata_moe_layer* L, std::string* why) {
 // rows-per-expert threshold between the weight-streaming path and the tensor-core tile path
 bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
     if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) return false;
-    return (uint64_t)pairs >= (uint64_t)n_groups * 24u;
+    if (L->d.format == STRATA_MOE_FMT_MXFP4 && !L->f16_ok) return false;  // needs the f16 weight window
+    const char* e = getenv("STRATA_MOE_PREFILL_MIN_ROWS");  // average rows per expert that switch paths
+    const int thr = e ? atoi(e) : 24;
+    return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
@@ -226,7 +211,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     cudaStream_t s = ctx->stream;
     if (pairs == 0) return 0;
     if (use_prefill(L, pairs, n_groups)) {
-        launch_gather_rows_plain(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
+        launch_rows_to_f16_bf16(x_src, perm, k_div, pairs, L->d.hidden, L->xg, L->x_rowscale, s);
         mark(ctx, 4);
         PrefillArgs p{};
         p.fmt = L->d.format;
@@ -238,12 +223,11 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.gate = wt(L->tab[0]);
         p.up = wt(L->tab[1]);
         p.down = wt(L->tab[2]);
-        p.x = L->xg;
-        p.act = L->act_hi;
         p.y = y;
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
-        if (launch_prefill(p, s, ctx->timing ? ctx->pev[5] : nullptr) != 0)
+        if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, s,
+                           ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
         mark(ctx, 6);
         CK(cudaGetLastError());

@@ -87,6 +87,22 @@ void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* sc
                                float post_scale, uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
 void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_down(const DecodeArgs& a, cudaStream_t s);
+// prefill.cu : large-batch expert FFN (tcgen05 grouped GEMM path)
+struct PrefillArgs {
+    int fmt;
+    uint32_t H, I, n_groups, pairs;
+    const uint32_t* offsets;       // [n_groups + 1]
+    WeightTable gate, up, down;
+    float* y;                      // [pairs, H] fp32
+    uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
+    uint32_t* status;
+};
+bool prefill_supported(int fmt, uint32_t H, uint32_t I);
+size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
+// x16: [pairs_cap, H] f16 rows (pre-scaled, group order), x_rowscale [pairs_cap], act16:
+// [pairs_cap, I] f16 scratch.  mid, when non-null, is recorded between the two GEMMs.
+int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                   uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid);
 // combine.cu
 void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
                     uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,

@@ -1,10 +1,568 @@
-// Placeholder until the tcgen05 grouped-GEMM path lands: reports "not supported" so every
-// shape takes the weight-streaming path.
+// Large-batch ("prefill") expert FFN: grouped GEMMs on the 5th-generation tensor cores.
+//
+// Orientation: the WEIGHTS are the M operand (128 output features per tile) and the expert's
+// token rows are the N operand (up to 128 per tile, any multiple of 16), so ragged expert
+// groups cost at most 15 padded rows instead of a padded 128-row tile.  D (FP32) lives in
+// tensor memory: lane = output feature, column = token.
+//
+//   warp 0        TMA producer: activation tiles [N x 64] f16 -> shared memory (128-byte swizzle)
+//   warp 1        MMA issuer: one thread issues tcgen05.mma (kind::f16, M=128, K=16) per k-slice
+//   warps 2..9    weight producers: stream packed 4-bit rows from HBM (32 B per row per stage),
+//                 decode exactly to f16 (hardware E2M1 conversion / INT4 magic-number trick),
+//                 apply the block scale and store the tile K-major with the 128-byte swizzle the
+//                 MMA descriptor expects
+//   warps 10..13  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
+//                 scale (down), store
+// Accumulators are double-buffered in tensor memory (2 x 256 columns), so the epilogue of one
+// tile overlaps the main loop of the next.  CTAs are persistent (one per SM) and walk a tile
+// list built on the device from the per-expert offsets.
+//
+// Every wait is bounded: on expiry the kernel raises kStatusWaitTimeout, all roles leave their
+// loops, tensor memory is released and the kernel returns normally.
+//
+// Replaces the reference's per-row page kernels (kernels/cuda/backend.cu:2439-2582, 2600-2779)
+// and the per-expert matmul fallbacks (kernels/cuda/backend.cu:1140-1207).
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace smoe {
-struct PrefillArgs;
-bool prefill_supported(int, uint32_t, uint32_t) { return false; }
-size_t prefill_scratch_bytes(uint32_t, uint32_t) { return 0; }
-int launch_prefill(const PrefillArgs&, cudaStream_t, cudaEvent_t) { return -1; }
+
+constexpr uint32_t kNTile = 128;    // tokens per tile
+constexpr uint32_t kMTile = 128;    // output features per tile
+constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
+constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
+constexpr uint32_t kThreads = 14 * 32;
+constexpr uint32_t kDequantThreads = 256;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+// ------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+// Bounded wait: false when the phase did not complete within the spin limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint32_t x, uint32_t y,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);       // start address
+    d |= (uint64_t)1 << 16;                         // leading byte offset: unused for swizzled K-major
+    d |= (uint64_t)(1024u >> 4) << 32;              // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                         // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                         // 128-byte swizzle
+    return d;
+}
+// Instruction descriptor, kind::f16: F16 x F16 -> F32, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n) {
+    uint32_t d = 0;
+    d |= 1u << 4;               // D format F32
+    d |= 0u << 7;               // A format F16
+    d |= 0u << 10;              // B format F16
+    d |= (n >> 3) << 17;        // N
+    d |= (kMTile >> 4) << 24;   // M
+    return d;
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,"
+        "%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 ldg_stream16_c(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+// ------------------------------------------------------------------------------ decoders (f16)
+__device__ __forceinline__ void p_e2m1x8_f16(uint32_t w, uint32_t r[4]) {
+    asm("{\n .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n"
+        " cvt.rn.f16x2.e2m1x2 %0, b0;\n cvt.rn.f16x2.e2m1x2 %1, b1;\n"
+        " cvt.rn.f16x2.e2m1x2 %2, b2;\n cvt.rn.f16x2.e2m1x2 %3, b3;\n}"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+        : "r"(w));
+}
+__device__ __forceinline__ uint32_t p_mul_f16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t p_sub_f16x2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+// 8 offset-binary INT4 nibbles -> 4 f16x2 of (q - 8) in natural column order.
+// 0x6400 | q is the f16 number 1024 + q; the zero bytes come from PRMT's sign-replicate mode
+// applied to bytes whose top bit is clear.
+__device__ __forceinline__ void p_int4x8_f16(uint32_t w, uint32_t r[4]) {
+    const uint32_t lo = w & 0x0F0F0F0Fu;         // nibbles 0,2,4,6
+    const uint32_t hi = (w >> 4) & 0x0F0F0F0Fu;  // nibbles 1,3,5,7
+    const uint32_t k1032 = 0x64086408u;
+    r[0] = p_sub_f16x2(__byte_perm(lo, hi, 0x8480) | 0x64006400u, k1032);
+    r[1] = p_sub_f16x2(__byte_perm(lo, hi, 0x8581) | 0x64006400u, k1032);
+    r[2] = p_sub_f16x2(__byte_perm(lo, hi, 0x8682) | 0x64006400u, k1032);
+    r[3] = p_sub_f16x2(__byte_perm(lo, hi, 0x8783) | 0x64006400u, k1032);
+}
+
+// One row's 16 packed bytes (32 columns) -> 4 x 16-byte f16 chunks, scaled.
+// m[c] multiplies chunk c (8 columns).
+template <int FMT>
+__device__ __forceinline__ void decode16(const uint4& p, const uint32_t m[4], uint4 out[4]) {
+    const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        uint32_t r[4];
+        if (FMT == STRATA_MOE_FMT_INT4G128) p_int4x8_f16(w[c], r);
+        else p_e2m1x8_f16(w[c], r);
+        out[c] = make_uint4(p_mul_f16x2(r[0], m[c]), p_mul_f16x2(r[1], m[c]), p_mul_f16x2(r[2], m[c]),
+                            p_mul_f16x2(r[3], m[c]));
+    }
+}
+
+struct TileInfo {
+    uint32_t g, row0, n;  // expert, first row of this n-tile, valid rows (1..kNTile)
+    uint32_t m0;          // first output feature
+};
+
+struct __align__(1024) PrefillSmem {
+    uint8_t a0[kStages][kATile];  // gate (or down) weight tile
+    uint8_t a1[kStages][kATile];  // up weight tile (gate/up kernel only)
+    uint8_t b[kStages][kBTile];   // activation tile
+    uint64_t full_a[kStages], full_b[kStages], empty[kStages];
+    uint64_t acc_full[2], acc_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+__device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile, uint32_t m_tiles, TileInfo& t) {
+    const uint32_t total = table[0] * m_tiles;
+    if (tile >= total) return false;
+    const uint32_t j = tile / m_tiles;
+    t.g = table[4 + 3 * j];
+    t.row0 = table[4 + 3 * j + 1];
+    t.n = table[4 + 3 * j + 2];
+    t.m0 = (tile - j * m_tiles) * kMTile;
+    return true;
+}
+
+// DUAL = true : gate + up tiles, SwiGLU, act (f16) out.   K = H, features over I.
+// DUAL = false: down tile, y (fp32) out.                    K = I, features over H.
+template <int FMT, bool DUAL>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, const float* __restrict__ rowscale,
+                   __half* __restrict__ act_out) {
+    extern __shared__ uint8_t smem_raw[];
+    PrefillSmem& S = *reinterpret_cast<PrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t K = DUAL ? a.H : a.I;
+    const uint32_t R = DUAL ? a.I : a.H;
+    const uint32_t m_tiles = R / kMTile;
+    const uint32_t k_stages = K / kBK;
+    volatile uint32_t* abort_flag = &S.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(&S.full_a[s], kDequantThreads / 32);  // one arrival per producer warp
+            mbar_init(&S.full_b[s], 1);
+            mbar_init(&S.empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&S.acc_full[i], 1);
+            mbar_init(&S.acc_empty[i], 4);  // one arrival per epilogue warp
+        }
+        S.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {  // tensor-memory allocation: all 512 columns (one CTA per SM)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&S.tmem_base)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = S.tmem_base;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
+                TileInfo t;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+                for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&S.full_b[s], kBTile);
+                    tma_load_2d(S.b[s], &map_b, ks * kBK, t.row0, &S.full_b[s]);
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
+            if (*abort_flag) {
+                // copies issued but possibly not consumed: give each a bounded chance to land
+                // before the CTA's shared memory is released
+                const uint32_t pending = it < kStages ? it : kStages;
+                for (uint32_t q = 0; q < pending; ++q) {
+                    const uint32_t j = it - 1u - q;
+                    const uint32_t addr = smem_u32(&S.full_b[j % kStages]);
+                    for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+                        uint32_t done;
+                        asm volatile(
+                            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                            " selp.u32 %0, 1, 0, p;\n}"
+                            : "=r"(done)
+                            : "r"(addr), "r"((j / kStages) & 1u)
+                            : "memory");
+                        if (done) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
+                TileInfo t;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+                const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+                if (!mbar_wait(&S.acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t n = (t.n + 15u) & ~15u;
+                const uint32_t idesc = umma_idesc_f16(n);
+                const uint32_t d0 = tmem_base + buf * 256u, d1 = d0 + kNTile;
+                for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    if (!mbar_wait(&S.full_a[s], ph, abort_flag) || !mbar_wait(&S.full_b[s], ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a0 = smem_u32(S.a0[s]), a1 = smem_u32(S.a1[s]), b = smem_u32(S.b[s]);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
+                        const uint64_t bd = umma_desc_sw128(b + kk * 32u);
+                        umma_f16(d0, umma_desc_sw128(a0 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
+                        if (DUAL) umma_f16(d1, umma_desc_sw128(a1 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
+                    }
+                    umma_commit(&S.empty[s]);  // frees the stage once these MMAs have read it
+                }
+                if (ok) umma_commit(&S.acc_full[buf]);
+            }
+            if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
+        }
+    } else if (warp < 10) {
+        // ---------------------------------------------------------------- weight producers
+        const uint32_t d = threadIdx.x - 64u;  // 0..255
+        // DUAL: thread d decodes row d % 128 of gate (d < 128) or up (d >= 128), 64 columns.
+        // else: thread d decodes row d / 2 of down, 32 columns (half d % 2).
+        const uint32_t arow = DUAL ? (d & 127u) : (d >> 1);
+        const uint32_t which = DUAL ? (d >> 7) : 0u;
+        const uint32_t half = DUAL ? 0u : (d & 1u);
+        constexpr uint32_t CH = DUAL ? 2u : 1u;  // 16-byte packed chunks per thread per stage
+        uint32_t it = 0;
+        bool ok = true;
+        for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
+            TileInfo t;
+            if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+            const WeightTable& wt = DUAL ? (which ? a.up : a.gate) : a.down;
+            const uint32_t row = t.m0 + arow;
+            const uint8_t* prow = wt.packed[t.g] + (size_t)row * (K / 2u) + half * 16u;
+            const uint8_t* srow = wt.scales[t.g];
+            int32_t mx_off = 0;
+            if (FMT == STRATA_MOE_FMT_MXFP4) {
+                srow += (size_t)row * (K / 32u);
+                mx_off = 2 - (int32_t)wt.emin[t.g];
+            } else if (FMT == STRATA_MOE_FMT_NVFP4) {
+                srow += (size_t)row * (K / 16u);
+            } else {
+                srow += (size_t)row * (K / 128u) * 2u;
+            }
+            uint4 cur[CH], nxt[CH];
+#pragma unroll
+            for (uint32_t c = 0; c < CH; ++c) cur[c] = ldg_stream16_c(prow + c * 16u);
+            for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
+                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                const uint32_t kn = ks + 1u < k_stages ? ks + 1u : ks;
+#pragma unroll
+                for (uint32_t c = 0; c < CH; ++c) nxt[c] = ldg_stream16_c(prow + (size_t)kn * 32u + c * 16u);
+                // block multipliers of this thread's 32-column chunks
+                uint32_t m[CH][4];
+#pragma unroll
+                for (uint32_t c = 0; c < CH; ++c) {
+                    const uint32_t col32 = ks * 2u + (DUAL ? c : half);  // index of the 32-column chunk
+                    if (FMT == STRATA_MOE_FMT_MXFP4) {
+                        const uint32_t e = __ldg(srow + col32);
+                        const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
+                        m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
+                    } else if (FMT == STRATA_MOE_FMT_NVFP4) {
+                        const uint32_t sb = __ldg(reinterpret_cast<const unsigned short*>(srow + col32 * 2u));
+                        uint32_t pair;
+                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)sb));
+                        m[c][0] = m[c][1] = __byte_perm(pair, pair, 0x1010);
+                        m[c][2] = m[c][3] = __byte_perm(pair, pair, 0x3232);
+                    } else {
+                        const uint32_t sb = __ldg(reinterpret_cast<const unsigned short*>(srow + (col32 >> 2) * 2u));
+                        const uint32_t h = __half_as_ushort(__float2half_rn(__uint_as_float(sb << 16)));
+                        m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
+                    }
+                }
+                if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
+#pragma unroll
+                for (uint32_t c = 0; c < CH; ++c) {
+                    uint4 o[4];
+                    decode16<FMT>(cur[c], m[c], o);
+                    const uint32_t chunk0 = (DUAL ? c : half) * 4u;  // first 16-byte chunk (8 columns each)
+#pragma unroll
+                    for (uint32_t q = 0; q < 4; ++q)
+                        *reinterpret_cast<uint4*>(tile_base + (((chunk0 + q) ^ (arow & 7u)) << 4)) = o[q];
+                }
+                fence_async_smem();  // make the generic-proxy stores visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&S.full_a[s]);
+#pragma unroll
+                for (uint32_t c = 0; c < CH; ++c) cur[c] = nxt[c];
+            }
+        }
+        if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const uint32_t ew = warp - 10u;          // == warp % 4: tensor-memory lane quarter
+        const uint32_t lane_base = (warp & 3u) * 32u;
+        uint32_t tcount = 0;
+        bool ok = true, bad = false;
+        (void)ew;
+        for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
+            TileInfo t;
+            if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+            const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
+            if (!mbar_wait(&S.acc_full[buf], aph, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t feat = t.m0 + lane_base + lane;
+            float s0, s1 = 1.0f;
+            if (DUAL) {
+                s0 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.gate.post_scale[t.g];
+                s1 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.up.post_scale[t.g];
+            } else {
+                s0 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.down.post_scale[t.g];
+            }
+            const uint32_t taddr = tmem_base + (lane_base << 16) + buf * 256u;
+            for (uint32_t c0 = 0; c0 < t.n; c0 += 32u) {
+                uint32_t g[32], u[32];
+                tmem_ld32(taddr + c0, g);
+                if (DUAL) tmem_ld32(taddr + kNTile + c0, u);
+                tmem_ld_wait();
+#pragma unroll
+                for (uint32_t j = 0; j < 32u; ++j) {
+                    if (c0 + j >= t.n) break;
+                    const size_t pos = (size_t)t.row0 + c0 + j;
+                    if (DUAL) {
+                        const float rs = rowscale[pos];
+                        const float gv = __uint_as_float(g[j]) * s0 * rs, uv = __uint_as_float(u[j]) * s1 * rs;
+                        const float e = __expf(-fabsf(gv));
+                        const float sig = gv >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
+                        const float v = gv * sig * uv;
+                        if (!(fabsf(v) <= 65504.0f)) bad = true;
+                        act_out[pos * R + feat] = __float2half_rn(v);
+                    } else {
+                        const float v = __uint_as_float(g[j]) * s0;
+                        if (!(fabsf(v) <= 3.0e38f)) bad = true;
+                        a.y[pos * R + feat] = v;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
+        }
+        if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
+        if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------ tile list
+// table[0] = number of n-tiles, then (expert, first row, rows) per n-tile, experts ascending.
+__global__ void __launch_bounds__(1024) prefill_tiles_kernel(const uint32_t* __restrict__ offsets, uint32_t n_groups,
+                                                             uint32_t* __restrict__ table) {
+    __shared__ uint32_t scan[1024];
+    const uint32_t tid = threadIdx.x;
+    uint32_t cnt = 0, r0 = 0;
+    if (tid < n_groups) {
+        r0 = offsets[tid];
+        cnt = offsets[tid + 1] - r0;
+    }
+    const uint32_t mine = (cnt + kNTile - 1) / kNTile;
+    scan[tid] = mine;
+    __syncthreads();
+    for (uint32_t off = 1; off < 1024u; off <<= 1) {
+        const uint32_t v = tid >= off ? scan[tid - off] : 0u;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    const uint32_t base = scan[tid] - mine;
+    for (uint32_t i = 0; i < mine; ++i) {
+        table[4 + 3 * (base + i)] = tid;
+        table[4 + 3 * (base + i) + 1] = r0 + i * kNTile;
+        table[4 + 3 * (base + i) + 2] = min(kNTile, cnt - i * kNTile);
+    }
+    if (tid == 1023u) table[0] = scan[1023];
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// f16 matrix [rows, cols] row-major; box = 64 columns x kNTile rows, 128-byte swizzle.
+static bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2] = {kBK, kNTile};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool prefill_supported(int fmt, uint32_t H, uint32_t I) {
+    if (getenv("STRATA_MOE_NO_PREFILL_PATH")) return false;
+    if (fmt < 0 || fmt > STRATA_MOE_FMT_INT4G128) return false;
+    return H % 128u == 0 && I % 128u == 0 && encode_fn() != nullptr;
+}
+
+size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs) {
+    return (4 + 3 * ((size_t)pairs / kNTile + n_groups + 1)) * sizeof(uint32_t);
+}
+
+struct PrefillPlan {
+    const void* x16;          // [pairs_cap, H] f16 (pre-scaled rows)
+    const float* x_rowscale;  // [pairs_cap]
+    void* act16;              // [pairs_cap, I] f16
+    uint32_t pairs_cap;
+};
+
+template <int FMT>
+static int launch_fmt(const PrefillArgs& a, const PrefillPlan& p, cudaStream_t s, cudaEvent_t mid) {
+    CUtensorMap map_x, map_act;
+    if (!make_map(&map_x, p.x16, p.pairs_cap, a.H) || !make_map(&map_act, p.act16, p.pairs_cap, a.I)) return -1;
+    const size_t smem = sizeof(PrefillSmem) + 1024;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[0]) {
+        if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return -2;
+        if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess)
+            return -2;
+        attr_set[0] = true;
+    }
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, a, p.x_rowscale,
+                                                                  static_cast<__half*>(p.act16));
+    if (mid) cudaEventRecord(mid, s);
+    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, a, nullptr, nullptr);
+    g_kernel_launches += 3;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                   uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid) {
+    PrefillPlan p{x16, x_rowscale, act16, pairs_cap};
+    switch (a.fmt) {
+        case STRATA_MOE_FMT_MXFP4: return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, p, s, mid);
+        case STRATA_MOE_FMT_NVFP4: return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, p, s, mid);
+        case STRATA_MOE_FMT_INT4G128: return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, p, s, mid);
+        default: return -1;
+    }
+}
+
 }  // namespace smoe

@@ -189,3 +189,41 @@ def test_general_bf16_decoder_path(ctx, fmt, monkeypatch):
     assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
     rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
     assert rel <= TIGHT_REL_L2 and mx <= MAX_ABS
+
+
+PREFILL_TIGHT = 2e-3   # the tensor-core path keeps the SwiGLU output in f16 (11-bit significand)
+
+
+@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4, synth.FMT_INT4])
+def test_prefill_path_matches_oracle(ctx, fmt):
+    # 600 tokens x top-2 over 8 experts: ~150 rows per expert -> tcgen05 grouped GEMM path,
+    # ragged groups (row counts that are not multiples of 16 or 128)
+    cfg = small(fmt, T=600, E=8, k=2, H=512, I=256, name=f"prefill{fmt}",
+                I_shared=0, norm_init=1e-20 if fmt == synth.FMT_INT4 else 0.0)
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= REL_L2 and mx <= MAX_ABS
+    assert rel <= PREFILL_TIGHT, rel
+
+
+def test_prefill_path_tiny_and_empty_groups(ctx, monkeypatch):
+    # force the tensor-core path on a page where most experts get 0-3 rows
+    monkeypatch.setenv("STRATA_MOE_PREFILL_MIN_ROWS", "0")
+    cfg = small(synth.FMT_NVFP4, T=5, E=16, k=2, H=256, I=128, name="prefill_tiny")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= PREFILL_TIGHT and mx <= MAX_ABS
+
+
+def test_prefill_and_streaming_paths_agree(ctx, monkeypatch):
+    cfg = small(synth.FMT_MXFP4, T=300, E=8, k=2, H=512, I=256, name="paths")
+    layer, ml, out_tc, _ = run_layer(ctx, cfg)
+    monkeypatch.setenv("STRATA_MOE_NO_PREFILL_PATH", "1")
+    out_stream = ml.forward(layer.x)
+    ctx.synchronize()
+    rel, mx = Hh.error_metrics(out_tc.cpu().numpy(), out_stream.cpu().numpy())
+    assert rel <= PREFILL_TIGHT
