@@ -155,16 +155,23 @@ __device__ __forceinline__ uint32_t p_sub_f16x2(uint32_t a, uint32_t b) {
     return d;
 }
 // 8 offset-binary INT4 nibbles -> 4 f16x2 of (q - 8) in natural column order.
-// 0x6400 | q is the f16 number 1024 + q; the zero bytes come from PRMT's sign-replicate mode
-// applied to bytes whose top bit is clear.
+// Byte permutes gather adjacent nibbles and splice in the high byte 0x64: 0x6400 | q is the f16
+// number 1024 + q, and subtracting 1032 leaves q - 8 exactly.
+__device__ __forceinline__ uint32_t p_prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
 __device__ __forceinline__ void p_int4x8_f16(uint32_t w, uint32_t r[4]) {
-    const uint32_t lo = w & 0x0F0F0F0Fu;         // nibbles 0,2,4,6
-    const uint32_t hi = (w >> 4) & 0x0F0F0F0Fu;  // nibbles 1,3,5,7
-    const uint32_t k1032 = 0x64086408u;
-    r[0] = p_sub_f16x2(__byte_perm(lo, hi, 0x8480) | 0x64006400u, k1032);
-    r[1] = p_sub_f16x2(__byte_perm(lo, hi, 0x8581) | 0x64006400u, k1032);
-    r[2] = p_sub_f16x2(__byte_perm(lo, hi, 0x8682) | 0x64006400u, k1032);
-    r[3] = p_sub_f16x2(__byte_perm(lo, hi, 0x8783) | 0x64006400u, k1032);
+    const uint32_t lo = w & 0x0F0F0F0Fu;          // nibbles 0,2,4,6
+    const uint32_t hi = (w >> 4) & 0x0F0F0F0Fu;   // nibbles 1,3,5,7
+    const uint32_t n03 = p_prmt(lo, hi, 0x5140u);  // bytes n0,n1,n2,n3
+    const uint32_t n47 = p_prmt(lo, hi, 0x7362u);  // bytes n4,n5,n6,n7
+    const uint32_t k64 = 0x00000064u, k1032 = 0x64086408u;
+    r[0] = p_sub_f16x2(p_prmt(n03, k64, 0x4140u), k1032);
+    r[1] = p_sub_f16x2(p_prmt(n03, k64, 0x4342u), k1032);
+    r[2] = p_sub_f16x2(p_prmt(n47, k64, 0x4140u), k1032);
+    r[3] = p_sub_f16x2(p_prmt(n47, k64, 0x4342u), k1032);
 }
 
 // One row's 16 packed bytes (32 columns) -> 4 x 16-byte f16 chunks, scaled.
