@@ -291,6 +291,8 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="multi-GPU: weak = --tokens per rank (default), strong = --tokens in total")
     args = ap.parse_args()
     from strata_b200 import synth
     rank = int(os.environ.get("RANK", 0))
@@ -298,6 +300,8 @@ def main():
     name = args.workload or "c1"
     cfg = synth.CONFIGS[name]
     T = args.tokens or cfg.T
+    if args.scaling is None:
+        args.scaling = "strong" if name in ("c2", "c3", "c4") else "weak"
 
     if args.impl == "reference":
         if rank != 0:

@@ -172,7 +172,21 @@ int strata_moe_route(strata_moe_layer* layer, const void* x_bf16, uint32_t token
  * pairs = number of entries of ids; perm[pos] = index into ids. */
 int strata_moe_group(strata_moe_layer* layer, const uint32_t* ids, uint32_t pairs,
                      uint32_t expert_begin, uint32_t n_experts, uint32_t* counts,
-                     uint32_t* offsets, uint32_t* perm);
+                     uint32_t* offsets, uint32_t* perm, uint32_t* inv /* [pairs] or NULL: entry ->
+                     position, 0xFFFFFFFF for an entry outside the expert range */);
+/* dst row i = src row (index[i] / index_div); rows are row_bytes long (multiple of 16).
+ * ref: the hidden-row and row-list upload of the grouped command,
+ * kernels/cuda/backend.cu:15346-15996, and the placement-driven copies the runtimes do on the
+ * host around it (src/models/dsv4/deepseek_runtime.cpp:6364-6387).  Used to pack the rows an
+ * expert-parallel rank sends and to restore received order. */
+int strata_moe_gather_rows(strata_moe_layer* layer, const void* src, uint32_t row_bytes,
+                           const uint32_t* index, uint32_t index_div, uint32_t n, void* dst);
+/* out[t] = output_scale * sum_r weights[t,r] * y[inv[t*k+r]] + shared(x_shared[t]), rank order.
+ * x_shared may be NULL (no shared expert term).
+ * ref: the host combine loops, src/models/glm52/glm_runtime.cpp:1586-1617,
+ * src/models/laguna/laguna_runtime.cpp:1129-1156, src/models/dsv4/deepseek_runtime.cpp:5897-5914. */
+int strata_moe_combine(strata_moe_layer* layer, const float* y, const uint32_t* inv,
+                       const float* weights, const void* x_shared_bf16, uint32_t tokens, float* out);
 /* Grouped expert FFN on rows already sorted by local expert.
  * ref: CudaBackend::enqueue_deepseek_moe_rows (the grouped command),
  * include/strata/cuda_backend.hpp:1139-1146, kernels/cuda/backend.cu:15346-15996.

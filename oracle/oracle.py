@@ -89,6 +89,7 @@ def port():
         lib.orc_moe_layer.argtypes = [C.POINTER(LayerDesc), u16p, u16p, f32p, C.POINTER(Expert),
                                       C.POINTER(Expert), u32p, C.c_uint32, f32p, u32p, f32p, u32p,
                                       u32p, u32p, f32p]
+        lib.orc_expert_ffn.argtypes = [C.POINTER(Expert), f32p, C.c_float, C.c_int, C.c_int, f32p, f32p, f32p]
         lib.orc_experts_all.argtypes = [C.POINTER(LayerDesc), u16p, C.POINTER(Expert), u32p, f32p,
                                         u32p, u32p, f32p]
         _port = lib

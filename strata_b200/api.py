@@ -14,7 +14,7 @@ EXPORTS = [
     "strata_moe_get_stats", "strata_moe_set_timing", "strata_moe_get_phase_ms", "strata_moe_layer_create",
     "strata_moe_layer_destroy", "strata_moe_set_router", "strata_moe_set_expert",
     "strata_moe_set_shared", "strata_moe_forward", "strata_moe_forward_host", "strata_moe_route",
-    "strata_moe_group", "strata_moe_experts_grouped", "strata_moe_dequant_export",
+    "strata_moe_group", "strata_moe_gather_rows", "strata_moe_combine", "strata_moe_experts_grouped", "strata_moe_dequant_export",
     "strata_moe_enqueue_dense", "strata_moe_collect_dense",
 ]
 
@@ -80,7 +80,9 @@ def load_library():
     lib.strata_moe_forward.argtypes = [vp, vp, u32, vp, C.POINTER(Aux)]
     lib.strata_moe_forward_host.argtypes = [vp, vp, u32, vp]
     lib.strata_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
-    lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp]
+    lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp]
+    lib.strata_moe_gather_rows.argtypes = [vp, vp, u32, vp, u32, u32, vp]
+    lib.strata_moe_combine.argtypes = [vp, vp, vp, vp, vp, u32, vp]
     lib.strata_moe_experts_grouped.argtypes = [vp, vp, u32, vp, vp]
     lib.strata_moe_dequant_export.argtypes = [vp, u32, i32, vp]
     lib.strata_moe_enqueue_dense.argtypes = [vp, vp, u32, vp, vp, u32, i32]
@@ -244,18 +246,42 @@ class MoeLayer:
         self.ctx.leave()
         return (ids, w, logits) if want_logits else (ids, w)
 
-    def group(self, ids, expert_begin=0, n_experts=None):
+    def group(self, ids, expert_begin=0, n_experts=None, want_inv=False):
         n_experts = self.cfg.E if n_experts is None else n_experts
         flat = ids.reshape(-1)
         dev = ids.device
         counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
         offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
         perm = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
+        inv = torch.empty(flat.numel(), dtype=torch.int32, device=dev) if want_inv else None
         self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_group(self.h, _ptr(flat), flat.numel(), expert_begin, n_experts,
-                                                 _ptr(counts), _ptr(offsets), _ptr(perm)))
+                                                 _ptr(counts), _ptr(offsets), _ptr(perm), _ptr(inv)))
         self.ctx.leave()
-        return counts, offsets, perm
+        return (counts, offsets, perm, inv) if want_inv else (counts, offsets, perm)
+
+    def gather_rows(self, src, index, index_div=1, n=None):
+        """dst[i] = src[index[i] // index_div] for i < n (rows of any dtype, 16-byte multiples)."""
+        n = index.numel() if n is None else n
+        dst = torch.empty((n,) + tuple(src.shape[1:]), dtype=src.dtype, device=src.device)
+        if n:
+            row_bytes = src[0].numel() * src.element_size()
+            self.ctx.enter()
+            self.ctx.check(self.lib.strata_moe_gather_rows(self.h, _ptr(src), row_bytes, _ptr(index), index_div,
+                                                           n, _ptr(dst)))
+            self.ctx.leave()
+        return dst
+
+    def combine(self, y, inv, weights, x_shared=None, out=None):
+        T = weights.shape[0]
+        if out is None:
+            out = torch.empty(T, self.cfg.H, dtype=torch.float32, device=weights.device)
+        if T:
+            self.ctx.enter()
+            self.ctx.check(self.lib.strata_moe_combine(self.h, _ptr(y), _ptr(inv), _ptr(weights), _ptr(x_shared),
+                                                       T, _ptr(out)))
+            self.ctx.leave()
+        return out
 
     def experts_grouped(self, rows, offsets, y=None):
         if y is None:

@@ -620,7 +620,8 @@ int strata_moe_route(strata_moe_layer* L, const void* x, uint32_t T, float* logi
 }
 
 int strata_moe_group(strata_moe_layer* L, const uint32_t* ids, uint32_t pairs, uint32_t expert_begin,
-                     uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm) {
+                     uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm,
+                     uint32_t* inv) {
     if (!L) return STRATA_MOE_E_INVALID;
     strata_moe_ctx* ctx = L->ctx;
     if (!ids || !counts || !offsets || !perm) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
@@ -628,7 +629,7 @@ int strata_moe_group(strata_moe_layer* L, const uint32_t* ids, uint32_t pairs, u
     if ((uint64_t)pairs > (uint64_t)L->d.max_tokens * L->d.top_k && pairs > L->max_pairs)
         return fail(ctx, STRATA_MOE_E_INVALID, "pairs exceed the layer's workspace");
     CK(cudaSetDevice(ctx->device));
-    launch_group(ids, pairs, expert_begin, n_experts, counts, offsets, perm, nullptr, nullptr, nullptr,
+    launch_group(ids, pairs, expert_begin, n_experts, counts, offsets, perm, inv, nullptr, nullptr,
                  L->group_scratch, ctx->stream);
     CK(cudaGetLastError());
     return 0;
@@ -649,6 +650,46 @@ int strata_moe_experts_grouped(strata_moe_layer* L, const void* rows, uint32_t p
     if (rc) return rc;
     return run_experts(L, (const __nv_bfloat16*)rows, nullptr, 1, pairs, L->d.expert_count, offsets,
                        nullptr, nullptr, pairs, y);
+}
+
+int strata_moe_gather_rows(strata_moe_layer* L, const void* src, uint32_t row_bytes,
+                           const uint32_t* index, uint32_t index_div, uint32_t n, void* dst) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!src || !dst || !index) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (row_bytes == 0 || row_bytes % 16u || index_div == 0)
+        return fail(ctx, STRATA_MOE_E_INVALID, "rows must be a multiple of 16 bytes");
+    CK(cudaSetDevice(ctx->device));
+    // a row of row_bytes is copied as row_bytes / 16 sixteen-byte vectors
+    launch_gather_rows_plain(static_cast<const __nv_bfloat16*>(src), index, index_div, n, row_bytes / 2u,
+                             static_cast<__nv_bfloat16*>(dst), ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_combine(strata_moe_layer* L, const float* y, const uint32_t* inv, const float* weights,
+                       const void* x_shared, uint32_t T, float* out) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!y || !inv || !weights || !out) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (T == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    const float* shared = nullptr;
+    if (x_shared && L->d.shared_intermediate) {
+        for (int r = 0; r < 3; ++r)
+            if (!L->shared_w[r]) return fail(ctx, STRATA_MOE_E_INVALID, "shared expert weights were never set");
+        uint32_t* off2 = L->offsets + L->d.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, ctx->stream>>>(off2, 0u, T);
+        ++g_kernel_launches;
+        int rc = run_shared(L, static_cast<const __nv_bfloat16*>(x_shared), nullptr, T, off2);
+        if (rc) return rc;
+        shared = L->sh_y;
+    }
+    launch_combine(y, inv, weights, shared, T, L->d.top_k, L->d.hidden, L->d.output_scale, out,
+                   ctx->d_status, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
 }
 
 int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* out,
