@@ -351,51 +351,69 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
             } else {
                 srow += (size_t)row * (K / 128u) * 2u;
             }
-            uint4 cur[CH], nxt[CH];
+            // Register ring of kPF stages: HBM latency (~1 us) spans several 64-column stages of
+            // tensor-core work, so the loads of stage ks + kPF are issued when stage ks is decoded.
+            constexpr uint32_t kPF = 4;
+            uint4 buf[kPF][CH];
+            uint32_t sbuf[kPF];
+            auto issue = [&](uint32_t ks, uint4(&dst)[CH], uint32_t& sdst) {
+                ks = ks < k_stages ? ks : k_stages - 1u;
 #pragma unroll
-            for (uint32_t c = 0; c < CH; ++c) cur[c] = ldg_stream16_c(prow + c * 16u);
-            for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
-                const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                const uint32_t kn = ks + 1u < k_stages ? ks + 1u : ks;
+                for (uint32_t c = 0; c < CH; ++c) dst[c] = ldg_stream16_c(prow + (size_t)ks * 32u + c * 16u);
+                if (FMT == STRATA_MOE_FMT_MXFP4) {
+                    sdst = DUAL ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + ks * 2u))
+                                : (uint32_t)__ldg(srow + ks * 2u + half);
+                } else if (FMT == STRATA_MOE_FMT_NVFP4) {
+                    sdst = DUAL ? __ldg(reinterpret_cast<const uint32_t*>(srow + ks * 4u))
+                                : (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + ks * 4u + half * 2u));
+                } else {
+                    sdst = __ldg(reinterpret_cast<const unsigned short*>(srow + (ks >> 1) * 2u));
+                }
+            };
 #pragma unroll
-                for (uint32_t c = 0; c < CH; ++c) nxt[c] = ldg_stream16_c(prow + (size_t)kn * 32u + c * 16u);
-                // block multipliers of this thread's 32-column chunks
-                uint32_t m[CH][4];
+            for (uint32_t j = 0; j < kPF; ++j) issue(j, buf[j], sbuf[j]);
+            for (uint32_t ks0 = 0; ks0 < k_stages && ok; ks0 += kPF) {
 #pragma unroll
-                for (uint32_t c = 0; c < CH; ++c) {
-                    const uint32_t col32 = ks * 2u + (DUAL ? c : half);  // index of the 32-column chunk
-                    if (FMT == STRATA_MOE_FMT_MXFP4) {
-                        const uint32_t e = __ldg(srow + col32);
-                        const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
-                        m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
-                    } else if (FMT == STRATA_MOE_FMT_NVFP4) {
-                        const uint32_t sb = __ldg(reinterpret_cast<const unsigned short*>(srow + col32 * 2u));
-                        uint32_t pair;
-                        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)sb));
-                        m[c][0] = m[c][1] = __byte_perm(pair, pair, 0x1010);
-                        m[c][2] = m[c][3] = __byte_perm(pair, pair, 0x3232);
-                    } else {
-                        const uint32_t sb = __ldg(reinterpret_cast<const unsigned short*>(srow + (col32 >> 2) * 2u));
-                        const uint32_t h = __half_as_ushort(__float2half_rn(__uint_as_float(sb << 16)));
-                        m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
+                for (uint32_t j = 0; j < kPF; ++j) {
+                    const uint32_t ks = ks0 + j;
+                    if (ks >= k_stages) break;
+                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    ++it;
+                    // block multipliers of this thread's 32-column chunks
+                    uint32_t m[CH][4];
+#pragma unroll
+                    for (uint32_t c = 0; c < CH; ++c) {
+                        if (FMT == STRATA_MOE_FMT_MXFP4) {
+                            const uint32_t e = (sbuf[j] >> (8u * c)) & 0xFFu;
+                            const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
+                            m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
+                        } else if (FMT == STRATA_MOE_FMT_NVFP4) {
+                            const uint32_t sb = (sbuf[j] >> (16u * c)) & 0xFFFFu;
+                            uint32_t pair;
+                            asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)sb));
+                            m[c][0] = m[c][1] = __byte_perm(pair, pair, 0x1010);
+                            m[c][2] = m[c][3] = __byte_perm(pair, pair, 0x3232);
+                        } else {
+                            const uint32_t h = __half_as_ushort(__float2half_rn(__uint_as_float(sbuf[j] << 16)));
+                            m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
+                        }
                     }
+                    if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
+#pragma unroll
+                    for (uint32_t c = 0; c < CH; ++c) {
+                        uint4 o[4];
+                        decode16<FMT>(buf[j][c], m[c], o);
+                        const uint32_t chunk0 = (DUAL ? c : half) * 4u;  // first 16-byte chunk (8 columns each)
+#pragma unroll
+                        for (uint32_t q = 0; q < 4; ++q)
+                            *reinterpret_cast<uint4*>(tile_base + (((chunk0 + q) ^ (arow & 7u)) << 4)) = o[q];
+                    }
+                    fence_async_smem();  // make the generic-proxy stores visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&S.full_a[s]);
+                    issue(ks + kPF, buf[j], sbuf[j]);
                 }
-                if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
-#pragma unroll
-                for (uint32_t c = 0; c < CH; ++c) {
-                    uint4 o[4];
-                    decode16<FMT>(cur[c], m[c], o);
-                    const uint32_t chunk0 = (DUAL ? c : half) * 4u;  // first 16-byte chunk (8 columns each)
-#pragma unroll
-                    for (uint32_t q = 0; q < 4; ++q)
-                        *reinterpret_cast<uint4*>(tile_base + (((chunk0 + q) ^ (arow & 7u)) << 4)) = o[q];
-                }
-                fence_async_smem();  // make the generic-proxy stores visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&S.full_a[s]);
-#pragma unroll
-                for (uint32_t c = 0; c < CH; ++c) cur[c] = nxt[c];
             }
         }
         if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }

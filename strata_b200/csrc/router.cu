@@ -105,20 +105,146 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     }
 }
 
+// Large token counts: every warp owns RW expert rows and a 16-token tile, so one staged
+// activation value feeds RW multiply-add chains and the staging cost is shared by 8 * RW rows.
+// Same per-lane accumulation order as above (the order is a property of one (token, row) dot
+// product, not of how dot products are batched).
+// Shared layout per (token or row): lane l holds its 8 columns contiguously (32 bytes); the two
+// 16-byte halves are swapped for lanes with bit 2 set, which makes the float4 reads conflict-free.
+constexpr int kBigRW = 4;
+constexpr int kBigWarps = 8;
+constexpr int kBigTT = 16;
+
+__device__ __forceinline__ void router_stage8_b(float* dst, uint32_t c8, const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+        const uint32_t c = c8 + p, l = c & 31u, j = c >> 5;
+        const uint32_t bits = (p & 1) ? (w[p >> 1] & 0xFFFF0000u) : (w[p >> 1] << 16);
+        dst[l * 8u + ((((j >> 2) ^ (l >> 2)) & 1u) << 2) + (j & 3u)] = __uint_as_float(bits);
+    }
+}
+
+__global__ void __launch_bounds__(kBigWarps * 32, 1) router_logits_big_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
+    uint32_t E, float* __restrict__ logits) {
+    extern __shared__ __align__(16) float rsm[];
+    float* xs = rsm;                              // [kBigTT][256]
+    float* ws = rsm + kBigTT * kRouterChunk;      // [kBigWarps * kBigRW][256]
+    constexpr int THREADS = kBigWarps * 32;
+    constexpr int ROWS = kBigWarps * kBigRW;
+    constexpr int XV = kBigTT * (kRouterChunk / 8) / THREADS;  // 2
+    constexpr int WV = ROWS * (kRouterChunk / 8) / THREADS;    // 4
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t e0 = blockIdx.x * ROWS;
+    const uint32_t t0 = blockIdx.y * kBigTT;
+    const uint32_t nt = min((uint32_t)kBigTT, T - t0);
+    float sum[kBigRW][kBigTT];
+#pragma unroll
+    for (int r = 0; r < kBigRW; ++r)
+#pragma unroll
+        for (int i = 0; i < kBigTT; ++i) sum[r][i] = 0.0f;
+
+    uint4 xr[XV], wr[WV];
+    auto fetch = [&](uint32_t c0) {
+        const uint32_t cols = min((uint32_t)kRouterChunk, H - c0);
+#pragma unroll
+        for (int q = 0; q < XV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            const uint32_t tok = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
+            xr[q] = make_uint4(0, 0, 0, 0);
+            if (tok < nt && c8 < cols)
+                xr[q] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H + c0 + c8));
+        }
+#pragma unroll
+        for (int q = 0; q < WV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            const uint32_t row = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
+            wr[q] = make_uint4(0, 0, 0, 0);
+            if (e0 + row < E && c8 < cols)
+                wr[q] = __ldg(reinterpret_cast<const uint4*>(wg + (size_t)(e0 + row) * H + c0 + c8));
+        }
+    };
+    fetch(0);
+    const uint32_t swz = ((lane >> 2) & 1u) << 2;  // which half holds j = 0..3 for this lane
+    for (uint32_t c0 = 0; c0 < H; c0 += kRouterChunk) {
+        const uint32_t cols = min((uint32_t)kRouterChunk, H - c0);
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < XV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            router_stage8_b(xs + (i / (kRouterChunk / 8)) * kRouterChunk, (i % (kRouterChunk / 8)) * 8u, xr[q]);
+        }
+#pragma unroll
+        for (int q = 0; q < WV; ++q) {
+            const uint32_t i = threadIdx.x + q * THREADS;
+            router_stage8_b(ws + (i / (kRouterChunk / 8)) * kRouterChunk, (i % (kRouterChunk / 8)) * 8u, wr[q]);
+        }
+        __syncthreads();
+        if (c0 + kRouterChunk < H) fetch(c0 + kRouterChunk);
+        const uint32_t nj = cols >> 5;
+        float wv[kBigRW][8];
+#pragma unroll
+        for (int r = 0; r < kBigRW; ++r) {
+            const float* wp = ws + (warp * kBigRW + r) * kRouterChunk + lane * 8u;
+            const float4 a = *reinterpret_cast<const float4*>(wp + swz);
+            const float4 b = *reinterpret_cast<const float4*>(wp + (swz ^ 4u));
+            wv[r][0] = a.x; wv[r][1] = a.y; wv[r][2] = a.z; wv[r][3] = a.w;
+            wv[r][4] = b.x; wv[r][5] = b.y; wv[r][6] = b.z; wv[r][7] = b.w;
+        }
+#pragma unroll
+        for (int tok = 0; tok < kBigTT; ++tok) {
+            const float* xp = xs + tok * kRouterChunk + lane * 8u;
+            const float4 a = *reinterpret_cast<const float4*>(xp + swz);
+            const float4 b = *reinterpret_cast<const float4*>(xp + (swz ^ 4u));
+            const float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            if (nj == 8u) {
+#pragma unroll
+                for (int r = 0; r < kBigRW; ++r)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
+            } else {
+#pragma unroll
+                for (int r = 0; r < kBigRW; ++r)
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if ((uint32_t)j < nj) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kBigRW; ++r) {
+        const uint32_t e = e0 + warp * kBigRW + r;
+#pragma unroll
+        for (int tok = 0; tok < kBigTT; ++tok) {
+            float v = sum[r][tok];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
+            if (lane == 0 && (uint32_t)tok < nt && e < E) logits[(size_t)(t0 + tok) * E + e] = v;
+        }
+    }
+}
+
 void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
                           uint32_t E, float* logits, cudaStream_t s) {
     if (T == 0) return;
     // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
-    // many tokens: 8 rows share one staged 16-token tile
+    // many tokens: register-blocked kernel (4 rows per warp, 32 rows per CTA)
     if (T <= 8) {
         dim3 grid((E + 1) / 2, 1);
         router_logits_kernel<2, 8><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
-    } else if ((size_t)((T + 15) / 16) * ((E + 7) / 8) < 2u * kNumSMs) {
+    } else if ((size_t)((T + 15) / 16) * ((E + 31) / 32) < (size_t)kNumSMs) {
         dim3 grid((E + 1) / 2, (T + 15) / 16);
         router_logits_kernel<2, 16><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
     } else {
-        dim3 grid((E + 7) / 8, (T + 15) / 16);
-        router_logits_kernel<8, 16><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
+        static bool attr = false;
+        const size_t smem = (size_t)(kBigTT + kBigWarps * kBigRW) * kRouterChunk * sizeof(float);
+        if (!attr) {
+            cudaFuncSetAttribute(router_logits_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr = true;
+        }
+        dim3 grid((E + 31) / 32, (T + 15) / 16);
+        router_logits_big_kernel<<<grid, kBigWarps * 32, smem, s>>>(x, wg, T, H, E, logits);
     }
     ++g_kernel_launches;
 }
