@@ -281,6 +281,26 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
 int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16* x_lo, uint32_t T,
                const uint32_t* offsets2) {
     strata_moe_ctx* ctx = L->ctx;
+    // enough rows to fill tensor-core tiles (and BF16 inputs): grouped-GEMM path with one group
+    const char* thr_env = getenv("STRATA_MOE_PREFILL_MIN_ROWS");
+    const uint32_t thr = thr_env ? (uint32_t)atoi(thr_env) : 24u;
+    if (!x_lo && T >= thr && prefill_supported(3, L->d.hidden, L->d.shared_intermediate)) {
+        PrefillArgs p{};
+        p.fmt = 3;
+        p.H = L->d.hidden;
+        p.I = L->d.shared_intermediate;
+        p.n_groups = 1;
+        p.pairs = T;
+        p.offsets = offsets2;
+        p.y = L->sh_y;
+        p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
+        p.status = ctx->d_status;
+        if (launch_prefill_bf16(p, x, T, L->shared_w[0], L->shared_w[1], L->shared_w[2], L->sh_act_hi,
+                                L->d.max_tokens, ctx->stream) != 0)
+            return fail(ctx, STRATA_MOE_E_CUDA, "shared expert prefill launch failed");
+        CK(cudaGetLastError());
+        return 0;
+    }
     DecodeArgs a{};
     a.fmt = 3;
     a.H = L->d.hidden;
@@ -288,9 +308,9 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
     a.n_groups = 1;
     a.offsets = offsets2;
     a.max_rows_per_group = T;
-    WeightTable g{L->d_shared_ptr[0], L->d_shared_ptr[0], L->one_global};
-    WeightTable u{L->d_shared_ptr[1], L->d_shared_ptr[1], L->one_global};
-    WeightTable dn{L->d_shared_ptr[2], L->d_shared_ptr[2], L->one_global};
+    WeightTable g{L->d_shared_ptr[0], L->d_shared_ptr[0], L->one_global, nullptr, nullptr};
+    WeightTable u{L->d_shared_ptr[1], L->d_shared_ptr[1], L->one_global, nullptr, nullptr};
+    WeightTable dn{L->d_shared_ptr[2], L->d_shared_ptr[2], L->one_global, nullptr, nullptr};
     a.gate = g;
     a.up = u;
     a.down = dn;

@@ -103,6 +103,8 @@ size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
 // [pairs_cap, I] f16 scratch.  mid, when non-null, is recorded between the two GEMMs.
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                    uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid);
+int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
+                        const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s);
 // combine.cu
 void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
                     uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,

@@ -40,6 +40,7 @@ constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kThreads = 14 * 32;
 constexpr uint32_t kDequantThreads = 256;
 constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr int kFmtBf16W = 3;  // plain BF16 weights (shared expert): tiles arrive by TMA, no decode
 
 // ------------------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -92,12 +93,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                         // 128-byte swizzle
     return d;
 }
-// Instruction descriptor, kind::f16: F16 x F16 -> F32, both operands K-major, M = 128.
-__device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n) {
+// Instruction descriptor, kind::f16: F16 x F16 (or BF16 x BF16) -> F32, both operands K-major, M = 128.
+__device__ __forceinline__ uint32_t umma_idesc_f16(uint32_t n, uint32_t ab_format /* 0 = F16, 1 = BF16 */) {
     uint32_t d = 0;
     d |= 1u << 4;               // D format F32
-    d |= 0u << 7;               // A format F16
-    d |= 0u << 10;              // B format F16
+    d |= ab_format << 7;        // A format
+    d |= ab_format << 10;       // B format
     d |= (n >> 3) << 17;        // N
     d |= (kMTile >> 4) << 24;   // M
     return d;
@@ -219,8 +220,9 @@ __device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile
 // DUAL = false: down tile, y (fp32) out.                    K = I, features over H.
 template <int FMT, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, const float* __restrict__ rowscale,
-                   __half* __restrict__ act_out) {
+prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_a0,
+                   const __grid_constant__ CUtensorMap map_a1, PrefillArgs a, const float* __restrict__ rowscale,
+                   void* __restrict__ act_out_v) {
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem& S = *reinterpret_cast<PrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -232,7 +234,8 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
-            mbar_init(&S.full_a[s], kDequantThreads / 32);  // one arrival per producer warp
+            // one arrival per producer warp, or one TMA transaction group for BF16 weights
+            mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : kDequantThreads / 32);
             mbar_init(&S.full_b[s], 1);
             mbar_init(&S.empty[s], 1);
         }
@@ -267,6 +270,11 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
                     if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&S.full_b[s], kBTile);
                     tma_load_2d(S.b[s], &map_b, ks * kBK, t.row0, &S.full_b[s]);
+                    if (FMT == kFmtBf16W) {
+                        mbar_arrive_expect_tx(&S.full_a[s], DUAL ? 2u * kATile : kATile);
+                        tma_load_2d(S.a0[s], &map_a0, ks * kBK, t.m0, &S.full_a[s]);
+                        if (DUAL) tma_load_2d(S.a1[s], &map_a1, ks * kBK, t.m0, &S.full_a[s]);
+                    }
                 }
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
@@ -302,7 +310,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
                 if (!mbar_wait(&S.acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t n = (t.n + 15u) & ~15u;
-                const uint32_t idesc = umma_idesc_f16(n);
+                const uint32_t idesc = umma_idesc_f16(n, FMT == kFmtBf16W ? 1u : 0u);
                 const uint32_t d0 = tmem_base + buf * 256u, d1 = d0 + kNTile;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
@@ -324,6 +332,8 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
         }
+    } else if (warp < 10 && FMT == kFmtBf16W) {
+        // BF16 weights need no decode: the TMA producer loads their tiles
     } else if (warp < 10) {
         // ---------------------------------------------------------------- weight producers
         const uint32_t d = threadIdx.x - 64u;  // 0..255
@@ -432,11 +442,12 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
             tc_fence_after();
             const uint32_t feat = t.m0 + lane_base + lane;
             float s0, s1 = 1.0f;
+            constexpr bool kNoPost = FMT == STRATA_MOE_FMT_INT4G128 || FMT == kFmtBf16W;
             if (DUAL) {
-                s0 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.gate.post_scale[t.g];
-                s1 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.up.post_scale[t.g];
+                s0 = kNoPost ? 1.0f : a.gate.post_scale[t.g];
+                s1 = kNoPost ? 1.0f : a.up.post_scale[t.g];
             } else {
-                s0 = (FMT == STRATA_MOE_FMT_INT4G128) ? 1.0f : a.down.post_scale[t.g];
+                s0 = kNoPost ? 1.0f : a.down.post_scale[t.g];
             }
             const uint32_t taddr = tmem_base + (lane_base << 16) + buf * 256u;
             for (uint32_t c0 = 0; c0 < t.n; c0 += 32u) {
@@ -449,13 +460,16 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, PrefillArgs a, con
                     if (c0 + j >= t.n) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
                     if (DUAL) {
-                        const float rs = rowscale[pos];
+                        const float rs = rowscale ? rowscale[pos] : 1.0f;
                         const float gv = __uint_as_float(g[j]) * s0 * rs, uv = __uint_as_float(u[j]) * s1 * rs;
                         const float e = __expf(-fabsf(gv));
                         const float sig = gv >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
                         const float v = gv * sig * uv;
                         if (!(fabsf(v) <= 65504.0f)) bad = true;
-                        act_out[pos * R + feat] = __float2half_rn(v);
+                        if (FMT == kFmtBf16W)
+                            static_cast<__nv_bfloat16*>(act_out_v)[pos * R + feat] = __float2bfloat16_rn(v);
+                        else
+                            static_cast<__half*>(act_out_v)[pos * R + feat] = __float2half_rn(v);
                     } else {
                         const float v = __uint_as_float(g[j]) * s0;
                         if (!(fabsf(v) <= 3.0e38f)) bad = true;
@@ -525,13 +539,13 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// f16 matrix [rows, cols] row-major; box = 64 columns x kNTile rows, 128-byte swizzle.
-static bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+// 16-bit matrix [rows, cols] row-major; box = 64 columns x box_rows rows, 128-byte swizzle.
+static bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {cols, rows};
     const cuuint64_t strides[1] = {cols * 2};
-    const cuuint32_t box[2] = {kBK, kNTile};
+    const cuuint32_t box[2] = {kBK, box_rows};
     const cuuint32_t estr[2] = {1, 1};
     return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -540,7 +554,7 @@ static bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 
 bool prefill_supported(int fmt, uint32_t H, uint32_t I) {
     if (getenv("STRATA_MOE_NO_PREFILL_PATH")) return false;
-    if (fmt < 0 || fmt > STRATA_MOE_FMT_INT4G128) return false;
+    if (fmt < 0 || fmt > kFmtBf16W) return false;
     return H % 128u == 0 && I % 128u == 0 && encode_fn() != nullptr;
 }
 
@@ -548,46 +562,63 @@ size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs) {
     return (4 + 3 * ((size_t)pairs / kNTile + n_groups + 1)) * sizeof(uint32_t);
 }
 
-struct PrefillPlan {
-    const void* x16;          // [pairs_cap, H] f16 (pre-scaled rows)
-    const float* x_rowscale;  // [pairs_cap]
-    void* act16;              // [pairs_cap, I] f16
-    uint32_t pairs_cap;
-};
+template <int FMT>
+static int set_smem_attr(size_t smem) {
+    static bool done = false;
+    if (done) return 0;
+    if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess)
+        return -2;
+    done = true;
+    return 0;
+}
 
 template <int FMT>
-static int launch_fmt(const PrefillArgs& a, const PrefillPlan& p, cudaStream_t s, cudaEvent_t mid) {
+static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                      uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid) {
     CUtensorMap map_x, map_act;
-    if (!make_map(&map_x, p.x16, p.pairs_cap, a.H) || !make_map(&map_act, p.act16, p.pairs_cap, a.I)) return -1;
+    if (!make_map(&map_x, x16, pairs_cap, a.H, kNTile) || !make_map(&map_act, act16, pairs_cap, a.I, kNTile))
+        return -1;
     const size_t smem = sizeof(PrefillSmem) + 1024;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[0]) {
-        if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return -2;
-        if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return -2;
-        attr_set[0] = true;
-    }
+    if (set_smem_attr<FMT>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, a, p.x_rowscale,
-                                                                  static_cast<__half*>(p.act16));
+    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16);
     if (mid) cudaEventRecord(mid, s);
-    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, a, nullptr, nullptr);
+    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                    uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid) {
-    PrefillPlan p{x16, x_rowscale, act16, pairs_cap};
     switch (a.fmt) {
-        case STRATA_MOE_FMT_MXFP4: return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, p, s, mid);
-        case STRATA_MOE_FMT_NVFP4: return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, p, s, mid);
-        case STRATA_MOE_FMT_INT4G128: return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, p, s, mid);
+        case STRATA_MOE_FMT_MXFP4: return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
+        case STRATA_MOE_FMT_NVFP4: return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
+        case STRATA_MOE_FMT_INT4G128:
+            return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
         default: return -1;
     }
+}
+
+// BF16 expert (the shared expert) over `rows` token rows in natural order: x [rows, H] BF16,
+// gate/up [I, H], down [H, I] BF16, act [rows_cap, I] BF16 scratch, y [rows, H] fp32.
+// a.offsets must hold {0, rows}; a.n_groups = 1.
+int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
+                        const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
+    CUtensorMap map_x, map_act, map_g, map_u, map_d;
+    if (!make_map(&map_x, x, rows, a.H, kNTile) || !make_map(&map_act, act, rows_cap, a.I, kNTile) ||
+        !make_map(&map_g, w_gate, a.I, a.H, kMTile) || !make_map(&map_u, w_up, a.I, a.H, kMTile) ||
+        !make_map(&map_d, w_down, a.H, a.I, kMTile))
+        return -1;
+    const size_t smem = sizeof(PrefillSmem) + 1024;
+    if (set_smem_attr<kFmtBf16W>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    prefill_ffn_kernel<kFmtBf16W, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act);
+    prefill_ffn_kernel<kFmtBf16W, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr);
+    g_kernel_launches += 3;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 }  // namespace smoe

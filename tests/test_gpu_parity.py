@@ -227,3 +227,14 @@ def test_prefill_and_streaming_paths_agree(ctx, monkeypatch):
     ctx.synchronize()
     rel, mx = Hh.error_metrics(out_tc.cpu().numpy(), out_stream.cpu().numpy())
     assert rel <= PREFILL_TIGHT
+
+
+def test_shared_expert_on_tensor_core_path(ctx):
+    # 200 tokens: the BF16 shared expert runs as a one-group grouped GEMM, the routed NVFP4
+    # experts (50 rows each on average) take the tensor-core path as well
+    cfg = small(synth.FMT_NVFP4, T=200, I_shared=256, output_scale=2.5, name="shared_tc")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
