@@ -174,6 +174,19 @@ int strata_moe_group(strata_moe_layer* layer, const uint32_t* ids, uint32_t pair
                      uint32_t expert_begin, uint32_t n_experts, uint32_t* counts,
                      uint32_t* offsets, uint32_t* perm, uint32_t* inv /* [pairs] or NULL: entry ->
                      position, 0xFFFFFFFF for an entry outside the expert range */);
+/* Allocation-free variant of strata_moe_group.  It has no counterpart in the reference.
+ * For hosts that must not let a library allocate device memory -- a runtime that gave the
+ * whole GPU to its own arena at start-up, or a caller in a section where cudaMalloc's implicit
+ * device synchronisation is unacceptable.  It needs no context or layer (creating those
+ * allocates): inputs and outputs are caller memory, `stream` is a cudaStream_t (NULL = default
+ * stream), and the scratch is a fixed 520 KiB device array inside the library, resident on every
+ * GPU that loads it.  Limits: pairs <= 65536, n_experts <= 256; larger calls are rejected with a
+ * message in `err`.  The first call on a device resolves the array's address: issue it before
+ * any stream capture on that device.  All calls share the array, so calls that overlap on the
+ * GPU race; serialise them.  Returns 0 or a negative STRATA_MOE_E_* and a message in err. */
+int strata_moe_group_static(void* stream, const uint32_t* ids, uint32_t pairs, uint32_t expert_begin,
+                            uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm,
+                            uint32_t* inv /* or NULL */, char* err, size_t err_cap);
 /* dst row i = src row (index[i] / index_div); rows are row_bytes long (multiple of 16).
  * ref: the hidden-row and row-list upload of the grouped command,
  * kernels/cuda/backend.cu:15346-15996, and the placement-driven copies the runtimes do on the

@@ -15,7 +15,7 @@ EXPORTS = [
     "strata_moe_layer_destroy", "strata_moe_set_router", "strata_moe_set_expert",
     "strata_moe_set_shared", "strata_moe_forward", "strata_moe_forward_host", "strata_moe_route",
     "strata_moe_group", "strata_moe_gather_rows", "strata_moe_combine", "strata_moe_experts_grouped", "strata_moe_dequant_export",
-    "strata_moe_enqueue_dense", "strata_moe_collect_dense",
+    "strata_moe_enqueue_dense", "strata_moe_collect_dense", "strata_moe_group_static",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -87,12 +87,32 @@ def load_library():
     lib.strata_moe_dequant_export.argtypes = [vp, u32, i32, vp]
     lib.strata_moe_enqueue_dense.argtypes = [vp, vp, u32, vp, vp, u32, i32]
     lib.strata_moe_collect_dense.argtypes = [vp, vp, vp]
+    lib.strata_moe_group_static.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp, C.c_char_p, C.c_size_t]
     _LIB = lib
     return lib
 
 
 def _ptr(t):
     return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def group_static(ids, expert_begin, n_experts, stream=None, want_inv=True):
+    """strata_moe_group_static on torch tensors: the grouping call that allocates nothing inside the
+    library (the output tensors here are the caller's).  Raises StrataMoeError with the library's text."""
+    lib = load_library()
+    flat = ids.reshape(-1)
+    dev = ids.device
+    counts = torch.empty(n_experts, dtype=torch.int32, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    perm = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
+    inv = torch.empty(flat.numel(), dtype=torch.int32, device=dev) if want_inv else None
+    stream = torch.cuda.current_stream(dev) if stream is None else stream
+    err = C.create_string_buffer(256)
+    rc = lib.strata_moe_group_static(C.c_void_p(stream.cuda_stream), _ptr(flat), flat.numel(), expert_begin,
+                                     n_experts, _ptr(counts), _ptr(offsets), _ptr(perm), _ptr(inv), err, 256)
+    if rc != 0:
+        raise StrataMoeError(rc, err.value.decode())
+    return counts, offsets, perm, inv
 
 
 class MoeContext:

@@ -213,4 +213,83 @@ void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, ui
     g_kernel_launches += 4;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Grouping without any allocation.
+//
+// Some hosts of this library cannot let it allocate device memory: a serving runtime that has
+// handed the whole GPU to its own arena at start-up (a later cudaMalloc then fails or stalls),
+// or a caller sitting in a latency-critical section where cudaMalloc's implicit device
+// synchronisation is not acceptable.  Those callers have no layer object (creating one
+// allocates workspaces), so this entry point works on caller-provided inputs and outputs only
+// and keeps its scratch -- the per-segment histograms of the segmented path -- in a fixed
+// device array that is part of the loaded module.
+//
+// Limits and rules:
+//   * at most kStaticMaxPairs pairs and kStaticMaxExperts experts per call (520 KiB of scratch,
+//     held by every GPU that loads the library until the process exits);
+//   * the first call on a device looks up the array's device address; make that first call
+//     before any stream capture on that device;
+//   * all calls share the one array: two calls whose kernels overlap on the GPU (different
+//     streams, or different host threads) race on it.  Serialise them;
+//   * nothing has to be cleared between calls: every histogram row a call reads was written by
+//     that call's first kernel.
+constexpr uint32_t kStaticMaxPairs = 65536;
+constexpr uint32_t kStaticMaxExperts = 256;
+static __device__ __align__(256) uint32_t g_group_static_scratch[(kStaticMaxPairs / kSegPairs + 8) * kStaticMaxExperts];
+
 }  // namespace smoe
+
+#include <cstdio>
+#include <mutex>
+
+extern "C" int strata_moe_group_static(void* stream, const uint32_t* ids, uint32_t pairs,
+                                       uint32_t expert_begin, uint32_t n_experts, uint32_t* counts,
+                                       uint32_t* offsets, uint32_t* perm, uint32_t* inv, char* err,
+                                       size_t err_cap) {
+    using namespace smoe;
+    auto fail = [&](int code, const char* what, const char* detail) {
+        if (err && err_cap) snprintf(err, err_cap, "strata_moe_group_static: %s%s%s", what, detail ? ": " : "",
+                                     detail ? detail : "");
+        return code;
+    };
+    if (!ids || !counts || !offsets || !perm) return fail(STRATA_MOE_E_INVALID, "null pointer", nullptr);
+    if (pairs > kStaticMaxPairs)
+        return fail(STRATA_MOE_E_INVALID, "too many pairs for the fixed scratch (limit 65536); use strata_moe_group",
+                    nullptr);
+    if (n_experts == 0 || n_experts > kStaticMaxExperts)
+        return fail(STRATA_MOE_E_INVALID, "expert count must be in 1..256 for the fixed scratch; use strata_moe_group",
+                    nullptr);
+    // device address of the scratch array, looked up once per device with that device current
+    static std::mutex mu;
+    static uint32_t* dev_ptr[64] = {};
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(STRATA_MOE_E_CUDA, "cudaGetDevice", cudaGetErrorString(e));
+    if (dev < 0 || dev >= 64) return fail(STRATA_MOE_E_INVALID, "device ordinal out of range", nullptr);
+    uint32_t* scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!dev_ptr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_group_static_scratch);
+            if (e != cudaSuccess) return fail(STRATA_MOE_E_CUDA, "cudaGetSymbolAddress", cudaGetErrorString(e));
+            dev_ptr[dev] = static_cast<uint32_t*>(p);
+        }
+        scratch = dev_ptr[dev];
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint32_t nseg = (pairs + kSegPairs - 1) / kSegPairs;
+    const uint32_t blocks = (nseg + 7) / 8;
+    const size_t smem = 8u * (size_t)n_experts * sizeof(uint32_t);
+    if (nseg) group_hist_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, scratch);
+    group_segscan_kernel<<<(n_experts + 127) / 128, 128, 0, s>>>(scratch, nseg, n_experts, counts);
+    group_offsets_kernel<<<1, 1024, 0, s>>>(counts, n_experts, offsets, nullptr, nullptr);
+    if (nseg)
+        group_scatter_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, scratch, offsets, perm,
+                                                       inv);
+    g_kernel_launches += nseg ? 4 : 2;
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(STRATA_MOE_E_CUDA, "kernel launch", cudaGetErrorString(e));
+    return 0;
+}
