@@ -230,12 +230,16 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
     if (T == 0) return;
     // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
     // many tokens: register-blocked kernel (4 rows per warp, 32 rows per CTA)
+    const size_t big_tiles = (size_t)((T + 15) / 16) * ((E + 31) / 32);
     if (T <= 8) {
         dim3 grid((E + 1) / 2, 1);
         router_logits_kernel<2, 8><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
-    } else if ((size_t)((T + 15) / 16) * ((E + 31) / 32) < (size_t)kNumSMs) {
+    } else if (T <= 32) {
         dim3 grid((E + 1) / 2, (T + 15) / 16);
         router_logits_kernel<2, 16><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+    } else if (big_tiles < 96) {
+        dim3 grid((E + 7) / 8, (T + 15) / 16);
+        router_logits_kernel<8, 16><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
     } else {
         static bool attr = false;
         const size_t smem = (size_t)(kBigTT + kBigWarps * kBigRW) * kRouterChunk * sizeof(float);
