@@ -62,6 +62,8 @@ struct strata_moe_layer {
     float* out_stage = nullptr;
     void* prefill_scratch = nullptr;
     float* one_global = nullptr;  // device float 1.0 for the shared expert table
+    void* d_wmaps = nullptr;      // [3][n_local] tensor-map descriptors of the packed weights
+    bool wmaps_ok = false;
     // f16 decode path for the FP4 formats
     bool f16_ok = false;
     uint32_t* d_not_ok = nullptr;
@@ -158,6 +160,24 @@ int sync_tables(strata_moe_layer* L) {
         }
     }
     if (getenv("STRATA_MOE_NO_F16_PATH")) L->f16_ok = false;
+    // tensor maps of the packed weights for the tensor-core path's TMA producer
+    L->wmaps_ok = false;
+    if (prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) {
+        struct alignas(64) Blob { unsigned char b[128]; };
+        std::vector<Blob> maps((size_t)3 * n);
+        bool ok = true;
+        for (int r = 0; r < 3 && ok; ++r) {
+            const uint32_t rows = r == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
+            const uint32_t cols = r == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+            for (uint32_t e = 0; e < n && ok; ++e)
+                ok = L->tab[r].packed[e] && ((uintptr_t)L->tab[r].packed[e] & 15u) == 0 &&
+                     prefill_encode_weight_map(&maps[(size_t)r * n + e], L->tab[r].packed[e], rows, cols) == 0;
+        }
+        if (ok) {
+            CK(cudaMemcpy(L->d_wmaps, maps.data(), maps.size() * sizeof(Blob), cudaMemcpyHostToDevice));
+            L->wmaps_ok = true;
+        }
+    }
     L->tables_dirty = false;
     return 0;
 }
@@ -197,6 +217,7 @@ bool all_registered(const strata_moe_layer* L, std::string* why) {
 bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
     if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) return false;
     if (L->d.format == STRATA_MOE_FMT_MXFP4 && !L->f16_ok) return false;  // needs the f16 weight window
+    if (!L->wmaps_ok) return false;
     const char* e = getenv("STRATA_MOE_PREFILL_MIN_ROWS");  // average rows per expert that switch paths
     const int thr = e ? atoi(e) : 24;
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
@@ -226,7 +247,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.y = y;
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
-        if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, s,
+        if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s,
                            ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
         mark(ctx, 6);
@@ -508,6 +529,12 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
     A(dalloc(L, &L->y, (size_t)P * H));
     A(dalloc(L, &L->one_global, 1));
     A(dalloc(L, &L->d_not_ok, 1));
+    {
+        void* wm = nullptr;
+        A(cudaMalloc(&wm, (size_t)3 * n * 128 + 128));
+        if (wm) L->owned.push_back(wm);
+        L->d_wmaps = wm;
+    }
     A(dalloc(L, &L->act_f32, (size_t)P * I));
     A(dalloc(L, &L->x_rowscale, (size_t)P));
     A(dalloc(L, &L->act_rowscale, (size_t)P));

@@ -101,8 +101,11 @@ bool prefill_supported(int fmt, uint32_t H, uint32_t I);
 size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
 // x16: [pairs_cap, H] f16 rows (pre-scaled, group order), x_rowscale [pairs_cap], act16:
 // [pairs_cap, I] f16 scratch.  mid, when non-null, is recorded between the two GEMMs.
+// wmaps: device array [3][n_groups] of 128-byte tensor-map descriptors made by
+// prefill_encode_weight_map (gate, up, down of every local expert).
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
-                   uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid);
+                   uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid);
+int prefill_encode_weight_map(void* out128, const void* packed, uint32_t rows, uint32_t K);
 int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
                         const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s);
 // combine.cu

@@ -7,11 +7,13 @@
 //
 //   warp 0        TMA producer: activation tiles [N x 64] f16 -> shared memory (128-byte swizzle)
 //   warp 1        MMA issuer: one thread issues tcgen05.mma (kind::f16, M=128, K=16) per k-slice
-//   warps 2..9    weight producers: stream packed 4-bit rows from HBM (32 B per row per stage),
+//   warp 2        TMA producer for the packed 4-bit weights: [128 rows x 128 B] blocks (256 columns,
+//                 four pipeline stages) land in a double-buffered, 128-byte-swizzled staging area
+//   warps 3..10   decoders: read their row's 32 packed bytes per stage from the staging area,
 //                 decode exactly to f16 (hardware E2M1 conversion / INT4 magic-number trick),
 //                 apply the block scale and store the tile K-major with the 128-byte swizzle the
 //                 MMA descriptor expects
-//   warps 10..13  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
+//   warps 11..14  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
 //                 scale (down), store
 // Accumulators are double-buffered in tensor memory (2 x 256 columns), so the epilogue of one
 // tile overlaps the main loop of the next.  CTAs are persistent (one per SM) and walk a tile
@@ -34,11 +36,14 @@ namespace smoe {
 constexpr uint32_t kNTile = 128;    // tokens per tile
 constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
-constexpr uint32_t kStages = 4;
+constexpr uint32_t kStages = 3;
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
-constexpr uint32_t kThreads = 14 * 32;
+constexpr uint32_t kThreads = 15 * 32;
 constexpr uint32_t kDequantThreads = 256;
+constexpr uint32_t kPkCols = 256;                       // columns per packed staging block (4 stages)
+constexpr uint32_t kPkTile = kMTile * (kPkCols / 2);    // 16 KiB of 4-bit weights: 128 rows x 128 B
+constexpr uint32_t kFirstDecodeWarp = 3, kFirstEpilogueWarp = 11;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kFmtBf16W = 3;  // plain BF16 weights (shared expert): tiles arrive by TMA, no decode
 
@@ -199,7 +204,9 @@ struct __align__(1024) PrefillSmem {
     uint8_t a0[kStages][kATile];  // gate (or down) weight tile
     uint8_t a1[kStages][kATile];  // up weight tile (gate/up kernel only)
     uint8_t b[kStages][kBTile];   // activation tile
+    uint8_t pk[2][2][kPkTile];    // packed 4-bit staging: [buffer][gate/down, up]
     uint64_t full_a[kStages], full_b[kStages], empty[kStages];
+    uint64_t pk_full[2], pk_empty[2];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     uint32_t abort_flag;
@@ -222,7 +229,7 @@ template <int FMT, bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_a0,
                    const __grid_constant__ CUtensorMap map_a1, PrefillArgs a, const float* __restrict__ rowscale,
-                   void* __restrict__ act_out_v) {
+                   void* __restrict__ act_out_v, const CUtensorMap* __restrict__ wmaps /* [3][n_groups] */) {
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem& S = *reinterpret_cast<PrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
@@ -242,6 +249,8 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
         for (int i = 0; i < 2; ++i) {
             mbar_init(&S.acc_full[i], 1);
             mbar_init(&S.acc_empty[i], 4);  // one arrival per epilogue warp
+            mbar_init(&S.pk_full[i], 1);
+            mbar_init(&S.pk_empty[i], kDequantThreads / 32);
         }
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -332,25 +341,61 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
         }
-    } else if (warp < 10 && FMT == kFmtBf16W) {
+    } else if (warp == 2) {
+        // ---------------------------------------------------------------- packed-weight TMA producer
+        if (lane == 0 && FMT != kFmtBf16W) {
+            const uint32_t blocks = (K + kPkCols - 1u) / kPkCols;
+            uint32_t bi = 0;
+            bool ok = true;
+            for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
+                TileInfo t;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+                const CUtensorMap* m0 = wmaps + (DUAL ? 0u : 2u) * a.n_groups + t.g;
+                const CUtensorMap* m1 = wmaps + 1u * a.n_groups + t.g;
+                for (uint32_t q = 0; q < blocks; ++q, ++bi) {
+                    const uint32_t pb = bi & 1u, ph = (bi >> 1) & 1u;
+                    if (!mbar_wait(&S.pk_empty[pb], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&S.pk_full[pb], DUAL ? 2u * kPkTile : kPkTile);
+                    tma_load_2d(S.pk[pb][0], m0, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
+                    if (DUAL) tma_load_2d(S.pk[pb][1], m1, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
+                }
+            }
+            if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
+            if (*abort_flag) {
+                for (uint32_t q = 0; q < (bi < 2u ? bi : 2u); ++q) {
+                    const uint32_t j = bi - 1u - q;
+                    const uint32_t addr = smem_u32(&S.pk_full[j & 1u]);
+                    for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
+                        uint32_t done;
+                        asm volatile(
+                            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+                            " selp.u32 %0, 1, 0, p;\n}"
+                            : "=r"(done)
+                            : "r"(addr), "r"((j >> 1) & 1u)
+                            : "memory");
+                        if (done) break;
+                    }
+                }
+            }
+        }
+    } else if (warp < kFirstEpilogueWarp && FMT == kFmtBf16W) {
         // BF16 weights need no decode: the TMA producer loads their tiles
-    } else if (warp < 10) {
+    } else if (warp < kFirstEpilogueWarp) {
         // ---------------------------------------------------------------- weight producers
-        const uint32_t d = threadIdx.x - 64u;  // 0..255
+        const uint32_t d = threadIdx.x - kFirstDecodeWarp * 32u;  // 0..255
         // DUAL: thread d decodes row d % 128 of gate (d < 128) or up (d >= 128), 64 columns.
         // else: thread d decodes row d / 2 of down, 32 columns (half d % 2).
         const uint32_t arow = DUAL ? (d & 127u) : (d >> 1);
         const uint32_t which = DUAL ? (d >> 7) : 0u;
         const uint32_t half = DUAL ? 0u : (d & 1u);
         constexpr uint32_t CH = DUAL ? 2u : 1u;  // 16-byte packed chunks per thread per stage
-        uint32_t it = 0;
+        uint32_t it = 0, bi = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
             TileInfo t;
             if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
             const WeightTable& wt = DUAL ? (which ? a.up : a.gate) : a.down;
             const uint32_t row = t.m0 + arow;
-            const uint8_t* prow = wt.packed[t.g] + (size_t)row * (K / 2u) + half * 16u;
             const uint8_t* srow = wt.scales[t.g];
             int32_t mx_off = 0;
             if (FMT == STRATA_MOE_FMT_MXFP4) {
@@ -361,50 +406,72 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             } else {
                 srow += (size_t)row * (K / 128u) * 2u;
             }
-            // Register ring of kPF stages: HBM latency (~1 us) spans several 64-column stages of
-            // tensor-core work, so the loads of stage ks + kPF are issued when stage ks is decoded.
-            constexpr uint32_t kPF = 4;
-            uint4 buf[kPF][CH];
-            uint32_t sbuf[kPF];
-            auto issue = [&](uint32_t ks, uint4(&dst)[CH], uint32_t& sdst) {
-                ks = ks < k_stages ? ks : k_stages - 1u;
-#pragma unroll
-                for (uint32_t c = 0; c < CH; ++c) dst[c] = ldg_stream16_c(prow + (size_t)ks * 32u + c * 16u);
+            // Scale bytes of one 256-column block of this thread's row, fetched one block ahead:
+            // MXFP4 8 bytes, NVFP4 16 bytes, INT4 two BF16 values.
+            auto load_scales = [&](uint32_t q) -> uint4 {
+                const uint32_t blocks = (K + kPkCols - 1u) / kPkCols;
+                q = q < blocks ? q : blocks - 1u;
+                uint4 v = make_uint4(0, 0, 0, 0);
                 if (FMT == STRATA_MOE_FMT_MXFP4) {
-                    sdst = DUAL ? (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + ks * 2u))
-                                : (uint32_t)__ldg(srow + ks * 2u + half);
+                    if ((q + 1u) * 8u <= K / 32u) {
+                        const uint2 w = __ldg(reinterpret_cast<const uint2*>(srow + q * 8u));
+                        v.x = w.x; v.y = w.y;
+                    } else {
+                        v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 8u));  // K % 256 == 128
+                    }
                 } else if (FMT == STRATA_MOE_FMT_NVFP4) {
-                    sdst = DUAL ? __ldg(reinterpret_cast<const uint32_t*>(srow + ks * 4u))
-                                : (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + ks * 4u + half * 2u));
+                    if ((q + 1u) * 16u <= K / 16u) {
+                        v = __ldg(reinterpret_cast<const uint4*>(srow + q * 16u));
+                    } else {
+                        const uint2 w = __ldg(reinterpret_cast<const uint2*>(srow + q * 16u));
+                        v.x = w.x; v.y = w.y;
+                    }
                 } else {
-                    sdst = __ldg(reinterpret_cast<const unsigned short*>(srow + (ks >> 1) * 2u));
+                    if ((q + 1u) * 2u <= K / 128u) v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 4u));
+                    else v.x = __ldg(reinterpret_cast<const unsigned short*>(srow + q * 4u));
                 }
+                return v;
             };
+            const uint32_t blocks = (K + kPkCols - 1u) / kPkCols;
+            uint4 sc_next = load_scales(0);
+            for (uint32_t q = 0; q < blocks && ok; ++q, ++bi) {
+                const uint4 sc = sc_next;
+                sc_next = load_scales(q + 1u);
+                const uint32_t pb = bi & 1u, pph = (bi >> 1) & 1u;
+                if (!mbar_wait(&S.pk_full[pb], pph, abort_flag)) { ok = false; break; }
+                const uint8_t* pk_row = S.pk[pb][which] + arow * 128u;
+                const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
-            for (uint32_t j = 0; j < kPF; ++j) issue(j, buf[j], sbuf[j]);
-            for (uint32_t ks0 = 0; ks0 < k_stages && ok; ks0 += kPF) {
-#pragma unroll
-                for (uint32_t j = 0; j < kPF; ++j) {
-                    const uint32_t ks = ks0 + j;
+                for (uint32_t j = 0; j < kPkCols / kBK; ++j) {
+                    const uint32_t ks = q * (kPkCols / kBK) + j;
                     if (ks >= k_stages) break;
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     ++it;
+                    // this thread's packed bytes of the stage: 16-byte chunks 2j (+1), swizzled by row
+                    uint4 pkv[CH];
+#pragma unroll
+                    for (uint32_t c = 0; c < CH; ++c) {
+                        const uint32_t chunk = 2u * j + (DUAL ? c : half);
+                        pkv[c] = *reinterpret_cast<const uint4*>(pk_row + ((chunk ^ (arow & 7u)) << 4));
+                    }
                     // block multipliers of this thread's 32-column chunks
                     uint32_t m[CH][4];
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
+                        const uint32_t c32 = 2u * j + (DUAL ? c : half);  // 32-column chunk inside the block
                         if (FMT == STRATA_MOE_FMT_MXFP4) {
-                            const uint32_t e = (sbuf[j] >> (8u * c)) & 0xFFu;
+                            const uint32_t e = (scw[c32 >> 2] >> (8u * (c32 & 3u))) & 0xFFu;
                             const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
                             m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
                         } else if (FMT == STRATA_MOE_FMT_NVFP4) {
-                            const uint32_t sb = (sbuf[j] >> (16u * c)) & 0xFFFFu;
+                            const uint32_t sb = (scw[c32 >> 1] >> (16u * (c32 & 1u))) & 0xFFFFu;
                             uint32_t pair;
                             asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"((unsigned short)sb));
                             m[c][0] = m[c][1] = __byte_perm(pair, pair, 0x1010);
                             m[c][2] = m[c][3] = __byte_perm(pair, pair, 0x3232);
                         } else {
-                            const uint32_t h = __half_as_ushort(__float2half_rn(__uint_as_float(sbuf[j] << 16)));
+                            const uint32_t sb = (scw[0] >> (16u * (c32 >> 2))) & 0xFFFFu;
+                            const uint32_t h = __half_as_ushort(__float2half_rn(__uint_as_float(sb << 16)));
                             m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
                         }
                     }
@@ -413,23 +480,24 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
                         uint4 o[4];
-                        decode16<FMT>(buf[j][c], m[c], o);
+                        decode16<FMT>(pkv[c], m[c], o);
                         const uint32_t chunk0 = (DUAL ? c : half) * 4u;  // first 16-byte chunk (8 columns each)
 #pragma unroll
-                        for (uint32_t q = 0; q < 4; ++q)
-                            *reinterpret_cast<uint4*>(tile_base + (((chunk0 + q) ^ (arow & 7u)) << 4)) = o[q];
+                        for (uint32_t qq = 0; qq < 4; ++qq)
+                            *reinterpret_cast<uint4*>(tile_base + (((chunk0 + qq) ^ (arow & 7u)) << 4)) = o[qq];
                     }
                     fence_async_smem();  // make the generic-proxy stores visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&S.full_a[s]);
-                    issue(ks + kPF, buf[j], sbuf[j]);
                 }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&S.pk_empty[pb]);  // this warp is done reading the block
             }
         }
         if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
     } else {
         // ---------------------------------------------------------------- epilogue
-        const uint32_t ew = warp - 10u;          // == warp % 4: tensor-memory lane quarter
+        const uint32_t ew = warp - kFirstEpilogueWarp;
         const uint32_t lane_base = (warp & 3u) * 32u;
         uint32_t tcount = 0;
         bool ok = true, bad = false;
@@ -575,29 +643,50 @@ static int set_smem_attr(size_t smem) {
     return 0;
 }
 
+// Tensor map over one projection's packed 4-bit rows ([rows, K/2] bytes): 128-byte x 128-row
+// boxes, 128-byte swizzle.  `out` receives the 128-byte descriptor (host memory).
+int prefill_encode_weight_map(void* out, const void* packed, uint32_t rows, uint32_t K) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return -1;
+    const cuuint64_t dims[2] = {K / 2u, rows};
+    const cuuint64_t strides[1] = {K / 2u};
+    const cuuint32_t box[2] = {kPkCols / 2u, kMTile};
+    const cuuint32_t estr[2] = {1, 1};
+    static_assert(sizeof(CUtensorMap) == 128, "descriptor size");
+    return fn(static_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(packed), dims,
+              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+               ? 0
+               : -1;
+}
+
 template <int FMT>
 static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
-                      uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid) {
+                      uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid) {
+    const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
     CUtensorMap map_x, map_act;
     if (!make_map(&map_x, x16, pairs_cap, a.H, kNTile) || !make_map(&map_act, act16, pairs_cap, a.I, kNTile))
         return -1;
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<FMT>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16);
+    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16, wm);
     if (mid) cudaEventRecord(mid, s);
-    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr);
+    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr,
+                                                                   wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
-                   uint32_t pairs_cap, cudaStream_t s, cudaEvent_t mid) {
+                   uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid) {
     switch (a.fmt) {
-        case STRATA_MOE_FMT_MXFP4: return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
-        case STRATA_MOE_FMT_NVFP4: return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
+        case STRATA_MOE_FMT_MXFP4:
+            return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
+        case STRATA_MOE_FMT_NVFP4:
+            return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
         case STRATA_MOE_FMT_INT4G128:
-            return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, x16, x_rowscale, act16, pairs_cap, s, mid);
+            return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
         default: return -1;
     }
 }
@@ -615,8 +704,9 @@ int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, cons
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<kFmtBf16W>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<kFmtBf16W, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act);
-    prefill_ffn_kernel<kFmtBf16W, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr);
+    prefill_ffn_kernel<kFmtBf16W, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
+    prefill_ffn_kernel<kFmtBf16W, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
+                                                                         nullptr);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
