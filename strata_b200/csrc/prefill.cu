@@ -212,20 +212,24 @@ struct __align__(1024) PrefillSmem {
     uint32_t abort_flag;
 };
 
-__device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile, uint32_t m_tiles, TileInfo& t) {
+__device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile, uint32_t m_tiles, TileInfo& t,
+                                            uint32_t tile_feat = kMTile) {
     const uint32_t total = table[0] * m_tiles;
     if (tile >= total) return false;
     const uint32_t j = tile / m_tiles;
     t.g = table[4 + 3 * j];
     t.row0 = table[4 + 3 * j + 1];
     t.n = table[4 + 3 * j + 2];
-    t.m0 = (tile - j * m_tiles) * kMTile;
+    t.m0 = (tile - j * m_tiles) * tile_feat;
     return true;
 }
 
-// DUAL = true : gate + up tiles, SwiGLU, act (f16) out.   K = H, features over I.
-// DUAL = false: down tile, y (fp32) out.                    K = I, features over H.
-template <int FMT, bool DUAL>
+// MODE 0: gate + up tiles of the same 128 features, SwiGLU, act (16-bit) out.  K = H, features over I.
+// MODE 1: one down tile (128 features), y (fp32) out.                          K = I, features over H.
+// MODE 2: two adjacent down tiles (256 features) against the same activation tile -- halves the
+//         shared-memory traffic per MMA of MODE 1; needs H % 256 == 0.
+// DUAL (two weight tiles and two accumulators per activation tile) = MODE 0 or 2.
+template <int FMT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_a0,
                    const __grid_constant__ CUtensorMap map_a1, PrefillArgs a, const float* __restrict__ rowscale,
@@ -233,9 +237,13 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem& S = *reinterpret_cast<PrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t K = DUAL ? a.H : a.I;
-    const uint32_t R = DUAL ? a.I : a.H;
-    const uint32_t m_tiles = R / kMTile;
+    constexpr bool DUAL = MODE != 1;
+    constexpr bool GU = MODE == 0;
+    constexpr uint32_t kTileFeat = MODE == 2 ? 2u * kMTile : kMTile;  // features per tile
+    constexpr uint32_t kSecond = MODE == 2 ? kMTile : 0u;              // row offset of the second weight tile
+    const uint32_t K = GU ? a.H : a.I;
+    const uint32_t R = GU ? a.I : a.H;
+    const uint32_t m_tiles = R / kTileFeat;
     const uint32_t k_stages = K / kBK;
     volatile uint32_t* abort_flag = &S.abort_flag;
 
@@ -273,7 +281,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
                 TileInfo t;
-                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -282,7 +290,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                     if (FMT == kFmtBf16W) {
                         mbar_arrive_expect_tx(&S.full_a[s], DUAL ? 2u * kATile : kATile);
                         tma_load_2d(S.a0[s], &map_a0, ks * kBK, t.m0, &S.full_a[s]);
-                        if (DUAL) tma_load_2d(S.a1[s], &map_a1, ks * kBK, t.m0, &S.full_a[s]);
+                        if (DUAL) tma_load_2d(S.a1[s], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[s]);
                     }
                 }
             }
@@ -314,7 +322,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
                 TileInfo t;
-                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
                 const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
                 if (!mbar_wait(&S.acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
@@ -349,15 +357,15 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
                 TileInfo t;
-                if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
-                const CUtensorMap* m0 = wmaps + (DUAL ? 0u : 2u) * a.n_groups + t.g;
-                const CUtensorMap* m1 = wmaps + 1u * a.n_groups + t.g;
+                if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
+                const CUtensorMap* m0 = wmaps + (GU ? 0u : 2u) * a.n_groups + t.g;
+                const CUtensorMap* m1 = wmaps + (GU ? 1u : 2u) * a.n_groups + t.g;
                 for (uint32_t q = 0; q < blocks; ++q, ++bi) {
                     const uint32_t pb = bi & 1u, ph = (bi >> 1) & 1u;
                     if (!mbar_wait(&S.pk_empty[pb], ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&S.pk_full[pb], DUAL ? 2u * kPkTile : kPkTile);
                     tma_load_2d(S.pk[pb][0], m0, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
-                    if (DUAL) tma_load_2d(S.pk[pb][1], m1, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
+                    if (DUAL) tma_load_2d(S.pk[pb][1], m1, q * (kPkCols / 2u), t.m0 + kSecond, &S.pk_full[pb]);
                 }
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
@@ -393,9 +401,9 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
             TileInfo t;
-            if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
-            const WeightTable& wt = DUAL ? (which ? a.up : a.gate) : a.down;
-            const uint32_t row = t.m0 + arow;
+            if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
+            const WeightTable& wt = GU ? (which ? a.up : a.gate) : a.down;
+            const uint32_t row = t.m0 + arow + which * kSecond;
             const uint8_t* srow = wt.scales[t.g];
             int32_t mx_off = 0;
             if (FMT == STRATA_MOE_FMT_MXFP4) {
@@ -504,18 +512,18 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
         (void)ew;
         for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
             TileInfo t;
-            if (!tile_lookup(a.tile_table, tile, m_tiles, t)) break;
+            if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
             const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
             if (!mbar_wait(&S.acc_full[buf], aph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t feat = t.m0 + lane_base + lane;
             float s0, s1 = 1.0f;
             constexpr bool kNoPost = FMT == STRATA_MOE_FMT_INT4G128 || FMT == kFmtBf16W;
-            if (DUAL) {
+            if (GU) {
                 s0 = kNoPost ? 1.0f : a.gate.post_scale[t.g];
                 s1 = kNoPost ? 1.0f : a.up.post_scale[t.g];
             } else {
-                s0 = kNoPost ? 1.0f : a.down.post_scale[t.g];
+                s0 = s1 = kNoPost ? 1.0f : a.down.post_scale[t.g];
             }
             const uint32_t taddr = tmem_base + (lane_base << 16) + buf * 256u;
             for (uint32_t c0 = 0; c0 < t.n; c0 += 32u) {
@@ -527,7 +535,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                 for (uint32_t j = 0; j < 32u; ++j) {
                     if (c0 + j >= t.n) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
-                    if (DUAL) {
+                    if (GU) {
                         const float rs = rowscale ? rowscale[pos] : 1.0f;
                         const float gv = __uint_as_float(g[j]) * s0 * rs, uv = __uint_as_float(u[j]) * s1 * rs;
                         const float e = __expf(-fabsf(gv));
@@ -542,6 +550,11 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                         const float v = __uint_as_float(g[j]) * s0;
                         if (!(fabsf(v) <= 3.0e38f)) bad = true;
                         a.y[pos * R + feat] = v;
+                        if (MODE == 2) {
+                            const float v2 = __uint_as_float(u[j]) * s1;
+                            if (!(fabsf(v2) <= 3.0e38f)) bad = true;
+                            a.y[pos * R + feat + kMTile] = v2;
+                        }
                     }
                 }
             }
@@ -634,9 +647,11 @@ template <int FMT>
 static int set_smem_attr(size_t smem) {
     static bool done = false;
     if (done) return 0;
-    if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)smem) != cudaSuccess ||
+        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
         return -2;
     done = true;
@@ -670,10 +685,12 @@ static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rows
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<FMT>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<FMT, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16, wm);
+    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16, wm);
     if (mid) cudaEventRecord(mid, s);
-    prefill_ffn_kernel<FMT, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr,
-                                                                   wm);
+    if (a.H % 256u == 0u)
+        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr, wm);
+    else
+        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr, wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -704,8 +721,12 @@ int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, cons
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<kFmtBf16W>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<kFmtBf16W, true><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
-    prefill_ffn_kernel<kFmtBf16W, false><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
+    prefill_ffn_kernel<kFmtBf16W, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
+    if (a.H % 256u == 0u)
+        prefill_ffn_kernel<kFmtBf16W, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
+                                                                         nullptr);
+    else
+        prefill_ffn_kernel<kFmtBf16W, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
                                                                          nullptr);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;

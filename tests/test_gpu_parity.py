@@ -238,3 +238,13 @@ def test_shared_expert_on_tensor_core_path(ctx):
     assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
     rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
     assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
+
+
+def test_prefill_path_odd_hidden_size(ctx):
+    # H = 384: not a multiple of 256, so the down projection takes the single-tile mode and the
+    # last packed staging block of every row is half filled
+    cfg = small(synth.FMT_MXFP4, T=400, E=8, k=2, H=384, I=128, name="prefill_odd")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
