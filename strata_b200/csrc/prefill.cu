@@ -416,27 +416,40 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             }
             // Scale bytes of one 256-column block of this thread's row, fetched one block ahead:
             // MXFP4 8 bytes, NVFP4 16 bytes, INT4 two BF16 values.
+            // Vector loads need the row's scale bytes aligned to the vector: true when K % 256 == 0
+            // (then every row holds a whole number of blocks); otherwise fall back to narrow loads.
+            const bool whole_blocks = (K % kPkCols) == 0u;
             auto load_scales = [&](uint32_t q) -> uint4 {
-                const uint32_t blocks = (K + kPkCols - 1u) / kPkCols;
-                q = q < blocks ? q : blocks - 1u;
+                const uint32_t nblk = (K + kPkCols - 1u) / kPkCols;
+                q = q < nblk ? q : nblk - 1u;
                 uint4 v = make_uint4(0, 0, 0, 0);
-                if (FMT == STRATA_MOE_FMT_MXFP4) {
-                    if ((q + 1u) * 8u <= K / 32u) {
+                if (FMT == STRATA_MOE_FMT_MXFP4) {          // 8 bytes per block, rows 4-byte aligned
+                    if (whole_blocks) {
                         const uint2 w = __ldg(reinterpret_cast<const uint2*>(srow + q * 8u));
                         v.x = w.x; v.y = w.y;
                     } else {
-                        v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 8u));  // K % 256 == 128
+                        v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 8u));
+                        if ((q + 1u) * 8u <= K / 32u) v.y = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 8u + 4u));
                     }
-                } else if (FMT == STRATA_MOE_FMT_NVFP4) {
-                    if ((q + 1u) * 16u <= K / 16u) {
+                } else if (FMT == STRATA_MOE_FMT_NVFP4) {   // 16 bytes per block, rows 8-byte aligned
+                    if (whole_blocks) {
                         v = __ldg(reinterpret_cast<const uint4*>(srow + q * 16u));
                     } else {
                         const uint2 w = __ldg(reinterpret_cast<const uint2*>(srow + q * 16u));
                         v.x = w.x; v.y = w.y;
+                        if ((q + 1u) * 16u <= K / 16u) {
+                            const uint2 w2 = __ldg(reinterpret_cast<const uint2*>(srow + q * 16u + 8u));
+                            v.z = w2.x; v.w = w2.y;
+                        }
                     }
-                } else {
-                    if ((q + 1u) * 2u <= K / 128u) v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 4u));
-                    else v.x = __ldg(reinterpret_cast<const unsigned short*>(srow + q * 4u));
+                } else {                                     // two BF16 per block, rows 2-byte aligned
+                    if (whole_blocks) {
+                        v.x = __ldg(reinterpret_cast<const uint32_t*>(srow + q * 4u));
+                    } else {
+                        v.x = __ldg(reinterpret_cast<const unsigned short*>(srow + q * 4u));
+                        if ((q + 1u) * 2u <= K / 128u)
+                            v.x |= (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(srow + q * 4u + 2u)) << 16;
+                    }
                 }
                 return v;
             };
