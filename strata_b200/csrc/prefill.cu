@@ -9,11 +9,11 @@
 //   warp 1        MMA issuer: one thread issues tcgen05.mma (kind::f16, M=128, K=16) per k-slice
 //   warp 2        TMA producer for the packed 4-bit weights: [128 rows x 128 B] blocks (256 columns,
 //                 four pipeline stages) land in a double-buffered, 128-byte-swizzled staging area
-//   warps 3..10   decoders: read their row's 32 packed bytes per stage from the staging area,
+//   warps 3..18   decoders: each lane reads 16 packed bytes (32 columns of one row) per stage from the staging area,
 //                 decode exactly to f16 (hardware E2M1 conversion / INT4 magic-number trick),
 //                 apply the block scale and store the tile K-major with the 128-byte swizzle the
 //                 MMA descriptor expects
-//   warps 11..14  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
+//   warps 19..22  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
 //                 scale (down), store
 // Accumulators are double-buffered in tensor memory (2 x 256 columns), so the epilogue of one
 // tile overlaps the main loop of the next.  CTAs are persistent (one per SM) and walk a tile
@@ -39,11 +39,11 @@ constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 pe
 constexpr uint32_t kStages = 3;
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
-constexpr uint32_t kThreads = 15 * 32;
-constexpr uint32_t kDequantThreads = 256;
+constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
+constexpr uint32_t kThreads = (3 + kDecodeWarps + 4) * 32;
 constexpr uint32_t kPkCols = 256;                       // columns per packed staging block (4 stages)
 constexpr uint32_t kPkTile = kMTile * (kPkCols / 2);    // 16 KiB of 4-bit weights: 128 rows x 128 B
-constexpr uint32_t kFirstDecodeWarp = 3, kFirstEpilogueWarp = 11;
+constexpr uint32_t kFirstDecodeWarp = 3, kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kFmtBf16W = 3;  // plain BF16 weights (shared expert): tiles arrive by TMA, no decode
 
@@ -129,6 +129,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t v[32]) {
           "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
           "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
           "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t v[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
 }
@@ -250,7 +259,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
             // one arrival per producer warp, or one TMA transaction group for BF16 weights
-            mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : kDequantThreads / 32);
+            mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps : kDecodeWarps / 2u));
             mbar_init(&S.full_b[s], 1);
             mbar_init(&S.empty[s], 1);
         }
@@ -258,7 +267,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
             mbar_init(&S.acc_full[i], 1);
             mbar_init(&S.acc_empty[i], 4);  // one arrival per epilogue warp
             mbar_init(&S.pk_full[i], 1);
-            mbar_init(&S.pk_empty[i], kDequantThreads / 32);
+            mbar_init(&S.pk_empty[i], DUAL ? kDecodeWarps : kDecodeWarps / 2u);
         }
         S.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -390,16 +399,19 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
         // BF16 weights need no decode: the TMA producer loads their tiles
     } else if (warp < kFirstEpilogueWarp) {
         // ---------------------------------------------------------------- weight producers
-        const uint32_t d = threadIdx.x - kFirstDecodeWarp * 32u;  // 0..255
-        // DUAL: thread d decodes row d % 128 of gate (d < 128) or up (d >= 128), 64 columns.
-        // else: thread d decodes row d / 2 of down, 32 columns (half d % 2).
-        const uint32_t arow = DUAL ? (d & 127u) : (d >> 1);
-        const uint32_t which = DUAL ? (d >> 7) : 0u;
-        const uint32_t half = DUAL ? 0u : (d & 1u);
-        constexpr uint32_t CH = DUAL ? 2u : 1u;  // 16-byte packed chunks per thread per stage
+        // Decode warp wd owns 16 rows of one weight tile: lanes 0-15 take the first 32 columns of
+        // a stage, lanes 16-31 the second 32 (8 consecutive rows per quarter-warp keeps both the
+        // swizzled reads and the swizzled writes free of bank conflicts).  With one weight tile
+        // per stage (MODE 1) only the first half of the decode warps work.
+        const uint32_t wd = warp - kFirstDecodeWarp;
+        const uint32_t which = DUAL ? (wd >> 3) : 0u;
+        const uint32_t arow = (wd & 7u) * 16u + (lane & 15u);
+        const uint32_t half = lane >> 4;
+        constexpr uint32_t CH = 1u;  // 16-byte packed chunks per thread per stage
+        const bool active = DUAL || wd < kDecodeWarps / 2u;
         uint32_t it = 0, bi = 0;
         bool ok = true;
-        for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x) {
+        for (uint32_t tile = blockIdx.x; ok && active; tile += gridDim.x) {
             TileInfo t;
             if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
             const WeightTable& wt = GU ? (which ? a.up : a.gate) : a.down;
@@ -472,14 +484,14 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                     uint4 pkv[CH];
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
-                        const uint32_t chunk = 2u * j + (DUAL ? c : half);
+                        const uint32_t chunk = 2u * j + half + c;
                         pkv[c] = *reinterpret_cast<const uint4*>(pk_row + ((chunk ^ (arow & 7u)) << 4));
                     }
                     // block multipliers of this thread's 32-column chunks
                     uint32_t m[CH][4];
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
-                        const uint32_t c32 = 2u * j + (DUAL ? c : half);  // 32-column chunk inside the block
+                        const uint32_t c32 = 2u * j + half + c;  // 32-column chunk inside the block
                         if (FMT == STRATA_MOE_FMT_MXFP4) {
                             const uint32_t e = (scw[c32 >> 2] >> (8u * (c32 & 3u))) & 0xFFu;
                             const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
@@ -502,7 +514,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                     for (uint32_t c = 0; c < CH; ++c) {
                         uint4 o[4];
                         decode16<FMT>(pkv[c], m[c], o);
-                        const uint32_t chunk0 = (DUAL ? c : half) * 4u;  // first 16-byte chunk (8 columns each)
+                        const uint32_t chunk0 = (half + c) * 4u;  // first 16-byte chunk (8 columns each)
 #pragma unroll
                         for (uint32_t qq = 0; qq < 4; ++qq)
                             *reinterpret_cast<uint4*>(tile_base + (((chunk0 + qq) ^ (arow & 7u)) << 4)) = o[qq];
@@ -539,13 +551,13 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                 s0 = s1 = kNoPost ? 1.0f : a.down.post_scale[t.g];
             }
             const uint32_t taddr = tmem_base + (lane_base << 16) + buf * 256u;
-            for (uint32_t c0 = 0; c0 < t.n; c0 += 32u) {
-                uint32_t g[32], u[32];
-                tmem_ld32(taddr + c0, g);
-                if (DUAL) tmem_ld32(taddr + kNTile + c0, u);
+            for (uint32_t c0 = 0; c0 < t.n; c0 += 16u) {
+                uint32_t g[16], u[16];
+                tmem_ld16(taddr + c0, g);
+                if (DUAL) tmem_ld16(taddr + kNTile + c0, u);
                 tmem_ld_wait();
 #pragma unroll
-                for (uint32_t j = 0; j < 32u; ++j) {
+                for (uint32_t j = 0; j < 16u; ++j) {
                     if (c0 + j >= t.n) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
                     if (GU) {
