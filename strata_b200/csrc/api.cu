@@ -247,6 +247,10 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.y = y;
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
+        {
+            const char* dbg = getenv("STRATA_MOE_PREFILL_DEBUG");
+            p.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
+        }
         if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s,
                            ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");

@@ -96,6 +96,7 @@ struct PrefillArgs {
     float* y;                      // [pairs, H] fp32
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
+    uint32_t debug;                // timing experiments only (wrong results): 1 = no MMA, 2 = no decode, 4 = no stores
 };
 bool prefill_supported(int fmt, uint32_t H, uint32_t I);
 size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);

@@ -204,6 +204,12 @@ __device__ __forceinline__ void decode16(const uint4& p, const uint32_t m[4], ui
     }
 }
 
+// Activation tensor maps with boxes of 16, 32, 64 and 128 rows: a tile with few valid rows
+// fetches only the rows the MMA will read (rounded up to the next box size).
+struct BMaps {
+    CUtensorMap m[4];
+};
+
 struct TileInfo {
     uint32_t g, row0, n;  // expert, first row of this n-tile, valid rows (1..kNTile)
     uint32_t m0;          // first output feature
@@ -240,7 +246,7 @@ __device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile
 // DUAL (two weight tiles and two accumulators per activation tile) = MODE 0 or 2.
 template <int FMT, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_a0,
+prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__ CUtensorMap map_a0,
                    const __grid_constant__ CUtensorMap map_a1, PrefillArgs a, const float* __restrict__ rowscale,
                    void* __restrict__ act_out_v, const CUtensorMap* __restrict__ wmaps /* [3][n_groups] */) {
     extern __shared__ uint8_t smem_raw[];
@@ -294,8 +300,9 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
                     if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&S.full_b[s], kBTile);
-                    tma_load_2d(S.b[s], &map_b, ks * kBK, t.row0, &S.full_b[s]);
+                    const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
+                    mbar_arrive_expect_tx(&S.full_b[s], (16u << bsel) * kBK * 2u);
+                    tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
                         mbar_arrive_expect_tx(&S.full_a[s], DUAL ? 2u * kATile : kATile);
                         tma_load_2d(S.a0[s], &map_a0, ks * kBK, t.m0, &S.full_a[s]);
@@ -348,6 +355,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                     const uint32_t a0 = smem_u32(S.a0[s]), a1 = smem_u32(S.a1[s]), b = smem_u32(S.b[s]);
 #pragma unroll
                     for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
+                        if (a.debug & 1u) break;
                         const uint64_t bd = umma_desc_sw128(b + kk * 32u);
                         umma_f16(d0, umma_desc_sw128(a0 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
                         if (DUAL) umma_f16(d1, umma_desc_sw128(a1 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
@@ -512,6 +520,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                     uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
+                        if (a.debug & 2u) break;
                         uint4 o[4];
                         decode16<FMT>(pkv[c], m[c], o);
                         const uint32_t chunk0 = (half + c) * 4u;  // first 16-byte chunk (8 columns each)
@@ -558,7 +567,7 @@ prefill_ffn_kernel(const __grid_constant__ CUtensorMap map_b, const __grid_const
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t j = 0; j < 16u; ++j) {
-                    if (c0 + j >= t.n) break;
+                    if (c0 + j >= t.n || (a.debug & 4u)) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
                     if (GU) {
                         const float rs = rowscale ? rowscale[pos] : 1.0f;
@@ -668,6 +677,12 @@ size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs) {
     return (4 + 3 * ((size_t)pairs / kNTile + n_groups + 1)) * sizeof(uint32_t);
 }
 
+static bool make_bmaps(BMaps* b, const void* base, uint64_t rows, uint64_t cols) {
+    for (int i = 0; i < 4; ++i)
+        if (!make_map(&b->m[i], base, rows, cols, 16u << i)) return false;
+    return true;
+}
+
 template <int FMT>
 static int set_smem_attr(size_t smem) {
     static bool done = false;
@@ -704,18 +719,18 @@ template <int FMT>
 static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                       uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid) {
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
-    CUtensorMap map_x, map_act;
-    if (!make_map(&map_x, x16, pairs_cap, a.H, kNTile) || !make_map(&map_act, act16, pairs_cap, a.I, kNTile))
-        return -1;
+    BMaps map_x, map_act;
+    if (!make_bmaps(&map_x, x16, pairs_cap, a.H) || !make_bmaps(&map_act, act16, pairs_cap, a.I)) return -1;
+    const CUtensorMap& dummy = map_x.m[0];
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<FMT>(smem)) return -2;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
-    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, map_x, map_x, a, x_rowscale, act16, wm);
+    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
     if (mid) cudaEventRecord(mid, s);
     if (a.H % 256u == 0u)
-        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr, wm);
+        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     else
-        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, map_act, map_act, a, nullptr, nullptr, wm);
+        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
@@ -738,8 +753,9 @@ int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscal
 // a.offsets must hold {0, rows}; a.n_groups = 1.
 int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
                         const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
-    CUtensorMap map_x, map_act, map_g, map_u, map_d;
-    if (!make_map(&map_x, x, rows, a.H, kNTile) || !make_map(&map_act, act, rows_cap, a.I, kNTile) ||
+    BMaps map_x, map_act;
+    CUtensorMap map_g, map_u, map_d;
+    if (!make_bmaps(&map_x, x, rows, a.H) || !make_bmaps(&map_act, act, rows_cap, a.I) ||
         !make_map(&map_g, w_gate, a.I, a.H, kMTile) || !make_map(&map_u, w_up, a.I, a.H, kMTile) ||
         !make_map(&map_d, w_down, a.H, a.I, kMTile))
         return -1;
