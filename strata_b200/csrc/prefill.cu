@@ -36,7 +36,10 @@ namespace smoe {
 constexpr uint32_t kNTile = 128;    // tokens per tile
 constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
-constexpr uint32_t kStages = 3;
+// Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
+// the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
+constexpr uint32_t kAStages = 2;
+constexpr uint32_t kBStages = 5;
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
@@ -216,11 +219,11 @@ struct TileInfo {
 };
 
 struct __align__(1024) PrefillSmem {
-    uint8_t a0[kStages][kATile];  // gate (or down) weight tile
-    uint8_t a1[kStages][kATile];  // up weight tile (gate/up kernel only)
-    uint8_t b[kStages][kBTile];   // activation tile
+    uint8_t a0[kAStages][kATile];  // gate (or down) weight tile
+    uint8_t a1[kAStages][kATile];  // up (or second down) weight tile
+    uint8_t b[kBStages][kBTile];   // activation tile
     uint8_t pk[2][2][kPkTile];    // packed 4-bit staging: [buffer][gate/down, up]
-    uint64_t full_a[kStages], full_b[kStages], empty[kStages];
+    uint64_t full_a[kAStages], empty_a[kAStages], full_b[kBStages], empty_b[kBStages];
     uint64_t pk_full[2], pk_empty[2];
     uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
@@ -263,11 +266,14 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     volatile uint32_t* abort_flag = &S.abort_flag;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kStages; ++s) {
+        for (uint32_t s = 0; s < kAStages; ++s) {
             // one arrival per producer warp, or one TMA transaction group for BF16 weights
             mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps : kDecodeWarps / 2u));
+            mbar_init(&S.empty_a[s], 1);
+        }
+        for (uint32_t s = 0; s < kBStages; ++s) {
             mbar_init(&S.full_b[s], 1);
-            mbar_init(&S.empty[s], 1);
+            mbar_init(&S.empty_b[s], 1);
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&S.acc_full[i], 1);
@@ -298,15 +304,17 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 TileInfo t;
                 if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
+                    if (!mbar_wait(&S.empty_b[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
                     mbar_arrive_expect_tx(&S.full_b[s], (16u << bsel) * kBK * 2u);
                     tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
-                        mbar_arrive_expect_tx(&S.full_a[s], DUAL ? 2u * kATile : kATile);
-                        tma_load_2d(S.a0[s], &map_a0, ks * kBK, t.m0, &S.full_a[s]);
-                        if (DUAL) tma_load_2d(S.a1[s], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[s]);
+                        const uint32_t sa = it % kAStages, pa = (it / kAStages) & 1u;
+                        if (!mbar_wait(&S.empty_a[sa], pa ^ 1u, abort_flag)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&S.full_a[sa], DUAL ? 2u * kATile : kATile);
+                        tma_load_2d(S.a0[sa], &map_a0, ks * kBK, t.m0, &S.full_a[sa]);
+                        if (DUAL) tma_load_2d(S.a1[sa], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[sa]);
                     }
                 }
             }
@@ -314,17 +322,17 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
             if (*abort_flag) {
                 // copies issued but possibly not consumed: give each a bounded chance to land
                 // before the CTA's shared memory is released
-                const uint32_t pending = it < kStages ? it : kStages;
+                const uint32_t pending = it < kBStages ? it : kBStages;
                 for (uint32_t q = 0; q < pending; ++q) {
                     const uint32_t j = it - 1u - q;
-                    const uint32_t addr = smem_u32(&S.full_b[j % kStages]);
+                    const uint32_t addr = smem_u32(&S.full_b[j % kBStages]);
                     for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
                         uint32_t done;
                         asm volatile(
                             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                             " selp.u32 %0, 1, 0, p;\n}"
                             : "=r"(done)
-                            : "r"(addr), "r"((j / kStages) & 1u)
+                            : "r"(addr), "r"((j / kBStages) & 1u)
                             : "memory");
                         if (done) break;
                     }
@@ -346,13 +354,14 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 const uint32_t idesc = umma_idesc_f16(n, FMT == kFmtBf16W ? 1u : 0u);
                 const uint32_t d0 = tmem_base + buf * 256u, d1 = d0 + kNTile;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
-                    if (!mbar_wait(&S.full_a[s], ph, abort_flag) || !mbar_wait(&S.full_b[s], ph, abort_flag)) {
+                    const uint32_t sa = it % kAStages, pa = (it / kAStages) & 1u;
+                    const uint32_t sb = it % kBStages, pb = (it / kBStages) & 1u;
+                    if (!mbar_wait(&S.full_a[sa], pa, abort_flag) || !mbar_wait(&S.full_b[sb], pb, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a0 = smem_u32(S.a0[s]), a1 = smem_u32(S.a1[s]), b = smem_u32(S.b[s]);
+                    const uint32_t a0 = smem_u32(S.a0[sa]), a1 = smem_u32(S.a1[sa]), b = smem_u32(S.b[sb]);
 #pragma unroll
                     for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
                         if (a.debug & 1u) break;
@@ -360,7 +369,8 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         umma_f16(d0, umma_desc_sw128(a0 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
                         if (DUAL) umma_f16(d1, umma_desc_sw128(a1 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
                     }
-                    umma_commit(&S.empty[s]);  // frees the stage once these MMAs have read it
+                    umma_commit(&S.empty_a[sa]);  // both tiles are free once these MMAs have read them
+                    umma_commit(&S.empty_b[sb]);
                 }
                 if (ok) umma_commit(&S.acc_full[buf]);
             }
@@ -486,7 +496,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 for (uint32_t j = 0; j < kPkCols / kBK; ++j) {
                     const uint32_t ks = q * (kPkCols / kBK) + j;
                     if (ks >= k_stages) break;
-                    const uint32_t s = it % kStages, ph = (it / kStages) & 1u;
+                    const uint32_t s = it % kAStages, ph = (it / kAStages) & 1u;
                     ++it;
                     // this thread's packed bytes of the stage: 16-byte chunks 2j (+1), swizzled by row
                     uint4 pkv[CH];
@@ -516,7 +526,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                             m[c][0] = m[c][1] = m[c][2] = m[c][3] = h * 0x00010001u;
                         }
                     }
-                    if (!mbar_wait(&S.empty[s], ph ^ 1u, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&S.empty_a[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
