@@ -60,20 +60,6 @@ __device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
     return d;
 }
 
-constexpr uint32_t kRing = 6;  // steps of weight bytes in flight per warp (cp.async ring in shared memory)
-
-__device__ __forceinline__ uint32_t smem_u32_fp4(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ uint4 lds16(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-
 constexpr int kMxBias = 2;  // f16 exponent field of the weight multiplier is e - emin + kMxBias (2..28)
 
 struct Fp4Stream {
@@ -195,7 +181,6 @@ __device__ __forceinline__ float silu_mul_f(float g, float u) {
 // DUAL = false: two adjacent down tiles, writes y fp32 [pairs, H]
 template <int FMT, int NT, bool SPLIT, bool DUAL>
 __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_fp4_kernel(DecodeArgs a) {
-    extern __shared__ uint4 ring[];  // [4 warps][kRing][4 streams][32 lanes]
     const uint32_t lane = threadIdx.x & 31u, gid = lane >> 2, t = lane & 3u;
     const uint32_t K = DUAL ? a.H : a.I;
     const uint32_t R = DUAL ? a.I : a.H;
@@ -254,76 +239,20 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc0[nt][j] = acc1[nt][j] = 0.0f;
 
-            // Weight bytes travel HBM -> shared memory with cp.async into a per-warp ring of kRing
-            // steps (each lane owns its four 16-byte slots, so no cross-lane synchronisation is
-            // needed); that keeps kRing steps of loads in flight without holding them in registers.
-            // Scale bytes come as one 16-byte vector per row per group of G steps (MXFP4: 4 steps,
-            // NVFP4: 2 steps), fetched one group ahead.
-            const uint32_t ring_base = smem_u32_fp4(ring + (size_t)(threadIdx.x >> 5) * kRing * 4u * 32u) + lane * 16u;
-            auto issue = [&](uint32_t kb) {
-                if (kb < steps) {
-                    const uint32_t slot = ring_base + (kb % kRing) * (4u * 32u * 16u);
-                    cp_async16(slot + 0u * 512u, p0.row_lo + (size_t)kb * 64u);
-                    cp_async16(slot + 1u * 512u, p0.row_hi + (size_t)kb * 64u);
-                    cp_async16(slot + 2u * 512u, p1.row_lo + (size_t)kb * 64u);
-                    cp_async16(slot + 3u * 512u, p1.row_hi + (size_t)kb * 64u);
-                }
-                asm volatile("cp.async.commit_group;" ::: "memory");
-            };
-            constexpr uint32_t G = FMT == STRATA_MOE_FMT_MXFP4 ? 4u : 2u;
-            const bool vec_ok = FMT == STRATA_MOE_FMT_MXFP4 ? (K % 512u == 0u) : (K % 256u == 0u);
-            // row base pointers of the scale bytes (without the per-lane offset fp4_init added)
-            const uint32_t tsub = FMT == STRATA_MOE_FMT_MXFP4 ? t : t * 2u;
-            const uint8_t* srow[4] = {p0.sc_lo - tsub, p0.sc_hi - tsub, p1.sc_lo - tsub, p1.sc_hi - tsub};
-            uint4 sv[4], sv_next[4];
-            auto load_group = [&](uint32_t grp, uint4(&dst)[4]) {
-                const uint32_t ngrp = steps / G;
-                grp = grp < ngrp ? grp : ngrp - 1u;
-#pragma unroll
-                for (int r = 0; r < 4; ++r) dst[r] = __ldg(reinterpret_cast<const uint4*>(srow[r] + grp * 16u));
-            };
-#pragma unroll
-            for (uint32_t j = 0; j < kRing; ++j) issue(j);
-            if (vec_ok) load_group(0, sv_next);
-            for (uint32_t kb = 0; kb < steps; ++kb) {
-                if (vec_ok && (kb % G) == 0u) {
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) sv[r] = sv_next[r];
-                    load_group(kb / G + 1u, sv_next);
-                }
-                asm volatile("cp.async.wait_group %0;" ::"n"(kRing - 1) : "memory");
-                Fp4Load L0, L1;
-                const uint32_t slot = ring_base + (kb % kRing) * (4u * 32u * 16u);
-                L0.lo = lds16(slot + 0u * 512u);
-                L0.hi = lds16(slot + 1u * 512u);
-                L1.lo = lds16(slot + 2u * 512u);
-                L1.hi = lds16(slot + 3u * 512u);
-                if (vec_ok) {
-                    const uint32_t j = kb % G;
-                    uint32_t sc[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        if (FMT == STRATA_MOE_FMT_MXFP4) {
-                            sc[r] = (pick4(sv[r], (int)j) >> (8u * t)) & 0xFFu;  // byte 4 j + t
-                        } else {
-                            const uint32_t h = j * 4u + t;                       // 16-bit index
-                            sc[r] = (pick4(sv[r], (int)(h >> 1)) >> (16u * (h & 1u))) & 0xFFFFu;
-                        }
-                    }
-                    L0.s_lo = sc[0]; L0.s_hi = sc[1]; L1.s_lo = sc[2]; L1.s_hi = sc[3];
-                } else if (FMT == STRATA_MOE_FMT_MXFP4) {
-                    L0.s_lo = __ldg(p0.sc_lo + kb * 4u); L0.s_hi = __ldg(p0.sc_hi + kb * 4u);
-                    L1.s_lo = __ldg(p1.sc_lo + kb * 4u); L1.s_hi = __ldg(p1.sc_hi + kb * 4u);
-                } else {
-                    L0.s_lo = __ldg(reinterpret_cast<const unsigned short*>(p0.sc_lo + kb * 8u));
-                    L0.s_hi = __ldg(reinterpret_cast<const unsigned short*>(p0.sc_hi + kb * 8u));
-                    L1.s_lo = __ldg(reinterpret_cast<const unsigned short*>(p1.sc_lo + kb * 8u));
-                    L1.s_hi = __ldg(reinterpret_cast<const unsigned short*>(p1.sc_hi + kb * 8u));
-                }
-                issue(kb + kRing);  // the slot just read is free again
-                fp4_step<FMT, NT, SPLIT>(L0, L1, p0, p1, xh, xl, valid, kb, t, acc0, acc1);
+            Fp4Load A0, A1, B0, B1;  // current and next step of the two streams
+            fp4_load<FMT>(p0, 0, A0);
+            fp4_load<FMT>(p1, 0, A1);
+            for (uint32_t kb = 0; kb < steps; kb += 2u) {
+                const uint32_t k1 = kb + 1u < steps ? kb + 1u : kb;
+                fp4_load<FMT>(p0, k1, B0);
+                fp4_load<FMT>(p1, k1, B1);
+                fp4_step<FMT, NT, SPLIT>(A0, A1, p0, p1, xh, xl, valid, kb, t, acc0, acc1);
+                const uint32_t k2 = kb + 2u < steps ? kb + 2u : kb;
+                fp4_load<FMT>(p0, k2, A0);
+                fp4_load<FMT>(p1, k2, A1);
+                if (kb + 1u < steps)
+                    fp4_step<FMT, NT, SPLIT>(B0, B1, p0, p1, xh, xl, valid, kb + 1u, t, acc0, acc1);
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
 
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
@@ -373,17 +302,9 @@ static void launch_fp4_nt(const DecodeArgs& a, cudaStream_t s) {
     uint32_t grid = (total + 3u) / 4u;
     const uint32_t cap = kNumSMs * fp4_ctas_per_sm(nt);
     if (grid > cap) grid = cap;
-    const size_t smem = (size_t)4 * kRing * 4 * 32 * 16;  // 48 KiB: the per-warp cp.async rings
-    static bool attr = false;
-    if (!attr) {
-        cudaFuncSetAttribute(decode_fp4_kernel<FMT, 1, SPLIT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(decode_fp4_kernel<FMT, 2, SPLIT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(decode_fp4_kernel<FMT, 4, SPLIT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attr = true;
-    }
-    if (nt == 1u) decode_fp4_kernel<FMT, 1, SPLIT, DUAL><<<grid, 128, smem, s>>>(a);
-    else if (nt == 2u) decode_fp4_kernel<FMT, 2, SPLIT, DUAL><<<grid, 128, smem, s>>>(a);
-    else decode_fp4_kernel<FMT, 4, SPLIT, DUAL><<<grid, 128, smem, s>>>(a);
+    if (nt == 1u) decode_fp4_kernel<FMT, 1, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
+    else if (nt == 2u) decode_fp4_kernel<FMT, 2, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
+    else decode_fp4_kernel<FMT, 4, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
     ++g_kernel_launches;
 }
 

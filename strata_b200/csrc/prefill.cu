@@ -38,8 +38,8 @@ constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
 // Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
-constexpr uint32_t kAStages = 3;
-constexpr uint32_t kBStages = 4;
+constexpr uint32_t kAStages = 2;
+constexpr uint32_t kBStages = 5;
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
