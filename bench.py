@@ -88,6 +88,16 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def measured_traffic(workload, tokens, kernel):
+    """DRAM bytes per launch of `kernel` from the committed ncu summary (profiles/traffic.json), or None."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        table = json.load(f)
+    return table.get(f"{workload}/T{tokens}/{kernel}")
+
+
 def expert_weight_bytes(cfg):
     from strata_b200 import synth
     return sum(sum(synth.expert_bytes(cfg, r)) for r in synth.ROLES)
@@ -137,13 +147,20 @@ def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None):
         ptrs[e].gate_global, ptrs[e].up_global, ptrs[e].down_global = g["gate"], g["up"], g["down"]
     xf = np.ascontiguousarray(x.float().numpy())
     y = np.empty((len(perm), cfg.H), np.float32)
+    passes = 1
     if ref is not None:
-        ns = ref.ref_cpu_experts(cfg.fmt, cfg.H, cfg.I, cfg.E, ptrs, xf.ctypes.data_as(O.f32p),
-                                 offsets.ctypes.data_as(O.u32p), pair_token.ctypes.data_as(O.u32p),
-                                 y.ctypes.data_as(O.f32p), threads)
+        def one_pass():
+            ns = ref.ref_cpu_experts(cfg.fmt, cfg.H, cfg.I, cfg.E, ptrs, xf.ctypes.data_as(O.f32p),
+                                     offsets.ctypes.data_as(O.u32p), pair_token.ctypes.data_as(O.u32p),
+                                     y.ctypes.data_as(O.f32p), threads)
+            assert ns > 0
+            return ns * 1e-9
         kind = "reference"
-        assert ns > 0
-        secs = ns * 1e-9
+        secs = one_pass()
+        # a whole workload that takes well under the budget is repeated and the passes averaged
+        if n_tok == T and secs < sample_pairs_budget_s / 8:
+            passes = int(min(50, max(2, sample_pairs_budget_s / 2 / max(secs, 1e-4))))
+            secs = float(np.mean([one_pass() for _ in range(passes)]))
     else:
         # compiled reference missing on this machine: time the plain-C restatement instead
         kind = "port"
@@ -159,7 +176,7 @@ def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None):
         assert rc == 0
     bytes_read = float(len(needed)) * expert_weight_bytes(cfg)
     info = dict(kind=kind, cores=threads, sample=f"{n_tok} of {T} tokens ({len(perm)} token-expert rows over "
-                f"{len(needed)} experts), routed experts only, one pass, {secs:.2f} s",
+                f"{len(needed)} experts), routed experts only, mean of {passes} pass(es), {secs:.3f} s each",
                 eff_gbs=bytes_read / secs / 1e9)
     return n_tok / secs, info
 
@@ -255,9 +272,34 @@ def run_gpu(args, cfg, T, rank, world):
     else:
         roof = dict(bound="tensor", achieved=flops / dur / 1e12, peak=peaks["bf16_tflops"], unit="TFLOP/s")
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update(traffic=None, kernel=dominant, kernel_ms=phase_ms[dominant], peak_source=peaks["source"],
+    roof.update(traffic=measured_traffic(cfg.name, T, dominant), kernel=dominant, kernel_ms=phase_ms[dominant], peak_source=peaks["source"],
                 active_experts=active, algorithmic_bytes=int(alg_bytes))
     layer_bytes = active * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
+
+    # batch sweep of the same layer (config 1 names 1/4/16/64/256 tokens): tokens/s and the
+    # fraction of HBM peak the whole layer reaches on its algorithmic bytes
+    sweep = []
+    if args.sweep:
+        for Ts in [t for t in (1, 4, 16, 64, 256) if t <= T]:
+            xs = layer.x[:Ts].contiguous()
+            outs = torch.empty(Ts, cfg.H, dtype=torch.float32, device=device)
+            for _ in range(3):
+                flush.zero_()
+                ml.forward(xs, outs)
+            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+            for a, b in ev:
+                flush.zero_()
+                a.record()
+                ml.forward(xs, outs)
+                b.record()
+            torch.cuda.synchronize()
+            t_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+            _, ax = ml.forward(xs, want_aux=True)
+            ctx.synchronize()
+            act_s = int((ax["counts"] > 0).sum().item())
+            lb = act_s * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
+            sweep.append({"tokens": Ts, "ms": t_ms, "tokens_per_s": Ts / (t_ms * 1e-3), "active_experts": act_s,
+                          "layer_hbm_frac": lb / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
 
     cpu_v, cpu_info = cpu_reference_run(cfg, T, args.cpu_seconds)
     line = {
@@ -272,6 +314,7 @@ def run_gpu(args, cfg, T, rank, world):
         "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
         "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
         "phase_ms": phase_ms,
+        "sweep": sweep,
         "roofline": roof,
         "cpu_baseline": {"value": cpu_v, "unit": "tokens/s", **cpu_info},
         "e2e": {"value": T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": T * cfg.H * 2,
@@ -291,6 +334,7 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="skip the batch sweep")
     ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
                     help="multi-GPU: weak = --tokens per rank (default), strong = --tokens in total")
     args = ap.parse_args()

@@ -21,6 +21,8 @@ struct strata_moe_ctx {
     strata_moe_stats stats{};
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaStream_t side = nullptr;                  // shared expert runs here, beside the routed experts
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaEvent_t pev[STRATA_MOE_PHASES + 1] = {};  // phase boundaries of the last timed forward
     bool pev_valid = false;
     unsigned long long launches_at_create = 0;
@@ -61,6 +63,7 @@ struct strata_moe_layer {
     __nv_bfloat16* x_stage = nullptr;
     float* out_stage = nullptr;
     void* prefill_scratch = nullptr;
+    uint32_t* shared_tiles = nullptr;  // tile list of the shared expert's grouped GEMM
     float* one_global = nullptr;  // device float 1.0 for the shared expert table
     void* d_wmaps = nullptr;      // [3][n_local] tensor-map descriptors of the packed weights
     bool wmaps_ok = false;
@@ -266,7 +269,13 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     a.offsets = offsets;
     a.active_list = active;
     a.n_active = n_active;
-    a.max_rows_per_group = max_rows;
+    // token tile of the streaming kernels: sized for the typical group (1.5 x the average rows per
+    // expert), not the worst case -- a larger group just takes another pass over its weights
+    {
+        const uint64_t avg15 = ((uint64_t)pairs * 3u) / ((uint64_t)n_groups * 2u);
+        uint32_t hint = (uint32_t)(avg15 < 1u ? 1u : avg15);
+        a.max_rows_per_group = hint < max_rows ? hint : max_rows;
+    }
     a.gate = wt(L->tab[0]);
     a.up = wt(L->tab[1]);
     a.down = wt(L->tab[2]);
@@ -304,8 +313,9 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
 
 // shared expert over T rows in natural order; offsets table = {0, T} in L->offsets scratch tail
 int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16* x_lo, uint32_t T,
-               const uint32_t* offsets2) {
+               const uint32_t* offsets2, cudaStream_t st = nullptr) {
     strata_moe_ctx* ctx = L->ctx;
+    if (!st) st = ctx->stream;
     // enough rows to fill tensor-core tiles (and BF16 inputs): grouped-GEMM path with one group
     const char* thr_env = getenv("STRATA_MOE_PREFILL_MIN_ROWS");
     const uint32_t thr = thr_env ? (uint32_t)atoi(thr_env) : 24u;
@@ -318,10 +328,10 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
         p.pairs = T;
         p.offsets = offsets2;
         p.y = L->sh_y;
-        p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
+        p.tile_table = L->shared_tiles;
         p.status = ctx->d_status;
         if (launch_prefill_bf16(p, x, T, L->shared_w[0], L->shared_w[1], L->shared_w[2], L->sh_act_hi,
-                                L->d.max_tokens, ctx->stream) != 0)
+                                L->d.max_tokens, st) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "shared expert prefill launch failed");
         CK(cudaGetLastError());
         return 0;
@@ -345,8 +355,8 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
     a.act_lo = L->sh_act_lo;
     a.y = L->sh_y;
     a.status = ctx->d_status;
-    launch_decode_gate_up(a, ctx->stream);
-    launch_decode_down(a, ctx->stream);
+    launch_decode_gate_up(a, st);
+    launch_decode_down(a, st);
     CK(cudaGetLastError());
     return 0;
 }
@@ -406,6 +416,12 @@ int strata_moe_create(int device, void* stream, strata_moe_ctx** out) {
             strata_moe_destroy(ctx);
             return STRATA_MOE_E_CUDA;
         }
+    if (cudaStreamCreateWithFlags(&ctx->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ctx->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        strata_moe_destroy(ctx);
+        return STRATA_MOE_E_CUDA;
+    }
     ctx->launches_at_create = g_kernel_launches;
     *out = ctx;
     return 0;
@@ -419,6 +435,9 @@ void strata_moe_destroy(strata_moe_ctx* ctx) {
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+    if (ctx->side) { cudaStreamSynchronize(ctx->side); cudaStreamDestroy(ctx->side); }
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    if (ctx->ev_join) cudaEventDestroy(ctx->ev_join);
     for (int i = 0; i <= STRATA_MOE_PHASES; ++i)
         if (ctx->pev[i]) cudaEventDestroy(ctx->pev[i]);
     if (ctx->own_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -543,6 +562,7 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
     A(dalloc(L, &L->x_rowscale, (size_t)P));
     A(dalloc(L, &L->act_rowscale, (size_t)P));
     if (d.shared_intermediate) {
+        A(dalloc(L, &L->shared_tiles, prefill_scratch_bytes(1, T) / sizeof(uint32_t) + 4));
         A(dalloc(L, &L->sh_act_hi, (size_t)T * d.shared_intermediate));
         A(dalloc(L, &L->sh_act_lo, (size_t)T * d.shared_intermediate));
         A(dalloc(L, &L->sh_y, (size_t)T * H));
@@ -762,6 +782,7 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     const strata_moe_layer_desc& d = L->d;
     if (ctx->timing) CK(cudaEventRecord(ctx->ev0, s));
     mark(ctx, 0);
+    const bool fork_shared = d.shared_intermediate != 0 && !ctx->timing;
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
     float* lg = (aux && aux->logits) ? aux->logits : L->logits;
     uint32_t* ids = (aux && aux->ids) ? aux->ids : L->ids;
@@ -770,6 +791,17 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     uint32_t* offsets = (aux && aux->offsets) ? aux->offsets : L->offsets;
     uint32_t* perm = (aux && aux->perm) ? aux->perm : L->perm;
     const uint32_t P = T * d.top_k;
+    if (fork_shared) {
+        // the shared expert needs only x: it runs on the side stream while the routed path runs here
+        uint32_t* off2 = L->offsets + d.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, T);
+        ++g_kernel_launches;
+        CK(cudaEventRecord(ctx->ev_fork, s));
+        CK(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+        rc = run_shared(L, xb, nullptr, T, off2, ctx->side);
+        if (rc) return rc;
+        CK(cudaEventRecord(ctx->ev_join, ctx->side));
+    }
     launch_router_logits(xb, L->router, T, d.hidden, d.experts, lg, s);
     mark(ctx, 1);
     RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
@@ -781,7 +813,10 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y);
     if (rc) return rc;
     const float* shared = nullptr;
-    if (d.shared_intermediate) {
+    if (fork_shared) {
+        CK(cudaStreamWaitEvent(s, ctx->ev_join, 0));
+        shared = L->sh_y;
+    } else if (d.shared_intermediate) {   // timed run: keep the phases serial so they can be told apart
         uint32_t* off2 = L->offsets + d.experts + 1 + 2;
         set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, T);
         ++g_kernel_launches;
