@@ -62,6 +62,7 @@ struct DecodeArgs {
     const uint32_t* active_list;   // [n_active] groups with rows, or nullptr = all groups
     const uint32_t* n_active;      // device scalar (nullptr when active_list is nullptr)
     uint32_t max_rows_per_group;   // upper bound used to pick the token tile
+    uint32_t ksplit;               // decode.cu: 1 = the four warps of a CTA split K of one tile (few tiles)
     WeightTable gate, up, down;
     const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
     const __nv_bfloat16* x_lo;     // optional low part (fp32 inputs), nullptr otherwise

@@ -254,15 +254,23 @@ __global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(Decode
     const uint32_t n_act = a.active_list ? *a.n_active : a.n_groups;
     const uint32_t total = n_act * tiles_per_group;
     if (total == 0u) return;
-    const uint32_t W = gridDim.x * 4u;
+    // With only a handful of tiles (one always-on expert and a few rows) a warp per tile would
+    // leave most SMs idle: then the four warps of a CTA share one tile, each streaming a quarter
+    // of K, and warp 0 adds the four partial sums in a fixed order.
+    const bool ks = a.ksplit != 0u;
+    const uint32_t kw = threadIdx.x >> 5;
+    const uint32_t W = ks ? gridDim.x : gridDim.x * 4u;
     const uint32_t rounds = (total + W - 1u) / W;
     const uint32_t W_eff = (total + rounds - 1u) / rounds;  // equal tiles per warp, no ragged tail
-    const uint32_t wid = blockIdx.x * 4u + (threadIdx.x >> 5);
+    const uint32_t wid = ks ? blockIdx.x : blockIdx.x * 4u + kw;
     if (wid >= W_eff) return;
     constexpr uint32_t KSTEP = FMT == kFmtBf16 ? 32u : 128u;
     constexpr int U = 2;
     const uint32_t steps = K / KSTEP;
     const uint32_t nsuper = (steps + U - 1u) / U;
+    const uint32_t sb_begin = ks ? kw * nsuper / 4u : 0u;
+    const uint32_t sb_end = ks ? (kw + 1u) * nsuper / 4u : nsuper;
+    __shared__ float red[3][2 * NT * 4][32];
     bool bad = false;
 
     for (uint32_t tile = wid; tile < total; tile += W_eff) {
@@ -311,13 +319,13 @@ __global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(Decode
             StepLoad<FMT> Lg[U], Lu[U], Ng[U], Nu[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const uint32_t kb = min((uint32_t)u, steps - 1u);
+                const uint32_t kb = min(sb_begin * U + (uint32_t)u, steps - 1u);
                 step_load(pg, kb, Lg[u]);
                 step_load(pu, kb, Lu[u]);
             }
-            for (uint32_t sb = 0; sb < nsuper; ++sb) {
+            for (uint32_t sb = sb_begin; sb < sb_end; ++sb) {
                 // next super-step's weights are requested before this one is decoded
-                const uint32_t sn = sb + 1u < nsuper ? sb + 1u : sb;
+                const uint32_t sn = sb + 1u < sb_end ? sb + 1u : sb;
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const uint32_t kb = min(sn * U + u, steps - 1u);
@@ -337,13 +345,37 @@ __global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(Decode
                 }
             }
 
+            if (ks) {  // fold the four K-quarters: warps 1..3 publish, warp 0 adds them in order
+                if (kw > 0u) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            red[kw - 1u][nt * 8 + j][lane] = accg[nt][j];
+                            red[kw - 1u][nt * 8 + 4 + j][lane] = accu[nt][j];
+                        }
+                }
+                __syncthreads();
+                if (kw == 0u) {
+#pragma unroll
+                    for (int w = 0; w < 3; ++w)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                accg[nt][j] += red[w][nt * 8 + j][lane];
+                                accu[nt][j] += red[w][nt * 8 + 4 + j][lane];
+                            }
+                }
+                __syncthreads();
+            }
             // epilogue: c0,c1 = (row gid, tokens 2t, 2t+1); c2,c3 = (row gid + 8, same tokens)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t tok = tb + nt * 8u + t * 2u + (j & 1u);
-                    if (tok >= cnt) continue;
+                    if (tok >= cnt || (ks && kw != 0u)) continue;
                     const uint32_t orow = row + ((j & 2u) ? 8u : 0u);
                     const size_t pos = row0 + tok;
                     if (DUAL) {
@@ -383,13 +415,15 @@ static void launch_nt(const DecodeArgs& a, cudaStream_t s) {
     const uint32_t R = DUAL ? a.I : a.H;
     const uint32_t total = a.n_groups * (DUAL ? R / 16u : R / 32u);
     if (total == 0u) return;
-    uint32_t grid = (total + 3u) / 4u;
     const uint32_t cap = kNumSMs * decode_ctas_per_sm();
+    DecodeArgs b = a;
+    b.ksplit = total <= 2u * kNumSMs ? 1u : 0u;  // too few tiles to fill the GPU one warp each
+    uint32_t grid = b.ksplit ? total : (total + 3u) / 4u;
     if (grid > cap) grid = cap;
     const uint32_t m = a.max_rows_per_group;
-    if (m <= 8u) decode_ffn_kernel<FMT, 1, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
-    else if (m <= 16u) decode_ffn_kernel<FMT, 2, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
-    else decode_ffn_kernel<FMT, 4, SPLIT, DUAL><<<grid, 128, 0, s>>>(a);
+    if (m <= 8u) decode_ffn_kernel<FMT, 1, SPLIT, DUAL><<<grid, 128, 0, s>>>(b);
+    else if (m <= 16u) decode_ffn_kernel<FMT, 2, SPLIT, DUAL><<<grid, 128, 0, s>>>(b);
+    else decode_ffn_kernel<FMT, 4, SPLIT, DUAL><<<grid, 128, 0, s>>>(b);
     ++g_kernel_launches;
 }
 
