@@ -335,6 +335,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="skip the batch sweep")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="multi-GPU row exchange: the library's peer-memory kernels or NCCL all-to-allv")
     ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
                     help="multi-GPU: weak = --tokens per rank (default), strong = --tokens in total")
     args = ap.parse_args()

@@ -224,6 +224,48 @@ int strata_moe_enqueue_dense(strata_moe_layer* layer, const float* hidden_host, 
                              int with_shared);
 int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, float* shared_output);
 
+/* ---- expert parallelism over peer memory (one process per GPU) ---------------------------
+ * ref: the reference shards experts over the GPUs of ONE process and carries activations
+ * through host memory (src/models/glm52/glm_runtime.cpp:650-652 placement, 1561-1576 per-device
+ * enqueue/collect); these calls replace that transport for one rank per GPU.  Rank r holds the
+ * experts [r * E / world, (r + 1) * E / world) (a layer created with that expert_begin /
+ * expert_count) and its own tokens.  Each rank owns a "window" of device memory that all peers
+ * map; the dispatch kernel stores token rows straight into the owners' windows and the combine
+ * kernel loads expert outputs straight from them (NVLink peer loads and stores, flags with
+ * release/acquire at system scope, every wait bounded by wait_ms).
+ *
+ * Set-up: every rank calls ep_window_bytes (same arguments everywhere), ep_window_alloc, sends
+ * the 64-byte handle to its peers by any host channel, opens the peers' handles with
+ * ep_window_open, passes the `world` window pointers (its own at index rank) to ep_create, and
+ * the ranks synchronise on the host once before the first step.  row_capacity bounds the rows a
+ * rank can receive in one step; a step that would exceed it on any rank stores nothing, computes
+ * nothing and reports STRATA_MOE_E_NUMERIC ("inconsistent group table") at the next synchronize
+ * on every rank.  A rank that stops taking part makes its peers' waits run out after wait_ms
+ * (0 = 10 s): "bounded wait timed out" from synchronize, context still usable. */
+typedef struct strata_moe_ep strata_moe_ep;
+size_t strata_moe_ep_window_bytes(const strata_moe_layer_desc* desc, uint32_t world, uint32_t row_capacity);
+int strata_moe_ep_window_alloc(strata_moe_ctx* ctx, size_t bytes, void** window, void* handle64 /* or NULL */);
+int strata_moe_ep_window_open(strata_moe_ctx* ctx, const void* handle64, void** window);
+int strata_moe_ep_window_close(strata_moe_ctx* ctx, void* window);
+int strata_moe_ep_window_free(strata_moe_ctx* ctx, void* window);
+int strata_moe_ep_create(strata_moe_layer* layer, uint32_t rank, uint32_t world, uint32_t row_capacity,
+                         void* const* windows /* [world] */, uint32_t wait_ms, strata_moe_ep** out);
+void strata_moe_ep_destroy(strata_moe_ep* ep);
+/* One step = begin, dispatch, experts, finish, each only enqueueing work on the context's stream.
+ * x_bf16 [tokens, H] are this rank's tokens, out [tokens, H] fp32 its results.  expected_rows is
+ * a hint for the number of rows this rank will receive (0 = as many as it sends); the exact
+ * number never reaches the host.  ep_forward runs the four stages back to back.  The stages are
+ * separate entry points so that a host can interleave other work, and so that several ranks can
+ * be stepped by one process in tests. */
+int strata_moe_ep_begin(strata_moe_ep* ep, const void* x_bf16, uint32_t tokens);
+int strata_moe_ep_dispatch(strata_moe_ep* ep);
+int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows);
+int strata_moe_ep_finish(strata_moe_ep* ep, float* out);
+int strata_moe_ep_forward(strata_moe_ep* ep, const void* x_bf16, uint32_t tokens, float* out,
+                          uint32_t expected_rows);
+/* Drops a step that failed between stages so that the next ep_begin is accepted. */
+int strata_moe_ep_abandon(strata_moe_ep* ep);
+
 #ifdef __cplusplus
 }
 #endif

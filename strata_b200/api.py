@@ -16,6 +16,10 @@ EXPORTS = [
     "strata_moe_set_shared", "strata_moe_forward", "strata_moe_forward_host", "strata_moe_route",
     "strata_moe_group", "strata_moe_gather_rows", "strata_moe_combine", "strata_moe_experts_grouped", "strata_moe_dequant_export",
     "strata_moe_enqueue_dense", "strata_moe_collect_dense", "strata_moe_group_static",
+    "strata_moe_ep_window_bytes", "strata_moe_ep_window_alloc", "strata_moe_ep_window_open",
+    "strata_moe_ep_window_close", "strata_moe_ep_window_free", "strata_moe_ep_create", "strata_moe_ep_destroy",
+    "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
+    "strata_moe_ep_forward", "strata_moe_ep_abandon",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -88,6 +92,21 @@ def load_library():
     lib.strata_moe_enqueue_dense.argtypes = [vp, vp, u32, vp, vp, u32, i32]
     lib.strata_moe_collect_dense.argtypes = [vp, vp, vp]
     lib.strata_moe_group_static.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp, C.c_char_p, C.c_size_t]
+    lib.strata_moe_ep_window_bytes.argtypes = [C.POINTER(LayerDesc), u32, u32]
+    lib.strata_moe_ep_window_bytes.restype = C.c_size_t
+    lib.strata_moe_ep_window_alloc.argtypes = [vp, C.c_size_t, C.POINTER(vp), vp]
+    lib.strata_moe_ep_window_open.argtypes = [vp, vp, C.POINTER(vp)]
+    lib.strata_moe_ep_window_close.argtypes = [vp, vp]
+    lib.strata_moe_ep_window_free.argtypes = [vp, vp]
+    lib.strata_moe_ep_create.argtypes = [vp, u32, u32, u32, C.POINTER(vp), u32, C.POINTER(vp)]
+    lib.strata_moe_ep_destroy.argtypes = [vp]
+    lib.strata_moe_ep_destroy.restype = None
+    lib.strata_moe_ep_begin.argtypes = [vp, vp, u32]
+    lib.strata_moe_ep_dispatch.argtypes = [vp]
+    lib.strata_moe_ep_experts.argtypes = [vp, u32]
+    lib.strata_moe_ep_finish.argtypes = [vp, vp]
+    lib.strata_moe_ep_forward.argtypes = [vp, vp, u32, vp, u32]
+    lib.strata_moe_ep_abandon.argtypes = [vp]
     _LIB = lib
     return lib
 
@@ -340,3 +359,83 @@ class MoeLayer:
             self.close()
         except Exception:
             pass
+
+
+class EpWindow:
+    """A rank's exchange window (device memory that peers map).  `handle` is the 64-byte token a
+    peer process passes to EpWindow.open."""
+
+    def __init__(self, ctx, ptr, handle=None, owned=True):
+        self.ctx, self.ptr, self.handle, self.owned = ctx, ptr, handle, owned
+
+    @staticmethod
+    def bytes_needed(layer, world, row_capacity):
+        n = load_library().strata_moe_ep_window_bytes(C.byref(layer.desc), world, row_capacity)
+        if n == 0:
+            raise StrataMoeError(-1, "bad window geometry")
+        return n
+
+    @classmethod
+    def alloc(cls, ctx, nbytes):
+        p = C.c_void_p()
+        h = C.create_string_buffer(64)
+        ctx.check(ctx.lib.strata_moe_ep_window_alloc(ctx.h, nbytes, C.byref(p), h))
+        return cls(ctx, p.value, h.raw, True)
+
+    @classmethod
+    def open(cls, ctx, handle):
+        p = C.c_void_p()
+        ctx.check(ctx.lib.strata_moe_ep_window_open(ctx.h, C.create_string_buffer(handle, 64), C.byref(p)))
+        return cls(ctx, p.value, handle, False)
+
+    def close(self):
+        if self.ptr and self.ctx.h:
+            fn = self.ctx.lib.strata_moe_ep_window_free if self.owned else self.ctx.lib.strata_moe_ep_window_close
+            self.ctx.check(fn(self.ctx.h, C.c_void_p(self.ptr)))
+        self.ptr = None
+
+
+class EpState:
+    """strata_moe_ep: one rank of an expert-parallel layer over peer-mapped windows."""
+
+    def __init__(self, layer, rank, world, row_capacity, window_ptrs, wait_ms=0):
+        self.layer, self.ctx, self.lib = layer, layer.ctx, layer.lib
+        arr = (C.c_void_p * world)(*[C.c_void_p(p) for p in window_ptrs])
+        h = C.c_void_p()
+        self.ctx.check(self.lib.strata_moe_ep_create(layer.h, rank, world, row_capacity, arr, wait_ms, C.byref(h)))
+        self.h = h
+
+    def begin(self, x):
+        self._x = x
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_ep_begin(self.h, _ptr(x), x.shape[0]))
+
+    def dispatch(self):
+        self.ctx.check(self.lib.strata_moe_ep_dispatch(self.h))
+
+    def experts(self, expected_rows=0):
+        self.ctx.check(self.lib.strata_moe_ep_experts(self.h, expected_rows))
+
+    def finish(self, out=None):
+        x = self._x
+        if out is None:
+            out = torch.empty(x.shape[0], self.layer.cfg.H, dtype=torch.float32, device=x.device)
+        self.ctx.check(self.lib.strata_moe_ep_finish(self.h, _ptr(out)))
+        self.ctx.leave()
+        return out
+
+    def forward(self, x, out=None, expected_rows=0):
+        if out is None:
+            out = torch.empty(x.shape[0], self.layer.cfg.H, dtype=torch.float32, device=x.device)
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_ep_forward(self.h, _ptr(x), x.shape[0], _ptr(out), expected_rows))
+        self.ctx.leave()
+        return out
+
+    def abandon(self):
+        self.ctx.check(self.lib.strata_moe_ep_abandon(self.h))
+
+    def close(self):
+        if self.h:
+            self.lib.strata_moe_ep_destroy(self.h)
+            self.h = None

@@ -230,12 +230,17 @@ bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
 // If x_kperm is non-null it already holds the K-permuted copy.
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
                 uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
-                const uint32_t* n_active, uint32_t max_rows, float* y) {
+                const uint32_t* n_active, uint32_t max_rows, float* y, uint32_t expected_pairs = 0,
+                const uint32_t* pairs_dev = nullptr) {
+    // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
+    // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
     strata_moe_ctx* ctx = L->ctx;
     cudaStream_t s = ctx->stream;
     if (pairs == 0) return 0;
+    const uint32_t bound = pairs;
+    if (pairs_dev && expected_pairs) pairs = expected_pairs < bound ? expected_pairs : bound;
     if (use_prefill(L, pairs, n_groups)) {
-        launch_rows_to_f16_bf16(x_src, perm, k_div, pairs, L->d.hidden, L->xg, L->x_rowscale, s);
+        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         PrefillArgs p{};
         p.fmt = L->d.format;
@@ -290,18 +295,18 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         a.x_rowscale = L->x_rowscale;
         a.act_f32 = L->act_f32;
         a.act_rowscale = L->act_rowscale;
-        launch_rows_to_f16_bf16(x_src, perm, k_div, pairs, L->d.hidden, L->xg, L->x_rowscale, s);
+        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         launch_decode_fp4_gate_up(a, s);
         mark(ctx, 5);
-        launch_rows_to_f16_f32(L->act_f32, 0, pairs, L->d.intermediate, L->act_hi, L->act_lo,
-                               L->act_rowscale, s);
+        launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
+                               L->act_rowscale, s, pairs_dev);
         launch_decode_fp4_down(a, s);
         mark(ctx, 6);
         CK(cudaGetLastError());
         return 0;
     }
-    launch_gather_rows_kperm(x_src, perm, k_div, pairs, L->d.hidden, L->xg, s);
+    launch_gather_rows_kperm(x_src, perm, k_div, bound, L->d.hidden, L->xg, s, pairs_dev);
     mark(ctx, 4);
     launch_decode_gate_up(a, s);
     mark(ctx, 5);
@@ -1013,6 +1018,248 @@ int strata_moe_collect_dense(strata_moe_layer* L, float* routed_output, float* s
     }
     CK(cudaStreamSynchronize(ctx->stream));
     return 0;
+}
+
+// ------------------------------------------------------------------------- expert parallelism
+struct strata_moe_ep {
+    strata_moe_layer* L = nullptr;
+    EpWindows w{};
+    uint32_t* dst_row = nullptr;    // [E]
+    uint32_t* loffsets = nullptr;   // [B + 1]
+    uint32_t* abort_word = nullptr;
+    uint32_t* done = nullptr;
+    const __nv_bfloat16* x = nullptr;   // inputs of the step in progress
+    uint32_t T = 0;
+    int stage = 0;                  // 0 idle, 1 counts published, 2 rows sent, 3 experts done
+    bool forked = false;
+};
+
+size_t strata_moe_ep_window_bytes(const strata_moe_layer_desc* desc, uint32_t world, uint32_t row_capacity) {
+    if (!desc || world == 0 || world > kEpMaxWorld || row_capacity == 0) return 0;
+    return ep_window_bytes(world, desc->experts, desc->hidden, row_capacity);
+}
+
+int strata_moe_ep_window_alloc(strata_moe_ctx* ctx, size_t bytes, void** window, void* handle64) {
+    if (!ctx || !window || bytes == 0) return STRATA_MOE_E_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    CK(cudaSetDevice(ctx->device));
+    void* p = nullptr;
+    CK(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    if (e == cudaSuccess && handle64) {
+        cudaIpcMemHandle_t h;
+        e = cudaIpcGetMemHandle(&h, p);
+        if (e == cudaSuccess) memcpy(handle64, &h, sizeof(h));
+    }
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("window allocation: ") + cudaGetErrorString(e));
+    }
+    *window = p;
+    return 0;
+}
+
+int strata_moe_ep_window_open(strata_moe_ctx* ctx, const void* handle64, void** window) {
+    if (!ctx || !handle64 || !window) return STRATA_MOE_E_INVALID;
+    CK(cudaSetDevice(ctx->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    void* p = nullptr;
+    CK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *window = p;
+    return 0;
+}
+
+int strata_moe_ep_window_close(strata_moe_ctx* ctx, void* window) {
+    if (!ctx || !window) return STRATA_MOE_E_INVALID;
+    CK(cudaSetDevice(ctx->device));
+    CK(cudaIpcCloseMemHandle(window));
+    return 0;
+}
+
+int strata_moe_ep_window_free(strata_moe_ctx* ctx, void* window) {
+    if (!ctx || !window) return STRATA_MOE_E_INVALID;
+    CK(cudaSetDevice(ctx->device));
+    CK(cudaDeviceSynchronize());
+    CK(cudaFree(window));
+    return 0;
+}
+
+int strata_moe_ep_create(strata_moe_layer* L, uint32_t rank, uint32_t world, uint32_t row_capacity,
+                         void* const* windows, uint32_t wait_ms, strata_moe_ep** out) {
+    if (!L || !out) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    *out = nullptr;
+    const strata_moe_layer_desc& d = L->d;
+    if (!windows) return fail(ctx, STRATA_MOE_E_INVALID, "null window table");
+    if (world == 0 || world > kEpMaxWorld || rank >= world)
+        return fail(ctx, STRATA_MOE_E_INVALID, "world must be 1..16 and rank below it");
+    if (d.experts % world) return fail(ctx, STRATA_MOE_E_INVALID, "experts must divide evenly over the ranks");
+    const uint32_t B = d.experts / world;
+    if (d.expert_count != B || d.expert_begin != rank * B)
+        return fail(ctx, STRATA_MOE_E_INVALID, "layer must hold exactly this rank's block of experts");
+    if (row_capacity == 0 || row_capacity > L->max_pairs)
+        return fail(ctx, STRATA_MOE_E_INVALID, "row capacity must be in 1..max_pairs of the layer");
+    if ((uint64_t)d.max_tokens * d.top_k > L->max_pairs)
+        return fail(ctx, STRATA_MOE_E_INVALID, "max_pairs must cover max_tokens * top_k");
+    for (uint32_t r = 0; r < world; ++r)
+        if (!windows[r] || ((uintptr_t)windows[r] & 255u))
+            return fail(ctx, STRATA_MOE_E_INVALID, "windows must be non-null and 256-byte aligned");
+    CK(cudaSetDevice(ctx->device));
+    strata_moe_ep* ep = new (std::nothrow) strata_moe_ep();
+    if (!ep) return fail(ctx, STRATA_MOE_E_INVALID, "out of host memory");
+    ep->L = L;
+    for (uint32_t r = 0; r < world; ++r) ep->w.win[r] = static_cast<uint8_t*>(windows[r]);
+    ep->w.world = world;
+    ep->w.rank = rank;
+    ep->w.E = d.experts;
+    ep->w.H = d.hidden;
+    ep->w.cap = row_capacity;
+    ep->w.step = 0;
+    ep->w.wait_ns = (unsigned long long)(wait_ms ? wait_ms : 10000u) * 1000000ull;
+    cudaError_t e = dalloc(L, &ep->dst_row, (size_t)d.experts);
+    if (e == cudaSuccess) e = dalloc(L, &ep->loffsets, (size_t)B + 1);
+    if (e == cudaSuccess) e = dalloc(L, &ep->abort_word, 1);
+    if (e == cudaSuccess) e = dalloc(L, &ep->done, 1);
+    if (e == cudaSuccess) e = cudaMemset(ep->done, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ep->abort_word, 0, sizeof(uint32_t));
+    if (e != cudaSuccess) {
+        delete ep;
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("ep allocation: ") + cudaGetErrorString(e));
+    }
+    *out = ep;
+    return 0;
+}
+
+void strata_moe_ep_destroy(strata_moe_ep* ep) {
+    if (!ep) return;
+    cudaSetDevice(ep->L->ctx->device);
+    cudaStreamSynchronize(ep->L->ctx->stream);
+    delete ep;   // device scratch belongs to the layer
+}
+
+// Stage 1: route this rank's tokens, group the pairs by global expert, publish the counts.
+int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_layer* L = ep->L;
+    strata_moe_ctx* ctx = L->ctx;
+    const strata_moe_layer_desc& d = L->d;
+    if (ep->stage != 0) return fail(ctx, STRATA_MOE_E_BUSY, "an expert-parallel step is in progress");
+    if (!x && T) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    std::string why;
+    if (!all_registered(L, &why)) return fail(ctx, STRATA_MOE_E_INVALID, why);
+    CK(cudaSetDevice(ctx->device));
+    int rc = sync_tables(L);
+    if (rc) return rc;
+    cudaStream_t s = ctx->stream;
+    ep->w.step += 1;
+    ep->x = static_cast<const __nv_bfloat16*>(x);
+    ep->T = T;
+    ep->forked = false;
+    if (d.shared_intermediate && T) {
+        uint32_t* off2 = L->offsets + d.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, T);
+        ++g_kernel_launches;
+        CK(cudaEventRecord(ctx->ev_fork, s));
+        CK(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+        rc = run_shared(L, ep->x, nullptr, T, off2, ctx->side);
+        if (rc) return rc;
+        CK(cudaEventRecord(ctx->ev_join, ctx->side));
+        ep->forked = true;
+    }
+    if (T) {
+        launch_router_logits(ep->x, L->router, T, d.hidden, d.experts, L->logits, s);
+        RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
+        launch_route(rp, L->logits, L->bias, T, L->ids, L->weights, ctx->d_status, s);
+        launch_group(L->ids, T * d.top_k, 0, d.experts, L->counts, L->offsets, L->perm, L->inv, nullptr, nullptr,
+                     L->group_scratch, s);
+    } else {
+        CK(cudaMemsetAsync(L->counts, 0, (size_t)d.experts * sizeof(uint32_t), s));
+        CK(cudaMemsetAsync(L->offsets, 0, ((size_t)d.experts + 1) * sizeof(uint32_t), s));
+    }
+    launch_ep_publish(ep->w, L->counts, s);
+    CK(cudaGetLastError());
+    ep->stage = 1;
+    return 0;
+}
+
+// Stage 2: wait for every rank's counts, lay out the owners' buffers, store the rows there.
+int strata_moe_ep_dispatch(strata_moe_ep* ep) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_layer* L = ep->L;
+    strata_moe_ctx* ctx = L->ctx;
+    if (ep->stage != 1) return fail(ctx, STRATA_MOE_E_INVALID, "ep_dispatch must follow ep_begin");
+    CK(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    launch_ep_plan(ep->w, ep->dst_row, ep->loffsets, ep->abort_word, ctx->d_status, s);
+    launch_ep_dispatch(ep->w, ep->x, L->ids, L->perm, L->offsets, ep->dst_row, ep->T * L->d.top_k, L->d.top_k,
+                       ep->abort_word, ep->done, s);
+    CK(cudaGetLastError());
+    ep->stage = 2;
+    return 0;
+}
+
+// Stage 3: wait for every rank's rows, run this rank's experts over them, announce the outputs.
+int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_layer* L = ep->L;
+    strata_moe_ctx* ctx = L->ctx;
+    if (ep->stage != 2) return fail(ctx, STRATA_MOE_E_INVALID, "ep_experts must follow ep_dispatch");
+    CK(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    const uint32_t par = ep->w.step & 1u, B = L->d.expert_count;
+    launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
+    if (expected_rows == 0) expected_rows = ep->T * L->d.top_k ? ep->T * L->d.top_k : 1u;
+    int rc = run_experts(L, ep->w.rows(ep->w.rank, par), nullptr, 1, ep->w.cap, B, ep->loffsets, nullptr, nullptr,
+                         ep->w.cap, ep->w.y(ep->w.rank, par), expected_rows, ep->loffsets + B);
+    if (rc) return rc;
+    launch_ep_signal(ep->w, 2, s);
+    CK(cudaGetLastError());
+    ep->stage = 3;
+    return 0;
+}
+
+// Stage 4: wait for every owner's outputs and form this rank's tokens from them.
+int strata_moe_ep_finish(strata_moe_ep* ep, float* out) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_layer* L = ep->L;
+    strata_moe_ctx* ctx = L->ctx;
+    if (ep->stage != 3) return fail(ctx, STRATA_MOE_E_INVALID, "ep_finish must follow ep_experts");
+    if (!out && ep->T) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    CK(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    const float* shared = nullptr;
+    if (ep->forked) {
+        CK(cudaStreamWaitEvent(s, ctx->ev_join, 0));
+        shared = L->sh_y;
+    }
+    launch_ep_combine(ep->w, L->ids, L->inv, L->offsets, ep->dst_row, L->weights, shared, ep->T, L->d.top_k,
+                      L->d.output_scale, out, ep->abort_word, ctx->d_status, s);
+    CK(cudaGetLastError());
+    ep->stage = 0;
+    ctx->stats.forward_calls++;
+    return 0;
+}
+
+int strata_moe_ep_abandon(strata_moe_ep* ep) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = ep->L->ctx;
+    if (ep->forked) {
+        CK(cudaStreamWaitEvent(ctx->stream, ctx->ev_join, 0));
+        ep->forked = false;
+    }
+    ep->stage = 0;
+    return 0;
+}
+
+int strata_moe_ep_forward(strata_moe_ep* ep, const void* x, uint32_t T, float* out, uint32_t expected_rows) {
+    int rc = strata_moe_ep_begin(ep, x, T);
+    if (rc == 0) rc = strata_moe_ep_dispatch(ep);
+    if (rc == 0) rc = strata_moe_ep_experts(ep, expected_rows);
+    if (rc == 0) rc = strata_moe_ep_finish(ep, out);
+    return rc;
 }
 
 }  // extern "C"

@@ -48,7 +48,8 @@ void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, ui
 // K-permuted copy of activation rows (layout the decode kernel's B operand reads).
 // src_row[pos] = perm[pos] / k_div when perm != nullptr, else pos.
 void launch_gather_rows_kperm(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
-                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s);
+                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s,
+                              const uint32_t* pairs_dev = nullptr);
 void launch_gather_rows_kperm_f32(const float* x, uint32_t rows, uint32_t reps, uint32_t H,
                                   __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s);
 void launch_gather_rows_plain(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
@@ -79,9 +80,10 @@ struct DecodeArgs {
 void launch_decode_fp4_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_fp4_down(const DecodeArgs& a, cudaStream_t s);
 void launch_rows_to_f16_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows,
-                             uint32_t C, void* hi, float* rowscale, cudaStream_t s);
+                             uint32_t C, void* hi, float* rowscale, cudaStream_t s,
+                             const uint32_t* rows_dev = nullptr);
 void launch_rows_to_f16_f32(const float* x, uint32_t src_rows, uint32_t rows, uint32_t C, void* hi, void* lo,
-                            float* rowscale, cudaStream_t s);
+                            float* rowscale, cudaStream_t s, const uint32_t* rows_dev = nullptr);
 void launch_mx_scale_range(const uint8_t* const* scales, uint32_t n, size_t bytes, uint32_t* emin,
                            float* post_scale, uint32_t* not_ok, cudaStream_t s);
 void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* scales, uint32_t emin,
@@ -116,6 +118,48 @@ void launch_combine(const float* y, const uint32_t* inv, const float* weights, c
                     uint32_t* status, cudaStream_t s);
 void launch_dequant_export(int fmt, const uint8_t* packed, const uint8_t* scales, float global_scale,
                            uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
+
+// ep.cu : expert-parallel exchange over peer memory
+constexpr uint32_t kEpMaxWorld = 16;
+// The windows of all ranks as mapped into this process, plus the step being executed.  Passed to
+// the kernels by value.  Layout of one window (byte offsets, every region 256-byte aligned):
+// flags | counts [2][world][E] u32 | rows [2][cap][H] bf16 | y [2][cap][H] f32.
+struct EpWindows {
+    uint8_t* win[kEpMaxWorld];
+    uint32_t world, rank, E, H, cap, step;
+    unsigned long long wait_ns;
+    __host__ __device__ static size_t up256(size_t v) { return (v + 255u) / 256u * 256u; }
+    __host__ __device__ size_t flags_bytes() const { return up256((size_t)3 * kEpMaxWorld * 4u); }
+    __host__ __device__ size_t counts_bytes() const { return up256((size_t)2 * world * E * 4u); }
+    __host__ __device__ size_t rows_bytes() const { return up256((size_t)2 * cap * H * 2u); }
+    __host__ __device__ size_t y_bytes() const { return up256((size_t)2 * cap * H * 4u); }
+    __host__ __device__ size_t total_bytes() const { return flags_bytes() + counts_bytes() + rows_bytes() + y_bytes(); }
+    __host__ __device__ uint32_t* flag(uint32_t r, uint32_t kind, uint32_t src) const {
+        return reinterpret_cast<uint32_t*>(win[r]) + kind * kEpMaxWorld + src;
+    }
+    __host__ __device__ uint32_t* counts(uint32_t r, uint32_t parity, uint32_t src) const {
+        return reinterpret_cast<uint32_t*>(win[r] + flags_bytes()) + ((size_t)parity * world + src) * E;
+    }
+    __host__ __device__ __nv_bfloat16* rows(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<__nv_bfloat16*>(win[r] + flags_bytes() + counts_bytes()) + (size_t)parity * cap * H;
+    }
+    __host__ __device__ float* y(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<float*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes()) +
+               (size_t)parity * cap * H;
+    }
+};
+size_t ep_window_bytes(uint32_t world, uint32_t E, uint32_t H, uint32_t cap);
+void launch_ep_publish(const EpWindows& w, const uint32_t* counts, cudaStream_t s);
+void launch_ep_plan(const EpWindows& w, uint32_t* dst_row, uint32_t* loffsets, uint32_t* abort_word,
+                    uint32_t* status, cudaStream_t s);
+void launch_ep_dispatch(const EpWindows& w, const __nv_bfloat16* x, const uint32_t* ids, const uint32_t* perm,
+                        const uint32_t* offsets, const uint32_t* dst_row, uint32_t pairs, uint32_t k,
+                        const uint32_t* abort_word, uint32_t* done, cudaStream_t s);
+void launch_ep_wait(const EpWindows& w, uint32_t kind, uint32_t* abort_word, uint32_t* status, cudaStream_t s);
+void launch_ep_signal(const EpWindows& w, uint32_t kind, cudaStream_t s);
+void launch_ep_combine(const EpWindows& w, const uint32_t* ids, const uint32_t* inv, const uint32_t* offsets,
+                       const uint32_t* dst_row, const float* weights, const float* shared, uint32_t T, uint32_t k,
+                       float output_scale, float* out, uint32_t* abort_word, uint32_t* status, cudaStream_t s);
 
 // Launch counter (every wrapper above bumps it once per kernel launch).
 extern unsigned long long g_kernel_launches;

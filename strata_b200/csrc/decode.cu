@@ -456,8 +456,10 @@ void launch_decode_down(const DecodeArgs& a, cudaStream_t s) { launch_fmt<false>
 // Activation row copies into the layouts the expert kernels read.
 __global__ void gather_rows_kperm_kernel(const __nv_bfloat16* __restrict__ x,
                                          const uint32_t* __restrict__ perm, uint32_t k_div,
-                                         uint32_t pairs, uint32_t H, __nv_bfloat16* __restrict__ dst) {
+                                         uint32_t pairs, uint32_t H, __nv_bfloat16* __restrict__ dst,
+                                         const uint32_t* __restrict__ pairs_dev) {
     const uint32_t per_row = H / 8u;
+    if (pairs_dev) pairs = min(pairs, *pairs_dev);   // `pairs` is only an upper bound in that case
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)pairs * per_row;
          i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t pos = (uint32_t)(i / per_row), c8 = (uint32_t)(i % per_row) * 8u;
@@ -478,11 +480,12 @@ __global__ void gather_rows_kperm_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 void launch_gather_rows_kperm(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
-                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s) {
+                              uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s,
+                              const uint32_t* pairs_dev) {
     if (pairs == 0) return;
     const size_t n = (size_t)pairs * (H / 8u);
     const uint32_t grid = (uint32_t)((n + 255) / 256 < 148u * 8u ? (n + 255) / 256 : 148u * 8u);
-    gather_rows_kperm_kernel<<<grid, 256, 0, s>>>(x, perm, k_div, pairs, H, dst);
+    gather_rows_kperm_kernel<<<grid, 256, 0, s>>>(x, perm, k_div, pairs, H, dst, pairs_dev);
     ++g_kernel_launches;
 }
 

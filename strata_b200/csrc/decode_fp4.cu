@@ -333,10 +333,12 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
                                                           uint32_t k_div, uint32_t src_rows, uint32_t rows,
                                                           uint32_t C, __half* __restrict__ hi,
                                                           __half* __restrict__ lo,
-                                                          float* __restrict__ rowscale) {
+                                                          float* __restrict__ rowscale,
+                                                          const uint32_t* __restrict__ rows_dev) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t pos = blockIdx.x * 8u + (threadIdx.x >> 5);
     if (pos >= rows) return;
+    if (rows_dev && pos >= *rows_dev) return;   // `rows` is only an upper bound; the count lives on the device
     const uint32_t srow = perm ? perm[pos] / k_div : (src_rows ? pos % src_rows : pos);
     float mx = 0.0f;
     if (SRC_F32) {
@@ -402,19 +404,19 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
 }
 
 void launch_rows_to_f16_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows,
-                             uint32_t C, void* hi, float* rowscale, cudaStream_t s) {
+                             uint32_t C, void* hi, float* rowscale, cudaStream_t s, const uint32_t* rows_dev) {
     if (rows == 0) return;
     rows_to_f16_kernel<false><<<(rows + 7) / 8, 256, 0, s>>>(x, perm, k_div, 0, rows, C,
-                                                            static_cast<__half*>(hi), nullptr, rowscale);
+                                                            static_cast<__half*>(hi), nullptr, rowscale, rows_dev);
     ++g_kernel_launches;
 }
 
 void launch_rows_to_f16_f32(const float* x, uint32_t src_rows, uint32_t rows, uint32_t C, void* hi, void* lo,
-                            float* rowscale, cudaStream_t s) {
+                            float* rowscale, cudaStream_t s, const uint32_t* rows_dev) {
     if (rows == 0) return;
     rows_to_f16_kernel<true><<<(rows + 7) / 8, 256, 0, s>>>(x, nullptr, 1, src_rows, rows, C,
                                                            static_cast<__half*>(hi), static_cast<__half*>(lo),
-                                                           rowscale);
+                                                           rowscale, rows_dev);
     ++g_kernel_launches;
 }
 

@@ -95,6 +95,49 @@ class EpMoe:
         return out
 
 
+class EpMoePeer:
+    """The same layer with the exchange done by the library's own kernels over peer memory
+    (strata_moe_ep_*): rows are stored straight into the owners' windows by the dispatch kernel and
+    expert outputs are loaded straight from them by the combine kernel.  Nothing on the data path
+    goes through NCCL or the host; torch.distributed only carries the 64-byte window handles once."""
+
+    def __init__(self, layer, cfg, rank, world, row_capacity, group=None, wait_ms=0):
+        from .api import EpState, EpWindow
+        self.layer, self.cfg, self.rank, self.world = layer, cfg, rank, world
+        ctx = layer.ctx
+        self.own, self.windows, self.state, err = None, [], None, None
+        try:
+            self.own = EpWindow.alloc(ctx, EpWindow.bytes_needed(layer, world, row_capacity))
+        except Exception as e:      # still take part in the handle exchange below
+            err = e
+        handles = [None] * world
+        dist.all_gather_object(handles, self.own.handle if self.own else None, group=group)
+        try:
+            if err is None and any(h is None for h in handles):
+                err = RuntimeError("a peer could not allocate its window")
+            if err is None:
+                self.windows = [self.own if r == rank else EpWindow.open(ctx, handles[r]) for r in range(world)]
+                self.state = EpState(layer, rank, world, row_capacity, [w.ptr for w in self.windows], wait_ms)
+        except Exception as e:
+            err = e
+        # agree on the outcome; this is also the barrier after which every window is zeroed and mapped
+        ok = torch.tensor([0 if err else 1], device=ctx.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            raise RuntimeError(f"peer-memory exchange unavailable: {err or 'a peer failed to map the windows'}")
+
+    def forward(self, x, out=None, expected_rows=0):
+        return self.state.forward(x, out, expected_rows)
+
+    def close(self):
+        self.state.close()
+        for w in self.windows:
+            if not w.owned:
+                w.close()
+        dist.barrier()
+        self.own.close()
+
+
 # ------------------------------------------------------------------------------------------
 def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
     """Multi-GPU leg of bench.py: one layer over `world` ranks, E/world experts per rank.
@@ -121,7 +164,18 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
     x_local = layer.x[rank * Tl:(rank + 1) * Tl].contiguous()
     ml = MoeLayer(ctx, cfg, max_tokens=Tl, expert_begin=rank * B, expert_count=B, max_pairs=max_pairs)
     ml.load_synth(layer)
-    ep = EpMoe(ml, cfg, rank, world)
+    exchange_kind = getattr(args, "exchange", "peer")
+    exchange_text = None
+    if exchange_kind == "peer":
+        try:
+            ep = EpMoePeer(ml, cfg, rank, world, max_pairs)
+            exchange_text = "library kernels over peer memory (NVLink stores / loads, no collective on the data path)"
+        except RuntimeError as e:    # every rank raises together; the NCCL exchange is the other GPU path
+            exchange_text = f"NCCL all-to-allv (counts, rows, outputs); peer windows failed: {e}"
+            ep = EpMoe(ml, cfg, rank, world)
+    else:
+        ep = EpMoe(ml, cfg, rank, world)
+        exchange_text = "NCCL all-to-allv (counts, rows, outputs)"
     flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
 
     warm = max(args.warmup, 3)
@@ -148,9 +202,11 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
     ms = torch.tensor([a.elapsed_time(b) for a, b in evs], device=device, dtype=torch.float64)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)           # per step: the slowest rank
     ms_per_step = float(ms.mean())
-    recv = torch.tensor([float(ep.last["recv_pairs"])], device=device, dtype=torch.float64)
-    recv_max = recv.clone()
-    dist.all_reduce(recv_max, op=dist.ReduceOp.MAX)
+    ctx.synchronize()    # raises if any step tripped the device status word (overflow, timeout, non-finite)
+    ids_loc, _ = ml.route(x_local)
+    per_rank = torch.bincount((ids_loc.reshape(-1) // B).long(), minlength=world).double()
+    dist.all_reduce(per_rank)     # rows every rank receives in one step
+    recv_max = per_rank.max()
 
     # end to end: pinned host activations in, fp32 result out, every step
     x_host = x_local.cpu().pin_memory()
@@ -183,7 +239,7 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
             "config": {"workload": f"{cfg.name}: {cfg.description}", "tokens": T, "tokens_per_rank": Tl,
                        "hidden": cfg.H, "intermediate": cfg.I, "experts": cfg.E, "experts_per_rank": B,
                        "top_k": cfg.k, "format": ["mxfp4", "nvfp4", "int4g128"][cfg.fmt],
-                       "parallelism": f"ep{world}", "exchange": "NCCL all-to-allv (counts, rows, outputs)",
+                       "parallelism": f"ep{world}", "exchange": exchange_text,
                        "l2": "512 MiB buffer rewritten between timed iterations"},
             "roofline": {"bound": "tensor", "achieved": flops / (ms_per_step * 1e-3) / 1e12 / world,
                          "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
