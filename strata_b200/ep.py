@@ -227,6 +227,31 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
     dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
     clocks = sampler.stop() if rank == 0 else None
     ctx.synchronize()
+    # where a step's time goes: the four stages of the peer exchange, timed on this rank's stream
+    # (each stage's time includes waiting for the slowest peer)
+    stage_ms = None
+    if isinstance(ep, EpMoePeer):
+        st = ep.state
+        acc = torch.zeros(4, dtype=torch.float64)
+        reps = 5
+        for _ in range(reps):
+            flush.zero_()
+            dist.barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+            ev[0].record()
+            st.begin(x_local)
+            ev[1].record()
+            st.dispatch()
+            ev[2].record()
+            st.experts()
+            ev[3].record()
+            st.finish(out)
+            ev[4].record()
+            torch.cuda.synchronize()
+            acc += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(4)], dtype=torch.float64)
+        ctx.synchronize()
+        stage_ms = dict(zip(("route_group_publish", "plan_dispatch", "wait_experts_signal", "wait_combine"),
+                            [round(float(v), 4) for v in acc / reps]))
 
     line = None
     if rank == 0:
@@ -250,6 +275,7 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
             "e2e": {"value": T / float(e2e_t.mean()), "unit": "tokens/s",
                     "h2d_bytes_per_step": Tl * cfg.H * 2, "d2h_bytes_per_step": Tl * cfg.H * 4},
             "gpu_launches": int(launches),
+            "stage_ms_rank0": stage_ms,
             "clocks": clocks,
         }
     dist.barrier()
