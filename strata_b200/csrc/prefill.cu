@@ -6,18 +6,25 @@
 // tensor memory: lane = output feature, column = token.
 //
 //   warp 0        TMA producer: activation tiles [N x 64] f16 -> shared memory (128-byte swizzle)
-//   warp 1        MMA issuer: one thread issues tcgen05.mma (kind::f16, M=128, K=16) per k-slice
+//   warps 1, 3    MMA issuers: one thread each issues tcgen05.mma (kind::f16, M=128, K=16) per k-slice,
+//                 warp 1 for the first weight tile of a stage, warp 3 for the second.  An issuing
+//                 thread is serial (barrier polls, descriptor arithmetic, commits) and the tensor
+//                 pipe drains whenever it is not issuing; two issuers cover each other's gaps
 //   warp 2        TMA producer for the packed 4-bit weights: [128 rows x 128 B] blocks (256 columns,
 //                 four pipeline stages) land in a double-buffered, 128-byte-swizzled staging area
-//   warps 3..18   decoders: each lane reads 16 packed bytes (32 columns of one row) per stage from the staging area,
-//                 decode exactly to f16 (hardware E2M1 conversion / INT4 magic-number trick),
-//                 apply the block scale and store the tile K-major with the 128-byte swizzle the
-//                 MMA descriptor expects
-//   warps 19..22  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
+//   warps 4..19   decoders: each lane owns one weight row (= one tensor-memory lane) and reads 16
+//                 packed bytes (32 columns) of it per stage from the staging area, decodes exactly
+//                 to f16 (hardware E2M1 conversion / INT4 magic-number trick), applies the block
+//                 scale and writes the 16 f16x2 words straight into TENSOR MEMORY (tcgen05.st):
+//                 the decoded weights are the A operand of a tensor-memory-sourced MMA and never
+//                 touch shared memory, which halves the shared-memory traffic per MMA
+//   warps 20..23  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
 //                 scale (down), store
-// Accumulators are double-buffered in tensor memory (2 x 256 columns), so the epilogue of one
-// tile overlaps the main loop of the next.  CTAs are persistent (one per SM) and walk a tile
-// list built on the device from the per-expert offsets.
+// Tensor memory (512 columns): accumulators in columns 0..255 (two tiles x up to 128 tokens),
+// a four-stage ring of decoded weight slices in columns 256..511 (2 tiles x 32 columns per
+// stage).  BF16 weights (the shared expert) need no decode and keep the shared-memory A operand.
+// CTAs are persistent (one per SM) and walk a tile list built on the device from the
+// per-expert offsets.
 //
 // Every wait is bounded: on expiry the kernel raises kStatusWaitTimeout, all roles leave their
 // loops, tensor memory is released and the kernel returns normally.
@@ -38,15 +45,19 @@ constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
 // Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
-constexpr uint32_t kAStages = 2;
+constexpr uint32_t kAStages = 4;   // tensor-memory ring of decoded weight slices (shared-memory ring for BF16 weights uses 2)
+constexpr uint32_t kASmemStages = 2;
 constexpr uint32_t kBStages = 5;
+constexpr uint32_t kPkBufs = 4;      // packed-weight staging blocks in flight (they come from HBM: the long latency)
+constexpr uint32_t kAccCols = 256;                      // accumulator columns (2 tiles x kNTile)
+constexpr uint32_t kAStageCols = 64;                    // tensor-memory columns per A stage: 2 tiles x (kBK / 2)
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
-constexpr uint32_t kThreads = (3 + kDecodeWarps + 4) * 32;
+constexpr uint32_t kThreads = (4 + kDecodeWarps + 4) * 32;
 constexpr uint32_t kPkCols = 256;                       // columns per packed staging block (4 stages)
 constexpr uint32_t kPkTile = kMTile * (kPkCols / 2);    // 16 KiB of 4-bit weights: 128 rows x 128 B
-constexpr uint32_t kFirstDecodeWarp = 3, kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps;
+constexpr uint32_t kFirstDecodeWarp = 4, kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps;
 constexpr uint32_t kSpinLimit = 1u << 24;
 constexpr int kFmtBf16W = 3;  // plain BF16 weights (shared expert): tiles arrive by TMA, no decode
 
@@ -119,6 +130,25 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same MMA with the A operand read from tensor memory (lane = row, 32-bit column = two K values).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// This thread's 16 words -> 16 consecutive columns of its tensor-memory lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t v[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
@@ -219,13 +249,13 @@ struct TileInfo {
 };
 
 struct __align__(1024) PrefillSmem {
-    uint8_t a0[kAStages][kATile];  // gate (or down) weight tile
-    uint8_t a1[kAStages][kATile];  // up (or second down) weight tile
+    // 4-bit formats: packed staging [buffer][gate/down, up][kPkTile].
+    // BF16 weights: A tiles [stage][gate/down, up][kATile] (kPkTile == kATile).
+    uint8_t w[kPkBufs][2][kPkTile];
     uint8_t b[kBStages][kBTile];   // activation tile
-    uint8_t pk[2][2][kPkTile];    // packed 4-bit staging: [buffer][gate/down, up]
     uint64_t full_a[kAStages], empty_a[kAStages], full_b[kBStages], empty_b[kBStages];
-    uint64_t pk_full[2], pk_empty[2];
-    uint64_t acc_full[2], acc_empty[2];
+    uint64_t pk_full[kPkBufs], pk_empty[kPkBufs];
+    uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -269,15 +299,15 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
         for (uint32_t s = 0; s < kAStages; ++s) {
             // one arrival per producer warp, or one TMA transaction group for BF16 weights
             mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps : kDecodeWarps / 2u));
-            mbar_init(&S.empty_a[s], 1);
+            mbar_init(&S.empty_a[s], DUAL ? 2u : 1u);   // one commit per MMA issuer
         }
         for (uint32_t s = 0; s < kBStages; ++s) {
             mbar_init(&S.full_b[s], 1);
-            mbar_init(&S.empty_b[s], 1);
+            mbar_init(&S.empty_b[s], DUAL ? 2u : 1u);
         }
-        for (int i = 0; i < 2; ++i) {
-            mbar_init(&S.acc_full[i], 1);
-            mbar_init(&S.acc_empty[i], 4);  // one arrival per epilogue warp
+        mbar_init(&S.acc_full, DUAL ? 2u : 1u);
+        mbar_init(&S.acc_empty, 4);  // one arrival per epilogue warp
+        for (uint32_t i = 0; i < kPkBufs; ++i) {
             mbar_init(&S.pk_full[i], 1);
             mbar_init(&S.pk_empty[i], DUAL ? kDecodeWarps : kDecodeWarps / 2u);
         }
@@ -306,15 +336,16 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
                     if (!mbar_wait(&S.empty_b[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                    const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
+                    uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
+                    if ((a.debug & 8u) && bsel > 2u) bsel = 2u;   // timing experiment: half the activation bytes
                     mbar_arrive_expect_tx(&S.full_b[s], (16u << bsel) * kBK * 2u);
                     tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
-                        const uint32_t sa = it % kAStages, pa = (it / kAStages) & 1u;
+                        const uint32_t sa = it % kASmemStages, pa = (it / kASmemStages) & 1u;
                         if (!mbar_wait(&S.empty_a[sa], pa ^ 1u, abort_flag)) { ok = false; break; }
                         mbar_arrive_expect_tx(&S.full_a[sa], DUAL ? 2u * kATile : kATile);
-                        tma_load_2d(S.a0[sa], &map_a0, ks * kBK, t.m0, &S.full_a[sa]);
-                        if (DUAL) tma_load_2d(S.a1[sa], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[sa]);
+                        tma_load_2d(S.w[sa][0], &map_a0, ks * kBK, t.m0, &S.full_a[sa]);
+                        if (DUAL) tma_load_2d(S.w[sa][1], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[sa]);
                     }
                 }
             }
@@ -339,40 +370,52 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 3) {
+        // ---------------------------------------------------------------- MMA issuers
+        const uint32_t mi = warp == 3 ? 1u : 0u;   // which weight tile of the stage this thread feeds
+        if (lane == 0 && (DUAL || mi == 0u)) {
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
                 TileInfo t;
                 if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
-                const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
-                if (!mbar_wait(&S.acc_empty[buf], aph ^ 1u, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&S.acc_empty, (tcount & 1u) ^ 1u, abort_flag)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t n = (t.n + 15u) & ~15u;
                 const uint32_t idesc = umma_idesc_f16(n, FMT == kFmtBf16W ? 1u : 0u);
-                const uint32_t d0 = tmem_base + buf * 256u, d1 = d0 + kNTile;
+                const uint32_t d = tmem_base + mi * kNTile;
+                constexpr uint32_t kRing = FMT == kFmtBf16W ? kASmemStages : kAStages;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
-                    const uint32_t sa = it % kAStages, pa = (it / kAStages) & 1u;
+                    const uint32_t sa = it % kRing, pa = (it / kRing) & 1u;
                     const uint32_t sb = it % kBStages, pb = (it / kBStages) & 1u;
                     if (!mbar_wait(&S.full_a[sa], pa, abort_flag) || !mbar_wait(&S.full_b[sb], pb, abort_flag)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a0 = smem_u32(S.a0[sa]), a1 = smem_u32(S.a1[sa]), b = smem_u32(S.b[sb]);
+                    const uint32_t b = smem_u32(S.b[sb]);
+                    if (FMT == kFmtBf16W) {
+                        const uint32_t a0 = smem_u32(S.w[sa][mi]);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
-                        if (a.debug & 1u) break;
-                        const uint64_t bd = umma_desc_sw128(b + kk * 32u);
-                        umma_f16(d0, umma_desc_sw128(a0 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
-                        if (DUAL) umma_f16(d1, umma_desc_sw128(a1 + kk * 32u), bd, idesc, (ks | kk) ? 1u : 0u);
+                        for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
+                            if (a.debug & 1u) break;
+                            umma_f16(d, umma_desc_sw128(a0 + kk * 32u), umma_desc_sw128(b + kk * 32u), idesc,
+                                     (ks | kk) ? 1u : 0u);
+                        }
+                    } else {
+                        // decoded weights of this stage: columns [ta, ta + 32) tile 0, [ta + 32, ta + 64) tile 1;
+                        // a K = 16 slice is 8 columns
+                        const uint32_t ta = tmem_base + kAccCols + sa * kAStageCols + mi * (kBK / 2u);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
+                            if (a.debug & 1u) break;
+                            umma_f16_ts(d, ta + kk * 8u, umma_desc_sw128(b + kk * 32u), idesc, (ks | kk) ? 1u : 0u);
+                        }
                     }
-                    umma_commit(&S.empty_a[sa]);  // both tiles are free once these MMAs have read them
+                    umma_commit(&S.empty_a[sa]);  // a stage is free once both issuers' MMAs have read it
                     umma_commit(&S.empty_b[sb]);
                 }
-                if (ok) umma_commit(&S.acc_full[buf]);
+                if (ok) umma_commit(&S.acc_full);
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
         }
@@ -388,25 +431,25 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 const CUtensorMap* m0 = wmaps + (GU ? 0u : 2u) * a.n_groups + t.g;
                 const CUtensorMap* m1 = wmaps + (GU ? 1u : 2u) * a.n_groups + t.g;
                 for (uint32_t q = 0; q < blocks; ++q, ++bi) {
-                    const uint32_t pb = bi & 1u, ph = (bi >> 1) & 1u;
+                    const uint32_t pb = bi % kPkBufs, ph = (bi / kPkBufs) & 1u;
                     if (!mbar_wait(&S.pk_empty[pb], ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&S.pk_full[pb], DUAL ? 2u * kPkTile : kPkTile);
-                    tma_load_2d(S.pk[pb][0], m0, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
-                    if (DUAL) tma_load_2d(S.pk[pb][1], m1, q * (kPkCols / 2u), t.m0 + kSecond, &S.pk_full[pb]);
+                    tma_load_2d(S.w[pb][0], m0, q * (kPkCols / 2u), t.m0, &S.pk_full[pb]);
+                    if (DUAL) tma_load_2d(S.w[pb][1], m1, q * (kPkCols / 2u), t.m0 + kSecond, &S.pk_full[pb]);
                 }
             }
             if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
             if (*abort_flag) {
-                for (uint32_t q = 0; q < (bi < 2u ? bi : 2u); ++q) {
+                for (uint32_t q = 0; q < (bi < kPkBufs ? bi : kPkBufs); ++q) {
                     const uint32_t j = bi - 1u - q;
-                    const uint32_t addr = smem_u32(&S.pk_full[j & 1u]);
+                    const uint32_t addr = smem_u32(&S.pk_full[j % kPkBufs]);
                     for (uint32_t spin = 0; spin < (1u << 16); ++spin) {
                         uint32_t done;
                         asm volatile(
                             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
                             " selp.u32 %0, 1, 0, p;\n}"
                             : "=r"(done)
-                            : "r"(addr), "r"((j >> 1) & 1u)
+                            : "r"(addr), "r"((j / kPkBufs) & 1u)
                             : "memory");
                         if (done) break;
                     }
@@ -417,16 +460,21 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
         // BF16 weights need no decode: the TMA producer loads their tiles
     } else if (warp < kFirstEpilogueWarp) {
         // ---------------------------------------------------------------- weight producers
-        // Decode warp wd owns 16 rows of one weight tile: lanes 0-15 take the first 32 columns of
-        // a stage, lanes 16-31 the second 32 (8 consecutive rows per quarter-warp keeps both the
-        // swizzled reads and the swizzled writes free of bank conflicts).  With one weight tile
-        // per stage (MODE 1) only the first half of the decode warps work.
+        // A warp can only write the tensor-memory lanes 32 * (warp % 4) .. + 31, and a lane holds one
+        // weight row: lane i of a decode warp owns row 32 * (warp % 4) + i of one weight tile and
+        // decodes 32 of its columns per stage.  The four decode warps that share a lane quarter
+        // split into tile 0 / tile 1 and first / second 32 columns of the stage.  (32 consecutive
+        // rows reading the same swizzled 16-byte chunk index are free of bank conflicts.)  With one
+        // weight tile per stage (MODE 1) only the tile-0 warps work.
         const uint32_t wd = warp - kFirstDecodeWarp;
         const uint32_t which = DUAL ? (wd >> 3) : 0u;
-        const uint32_t arow = (wd & 7u) * 16u + (lane & 15u);
-        const uint32_t half = lane >> 4;
+        const uint32_t half = (wd >> 2) & 1u;
+        const uint32_t arow = (warp & 3u) * 32u + lane;
         constexpr uint32_t CH = 1u;  // 16-byte packed chunks per thread per stage
         const bool active = DUAL || wd < kDecodeWarps / 2u;
+        // this thread's first column in an A stage: tile, then 16 columns (32 K values) per half
+        const uint32_t a_col = kAccCols + which * (kBK / 2u) + half * 16u;
+        const uint32_t a_lane_addr = tmem_base + (((warp & 3u) * 32u) << 16) + a_col;
         uint32_t it = 0, bi = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; ok && active; tile += gridDim.x) {
@@ -488,9 +536,9 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
             for (uint32_t q = 0; q < blocks && ok; ++q, ++bi) {
                 const uint4 sc = sc_next;
                 sc_next = load_scales(q + 1u);
-                const uint32_t pb = bi & 1u, pph = (bi >> 1) & 1u;
+                const uint32_t pb = bi % kPkBufs, pph = (bi / kPkBufs) & 1u;
                 if (!mbar_wait(&S.pk_full[pb], pph, abort_flag)) { ok = false; break; }
-                const uint8_t* pk_row = S.pk[pb][which] + arow * 128u;
+                const uint8_t* pk_row = S.w[pb][which] + arow * 128u;
                 const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
 #pragma unroll
                 for (uint32_t j = 0; j < kPkCols / kBK; ++j) {
@@ -527,18 +575,16 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         }
                     }
                     if (!mbar_wait(&S.empty_a[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                    uint8_t* tile_base = (which ? S.a1[s] : S.a0[s]) + arow * 128u;
-#pragma unroll
-                    for (uint32_t c = 0; c < CH; ++c) {
-                        if (a.debug & 2u) break;
+                    tc_fence_after();   // the MMAs that read this stage have completed
+                    if (!(a.debug & 2u)) {
                         uint4 o[4];
-                        decode16<FMT>(pkv[c], m[c], o);
-                        const uint32_t chunk0 = (half + c) * 4u;  // first 16-byte chunk (8 columns each)
-#pragma unroll
-                        for (uint32_t qq = 0; qq < 4; ++qq)
-                            *reinterpret_cast<uint4*>(tile_base + (((chunk0 + qq) ^ (arow & 7u)) << 4)) = o[qq];
+                        decode16<FMT>(pkv[0], m[0], o);
+                        const uint32_t v[16] = {o[0].x, o[0].y, o[0].z, o[0].w, o[1].x, o[1].y, o[1].z, o[1].w,
+                                                o[2].x, o[2].y, o[2].z, o[2].w, o[3].x, o[3].y, o[3].z, o[3].w};
+                        tmem_st16(a_lane_addr + s * kAStageCols, v);
+                        tmem_st_wait();
                     }
-                    fence_async_smem();  // make the generic-proxy stores visible to the tensor core
+                    tc_fence_before();   // order the tensor-memory stores before the MMA issuer's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&S.full_a[s]);
                 }
@@ -557,8 +603,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
         for (uint32_t tile = blockIdx.x; ok; tile += gridDim.x, ++tcount) {
             TileInfo t;
             if (!tile_lookup(a.tile_table, tile, m_tiles, t, kTileFeat)) break;
-            const uint32_t buf = tcount & 1u, aph = (tcount >> 1) & 1u;
-            if (!mbar_wait(&S.acc_full[buf], aph, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&S.acc_full, tcount & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t feat = t.m0 + lane_base + lane;
             float s0, s1 = 1.0f;
@@ -569,7 +614,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
             } else {
                 s0 = s1 = kNoPost ? 1.0f : a.down.post_scale[t.g];
             }
-            const uint32_t taddr = tmem_base + (lane_base << 16) + buf * 256u;
+            const uint32_t taddr = tmem_base + (lane_base << 16);
             for (uint32_t c0 = 0; c0 < t.n; c0 += 16u) {
                 uint32_t g[16], u[16];
                 tmem_ld16(taddr + c0, g);
@@ -604,7 +649,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
+            if (lane == 0) mbar_arrive(&S.acc_empty);
         }
         if (!ok) { *abort_flag = 1; atomicOr(a.status, kStatusWaitTimeout); }
         if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
