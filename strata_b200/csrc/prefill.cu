@@ -18,7 +18,7 @@
 //                 scale and writes the 16 f16x2 words straight into TENSOR MEMORY (tcgen05.st):
 //                 the decoded weights are the A operand of a tensor-memory-sourced MMA and never
 //                 touch shared memory, which halves the shared-memory traffic per MMA
-//   warps 20..23  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
+//   warps 20..27  epilogue: tcgen05.ld the accumulators, fuse SwiGLU (gate/up) or the output
 //                 scale (down), store
 // Tensor memory (512 columns): accumulators in columns 0..255 (two tiles x up to 128 tokens),
 // a four-stage ring of decoded weight slices in columns 256..511 (2 tiles x 32 columns per
@@ -47,14 +47,15 @@ constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 pe
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
 constexpr uint32_t kAStages = 4;   // tensor-memory ring of decoded weight slices (shared-memory ring for BF16 weights uses 2)
 constexpr uint32_t kASmemStages = 2;
-constexpr uint32_t kBStages = 5;
-constexpr uint32_t kPkBufs = 4;      // packed-weight staging blocks in flight (they come from HBM: the long latency)
+constexpr uint32_t kBStages = 8;
+constexpr uint32_t kPkBufs = 2;      // packed-weight staging blocks (256 columns each) in flight
 constexpr uint32_t kAccCols = 256;                      // accumulator columns (2 tiles x kNTile)
 constexpr uint32_t kAStageCols = 64;                    // tensor-memory columns per A stage: 2 tiles x (kBK / 2)
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
-constexpr uint32_t kThreads = (4 + kDecodeWarps + 4) * 32;
+constexpr uint32_t kEpilogueWarps = 8;   // two per tensor-memory lane quarter: even / odd 16-token chunks
+constexpr uint32_t kThreads = (4 + kDecodeWarps + kEpilogueWarps) * 32;
 constexpr uint32_t kPkCols = 256;                       // columns per packed staging block (4 stages)
 constexpr uint32_t kPkTile = kMTile * (kPkCols / 2);    // 16 KiB of 4-bit weights: 128 rows x 128 B
 constexpr uint32_t kFirstDecodeWarp = 4, kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps;
@@ -306,7 +307,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
             mbar_init(&S.empty_b[s], DUAL ? 2u : 1u);
         }
         mbar_init(&S.acc_full, DUAL ? 2u : 1u);
-        mbar_init(&S.acc_empty, 4);  // one arrival per epilogue warp
+        mbar_init(&S.acc_empty, kEpilogueWarps);  // one arrival per epilogue warp
         for (uint32_t i = 0; i < kPkBufs; ++i) {
             mbar_init(&S.pk_full[i], 1);
             mbar_init(&S.pk_empty[i], DUAL ? kDecodeWarps : kDecodeWarps / 2u);
@@ -615,7 +616,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 s0 = s1 = kNoPost ? 1.0f : a.down.post_scale[t.g];
             }
             const uint32_t taddr = tmem_base + (lane_base << 16);
-            for (uint32_t c0 = 0; c0 < t.n; c0 += 16u) {
+            for (uint32_t c0 = (ew >> 2) * 16u; c0 < t.n; c0 += 16u * (kEpilogueWarps / 4u)) {
                 uint32_t g[16], u[16];
                 tmem_ld16(taddr + c0, g);
                 if (DUAL) tmem_ld16(taddr + kNTile + c0, u);
