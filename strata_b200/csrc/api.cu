@@ -226,6 +226,13 @@ bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
+bool use_prefill_down(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
+    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return false;
+    const char* e = getenv("STRATA_MOE_PREFILL_DOWN_MIN_ROWS");
+    const int thr = e ? atoi(e) : 8;
+    return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
+}
+
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
 // If x_kperm is non-null it already holds the K-permuted copy.
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
@@ -301,7 +308,27 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         mark(ctx, 5);
         launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
                                L->act_rowscale, s, pairs_dev);
-        launch_decode_fp4_down(a, s);
+        // Medium batches: the down projection (short K, many output tiles) is faster on the tensor-core
+        // path from about 8 rows per expert, the gate/up projection only from about 24.
+        if (use_prefill_down(L, pairs, n_groups)) {
+            PrefillArgs p{};
+            p.fmt = L->d.format;
+            p.H = L->d.hidden;
+            p.I = L->d.intermediate;
+            p.n_groups = n_groups;
+            p.pairs = pairs;
+            p.offsets = offsets;
+            p.gate = wt(L->tab[0]);
+            p.up = wt(L->tab[1]);
+            p.down = wt(L->tab[2]);
+            p.y = y;
+            p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
+            p.status = ctx->d_status;
+            if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
+                return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
+        } else {
+            launch_decode_fp4_down(a, s);
+        }
         mark(ctx, 6);
         CK(cudaGetLastError());
         return 0;

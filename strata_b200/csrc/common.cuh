@@ -109,6 +109,10 @@ size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
 // prefill_encode_weight_map (gate, up, down of every local expert).
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                    uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid);
+// Down projection alone on the tensor-core path: act16 [pairs_cap, I] f16 rows pre-scaled per row,
+// act_rowscale [pairs_cap] the factors that undo it.
+int launch_prefill_down(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
+                        const void* wmaps, cudaStream_t s);
 int prefill_encode_weight_map(void* out128, const void* packed, uint32_t rows, uint32_t K);
 int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
                         const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s);

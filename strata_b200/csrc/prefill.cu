@@ -637,11 +637,12 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         else
                             static_cast<__half*>(act_out_v)[pos * R + feat] = __float2half_rn(v);
                     } else {
-                        const float v = __uint_as_float(g[j]) * s0;
+                        const float rs = rowscale ? rowscale[pos] : 1.0f;   // pre-scaled activation rows
+                        const float v = __uint_as_float(g[j]) * s0 * rs;
                         if (!(fabsf(v) <= 3.0e38f)) bad = true;
                         a.y[pos * R + feat] = v;
                         if (MODE == 2) {
-                            const float v2 = __uint_as_float(u[j]) * s1;
+                            const float v2 = __uint_as_float(u[j]) * s1 * rs;
                             if (!(fabsf(v2) <= 3.0e38f)) bad = true;
                             a.y[pos * R + feat + kMTile] = v2;
                         }
@@ -789,6 +790,34 @@ static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rows
         prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Down projection only, over f16 activation rows that carry a per-row factor (act_rowscale undoes it).
+template <int FMT>
+static int launch_down_fmt(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
+                           const void* wmaps, cudaStream_t s) {
+    const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
+    BMaps map_act;
+    if (!make_bmaps(&map_act, act16, pairs_cap, a.I)) return -1;
+    const CUtensorMap& dummy = map_act.m[0];
+    const size_t smem = sizeof(PrefillSmem) + 1024;
+    if (set_smem_attr<FMT>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    if (a.H % 256u == 0u)
+        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
+    else
+        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
+    g_kernel_launches += 2;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_prefill_down(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
+                        const void* wmaps, cudaStream_t s) {
+    switch (a.fmt) {
+        case STRATA_MOE_FMT_MXFP4: return launch_down_fmt<STRATA_MOE_FMT_MXFP4>(a, act16, act_rowscale, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_NVFP4: return launch_down_fmt<STRATA_MOE_FMT_NVFP4>(a, act16, act_rowscale, pairs_cap, wmaps, s);
+        default: return -1;
+    }
 }
 
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,

@@ -16,7 +16,15 @@ from tests import helpers as Hh
 pytestmark = pytest.mark.gpu
 
 REL_L2, MAX_ABS = 1e-2, 2.0 ** -6
-TIGHT_REL_L2 = 2e-4
+TIGHT_REL_L2 = 2e-4          # weight-streaming kernels: activations carried as an f16 hi/lo pair
+TENSOR_REL_L2 = 1e-3         # tensor-core kernels: one f16 per activation element
+
+
+def tight_bound(cfg, T):
+    """From 8 rows per expert on, the down projection runs on the tensor-core path (FP4 formats)."""
+    if cfg.fmt != synth.FMT_INT4 and T * cfg.k >= 8 * cfg.E:
+        return TENSOR_REL_L2
+    return TIGHT_REL_L2
 
 
 @pytest.fixture(scope="module")
@@ -65,7 +73,7 @@ def test_small_layer_matches_oracle(ctx, cfg):
     assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
     rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
     assert rel <= REL_L2 and mx <= MAX_ABS
-    assert rel <= TIGHT_REL_L2, rel
+    assert rel <= tight_bound(cfg, layer.x.shape[0]), rel
 
 
 @pytest.mark.parametrize("fmt,wide", [(synth.FMT_MXFP4, True), (synth.FMT_MXFP4, False),
