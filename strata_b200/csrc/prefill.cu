@@ -59,7 +59,7 @@ constexpr uint32_t kThreads = (4 + kDecodeWarps + kEpilogueWarps) * 32;
 constexpr uint32_t kPkCols = 256;                       // columns per packed staging block (4 stages)
 constexpr uint32_t kPkTile = kMTile * (kPkCols / 2);    // 16 KiB of 4-bit weights: 128 rows x 128 B
 constexpr uint32_t kFirstDecodeWarp = 4, kFirstEpilogueWarp = kFirstDecodeWarp + kDecodeWarps;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 19;   // x up to kWaitHintNs each: about two seconds
 constexpr int kFmtBf16W = 3;  // plain BF16 weights (shared expert): tiles arrive by TMA, no decode
 
 // ------------------------------------------------------------------------------ PTX helpers
@@ -76,18 +76,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                  : "memory");
 }
-// Bounded wait: false when the phase did not complete within the spin limit.
+// Bounded wait: false when the phase did not complete within the spin limit.  Each try_wait
+// carries a suspend-time hint: the hardware parks the thread until the phase completes or the
+// hint expires, so waiting warps (the epilogue during a main loop, producers on a full ring) do
+// not burn issue slots that the decode warps need.
+constexpr uint32_t kWaitHintNs = 4096;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
         uint32_t done;
         asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"(kWaitHintNs)
             : "memory");
         if (done) return true;
-        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+        if ((spin & 63u) == 63u && *abort_flag) return false;
     }
     return false;
 }
