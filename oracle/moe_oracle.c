@@ -593,3 +593,130 @@ ORC_API int orc_experts_all(const orc_layer_desc* d, const uint16_t* x_bf16, con
     (void)ids;
     return fail ? -3 : 0;
 }
+
+/* ======================================================================================
+ * DSV4-exact expert (bit-exact numerical mode of the DeepSeek-V4 routed expert).
+ * Follows kernels/cpu/dsv4_fp4_expert.cpp, which itself replays the device kernels
+ * deepseek_fp4_gate_up_kernel / deepseek_fp4_down_kernel / quantize_activation_e4m3_kernel
+ * (kernels/cuda/backend.cu:247-272, 2308-2413).
+ * ====================================================================================== */
+
+/* bf16_round, kernels/cpu/dsv4_fp4_expert.cpp:94-104 (__float2bfloat16_rn widened back). */
+ORC_API float orc_bf16_round(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    if ((bits & 0x7FFFFFFFu) > 0x7F800000u) bits = (bits | 0x00400000u) & 0xFFFF0000u;
+    else bits = (bits + 0x7FFFu + ((bits >> 16) & 1u)) & 0xFFFF0000u;
+    memcpy(&value, &bits, 4);
+    return value;
+}
+
+/* quantize_e4m3_value, kernels/cpu/dsv4_fp4_expert.cpp:58-72 (backend.cu:212-225). */
+ORC_API float orc_quantize_e4m3_value(float value) {
+    const float magnitude = fminf(fabsf(value), 448.0f);
+    float quantized;
+    if (magnitude < 0.015625f) {
+        quantized = rintf(ldexpf(magnitude, 9)) * ldexpf(1.0f, -9);
+    } else {
+        int exponent = 0;
+        (void)frexpf(magnitude, &exponent);
+        exponent = exponent - 1;
+        if (exponent > 8) exponent = 8;
+        if (exponent < -6) exponent = -6;
+        const float step = ldexpf(1.0f, exponent - 3);
+        quantized = fminf(rintf(magnitude / step) * step, 448.0f);
+    }
+    return copysignf(quantized, value);
+}
+
+/* quantize_activation_e4m3, kernels/cpu/dsv4_fp4_expert.cpp:78-92: one power-of-two scale
+ * per 128-column block of one row, in place. */
+ORC_API void orc_quantize_activation_e4m3(float* values, uint64_t columns) {
+    for (uint64_t begin = 0; begin < columns; begin += 128u) {
+        const uint64_t end = begin + 128u < columns ? begin + 128u : columns;
+        float maximum = 0.0f;
+        for (uint64_t i = begin; i < end; ++i) maximum = fmaxf(maximum, fabsf(values[i]));
+        float scale = 1.0f;
+        if (maximum > 0.0f) scale = exp2f(ceilf(log2f(maximum / 448.0f)));
+        for (uint64_t i = begin; i < end; ++i) values[i] = orc_quantize_e4m3_value(values[i] / scale) * scale;
+    }
+}
+
+/* e8m0_scale with the DSV4 edge rule, kernels/cpu/dsv4_fp4_expert.cpp:46-52. */
+static float dsv4_e8m0(uint8_t bits) {
+    uint32_t u = bits == 0xFFu ? 0x7FC00000u : (bits == 0u ? 0x00400000u : (uint32_t)bits << 23);
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* One output row: 256 strided partial sums (row_partials_scalar, :146-163) reduced by the
+ * device's block tree (reduce_lane0 / reduce_block, :111-144). */
+static float dsv4_row(const float* input, const uint8_t* packed, const uint8_t* scales, uint64_t columns,
+                      uint64_t packed_base, uint64_t scale_base) {
+    static const float kValue[16] = {0.0f, 0.5f, 1.0f, 1.5f, 2.0f, 3.0f, 4.0f, 6.0f,
+                                     -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+    float partials[256];
+    for (uint32_t thread = 0; thread < 256u; ++thread) {
+        float sum = 0.0f;
+        for (uint64_t c = thread; c < columns; c += 256u) {
+            const uint8_t byte = packed[packed_base + c / 2u];
+            const unsigned enc = (c % 2u == 0u) ? (byte & 0x0Fu) : (byte >> 4);
+            const float scale = dsv4_e8m0(scales[scale_base + c / 32u]);
+            sum = fmaf(input[c] * kValue[enc], scale, sum);
+        }
+        partials[thread] = sum;
+    }
+    float ws[8];
+    for (uint32_t w = 0; w < 8u; ++w) {
+        const float* l = partials + w * 32u;
+        float a[16];
+        for (int i = 0; i < 16; ++i) a[i] = l[i] + l[i + 16];
+        for (int i = 0; i < 8; ++i) a[i] += a[i + 8];
+        for (int i = 0; i < 4; ++i) a[i] += a[i + 4];
+        a[0] += a[2];
+        a[1] += a[3];
+        ws[w] = a[0] + a[1];
+    }
+    for (int i = 0; i < 8; ++i) ws[i] += 0.0f;
+    for (int i = 0; i < 4; ++i) ws[i] += ws[i + 4];
+    ws[0] += ws[2];
+    ws[1] += ws[3];
+    return ws[0] + ws[1];
+}
+
+/* dsv4_host_expert_fp4, kernels/cpu/dsv4_fp4_expert.cpp:864-884 with its phases :774-862.
+ * in [hidden] fp32 (raw hidden state), out [hidden].  scratch [intermediate] receives the
+ * quantised activation.  Returns 1 when gate/up produced a non-finite value. */
+ORC_API int orc_dsv4_expert(float* out, const float* in, const uint8_t* w1, const uint8_t* s1, const uint8_t* w3,
+                            const uint8_t* s3, const uint8_t* w2, const uint8_t* s2, uint32_t hidden,
+                            uint32_t intermediate, float coefficient, float swiglu_limit, float* scratch) {
+    float* q = (float*)malloc((size_t)hidden * sizeof(float));
+    memcpy(q, in, (size_t)hidden * sizeof(float));
+    orc_quantize_activation_e4m3(q, hidden);
+    for (uint64_t row = 0; row < intermediate; ++row) {
+        const float g = orc_bf16_round(dsv4_row(q, w1, s1, hidden, row * (hidden / 2u), row * (hidden / 32u)));
+        const float u = orc_bf16_round(dsv4_row(q, w3, s3, hidden, row * (hidden / 2u), row * (hidden / 32u)));
+        if (!isfinite(g) || !isfinite(u)) {
+            free(q);
+            return 1;
+        }
+        const float lg = fminf(g, swiglu_limit);
+        const float lu = fmaxf(-swiglu_limit, fminf(u, swiglu_limit));
+        uint32_t gb;
+        memcpy(&gb, &lg, 4);
+        gb &= 0xFFFF0000u;                      /* the table is indexed by the top 16 bits */
+        float gt;
+        memcpy(&gt, &gb, 4);
+        const float silu = isfinite(gt) ? orc_silu(gt) : gt;
+        float act = silu * lu;
+        act *= coefficient;
+        scratch[row] = orc_bf16_round(act);
+    }
+    free(q);
+    orc_quantize_activation_e4m3(scratch, intermediate);
+    for (uint64_t row = 0; row < hidden; ++row)
+        out[row] = orc_bf16_round(dsv4_row(scratch, w2, s2, intermediate, row * (intermediate / 2u),
+                                           row * (intermediate / 32u)));
+    return 0;
+}

@@ -90,6 +90,14 @@ def port():
                                       C.POINTER(Expert), u32p, C.c_uint32, f32p, u32p, f32p, u32p,
                                       u32p, u32p, f32p]
         lib.orc_expert_ffn.argtypes = [C.POINTER(Expert), f32p, C.c_float, C.c_int, C.c_int, f32p, f32p, f32p]
+        lib.orc_bf16_round.argtypes = [C.c_float]
+        lib.orc_bf16_round.restype = C.c_float
+        lib.orc_quantize_e4m3_value.argtypes = [C.c_float]
+        lib.orc_quantize_e4m3_value.restype = C.c_float
+        lib.orc_quantize_activation_e4m3.argtypes = [f32p, C.c_uint64]
+        lib.orc_quantize_activation_e4m3.restype = None
+        lib.orc_dsv4_expert.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32, C.c_uint32,
+                                        C.c_float, C.c_float, f32p]
         lib.orc_experts_all.argtypes = [C.POINTER(LayerDesc), u16p, C.POINTER(Expert), u32p, f32p,
                                         u32p, u32p, f32p]
         _port = lib
@@ -126,6 +134,7 @@ def ref():
         lib.ref_dsv4_host_expert.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32,
                                              C.c_uint32, C.c_float, C.c_float, C.c_int]
         lib.ref_cpu_experts.restype = C.c_int64
+        lib.ref_dsv4_quantize.argtypes = [f32p, C.c_uint32]
         lib.ref_cpu_experts.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,
                                         C.POINTER(RefExpertPtrs), f32p, u32p, u32p, f32p, C.c_uint32]
         _ref = lib

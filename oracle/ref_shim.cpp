@@ -209,6 +209,11 @@ REF_API int ref_dsv4_host_expert(float* out, const float* in, const uint8_t* w1,
                : 1;
 }
 
+// dsv4_host_expert_quantize, kernels/cpu/dsv4_fp4_expert.cpp:826-836 (in place, one row).
+REF_API int ref_dsv4_quantize(float* values, uint32_t columns) {
+    return strata::dsv4_host_expert_quantize({values, columns}, columns).ok() ? 0 : 1;
+}
+
 // ---- timed CPU arm ------------------------------------------------------------------
 // One MoE layer's routed experts on the host cores through the reference's own matvec
 // kernels, scheduled the way the reference schedules its host experts: one parallel region
