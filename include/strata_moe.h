@@ -224,6 +224,26 @@ int strata_moe_enqueue_dense(strata_moe_layer* layer, const float* hidden_host, 
                              int with_shared);
 int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, float* shared_output);
 
+/* ---- DSV4-exact numerical mode ---------------------------------------------------------
+ * Bit-exact DeepSeek-V4 routed-expert arithmetic (ref: enqueue_deepseek_moe_rows, the grouped
+ * command, include/strata/cuda_backend.hpp:1139-1146; kernels deepseek_fp4_gate_up_kernel /
+ * deepseek_fp4_down_kernel / quantize_activation_e4m3_kernel, kernels/cuda/backend.cu:2308-2413,
+ * 247-272; CPU replay kernels/cpu/dsv4_fp4_expert.cpp:774-884): the input rows and the SwiGLU
+ * output are quantised to E4M3 with one power-of-two scale per 128 columns, every dot product is
+ * summed in the reference's order (256 strided partial sums, fixed tree), gate and up are rounded
+ * to BF16, clamped (gate from above, up on both sides) to swiglu_limit, SiLU is taken of the
+ * BF16 gate, the coefficient (route weight) multiplies the activation before its BF16 rounding,
+ * and the output rows are BF16-rounded fp32.  Needs MXFP4-format weights (E2M1 + E8M0/32; scale
+ * byte 0 means 2^-127 and 0xFF NaN, as in DSV4).  rows_f32 [pairs, H] fp32 in group order (device),
+ * offsets [expert_count + 1], coefficients [pairs] or NULL (= 1), y [pairs, H] fp32: un-combined
+ * expert outputs, to be summed in selection-rank order (weights already applied). */
+int strata_moe_experts_grouped_dsv4(strata_moe_layer* layer, const float* rows_f32, uint32_t pairs,
+                                    const uint32_t* offsets, const float* coefficients, float swiglu_limit,
+                                    float* y);
+/* The activation quantisation alone, in place on fp32 [rows, cols] (device memory).
+ * ref: quantize_activation_e4m3_kernel, kernels/cuda/backend.cu:247-272. */
+int strata_moe_quantize_e4m3(strata_moe_ctx* ctx, float* values, uint32_t rows, uint32_t cols);
+
 /* ---- expert parallelism over peer memory (one process per GPU) ---------------------------
  * ref: the reference shards experts over the GPUs of ONE process and carries activations
  * through host memory (src/models/glm52/glm_runtime.cpp:650-652 placement, 1561-1576 per-device

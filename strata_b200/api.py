@@ -20,6 +20,7 @@ EXPORTS = [
     "strata_moe_ep_window_close", "strata_moe_ep_window_free", "strata_moe_ep_create", "strata_moe_ep_destroy",
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
+    "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -107,6 +108,8 @@ def load_library():
     lib.strata_moe_ep_finish.argtypes = [vp, vp]
     lib.strata_moe_ep_forward.argtypes = [vp, vp, u32, vp, u32]
     lib.strata_moe_ep_abandon.argtypes = [vp]
+    lib.strata_moe_experts_grouped_dsv4.argtypes = [vp, vp, u32, vp, vp, f32, vp]
+    lib.strata_moe_quantize_e4m3.argtypes = [vp, vp, u32, u32]
     _LIB = lib
     return lib
 
@@ -175,6 +178,13 @@ class MoeContext:
         s = Stats()
         self.check(self.lib.strata_moe_get_stats(self.h, C.byref(s)))
         return s
+
+    def quantize_e4m3(self, values):
+        """In-place E4M3 activation quantisation of fp32 [rows, cols] (one power-of-two scale per 128 columns)."""
+        self.enter()
+        self.check(self.lib.strata_moe_quantize_e4m3(self.h, _ptr(values), values.shape[0], values.shape[1]))
+        self.leave()
+        return values
 
     def set_timing(self, on):
         self.lib.strata_moe_set_timing(self.h, int(on))
@@ -327,6 +337,17 @@ class MoeLayer:
             y = torch.empty(rows.shape[0], self.cfg.H, dtype=torch.float32, device=rows.device)
         self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_experts_grouped(self.h, _ptr(rows), rows.shape[0], _ptr(offsets), _ptr(y)))
+        self.ctx.leave()
+        return y
+
+    def experts_grouped_dsv4(self, rows_f32, offsets, coefficients=None, swiglu_limit=10.0, y=None):
+        """Bit-exact DeepSeek-V4 expert arithmetic on fp32 rows in group order (MXFP4-format weights)."""
+        if y is None:
+            y = torch.empty(rows_f32.shape[0], self.cfg.H, dtype=torch.float32, device=rows_f32.device)
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_experts_grouped_dsv4(self.h, _ptr(rows_f32), rows_f32.shape[0],
+                                                                _ptr(offsets), _ptr(coefficients),
+                                                                float(swiglu_limit), _ptr(y)))
         self.ctx.leave()
         return y
 

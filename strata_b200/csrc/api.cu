@@ -1047,6 +1047,47 @@ int strata_moe_collect_dense(strata_moe_layer* L, float* routed_output, float* s
     return 0;
 }
 
+// ------------------------------------------------------------------------- DSV4-exact mode
+int strata_moe_quantize_e4m3(strata_moe_ctx* ctx, float* values, uint32_t rows, uint32_t cols) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (!values && rows && cols) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    CK(cudaSetDevice(ctx->device));
+    launch_dsv4_quantize(values, nullptr, 1, rows, cols, values, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_experts_grouped_dsv4(strata_moe_layer* L, const float* rows_f32, uint32_t pairs,
+                                    const uint32_t* offsets, const float* coefficients, float swiglu_limit,
+                                    float* y) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!rows_f32 || !offsets || !y) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (L->d.format != STRATA_MOE_FMT_MXFP4)
+        return fail(ctx, STRATA_MOE_E_INVALID, "the DSV4-exact mode needs FP4 E2M1 weights with E8M0 block scales");
+    if (pairs > L->max_pairs) return fail(ctx, STRATA_MOE_E_INVALID, "pairs exceed max_pairs");
+    if (!(swiglu_limit > 0.0f && swiglu_limit < 3.0e38f))
+        return fail(ctx, STRATA_MOE_E_INVALID, "SwiGLU limit must be finite and positive");
+    for (int r = 0; r < 3; ++r)
+        for (uint32_t e = 0; e < L->d.expert_count; ++e)
+            if (!L->tab[r].packed[e] || !L->tab[r].scales[e]) return fail(ctx, STRATA_MOE_E_INVALID, "an expert has no weights");
+    if (pairs == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    int rc = sync_tables(L);
+    if (rc) return rc;
+    cudaStream_t s = ctx->stream;
+    const uint32_t H = L->d.hidden, I = L->d.intermediate, n = L->d.expert_count;
+    float* xq = L->y;            // [pairs, H] scratch: the E4M3-quantised input rows
+    float* act = L->act_f32;     // [pairs, I]
+    launch_dsv4_quantize(rows_f32, nullptr, 1, pairs, H, xq, s);
+    launch_dsv4_gate_up(n, offsets, H, I, wt(L->tab[0]), wt(L->tab[1]), xq, coefficients, swiglu_limit, act,
+                        ctx->d_status, s);
+    launch_dsv4_quantize(act, nullptr, 1, pairs, I, act, s);
+    launch_dsv4_down(n, offsets, H, I, wt(L->tab[2]), act, y, ctx->d_status, s);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 // ------------------------------------------------------------------------- expert parallelism
 struct strata_moe_ep {
     strata_moe_layer* L = nullptr;

@@ -165,6 +165,15 @@ void launch_ep_combine(const EpWindows& w, const uint32_t* ids, const uint32_t* 
                        const uint32_t* dst_row, const float* weights, const float* shared, uint32_t T, uint32_t k,
                        float output_scale, float* out, uint32_t* abort_word, uint32_t* status, cudaStream_t s);
 
+// dsv4_exact.cu : bit-exact DeepSeek-V4 numerical mode (CUDA-core kernels, reference summation order)
+void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t cols,
+                          float* dst, cudaStream_t s);
+void launch_dsv4_gate_up(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& gate,
+                         const WeightTable& up, const float* xq, const float* coef, float limit, float* act,
+                         uint32_t* status, cudaStream_t s);
+void launch_dsv4_down(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& down,
+                      const float* actq, float* y, uint32_t* status, cudaStream_t s);
+
 // Launch counter (every wrapper above bumps it once per kernel launch).
 extern unsigned long long g_kernel_launches;
 
