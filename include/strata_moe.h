@@ -48,8 +48,10 @@ enum {
  *   NVFP4    u8 [rows, cols/2]; E4M3 u8 [rows, cols/16]; fp32 global scale;
  *            w = e2m1 * (e4m3 / global)   (ref: include/strata/cuda_backend.hpp:24-29)
  *   INT4G128 little-endian u32 [rows, cols/8], nibble j = column 8w+j, value raw-8;
- *            BF16 scale [rows, cols/128]  (ref: kernels/cuda/backend.cu:1908-1916) */
-enum { STRATA_MOE_FMT_MXFP4 = 0, STRATA_MOE_FMT_NVFP4 = 1, STRATA_MOE_FMT_INT4G128 = 2 };
+ *            BF16 scale [rows, cols/128]  (ref: kernels/cuda/backend.cu:1908-1916)
+ *   BF16     plain BF16 [rows, cols] row-major, no scales (scales pointer ignored, may be NULL)
+ *            (ref: the plain-BF16 expert layers, kernels/cuda/backend.cu:2075-2152) */
+enum { STRATA_MOE_FMT_MXFP4 = 0, STRATA_MOE_FMT_NVFP4 = 1, STRATA_MOE_FMT_INT4G128 = 2, STRATA_MOE_FMT_BF16 = 3 };
 
 /* Router score functions (ref: include/strata/model.hpp:43-48 RouterScoreKind). */
 enum {

@@ -1,6 +1,7 @@
 """ctypes binding of include/strata_moe.h.  torch is used only for device memory and streams."""
 import ctypes as C
 import os
+import weakref
 
 import torch
 
@@ -154,6 +155,9 @@ class MoeContext:
         if rc != 0:
             raise StrataMoeError(rc, "strata_moe_create failed (needs an sm_100 device)")
         self.h = h
+        # objects that hold pointers into this context; closed before it, whatever order the
+        # garbage collector picks
+        self._children = weakref.WeakSet()
 
     def enter(self):
         """Orders the library's stream after the caller's current stream."""
@@ -198,6 +202,10 @@ class MoeContext:
 
     def close(self):
         if self.h:
+            for order in (2, 1, 0):          # ep states, then windows, then layers
+                for child in list(self._children):
+                    if getattr(child, "_close_order", 0) == order:
+                        child.close()
             self.lib.strata_moe_destroy(self.h)
             self.h = None
 
@@ -227,6 +235,7 @@ class MoeLayer:
         ctx.check(self.lib.strata_moe_layer_create(ctx.h, C.byref(d), C.byref(h)))
         self.h = h
         self._keep = []
+        ctx._children.add(self)
 
     # ---- weights -------------------------------------------------------------------
     def set_router(self, gate_bf16, bias=None):
@@ -372,7 +381,8 @@ class MoeLayer:
 
     def close(self):
         if self.h:
-            self.lib.strata_moe_layer_destroy(self.h)
+            if self.ctx.h:               # a closed context has already closed this layer
+                self.lib.strata_moe_layer_destroy(self.h)
             self.h = None
 
     def __del__(self):
@@ -386,8 +396,11 @@ class EpWindow:
     """A rank's exchange window (device memory that peers map).  `handle` is the 64-byte token a
     peer process passes to EpWindow.open."""
 
+    _close_order = 1
+
     def __init__(self, ctx, ptr, handle=None, owned=True):
         self.ctx, self.ptr, self.handle, self.owned = ctx, ptr, handle, owned
+        ctx._children.add(self)
 
     @staticmethod
     def bytes_needed(layer, world, row_capacity):
@@ -419,8 +432,12 @@ class EpWindow:
 class EpState:
     """strata_moe_ep: one rank of an expert-parallel layer over peer-mapped windows."""
 
+    _close_order = 2
+
     def __init__(self, layer, rank, world, row_capacity, window_ptrs, wait_ms=0):
         self.layer, self.ctx, self.lib = layer, layer.ctx, layer.lib
+        self.h = None
+        self.ctx._children.add(self)
         arr = (C.c_void_p * world)(*[C.c_void_p(p) for p in window_ptrs])
         h = C.c_void_p()
         self.ctx.check(self.lib.strata_moe_ep_create(layer.h, rank, world, row_capacity, arr, wait_ms, C.byref(h)))
@@ -458,5 +475,12 @@ class EpState:
 
     def close(self):
         if self.h:
-            self.lib.strata_moe_ep_destroy(self.h)
+            if self.ctx.h and self.layer.h:
+                self.lib.strata_moe_ep_destroy(self.h)
             self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

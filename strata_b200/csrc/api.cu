@@ -113,8 +113,11 @@ cudaError_t dalloc(strata_moe_layer* L, T** p, size_t n) {
     return e;
 }
 
-size_t packed_bytes(uint32_t rows, uint32_t cols) { return (size_t)rows * cols / 2; }
+size_t packed_bytes(int fmt, uint32_t rows, uint32_t cols) {
+    return fmt == STRATA_MOE_FMT_BF16 ? (size_t)rows * cols * 2 : (size_t)rows * cols / 2;
+}
 size_t scale_bytes(int fmt, uint32_t rows, uint32_t cols) {
+    if (fmt == STRATA_MOE_FMT_BF16) return 0;
     if (fmt == STRATA_MOE_FMT_MXFP4) return (size_t)rows * cols / 32;
     if (fmt == STRATA_MOE_FMT_NVFP4) return (size_t)rows * cols / 16;
     return (size_t)rows * cols / 128 * 2;
@@ -165,7 +168,7 @@ int sync_tables(strata_moe_layer* L) {
     if (getenv("STRATA_MOE_NO_F16_PATH")) L->f16_ok = false;
     // tensor maps of the packed weights for the tensor-core path's TMA producer
     L->wmaps_ok = false;
-    if (prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) {
+    if (L->d.format != STRATA_MOE_FMT_BF16 && prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) {
         struct alignas(64) Blob { unsigned char b[128]; };
         std::vector<Blob> maps((size_t)3 * n);
         bool ok = true;
@@ -333,7 +336,10 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         CK(cudaGetLastError());
         return 0;
     }
-    launch_gather_rows_kperm(x_src, perm, k_div, bound, L->d.hidden, L->xg, s, pairs_dev);
+    if (L->d.format == STRATA_MOE_FMT_BF16)   // BF16 weights read the activations in natural column order
+        launch_gather_rows_plain(x_src, perm, k_div, bound, L->d.hidden, L->xg, s);
+    else
+        launch_gather_rows_kperm(x_src, perm, k_div, bound, L->d.hidden, L->xg, s, pairs_dev);
     mark(ctx, 4);
     launch_decode_gate_up(a, s);
     mark(ctx, 5);
@@ -399,6 +405,10 @@ __global__ void set_pair_kernel(uint32_t* p, uint32_t a, uint32_t b) {
 }
 __global__ void uniform_offsets_kernel(uint32_t* p, uint32_t n, uint32_t rows) {
     for (uint32_t i = threadIdx.x; i <= n; i += blockDim.x) p[i] = i * rows;
+}
+__global__ void widen_bf16_kernel(const __nv_bfloat16* x, size_t n, float* out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = __bfloat162float(x[i]);
 }
 __global__ void split_f32_kernel(const float* x, size_t n, __nv_bfloat16* hi, __nv_bfloat16* lo) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -522,7 +532,7 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         return fail(ctx, STRATA_MOE_E_INVALID, "hidden and intermediate must be positive multiples of 128");
     if (d.experts == 0 || d.experts > 1024 || d.top_k == 0 || d.top_k > 32 || d.top_k > d.experts)
         return fail(ctx, STRATA_MOE_E_INVALID, "experts must be in 1..1024 and top_k in 1..min(32, experts)");
-    if (d.format < 0 || d.format > STRATA_MOE_FMT_INT4G128)
+    if (d.format < 0 || d.format > STRATA_MOE_FMT_BF16)
         return fail(ctx, STRATA_MOE_E_INVALID, "unknown weight format");
     if (d.score_kind < 0 || d.score_kind > STRATA_MOE_SCORE_SQRTSOFTPLUS)
         return fail(ctx, STRATA_MOE_E_INVALID, "unknown router score kind");
@@ -679,10 +689,14 @@ int strata_moe_set_expert(strata_moe_layer* L, uint32_t expert, int role, const 
     const uint32_t rows = role == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
     const uint32_t cols = role == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
     const void *pp = nullptr, *ps = nullptr;
-    int rc = put(L, packed, packed_bytes(rows, cols), source, &pp);
+    int rc = put(L, packed, packed_bytes(L->d.format, rows, cols), source, &pp);
     if (rc) return rc;
-    rc = put(L, scales, scale_bytes(L->d.format, rows, cols), source, &ps);
-    if (rc) return rc;
+    if (L->d.format == STRATA_MOE_FMT_BF16) {
+        ps = pp;   // no scales: the table entry only has to be non-null
+    } else {
+        rc = put(L, scales, scale_bytes(L->d.format, rows, cols), source, &ps);
+        if (rc) return rc;
+    }
     const uint32_t le = expert - L->d.expert_begin;
     L->tab[role].packed[le] = (const uint8_t*)pp;
     L->tab[role].scales[le] = (const uint8_t*)ps;
@@ -902,7 +916,11 @@ int strata_moe_dequant_export(strata_moe_layer* L, uint32_t expert, int role, fl
     if (rc0) return rc0;
     float* tmp = nullptr;
     CK(cudaMalloc(&tmp, (size_t)rows * cols * 4));
-    if (L->f16_ok) {
+    if (L->d.format == STRATA_MOE_FMT_BF16) {
+        widen_bf16_kernel<<<148 * 4, 256, 0, ctx->stream>>>(
+            reinterpret_cast<const __nv_bfloat16*>(L->tab[role].packed[le]), (size_t)rows * cols, tmp);
+        ++g_kernel_launches;
+    } else if (L->f16_ok) {
         // export what the f16 weight-streaming kernels consume
         uint32_t emin = 0;
         float post = 1.0f;
@@ -979,7 +997,7 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
         CK(cudaMemcpyAsync(L->dense_coef, hc, (size_t)n * rows * sizeof(float), cudaMemcpyHostToDevice, s));
         uniform_offsets_kernel<<<1, 256, 0, s>>>(off, n, rows);
         ++g_kernel_launches;
-        launch_gather_rows_kperm_f32(L->dense_hidden, rows, n, H, L->xg, L->xg_lo, s);
+        launch_gather_rows_kperm_f32(L->dense_hidden, rows, n, H, L->xg, L->xg_lo, s, d.format == STRATA_MOE_FMT_BF16);
         DecodeArgs a{};
         a.fmt = d.format;
         a.H = H;

@@ -51,7 +51,7 @@ void launch_gather_rows_kperm(const __nv_bfloat16* x, const uint32_t* perm, uint
                               uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s,
                               const uint32_t* pairs_dev = nullptr);
 void launch_gather_rows_kperm_f32(const float* x, uint32_t rows, uint32_t reps, uint32_t H,
-                                  __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s);
+                                  __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s, bool natural = false);
 void launch_gather_rows_plain(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div,
                               uint32_t pairs, uint32_t H, __nv_bfloat16* dst, cudaStream_t s);
 // decode.cu : small-batch expert FFN (warp-level MMA GEMV path)

@@ -493,7 +493,7 @@ void launch_gather_rows_kperm(const __nv_bfloat16* x, const uint32_t* perm, uint
 // (dense command: every listed expert sees all rows).  dst row = rep * rows + row.
 __global__ void gather_rows_kperm_f32_kernel(const float* __restrict__ x, uint32_t rows, uint32_t reps,
                                              uint32_t H, __nv_bfloat16* __restrict__ hi,
-                                             __nv_bfloat16* __restrict__ lo) {
+                                             __nv_bfloat16* __restrict__ lo, bool natural) {
     const size_t n = (size_t)rows * reps * H;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (size_t)gridDim.x * blockDim.x) {
@@ -502,17 +502,18 @@ __global__ void gather_rows_kperm_f32_kernel(const float* __restrict__ x, uint32
         const uint32_t srow = (uint32_t)(drow % rows);
         const float v = x[(size_t)srow * H + c];
         const __nv_bfloat16 h = __float2bfloat16_rn(v);
-        hi[drow * H + kperm_index(c)] = h;
-        lo[drow * H + kperm_index(c)] = __float2bfloat16_rn(v - __bfloat162float(h));
+        const uint32_t dc = natural ? c : kperm_index(c);   // BF16 weights read natural column order
+        hi[drow * H + dc] = h;
+        lo[drow * H + dc] = __float2bfloat16_rn(v - __bfloat162float(h));
     }
 }
 
 void launch_gather_rows_kperm_f32(const float* x, uint32_t rows, uint32_t reps, uint32_t H,
-                                  __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s) {
+                                  __nv_bfloat16* hi, __nv_bfloat16* lo, cudaStream_t s, bool natural) {
     const size_t n = (size_t)rows * reps * H;
     if (n == 0) return;
     const uint32_t grid = (uint32_t)((n + 255) / 256 < 148u * 8u ? (n + 255) / 256 : 148u * 8u);
-    gather_rows_kperm_f32_kernel<<<grid, 256, 0, s>>>(x, rows, reps, H, hi, lo);
+    gather_rows_kperm_f32_kernel<<<grid, 256, 0, s>>>(x, rows, reps, H, hi, lo, natural);
     ++g_kernel_launches;
 }
 

@@ -146,6 +146,8 @@ def expert_bytes(cfg, role):
         return packed, rows * cols // 16
     if cfg.fmt == FMT_INT4:
         return packed, rows * cols // 128 * 2
+    if cfg.fmt == FMT_BF16:
+        return rows * cols * 2, 0
     raise ValueError(cfg.fmt)
 
 
@@ -154,6 +156,11 @@ def gen_expert_range(cfg, role, e0, e1, device):
     pb, sb = expert_bytes(cfg, role)
     n = e1 - e0
     packed = hash_bytes(e0 * pb, n * pb, _tensor_seed(cfg, role + ".packed"), device).view(n, pb)
+    if cfg.fmt == FMT_BF16:
+        # plain BF16 weights, uniform with std 0.02, built from byte pairs
+        u = packed.view(torch.int16).to(torch.int32) & 0xFFFF
+        val = (u.to(torch.float32) / 65536.0 - 0.5) * (0.02 * 12.0 ** 0.5)
+        return val.to(torch.bfloat16).view(torch.uint8).view(n, pb), torch.zeros(n, 0, dtype=torch.uint8, device=device)
     raw = hash_bytes(e0 * sb, n * sb, _tensor_seed(cfg, role + ".scales"), device)
     if cfg.fmt == FMT_MXFP4:
         # constant 2^-7 with a -1/0/+1 octave jitter: dequantised std ~ 0.02; never 0x00/0xFF

@@ -43,7 +43,7 @@ def oracle_dense(cfg, hidden, experts, coefs):
     return out
 
 
-@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4, synth.FMT_INT4])
+@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4, synth.FMT_INT4, synth.FMT_BF16])
 def test_dense_command_matches_oracle(ctx, fmt):
     cfg, layer, ml = make(ctx, fmt, shared=128 if fmt == synth.FMT_NVFP4 else 0)
     rng = np.random.default_rng(7)

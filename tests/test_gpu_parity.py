@@ -22,7 +22,7 @@ TENSOR_REL_L2 = 1e-3         # tensor-core kernels: one f16 per activation eleme
 
 def tight_bound(cfg, T):
     """From 8 rows per expert on, the down projection runs on the tensor-core path (FP4 formats)."""
-    if cfg.fmt != synth.FMT_INT4 and T * cfg.k >= 8 * cfg.E:
+    if cfg.fmt in (synth.FMT_MXFP4, synth.FMT_NVFP4) and T * cfg.k >= 8 * cfg.E:
         return TENSOR_REL_L2
     return TIGHT_REL_L2
 
@@ -48,6 +48,8 @@ SMALL_CASES = [
     small(synth.FMT_INT4, T=5, score_kind=synth.SCORE_SIGMOID_PLAIN, E=32, k=16, name="kimi_like"),
     small(synth.FMT_NVFP4, T=9, output_scale=2.5, I_shared=256, name="laguna_like"),
     small(synth.FMT_MXFP4, T=8, zipf_s=1.1, E=64, k=8, name="zipf_bias"),
+    small(synth.FMT_BF16, T=6, name="plain_bf16"),
+    small(synth.FMT_BF16, T=40, E=8, k=2, name="plain_bf16_rows"),
 ]
 
 
@@ -77,7 +79,7 @@ def test_small_layer_matches_oracle(ctx, cfg):
 
 
 @pytest.mark.parametrize("fmt,wide", [(synth.FMT_MXFP4, True), (synth.FMT_MXFP4, False),
-                                      (synth.FMT_NVFP4, True), (synth.FMT_INT4, False)])
+                                      (synth.FMT_NVFP4, True), (synth.FMT_INT4, False), (synth.FMT_BF16, False)])
 def test_dequantised_weights_bit_exact(ctx, fmt, wide):
     # wide MXFP4 scales force the general BF16 decoders; narrow ones take the f16 path
     cfg = small(fmt, H=256, I=128, E=4, k=2, name=f"deq{fmt}")
