@@ -224,8 +224,10 @@ bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
     if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) return false;
     if (L->d.format == STRATA_MOE_FMT_MXFP4 && !L->f16_ok) return false;  // needs the f16 weight window
     if (!L->wmaps_ok) return false;
-    const char* e = getenv("STRATA_MOE_PREFILL_MIN_ROWS");  // average rows per expert that switch paths
-    const int thr = e ? atoi(e) : 24;
+    // average rows per expert from which the tensor-core path wins (measured: FP4 formats cross over
+    // at 11-12 rows, INT4, whose streaming kernel is slower, at about 8)
+    const char* e = getenv("STRATA_MOE_PREFILL_MIN_ROWS");
+    const int thr = e ? atoi(e) : (L->d.format == STRATA_MOE_FMT_INT4G128 ? 8 : 12);
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 

@@ -13,7 +13,7 @@
 namespace smoe {
 
 constexpr uint32_t kSegPairs = 128;   // pairs per warp segment
-constexpr uint32_t kSmallPairs = 4096; // single-CTA path up to this many pairs
+constexpr uint32_t kSmallPairs = 2048; // single-CTA path up to this many pairs (above, the segmented path is faster: 35 vs ~22 us at 2560 pairs)
 
 // ---- small path: one CTA does everything ---------------------------------------------------
 __global__ void __launch_bounds__(1024) group_small_kernel(

@@ -21,8 +21,8 @@ TENSOR_REL_L2 = 1e-3         # tensor-core kernels: one f16 per activation eleme
 
 
 def tight_bound(cfg, T):
-    """From 8 rows per expert on, the down projection runs on the tensor-core path (FP4 formats)."""
-    if cfg.fmt in (synth.FMT_MXFP4, synth.FMT_NVFP4) and T * cfg.k >= 8 * cfg.E:
+    """From 8 rows per expert on, the down projection (from 12 on, both GEMMs) runs on the tensor-core path."""
+    if cfg.fmt != synth.FMT_BF16 and T * cfg.k >= 8 * cfg.E:
         return TENSOR_REL_L2
     return TIGHT_REL_L2
 
