@@ -242,6 +242,12 @@ int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, floa
 int strata_moe_experts_grouped_dsv4(strata_moe_layer* layer, const float* rows_f32, uint32_t pairs,
                                     const uint32_t* offsets, const float* coefficients, float swiglu_limit,
                                     float* y);
+/* The DSV4 join: out[t] = bf16(sum over the token's k rows of y, in selection-rank order, + bf16(shared[t])).
+ * y are the rows strata_moe_experts_grouped_dsv4 produced (route weights already applied), inv the
+ * entry -> row map of strata_moe_group, shared_rows [tokens, H] fp32 the shared expert's output (or NULL).
+ * ref: src/models/dsv4/deepseek_runtime.cpp:5897-5914, kernels/cuda/backend.cu:2868-2880. */
+int strata_moe_combine_dsv4(strata_moe_layer* layer, const float* y, const uint32_t* inv,
+                            const float* shared_rows, uint32_t tokens, float* out);
 /* The activation quantisation alone, in place on fp32 [rows, cols] (device memory).
  * ref: quantize_activation_e4m3_kernel, kernels/cuda/backend.cu:247-272. */
 int strata_moe_quantize_e4m3(strata_moe_ctx* ctx, float* values, uint32_t rows, uint32_t cols);

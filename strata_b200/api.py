@@ -21,7 +21,7 @@ EXPORTS = [
     "strata_moe_ep_window_close", "strata_moe_ep_window_free", "strata_moe_ep_create", "strata_moe_ep_destroy",
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
-    "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3",
+    "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -111,6 +111,7 @@ def load_library():
     lib.strata_moe_ep_abandon.argtypes = [vp]
     lib.strata_moe_experts_grouped_dsv4.argtypes = [vp, vp, u32, vp, vp, f32, vp]
     lib.strata_moe_quantize_e4m3.argtypes = [vp, vp, u32, u32]
+    lib.strata_moe_combine_dsv4.argtypes = [vp, vp, vp, vp, u32, vp]
     _LIB = lib
     return lib
 
@@ -359,6 +360,14 @@ class MoeLayer:
                                                                 float(swiglu_limit), _ptr(y)))
         self.ctx.leave()
         return y
+
+    def combine_dsv4(self, y, inv, tokens, shared_rows=None, out=None):
+        if out is None:
+            out = torch.empty(tokens, self.cfg.H, dtype=torch.float32, device=y.device)
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_combine_dsv4(self.h, _ptr(y), _ptr(inv), _ptr(shared_rows), tokens, _ptr(out)))
+        self.ctx.leave()
+        return out
 
     def dequant_export(self, expert, role):
         rows, cols = self.cfg.role_shape(synth.ROLES[role])

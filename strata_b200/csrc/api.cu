@@ -1108,6 +1108,18 @@ int strata_moe_experts_grouped_dsv4(strata_moe_layer* L, const float* rows_f32, 
     return 0;
 }
 
+int strata_moe_combine_dsv4(strata_moe_layer* L, const float* y, const uint32_t* inv, const float* shared_rows,
+                            uint32_t T, float* out) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!y || !inv || !out) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    CK(cudaSetDevice(ctx->device));
+    launch_dsv4_join(y, inv, shared_rows, T, L->d.top_k, L->d.hidden, out, ctx->d_status, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 // ------------------------------------------------------------------------- expert parallelism
 struct strata_moe_ep {
     strata_moe_layer* L = nullptr;

@@ -171,6 +171,8 @@ void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div
 void launch_dsv4_gate_up(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& gate,
                          const WeightTable& up, const float* xq, const float* coef, float limit, float* act,
                          uint32_t* status, cudaStream_t s);
+void launch_dsv4_join(const float* y, const uint32_t* inv, const float* shared, uint32_t T, uint32_t k, uint32_t H,
+                      float* out, uint32_t* status, cudaStream_t s);
 void launch_dsv4_down(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& down,
                       const float* actq, float* y, uint32_t* status, cudaStream_t s);
 

@@ -213,6 +213,41 @@ __global__ void __launch_bounds__(128) dsv4_rows_kernel(Dsv4Args a) {
     if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
 }
 
+// ------------------------------------------------------------------------------ join
+// out[t] = bf16(sum_r y[inv[t * k + r]] + bf16(shared[t])): the routed rows (already BF16-rounded, route
+// weight already applied) are added in selection-rank order starting from +0, the shared row is
+// rounded on its own, then the total is rounded (src/models/dsv4/deepseek_runtime.cpp:5897-5914;
+// device form kernels/cuda/backend.cu:2868-2880).
+__global__ void __launch_bounds__(256) dsv4_join_kernel(const float* __restrict__ y, const uint32_t* __restrict__ inv,
+                                                        const float* __restrict__ shared, uint32_t T, uint32_t k,
+                                                        uint32_t H, float* __restrict__ out, uint32_t* status) {
+    bool bad = false;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)T * H;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t t = (uint32_t)(i / H), c = (uint32_t)(i % H);
+        float o = 0.0f;
+        for (uint32_t r = 0; r < k; ++r) {
+            const uint32_t pos = inv[(size_t)t * k + r];
+            if (pos == 0xFFFFFFFFu) continue;
+            o = __fadd_rn(o, bf16_round_dev(y[(size_t)pos * H + c]));
+        }
+        const float sh = shared ? bf16_round_dev(shared[i]) : 0.0f;
+        o = bf16_round_dev(__fadd_rn(o, sh));
+        bad |= !(fabsf(o) <= 3.0e38f);
+        out[i] = o;
+    }
+    if (bad) atomicOr(status, kStatusNonFiniteOutput);
+}
+
+void launch_dsv4_join(const float* y, const uint32_t* inv, const float* shared, uint32_t T, uint32_t k, uint32_t H,
+                      float* out, uint32_t* status, cudaStream_t s) {
+    if (T == 0) return;
+    const size_t n = (size_t)T * H;
+    const unsigned grid = (unsigned)((n + 255) / 256 < (size_t)kNumSMs * 8u ? (n + 255) / 256 : (size_t)kNumSMs * 8u);
+    dsv4_join_kernel<<<grid, 256, 0, s>>>(y, inv, shared, T, k, H, out, status);
+    ++g_kernel_launches;
+}
+
 // ------------------------------------------------------------------------------ launchers
 void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t cols,
                           float* dst, cudaStream_t s) {

@@ -81,3 +81,51 @@ def test_rejects_other_formats(ctx):
     with pytest.raises(StrataMoeError):
         ml.experts_grouped_dsv4(torch.zeros(2, 256, device="cuda"), torch.tensor([0, 1, 2], dtype=torch.int32,
                                                                                device="cuda"))
+
+
+def _bf16_round(a):
+    b = a.astype(np.float32).view(np.uint32)
+    r = ((b + 0x7FFF + ((b >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+    return r.view(np.float32)
+
+
+def test_page_through_group_experts_join(ctx):
+    """A DSV4 page end to end through the stage calls: route, group, gather the fp32 rows, exact
+    experts with the route weights as coefficients, join.  Checked against the oracle's experts and a
+    numpy restatement of the join (src/models/dsv4/deepseek_runtime.cpp:5897-5914)."""
+    cfg = synth.MoeConfig("dsv4page", H=512, I=256, E=8, k=3, fmt=synth.FMT_MXFP4, T=6, seed=23,
+                          score_kind=synth.SCORE_SIGMOID, normalize=True, weight_scale=1.5)
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg, max_tokens=cfg.T)
+    ml.load_synth(layer)
+    T, k, H, I = cfg.T, cfg.k, cfg.H, cfg.I
+    ids, w = ml.route(layer.x)
+    counts, offsets, perm, inv = ml.group(ids, 0, cfg.E, want_inv=True)
+    xf = layer.x.float()
+    rows = xf[(perm.long() // k)]
+    coef = w.reshape(-1)[perm.long()].contiguous()
+    y = ml.experts_grouped_dsv4(rows.contiguous(), offsets, coef, swiglu_limit=10.0)
+    rng = np.random.default_rng(5)
+    shared = rng.standard_normal((T, H)).astype(np.float32)
+    out = ml.combine_dsv4(y, inv, T, torch.from_numpy(shared).cuda())
+    ctx.synchronize()
+    # oracle
+    port = O.port()
+    ids_h, w_h, perm_h, inv_h = ids.cpu().numpy(), w.cpu().numpy(), perm.cpu().numpy(), inv.cpu().numpy()
+    wt = {r: [layer.packed[r][e].cpu().numpy().reshape(-1) for e in range(cfg.E)] for r in synth.ROLES}
+    sc = {r: [layer.scales[r][e].cpu().numpy().reshape(-1) for e in range(cfg.E)] for r in synth.ROLES}
+    x_h = xf.cpu().numpy()
+    scratch = np.empty(I, np.float32)
+    want = np.zeros((T, H), np.float32)
+    for t in range(T):
+        acc = np.zeros(H, np.float32)
+        for r in range(k):
+            e = int(ids_h[t, r])
+            row = np.empty(H, np.float32)
+            xin = np.ascontiguousarray(x_h[t])
+            assert port.orc_dsv4_expert(_p(row, f32p), _p(xin, f32p), _p(wt["gate"][e], u8p), _p(sc["gate"][e], u8p),
+                                        _p(wt["up"][e], u8p), _p(sc["up"][e], u8p), _p(wt["down"][e], u8p),
+                                        _p(sc["down"][e], u8p), H, I, float(w_h[t, r]), 10.0, _p(scratch, f32p)) == 0
+            acc = acc + _bf16_round(row)
+        want[t] = _bf16_round(acc + _bf16_round(shared[t]))
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
