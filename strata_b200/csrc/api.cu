@@ -238,6 +238,16 @@ bool use_prefill_down(const strata_moe_layer* L, uint32_t pairs, uint32_t n_grou
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
+// Row count from which a single group is handed to the tensor-core path inside an otherwise
+// weight-streaming step; 0 = mixed dispatch off.
+uint32_t mixed_min_rows(const strata_moe_layer* L, uint32_t max_rows_per_group) {
+    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return 0;
+    const char* e = getenv("STRATA_MOE_MIXED_MIN_ROWS");
+    const int thr = e ? atoi(e) : 24;   // above what one or two passes of the streaming kernel cover
+    if (thr <= 0) return 0;
+    return max_rows_per_group >= (uint32_t)thr ? (uint32_t)thr : 0u;
+}
+
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
 // If x_kperm is non-null it already holds the K-permuted copy.
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
@@ -307,32 +317,52 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         a.x_rowscale = L->x_rowscale;
         a.act_f32 = L->act_f32;
         a.act_rowscale = L->act_rowscale;
+        // Mixed dispatch for uneven loads: groups with many rows (a hot expert under a skewed router) go
+        // to the tensor-core path, the rest stay on the weight-streaming kernels.  An expert receives at
+        // most one row per token, so nothing qualifies while max_rows is below the threshold.
+        const uint32_t big = mixed_min_rows(L, max_rows);
+        const bool down_all_tensor = use_prefill_down(L, pairs, n_groups);
+        PrefillArgs p{};
+        p.fmt = L->d.format;
+        p.H = L->d.hidden;
+        p.I = L->d.intermediate;
+        p.n_groups = n_groups;
+        p.pairs = pairs;
+        p.offsets = offsets;
+        p.gate = wt(L->tab[0]);
+        p.up = wt(L->tab[1]);
+        p.down = wt(L->tab[2]);
+        p.y = y;
+        p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
+        p.status = ctx->d_status;
+        a.skip_from = big;
         launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         launch_decode_fp4_gate_up(a, s);
-        mark(ctx, 5);
         launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
                                L->act_rowscale, s, pairs_dev);
+        if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
+            p.min_rows = big;
+            p.act_rowscale_out = L->act_rowscale;
+            if (launch_prefill_gate_up(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s) != 0)
+                return fail(ctx, STRATA_MOE_E_CUDA, "prefill gate/up launch failed");
+        }
+        mark(ctx, 5);
         // Medium batches: the down projection (short K, many output tiles) is faster on the tensor-core
-        // path from about 8 rows per expert, the gate/up projection only from about 24.
-        if (use_prefill_down(L, pairs, n_groups)) {
-            PrefillArgs p{};
-            p.fmt = L->d.format;
-            p.H = L->d.hidden;
-            p.I = L->d.intermediate;
-            p.n_groups = n_groups;
-            p.pairs = pairs;
-            p.offsets = offsets;
-            p.gate = wt(L->tab[0]);
-            p.up = wt(L->tab[1]);
-            p.down = wt(L->tab[2]);
-            p.y = y;
-            p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
-            p.status = ctx->d_status;
+        // path from about 8 rows per expert, the gate/up projection only from about 12.
+        p.act_rowscale_out = nullptr;
+        if (down_all_tensor) {
+            p.min_rows = 0;
             if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
         } else {
             launch_decode_fp4_down(a, s);
+            if (big) {
+                p.min_rows = big;
+                p.reuse_tiles = 1;   // same groups as the gate/up launch above
+                if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
+                    return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
+            }
         }
         mark(ctx, 6);
         CK(cudaGetLastError());
@@ -617,6 +647,8 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         const float one = 1.0f;
         e = cudaMemcpy(L->one_global, &one, sizeof(float), cudaMemcpyHostToDevice);
     }
+    // rows the tensor-core path owns are still swept by the f32 -> f16 conversion pass: keep them finite
+    if (e == cudaSuccess) e = cudaMemset(L->act_f32, 0, (size_t)P * I * sizeof(float));
     if (e != cudaSuccess) {
         strata_moe_layer_destroy(L);
         return fail(ctx, STRATA_MOE_E_CUDA, std::string("layer allocation: ") + cudaGetErrorString(e));

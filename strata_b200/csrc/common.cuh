@@ -64,6 +64,7 @@ struct DecodeArgs {
     const uint32_t* n_active;      // device scalar (nullptr when active_list is nullptr)
     uint32_t max_rows_per_group;   // upper bound used to pick the token tile
     uint32_t ksplit;               // decode.cu: 1 = the four warps of a CTA split K of one tile (few tiles)
+    uint32_t skip_from;            // decode_fp4.cu: groups with at least this many rows are left to the tensor-core path (0 = none)
     WeightTable gate, up, down;
     const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
     const __nv_bfloat16* x_lo;     // optional low part (fp32 inputs), nullptr otherwise
@@ -100,6 +101,9 @@ struct PrefillArgs {
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
     uint32_t debug;                // timing experiments only (wrong results): 1 = no MMA, 2 = no decode, 4 = no stores
+    uint32_t min_rows;             // only groups with at least this many rows get tiles (0 = all)
+    uint32_t reuse_tiles;          // down-only launch: the tile list of the preceding gate/up launch is still valid
+    float* act_rowscale_out;       // gate/up: receives 1.0 for every row written (the activation is not pre-scaled), or nullptr
 };
 bool prefill_supported(int fmt, uint32_t H, uint32_t I);
 size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs);
@@ -111,6 +115,9 @@ int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscal
                    uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid);
 // Down projection alone on the tensor-core path: act16 [pairs_cap, I] f16 rows pre-scaled per row,
 // act_rowscale [pairs_cap] the factors that undo it.
+// Gate/up + SwiGLU alone (tile list + one kernel): act16 rows of the listed groups are written.
+int launch_prefill_gate_up(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                           uint32_t pairs_cap, const void* wmaps, cudaStream_t s);
 int launch_prefill_down(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
                         const void* wmaps, cudaStream_t s);
 int prefill_encode_weight_map(void* out128, const void* packed, uint32_t rows, uint32_t K);

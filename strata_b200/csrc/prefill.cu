@@ -299,6 +299,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     const uint32_t m_tiles = R / kTileFeat;
     const uint32_t k_stages = K / kBK;
     volatile uint32_t* abort_flag = &S.abort_flag;
+    if (a.tile_table[0] == 0u) return;   // nothing listed (mixed dispatch with no large group): leave before any set-up
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kAStages; ++s) {
@@ -630,6 +631,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     if (c0 + j >= t.n || (a.debug & 4u)) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
                     if (GU) {
+                        if (a.act_rowscale_out != nullptr && feat == 0u) a.act_rowscale_out[pos] = 1.0f;
                         const float rs = rowscale ? rowscale[pos] : 1.0f;
                         const float gv = __uint_as_float(g[j]) * s0 * rs, uv = __uint_as_float(u[j]) * s1 * rs;
                         const float e = __expf(-fabsf(gv));
@@ -672,7 +674,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
 // ------------------------------------------------------------------------------ tile list
 // table[0] = number of n-tiles, then (expert, first row, rows) per n-tile, experts ascending.
 __global__ void __launch_bounds__(1024) prefill_tiles_kernel(const uint32_t* __restrict__ offsets, uint32_t n_groups,
-                                                             uint32_t* __restrict__ table) {
+                                                             uint32_t* __restrict__ table, uint32_t min_rows) {
     __shared__ uint32_t scan[1024];
     const uint32_t tid = threadIdx.x;
     uint32_t cnt = 0, r0 = 0;
@@ -680,7 +682,7 @@ __global__ void __launch_bounds__(1024) prefill_tiles_kernel(const uint32_t* __r
         r0 = offsets[tid];
         cnt = offsets[tid + 1] - r0;
     }
-    const uint32_t mine = (cnt + kNTile - 1) / kNTile;
+    const uint32_t mine = cnt >= min_rows ? (cnt + kNTile - 1) / kNTile : 0u;   // small groups: weight-streaming path
     scan[tid] = mine;
     __syncthreads();
     for (uint32_t off = 1; off < 1024u; off <<= 1) {
@@ -785,7 +787,7 @@ static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rows
     const CUtensorMap& dummy = map_x.m[0];
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<FMT>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
     prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
     if (mid) cudaEventRecord(mid, s);
     if (a.H % 256u == 0u)
@@ -794,6 +796,30 @@ static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rows
         prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+template <int FMT>
+static int launch_gate_up_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                              uint32_t pairs_cap, const void* wmaps, cudaStream_t s) {
+    const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
+    BMaps map_x;
+    if (!make_bmaps(&map_x, x16, pairs_cap, a.H)) return -1;
+    const CUtensorMap& dummy = map_x.m[0];
+    const size_t smem = sizeof(PrefillSmem) + 1024;
+    if (set_smem_attr<FMT>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
+    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
+    g_kernel_launches += 2;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_prefill_gate_up(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
+                           uint32_t pairs_cap, const void* wmaps, cudaStream_t s) {
+    switch (a.fmt) {
+        case STRATA_MOE_FMT_MXFP4: return launch_gate_up_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_NVFP4: return launch_gate_up_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
+        default: return -1;
+    }
 }
 
 // Down projection only, over f16 activation rows that carry a per-row factor (act_rowscale undoes it).
@@ -806,12 +832,15 @@ static int launch_down_fmt(const PrefillArgs& a, const void* act16, const float*
     const CUtensorMap& dummy = map_act.m[0];
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<FMT>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    if (!a.reuse_tiles) {
+        prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
+        ++g_kernel_launches;
+    }
     if (a.H % 256u == 0u)
         prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
     else
         prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
-    g_kernel_launches += 2;
+    ++g_kernel_launches;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
@@ -850,7 +879,7 @@ int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, cons
         return -1;
     const size_t smem = sizeof(PrefillSmem) + 1024;
     if (set_smem_attr<kFmtBf16W>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table);
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
     prefill_ffn_kernel<kFmtBf16W, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
     if (a.H % 256u == 0u)
         prefill_ffn_kernel<kFmtBf16W, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,

@@ -258,3 +258,17 @@ def test_prefill_path_odd_hidden_size(ctx):
     ref = Hh.run_oracle(cfg, layer.x.cpu())
     rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
     assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
+
+
+def test_mixed_dispatch_under_a_skewed_router(ctx):
+    """A Zipf-biased router gives a few experts many rows and most experts few: inside one step the
+    hot experts run on the tensor-core path and the rest on the weight-streaming kernels."""
+    cfg = small(synth.FMT_MXFP4, T=64, E=64, k=6, zipf_s=1.3, name="skewed")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    counts = aux["counts"].cpu().numpy()
+    assert counts.max() >= 24 and ((counts > 0) & (counts < 24)).any(), counts
+    assert counts.sum() * 1.0 / cfg.E < 8           # the step as a whole is in the streaming regime
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= TENSOR_REL_L2 and mx <= MAX_ABS, (rel, mx)
