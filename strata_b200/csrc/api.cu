@@ -245,7 +245,11 @@ uint32_t mixed_min_rows(const strata_moe_layer* L, uint32_t max_rows_per_group) 
     const char* e = getenv("STRATA_MOE_MIXED_MIN_ROWS");
     const int thr = e ? atoi(e) : 24;   // above what one or two passes of the streaming kernel cover
     if (thr <= 0) return 0;
-    return max_rows_per_group >= (uint32_t)thr ? (uint32_t)thr : 0u;
+    // The two extra launches cost about 10 us even when no group qualifies: worth it only for steps
+    // long enough that a hot expert's repeated passes would dominate.
+    const char* m = getenv("STRATA_MOE_MIXED_MIN_TOKENS");
+    const uint32_t min_tokens = m ? (uint32_t)atoi(m) : 128u;
+    return max_rows_per_group >= (uint32_t)thr && max_rows_per_group >= min_tokens ? (uint32_t)thr : 0u;
 }
 
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).

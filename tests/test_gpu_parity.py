@@ -260,9 +260,10 @@ def test_prefill_path_odd_hidden_size(ctx):
     assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
 
 
-def test_mixed_dispatch_under_a_skewed_router(ctx):
+def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     """A Zipf-biased router gives a few experts many rows and most experts few: inside one step the
     hot experts run on the tensor-core path and the rest on the weight-streaming kernels."""
+    monkeypatch.setenv("STRATA_MOE_MIXED_MIN_TOKENS", "1")   # the default only switches it on from 128 tokens
     cfg = small(synth.FMT_MXFP4, T=64, E=64, k=6, zipf_s=1.3, name="skewed")
     layer, ml, out, aux = run_layer(ctx, cfg)
     counts = aux["counts"].cpu().numpy()
