@@ -63,6 +63,12 @@ enum {
 
 enum { STRATA_MOE_ROLE_GATE = 0, STRATA_MOE_ROLE_UP = 1, STRATA_MOE_ROLE_DOWN = 2 };
 
+/* Gated activations between the gate/up and the down projection.
+ *   SWIGLU    silu(gate) * up                    (ref: kernels/cuda/backend.cu:2016-2032)
+ *   SITU_GLU  gate_beta * tanh(gate / gate_beta) * sigmoid(gate) * linear_beta * tanh(up / linear_beta)
+ *             (ref: kimi_situ_glu, src/models/kimi_k3/kimi_k3_ops.cpp:39-62) */
+enum { STRATA_MOE_ACT_SWIGLU = 0, STRATA_MOE_ACT_SITU_GLU = 1 };
+
 /* Where a source pointer lives and what registration does with it. */
 enum {
     STRATA_MOE_SRC_HOST = 0,          /* host memory: copied to the device */
@@ -90,6 +96,9 @@ typedef struct strata_moe_layer_desc {
     uint32_t max_tokens;          /* largest T of a forward call (sizes the workspaces) */
     uint32_t max_pairs;           /* largest number of (token, expert) rows the local experts
                                      receive in one call; 0 = max_tokens * top_k */
+    int32_t activation;           /* STRATA_MOE_ACT_*, routed and shared experts alike */
+    float gate_beta;              /* SITU_GLU only, > 0 */
+    float linear_beta;            /* SITU_GLU only, > 0 */
 } strata_moe_layer_desc;
 
 /* Optional device outputs of strata_moe_forward (any may be NULL). */

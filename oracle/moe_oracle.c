@@ -440,7 +440,18 @@ ORC_API void orc_group(const uint32_t* ids, uint32_t T, uint32_t k, uint32_t E, 
 /* --------------------------------------------------------------- experts */
 typedef struct {
     orc_matrix gate, up, down; /* gate/up [I, H], down [H, I] */
+    int32_t activation;        /* 0 = SwiGLU, 1 = SiTU-GLU */
+    float gate_beta, linear_beta;
 } orc_expert;
+
+/* kimi_situ_glu, src/models/kimi_k3/kimi_k3_ops.cpp:39-62: both factors of the first bracket read
+ * the gate projection (tanh bounds it, the plain sigmoid of :12-14 gates it). */
+ORC_API float orc_situ_glu(float g, float u, float gate_beta, float linear_beta) {
+    const float sig = 1.0f / (1.0f + expf(-g));
+    const float bounded = gate_beta * tanhf(g / gate_beta) * sig;
+    const float linear = linear_beta * tanhf(u / linear_beta);
+    return bounded * linear;
+}
 
 /* One expert applied to one row: act = silu(gate.x) * up.x
  * (kernels/cuda/backend.cu:2016-2032; silu as gate * sigmoid(gate) with the
@@ -456,7 +467,8 @@ ORC_API int orc_expert_ffn(const orc_expert* ex, const float* x, float coef, int
     if (rc) return rc;
     for (uint32_t i = 0; i < I; ++i) {
         const float g = act_scratch[i];
-        float a = g * orc_sigmoid(g) * up_scratch[i];
+        float a = ex->activation == 1 ? orc_situ_glu(g, up_scratch[i], ex->gate_beta, ex->linear_beta)
+                                      : g * orc_sigmoid(g) * up_scratch[i];
         if (coef_before_down) a = a * coef;
         act_scratch[i] = a;
     }

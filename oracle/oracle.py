@@ -28,7 +28,8 @@ class Matrix(C.Structure):
 
 
 class Expert(C.Structure):
-    _fields_ = [("gate", Matrix), ("up", Matrix), ("down", Matrix)]
+    _fields_ = [("gate", Matrix), ("up", Matrix), ("down", Matrix), ("activation", C.c_int32),
+                ("gate_beta", C.c_float), ("linear_beta", C.c_float)]
 
 
 class RouterSpec(C.Structure):
@@ -90,6 +91,8 @@ def port():
                                       C.POINTER(Expert), u32p, C.c_uint32, f32p, u32p, f32p, u32p,
                                       u32p, u32p, f32p]
         lib.orc_expert_ffn.argtypes = [C.POINTER(Expert), f32p, C.c_float, C.c_int, C.c_int, f32p, f32p, f32p]
+        lib.orc_situ_glu.argtypes = [C.c_float] * 4
+        lib.orc_situ_glu.restype = C.c_float
         lib.orc_bf16_round.argtypes = [C.c_float]
         lib.orc_bf16_round.restype = C.c_float
         lib.orc_quantize_e4m3_value.argtypes = [C.c_float]
@@ -135,6 +138,7 @@ def ref():
                                              C.c_uint32, C.c_float, C.c_float, C.c_int]
         lib.ref_cpu_experts.restype = C.c_int64
         lib.ref_dsv4_quantize.argtypes = [f32p, C.c_uint32]
+        lib.ref_kimi_situ_glu.argtypes = [f32p, f32p, f32p, C.c_uint32, C.c_float, C.c_float]
         lib.ref_cpu_experts.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,
                                         C.POINTER(RefExpertPtrs), f32p, u32p, u32p, f32p, C.c_uint32]
         _ref = lib

@@ -214,6 +214,12 @@ REF_API int ref_dsv4_quantize(float* values, uint32_t columns) {
     return strata::dsv4_host_expert_quantize({values, columns}, columns).ok() ? 0 : 1;
 }
 
+// kimi_situ_glu, src/models/kimi_k3/kimi_k3_ops.cpp:39-62.
+REF_API int ref_kimi_situ_glu(float* out, const float* gate, const float* up, uint32_t n, float gate_beta,
+                              float linear_beta) {
+    return strata::kimi_situ_glu({out, n}, {gate, n}, {up, n}, gate_beta, linear_beta).ok() ? 0 : 1;
+}
+
 // ---- timed CPU arm ------------------------------------------------------------------
 // One MoE layer's routed experts on the host cores through the reference's own matvec
 // kernels, scheduled the way the reference schedules its host experts: one parallel region

@@ -39,7 +39,8 @@ class LayerDesc(C.Structure):
                 ("normalize", C.c_int32), ("norm_init", C.c_float), ("weight_scale", C.c_float),
                 ("output_scale", C.c_float), ("softcap", C.c_float),
                 ("shared_intermediate", C.c_uint32), ("expert_begin", C.c_uint32),
-                ("expert_count", C.c_uint32), ("max_tokens", C.c_uint32), ("max_pairs", C.c_uint32)]
+                ("expert_count", C.c_uint32), ("max_tokens", C.c_uint32), ("max_pairs", C.c_uint32),
+                ("activation", C.c_int32), ("gate_beta", C.c_float), ("linear_beta", C.c_float)]
 
 
 class Aux(C.Structure):
@@ -231,6 +232,8 @@ class MoeLayer:
         d.expert_count = cfg.E - expert_begin if expert_count is None else expert_count
         d.max_tokens = cfg.T if max_tokens is None else max_tokens
         d.max_pairs = max_pairs
+        d.activation = getattr(cfg, "activation", 0)
+        d.gate_beta, d.linear_beta = getattr(cfg, "gate_beta", 1.0), getattr(cfg, "linear_beta", 1.0)
         self.desc = d
         h = C.c_void_p()
         ctx.check(self.lib.strata_moe_layer_create(ctx.h, C.byref(d), C.byref(h)))

@@ -281,6 +281,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.y = y;
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
+        p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         {
             const char* dbg = getenv("STRATA_MOE_PREFILL_DEBUG");
             p.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
@@ -317,6 +318,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     a.act_lo = L->act_lo;
     a.y = y;
     a.status = ctx->d_status;
+    a.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
     if (L->f16_ok) {
         a.x_rowscale = L->x_rowscale;
         a.act_f32 = L->act_f32;
@@ -339,6 +341,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.y = y;
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
+        p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         a.skip_from = big;
         launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
@@ -404,6 +407,7 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
         p.y = L->sh_y;
         p.tile_table = L->shared_tiles;
         p.status = ctx->d_status;
+        p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         if (launch_prefill_bf16(p, x, T, L->shared_w[0], L->shared_w[1], L->shared_w[2], L->sh_act_hi,
                                 L->d.max_tokens, st) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "shared expert prefill launch failed");
@@ -429,6 +433,7 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
     a.act_lo = L->sh_act_lo;
     a.y = L->sh_y;
     a.status = ctx->d_status;
+    a.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
     launch_decode_gate_up(a, st);
     launch_decode_down(a, st);
     CK(cudaGetLastError());
@@ -577,6 +582,10 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
     if (d.shared_intermediate % 128)
         return fail(ctx, STRATA_MOE_E_INVALID, "shared intermediate must be a multiple of 128");
     if (d.max_tokens == 0) return fail(ctx, STRATA_MOE_E_INVALID, "max_tokens must be positive");
+    if (d.activation != STRATA_MOE_ACT_SWIGLU && d.activation != STRATA_MOE_ACT_SITU_GLU)
+        return fail(ctx, STRATA_MOE_E_INVALID, "unknown activation");
+    if (d.activation == STRATA_MOE_ACT_SITU_GLU && !(d.gate_beta > 0.0f && d.linear_beta > 0.0f))
+        return fail(ctx, STRATA_MOE_E_INVALID, "SiTU-GLU betas must be positive");
     if (!(d.weight_scale == d.weight_scale) || !(d.output_scale == d.output_scale))
         return fail(ctx, STRATA_MOE_E_INVALID, "router scales must be finite");
     CK(cudaSetDevice(ctx->device));
@@ -1053,6 +1062,7 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
         a.act_lo = L->act_lo;
         a.y = L->y;
         a.status = ctx->d_status;
+        a.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         launch_decode_gate_up(a, s);
         launch_decode_down(a, s);
     }

@@ -25,6 +25,18 @@ struct RouterParams {
     float norm_init, weight_scale, softcap;
 };
 
+// Gated activation of the expert FFN (STRATA_MOE_ACT_*); SwiGLU is evaluated by each kernel's own
+// fast path, the other kinds through glu_other().
+struct GluParams {
+    int32_t kind;
+    float gate_beta, linear_beta;
+};
+__device__ __forceinline__ float glu_other(float g, float u, const GluParams& p) {
+    // SiTU-GLU: the tanh bounds the gate, the plain sigmoid gates it, the up projection is bounded too
+    const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+    return p.gate_beta * tanhf(g / p.gate_beta) * sig * (p.linear_beta * tanhf(u / p.linear_beta));
+}
+
 // One projection of every local expert: base pointers per expert.
 struct WeightTable {
     const uint8_t* const* packed;  // [n_local] device array of device pointers
@@ -64,6 +76,7 @@ struct DecodeArgs {
     const uint32_t* n_active;      // device scalar (nullptr when active_list is nullptr)
     uint32_t max_rows_per_group;   // upper bound used to pick the token tile
     uint32_t ksplit;               // decode.cu: 1 = the four warps of a CTA split K of one tile (few tiles)
+    GluParams glu;                 // activation between gate/up and down
     uint32_t skip_from;            // decode_fp4.cu: groups with at least this many rows are left to the tensor-core path (0 = none)
     WeightTable gate, up, down;
     const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
@@ -101,6 +114,7 @@ struct PrefillArgs {
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
     uint32_t debug;                // timing experiments only (wrong results): 1 = no MMA, 2 = no decode, 4 = no stores
+    GluParams glu;                 // activation of the gate/up epilogue
     uint32_t min_rows;             // only groups with at least this many rows get tiles (0 = all)
     uint32_t reuse_tiles;          // down-only launch: the tile list of the preceding gate/up launch is still valid
     float* act_rowscale_out;       // gate/up: receives 1.0 for every row written (the activation is not pre-scaled), or nullptr

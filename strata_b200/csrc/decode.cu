@@ -379,7 +379,8 @@ __global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(Decode
                     const uint32_t orow = row + ((j & 2u) ? 8u : 0u);
                     const size_t pos = row0 + tok;
                     if (DUAL) {
-                        float v = silu_mul(accg[nt][j] * gs, accu[nt][j] * us);
+                        const float gv = accg[nt][j] * gs, uv = accu[nt][j] * us;
+                        float v = a.glu.kind == STRATA_MOE_ACT_SWIGLU ? silu_mul(gv, uv) : glu_other(gv, uv, a.glu);
                         if (a.coef) v *= a.coef[pos];
                         if (!(fabsf(v) <= 3.0e38f)) bad = true;
                         const __nv_bfloat16 hi = __float2bfloat16_rn(v);

@@ -264,7 +264,8 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
                     const size_t pos = row0 + tok;
                     const float rs = rowscale[pos];
                     if (DUAL) {
-                        float v = silu_mul_f(acc0[nt][j] * s0 * rs, acc1[nt][j] * s1 * rs);
+                        const float gv = acc0[nt][j] * s0 * rs, uv = acc1[nt][j] * s1 * rs;
+                        float v = a.glu.kind == STRATA_MOE_ACT_SWIGLU ? silu_mul_f(gv, uv) : glu_other(gv, uv, a.glu);
                         if (a.coef) v *= a.coef[pos];
                         if (!(fabsf(v) <= 3.0e38f)) bad = true;
                         a.act_f32[pos * R + orow] = v;

@@ -634,9 +634,14 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         if (a.act_rowscale_out != nullptr && feat == 0u) a.act_rowscale_out[pos] = 1.0f;
                         const float rs = rowscale ? rowscale[pos] : 1.0f;
                         const float gv = __uint_as_float(g[j]) * s0 * rs, uv = __uint_as_float(u[j]) * s1 * rs;
-                        const float e = __expf(-fabsf(gv));
-                        const float sig = gv >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
-                        const float v = gv * sig * uv;
+                        float v;
+                        if (a.glu.kind == STRATA_MOE_ACT_SWIGLU) {
+                            const float e = __expf(-fabsf(gv));
+                            const float sig = gv >= 0.0f ? __fdividef(1.0f, 1.0f + e) : __fdividef(e, 1.0f + e);
+                            v = gv * sig * uv;
+                        } else {
+                            v = glu_other(gv, uv, a.glu);
+                        }
                         if (!(fabsf(v) <= 65504.0f)) bad = true;
                         if (FMT == kFmtBf16W)
                             static_cast<__nv_bfloat16*>(act_out_v)[pos * R + feat] = __float2bfloat16_rn(v);

@@ -42,6 +42,9 @@ class MoeConfig:
     I_shared: int = 0             # BF16 shared expert width, 0 = none
     seed: int = 0
     zipf_s: float = 0.0           # > 0: Zipf(s) router bias over a seeded rank permutation
+    activation: int = 0           # 0 = SwiGLU, 1 = SiTU-GLU (Kimi-K3), routed and shared experts alike
+    gate_beta: float = 1.0
+    linear_beta: float = 1.0
     description: str = ""
 
     def with_(self, **kw):

@@ -26,6 +26,7 @@ def oracle_experts(cfg, needed):
             g = synth.NVFP4_GLOBAL[role] if cfg.fmt == synth.FMT_NVFP4 else 1.0
             mats.append(O.make_matrix(cfg.fmt, rows, cols, p, s, g))
         arr[e].gate, arr[e].up, arr[e].down = mats
+        arr[e].activation, arr[e].gate_beta, arr[e].linear_beta = cfg.activation, cfg.gate_beta, cfg.linear_beta
     return arr, keep
 
 
@@ -41,6 +42,7 @@ def oracle_shared(cfg):
         keep.append(w)
         mats.append(O.make_matrix(O.FMT_BF16, w.shape[0], w.shape[1], w))
     ex.gate, ex.up, ex.down = mats
+    ex.activation, ex.gate_beta, ex.linear_beta = cfg.activation, cfg.gate_beta, cfg.linear_beta
     return ex, keep
 
 

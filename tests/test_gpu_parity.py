@@ -22,6 +22,8 @@ TENSOR_REL_L2 = 1e-3         # tensor-core kernels: one f16 per activation eleme
 
 def tight_bound(cfg, T):
     """From 8 rows per expert on, the down projection (from 12 on, both GEMMs) runs on the tensor-core path."""
+    if cfg.I_shared and T >= 24:
+        return 2e-3          # shared expert on the tensor-core path: BF16 activation between its GEMMs
     if cfg.fmt != synth.FMT_BF16 and T * cfg.k >= 8 * cfg.E:
         return TENSOR_REL_L2
     return TIGHT_REL_L2
@@ -49,6 +51,9 @@ SMALL_CASES = [
     small(synth.FMT_NVFP4, T=9, output_scale=2.5, I_shared=256, name="laguna_like"),
     small(synth.FMT_MXFP4, T=8, zipf_s=1.1, E=64, k=8, name="zipf_bias"),
     small(synth.FMT_BF16, T=6, name="plain_bf16"),
+    small(synth.FMT_MXFP4, T=7, activation=1, gate_beta=2.5, linear_beta=4.0, name="situ_stream"),
+    small(synth.FMT_NVFP4, T=80, E=8, k=2, activation=1, gate_beta=1.5, linear_beta=2.0, I_shared=128, name="situ_tensor"),
+    small(synth.FMT_INT4, T=5, activation=1, gate_beta=3.0, linear_beta=3.0, name="situ_int4"),
     small(synth.FMT_BF16, T=40, E=8, k=2, name="plain_bf16_rows"),
 ]
 

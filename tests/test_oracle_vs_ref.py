@@ -152,3 +152,25 @@ def test_dequant_rows_match_reference_products(port, ref):
             nib = (byte >> 4) if c & 1 else (byte & 0xF)
             want = np.float32(ref.ref_fp4_e2m1(int(nib))) * np.float32(ref.ref_mxfp4_scale(int(scales[r * cols // 32 + c // 32])))
             assert deq[r, c] == want or (np.isinf(want) and np.isinf(deq[r, c]))
+
+
+def test_situ_glu_matches_reference_bitwise():
+    """kimi_situ_glu, src/models/kimi_k3/kimi_k3_ops.cpp:39-62; closed-form facts from the reference's
+    tests/test_kimi_k3_ops.cpp:39-69: zero gate gives zero, large inputs saturate at beta_g * beta_l."""
+    import ctypes as C
+    ref = O.ref()
+    if ref is None:
+        pytest.skip("compiled reference not built")
+    port = O.port()
+    rng = np.random.default_rng(11)
+    g = np.concatenate([rng.standard_normal(500) * 3, [0.0, -0.0, 40.0, -40.0, 1e-8]]).astype(np.float32)
+    u = np.concatenate([rng.standard_normal(500) * 3, [1.0, 2.0, 40.0, 40.0, -3.0]]).astype(np.float32)
+    out = np.empty_like(g)
+    f32p = C.POINTER(C.c_float)
+    for gb, lb in ((1.0, 1.0), (2.5, 0.75), (7.0, 30.0)):
+        assert ref.ref_kimi_situ_glu(out.ctypes.data_as(f32p), g.ctypes.data_as(f32p), u.ctypes.data_as(f32p),
+                                     len(g), gb, lb) == 0
+        mine = np.array([port.orc_situ_glu(float(a), float(b), gb, lb) for a, b in zip(g, u)], np.float32)
+        assert np.array_equal(mine.view(np.uint32), out.view(np.uint32)), (gb, lb)
+    assert port.orc_situ_glu(0.0, 5.0, 2.0, 3.0) == 0.0
+    assert abs(port.orc_situ_glu(40.0, 40.0, 2.0, 3.0) - 6.0) < 1e-6
