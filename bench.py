@@ -208,13 +208,13 @@ def run_gpu(args, cfg, T, rank, world):
     def step():
         ml.forward(layer.x, out)
 
+    sampler = ClockSampler(device.index)     # samples clocks and throttle reasons from the warm-up on
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         flush.zero_()
         step()
     ctx.synchronize()
 
-    sampler = ClockSampler(device.index)
-    sampler.start()
     launches0 = ctx.stats().kernel_launches
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
            for _ in range(args.steps)]
@@ -249,6 +249,12 @@ def run_gpu(args, cfg, T, rank, world):
         t0 = time.perf_counter()
         ml.forward_host(x_host, out_host)
         e2e_t.append(time.perf_counter() - t0)
+    # the timed regions above are short: keep the same load running until the clock log has a few samples
+    deadline = time.perf_counter() + 2.0
+    while len(sampler.rows) < 6 and time.perf_counter() < deadline:
+        flush.zero_()
+        step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
     e2e_s = float(np.mean(e2e_t))
 

@@ -200,10 +200,13 @@ __global__ void __launch_bounds__(kBigWarps * 32, 1) router_logits_big_kernel(
             const float4 b = *reinterpret_cast<const float4*>(xp + (swz ^ 4u));
             const float xv[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
             if (nj == 8u) {
+                // column-major over the rows: the kBigRW accumulators of a token form independent add chains,
+                // so consecutive instructions never wait on each other (per (token, row) the order over j is
+                // unchanged, which is all the reference order fixes)
 #pragma unroll
-                for (int r = 0; r < kBigRW; ++r)
+                for (int j = 0; j < 8; ++j)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
+                    for (int r = 0; r < kBigRW; ++r) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
             } else {
 #pragma unroll
                 for (int r = 0; r < kBigRW; ++r)

@@ -225,6 +225,18 @@ def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
         e2e.append(time.perf_counter() - t0)
     e2e_t = torch.tensor(e2e[2:], device=device, dtype=torch.float64)
     dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        t_end = time.perf_counter() + 2.0
+    go = torch.ones(1, device=device)
+    while True:     # same load until rank 0's clock log has a few samples (all ranks leave together)
+        if rank == 0:
+            go.fill_(1.0 if (len(sampler.rows) < 6 and time.perf_counter() < t_end) else 0.0)
+        dist.broadcast(go, 0)
+        if go.item() == 0.0:
+            break
+        flush.zero_()
+        ep.forward(x_local)
+        torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
     ctx.synchronize()
     # where a step's time goes: the four stages of the peer exchange, timed on this rank's stream
