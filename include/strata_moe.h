@@ -177,6 +177,12 @@ int strata_moe_forward_host(strata_moe_layer* layer, const void* x_bf16_host, ui
  * deepseek_ops.cpp:82-133); projection order as kernels/cuda/backend.cu:651-728. */
 int strata_moe_route(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens, float* logits,
                      uint32_t* ids, float* weights);
+/* Hash routing: the experts of every token are given (token_experts [T, k], device, e.g. looked up from the
+ * checkpoint's token-id table); the weights are the layer's scores of those experts, summed in rank order,
+ * normalised and scaled exactly as strata_moe_route does.  ids receives a copy of token_experts.
+ * ref: dsv4_route_hash_sqrtsoftplus_f32(_into), src/models/dsv4/deepseek_ops.cpp:390-461. */
+int strata_moe_route_hash(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens,
+                          const uint32_t* token_experts, float* logits, uint32_t* ids, float* weights);
 /* ref: job building in sparse_mlp (src/models/glm52/glm_runtime.cpp:1521-1541) and the page
  * group table (src/models/dsv4/deepseek_runtime.cpp:6216-6321).  Groups pairs whose expert lies
  * in [expert_begin, expert_begin + n_experts); counts/offsets are indexed from expert_begin.

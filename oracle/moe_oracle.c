@@ -396,6 +396,36 @@ ORC_API int orc_route_row(const orc_router_spec* s, const float* logits, const f
     return 0;
 }
 
+/* Hash routing, dsv4_route_hash_sqrtsoftplus_f32_into (src/models/dsv4/deepseek_ops.cpp:414-461): the
+ * experts are given, the weights are their scores summed in rank order, normalised and scaled.  Stated
+ * for every score kind; softmax is not covered (it has no reference).  Returns -3 for an id >= E. */
+ORC_API int orc_route_given_row(const orc_router_spec* s, const float* logits, const uint32_t* token_experts,
+                                uint32_t* ids, float* weights) {
+    const uint32_t E = s->experts, k = s->top_k;
+    for (uint32_t e = 0; e < E; ++e)
+        if (!isfinite(logits[e])) return -1;
+    for (uint32_t r = 0; r < k; ++r) {
+        const uint32_t e = token_experts[r];
+        if (e >= E) return -3;
+        float l = logits[e];
+        if (s->softcap > 0.0f) l = tanhf(l / s->softcap) * s->softcap;
+        ids[r] = e;
+        if (s->score_kind == ORC_SCORE_SIGMOID) weights[r] = orc_sigmoid(l);
+        else if (s->score_kind == ORC_SCORE_SIGMOID_PLAIN) weights[r] = 1.0f / (1.0f + expf(-l));
+        else if (s->score_kind == ORC_SCORE_SQRTSOFTPLUS) weights[r] = sqrtf(orc_softplus(l));
+        else return -4;
+    }
+    if (s->normalize) {
+        float sum = s->norm_init;
+        for (uint32_t r = 0; r < k; ++r) sum += weights[r];
+        if (!(sum > 0.0f) || !isfinite(sum)) return -2;
+        for (uint32_t r = 0; r < k; ++r) weights[r] = weights[r] / sum * s->weight_scale;
+    } else {
+        for (uint32_t r = 0; r < k; ++r) weights[r] = weights[r] * s->weight_scale;
+    }
+    return 0;
+}
+
 ORC_API int orc_route(const orc_router_spec* s, const float* logits, const float* bias, uint32_t T,
                       uint32_t* ids, float* weights) {
     int rc = 0;

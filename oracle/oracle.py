@@ -91,6 +91,7 @@ def port():
                                       C.POINTER(Expert), u32p, C.c_uint32, f32p, u32p, f32p, u32p,
                                       u32p, u32p, f32p]
         lib.orc_expert_ffn.argtypes = [C.POINTER(Expert), f32p, C.c_float, C.c_int, C.c_int, f32p, f32p, f32p]
+        lib.orc_route_given_row.argtypes = [C.POINTER(RouterSpec), f32p, u32p, u32p, f32p]
         lib.orc_situ_glu.argtypes = [C.c_float] * 4
         lib.orc_situ_glu.restype = C.c_float
         lib.orc_bf16_round.argtypes = [C.c_float]
@@ -137,6 +138,7 @@ def ref():
         lib.ref_dsv4_host_expert.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32,
                                              C.c_uint32, C.c_float, C.c_float, C.c_int]
         lib.ref_cpu_experts.restype = C.c_int64
+        lib.ref_dsv4_route_hash.argtypes = [f32p, u32p, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
         lib.ref_dsv4_quantize.argtypes = [f32p, C.c_uint32]
         lib.ref_kimi_situ_glu.argtypes = [f32p, f32p, f32p, C.c_uint32, C.c_float, C.c_float]
         lib.ref_cpu_experts.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,

@@ -111,6 +111,24 @@ REF_API int ref_dsv4_route(const float* logits, const float* bias, uint32_t expe
     return 0;
 }
 
+// dsv4_route_hash_sqrtsoftplus_f32_into, src/models/dsv4/deepseek_ops.cpp:414-461.
+REF_API int ref_dsv4_route_hash(const float* logits, const uint32_t* token_experts, uint32_t experts, uint32_t k,
+                                float routed_scale, uint32_t* ids, float* weights) {
+    strata::RouterSpec spec;
+    spec.selection = strata::RouterSelectionKind::NoAuxTc;
+    spec.scoring = strata::RouterScoreKind::SqrtSoftplus;
+    spec.routed_experts = experts;
+    spec.experts_per_token = k;
+    spec.normalize_topk = true;
+    spec.selection_bias = true;
+    spec.routed_scale = routed_scale;
+    return strata::dsv4_route_hash_sqrtsoftplus_f32_into({logits, experts}, {token_experts, k}, spec, {ids, k},
+                                                          {weights, k})
+                   .ok()
+               ? 0
+               : 1;
+}
+
 // ---- quantized matvecs --------------------------------------------------------
 // kimi_mxfp4_matvec, src/models/kimi_k3/kimi_k3_layer.cpp:237-301 (AVX2 when the CPU has it)
 REF_API int ref_kimi_mxfp4_matvec(float* out, const float* in, const uint8_t* packed,

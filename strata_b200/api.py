@@ -22,6 +22,7 @@ EXPORTS = [
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
+    "strata_moe_route_hash",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -87,6 +88,7 @@ def load_library():
     lib.strata_moe_forward.argtypes = [vp, vp, u32, vp, C.POINTER(Aux)]
     lib.strata_moe_forward_host.argtypes = [vp, vp, u32, vp]
     lib.strata_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
+    lib.strata_moe_route_hash.argtypes = [vp, vp, u32, vp, vp, vp, vp]
     lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp]
     lib.strata_moe_gather_rows.argtypes = [vp, vp, u32, vp, u32, u32, vp]
     lib.strata_moe_combine.argtypes = [vp, vp, vp, vp, vp, u32, vp]
@@ -307,6 +309,16 @@ class MoeLayer:
         self.ctx.check(self.lib.strata_moe_route(self.h, _ptr(x), T, _ptr(logits), _ptr(ids), _ptr(w)))
         self.ctx.leave()
         return (ids, w, logits) if want_logits else (ids, w)
+
+    def route_hash(self, x, token_experts):
+        """Weights for given experts per token (hash routing); returns (ids, weights)."""
+        T, dev = x.shape[0], x.device
+        ids = torch.empty(T, self.cfg.k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, self.cfg.k, dtype=torch.float32, device=dev)
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_route_hash(self.h, _ptr(x), T, _ptr(token_experts), None, _ptr(ids), _ptr(w)))
+        self.ctx.leave()
+        return ids, w
 
     def group(self, ids, expert_begin=0, n_experts=None, want_inv=False):
         n_experts = self.cfg.E if n_experts is None else n_experts

@@ -783,6 +783,24 @@ int strata_moe_route(strata_moe_layer* L, const void* x, uint32_t T, float* logi
     return 0;
 }
 
+int strata_moe_route_hash(strata_moe_layer* L, const void* x, uint32_t T, const uint32_t* token_experts,
+                          float* logits, uint32_t* ids, float* weights) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!x || !token_experts || !ids || !weights) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (!L->router) return fail(ctx, STRATA_MOE_E_INVALID, "router weights were never set");
+    CK(cudaSetDevice(ctx->device));
+    float* lg = logits ? logits : L->logits;
+    launch_router_logits((const __nv_bfloat16*)x, L->router, T, L->d.hidden, L->d.experts, lg, ctx->stream);
+    RouterParams p{L->d.experts, L->d.top_k, L->d.score_kind, L->d.normalize, L->d.norm_init,
+                   L->d.weight_scale, L->d.softcap};
+    // an expert id outside the layer raises the status word (kStatusNonFiniteLogit's neighbour: bad route)
+    launch_route(p, lg, nullptr, T, ids, weights, ctx->d_status, ctx->stream, token_experts);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 int strata_moe_group(strata_moe_layer* L, const uint32_t* ids, uint32_t pairs, uint32_t expert_begin,
                      uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm,
                      uint32_t* inv) {

@@ -51,7 +51,8 @@ struct WeightTable {
 void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
                           uint32_t E, float* logits, cudaStream_t s);
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
-                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s);
+                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s,
+                  const uint32_t* forced_ids = nullptr);
 // group.cu
 size_t group_scratch_bytes(uint32_t pairs, uint32_t n_experts);
 void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, uint32_t n_experts,

@@ -262,7 +262,8 @@ constexpr int kRouteWarps = 4;
 
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
-    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status) {
+    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
+    const uint32_t* __restrict__ forced_ids) {
     extern __shared__ float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
@@ -312,7 +313,14 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     // k rounds of arg-max over (value desc, index asc); taken entries drop to -inf.
     float my_w = 0.0f;
     uint32_t my_id = 0;
-    for (uint32_t r = 0; r < k; ++r) {
+    // Hash routing (src/models/dsv4/deepseek_ops.cpp:390-461): the experts of a token come from a
+    // table, only their weights are computed here -- same scores, same rank-order sum and division.
+    for (uint32_t r = 0; forced_ids != nullptr && r < k; ++r) {
+        uint32_t bi = forced_ids[(size_t)tok * k + r];
+        if (bi >= E) { bad = true; bi = 0; }
+        if (lane == r) { my_id = bi; my_w = score[bi]; }
+    }
+    for (uint32_t r = 0; forced_ids == nullptr && r < k; ++r) {
         float bv = -INFINITY;
         uint32_t bi = 0xFFFFFFFFu;
         for (uint32_t e = lane; e < E; e += 32u) {
@@ -354,11 +362,11 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
 }
 
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
-                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s) {
+                  uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s, const uint32_t* forced_ids) {
     if (T == 0) return;
     const size_t smem = (size_t)kRouteWarps * 2u * p.experts * sizeof(float);
     route_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, s>>>(
-        p, logits, bias, T, ids, weights, status);
+        p, logits, bias, T, ids, weights, status, forced_ids);
     ++g_kernel_launches;
 }
 

@@ -278,3 +278,35 @@ def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
     rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
     assert rel <= TENSOR_REL_L2 and mx <= MAX_ABS, (rel, mx)
+
+
+@pytest.mark.parametrize("kind", [synth.SCORE_SIGMOID, synth.SCORE_SQRTSOFTPLUS])
+def test_hash_routing_weights(ctx, kind):
+    """Experts given per token (hash routing): ids are passed through, weights equal the oracle's
+    (bit for bit for the sigmoid rule; within 2 ulp for sqrt-softplus, whose log1p is not the host's)."""
+    import ctypes as C
+    cfg = small(synth.FMT_MXFP4, T=9, E=32, k=4, score_kind=kind, weight_scale=1.5, name=f"hash{kind}")
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg, max_tokens=cfg.T)
+    ml.load_synth(layer)
+    rng = np.random.default_rng(8)
+    table = np.stack([rng.choice(cfg.E, size=cfg.k, replace=False) for _ in range(cfg.T)]).astype(np.int32)
+    ids, w = ml.route_hash(layer.x, torch.from_numpy(table).cuda())
+    _, _, logits = ml.route(layer.x, want_logits=True)
+    ctx.synchronize()
+    assert np.array_equal(ids.cpu().numpy(), table)
+    spec = O.router_spec(cfg.E, cfg.k, kind, normalize=True, weight_scale=1.5)
+    lg = logits.cpu().numpy()
+    f32p, u32p = C.POINTER(C.c_float), C.POINTER(C.c_uint32)
+    want = np.empty((cfg.T, cfg.k), np.float32)
+    tmp = np.empty(cfg.k, np.uint32)
+    for t in range(cfg.T):
+        row = np.ascontiguousarray(table[t].astype(np.uint32))
+        assert O.port().orc_route_given_row(C.byref(spec), np.ascontiguousarray(lg[t]).ctypes.data_as(f32p),
+                                            row.ctypes.data_as(u32p), tmp.ctypes.data_as(u32p),
+                                            want[t].ctypes.data_as(f32p)) == 0
+    got = w.cpu().numpy()
+    if kind == synth.SCORE_SIGMOID:
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    else:
+        assert np.all(np.abs(got - want) <= 2 * np.spacing(np.abs(want)))

@@ -174,3 +174,29 @@ def test_situ_glu_matches_reference_bitwise():
         assert np.array_equal(mine.view(np.uint32), out.view(np.uint32)), (gb, lb)
     assert port.orc_situ_glu(0.0, 5.0, 2.0, 3.0) == 0.0
     assert abs(port.orc_situ_glu(40.0, 40.0, 2.0, 3.0) - 6.0) < 1e-6
+
+
+def test_hash_route_matches_reference_bitwise():
+    """dsv4_route_hash_sqrtsoftplus_f32_into, src/models/dsv4/deepseek_ops.cpp:414-461."""
+    import ctypes as C
+    ref = O.ref()
+    if ref is None:
+        pytest.skip("compiled reference not built")
+    port = O.port()
+    f32p, u32p = C.POINTER(C.c_float), C.POINTER(C.c_uint32)
+    rng = np.random.default_rng(3)
+    E, k = 256, 6
+    spec = O.router_spec(E, k, O.SCORE_SQRTSOFTPLUS, normalize=True, weight_scale=1.5)
+    for _ in range(20):
+        logits = (rng.standard_normal(E) * 4).astype(np.float32)
+        table = rng.choice(E, size=k, replace=False).astype(np.uint32)
+        ids_a, w_a = np.empty(k, np.uint32), np.empty(k, np.float32)
+        ids_b, w_b = np.empty(k, np.uint32), np.empty(k, np.float32)
+        assert port.orc_route_given_row(C.byref(spec), logits.ctypes.data_as(f32p), table.ctypes.data_as(u32p),
+                                        ids_a.ctypes.data_as(u32p), w_a.ctypes.data_as(f32p)) == 0
+        assert ref.ref_dsv4_route_hash(logits.ctypes.data_as(f32p), table.ctypes.data_as(u32p), E, k, 1.5,
+                                       ids_b.ctypes.data_as(u32p), w_b.ctypes.data_as(f32p)) == 0
+        assert np.array_equal(ids_a, ids_b) and np.array_equal(w_a.view(np.uint32), w_b.view(np.uint32))
+    bad = np.array([0, 1, 2, 3, 4, E], np.uint32)
+    assert port.orc_route_given_row(C.byref(spec), logits.ctypes.data_as(f32p), bad.ctypes.data_as(u32p),
+                                    ids_a.ctypes.data_as(u32p), w_a.ctypes.data_as(f32p)) == -3
