@@ -40,19 +40,19 @@
 
 namespace smoe {
 
-constexpr uint32_t kNTile = 128;    // tokens per tile
+constexpr uint32_t kNTile = 192;    // tokens per tile (an expert with up to 192 rows is decoded once)
 constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
 // Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
-constexpr uint32_t kAStages = 4;   // tensor-memory ring of decoded weight slices (shared-memory ring for BF16 weights uses 2)
+constexpr uint32_t kAStages = 2;   // tensor-memory ring of decoded weight slices (shared-memory ring for BF16 weights uses 2)
 constexpr uint32_t kASmemStages = 2;
-constexpr uint32_t kBStages = 8;
+constexpr uint32_t kBStages = 6;
 constexpr uint32_t kPkBufs = 2;      // packed-weight staging blocks (256 columns each) in flight
-constexpr uint32_t kAccCols = 256;                      // accumulator columns (2 tiles x kNTile)
+constexpr uint32_t kAccCols = 2 * kNTile;                // accumulator columns (2 tiles x kNTile)
 constexpr uint32_t kAStageCols = 64;                    // tensor-memory columns per A stage: 2 tiles x (kBK / 2)
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
-constexpr uint32_t kBTile = kNTile * kBK * 2;  // 16 KiB
+constexpr uint32_t kBTile = kNTile * kBK * 2;  // 24 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
 constexpr uint32_t kEpilogueWarps = 8;   // two per tensor-memory lane quarter: even / odd 16-token chunks
 constexpr uint32_t kThreads = (4 + kDecodeWarps + kEpilogueWarps) * 32;
@@ -344,8 +344,10 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     if (!mbar_wait(&S.empty_b[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
                     if ((a.debug & 8u) && bsel > 2u) bsel = 2u;   // timing experiment: half the activation bytes
-                    mbar_arrive_expect_tx(&S.full_b[s], (16u << bsel) * kBK * 2u);
+                    const bool tail = t.n > 128u && !(a.debug & 8u);   // rows 128..191 arrive as a second, 64-row box
+                    mbar_arrive_expect_tx(&S.full_b[s], ((16u << bsel) + (tail ? 64u : 0u)) * kBK * 2u);
                     tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
+                    if (tail) tma_load_2d(S.b[s] + 128u * kBK * 2u, &maps_b.m[2], ks * kBK, t.row0 + 128u, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
                         const uint32_t sa = it % kASmemStages, pa = (it / kASmemStages) & 1u;
                         if (!mbar_wait(&S.empty_a[sa], pa ^ 1u, abort_flag)) { ok = false; break; }
