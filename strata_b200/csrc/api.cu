@@ -238,6 +238,14 @@ bool use_prefill_down(const strata_moe_layer* L, uint32_t pairs, uint32_t n_grou
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
+// Token tile of the tensor-core path: 192 when groups are large (an expert with up to 192 rows is decoded
+// once), 128 with its deeper weight ring when they are small.
+uint32_t prefill_ntile(uint64_t pairs, uint64_t n_groups) {
+    const char* e = getenv("STRATA_MOE_PREFILL_NTILE");
+    if (e) return (uint32_t)atoi(e) == 128u ? 128u : 192u;
+    return pairs > 96u * n_groups ? 192u : 128u;
+}
+
 // Row count from which a single group is handed to the tensor-core path inside an otherwise
 // weight-streaming step; 0 = mixed dispatch off.
 uint32_t mixed_min_rows(const strata_moe_layer* L, uint32_t max_rows_per_group) {
@@ -282,6 +290,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
+        p.ntile = prefill_ntile(pairs, n_groups);
         {
             const char* dbg = getenv("STRATA_MOE_PREFILL_DEBUG");
             p.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
@@ -342,6 +351,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
+        p.ntile = 128;   // hybrid down: few rows per expert
         a.skip_from = big;
         launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
@@ -350,6 +360,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
                                L->act_rowscale, s, pairs_dev);
         if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
             p.min_rows = big;
+            p.ntile = 128;   // measured at the c4 shape: 407 us with 128-token tiles, 439 us with 192
             p.act_rowscale_out = L->act_rowscale;
             if (launch_prefill_gate_up(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill gate/up launch failed");
@@ -360,6 +371,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.act_rowscale_out = nullptr;
         if (down_all_tensor) {
             p.min_rows = 0;
+            p.ntile = 128;
             if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
         } else {
@@ -403,6 +415,7 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
         p.I = L->d.shared_intermediate;
         p.n_groups = 1;
         p.pairs = T;
+        p.ntile = prefill_ntile(T, 1);
         p.offsets = offsets2;
         p.y = L->sh_y;
         p.tile_table = L->shared_tiles;

@@ -116,6 +116,7 @@ struct PrefillArgs {
     uint32_t* status;
     uint32_t debug;                // timing experiments only (wrong results): 1 = no MMA, 2 = no decode, 4 = no stores
     GluParams glu;                 // activation of the gate/up epilogue
+    uint32_t ntile;                // tokens per tile: 128, or anything else for 192 (large groups)
     uint32_t min_rows;             // only groups with at least this many rows get tiles (0 = all)
     uint32_t reuse_tiles;          // down-only launch: the tile list of the preceding gate/up launch is still valid
     float* act_rowscale_out;       // gate/up: receives 1.0 for every row written (the activation is not pre-scaled), or nullptr

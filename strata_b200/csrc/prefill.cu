@@ -40,19 +40,26 @@
 
 namespace smoe {
 
-constexpr uint32_t kNTile = 192;    // tokens per tile (an expert with up to 192 rows is decoded once)
+// Tokens per tile: 192 (an expert with up to 192 rows is decoded once; two tensor-memory weight stages) when
+// groups are large, 128 (four weight stages: shorter handshakes for small tiles) otherwise.
+template <int NT>
+struct Geo {
+    static_assert(NT == 128 || NT == 192, "tile sizes");
+    static constexpr uint32_t kNTile = NT;
+    static constexpr uint32_t kAccCols = 2u * NT;                    // accumulator columns (2 tiles x NT)
+    static constexpr uint32_t kAStages = (512u - 2u * NT) / 64u;     // tensor-memory ring of decoded weight slices
+    static constexpr uint32_t kBStages = NT == 192 ? 6u : 8u;        // activation tiles in flight
+    static constexpr uint32_t kBTile = NT * 64u * 2u;                // bytes of one activation tile stage
+};
+constexpr uint32_t kMaxAStages = 4;
 constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
 // Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
-constexpr uint32_t kAStages = 2;   // tensor-memory ring of decoded weight slices (shared-memory ring for BF16 weights uses 2)
 constexpr uint32_t kASmemStages = 2;
-constexpr uint32_t kBStages = 6;
 constexpr uint32_t kPkBufs = 2;      // packed-weight staging blocks (256 columns each) in flight
-constexpr uint32_t kAccCols = 2 * kNTile;                // accumulator columns (2 tiles x kNTile)
 constexpr uint32_t kAStageCols = 64;                    // tensor-memory columns per A stage: 2 tiles x (kBK / 2)
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
-constexpr uint32_t kBTile = kNTile * kBK * 2;  // 24 KiB
 constexpr uint32_t kDecodeWarps = 16;  // each lane decodes 32 columns of one row per stage
 constexpr uint32_t kEpilogueWarps = 8;   // two per tensor-memory lane quarter: even / odd 16-token chunks
 constexpr uint32_t kThreads = (4 + kDecodeWarps + kEpilogueWarps) * 32;
@@ -253,12 +260,13 @@ struct TileInfo {
     uint32_t m0;          // first output feature
 };
 
+template <int NT>
 struct __align__(1024) PrefillSmem {
     // 4-bit formats: packed staging [buffer][gate/down, up][kPkTile].
     // BF16 weights: A tiles [stage][gate/down, up][kATile] (kPkTile == kATile).
     uint8_t w[kPkBufs][2][kPkTile];
-    uint8_t b[kBStages][kBTile];   // activation tile
-    uint64_t full_a[kAStages], empty_a[kAStages], full_b[kBStages], empty_b[kBStages];
+    uint8_t b[Geo<NT>::kBStages][Geo<NT>::kBTile];   // activation tile
+    uint64_t full_a[kMaxAStages], empty_a[kMaxAStages], full_b[Geo<NT>::kBStages], empty_b[Geo<NT>::kBStages];
     uint64_t pk_full[kPkBufs], pk_empty[kPkBufs];
     uint64_t acc_full, acc_empty;
     uint32_t tmem_base;
@@ -282,13 +290,16 @@ __device__ __forceinline__ bool tile_lookup(const uint32_t* table, uint32_t tile
 // MODE 2: two adjacent down tiles (256 features) against the same activation tile -- halves the
 //         shared-memory traffic per MMA of MODE 1; needs H % 256 == 0.
 // DUAL (two weight tiles and two accumulators per activation tile) = MODE 0 or 2.
-template <int FMT, int MODE>
+template <int FMT, int MODE, int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__ CUtensorMap map_a0,
                    const __grid_constant__ CUtensorMap map_a1, PrefillArgs a, const float* __restrict__ rowscale,
                    void* __restrict__ act_out_v, const CUtensorMap* __restrict__ wmaps /* [3][n_groups] */) {
     extern __shared__ uint8_t smem_raw[];
-    PrefillSmem& S = *reinterpret_cast<PrefillSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    PrefillSmem<NT>& S =
+        *reinterpret_cast<PrefillSmem<NT>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr uint32_t kNTile = Geo<NT>::kNTile, kAccCols = Geo<NT>::kAccCols, kAStages = Geo<NT>::kAStages,
+                       kBStages = Geo<NT>::kBStages;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     constexpr bool DUAL = MODE != 1;
     constexpr bool GU = MODE == 0;
@@ -681,7 +692,8 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
 // ------------------------------------------------------------------------------ tile list
 // table[0] = number of n-tiles, then (expert, first row, rows) per n-tile, experts ascending.
 __global__ void __launch_bounds__(1024) prefill_tiles_kernel(const uint32_t* __restrict__ offsets, uint32_t n_groups,
-                                                             uint32_t* __restrict__ table, uint32_t min_rows) {
+                                                             uint32_t* __restrict__ table, uint32_t min_rows,
+                                                             uint32_t kNTile) {
     __shared__ uint32_t scan[1024];
     const uint32_t tid = threadIdx.x;
     uint32_t cnt = 0, r0 = 0;
@@ -744,7 +756,7 @@ bool prefill_supported(int fmt, uint32_t H, uint32_t I) {
 }
 
 size_t prefill_scratch_bytes(uint32_t n_groups, uint32_t pairs) {
-    return (4 + 3 * ((size_t)pairs / kNTile + n_groups + 1)) * sizeof(uint32_t);
+    return (4 + 3 * ((size_t)pairs / 128u + n_groups + 1)) * sizeof(uint32_t);   // the smaller tile size bounds it
 }
 
 static bool make_bmaps(BMaps* b, const void* base, uint64_t rows, uint64_t cols) {
@@ -753,15 +765,15 @@ static bool make_bmaps(BMaps* b, const void* base, uint64_t rows, uint64_t cols)
     return true;
 }
 
-template <int FMT>
+template <int FMT, int NT>
 static int set_smem_attr(size_t smem) {
     static bool done = false;
     if (done) return 0;
-    if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 0, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 1, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess ||
-        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 2, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
         return -2;
     done = true;
@@ -785,117 +797,137 @@ int prefill_encode_weight_map(void* out, const void* packed, uint32_t rows, uint
                : -1;
 }
 
-template <int FMT>
+template <int FMT, int NT>
 static int launch_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                       uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid) {
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
     BMaps map_x, map_act;
     if (!make_bmaps(&map_x, x16, pairs_cap, a.H) || !make_bmaps(&map_act, act16, pairs_cap, a.I)) return -1;
     const CUtensorMap& dummy = map_x.m[0];
-    const size_t smem = sizeof(PrefillSmem) + 1024;
-    if (set_smem_attr<FMT>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
-    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
+    const size_t smem = sizeof(PrefillSmem<NT>) + 1024;
+    if (set_smem_attr<FMT, NT>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows, NT);
+    prefill_ffn_kernel<FMT, 0, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
     if (mid) cudaEventRecord(mid, s);
     if (a.H % 256u == 0u)
-        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
+        prefill_ffn_kernel<FMT, 2, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     else
-        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
+        prefill_ffn_kernel<FMT, 1, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, nullptr, nullptr, wm);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
-template <int FMT>
+template <int FMT, int NT>
 static int launch_gate_up_fmt(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                               uint32_t pairs_cap, const void* wmaps, cudaStream_t s) {
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
     BMaps map_x;
     if (!make_bmaps(&map_x, x16, pairs_cap, a.H)) return -1;
     const CUtensorMap& dummy = map_x.m[0];
-    const size_t smem = sizeof(PrefillSmem) + 1024;
-    if (set_smem_attr<FMT>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
-    prefill_ffn_kernel<FMT, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
+    const size_t smem = sizeof(PrefillSmem<NT>) + 1024;
+    if (set_smem_attr<FMT, NT>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows, NT);
+    prefill_ffn_kernel<FMT, 0, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, dummy, dummy, a, x_rowscale, act16, wm);
     g_kernel_launches += 2;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int launch_prefill_gate_up(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                            uint32_t pairs_cap, const void* wmaps, cudaStream_t s) {
+    const bool wide = a.ntile != 128u;
     switch (a.fmt) {
-        case STRATA_MOE_FMT_MXFP4: return launch_gate_up_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
-        case STRATA_MOE_FMT_NVFP4: return launch_gate_up_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_MXFP4:
+            return wide ? launch_gate_up_fmt<STRATA_MOE_FMT_MXFP4, 192>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s)
+                        : launch_gate_up_fmt<STRATA_MOE_FMT_MXFP4, 128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_NVFP4:
+            return wide ? launch_gate_up_fmt<STRATA_MOE_FMT_NVFP4, 192>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s)
+                        : launch_gate_up_fmt<STRATA_MOE_FMT_NVFP4, 128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s);
         default: return -1;
     }
 }
 
 // Down projection only, over f16 activation rows that carry a per-row factor (act_rowscale undoes it).
-template <int FMT>
+template <int FMT, int NT>
 static int launch_down_fmt(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
                            const void* wmaps, cudaStream_t s) {
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(wmaps);
     BMaps map_act;
     if (!make_bmaps(&map_act, act16, pairs_cap, a.I)) return -1;
     const CUtensorMap& dummy = map_act.m[0];
-    const size_t smem = sizeof(PrefillSmem) + 1024;
-    if (set_smem_attr<FMT>(smem)) return -2;
+    const size_t smem = sizeof(PrefillSmem<NT>) + 1024;
+    if (set_smem_attr<FMT, NT>(smem)) return -2;
     if (!a.reuse_tiles) {
-        prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
+        prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows, NT);
         ++g_kernel_launches;
     }
     if (a.H % 256u == 0u)
-        prefill_ffn_kernel<FMT, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
+        prefill_ffn_kernel<FMT, 2, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
     else
-        prefill_ffn_kernel<FMT, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
+        prefill_ffn_kernel<FMT, 1, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, dummy, dummy, a, act_rowscale, nullptr, wm);
     ++g_kernel_launches;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
 int launch_prefill_down(const PrefillArgs& a, const void* act16, const float* act_rowscale, uint32_t pairs_cap,
                         const void* wmaps, cudaStream_t s) {
+    const bool wide = a.ntile != 128u;
     switch (a.fmt) {
-        case STRATA_MOE_FMT_MXFP4: return launch_down_fmt<STRATA_MOE_FMT_MXFP4>(a, act16, act_rowscale, pairs_cap, wmaps, s);
-        case STRATA_MOE_FMT_NVFP4: return launch_down_fmt<STRATA_MOE_FMT_NVFP4>(a, act16, act_rowscale, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_MXFP4:
+            return wide ? launch_down_fmt<STRATA_MOE_FMT_MXFP4, 192>(a, act16, act_rowscale, pairs_cap, wmaps, s)
+                        : launch_down_fmt<STRATA_MOE_FMT_MXFP4, 128>(a, act16, act_rowscale, pairs_cap, wmaps, s);
+        case STRATA_MOE_FMT_NVFP4:
+            return wide ? launch_down_fmt<STRATA_MOE_FMT_NVFP4, 192>(a, act16, act_rowscale, pairs_cap, wmaps, s)
+                        : launch_down_fmt<STRATA_MOE_FMT_NVFP4, 128>(a, act16, act_rowscale, pairs_cap, wmaps, s);
         default: return -1;
     }
 }
 
 int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscale, void* act16,
                    uint32_t pairs_cap, const void* wmaps, cudaStream_t s, cudaEvent_t mid) {
+    const bool wide = a.ntile != 128u;
+#define STRATA_PREFILL_CASE(F)                                                                              \
+    case F:                                                                                                 \
+        return wide ? launch_fmt<F, 192>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid)               \
+                    : launch_fmt<F, 128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
     switch (a.fmt) {
-        case STRATA_MOE_FMT_MXFP4:
-            return launch_fmt<STRATA_MOE_FMT_MXFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
-        case STRATA_MOE_FMT_NVFP4:
-            return launch_fmt<STRATA_MOE_FMT_NVFP4>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
-        case STRATA_MOE_FMT_INT4G128:
-            return launch_fmt<STRATA_MOE_FMT_INT4G128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
+        STRATA_PREFILL_CASE(STRATA_MOE_FMT_MXFP4)
+        STRATA_PREFILL_CASE(STRATA_MOE_FMT_NVFP4)
+        STRATA_PREFILL_CASE(STRATA_MOE_FMT_INT4G128)
         default: return -1;
     }
+#undef STRATA_PREFILL_CASE
 }
 
 // BF16 expert (the shared expert) over `rows` token rows in natural order: x [rows, H] BF16,
 // gate/up [I, H], down [H, I] BF16, act [rows_cap, I] BF16 scratch, y [rows, H] fp32.
 // a.offsets must hold {0, rows}; a.n_groups = 1.
-int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
-                        const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
+template <int NT>
+static int launch_bf16_nt(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
+                          const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
     BMaps map_x, map_act;
     CUtensorMap map_g, map_u, map_d;
     if (!make_bmaps(&map_x, x, rows, a.H) || !make_bmaps(&map_act, act, rows_cap, a.I) ||
         !make_map(&map_g, w_gate, a.I, a.H, kMTile) || !make_map(&map_u, w_up, a.I, a.H, kMTile) ||
         !make_map(&map_d, w_down, a.H, a.I, kMTile))
         return -1;
-    const size_t smem = sizeof(PrefillSmem) + 1024;
-    if (set_smem_attr<kFmtBf16W>(smem)) return -2;
-    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows);
-    prefill_ffn_kernel<kFmtBf16W, 0><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
+    const size_t smem = sizeof(PrefillSmem<NT>) + 1024;
+    if (set_smem_attr<kFmtBf16W, NT>(smem)) return -2;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, a.n_groups, a.tile_table, a.min_rows, NT);
+    prefill_ffn_kernel<kFmtBf16W, 0, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, map_g, map_u, a, nullptr, act, nullptr);
     if (a.H % 256u == 0u)
-        prefill_ffn_kernel<kFmtBf16W, 2><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
+        prefill_ffn_kernel<kFmtBf16W, 2, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
                                                                          nullptr);
     else
-        prefill_ffn_kernel<kFmtBf16W, 1><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
+        prefill_ffn_kernel<kFmtBf16W, 1, NT><<<kNumSMs, kThreads, smem, s>>>(map_act, map_d, map_d, a, nullptr, nullptr,
                                                                          nullptr);
     g_kernel_launches += 3;
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
+                        const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
+    return a.ntile != 128u ? launch_bf16_nt<192>(a, x, rows, w_gate, w_up, w_down, act, rows_cap, s)
+                           : launch_bf16_nt<128>(a, x, rows, w_gate, w_up, w_down, act, rows_cap, s);
 }
 
 }  // namespace smoe
