@@ -87,11 +87,11 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
             float s = sum[tok];
             if (nj == 8u) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) s = __fadd_rn(s, __fmul_rn(xv[j], wv[j]));
+                for (int j = 0; j < 8; ++j) s = __fmaf_rn(xv[j], wv[j], s);
             } else {
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
-                    if ((uint32_t)j < nj) s = __fadd_rn(s, __fmul_rn(xv[j], wv[j]));
+                    if ((uint32_t)j < nj) s = __fmaf_rn(xv[j], wv[j], s);
             }
             sum[tok] = s;
         }
@@ -106,6 +106,11 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     }
 }
 
+// Multiply-add: the reference rounds the product and the sum separately (__fmul_rn, __fadd_rn).  Both
+// operands here are BF16 values, whose product has at most 16 significant bits and is therefore exact in
+// FP32, so one fused multiply-add rounds exactly once, at the same place, and returns the same bits with
+// half the instructions.  (The only divergence would need a product below 2^-126 added to a subnormal sum.)
+//
 // Large token counts: every warp owns RW expert rows and a 16-token tile, so one staged
 // activation value feeds RW multiply-add chains and the staging cost is shared by 8 * RW rows.
 // Same per-lane accumulation order as above (the order is a property of one (token, row) dot
@@ -206,13 +211,13 @@ __global__ void __launch_bounds__(kBigWarps * 32, 1) router_logits_big_kernel(
 #pragma unroll
                 for (int j = 0; j < 8; ++j)
 #pragma unroll
-                    for (int r = 0; r < kBigRW; ++r) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
+                    for (int r = 0; r < kBigRW; ++r) sum[r][tok] = __fmaf_rn(xv[j], wv[r][j], sum[r][tok]);
             } else {
 #pragma unroll
                 for (int r = 0; r < kBigRW; ++r)
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        if ((uint32_t)j < nj) sum[r][tok] = __fadd_rn(sum[r][tok], __fmul_rn(xv[j], wv[r][j]));
+                        if ((uint32_t)j < nj) sum[r][tok] = __fmaf_rn(xv[j], wv[r][j], sum[r][tok]);
             }
         }
     }
