@@ -188,12 +188,23 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
     const uint32_t n_act = a.active_list ? *a.n_active : a.n_groups;
     const uint32_t total = n_act * tiles_per_group;
     if (total == 0u) return;
-    const uint32_t W = gridDim.x * 4u;
+    const uint32_t steps = K / 128u;
+    const uint32_t warp = threadIdx.x >> 5;
+    // Work split.  Normally one warp owns a tile for all of K.  When the tile count leaves the last round
+    // of warps badly filled, two warps of a CTA share a tile instead, each taking half of K (partial sums
+    // meet in shared memory): the granule halves, so the rounding loss of the last round halves too.
+    const uint32_t r4 = (total + gridDim.x * 4u - 1u) / (gridDim.x * 4u);
+    const uint32_t r2 = (total + gridDim.x * 2u - 1u) / (gridDim.x * 2u);
+    const bool ksplit = (steps % 2u == 0u) && (steps >= 4u) && (r2 * 10u <= r4 * 18u);   // >= 10 % fewer rounds
+    const uint32_t W = ksplit ? gridDim.x * 2u : gridDim.x * 4u;
     const uint32_t rounds = (total + W - 1u) / W;
     const uint32_t W_eff = (total + rounds - 1u) / rounds;
-    const uint32_t wid = blockIdx.x * 4u + (threadIdx.x >> 5);
-    if (wid >= W_eff) return;
-    const uint32_t steps = K / 128u;
+    const uint32_t wid = ksplit ? blockIdx.x * 2u + (warp >> 1) : blockIdx.x * 4u + warp;
+    const uint32_t khalf = ksplit ? (warp & 1u) : 0u;
+    if (wid >= W_eff) return;     // both warps of a pair leave together
+    const uint32_t kb_begin = ksplit ? khalf * (steps / 2u) : 0u;
+    const uint32_t kb_end = ksplit ? kb_begin + steps / 2u : steps;
+    __shared__ float xch[2][32][NT * 8];
     bool bad = false;
     const __half* bh_base = reinterpret_cast<const __half*>(DUAL ? a.x_hi : a.act_hi);
     const __half* bl_base = reinterpret_cast<const __half*>(DUAL ? a.x_lo : a.act_lo);
@@ -240,20 +251,45 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
                 for (int j = 0; j < 4; ++j) acc0[nt][j] = acc1[nt][j] = 0.0f;
 
             Fp4Load A0, A1, B0, B1;  // current and next step of the two streams
-            fp4_load<FMT>(p0, 0, A0);
-            fp4_load<FMT>(p1, 0, A1);
-            for (uint32_t kb = 0; kb < steps; kb += 2u) {
-                const uint32_t k1 = kb + 1u < steps ? kb + 1u : kb;
+            fp4_load<FMT>(p0, kb_begin, A0);
+            fp4_load<FMT>(p1, kb_begin, A1);
+            for (uint32_t kb = kb_begin; kb < kb_end; kb += 2u) {
+                const uint32_t k1 = kb + 1u < kb_end ? kb + 1u : kb;
                 fp4_load<FMT>(p0, k1, B0);
                 fp4_load<FMT>(p1, k1, B1);
                 fp4_step<FMT, NT, SPLIT>(A0, A1, p0, p1, xh, xl, valid, kb, t, acc0, acc1);
-                const uint32_t k2 = kb + 2u < steps ? kb + 2u : kb;
+                const uint32_t k2 = kb + 2u < kb_end ? kb + 2u : kb;
                 fp4_load<FMT>(p0, k2, A0);
                 fp4_load<FMT>(p1, k2, A1);
-                if (kb + 1u < steps)
+                if (kb + 1u < kb_end)
                     fp4_step<FMT, NT, SPLIT>(B0, B1, p0, p1, xh, xl, valid, kb + 1u, t, acc0, acc1);
             }
 
+            if (ksplit) {   // the upper-half warp hands its partial sums to its partner
+                float* slot = xch[warp >> 1][lane];
+                const uint32_t bar_id = 1u + (warp >> 1);
+                if (khalf == 1u) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            slot[nt * 8 + j] = acc0[nt][j];
+                            slot[nt * 8 + 4 + j] = acc1[nt][j];
+                        }
+                }
+                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+                if (khalf == 0u) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc0[nt][j] += slot[nt * 8 + j];
+                            acc1[nt][j] += slot[nt * 8 + 4 + j];
+                        }
+                }
+                asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");   // the slot may be rewritten after this
+                if (khalf == 1u) continue;                                    // only the lower half writes results
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
