@@ -7,6 +7,8 @@
 // a discontinuous function of the logits, so reproducing the order is what makes them
 // bit-identical to the reference's.  For the same reason the scores use an expf that follows
 // the host libm's algorithm step by step in double precision (see expf_libm below).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "libm_exact.cuh"
 
@@ -103,6 +105,55 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
         if (lane == 0 && (uint32_t)tok < nt) logits[(size_t)(t0 + tok) * E + e] = v;
+    }
+}
+
+// A single token (decode): the projection is a latency problem -- E rows of H BF16 values, a few bytes each
+// per lane.  One warp owns an expert row and issues ALL of its loads before the first use (lane l reads
+// its own columns l, l + 32, ... directly, 64 contiguous bytes per warp load), so the row costs one trip
+// to HBM instead of one per 256-column chunk; the activations of the few tokens come from L1/L2.
+// Same per-lane order and the same shuffle tree as the kernels above.
+constexpr int kTinyCols = 112;   // columns per lane held in registers at once (H <= 3584 in one pass)
+
+template <int TT>
+__global__ void __launch_bounds__(64) router_logits_tiny_kernel(const __nv_bfloat16* __restrict__ x,
+                                                                const __nv_bfloat16* __restrict__ wg, uint32_t T,
+                                                                uint32_t H, uint32_t E, float* __restrict__ logits) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t e = blockIdx.x * 2u + warp;
+    if (e >= E) return;
+    const unsigned short* wrow = reinterpret_cast<const unsigned short*>(wg) + (size_t)e * H + lane;
+    const unsigned short* xb = reinterpret_cast<const unsigned short*>(x) + lane;
+    const uint32_t per_lane = H / 32u;
+    float sum[TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) sum[i] = 0.0f;
+    for (uint32_t j0 = 0; j0 < per_lane; j0 += kTinyCols) {
+        float w[kTinyCols];
+#pragma unroll
+        for (int j = 0; j < kTinyCols; ++j)
+            w[j] = j0 + j < per_lane ? __uint_as_float((uint32_t)__ldg(wrow + (size_t)(j0 + j) * 32u) << 16) : 0.0f;
+#pragma unroll
+        for (int tok = 0; tok < TT; ++tok) {
+            if ((uint32_t)tok >= T) continue;   // uniform over the grid
+            const unsigned short* xr = xb + (size_t)tok * H + (size_t)j0 * 32u;
+            float s = sum[tok];
+#pragma unroll
+            for (int j = 0; j < kTinyCols; ++j) {
+                if (j0 + j < per_lane) {    // past the row's end nothing is added (not even +0)
+                    const float xv = __uint_as_float((uint32_t)__ldg(xr + (size_t)j * 32u) << 16);
+                    s = __fmaf_rn(xv, w[j], s);
+                }
+            }
+            sum[tok] = s;
+        }
+    }
+#pragma unroll
+    for (int tok = 0; tok < TT; ++tok) {
+        float v = sum[tok];
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
+        if (lane == 0 && (uint32_t)tok < T) logits[(size_t)tok * E + e] = v;
     }
 }
 
@@ -240,7 +291,11 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
     // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
     // many tokens: register-blocked kernel (4 rows per warp, 32 rows per CTA)
     const size_t big_tiles = (size_t)((T + 15) / 16) * ((E + 31) / 32);
-    if (T <= 8) {
+    if (T == 1 && !getenv("STRATA_MOE_NO_TINY_ROUTER")) {
+        // a single token: 10 vs 20 us at E = 256, H = 3072; with more tokens the staged kernel wins (the
+        // per-token scalar activation loads of this kernel cost 33 us at 2 tokens, 88 us at 8)
+        router_logits_tiny_kernel<2><<<(E + 1) / 2, 64, 0, s>>>(x, wg, T, H, E, logits);   // the 2-token build is the faster one even for one token (10 vs 31 us)
+    } else if (T <= 8) {
         dim3 grid((E + 1) / 2, 1);
         router_logits_kernel<2, 8><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
     } else if (T <= 32) {
