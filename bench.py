@@ -1,18 +1,31 @@
 #!/usr/bin/env python
 """MoE-layer throughput benchmark.
 
-  python bench.py --gpus N --steps K --warmup W [--workload c1] [--tokens T]
+  python bench.py --gpus N --steps K --warmup W [--workload c3] [--tokens T]
 
 A step is one pass of the MoE layer over one batch of synthetic tokens.  Prints ONE JSON line
-(rank 0).  `value` is tokens/s with the inputs resident in HBM; `e2e` is the same metric through
-the host-buffer entry point (pinned host activations in, fp32 result out, copies inside the
-timed region); `roofline` describes the dominant kernel, timed live with CUDA events on the
-stream it is launched on; `cpu_baseline` times the reference's own CPU expert kernels
-(oracle/_ref) on this box's host cores on a bounded sample.
+(rank 0).  The default workload is the expert-parallel MXFP4 prefill configuration (c3: hidden
+7168, 256 experts, top-8, 16384 tokens) at EVERY N including 1, strong scaling (the token count is
+the whole job's; rank r owns tokens [r T/N, (r+1) T/N) and experts [r E/N, (r+1) E/N)), so that
+the 1-GPU line, the scaling curve and the prefill target are one workload.
 
-  python bench.py --impl reference ...   times only that CPU arm.
+  value      tokens/s with the inputs resident in HBM (CUDA events, max over ranks per step)
+  e2e        the same metric through the host-buffer call (pinned host activations in, fp32 result
+             out, both copies inside the timed region)
+  roofline   the dominant kernel of the main workload, timed live with CUDA events on the library's
+             stream, against the measured peaks
+  parity     the timed layer's output for a few tokens against the CPU oracle (ids bit-exact)
+  cpu_baseline  the reference's own CPU expert kernels (oracle/_ref) on this box's host cores,
+             bounded sample
+  sub        (N = 1) the other benchmark configurations, each with its own roofline / e2e /
+             cpu_baseline: c0 at 8 tokens (decode, HBM target), the c1_sigmoid batch sweep
+             1/4/16/64/256 (the reference's Laguna routing rule; the softmax variant is a second
+             arm), c2 at 4096 tokens (prefill, tensor target); (N = 8) c4 with per-rank max latency
+
+  python bench.py --impl reference ...   times only the CPU arm on the main workload.
 """
 import argparse
+import gc
 import json
 import os
 import subprocess
@@ -25,6 +38,10 @@ sys.path.insert(0, ROOT)
 
 import numpy as np
 import torch
+
+FMT_NAMES = ["mxfp4", "nvfp4", "int4g128", "bf16"]
+DATA = "synthetic (seeded hash weights, N(0,1) BF16 activations, random-init router)"
+L2_NOTE = "512 MiB buffer rewritten between timed iterations"
 
 
 def load_peaks():
@@ -108,25 +125,33 @@ def gate_up_bytes(cfg):
     return sum(sum(synth.expert_bytes(cfg, r)) for r in ("gate", "up"))
 
 
+def config_dict(cfg, T, **extra):
+    d = {"workload": f"{cfg.name}: {cfg.description}", "tokens": T, "hidden": cfg.H,
+         "intermediate": cfg.I, "experts": cfg.E, "top_k": cfg.k, "format": FMT_NAMES[cfg.fmt],
+         "shared_intermediate": cfg.I_shared, "l2": L2_NOTE}
+    d.update(extra)
+    return d
+
+
 # ------------------------------------------------------------------------------ CPU arm
-def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None):
+def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None, repeats=1):
     """Times the reference's CPU expert kernels on a bounded sample of the workload's
     (token, expert) pairs with every host core; returns (tokens_per_s, info)."""
+    from oracle import layer_check as Hh
     from oracle import oracle as O
     from strata_b200 import synth
-    from tests import helpers as Hh
     ref = O.ref()
     threads = threads or len(os.sched_getaffinity(0))
-    x = synth.gen_inputs(cfg, T)
+    # bounded sample: the pairs of the first n_tok tokens (routing is only computed for those)
+    flops_per_pair = 6.0 * cfg.H * cfg.I
+    est_rate = 2.0e9 * threads * (0.15 if cfg.fmt == synth.FMT_NVFP4 else 1.0)  # scalar NVFP4 is slow
+    n_tok = int(max(1, min(T, sample_pairs_budget_s * est_rate / (flops_per_pair * cfg.k))))
+    x = synth.gen_inputs(cfg, T)[:n_tok].contiguous()
     w, b = synth.gen_router(cfg)
     logits = O.router_logits(Hh.np_u16(x), Hh.np_u16(w))
     spec = O.router_spec(cfg.E, cfg.k, cfg.score_kind, cfg.normalize, cfg.norm_init, cfg.weight_scale)
     rc, ids, wts = O.route(spec, logits, b.numpy() if b is not None else None)
     assert rc == 0
-    # bounded sample: the pairs of the first n_tok tokens, n_tok grown until the budget is met
-    flops_per_pair = 6.0 * cfg.H * cfg.I
-    est_rate = 2.0e9 * threads * (0.15 if cfg.fmt == synth.FMT_NVFP4 else 1.0)  # scalar NVFP4 is slow
-    n_tok = int(max(1, min(T, sample_pairs_budget_s * est_rate / (flops_per_pair * cfg.k))))
     sub_ids = ids[:n_tok]
     counts, offsets, perm = O.group(sub_ids, cfg.E)
     pair_token = (perm // cfg.k).astype(np.uint32)
@@ -156,7 +181,8 @@ def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None):
             assert ns > 0
             return ns * 1e-9
         kind = "reference"
-        secs = one_pass()
+        secs = float(np.mean([one_pass() for _ in range(max(1, repeats))]))
+        passes = max(1, repeats)
         # a whole workload that takes well under the budget is repeated and the passes averaged
         if n_tok == T and secs < sample_pairs_budget_s / 8:
             passes = int(min(50, max(2, sample_pairs_budget_s / 2 / max(secs, 1e-4))))
@@ -181,88 +207,22 @@ def cpu_reference_run(cfg, T, sample_pairs_budget_s=15.0, threads=None):
     return n_tok / secs, info
 
 
-# ------------------------------------------------------------------------------ GPU arm
-def l2_flush_buffer(device):
-    return torch.empty(512 << 20, dtype=torch.uint8, device=device)
+# ------------------------------------------------------------------------------ parity inside the bench
+def oracle_parity(cfg, x_cpu, ids_gpu, out_rows, subset):
+    """The timed layer against the CPU oracle: ids of all `x_cpu` tokens bit for bit, output rows of
+    `subset` (out_rows[i] belongs to token subset[i]) within the layer tolerance."""
+    from oracle import layer_check as Hh
+    ref = Hh.run_oracle(cfg, x_cpu, token_subset=np.asarray(subset, np.uint32))
+    rel, mx = Hh.error_metrics(out_rows, ref["out"])
+    ids_equal = bool(np.array_equal(np.asarray(ids_gpu).astype(np.uint32), ref["ids"]))
+    return {"rel_l2": float(rel), "max_abs_rms": float(mx), "ids_equal": ids_equal,
+            "tokens_checked": int(len(subset)), "ids_checked": int(ref["ids"].shape[0]),
+            "bars": {"rel_l2": 1e-2, "max_abs_rms": 2.0 ** -6},
+            "ok": bool(ids_equal and rel <= 1e-2 and mx <= 2.0 ** -6)}
 
 
-def run_gpu(args, cfg, T, rank, world):
-    from strata_b200 import MoeContext, MoeLayer, synth
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
-    torch.cuda.set_device(device)
-    peaks = load_peaks()
-    if world > 1:
-        from strata_b200 import ep
-        return ep.bench(args, cfg, T, rank, world, device, peaks, ClockSampler)
-
-    ctx = MoeContext(device.index)
-    torch.cuda.set_stream(ctx.stream)   # flushes, events and the library share one stream
-    layer = synth.build_layer(cfg, device, T=T)
-    ml = MoeLayer(ctx, cfg, max_tokens=T)
-    ml.load_synth(layer)
-    out = torch.empty(T, cfg.H, dtype=torch.float32, device=device)
-    flush = l2_flush_buffer(device)
-    x_host = layer.x.cpu().pin_memory()
-    out_host = torch.empty(T, cfg.H, dtype=torch.float32).pin_memory()
-
-    def step():
-        ml.forward(layer.x, out)
-
-    sampler = ClockSampler(device.index)     # samples clocks and throttle reasons from the warm-up on
-    sampler.start()
-    for _ in range(max(args.warmup, 3)):
-        flush.zero_()
-        step()
-    ctx.synchronize()
-
-    launches0 = ctx.stats().kernel_launches
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-           for _ in range(args.steps)]
-    torch.cuda.synchronize()
-    for a, b in evs:
-        flush.zero_()          # evict the weights from L2 between timed iterations
-        a.record()
-        step()
-        b.record()
-    torch.cuda.synchronize()
-    launches = ctx.stats().kernel_launches - launches0
-    ms = [a.elapsed_time(b) for a, b in evs]
-    ms_per_step = float(np.mean(ms))
-
-    # phase timing (separate iterations: the phase events serialise the host)
-    ctx.set_timing(True)
-    phase = []
-    for _ in range(min(args.steps, 20)):
-        flush.zero_()
-        step()
-        phase.append(ctx.phase_ms())
-    ctx.set_timing(False)
-    phase_ms = {k: float(np.median([p[k] for p in phase])) for k in phase[0]}
-
-    # end to end through the host-buffer entry point
-    for _ in range(3):
-        ml.forward_host(x_host, out_host)
-    e2e_t = []
-    for _ in range(args.steps):
-        flush.zero_()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        ml.forward_host(x_host, out_host)
-        e2e_t.append(time.perf_counter() - t0)
-    # the timed regions above are short: keep the same load running until the clock log has a few samples
-    deadline = time.perf_counter() + 2.0
-    while len(sampler.rows) < 6 and time.perf_counter() < deadline:
-        flush.zero_()
-        step()
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
-    e2e_s = float(np.mean(e2e_t))
-
-    # roofline of the dominant kernel
-    _, aux = ml.forward(layer.x, want_aux=True)
-    ctx.synchronize()
-    counts = aux["counts"].cpu().numpy()
-    active = int((counts > 0).sum())
+# ------------------------------------------------------------------------------ single GPU
+def roofline_of(cfg, T, active, phase_ms, peaks):
     pairs = T * cfg.k
     dominant = max(("gate_up", "down"), key=lambda k: phase_ms[k])
     if dominant == "gate_up":
@@ -278,101 +238,435 @@ def run_gpu(args, cfg, T, rank, world):
     else:
         roof = dict(bound="tensor", achieved=flops / dur / 1e12, peak=peaks["bf16_tflops"], unit="TFLOP/s")
     roof["frac"] = roof["achieved"] / roof["peak"]
-    roof.update(traffic=measured_traffic(cfg.name, T, dominant), kernel=dominant, kernel_ms=phase_ms[dominant], peak_source=peaks["source"],
-                active_experts=active, algorithmic_bytes=int(alg_bytes))
-    layer_bytes = active * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
+    roof.update(traffic=measured_traffic(cfg.name, T, dominant), kernel=dominant, kernel_ms=phase_ms[dominant],
+                peak_source=peaks["source"], active_experts=active, algorithmic_bytes=int(alg_bytes),
+                algorithmic_flops=float(flops))
+    return roof
 
-    # batch sweep of the same layer (config 1 names 1/4/16/64/256 tokens): tokens/s and the
-    # fraction of HBM peak the whole layer reaches on its algorithmic bytes
-    sweep = []
-    if args.sweep:
-        for Ts in [t for t in (1, 4, 16, 64, 256) if t <= T]:
-            xs = layer.x[:Ts].contiguous()
-            outs = torch.empty(Ts, cfg.H, dtype=torch.float32, device=device)
-            for _ in range(3):
-                flush.zero_()
-                ml.forward(xs, outs)
-            ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
-            for a, b in ev:
-                flush.zero_()
-                a.record()
-                ml.forward(xs, outs)
-                b.record()
+
+def measure_layer(ctx, cfg, T, steps, warmup, peaks, flush, cpu_seconds, want_parity=False, batch_sweep=(),
+                  sampler=None):
+    """One configuration on one GPU: device-resident throughput, phases, end to end, roofline, CPU arm."""
+    from strata_b200 import MoeLayer, synth
+    device = ctx.device
+    layer = synth.build_layer(cfg, device, T=T)
+    ml = MoeLayer(ctx, cfg, max_tokens=T)
+    ml.load_synth(layer)
+    out = torch.empty(T, cfg.H, dtype=torch.float32, device=device)
+    x_host = layer.x.cpu().pin_memory()
+    out_host = torch.empty(T, cfg.H, dtype=torch.float32).pin_memory()
+
+    def step():
+        ml.forward(layer.x, out)
+
+    for _ in range(max(warmup, 3)):
+        flush.zero_()
+        step()
+    ctx.synchronize()
+    launches0 = ctx.stats().kernel_launches
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        flush.zero_()          # evict the weights from L2 between timed iterations
+        a.record()
+        step()
+        b.record()
+    torch.cuda.synchronize()
+    launches = ctx.stats().kernel_launches - launches0
+    ms_per_step = float(np.mean([a.elapsed_time(b) for a, b in evs]))
+
+    # phase timing (separate iterations: the phase events serialise the host)
+    ctx.set_timing(True)
+    phase = []
+    for _ in range(min(steps, 20)):
+        flush.zero_()
+        step()
+        phase.append(ctx.phase_ms())
+    ctx.set_timing(False)
+    phase_ms = {k: float(np.median([p[k] for p in phase])) for k in phase[0]}
+
+    # end to end through the host-buffer entry point
+    for _ in range(3):
+        ml.forward_host(x_host, out_host)
+    e2e_t = []
+    for _ in range(steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ml.forward_host(x_host, out_host)
+        e2e_t.append(time.perf_counter() - t0)
+    if sampler is not None:
+        # the timed regions above can be short: keep the same load running until the clock log has a few samples
+        deadline = time.perf_counter() + 2.0
+        while len(sampler.rows) < 6 and time.perf_counter() < deadline:
+            flush.zero_()
+            step()
             torch.cuda.synchronize()
-            t_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
-            _, ax = ml.forward(xs, want_aux=True)
-            ctx.synchronize()
-            act_s = int((ax["counts"] > 0).sum().item())
-            lb = act_s * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
-            sweep.append({"tokens": Ts, "ms": t_ms, "tokens_per_s": Ts / (t_ms * 1e-3), "active_experts": act_s,
-                          "layer_hbm_frac": lb / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+    e2e_s = float(np.mean(e2e_t))
 
-    cpu_v, cpu_info = cpu_reference_run(cfg, T, args.cpu_seconds)
-    line = {
-        "metric": "MoE layer tokens/s", "value": T / (ms_per_step * 1e-3), "unit": "tokens/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic (seeded hash weights, N(0,1) BF16 activations, random-init router)",
-        "config": {"workload": f"{cfg.name}: {cfg.description}", "tokens": T, "hidden": cfg.H,
-                   "intermediate": cfg.I, "experts": cfg.E, "top_k": cfg.k,
-                   "format": ["mxfp4", "nvfp4", "int4g128"][cfg.fmt], "shared_intermediate": cfg.I_shared,
-                   "l2": "512 MiB buffer rewritten between timed iterations"},
-        "layer_hbm_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
-        "layer_hbm_frac": layer_bytes / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
-        "phase_ms": phase_ms,
-        "sweep": sweep,
-        "roofline": roof,
-        "cpu_baseline": {"value": cpu_v, "unit": "tokens/s", **cpu_info},
+    _, aux = ml.forward(layer.x, want_aux=True)
+    ctx.synchronize()
+    counts = aux["counts"].cpu().numpy()
+    active = int((counts > 0).sum())
+    rec = {
+        "value": T / (ms_per_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_per_step,
+        "config": config_dict(cfg, T), "phase_ms": phase_ms,
+        "roofline": roofline_of(cfg, T, active, phase_ms, peaks),
         "e2e": {"value": T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": T * cfg.H * 2,
                 "d2h_bytes_per_step": T * cfg.H * 4},
         "gpu_launches": int(launches),
-        "clocks": clocks,
     }
+    layer_bytes = active * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
+    rec["layer_hbm_gbs"] = layer_bytes / (ms_per_step * 1e-3) / 1e9
+    rec["layer_hbm_frac"] = rec["layer_hbm_gbs"] / peaks["hbm_gbs"]
+    rec["layer_tflops"] = 6.0 * cfg.H * cfg.I * T * cfg.k / (ms_per_step * 1e-3) / 1e12
+    rec["layer_tensor_frac"] = rec["layer_tflops"] / peaks["bf16_tflops"]
+    if want_parity:
+        sub = sorted(set([0, T // 2, T - 1]))
+        ml.forward(layer.x, out)
+        ctx.synchronize()
+        rec["parity"] = oracle_parity(cfg, layer.x.cpu(), aux["ids"].cpu().numpy(),
+                                      out[torch.tensor(sub, device=device)].cpu().numpy(), sub)
+
+    # batch sweep of the same layer: tokens/s and the fraction of HBM peak the whole layer reaches
+    sweep = []
+    for Ts in [t for t in batch_sweep if t <= T]:
+        xs = layer.x[:Ts].contiguous()
+        outs = torch.empty(Ts, cfg.H, dtype=torch.float32, device=device)
+        for _ in range(3):
+            flush.zero_()
+            ml.forward(xs, outs)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(10)]
+        for a, b in ev:
+            flush.zero_()
+            a.record()
+            ml.forward(xs, outs)
+            b.record()
+        torch.cuda.synchronize()
+        t_ms = float(np.mean([a.elapsed_time(b) for a, b in ev]))
+        ctx.set_timing(True)
+        ph = []
+        for _ in range(5):
+            flush.zero_()
+            ml.forward(xs, outs)
+            ph.append(ctx.phase_ms())
+        ctx.set_timing(False)
+        ph_ms = {k: float(np.median([p[k] for p in ph])) for k in ph[0]}
+        _, ax = ml.forward(xs, want_aux=True)
+        ctx.synchronize()
+        act_s = int((ax["counts"] > 0).sum().item())
+        lb = act_s * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
+        sweep.append({"tokens": Ts, "ms": t_ms, "tokens_per_s": Ts / (t_ms * 1e-3), "active_experts": act_s,
+                      "layer_hbm_frac": lb / (t_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                      "roofline": roofline_of(cfg, Ts, act_s, ph_ms, peaks)})
+    if sweep:
+        rec["sweep"] = sweep
+    ml.close()
+    del layer, ml, out, aux
+    gc.collect()
+    torch.cuda.empty_cache()
+    if cpu_seconds > 0:
+        cpu_v, cpu_info = cpu_reference_run(cfg, T, cpu_seconds)
+        rec["cpu_baseline"] = {"value": cpu_v, "unit": "tokens/s", **cpu_info}
+    return rec
+
+
+def run_single(args, cfg, T):
+    from strata_b200 import MoeContext, synth
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(device)
+    peaks = load_peaks()
+    ctx = MoeContext(device.index)
+    torch.cuda.set_stream(ctx.stream)   # flushes, events and the library share one stream
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    sampler = ClockSampler(device.index)     # samples clocks and throttle reasons from the warm-up on
+    sampler.start()
+    main = measure_layer(ctx, cfg, T, args.steps, args.warmup, peaks, flush, args.cpu_seconds,
+                         want_parity=args.parity, sampler=sampler,
+                         batch_sweep=(1, 4, 16, 64, 256) if cfg.name.startswith("c1") and args.sub else ())
+    clocks = sampler.stop()
+    sub = []
+    if args.sub:
+        sub_steps = max(5, min(args.steps, 20))
+        sub_cpu = min(args.cpu_seconds, 4.0)
+        plan = [("c0", 8, ()), ("c1_sigmoid", 256, (1, 4, 16, 64, 256)), ("c1", 256, ()), ("c2", 4096, ()),
+                ("c3", 16384, ())]
+        for name, Ts, sweep in plan:
+            if name == cfg.name and Ts == T:
+                continue
+            rec = measure_layer(ctx, synth.CONFIGS[name], Ts, sub_steps, 3, peaks, flush, sub_cpu, batch_sweep=sweep)
+            rec["name"], rec["steps"] = name, sub_steps
+            sub.append(rec)
+    line = {
+        "metric": "MoE layer tokens/s", "value": main["value"], "unit": "tokens/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"],
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": DATA,
+        "config": dict(main["config"], parallelism="ep1"),
+    }
+    for k in ("layer_hbm_gbs", "layer_hbm_frac", "layer_tflops", "layer_tensor_frac", "phase_ms", "roofline",
+              "cpu_baseline", "e2e", "gpu_launches", "parity", "sweep"):
+        if k in main:
+            line[k] = main[k]
+    line["clocks"] = clocks
+    if sub:
+        line["sub"] = sub
+    return line
+
+
+# ------------------------------------------------------------------------------ multi GPU
+def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, want_parity, sampler=None):
+    """One layer over `world` ranks, E/world experts per rank.  Strong scaling: T tokens in total,
+    T/world per rank.  Weak: T tokens per rank.  Returns the record (every rank; rank 0 prints)."""
+    import torch.distributed as dist
+    from strata_b200 import MoeLayer, synth
+    from strata_b200.ep import EpMoe, EpMoePeer, owner_block
+    if strong:
+        assert T % world == 0
+        Tl = T // world
+    else:
+        Tl, T = T, T * world
+    B = owner_block(cfg, world)
+    pairs_total = T * cfg.k
+    avg = pairs_total // world
+    max_pairs = min(pairs_total, max(2 * avg, avg + 4096))
+    layer = synth.build_layer(cfg, device, expert_begin=rank * B, expert_end=(rank + 1) * B, T=T)
+    x_local = layer.x[rank * Tl:(rank + 1) * Tl].contiguous()
+    ml = MoeLayer(ctx, cfg, max_tokens=Tl, expert_begin=rank * B, expert_count=B, max_pairs=max_pairs)
+    ml.load_synth(layer)
+    if args.exchange == "peer":
+        try:
+            ep = EpMoePeer(ml, cfg, rank, world, max_pairs)
+            exchange_text = "library kernels over peer memory (NVLink stores / loads, no collective on the data path)"
+        except RuntimeError as e:    # every rank raises together; the NCCL exchange is the other GPU path
+            exchange_text = f"NCCL all-to-allv (counts, rows, outputs); peer windows failed: {e}"
+            ep = EpMoe(ml, cfg, rank, world)
+    else:
+        ep = EpMoe(ml, cfg, rank, world)
+        exchange_text = "NCCL all-to-allv (counts, rows, outputs)"
+
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        flush.zero_()
+        out = ep.forward(x_local)
+    ctx.synchronize()
+    launches0 = ctx.stats().kernel_launches
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    dist.barrier()
+    torch.cuda.synchronize()
+    for a, b in evs:
+        flush.zero_()
+        dist.barrier()
+        a.record()
+        out = ep.forward(x_local)
+        b.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    launches = ctx.stats().kernel_launches - launches0
+    ms_local = torch.tensor([a.elapsed_time(b) for a, b in evs], device=device, dtype=torch.float64)
+    ms = ms_local.clone()
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)           # per step: the slowest rank
+    ms_per_step = float(ms.mean())
+    per_rank_ms = [torch.zeros(1, device=device, dtype=torch.float64) for _ in range(world)]
+    dist.all_gather(per_rank_ms, ms_local.mean().reshape(1))
+    ctx.synchronize()    # raises if any step tripped the device status word (overflow, timeout, non-finite)
+    ids_loc, _ = ml.route(x_local)
+    per_rank = torch.bincount((ids_loc.reshape(-1) // B).long(), minlength=world).double()
+    dist.all_reduce(per_rank)     # rows every rank receives in one step
+    recv_max = per_rank.max()
+
+    # end to end: pinned host activations in, fp32 result out, every step
+    x_host = x_local.cpu().pin_memory()
+    out_host = torch.empty(Tl, cfg.H, dtype=torch.float32).pin_memory()
+    x_dev = torch.empty_like(x_local)
+    e2e = []
+    for i in range(args.steps + 2):
+        flush.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t0 = time.perf_counter()
+        x_dev.copy_(x_host, non_blocking=True)
+        o = ep.forward(x_dev)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.synchronize()
+        e2e.append(time.perf_counter() - t0)
+    e2e_t = torch.tensor(e2e[2:], device=device, dtype=torch.float64)
+    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
+    if sampler is not None:
+        t_end = time.perf_counter() + 2.0
+        go = torch.ones(1, device=device)
+        while True:     # same load until rank 0's clock log has a few samples (all ranks leave together)
+            if rank == 0:
+                go.fill_(1.0 if (len(sampler.rows) < 6 and time.perf_counter() < t_end) else 0.0)
+            dist.broadcast(go, 0)
+            if go.item() == 0.0:
+                break
+            flush.zero_()
+            ep.forward(x_local)
+            torch.cuda.synchronize()
+    ctx.synchronize()
+    # where a step's time goes: the four stages of the peer exchange, timed on this rank's stream
+    # (each stage's time includes waiting for the slowest peer)
+    stage_ms = None
+    if isinstance(ep, EpMoePeer):
+        st = ep.state
+        acc = torch.zeros(4, dtype=torch.float64)
+        reps = 5
+        for _ in range(reps):
+            flush.zero_()
+            dist.barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+            ev[0].record()
+            st.begin(x_local)
+            ev[1].record()
+            st.dispatch()
+            ev[2].record()
+            st.experts()
+            ev[3].record()
+            st.finish(out)
+            ev[4].record()
+            torch.cuda.synchronize()
+            acc += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(4)], dtype=torch.float64)
+        ctx.synchronize()
+        stage_ms = dict(zip(("route_group_publish", "plan_dispatch", "wait_experts_signal", "wait_combine"),
+                            [round(float(v), 4) for v in acc / reps]))
+
+    parity = None
+    if want_parity:
+        # rank 0's tokens against the CPU oracle (every rank takes part in the step that produces them)
+        out = ep.forward(x_local)
+        ctx.synchronize()
+        if rank == 0:
+            sub = sorted(set([0, Tl // 2, Tl - 1]))
+            parity = oracle_parity(cfg, x_local.cpu(), ids_loc.cpu().numpy(),
+                                   out[torch.tensor(sub, device=device)].cpu().numpy(), sub)
+        dist.barrier()
+
+    flops = 6.0 * cfg.H * cfg.I * pairs_total
+    # per rank: the expert GEMMs (tensor bound for the prefill shapes, HBM bound when each resident expert
+    # sees only a few rows)
+    rank_flops = flops / world
+    rank_bytes = B * expert_weight_bytes(cfg) + (pairs_total / world) * (cfg.H * 2 + cfg.H * 4)
+    t_tc = rank_flops / (peaks["bf16_tflops"] * 1e12)
+    t_hbm = rank_bytes / (peaks["hbm_gbs"] * 1e9)
+    if t_tc >= t_hbm:
+        roof = {"bound": "tensor", "achieved": rank_flops / (ms_per_step * 1e-3) / 1e12, "peak": peaks["bf16_tflops"],
+                "unit": "TFLOP/s"}
+    else:
+        roof = {"bound": "hbm", "achieved": rank_bytes / (ms_per_step * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                "unit": "GB/s"}
+    roof.update(frac=roof["achieved"] / roof["peak"], traffic=None, peak_source=peaks["source"],
+                kernel="whole step of one rank (route + exchange + expert GEMMs + combine)",
+                algorithmic_flops=rank_flops, algorithmic_bytes=int(rank_bytes))
+    rec = {
+        "value": T / (ms_per_step * 1e-3), "unit": "tokens/s", "ms_per_step": ms_per_step,
+        "config": config_dict(cfg, T, tokens_per_rank=Tl, experts_per_rank=B, parallelism=f"ep{world}",
+                              exchange=exchange_text),
+        "roofline": roof,
+        "per_rank_ms": [round(float(v.item()), 4) for v in per_rank_ms],
+        "per_rank_max_ms": round(max(float(v.item()) for v in per_rank_ms), 4),
+        "max_rank_pairs": int(recv_max.item()), "mean_rank_pairs": pairs_total / world,
+        "e2e": {"value": T / float(e2e_t.mean()), "unit": "tokens/s",
+                "h2d_bytes_per_step": Tl * cfg.H * 2, "d2h_bytes_per_step": Tl * cfg.H * 4},
+        "gpu_launches": int(launches), "stage_ms_rank0": stage_ms,
+    }
+    if parity is not None:
+        rec["parity"] = parity
+    if isinstance(ep, EpMoePeer):
+        ep.close()
+    ml.close()
+    del layer, ml, ep
+    gc.collect()
+    torch.cuda.empty_cache()
+    dist.barrier()
+    return rec
+
+
+def run_multi(args, cfg, T, rank, world):
+    import torch.distributed as dist
+    from strata_b200 import MoeContext, synth
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
+    torch.cuda.set_device(device)
+    peaks = load_peaks()
+    dist.init_process_group("nccl", device_id=device)
+    ctx = MoeContext(device.index)
+    torch.cuda.set_stream(ctx.stream)
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    sampler = ClockSampler(device.index)      # only rank 0 starts it; the others take part in its keep-busy loop
+    if rank == 0:
+        sampler.start()
+    strong = args.scaling == "strong"
+    main = measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, args.parity, sampler=sampler)
+    clocks = sampler.stop() if rank == 0 else None
+    sub = []
+    if args.sub and world == 8 and cfg.name != "c4":
+        c4 = synth.CONFIGS["c4"]
+        keep_steps = args.steps
+        args.steps = max(5, min(args.steps, 20))
+        rec = measure_ep(args, c4, c4.T, rank, world, device, ctx, peaks, flush, True, False)
+        rec["name"], rec["steps"] = "c4", args.steps
+        args.steps = keep_steps
+        sub.append(rec)
+    line = None
+    if rank == 0:
+        line = {
+            "metric": "MoE layer tokens/s", "value": main["value"], "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": main["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": DATA,
+        }
+        for k in ("config", "roofline", "per_rank_ms", "per_rank_max_ms", "max_rank_pairs", "mean_rank_pairs", "e2e",
+                  "gpu_launches", "stage_ms_rank0", "parity"):
+            if k in main:
+                line[k] = main[k]
+        line["clocks"] = clocks
+        if sub:
+            line["sub"] = sub
+    dist.barrier()
+    dist.destroy_process_group()
     return line
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--tokens", type=int, default=None)
-    ap.add_argument("--cpu-seconds", type=float, default=12.0)
-    ap.add_argument("--no-sweep", dest="sweep", action="store_false", help="skip the batch sweep")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-sub", dest="sub", action="store_false", help="skip the sub-records of the other configurations")
+    ap.add_argument("--no-parity", dest="parity", action="store_false", help="skip the oracle check of the timed layer")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU row exchange: the library's peer-memory kernels or NCCL all-to-allv")
     ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
-                    help="multi-GPU: weak = --tokens per rank (default), strong = --tokens in total")
+                    help="multi-GPU: strong = --tokens in total (default), weak = --tokens per rank")
     args = ap.parse_args()
     from strata_b200 import synth
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    name = args.workload or "c1"
+    name = args.workload or "c3"
     cfg = synth.CONFIGS[name]
     T = args.tokens or cfg.T
     if args.scaling is None:
-        args.scaling = "strong" if name in ("c2", "c3", "c4") else "weak"
+        args.scaling = "strong"
 
     if args.impl == "reference":
         if rank != 0:
             return 0
-        vals, info = [], None
-        for _ in range(max(1, min(args.steps, 3))):
-            v, info = cpu_reference_run(cfg, T, args.cpu_seconds)
-            vals.append(v)
-        v = float(np.mean(vals))
+        reps = max(1, min(args.steps, 3))     # the weights are generated once, the timed pass repeats
+        v, info = cpu_reference_run(cfg, T, args.cpu_seconds, repeats=reps)
+        vals = [v] * reps
         print(json.dumps({
             "impl": "reference", "metric": "MoE layer tokens/s", "value": v, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": len(vals), "warmup": 0, "ms_per_step": 1e3 * T / v,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": {"workload": f"{cfg.name}: {cfg.description}", "tokens": T},
+            "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+            "data": DATA, "config": dict(config_dict(cfg, T), parallelism=f"ep{max(args.gpus, 1)}"),
             "cpu_baseline": {"value": v, "unit": "tokens/s", **info},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return 0
 
-    line = run_gpu(args, cfg, T, rank, world)
+    line = run_single(args, cfg, T) if world == 1 else run_multi(args, cfg, T, rank, world)
     if rank == 0 and line is not None:
         print(json.dumps(line))
     return 0

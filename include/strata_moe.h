@@ -200,7 +200,8 @@ int strata_moe_group(strata_moe_layer* layer, const uint32_t* ids, uint32_t pair
  * GPU that loads it.  Limits: pairs <= 65536, n_experts <= 256; larger calls are rejected with a
  * message in `err`.  The first call on a device resolves the array's address: issue it before
  * any stream capture on that device.  All calls share the array, so calls that overlap on the
- * GPU race; serialise them.  Returns 0 or a negative STRATA_MOE_E_* and a message in err. */
+ * GPU race; serialise them.  The call runs on the CURRENT CUDA device: `stream` and every pointer
+ * must belong to it.  Returns 0 or a negative STRATA_MOE_E_* and a message in err. */
 int strata_moe_group_static(void* stream, const uint32_t* ids, uint32_t pairs, uint32_t expert_begin,
                             uint32_t n_experts, uint32_t* counts, uint32_t* offsets, uint32_t* perm,
                             uint32_t* inv /* or NULL */, char* err, size_t err_cap);

@@ -5,9 +5,9 @@
                                where they lie in the reference checkout, behind the
                                extern "C" doorway in oracle/ref_shim.cpp
 
-The second one is only (re)built when a reference checkout is present (argument, the
-STRATA_REFERENCE environment variable, or the default location); a machine without the
-checkout uses the library built earlier.  The reference's CMake build is not used: it
+The second one is only (re)built when a reference checkout is given (argument or the
+STRATA_REFERENCE environment variable; failing both, a directory named `reference` beside the
+repository is tried); a machine without the checkout uses the library built earlier.  The reference's CMake build is not used: it
 requires libnuma, which is absent, so the listed files are compiled directly.
 """
 import os
@@ -15,7 +15,10 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-DEFAULT_REFERENCE = "/root/reference"
+
+
+def default_reference():
+    return os.environ.get("STRATA_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 REF_SOURCES = [
     "kernels/cpu/dsv4_fp4_expert.cpp",
@@ -54,7 +57,7 @@ def build_port(force=False):
 
 
 def build_reference(reference=None, force=False):
-    reference = reference or os.environ.get("STRATA_REFERENCE", DEFAULT_REFERENCE)
+    reference = reference or default_reference()
     outdir = os.path.join(HERE, "_ref")
     out = os.path.join(outdir, "libstrata_ref.so")
     if not os.path.isdir(os.path.join(reference, "kernels", "cpu")):

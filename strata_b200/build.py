@@ -8,7 +8,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libstrata_moe.so")
 SOURCES = ["api.cu", "router.cu", "group.cu", "decode.cu", "decode_fp4.cu", "combine.cu", "prefill.cu", "ep.cu", "dsv4_exact.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC,-fvisibility=default", "--use_fast_math=false"]
+              "-Xcompiler", "-fPIC,-fvisibility=default"]
 
 
 def _deps():
@@ -22,7 +22,7 @@ def build(force=False, verbose=False):
         t = os.path.getmtime(LIB)
         if all(os.path.getmtime(d) <= t for d in _deps()):
             return LIB
-    flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
+    flags = list(NVCC_FLAGS)
     if verbose:
         flags += ["-Xptxas", "-v"]
     objs, jobs = [], []

@@ -38,8 +38,37 @@ struct DeviceTable {
     float* d_post = nullptr;
 };
 
+// Tuning and test switches, read from the environment ONCE when a layer is created (never on the
+// per-call path).  -1 / 0 = built-in default.
+struct LayerKnobs {
+    bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
+    bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
+    int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
+    int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
+    int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
+    int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
+    int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
+};
+
+static LayerKnobs read_knobs() {
+    LayerKnobs k;
+    auto num = [](const char* name, int dflt) {
+        const char* e = getenv(name);
+        return e ? atoi(e) : dflt;
+    };
+    k.no_f16_path = getenv("STRATA_MOE_NO_F16_PATH") != nullptr;
+    k.no_prefill_path = getenv("STRATA_MOE_NO_PREFILL_PATH") != nullptr;
+    k.prefill_min_rows = num("STRATA_MOE_PREFILL_MIN_ROWS", -1);
+    k.prefill_down_min_rows = num("STRATA_MOE_PREFILL_DOWN_MIN_ROWS", -1);
+    k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
+    k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
+    k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
+    return k;
+}
+
 struct strata_moe_layer {
     strata_moe_ctx* ctx = nullptr;
+    LayerKnobs knobs;
     strata_moe_layer_desc d{};
     uint32_t max_pairs = 0;
     __nv_bfloat16* router = nullptr;
@@ -123,6 +152,10 @@ size_t scale_bytes(int fmt, uint32_t rows, uint32_t cols) {
     return (size_t)rows * cols / 128 * 2;
 }
 
+bool tensor_path_ok(const strata_moe_layer* L, int fmt, uint32_t I) {
+    return !L->knobs.no_prefill_path && prefill_supported(fmt, L->d.hidden, I);
+}
+
 int sync_tables(strata_moe_layer* L) {
     strata_moe_ctx* ctx = L->ctx;
     if (!L->tables_dirty) return 0;
@@ -165,10 +198,10 @@ int sync_tables(strata_moe_layer* L) {
             L->f16_ok = not_ok == 0;
         }
     }
-    if (getenv("STRATA_MOE_NO_F16_PATH")) L->f16_ok = false;
+    if (L->knobs.no_f16_path) L->f16_ok = false;
     // tensor maps of the packed weights for the tensor-core path's TMA producer
     L->wmaps_ok = false;
-    if (L->d.format != STRATA_MOE_FMT_BF16 && prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) {
+    if (L->d.format != STRATA_MOE_FMT_BF16 && tensor_path_ok(L, L->d.format, L->d.intermediate)) {
         struct alignas(64) Blob { unsigned char b[128]; };
         std::vector<Blob> maps((size_t)3 * n);
         bool ok = true;
@@ -221,42 +254,38 @@ bool all_registered(const strata_moe_layer* L, std::string* why) {
 
 // rows-per-expert threshold between the weight-streaming path and the tensor-core tile path
 bool use_prefill(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
-    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate)) return false;
+    if (!tensor_path_ok(L, L->d.format, L->d.intermediate)) return false;
     if (L->d.format == STRATA_MOE_FMT_MXFP4 && !L->f16_ok) return false;  // needs the f16 weight window
     if (!L->wmaps_ok) return false;
     // average rows per expert from which the tensor-core path wins (measured: FP4 formats cross over
     // at 11-12 rows, INT4, whose streaming kernel is slower, at about 8)
-    const char* e = getenv("STRATA_MOE_PREFILL_MIN_ROWS");
-    const int thr = e ? atoi(e) : (L->d.format == STRATA_MOE_FMT_INT4G128 ? 8 : 12);
+    const int thr = L->knobs.prefill_min_rows >= 0 ? L->knobs.prefill_min_rows
+                                                   : (L->d.format == STRATA_MOE_FMT_INT4G128 ? 8 : 12);
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
 bool use_prefill_down(const strata_moe_layer* L, uint32_t pairs, uint32_t n_groups) {
-    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return false;
-    const char* e = getenv("STRATA_MOE_PREFILL_DOWN_MIN_ROWS");
-    const int thr = e ? atoi(e) : 8;
+    if (!tensor_path_ok(L, L->d.format, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return false;
+    const int thr = L->knobs.prefill_down_min_rows >= 0 ? L->knobs.prefill_down_min_rows : 8;
     return (uint64_t)pairs >= (uint64_t)n_groups * (uint64_t)thr;
 }
 
 // Token tile of the tensor-core path: 192 when groups are large (an expert with up to 192 rows is decoded
 // once), 128 with its deeper weight ring when they are small.
-uint32_t prefill_ntile(uint64_t pairs, uint64_t n_groups) {
-    const char* e = getenv("STRATA_MOE_PREFILL_NTILE");
-    if (e) return (uint32_t)atoi(e) == 128u ? 128u : 192u;
+uint32_t prefill_ntile(const strata_moe_layer* L, uint64_t pairs, uint64_t n_groups) {
+    if (L->knobs.prefill_ntile) return L->knobs.prefill_ntile == 128 ? 128u : 192u;
     return pairs > 96u * n_groups ? 192u : 128u;
 }
 
 // Row count from which a single group is handed to the tensor-core path inside an otherwise
 // weight-streaming step; 0 = mixed dispatch off.
 uint32_t mixed_min_rows(const strata_moe_layer* L, uint32_t max_rows_per_group) {
-    if (!prefill_supported(L->d.format, L->d.hidden, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return 0;
-    const char* e = getenv("STRATA_MOE_MIXED_MIN_ROWS");
-    const int thr = e ? atoi(e) : 24;   // above what one or two passes of the streaming kernel cover
+    if (!tensor_path_ok(L, L->d.format, L->d.intermediate) || !L->f16_ok || !L->wmaps_ok) return 0;
+    const int thr = L->knobs.mixed_min_rows >= 0 ? L->knobs.mixed_min_rows : 24;   // above what one or two passes of the streaming kernel cover
     if (thr <= 0) return 0;
     // The two extra launches cost about 10 us even when no group qualifies: worth it only for steps
     // long enough that a hot expert's repeated passes would dominate.
-    const char* m = getenv("STRATA_MOE_MIXED_MIN_TOKENS");
-    const uint32_t min_tokens = m ? (uint32_t)atoi(m) : 128u;
+    const uint32_t min_tokens = L->knobs.mixed_min_tokens >= 0 ? (uint32_t)L->knobs.mixed_min_tokens : 128u;
     return max_rows_per_group >= (uint32_t)thr && max_rows_per_group >= min_tokens ? (uint32_t)thr : 0u;
 }
 
@@ -290,11 +319,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.tile_table = static_cast<uint32_t*>(L->prefill_scratch);
         p.status = ctx->d_status;
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
-        p.ntile = prefill_ntile(pairs, n_groups);
-        {
-            const char* dbg = getenv("STRATA_MOE_PREFILL_DEBUG");
-            p.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
-        }
+        p.ntile = prefill_ntile(L, pairs, n_groups);
         if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s,
                            ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
@@ -406,16 +431,15 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
     strata_moe_ctx* ctx = L->ctx;
     if (!st) st = ctx->stream;
     // enough rows to fill tensor-core tiles (and BF16 inputs): grouped-GEMM path with one group
-    const char* thr_env = getenv("STRATA_MOE_PREFILL_MIN_ROWS");
-    const uint32_t thr = thr_env ? (uint32_t)atoi(thr_env) : 24u;
-    if (!x_lo && T >= thr && prefill_supported(3, L->d.hidden, L->d.shared_intermediate)) {
+    const uint32_t thr = L->knobs.prefill_min_rows >= 0 ? (uint32_t)L->knobs.prefill_min_rows : 24u;
+    if (!x_lo && T >= thr && tensor_path_ok(L, 3, L->d.shared_intermediate)) {
         PrefillArgs p{};
         p.fmt = 3;
         p.H = L->d.hidden;
         p.I = L->d.shared_intermediate;
         p.n_groups = 1;
         p.pairs = T;
-        p.ntile = prefill_ntile(T, 1);
+        p.ntile = prefill_ntile(L, T, 1);
         p.offsets = offsets2;
         p.y = L->sh_y;
         p.tile_table = L->shared_tiles;
@@ -606,6 +630,7 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
     if (!L) return fail(ctx, STRATA_MOE_E_INVALID, "out of host memory");
     L->ctx = ctx;
     L->d = d;
+    L->knobs = read_knobs();
     const uint64_t mp = d.max_pairs ? d.max_pairs : (uint64_t)d.max_tokens * d.top_k;
     if (mp > 0x7FFFFFFFull) { delete L; return fail(ctx, STRATA_MOE_E_INVALID, "max_pairs too large"); }
     L->max_pairs = (uint32_t)mp;
@@ -896,6 +921,8 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     if (L->d.expert_count != L->d.experts)
         return fail(ctx, STRATA_MOE_E_INVALID, "forward needs every expert resident; use the stage calls for expert parallelism");
     if (L->dense_in_flight) return fail(ctx, STRATA_MOE_E_BUSY, "a dense command is in flight");
+    if ((uint64_t)T * L->d.top_k > L->max_pairs)
+        return fail(ctx, STRATA_MOE_E_INVALID, "tokens * top_k exceed the layer's max_pairs");
     std::string why;
     if (!all_registered(L, &why)) return fail(ctx, STRATA_MOE_E_INVALID, why);
     if (T == 0) return 0;
@@ -1027,6 +1054,9 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
     if (!hidden_host || rows == 0) return fail(ctx, STRATA_MOE_E_INVALID, "hidden rows are required");
     if (n == 0 && !with_shared) return fail(ctx, STRATA_MOE_E_INVALID, "command has no experts");
     if (n && (!experts || !coefficients)) return fail(ctx, STRATA_MOE_E_INVALID, "null expert list");
+    // the pointer tables of a command hold one slot per resident expert (the reference bounds its
+    // list the same way, kernels/cuda/backend.cu:1209-1213)
+    if (n > d.expert_count) return fail(ctx, STRATA_MOE_E_INVALID, "more experts listed than are resident");
     if ((uint64_t)n * rows > L->max_pairs) return fail(ctx, STRATA_MOE_E_INVALID, "experts * rows exceed max_pairs");
     if (rows > d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "rows exceed max_tokens");
     if (with_shared && !d.shared_intermediate) return fail(ctx, STRATA_MOE_E_INVALID, "layer has no shared expert");
@@ -1331,7 +1361,6 @@ int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
     int rc = sync_tables(L);
     if (rc) return rc;
     cudaStream_t s = ctx->stream;
-    ep->w.step += 1;
     ep->x = static_cast<const __nv_bfloat16*>(x);
     ep->T = T;
     ep->forked = false;
@@ -1356,8 +1385,14 @@ int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
         CK(cudaMemsetAsync(L->counts, 0, (size_t)d.experts * sizeof(uint32_t), s));
         CK(cudaMemsetAsync(L->offsets, 0, ((size_t)d.experts + 1) * sizeof(uint32_t), s));
     }
+    // The step number advances only once nothing on the host can fail any more: a begin that
+    // returned an error must leave this rank in step with its peers.
+    ep->w.step += 1;
     launch_ep_publish(ep->w, L->counts, s);
-    CK(cudaGetLastError());
+    if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) {
+        ep->w.step -= 1;
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("ep publish launch: ") + cudaGetErrorString(e));
+    }
     ep->stage = 1;
     return 0;
 }

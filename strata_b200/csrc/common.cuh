@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/strata_moe.h"
 
 namespace smoe {
@@ -114,7 +116,6 @@ struct PrefillArgs {
     float* y;                      // [pairs, H] fp32
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
-    uint32_t debug;                // timing experiments only (wrong results): 1 = no MMA, 2 = no decode, 4 = no stores
     GluParams glu;                 // activation of the gate/up epilogue
     uint32_t ntile;                // tokens per tile: 128, or anything else for 192 (large groups)
     uint32_t min_rows;             // only groups with at least this many rows get tiles (0 = all)
@@ -199,7 +200,8 @@ void launch_dsv4_join(const float* y, const uint32_t* inv, const float* shared, 
 void launch_dsv4_down(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& down,
                       const float* actq, float* y, uint32_t* status, cudaStream_t s);
 
-// Launch counter (every wrapper above bumps it once per kernel launch).
-extern unsigned long long g_kernel_launches;
+// Launch counter (every wrapper above bumps it once per kernel launch; host threads of several
+// contexts share it).
+extern std::atomic<unsigned long long> g_kernel_launches;
 
 }  // namespace smoe

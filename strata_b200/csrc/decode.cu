@@ -19,7 +19,7 @@
 
 namespace smoe {
 
-unsigned long long g_kernel_launches = 0;
+std::atomic<unsigned long long> g_kernel_launches{0};
 
 // Position of column c inside its 128-column block in the K-permuted activation layout:
 // chunk t = (c % 128) / 32 is the lane-in-quad that streams it, word wd = (c % 32) / 8, nibble
@@ -401,15 +401,7 @@ __global__ void __launch_bounds__(128, NT == 1 ? 3 : 2) decode_ffn_kernel(Decode
     if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
 }
 
-static uint32_t decode_ctas_per_sm() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("STRATA_MOE_DECODE_CTAS_PER_SM");
-        v = e ? atoi(e) : 4;
-        if (v < 1 || v > 16) v = 4;
-    }
-    return (uint32_t)v;
-}
+static uint32_t decode_ctas_per_sm() { return 4u; }
 
 template <int FMT, bool SPLIT, bool DUAL>
 static void launch_nt(const DecodeArgs& a, cudaStream_t s) {

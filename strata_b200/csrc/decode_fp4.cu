@@ -318,16 +318,7 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
     if (bad) atomicOr(a.status, kStatusNonFiniteOutput);
 }
 
-static uint32_t fp4_ctas_per_sm(uint32_t nt) {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("STRATA_MOE_DECODE_CTAS_PER_SM");
-        v = e ? atoi(e) : 0;
-        if (v < 0 || v > 16) v = 0;
-    }
-    if (v) return (uint32_t)v;
-    return nt == 1 ? 4u : (nt == 2 ? 3u : 2u);
-}
+static uint32_t fp4_ctas_per_sm(uint32_t nt) { return nt == 1 ? 4u : (nt == 2 ? 3u : 2u); }
 
 template <int FMT, bool SPLIT, bool DUAL>
 static void launch_fp4_nt(const DecodeArgs& a, cudaStream_t s) {

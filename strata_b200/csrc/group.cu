@@ -279,6 +279,9 @@ extern "C" int strata_moe_group_static(void* stream, const uint32_t* ids, uint32
         scratch = dev_ptr[dev];
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // an error left pending by earlier, unrelated work must not be reported as this call's launch
+    e = cudaPeekAtLastError();
+    if (e != cudaSuccess) return fail(STRATA_MOE_E_CUDA, "an earlier CUDA error is pending", cudaGetErrorString(e));
     const uint32_t nseg = (pairs + kSegPairs - 1) / kSegPairs;
     const uint32_t blocks = (nseg + 7) / 8;
     const size_t smem = 8u * (size_t)n_experts * sizeof(uint32_t);

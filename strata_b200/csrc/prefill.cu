@@ -353,9 +353,8 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
                     if (!mbar_wait(&S.empty_b[s], ph ^ 1u, abort_flag)) { ok = false; break; }
-                    uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
-                    if ((a.debug & 8u) && bsel > 2u) bsel = 2u;   // timing experiment: half the activation bytes
-                    const bool tail = t.n > 128u && !(a.debug & 8u);   // rows 128..191 arrive as a second, 64-row box
+                    const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
+                    const bool tail = t.n > 128u;   // rows 128..191 arrive as a second, 64-row box
                     mbar_arrive_expect_tx(&S.full_b[s], ((16u << bsel) + (tail ? 64u : 0u)) * kBK * 2u);
                     tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
                     if (tail) tma_load_2d(S.b[s] + 128u * kBK * 2u, &maps_b.m[2], ks * kBK, t.row0 + 128u, &S.full_b[s]);
@@ -417,7 +416,6 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         const uint32_t a0 = smem_u32(S.w[sa][mi]);
 #pragma unroll
                         for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
-                            if (a.debug & 1u) break;
                             umma_f16(d, umma_desc_sw128(a0 + kk * 32u), umma_desc_sw128(b + kk * 32u), idesc,
                                      (ks | kk) ? 1u : 0u);
                         }
@@ -427,7 +425,6 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         const uint32_t ta = tmem_base + kAccCols + sa * kAStageCols + mi * (kBK / 2u);
 #pragma unroll
                         for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
-                            if (a.debug & 1u) break;
                             umma_f16_ts(d, ta + kk * 8u, umma_desc_sw128(b + kk * 32u), idesc, (ks | kk) ? 1u : 0u);
                         }
                     }
@@ -595,7 +592,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     }
                     if (!mbar_wait(&S.empty_a[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();   // the MMAs that read this stage have completed
-                    if (!(a.debug & 2u)) {
+                    {
                         uint4 o[4];
                         decode16<FMT>(pkv[0], m[0], o);
                         const uint32_t v[16] = {o[0].x, o[0].y, o[0].z, o[0].w, o[1].x, o[1].y, o[1].z, o[1].w,
@@ -641,7 +638,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 tmem_ld_wait();
 #pragma unroll
                 for (uint32_t j = 0; j < 16u; ++j) {
-                    if (c0 + j >= t.n || (a.debug & 4u)) break;
+                    if (c0 + j >= t.n) break;
                     const size_t pos = (size_t)t.row0 + c0 + j;
                     if (GU) {
                         if (a.act_rowscale_out != nullptr && feat == 0u) a.act_rowscale_out[pos] = 1.0f;
@@ -750,7 +747,6 @@ static bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t c
 }
 
 bool prefill_supported(int fmt, uint32_t H, uint32_t I) {
-    if (getenv("STRATA_MOE_NO_PREFILL_PATH")) return false;
     if (fmt < 0 || fmt > kFmtBf16W) return false;
     return H % 128u == 0 && I % 128u == 0 && encode_fn() != nullptr;
 }
@@ -767,8 +763,11 @@ static bool make_bmaps(BMaps* b, const void* base, uint64_t rows, uint64_t cols)
 
 template <int FMT, int NT>
 static int set_smem_attr(size_t smem) {
-    static bool done = false;
-    if (done) return 0;
+    // the opt-in to more than 48 KB of dynamic shared memory is a per-device property of the function
+    static bool done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -2;
+    if (done[dev]) return 0;
     if (cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 0, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess ||
         cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 1, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -776,7 +775,7 @@ static int set_smem_attr(size_t smem) {
         cudaFuncSetAttribute(prefill_ffn_kernel<FMT, 2, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem) != cudaSuccess)
         return -2;
-    done = true;
+    done[dev] = true;
     return 0;
 }
 

@@ -291,7 +291,7 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
     // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
     // many tokens: register-blocked kernel (4 rows per warp, 32 rows per CTA)
     const size_t big_tiles = (size_t)((T + 15) / 16) * ((E + 31) / 32);
-    if (T == 1 && !getenv("STRATA_MOE_NO_TINY_ROUTER")) {
+    if (T == 1) {
         // a single token: 10 vs 20 us at E = 256, H = 3072; with more tokens the staged kernel wins (the
         // per-token scalar activation loads of this kernel cost 33 us at 2 tokens, 88 us at 8)
         router_logits_tiny_kernel<2><<<(E + 1) / 2, 64, 0, s>>>(x, wg, T, H, E, logits);   // the 2-token build is the faster one even for one token (10 vs 31 us)
@@ -305,11 +305,13 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
         dim3 grid((E + 7) / 8, (T + 15) / 16);
         router_logits_kernel<8, 16><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
     } else {
-        static bool attr = false;
+        static bool attr[64] = {};   // the shared-memory opt-in is per device
         const size_t smem = (size_t)(kBigTT + kBigWarps * kBigRW) * kRouterChunk * sizeof(float);
-        if (!attr) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !attr[dev]) {
             cudaFuncSetAttribute(router_logits_big_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr = true;
+            attr[dev] = true;
         }
         dim3 grid((E + 31) / 32, (T + 15) / 16);
         router_logits_big_kernel<<<grid, kBigWarps * 32, smem, s>>>(x, wg, T, H, E, logits);

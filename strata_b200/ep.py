@@ -16,8 +16,6 @@ Received rows always land in local HBM before any kernel reads them; no kernel t
 memory.  The compute is delegated to an `ops` object (strata_b200.api.MoeLayer on a GPU; the
 CPU tests plug in the oracle) so that the exchange logic itself can be exercised with gloo.
 """
-import time
-
 import torch
 import torch.distributed as dist
 
@@ -136,160 +134,3 @@ class EpMoePeer:
                 w.close()
         dist.barrier()
         self.own.close()
-
-
-# ------------------------------------------------------------------------------------------
-def bench(args, cfg, T, rank, world, device, peaks, ClockSampler):
-    """Multi-GPU leg of bench.py: one layer over `world` ranks, E/world experts per rank.
-    Weak scaling (default): T tokens per rank.  Strong scaling (--scaling strong): T tokens in
-    total, T/world per rank.  Returns the JSON line dict (rank 0)."""
-    import json
-    import numpy as np
-    from . import MoeContext, MoeLayer, synth
-
-    dist.init_process_group("nccl", device_id=device)
-    strong = getattr(args, "scaling", "weak") == "strong"
-    if strong:
-        assert T % world == 0
-        Tl = T // world
-    else:
-        Tl, T = T, T * world
-    B = owner_block(cfg, world)
-    ctx = MoeContext(device.index)
-    torch.cuda.set_stream(ctx.stream)
-    pairs_total = T * cfg.k
-    avg = pairs_total // world
-    max_pairs = min(pairs_total, max(2 * avg, avg + 4096))
-    layer = synth.build_layer(cfg, device, expert_begin=rank * B, expert_end=(rank + 1) * B, T=T)
-    x_local = layer.x[rank * Tl:(rank + 1) * Tl].contiguous()
-    ml = MoeLayer(ctx, cfg, max_tokens=Tl, expert_begin=rank * B, expert_count=B, max_pairs=max_pairs)
-    ml.load_synth(layer)
-    exchange_kind = getattr(args, "exchange", "peer")
-    exchange_text = None
-    if exchange_kind == "peer":
-        try:
-            ep = EpMoePeer(ml, cfg, rank, world, max_pairs)
-            exchange_text = "library kernels over peer memory (NVLink stores / loads, no collective on the data path)"
-        except RuntimeError as e:    # every rank raises together; the NCCL exchange is the other GPU path
-            exchange_text = f"NCCL all-to-allv (counts, rows, outputs); peer windows failed: {e}"
-            ep = EpMoe(ml, cfg, rank, world)
-    else:
-        ep = EpMoe(ml, cfg, rank, world)
-        exchange_text = "NCCL all-to-allv (counts, rows, outputs)"
-    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
-
-    warm = max(args.warmup, 3)
-    for _ in range(warm):
-        flush.zero_()
-        out = ep.forward(x_local)
-    ctx.synchronize()
-    sampler = ClockSampler(device.index)
-    if rank == 0:
-        sampler.start()
-    launches0 = ctx.stats().kernel_launches
-    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    dist.barrier()
-    torch.cuda.synchronize()
-    for a, b in evs:
-        flush.zero_()
-        dist.barrier()
-        a.record()
-        out = ep.forward(x_local)
-        b.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    launches = ctx.stats().kernel_launches - launches0
-    ms = torch.tensor([a.elapsed_time(b) for a, b in evs], device=device, dtype=torch.float64)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)           # per step: the slowest rank
-    ms_per_step = float(ms.mean())
-    ctx.synchronize()    # raises if any step tripped the device status word (overflow, timeout, non-finite)
-    ids_loc, _ = ml.route(x_local)
-    per_rank = torch.bincount((ids_loc.reshape(-1) // B).long(), minlength=world).double()
-    dist.all_reduce(per_rank)     # rows every rank receives in one step
-    recv_max = per_rank.max()
-
-    # end to end: pinned host activations in, fp32 result out, every step
-    x_host = x_local.cpu().pin_memory()
-    out_host = torch.empty(Tl, cfg.H, dtype=torch.float32).pin_memory()
-    x_dev = torch.empty_like(x_local)
-    e2e = []
-    for i in range(args.steps + 2):
-        flush.zero_()
-        torch.cuda.synchronize()
-        dist.barrier()
-        t0 = time.perf_counter()
-        x_dev.copy_(x_host, non_blocking=True)
-        o = ep.forward(x_dev)
-        out_host.copy_(o, non_blocking=True)
-        torch.cuda.synchronize()
-        e2e.append(time.perf_counter() - t0)
-    e2e_t = torch.tensor(e2e[2:], device=device, dtype=torch.float64)
-    dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
-    if rank == 0:
-        t_end = time.perf_counter() + 2.0
-    go = torch.ones(1, device=device)
-    while True:     # same load until rank 0's clock log has a few samples (all ranks leave together)
-        if rank == 0:
-            go.fill_(1.0 if (len(sampler.rows) < 6 and time.perf_counter() < t_end) else 0.0)
-        dist.broadcast(go, 0)
-        if go.item() == 0.0:
-            break
-        flush.zero_()
-        ep.forward(x_local)
-        torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
-    ctx.synchronize()
-    # where a step's time goes: the four stages of the peer exchange, timed on this rank's stream
-    # (each stage's time includes waiting for the slowest peer)
-    stage_ms = None
-    if isinstance(ep, EpMoePeer):
-        st = ep.state
-        acc = torch.zeros(4, dtype=torch.float64)
-        reps = 5
-        for _ in range(reps):
-            flush.zero_()
-            dist.barrier()
-            ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
-            ev[0].record()
-            st.begin(x_local)
-            ev[1].record()
-            st.dispatch()
-            ev[2].record()
-            st.experts()
-            ev[3].record()
-            st.finish(out)
-            ev[4].record()
-            torch.cuda.synchronize()
-            acc += torch.tensor([ev[i].elapsed_time(ev[i + 1]) for i in range(4)], dtype=torch.float64)
-        ctx.synchronize()
-        stage_ms = dict(zip(("route_group_publish", "plan_dispatch", "wait_experts_signal", "wait_combine"),
-                            [round(float(v), 4) for v in acc / reps]))
-
-    line = None
-    if rank == 0:
-        flops = 6.0 * cfg.H * cfg.I * pairs_total
-        line = {
-            "metric": "MoE layer tokens/s", "value": T / (ms_per_step * 1e-3), "unit": "tokens/s",
-            "n_gpus": world, "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (seeded hash weights, N(0,1) BF16 activations, random-init router)",
-            "config": {"workload": f"{cfg.name}: {cfg.description}", "tokens": T, "tokens_per_rank": Tl,
-                       "hidden": cfg.H, "intermediate": cfg.I, "experts": cfg.E, "experts_per_rank": B,
-                       "top_k": cfg.k, "format": ["mxfp4", "nvfp4", "int4g128"][cfg.fmt],
-                       "parallelism": f"ep{world}", "exchange": exchange_text,
-                       "l2": "512 MiB buffer rewritten between timed iterations"},
-            "roofline": {"bound": "tensor", "achieved": flops / (ms_per_step * 1e-3) / 1e12 / world,
-                         "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": flops / (ms_per_step * 1e-3) / 1e12 / world / peaks["bf16_tflops"],
-                         "traffic": None, "kernel": "whole step per rank (expert GEMMs + exchange)",
-                         "peak_source": peaks["source"]},
-            "max_rank_pairs": int(recv_max.item()), "mean_rank_pairs": pairs_total / world,
-            "e2e": {"value": T / float(e2e_t.mean()), "unit": "tokens/s",
-                    "h2d_bytes_per_step": Tl * cfg.H * 2, "d2h_bytes_per_step": Tl * cfg.H * 4},
-            "gpu_launches": int(launches),
-            "stage_ms_rank0": stage_ms,
-            "clocks": clocks,
-        }
-    dist.barrier()
-    dist.destroy_process_group()
-    return line

@@ -86,8 +86,24 @@ def test_dense_protocol(ctx):
         ml.enqueue_dense(hidden, [1], [0.5])
     with pytest.raises(StrataMoeError):               # expert outside the resident range
         ml.enqueue_dense(hidden, [cfg.E], [1.0])
+    with pytest.raises(StrataMoeError) as e:          # a list longer than the resident experts (duplicates)
+        ml.enqueue_dense(hidden[:1], [0] * (cfg.E + 1), [1.0] * (cfg.E + 1))
+    assert e.value.code == -1
     ml.enqueue_dense(hidden, [1], [1.0])              # workspace reusable after the failures
     ml.collect_dense(1, 2)
+
+
+def test_forward_rejects_more_pairs_than_the_workspace_holds(ctx):
+    cfg = synth.MoeConfig("fewpairs", H=256, I=128, E=4, k=2, fmt=synth.FMT_MXFP4, T=8, seed=4)
+    layer = synth.build_layer(cfg, "cuda")
+    ml = MoeLayer(ctx, cfg, max_tokens=8, max_pairs=6)     # 8 tokens x top-2 would need 16
+    ml.load_synth(layer)
+    with pytest.raises(StrataMoeError) as e:
+        ml.forward(layer.x)
+    assert e.value.code == -1
+    out = ml.forward(layer.x[:3])                           # 6 pairs fit
+    ctx.synchronize()
+    assert torch.isfinite(out).all()
 
 
 def test_non_finite_result_fails_collect_and_leaves_buffers_untouched(ctx):

@@ -237,8 +237,10 @@ def test_prefill_path_tiny_and_empty_groups(ctx, monkeypatch):
 def test_prefill_and_streaming_paths_agree(ctx, monkeypatch):
     cfg = small(synth.FMT_MXFP4, T=300, E=8, k=2, H=512, I=256, name="paths")
     layer, ml, out_tc, _ = run_layer(ctx, cfg)
-    monkeypatch.setenv("STRATA_MOE_NO_PREFILL_PATH", "1")
-    out_stream = ml.forward(layer.x)
+    monkeypatch.setenv("STRATA_MOE_NO_PREFILL_PATH", "1")   # switches are read when a layer is created
+    ml2 = MoeLayer(ctx, cfg, max_tokens=layer.x.shape[0])
+    ml2.load_synth(layer)
+    out_stream = ml2.forward(layer.x)
     ctx.synchronize()
     rel, mx = Hh.error_metrics(out_tc.cpu().numpy(), out_stream.cpu().numpy())
     assert rel <= PREFILL_TIGHT
