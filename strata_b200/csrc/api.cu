@@ -43,6 +43,7 @@ struct DeviceTable {
 struct LayerKnobs {
     bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
     bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
+    bool no_stream_ring = false;    // STRATA_MOE_NO_STREAM_RING: small batches use the register-streaming kernels
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
     int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
@@ -58,6 +59,7 @@ static LayerKnobs read_knobs() {
     };
     k.no_f16_path = getenv("STRATA_MOE_NO_F16_PATH") != nullptr;
     k.no_prefill_path = getenv("STRATA_MOE_NO_PREFILL_PATH") != nullptr;
+    k.no_stream_ring = getenv("STRATA_MOE_NO_STREAM_RING") != nullptr;
     k.prefill_min_rows = num("STRATA_MOE_PREFILL_MIN_ROWS", -1);
     k.prefill_down_min_rows = num("STRATA_MOE_PREFILL_DOWN_MIN_ROWS", -1);
     k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
@@ -98,6 +100,7 @@ struct strata_moe_layer {
     bool wmaps_ok = false;
     // f16 decode path for the FP4 formats
     bool f16_ok = false;
+    bool stream_ok = false;   // shapes and alignments allow the bulk-copy ring kernels
     uint32_t* d_not_ok = nullptr;
     float *act_f32 = nullptr, *x_rowscale = nullptr, *act_rowscale = nullptr;
     // dense command state
@@ -199,6 +202,12 @@ int sync_tables(strata_moe_layer* L) {
         }
     }
     if (L->knobs.no_f16_path) L->f16_ok = false;
+    // the bulk-copy ring needs 16-byte aligned packed rows and scale rows
+    L->stream_ok = L->f16_ok && !L->knobs.no_stream_ring &&
+                   decode_stream_supported(L->d.format, L->d.hidden, L->d.intermediate);
+    for (int r = 0; r < 3 && L->stream_ok; ++r)
+        for (uint32_t e = 0; e < n && L->stream_ok; ++e)
+            L->stream_ok = (((uintptr_t)L->tab[r].packed[e] | (uintptr_t)L->tab[r].scales[e]) & 15u) == 0;
     // tensor maps of the packed weights for the tensor-core path's TMA producer
     L->wmaps_ok = false;
     if (L->d.format != STRATA_MOE_FMT_BF16 && tensor_path_ok(L, L->d.format, L->d.intermediate)) {
@@ -380,7 +389,11 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         a.skip_from = big;
         launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
-        launch_decode_fp4_gate_up(a, s);
+        if (L->stream_ok) {
+            if (launch_decode_stream_gate_up(a, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
+        } else {
+            launch_decode_fp4_gate_up(a, s);
+        }
         launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
                                L->act_rowscale, s, pairs_dev);
         if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
@@ -400,7 +413,11 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
             if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
         } else {
-            launch_decode_fp4_down(a, s);
+            if (L->stream_ok) {
+                if (launch_decode_stream_down(a, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
+            } else {
+                launch_decode_fp4_down(a, s);
+            }
             if (big) {
                 p.min_rows = big;
                 p.reuse_tiles = 1;   // same groups as the gate/up launch above

@@ -105,6 +105,10 @@ void launch_mx_scale_range(const uint8_t* const* scales, uint32_t n, size_t byte
                            float* post_scale, uint32_t* not_ok, cudaStream_t s);
 void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* scales, uint32_t emin,
                                float post_scale, uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
+// decode_stream.cu : the same two GEMMs with the weights streamed through a shared-memory ring by bulk copies
+bool decode_stream_supported(int fmt, uint32_t H, uint32_t I);
+int launch_decode_stream_gate_up(const DecodeArgs& a, cudaStream_t s);
+int launch_decode_stream_down(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_down(const DecodeArgs& a, cudaStream_t s);
 // prefill.cu : large-batch expert FFN (tcgen05 grouped GEMM path)

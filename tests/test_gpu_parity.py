@@ -55,6 +55,12 @@ SMALL_CASES = [
     small(synth.FMT_NVFP4, T=80, E=8, k=2, activation=1, gate_beta=1.5, linear_beta=2.0, I_shared=128, name="situ_tensor"),
     small(synth.FMT_INT4, T=5, activation=1, gate_beta=3.0, linear_beta=3.0, name="situ_int4"),
     small(synth.FMT_BF16, T=40, E=8, k=2, name="plain_bf16_rows"),
+    # shapes the bulk-copy ring kernels accept (MXFP4 needs K % 512 == 0 on both GEMMs, NVFP4 K % 256 == 0)
+    small(synth.FMT_MXFP4, I=512, name="ring_mx"),
+    small(synth.FMT_MXFP4, I=512, T=13, name="ring_mx_two_token_tiles"),
+    small(synth.FMT_MXFP4, H=1024, I=512, T=23, E=4, k=2, name="ring_mx_passes"),
+    small(synth.FMT_NVFP4, H=768, I=256, T=11, E=8, k=2, name="ring_nv_short_last_stage"),
+    small(synth.FMT_MXFP4, H=1536, I=1024, T=5, E=8, k=3, name="ring_mx_three_stages"),
 ]
 
 
@@ -244,6 +250,20 @@ def test_prefill_and_streaming_paths_agree(ctx, monkeypatch):
     ctx.synchronize()
     rel, mx = Hh.error_metrics(out_tc.cpu().numpy(), out_stream.cpu().numpy())
     assert rel <= PREFILL_TIGHT
+
+
+@pytest.mark.parametrize("fmt", [synth.FMT_MXFP4, synth.FMT_NVFP4])
+def test_ring_and_register_streaming_kernels_agree(ctx, fmt, monkeypatch):
+    # the same small batch through the bulk-copy ring kernels and through the register-streaming ones
+    cfg = small(fmt, H=1024, I=512, T=9, E=8, k=3, name=f"ring_vs_reg{fmt}")
+    layer, ml, out_ring, _ = run_layer(ctx, cfg)
+    monkeypatch.setenv("STRATA_MOE_NO_STREAM_RING", "1")   # switches are read when a layer is created
+    ml2 = MoeLayer(ctx, cfg, max_tokens=layer.x.shape[0])
+    ml2.load_synth(layer)
+    out_reg = ml2.forward(layer.x)
+    ctx.synchronize()
+    rel, mx = Hh.error_metrics(out_ring.cpu().numpy(), out_reg.cpu().numpy())
+    assert rel <= 1e-5, rel        # same products, different FP32 summation order
 
 
 def test_shared_expert_on_tensor_core_path(ctx):
