@@ -117,6 +117,10 @@ typedef struct strata_moe_stats {
     uint64_t h2d_bytes, d2h_bytes;
     uint64_t weight_bytes;    /* resident expert + router + shared bytes */
     float last_forward_ms;    /* CUDA-event time of the last forward when timing is on */
+    uint64_t router_fast_tokens;      /* tokens routed through the tensor-core projection + exact recheck */
+    uint64_t router_rechecked_tokens; /* of those, tokens recomputed completely by the canonical kernels */
+    uint64_t command_calls;           /* handle-based commands collected */
+    uint64_t workspace_allocations;   /* times a command had to (re)build its workspace */
 } strata_moe_stats;
 
 /* ---- context ------------------------------------------------------------------------
@@ -124,6 +128,9 @@ typedef struct strata_moe_stats {
  * kernels/cuda/backend.cu:5854-5895).  stream = an existing cudaStream_t to run on, or NULL
  * to create a non-blocking stream owned by the context. */
 int strata_moe_create(int device, void* stream, strata_moe_ctx** out);
+/* Number of CUDA devices this library can run on (compute capability 10.x), 0 when there is none.
+ * ref: CudaBackend::available_devices, include/strata/cuda_backend.hpp:783. */
+int strata_moe_device_count(void);
 void strata_moe_destroy(strata_moe_ctx* ctx);
 const char* strata_moe_last_error(const strata_moe_ctx* ctx);
 /* Waits for the stream, then reports and clears the device status word.
@@ -241,6 +248,65 @@ int strata_moe_enqueue_dense(strata_moe_layer* layer, const float* hidden_host, 
                              const uint32_t* experts, const float* coefficients, uint32_t n_experts,
                              int with_shared);
 int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, float* shared_output);
+
+/* ---- weight handles and handle-based commands: the reference backend's own call shape -----
+ * ref: CudaBackend::upload(device, CudaWeightDescriptor, weights, scales, CudaWeight&),
+ * include/strata/cuda_backend.hpp:819-823 (descriptor :41-51).  One uploaded matrix [rows, cols] in one
+ * of the STRATA_MOE_FMT_* encodings, or FP8 E4M3 with one E8M0 scale per 128 x 128 block
+ * (STRATA_MOE_FMT_FP8B128: weights u8 [rows, cols], scales u8 [ceil(rows/128), ceil(cols/128)];
+ * ref: CudaWeightEncoding::Fp8E4m3Block128, the DeepSeek-V4 shared expert).  The bytes are copied
+ * to the device; the handle owns them until strata_moe_weight_release. */
+#define STRATA_MOE_FMT_FP8B128 4
+typedef struct strata_moe_weight strata_moe_weight;
+typedef struct strata_moe_weight_desc {
+    int32_t format;      /* STRATA_MOE_FMT_* */
+    uint32_t rows, cols;
+    float global_scale;  /* NVFP4 divisor, 1 otherwise */
+} strata_moe_weight_desc;
+int strata_moe_weight_upload(strata_moe_ctx* ctx, const strata_moe_weight_desc* desc, const void* weights_host,
+                             size_t weight_bytes, const void* scales_host, size_t scale_bytes,
+                             strata_moe_weight** out);
+void strata_moe_weight_release(strata_moe_weight* w);
+/* ref: struct CudaMoeExpert, include/strata/cuda_backend.hpp:740-745. */
+typedef struct strata_moe_expert_ref {
+    const strata_moe_weight* gate; /* [I, H] */
+    const strata_moe_weight* up;   /* [I, H] */
+    const strata_moe_weight* down; /* [H, I] */
+    float coefficient;
+} strata_moe_expert_ref;
+/* ref: CudaBackend::enqueue_moe / collect_moe, include/strata/cuda_backend.hpp:1147-1153 and the
+ * validation in kernels/cuda/backend.cu:16003-16145.  Every routed expert (at most 10, plus the
+ * optional shared one) is applied to all `rows` fp32 rows of hidden_host; one encoding per
+ * command (INT4-g128, NVFP4 or plain BF16); the coefficient is folded before the down projection
+ * for INT4 and must be 1 otherwise and for the shared expert; non-finite hidden values are
+ * rejected.  One command may be in flight per context.  collect waits, checks the device status
+ * word and only then writes routed_out [n][rows][H] and shared_out [rows][H] (span sizes are
+ * checked); a failed collect leaves the buffers untouched and drains the command. */
+int strata_moe_command_enqueue(strata_moe_ctx* ctx, const float* hidden_host, size_t hidden_floats, uint32_t rows,
+                               const strata_moe_expert_ref* routed, uint32_t n_routed,
+                               const strata_moe_expert_ref* shared /* or NULL */);
+int strata_moe_command_collect(strata_moe_ctx* ctx, float* routed_out, size_t routed_floats, float* shared_out,
+                               size_t shared_floats);
+/* ref: struct CudaDeepSeekMoeRowGroup, include/strata/cuda_backend.hpp:724-736 (canonical w1/w3/w2 form). */
+typedef struct strata_moe_row_group {
+    const strata_moe_weight* w1; /* gate [I, H], MXFP4 encoding with DSV4 scale edges */
+    const strata_moe_weight* w3; /* up   [I, H] */
+    const strata_moe_weight* w2; /* down [H, I] */
+    const uint32_t* rows;        /* indices into the hidden rows this expert serves */
+    const float* coefficients;   /* that row's router coefficient, same order */
+    uint32_t n_rows;
+} strata_moe_row_group;
+/* ref: CudaBackend::enqueue_deepseek_moe_rows / collect_deepseek_moe_rows,
+ * include/strata/cuda_backend.hpp:1139-1146, kernels/cuda/backend.cu:15346-15996.  The row-grouped
+ * DSV4 command in the exact numerical mode described below; routed results are flattened group-major
+ * and, inside a group, in the group's own row order.  `shared` (FP8B128 weights, or NULL) runs over
+ * shared_rows and its results are flattened in that order. */
+int strata_moe_command_enqueue_rows_dsv4(strata_moe_ctx* ctx, const float* hidden_host, size_t hidden_floats,
+                                         uint32_t hidden_rows, const strata_moe_row_group* groups, uint32_t n_groups,
+                                         const strata_moe_expert_ref* shared, const uint32_t* shared_rows,
+                                         uint32_t n_shared_rows, float swiglu_limit);
+int strata_moe_command_collect_rows_dsv4(strata_moe_ctx* ctx, float* routed_out, size_t routed_floats,
+                                         float* shared_out, size_t shared_floats);
 
 /* ---- DSV4-exact numerical mode ---------------------------------------------------------
  * Bit-exact DeepSeek-V4 routed-expert arithmetic (ref: enqueue_deepseek_moe_rows, the grouped

@@ -762,3 +762,83 @@ ORC_API int orc_dsv4_expert(float* out, const float* in, const uint8_t* w1, cons
                                            row * (intermediate / 32u)));
     return 0;
 }
+
+/* ======================================================================================
+ * DSV4 shared expert: FP8 E4M3 weights with one E8M0 scale per 128 x 128 block.
+ * PARITY UNPINNED against compiled reference code: the reference has no CPU replay of these
+ * kernels (its host function dsv4_fp8_e4m3_matvec_f32, src/models/dsv4/deepseek_ops.cpp:523-560,
+ * accumulates in double and is only tolerance-close).  This restates the DEVICE kernels
+ * deepseek_fp8_gate_up_kernel / deepseek_fp8_down_kernel (kernels/cuda/backend.cu:2781-2863):
+ * thread t of a 256-thread block sums columns t, t + 256, ... with sum = fma(x * w, scale, sum),
+ * then the same block tree as the FP4 kernels; decode fp8_e4m3_value (:159-173).
+ * ====================================================================================== */
+static float dsv4_fp8_value(uint8_t enc) {
+    const unsigned exponent = (enc >> 3) & 0x0Fu, mantissa = enc & 7u;
+    float value;
+    if (exponent == 0u) value = ldexpf((float)mantissa / 8.0f, -6);
+    else if (exponent == 0x0Fu && mantissa == 7u) return nanf("");
+    else value = ldexpf(1.0f + (float)mantissa / 8.0f, (int)exponent - 7);
+    return (enc & 0x80u) ? -value : value;
+}
+
+static float dsv4_fp8_row(const float* input, const uint8_t* weights, const uint8_t* scales, uint64_t columns,
+                          uint64_t row) {
+    const uint64_t scale_columns = (columns + 127u) / 128u;
+    float partials[256];
+    for (uint32_t thread = 0; thread < 256u; ++thread) {
+        float sum = 0.0f;
+        for (uint64_t c = thread; c < columns; c += 256u) {
+            const float scale = dsv4_e8m0(scales[(row / 128u) * scale_columns + c / 128u]);
+            sum = fmaf(input[c] * dsv4_fp8_value(weights[row * columns + c]), scale, sum);
+        }
+        partials[thread] = sum;
+    }
+    float ws[8];
+    for (uint32_t w = 0; w < 8u; ++w) {
+        const float* l = partials + w * 32u;
+        float a[16];
+        for (int i = 0; i < 16; ++i) a[i] = l[i] + l[i + 16];
+        for (int i = 0; i < 8; ++i) a[i] += a[i + 8];
+        for (int i = 0; i < 4; ++i) a[i] += a[i + 4];
+        a[0] += a[2];
+        a[1] += a[3];
+        ws[w] = a[0] + a[1];
+    }
+    for (int i = 0; i < 8; ++i) ws[i] += 0.0f;
+    for (int i = 0; i < 4; ++i) ws[i] += ws[i + 4];
+    ws[0] += ws[2];
+    ws[1] += ws[3];
+    return ws[0] + ws[1];
+}
+
+/* The shared expert of one row: quantise the hidden state, FP8 gate/up with BF16 rounding, clamp,
+ * SiLU of the BF16 gate, BF16 activation, quantise, FP8 down, BF16 output (the sequence of
+ * enqueue_deepseek_moe, kernels/cuda/backend.cu:14509-14625).  Returns 1 on a non-finite gate/up. */
+ORC_API int orc_dsv4_fp8_shared(float* out, const float* in, const uint8_t* w1, const uint8_t* s1, const uint8_t* w3,
+                                const uint8_t* s3, const uint8_t* w2, const uint8_t* s2, uint32_t hidden,
+                                uint32_t intermediate, float swiglu_limit, float* scratch) {
+    float* q = (float*)malloc((size_t)hidden * sizeof(float));
+    memcpy(q, in, (size_t)hidden * sizeof(float));
+    orc_quantize_activation_e4m3(q, hidden);
+    for (uint64_t row = 0; row < intermediate; ++row) {
+        const float g = orc_bf16_round(dsv4_fp8_row(q, w1, s1, hidden, row));
+        const float u = orc_bf16_round(dsv4_fp8_row(q, w3, s3, hidden, row));
+        if (!isfinite(g) || !isfinite(u)) {
+            free(q);
+            return 1;
+        }
+        const float lg = fminf(g, swiglu_limit);
+        const float lu = fmaxf(-swiglu_limit, fminf(u, swiglu_limit));
+        uint32_t gb;
+        memcpy(&gb, &lg, 4);
+        gb &= 0xFFFF0000u;
+        float gt;
+        memcpy(&gt, &gb, 4);
+        const float silu = isfinite(gt) ? orc_silu(gt) : gt;
+        scratch[row] = orc_bf16_round(silu * lu);
+    }
+    free(q);
+    orc_quantize_activation_e4m3(scratch, intermediate);
+    for (uint64_t row = 0; row < hidden; ++row) out[row] = orc_bf16_round(dsv4_fp8_row(scratch, w2, s2, intermediate, row));
+    return 0;
+}

@@ -102,6 +102,8 @@ def port():
         lib.orc_quantize_activation_e4m3.restype = None
         lib.orc_dsv4_expert.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32, C.c_uint32,
                                         C.c_float, C.c_float, f32p]
+        lib.orc_dsv4_fp8_shared.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32, C.c_uint32,
+                                            C.c_float, f32p]
         lib.orc_experts_all.argtypes = [C.POINTER(LayerDesc), u16p, C.POINTER(Expert), u32p, f32p,
                                         u32p, u32p, f32p]
         _port = lib

@@ -23,6 +23,8 @@ EXPORTS = [
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
     "strata_moe_route_hash",
+    "strata_moe_device_count", "strata_moe_weight_upload", "strata_moe_weight_release", "strata_moe_command_enqueue",
+    "strata_moe_command_collect", "strata_moe_command_enqueue_rows_dsv4", "strata_moe_command_collect_rows_dsv4",
 ]
 
 SRC_HOST, SRC_DEVICE_COPY, SRC_DEVICE_BORROW = 0, 1, 2
@@ -52,7 +54,9 @@ class Aux(C.Structure):
 class Stats(C.Structure):
     _fields_ = [("forward_calls", C.c_uint64), ("kernel_launches", C.c_uint64),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
-                ("last_forward_ms", C.c_float)]
+                ("last_forward_ms", C.c_float), ("router_fast_tokens", C.c_uint64),
+                ("router_rechecked_tokens", C.c_uint64), ("command_calls", C.c_uint64),
+                ("workspace_allocations", C.c_uint64)]
 
 
 def library_path():
@@ -272,7 +276,9 @@ class MoeLayer:
                 self.set_shared(r, layer.shared[role])
 
     # ---- compute -------------------------------------------------------------------
-    def forward(self, x, out=None, want_aux=False):
+    def forward(self, x, out=None, want_aux=False, aux_logits=True):
+        """aux_logits=False leaves the logits out of the aux outputs: asking for them makes the library
+        compute every logit in the canonical order, which large batches otherwise avoid."""
         T = x.shape[0]
         dev = x.device
         if out is None:
@@ -289,7 +295,9 @@ class MoeLayer:
                          counts=torch.empty(E, dtype=torch.int32, device=dev),
                          offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
                          perm=torch.empty(T * k, dtype=torch.int32, device=dev))
-            aux = Aux(*[v.data_ptr() for v in aux_t.values()])
+            if not aux_logits:
+                aux_t["logits"] = None
+            aux = Aux(*[(v.data_ptr() if v is not None else None) for v in aux_t.values()])
         self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_forward(self.h, _ptr(x), T, _ptr(out),
                                                    C.byref(aux) if aux is not None else None))

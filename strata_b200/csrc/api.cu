@@ -26,6 +26,17 @@ struct strata_moe_ctx {
     cudaEvent_t pev[STRATA_MOE_PHASES + 1] = {};  // phase boundaries of the last timed forward
     bool pev_valid = false;
     unsigned long long launches_at_create = 0;
+    unsigned long long* d_router_rechecks = nullptr;   // tokens the fast router handed to the canonical kernels
+    uint64_t router_fast_tokens = 0;                    // tokens routed through the fast path
+    // handle-based commands (strata_moe_command_*): an internal layer whose expert slots borrow the
+    // uploaded weights named by the command in flight
+    strata_moe_layer* cmd_layer = nullptr;
+    uint32_t cmd_slots = 0;
+    int cmd_kind = 0;                  // 0 none, 1 dense command, 2 DSV4 row groups
+    uint32_t cmd_n = 0, cmd_rows = 0, cmd_pairs = 0, cmd_shared_rows = 0;
+    bool cmd_shared = false;
+    std::vector<void*> cmd_scratch;    // device buffers of the command in flight (row lists, gathered rows)
+    uint64_t workspace_allocations = 0;
 };
 
 struct DeviceTable {
@@ -49,6 +60,7 @@ struct LayerKnobs {
     int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
+    int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
 };
 
 static LayerKnobs read_knobs() {
@@ -65,6 +77,7 @@ static LayerKnobs read_knobs() {
     k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
+    k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
     return k;
 }
 
@@ -95,12 +108,17 @@ struct strata_moe_layer {
     float* out_stage = nullptr;
     void* prefill_scratch = nullptr;
     uint32_t* shared_tiles = nullptr;  // tile list of the shared expert's grouped GEMM
+    uint32_t* router_tiles = nullptr;  // tile list of the tensor-core router projection
+    uint32_t* router_off2 = nullptr;   // {0, T} for it
+    uint32_t* recheck_list = nullptr;  // [max_tokens] tokens the fast router hands to the canonical kernels
+    uint32_t* recheck_count = nullptr;
     float* one_global = nullptr;  // device float 1.0 for the shared expert table
     void* d_wmaps = nullptr;      // [3][n_local] tensor-map descriptors of the packed weights
     bool wmaps_ok = false;
     // f16 decode path for the FP4 formats
     bool f16_ok = false;
-    bool stream_ok = false;   // shapes and alignments allow the bulk-copy ring kernels
+    bool stream_ok = false;   // shapes and alignments allow the TMA ring kernels
+    void* d_smaps = nullptr;  // [3][n_local][3] tensor maps of the ring kernels
     uint32_t* d_not_ok = nullptr;
     float *act_f32 = nullptr, *x_rowscale = nullptr, *act_rowscale = nullptr;
     // dense command state
@@ -208,6 +226,18 @@ int sync_tables(strata_moe_layer* L) {
     for (int r = 0; r < 3 && L->stream_ok; ++r)
         for (uint32_t e = 0; e < n && L->stream_ok; ++e)
             L->stream_ok = (((uintptr_t)L->tab[r].packed[e] | (uintptr_t)L->tab[r].scales[e]) & 15u) == 0;
+    if (L->stream_ok) {
+        struct alignas(64) Blob3 { unsigned char b[3 * 128]; };
+        std::vector<Blob3> maps((size_t)3 * n);
+        for (int r = 0; r < 3 && L->stream_ok; ++r) {
+            const uint32_t rows = r == STRATA_MOE_ROLE_DOWN ? L->d.hidden : L->d.intermediate;
+            const uint32_t cols = r == STRATA_MOE_ROLE_DOWN ? L->d.intermediate : L->d.hidden;
+            for (uint32_t e = 0; e < n && L->stream_ok; ++e)
+                L->stream_ok = decode_stream_encode_maps(&maps[(size_t)r * n + e], L->d.format, L->tab[r].packed[e],
+                                                         L->tab[r].scales[e], rows, cols) == 0;
+        }
+        if (L->stream_ok) CK(cudaMemcpy(L->d_smaps, maps.data(), maps.size() * sizeof(Blob3), cudaMemcpyHostToDevice));
+    }
     // tensor maps of the packed weights for the tensor-core path's TMA producer
     L->wmaps_ok = false;
     if (L->d.format != STRATA_MOE_FMT_BF16 && tensor_path_ok(L, L->d.format, L->d.intermediate)) {
@@ -296,6 +326,42 @@ uint32_t mixed_min_rows(const strata_moe_layer* L, uint32_t max_rows_per_group) 
     // long enough that a hot expert's repeated passes would dominate.
     const uint32_t min_tokens = L->knobs.mixed_min_tokens >= 0 ? (uint32_t)L->knobs.mixed_min_tokens : 128u;
     return max_rows_per_group >= (uint32_t)thr && max_rows_per_group >= min_tokens ? (uint32_t)thr : 0u;
+}
+
+__global__ void set_pair_kernel(uint32_t* p, uint32_t a, uint32_t b) {
+    p[0] = a;
+    p[1] = b;
+}
+
+// Router projection, scores, top-k and weights for T tokens.  `logits_out` non-null means the caller
+// wants the canonical logits of every (token, expert): that always takes the canonical projection.
+// Otherwise large batches take the fast path: tensor-core projection into the layer's workspace, exact
+// selection and weights by route_fast_kernel, canonical recomputation of the tokens it does not trust.
+int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* logits_out, uint32_t* ids, float* w) {
+    strata_moe_ctx* ctx = L->ctx;
+    cudaStream_t s = ctx->stream;
+    const strata_moe_layer_desc& d = L->d;
+    RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
+    const int thr = L->knobs.fast_router_min_tokens == 0 ? 512 : L->knobs.fast_router_min_tokens;
+    const bool fast = logits_out == nullptr && thr > 0 && T >= (uint32_t)thr && route_fast_supported(rp, d.hidden) &&
+                      tensor_path_ok(L, 3, d.intermediate) && (((uintptr_t)x | (uintptr_t)L->router) & 15u) == 0;
+    if (fast) {
+        set_pair_kernel<<<1, 1, 0, s>>>(L->router_off2, 0u, T);
+        ++g_kernel_launches;
+        if (launch_router_tc(x, T, L->router, d.experts, d.hidden, L->logits, L->router_tiles, L->router_off2,
+                             ctx->d_status, s) != 0)
+            return fail(ctx, STRATA_MOE_E_CUDA, "tensor-core router projection launch failed");
+        mark(ctx, 1);
+        launch_route_fast(rp, L->logits, L->bias, x, L->router, T, d.hidden, ids, w, L->recheck_list, L->recheck_count,
+                          ctx->d_router_rechecks, ctx->d_status, s);
+        ctx->router_fast_tokens += T;
+        return 0;
+    }
+    float* lg = logits_out ? logits_out : L->logits;
+    launch_router_logits(x, L->router, T, d.hidden, d.experts, lg, s);
+    mark(ctx, 1);
+    launch_route(rp, lg, L->bias, T, ids, w, ctx->d_status, s);
+    return 0;
 }
 
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
@@ -390,7 +456,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         if (L->stream_ok) {
-            if (launch_decode_stream_gate_up(a, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
+            if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
@@ -414,7 +480,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
         } else {
             if (L->stream_ok) {
-                if (launch_decode_stream_down(a, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
+                if (launch_decode_stream_down(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
             } else {
                 launch_decode_fp4_down(a, s);
             }
@@ -494,10 +560,6 @@ int run_shared(strata_moe_layer* L, const __nv_bfloat16* x, const __nv_bfloat16*
     return 0;
 }
 
-__global__ void set_pair_kernel(uint32_t* p, uint32_t a, uint32_t b) {
-    p[0] = a;
-    p[1] = b;
-}
 __global__ void uniform_offsets_kernel(uint32_t* p, uint32_t n, uint32_t rows) {
     for (uint32_t i = threadIdx.x; i <= n; i += blockDim.x) p[i] = i * rows;
 }
@@ -559,16 +621,36 @@ int strata_moe_create(int device, void* stream, strata_moe_ctx** out) {
         strata_moe_destroy(ctx);
         return STRATA_MOE_E_CUDA;
     }
+    if (cudaMalloc(&ctx->d_router_rechecks, sizeof(unsigned long long)) != cudaSuccess ||
+        cudaMemset(ctx->d_router_rechecks, 0, sizeof(unsigned long long)) != cudaSuccess) {
+        strata_moe_destroy(ctx);
+        return STRATA_MOE_E_CUDA;
+    }
     ctx->launches_at_create = g_kernel_launches;
     *out = ctx;
     return 0;
+}
+
+int strata_moe_device_count(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) return 0;
+    int usable = 0;
+    for (int i = 0; i < n; ++i) {
+        cudaDeviceProp prop{};
+        if (cudaGetDeviceProperties(&prop, i) != cudaSuccess || prop.major != 10) break;   // ordinals stay contiguous
+        ++usable;
+    }
+    return usable;
 }
 
 void strata_moe_destroy(strata_moe_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    if (ctx->cmd_layer) strata_moe_layer_destroy(ctx->cmd_layer);
+    for (void* p : ctx->cmd_scratch) cudaFree(p);
     if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->d_router_rechecks) cudaFree(ctx->d_router_rechecks);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->ev0) cudaEventDestroy(ctx->ev0);
     if (ctx->ev1) cudaEventDestroy(ctx->ev1);
@@ -605,6 +687,14 @@ int strata_moe_get_stats(const strata_moe_ctx* ctx, strata_moe_stats* out) {
     if (!ctx || !out) return STRATA_MOE_E_INVALID;
     *out = ctx->stats;
     out->kernel_launches = g_kernel_launches - ctx->launches_at_create;
+    out->router_fast_tokens = ctx->router_fast_tokens;
+    out->workspace_allocations = ctx->workspace_allocations;
+    out->router_rechecked_tokens = 0;
+    if (ctx->d_router_rechecks) {   // waits for the work enqueued so far
+        unsigned long long v = 0;
+        if (cudaMemcpy(&v, ctx->d_router_rechecks, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess)
+            out->router_rechecked_tokens = v;
+    }
     return 0;
 }
 
@@ -699,6 +789,10 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         A(cudaMalloc(&wm, (size_t)3 * n * 128 + 128));
         if (wm) L->owned.push_back(wm);
         L->d_wmaps = wm;
+        void* sm = nullptr;
+        A(cudaMalloc(&sm, (size_t)9 * n * 128 + 128));
+        if (sm) L->owned.push_back(sm);
+        L->d_smaps = sm;
     }
     A(dalloc(L, &L->act_f32, (size_t)P * I));
     A(dalloc(L, &L->x_rowscale, (size_t)P));
@@ -709,6 +803,10 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         A(dalloc(L, &L->sh_act_lo, (size_t)T * d.shared_intermediate));
         A(dalloc(L, &L->sh_y, (size_t)T * H));
     }
+    A(dalloc(L, &L->router_tiles, prefill_scratch_bytes(1, T) / sizeof(uint32_t) + 4));
+    A(dalloc(L, &L->router_off2, 2));
+    A(dalloc(L, &L->recheck_list, (size_t)T));
+    A(dalloc(L, &L->recheck_count, 1));
     A(dalloc(L, &L->x_stage, (size_t)T * H));
     A(dalloc(L, &L->out_stage, (size_t)T * H));
     if (e == cudaSuccess) {
@@ -829,11 +927,8 @@ int strata_moe_route(strata_moe_layer* L, const void* x, uint32_t T, float* logi
     if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
     if (!L->router) return fail(ctx, STRATA_MOE_E_INVALID, "router weights were never set");
     CK(cudaSetDevice(ctx->device));
-    float* lg = logits ? logits : L->logits;
-    launch_router_logits((const __nv_bfloat16*)x, L->router, T, L->d.hidden, L->d.experts, lg, ctx->stream);
-    RouterParams p{L->d.experts, L->d.top_k, L->d.score_kind, L->d.normalize, L->d.norm_init,
-                   L->d.weight_scale, L->d.softcap};
-    launch_route(p, lg, L->bias, T, ids, weights, ctx->d_status, ctx->stream);
+    int rc = run_router(L, (const __nv_bfloat16*)x, T, logits, ids, weights);
+    if (rc) return rc;
     CK(cudaGetLastError());
     return 0;
 }
@@ -952,7 +1047,6 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     mark(ctx, 0);
     const bool fork_shared = d.shared_intermediate != 0 && !ctx->timing;
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
-    float* lg = (aux && aux->logits) ? aux->logits : L->logits;
     uint32_t* ids = (aux && aux->ids) ? aux->ids : L->ids;
     float* w = (aux && aux->weights) ? aux->weights : L->weights;
     uint32_t* counts = (aux && aux->counts) ? aux->counts : L->counts;
@@ -970,10 +1064,8 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
         if (rc) return rc;
         CK(cudaEventRecord(ctx->ev_join, ctx->side));
     }
-    launch_router_logits(xb, L->router, T, d.hidden, d.experts, lg, s);
-    mark(ctx, 1);
-    RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
-    launch_route(rp, lg, L->bias, T, ids, w, ctx->d_status, s);
+    rc = run_router(L, xb, T, (aux && aux->logits) ? aux->logits : nullptr, ids, w);
+    if (rc) return rc;
     mark(ctx, 2);
     launch_group(ids, P, 0, d.experts, counts, offsets, perm, L->inv, L->active, L->n_active,
                  L->group_scratch, s);
@@ -1201,10 +1293,10 @@ int strata_moe_quantize_e4m3(strata_moe_ctx* ctx, float* values, uint32_t rows, 
     return 0;
 }
 
-int strata_moe_experts_grouped_dsv4(strata_moe_layer* L, const float* rows_f32, uint32_t pairs,
-                                    const uint32_t* offsets, const float* coefficients, float swiglu_limit,
-                                    float* y) {
-    if (!L) return STRATA_MOE_E_INVALID;
+// rows_f32 [*, H] fp32; row_index (device, or nullptr = rows already in group order) names the source row of
+// every grouped row.
+static int dsv4_grouped_core(strata_moe_layer* L, const float* rows_f32, const uint32_t* row_index, uint32_t pairs,
+                             const uint32_t* offsets, const float* coefficients, float swiglu_limit, float* y) {
     strata_moe_ctx* ctx = L->ctx;
     if (!rows_f32 || !offsets || !y) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
     if (L->d.format != STRATA_MOE_FMT_MXFP4)
@@ -1223,13 +1315,20 @@ int strata_moe_experts_grouped_dsv4(strata_moe_layer* L, const float* rows_f32, 
     const uint32_t H = L->d.hidden, I = L->d.intermediate, n = L->d.expert_count;
     float* xq = L->y;            // [pairs, H] scratch: the E4M3-quantised input rows
     float* act = L->act_f32;     // [pairs, I]
-    launch_dsv4_quantize(rows_f32, nullptr, 1, pairs, H, xq, s);
+    launch_dsv4_quantize(rows_f32, row_index, 1, pairs, H, xq, s);
     launch_dsv4_gate_up(n, offsets, H, I, wt(L->tab[0]), wt(L->tab[1]), xq, coefficients, swiglu_limit, act,
                         ctx->d_status, s);
     launch_dsv4_quantize(act, nullptr, 1, pairs, I, act, s);
     launch_dsv4_down(n, offsets, H, I, wt(L->tab[2]), act, y, ctx->d_status, s);
     CK(cudaGetLastError());
     return 0;
+}
+
+int strata_moe_experts_grouped_dsv4(strata_moe_layer* L, const float* rows_f32, uint32_t pairs,
+                                    const uint32_t* offsets, const float* coefficients, float swiglu_limit,
+                                    float* y) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    return dsv4_grouped_core(L, rows_f32, nullptr, pairs, offsets, coefficients, swiglu_limit, y);
 }
 
 int strata_moe_combine_dsv4(strata_moe_layer* L, const float* y, const uint32_t* inv, const float* shared_rows,
@@ -1242,6 +1341,394 @@ int strata_moe_combine_dsv4(strata_moe_layer* L, const float* y, const uint32_t*
     launch_dsv4_join(y, inv, shared_rows, T, L->d.top_k, L->d.hidden, out, ctx->d_status, ctx->stream);
     CK(cudaGetLastError());
     return 0;
+}
+
+// ------------------------------------------------------------------------- weight handles + commands
+struct strata_moe_weight {
+    strata_moe_ctx* ctx = nullptr;
+    int fmt = 0;
+    uint32_t rows = 0, cols = 0;
+    float global_scale = 1.0f;
+    uint8_t* packed = nullptr;   // one allocation: packed bytes, then the scales at a 256-byte aligned offset
+    uint8_t* scales = nullptr;
+};
+
+static size_t handle_packed_bytes(int fmt, uint32_t rows, uint32_t cols) {
+    if (fmt == STRATA_MOE_FMT_FP8B128) return (size_t)rows * cols;
+    return packed_bytes(fmt, rows, cols);
+}
+static size_t handle_scale_bytes(int fmt, uint32_t rows, uint32_t cols) {
+    if (fmt == STRATA_MOE_FMT_FP8B128) return (size_t)((rows + 127u) / 128u) * ((cols + 127u) / 128u);
+    return scale_bytes(fmt, rows, cols);
+}
+
+int strata_moe_weight_upload(strata_moe_ctx* ctx, const strata_moe_weight_desc* desc, const void* weights_host,
+                             size_t weight_bytes, const void* scales_host, size_t scale_bytes_in,
+                             strata_moe_weight** out) {
+    if (!ctx || !desc || !out) return STRATA_MOE_E_INVALID;
+    *out = nullptr;
+    if (desc->format < 0 || desc->format > STRATA_MOE_FMT_FP8B128)
+        return fail(ctx, STRATA_MOE_E_INVALID, "unknown weight encoding");
+    if (desc->rows == 0 || desc->cols == 0 || desc->rows % 128u || desc->cols % 128u)
+        return fail(ctx, STRATA_MOE_E_INVALID, "weight rows and columns must be positive multiples of 128");
+    const size_t pb = handle_packed_bytes(desc->format, desc->rows, desc->cols);
+    const size_t sb = handle_scale_bytes(desc->format, desc->rows, desc->cols);
+    if (!weights_host || weight_bytes != pb) return fail(ctx, STRATA_MOE_E_INVALID, "weight payload size does not match the descriptor");
+    if (sb && (!scales_host || scale_bytes_in != sb))
+        return fail(ctx, STRATA_MOE_E_INVALID, "scale payload size does not match the descriptor");
+    if (desc->format == STRATA_MOE_FMT_NVFP4 && !(desc->global_scale > 0.0f && desc->global_scale < 3.0e38f))
+        return fail(ctx, STRATA_MOE_E_INVALID, "NVFP4 global scale must be finite and positive");
+    CK(cudaSetDevice(ctx->device));
+    strata_moe_weight* w = new (std::nothrow) strata_moe_weight();
+    if (!w) return fail(ctx, STRATA_MOE_E_INVALID, "out of host memory");
+    const size_t soff = (pb + 255) / 256 * 256;
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, soff + (sb ? sb : 16));
+    if (e == cudaSuccess) e = cudaMemcpyAsync(p, weights_host, pb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess && sb)
+        e = cudaMemcpyAsync(static_cast<uint8_t*>(p) + soff, scales_host, sb, cudaMemcpyHostToDevice, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);   // the host spans may go away when this returns
+    if (e != cudaSuccess) {
+        if (p) cudaFree(p);
+        delete w;
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("weight upload: ") + cudaGetErrorString(e));
+    }
+    w->ctx = ctx;
+    w->fmt = desc->format;
+    w->rows = desc->rows;
+    w->cols = desc->cols;
+    w->global_scale = desc->format == STRATA_MOE_FMT_NVFP4 ? desc->global_scale : 1.0f;
+    w->packed = static_cast<uint8_t*>(p);
+    w->scales = sb ? w->packed + soff : w->packed;
+    ctx->stats.h2d_bytes += pb + sb;
+    ctx->stats.weight_bytes += pb + sb;
+    *out = w;
+    return 0;
+}
+
+void strata_moe_weight_release(strata_moe_weight* w) {
+    if (!w) return;
+    cudaSetDevice(w->ctx->device);
+    cudaStreamSynchronize(w->ctx->stream);   // nothing enqueued may still read it
+    cudaFree(w->packed);
+    delete w;
+}
+
+}  // extern "C"
+
+namespace {
+
+// The internal layer of the handle-based commands: its expert slots borrow the weights of the command in
+// flight.  Rebuilt (and counted) only when the shape changes or a command needs more room.
+int ensure_cmd_layer(strata_moe_ctx* ctx, int fmt, uint32_t H, uint32_t I, uint32_t slots, uint32_t rows, uint32_t pairs) {
+    strata_moe_layer* L = ctx->cmd_layer;
+    if (L && L->d.format == fmt && L->d.hidden == H && L->d.intermediate == I && L->d.expert_count >= slots &&
+        L->d.max_tokens >= rows && L->max_pairs >= pairs)
+        return 0;
+    if (L) {
+        strata_moe_layer_destroy(L);
+        ctx->cmd_layer = nullptr;
+    }
+    strata_moe_layer_desc d{};
+    d.hidden = H;
+    d.intermediate = I;
+    d.experts = d.expert_count = slots < 16u ? 16u : (slots + 15u) / 16u * 16u;
+    d.top_k = 1;
+    d.format = fmt;
+    d.score_kind = STRATA_MOE_SCORE_SIGMOID;
+    d.weight_scale = d.output_scale = 1.0f;
+    d.max_tokens = rows < 64u ? 64u : rows + rows / 2u;
+    d.max_pairs = pairs < 256u ? 256u : pairs + pairs / 2u;
+    if (d.max_pairs < d.max_tokens) d.max_pairs = d.max_tokens;
+    d.activation = STRATA_MOE_ACT_SWIGLU;
+    int rc = strata_moe_layer_create(ctx, &d, &ctx->cmd_layer);
+    if (rc == 0) ++ctx->workspace_allocations;
+    return rc;
+}
+
+void cmd_release_scratch(strata_moe_ctx* ctx) {
+    for (void* p : ctx->cmd_scratch) cudaFree(p);
+    ctx->cmd_scratch.clear();
+}
+
+template <typename T>
+cudaError_t cmd_alloc(strata_moe_ctx* ctx, T** p, size_t n) {
+    void* v = nullptr;
+    cudaError_t e = cudaMalloc(&v, (n ? n : 1) * sizeof(T));
+    if (e == cudaSuccess) {
+        ctx->cmd_scratch.push_back(v);
+        *p = static_cast<T*>(v);
+    }
+    return e;
+}
+
+bool same_device(const strata_moe_ctx* ctx, const strata_moe_weight* w) { return w && w->ctx == ctx; }
+
+}  // namespace
+
+extern "C" {
+
+int strata_moe_command_enqueue(strata_moe_ctx* ctx, const float* hidden, size_t hidden_floats, uint32_t rows,
+                               const strata_moe_expert_ref* routed, uint32_t n, const strata_moe_expert_ref* shared) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (ctx->cmd_kind != 0) return fail(ctx, STRATA_MOE_E_BUSY, "MoE workspace already has an in-flight command");
+    const uint32_t total = n + (shared ? 1u : 0u);
+    // limits of the reference command: at most 10 routed experts, 11 with the shared one
+    if (rows == 0 || total == 0 || total > 11u || n > 10u || (n && !routed))
+        return fail(ctx, STRATA_MOE_E_INVALID, "MoE command has an unsupported row or expert count");
+    const strata_moe_weight* first = n ? routed[0].gate : shared->gate;
+    if (!same_device(ctx, first)) return fail(ctx, STRATA_MOE_E_INVALID, "MoE command has no valid leading expert");
+    const int fmt = first->fmt;
+    if (fmt != STRATA_MOE_FMT_INT4G128 && fmt != STRATA_MOE_FMT_NVFP4 && fmt != STRATA_MOE_FMT_BF16)
+        return fail(ctx, STRATA_MOE_E_INVALID, "MoE command has an unsupported weight encoding");
+    const uint32_t H = first->cols, I = first->rows;
+    for (uint32_t i = 0; i < total; ++i) {
+        const strata_moe_expert_ref& e = i < n ? routed[i] : *shared;
+        const strata_moe_weight* ws[3] = {e.gate, e.up, e.down};
+        for (const strata_moe_weight* w : ws)
+            if (!same_device(ctx, w) || w->fmt != fmt)
+                return fail(ctx, STRATA_MOE_E_INVALID, "MoE command contains an incompatible CUDA weight");
+        if (e.gate->rows != I || e.gate->cols != H || e.up->rows != I || e.up->cols != H || e.down->rows != H ||
+            e.down->cols != I)
+            return fail(ctx, STRATA_MOE_E_INVALID, i == 0 ? "MoE gate/up/down shapes are incompatible"
+                                                          : "MoE experts do not share one activation shape");
+        if (!(e.coefficient == e.coefficient) || !(fabsf(e.coefficient) <= 3.0e38f) ||
+            ((i >= n || fmt != STRATA_MOE_FMT_INT4G128) && e.coefficient != 1.0f))
+            return fail(ctx, STRATA_MOE_E_INVALID, "MoE expert coefficient is invalid");
+    }
+    if (!hidden || hidden_floats != (size_t)rows * H) return fail(ctx, STRATA_MOE_E_INVALID, "MoE hidden rows are incompatible");
+    for (size_t i = 0; i < hidden_floats; ++i)
+        if (!(fabsf(hidden[i]) <= 3.0e38f)) return fail(ctx, STRATA_MOE_E_INVALID, "MoE hidden rows are incompatible");
+    CK(cudaSetDevice(ctx->device));
+    int rc = ensure_cmd_layer(ctx, fmt, H, I, total, rows, total * rows);
+    if (rc) return rc;
+    strata_moe_layer* L = ctx->cmd_layer;
+    uint32_t ids[11];
+    float coefs[11];
+    for (uint32_t i = 0; i < total; ++i) {
+        const strata_moe_expert_ref& e = i < n ? routed[i] : *shared;
+        const strata_moe_weight* ws[3] = {e.gate, e.up, e.down};
+        for (int r = 0; r < 3; ++r) {
+            L->tab[r].packed[i] = ws[r]->packed;
+            L->tab[r].scales[i] = ws[r]->scales;
+            L->tab[r].global[i] = ws[r]->global_scale;
+        }
+        ids[i] = i;
+        coefs[i] = e.coefficient;
+    }
+    L->tables_dirty = true;
+    rc = strata_moe_enqueue_dense(L, hidden, rows, ids, coefs, total, 0);
+    if (rc) return rc;
+    ctx->cmd_kind = 1;
+    ctx->cmd_n = n;
+    ctx->cmd_rows = rows;
+    ctx->cmd_shared = shared != nullptr;
+    return 0;
+}
+
+int strata_moe_command_collect(strata_moe_ctx* ctx, float* routed_out, size_t routed_floats, float* shared_out,
+                               size_t shared_floats) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (ctx->cmd_kind != 1) return fail(ctx, STRATA_MOE_E_INVALID, "no MoE command is in flight");
+    strata_moe_layer* L = ctx->cmd_layer;
+    CK(cudaSetDevice(ctx->device));
+    // every return consumes or drains the command; results reach the caller only after completion and a
+    // clean status word are confirmed
+    const int rc = strata_moe_synchronize(ctx);
+    ctx->cmd_kind = 0;
+    L->dense_in_flight = false;
+    if (rc) return rc;
+    const size_t H = L->d.hidden, row_floats = (size_t)ctx->cmd_rows * H;
+    if (routed_floats != (size_t)ctx->cmd_n * row_floats || (ctx->cmd_n && !routed_out))
+        return fail(ctx, STRATA_MOE_E_INVALID, "routed output span does not match the command");
+    if (shared_floats != (ctx->cmd_shared ? row_floats : 0u) || (ctx->cmd_shared && !shared_out))
+        return fail(ctx, STRATA_MOE_E_INVALID, "shared output span does not match the command");
+    if (ctx->cmd_n)
+        CK(cudaMemcpyAsync(routed_out, L->y, routed_floats * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (ctx->cmd_shared)
+        CK(cudaMemcpyAsync(shared_out, L->y + (size_t)ctx->cmd_n * row_floats, shared_floats * 4,
+                           cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    ctx->stats.d2h_bytes += (routed_floats + shared_floats) * 4;
+    ++ctx->stats.command_calls;
+    return 0;
+}
+
+int strata_moe_command_enqueue_rows_dsv4(strata_moe_ctx* ctx, const float* hidden, size_t hidden_floats,
+                                         uint32_t hidden_rows, const strata_moe_row_group* groups, uint32_t n_groups,
+                                         const strata_moe_expert_ref* shared, const uint32_t* shared_rows,
+                                         uint32_t n_shared_rows, float swiglu_limit) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (ctx->cmd_kind != 0) return fail(ctx, STRATA_MOE_E_BUSY, "MoE workspace already has an in-flight command");
+    if (hidden_rows == 0 || (n_groups == 0 && !shared) || (n_groups && !groups))
+        return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek MoE command has no rows or no experts");
+    if (!(swiglu_limit > 0.0f && swiglu_limit < 3.0e38f))
+        return fail(ctx, STRATA_MOE_E_INVALID, "SwiGLU limit must be finite and positive");
+    const strata_moe_weight* first = n_groups ? groups[0].w1 : shared->gate;
+    if (!same_device(ctx, first)) return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek MoE command has no valid leading expert");
+    const uint32_t H = first->cols, I = first->rows;
+    uint64_t pairs64 = 0;
+    for (uint32_t g = 0; g < n_groups; ++g) {
+        const strata_moe_row_group& gr = groups[g];
+        const strata_moe_weight* ws[3] = {gr.w1, gr.w3, gr.w2};
+        for (const strata_moe_weight* w : ws)
+            if (!same_device(ctx, w) || w->fmt != STRATA_MOE_FMT_MXFP4)
+                return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek routed experts need FP4 E2M1 group-32 weights");
+        if (gr.w1->rows != I || gr.w1->cols != H || gr.w3->rows != I || gr.w3->cols != H || gr.w2->rows != H ||
+            gr.w2->cols != I)
+            return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek expert shapes are incompatible");
+        if (gr.n_rows == 0 || !gr.rows || !gr.coefficients)
+            return fail(ctx, STRATA_MOE_E_INVALID, "a row group is empty");
+        for (uint32_t i = 0; i < gr.n_rows; ++i) {
+            if (gr.rows[i] >= hidden_rows) return fail(ctx, STRATA_MOE_E_INVALID, "a row group names a row outside the page");
+            if (!(fabsf(gr.coefficients[i]) <= 3.0e38f)) return fail(ctx, STRATA_MOE_E_INVALID, "a coefficient is not finite");
+        }
+        pairs64 += gr.n_rows;
+    }
+    if (pairs64 > 0x3FFFFFFFull) return fail(ctx, STRATA_MOE_E_INVALID, "too many rows");
+    const uint32_t pairs = (uint32_t)pairs64;
+    if (shared) {
+        const strata_moe_weight* ws[3] = {shared->gate, shared->up, shared->down};
+        for (const strata_moe_weight* w : ws)
+            if (!same_device(ctx, w) || w->fmt != STRATA_MOE_FMT_FP8B128)
+                return fail(ctx, STRATA_MOE_E_INVALID, "the DeepSeek shared expert needs FP8 E4M3 block-128 weights");
+        if (shared->gate->rows != I || shared->gate->cols != H || shared->up->rows != I || shared->up->cols != H ||
+            shared->down->rows != H || shared->down->cols != I)
+            return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek shared expert shapes are incompatible");
+        if (n_shared_rows == 0 || !shared_rows) return fail(ctx, STRATA_MOE_E_INVALID, "the shared expert has no rows");
+        for (uint32_t i = 0; i < n_shared_rows; ++i)
+            if (shared_rows[i] >= hidden_rows) return fail(ctx, STRATA_MOE_E_INVALID, "a shared row lies outside the page");
+    } else {
+        n_shared_rows = 0;
+    }
+    if (!hidden || hidden_floats != (size_t)hidden_rows * H) return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek hidden rows are incompatible");
+    for (size_t i = 0; i < hidden_floats; ++i)
+        if (!(fabsf(hidden[i]) <= 3.0e38f)) return fail(ctx, STRATA_MOE_E_INVALID, "DeepSeek hidden rows are incompatible");
+    CK(cudaSetDevice(ctx->device));
+    const uint32_t slots = n_groups ? n_groups : 1u;
+    int rc = ensure_cmd_layer(ctx, STRATA_MOE_FMT_MXFP4, H, I, slots, hidden_rows > n_shared_rows ? hidden_rows : n_shared_rows,
+                              pairs > n_shared_rows ? pairs : n_shared_rows);
+    if (rc) return rc;
+    strata_moe_layer* L = ctx->cmd_layer;
+    cudaStream_t s = ctx->stream;
+    const uint32_t n_slots = L->d.expert_count;
+    // host staging of the row lists, coefficients and the group table
+    std::vector<uint32_t> h_rows(pairs + n_shared_rows), h_off(n_slots + 1 + 2);
+    std::vector<float> h_coef(pairs ? pairs : 1);
+    uint32_t at = 0;
+    for (uint32_t g = 0; g < n_slots; ++g) {
+        h_off[g] = at;
+        if (g < n_groups) {
+            const strata_moe_row_group& gr = groups[g];
+            const strata_moe_weight* ws[3] = {gr.w1, gr.w3, gr.w2};
+            for (int r = 0; r < 3; ++r) {
+                L->tab[r].packed[g] = ws[r]->packed;
+                L->tab[r].scales[g] = ws[r]->scales;
+                L->tab[r].global[g] = 1.0f;
+            }
+            for (uint32_t i = 0; i < gr.n_rows; ++i) {
+                h_rows[at + i] = gr.rows[i];
+                h_coef[at + i] = gr.coefficients[i];
+            }
+            at += gr.n_rows;
+        } else if (n_groups) {
+            for (int r = 0; r < 3; ++r) {   // unused slots: any valid pointers, zero rows
+                L->tab[r].packed[g] = L->tab[r].packed[0];
+                L->tab[r].scales[g] = L->tab[r].scales[0];
+                L->tab[r].global[g] = 1.0f;
+            }
+        }
+    }
+    h_off[n_slots] = at;
+    h_off[n_slots + 1] = 0;                 // the shared expert's one-group table {0, n_shared_rows}
+    h_off[n_slots + 2] = n_shared_rows;
+    for (uint32_t i = 0; i < n_shared_rows; ++i) h_rows[pairs + i] = shared_rows[i];
+    L->tables_dirty = true;
+    cmd_release_scratch(ctx);
+    float *d_hidden = nullptr, *d_coef = nullptr, *d_y = nullptr, *d_sx = nullptr, *d_sact = nullptr, *d_sy = nullptr;
+    uint32_t *d_rows = nullptr, *d_off = nullptr;
+    const uint8_t** d_sp = nullptr;
+    cudaError_t e = cmd_alloc(ctx, &d_hidden, hidden_floats);
+    if (e == cudaSuccess) e = cmd_alloc(ctx, &d_coef, h_coef.size());
+    if (e == cudaSuccess) e = cmd_alloc(ctx, &d_rows, h_rows.size());
+    if (e == cudaSuccess) e = cmd_alloc(ctx, &d_off, h_off.size());
+    if (e == cudaSuccess) e = cmd_alloc(ctx, &d_y, (size_t)(pairs + n_shared_rows) * H);
+    if (e == cudaSuccess && shared) e = cmd_alloc(ctx, &d_sx, (size_t)n_shared_rows * H);
+    if (e == cudaSuccess && shared) e = cmd_alloc(ctx, &d_sact, (size_t)n_shared_rows * I);
+    if (e == cudaSuccess && shared) e = cmd_alloc(ctx, &d_sp, 6);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_hidden, hidden, hidden_floats * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_coef, h_coef.data(), h_coef.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess && !h_rows.empty())
+        e = cudaMemcpyAsync(d_rows, h_rows.data(), h_rows.size() * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_off, h_off.data(), h_off.size() * 4, cudaMemcpyHostToDevice, s);
+    const uint8_t* sp[6] = {};
+    if (e == cudaSuccess && shared) {
+        sp[0] = shared->gate->packed; sp[1] = shared->gate->scales;
+        sp[2] = shared->up->packed;   sp[3] = shared->up->scales;
+        sp[4] = shared->down->packed; sp[5] = shared->down->scales;
+        e = cudaMemcpyAsync(d_sp, sp, sizeof(sp), cudaMemcpyHostToDevice, s);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);   // the host vectors above go out of scope
+    if (e != cudaSuccess) {
+        cmd_release_scratch(ctx);
+        return fail(ctx, STRATA_MOE_E_CUDA, std::string("DeepSeek MoE command set-up: ") + cudaGetErrorString(e));
+    }
+    ctx->stats.h2d_bytes += hidden_floats * 4;
+    if (pairs) {
+        rc = dsv4_grouped_core(L, d_hidden, d_rows, pairs, d_off, d_coef, swiglu_limit, d_y);
+        if (rc) { cmd_release_scratch(ctx); return rc; }
+    }
+    if (shared) {
+        d_sy = d_y + (size_t)pairs * H;
+        const uint32_t* off2 = d_off + n_slots + 1;
+        WeightTable g{d_sp + 0, d_sp + 1, nullptr, nullptr, nullptr}, u{d_sp + 2, d_sp + 3, nullptr, nullptr, nullptr},
+            dn{d_sp + 4, d_sp + 5, nullptr, nullptr, nullptr};
+        launch_dsv4_quantize(d_hidden, d_rows + pairs, 1, n_shared_rows, H, d_sx, s);
+        launch_dsv4_gate_up(1, off2, H, I, g, u, d_sx, nullptr, swiglu_limit, d_sact, ctx->d_status, s, true);
+        launch_dsv4_quantize(d_sact, nullptr, 1, n_shared_rows, I, d_sact, s);
+        launch_dsv4_down(1, off2, H, I, dn, d_sact, d_sy, ctx->d_status, s, true);
+        CK(cudaGetLastError());
+    }
+    ctx->cmd_kind = 2;
+    ctx->cmd_pairs = pairs;
+    ctx->cmd_shared_rows = n_shared_rows;
+    ctx->cmd_rows = hidden_rows;
+    ctx->cmd_shared = shared != nullptr;
+    return 0;
+}
+
+int strata_moe_command_collect_rows_dsv4(strata_moe_ctx* ctx, float* routed_out, size_t routed_floats, float* shared_out,
+                                         size_t shared_floats) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (ctx->cmd_kind != 2) return fail(ctx, STRATA_MOE_E_INVALID, "no DeepSeek MoE row command is in flight");
+    strata_moe_layer* L = ctx->cmd_layer;
+    CK(cudaSetDevice(ctx->device));
+    const int rc = strata_moe_synchronize(ctx);
+    ctx->cmd_kind = 0;
+    const size_t H = L->d.hidden;
+    const float* d_y = ctx->cmd_scratch.size() > 4 ? static_cast<const float*>(ctx->cmd_scratch[4]) : nullptr;
+    int out_rc = rc;
+    if (rc == 0) {
+        if (routed_floats != (size_t)ctx->cmd_pairs * H || (ctx->cmd_pairs && !routed_out))
+            out_rc = fail(ctx, STRATA_MOE_E_INVALID, "routed output span does not match the command");
+        else if (shared_floats != (size_t)ctx->cmd_shared_rows * H || (ctx->cmd_shared_rows && !shared_out))
+            out_rc = fail(ctx, STRATA_MOE_E_INVALID, "shared output span does not match the command");
+    }
+    if (out_rc == 0 && d_y) {
+        cudaError_t e = cudaSuccess;
+        if (ctx->cmd_pairs) e = cudaMemcpyAsync(routed_out, d_y, routed_floats * 4, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess && ctx->cmd_shared_rows)
+            e = cudaMemcpyAsync(shared_out, d_y + (size_t)ctx->cmd_pairs * H, shared_floats * 4, cudaMemcpyDeviceToHost,
+                                ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) out_rc = fail(ctx, STRATA_MOE_E_CUDA, cudaGetErrorString(e));
+        else {
+            ctx->stats.d2h_bytes += (routed_floats + shared_floats) * 4;
+            ++ctx->stats.command_calls;
+        }
+    }
+    cmd_release_scratch(ctx);
+    return out_rc;
 }
 
 // ------------------------------------------------------------------------- expert parallelism
@@ -1393,9 +1880,8 @@ int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
         ep->forked = true;
     }
     if (T) {
-        launch_router_logits(ep->x, L->router, T, d.hidden, d.experts, L->logits, s);
-        RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
-        launch_route(rp, L->logits, L->bias, T, L->ids, L->weights, ctx->d_status, s);
+        rc = run_router(L, ep->x, T, nullptr, L->ids, L->weights);
+        if (rc) return rc;
         launch_group(L->ids, T * d.top_k, 0, d.experts, L->counts, L->offsets, L->perm, L->inv, nullptr, nullptr,
                      L->group_scratch, s);
     } else {

@@ -55,6 +55,12 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
                   uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s,
                   const uint32_t* forced_ids = nullptr);
+// Fast router (tensor-core projection + exact recheck), see router.cu.
+bool route_fast_supported(const RouterParams& p, uint32_t H);
+void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
+                       const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,
+                       uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
+                       cudaStream_t s);
 // group.cu
 size_t group_scratch_bytes(uint32_t pairs, uint32_t n_experts);
 void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, uint32_t n_experts,
@@ -107,8 +113,10 @@ void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* sc
                                float post_scale, uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
 // decode_stream.cu : the same two GEMMs with the weights streamed through a shared-memory ring by bulk copies
 bool decode_stream_supported(int fmt, uint32_t H, uint32_t I);
-int launch_decode_stream_gate_up(const DecodeArgs& a, cudaStream_t s);
-int launch_decode_stream_down(const DecodeArgs& a, cudaStream_t s);
+// maps: device array [3 roles][n_groups][3] of 128-byte tensor maps made by decode_stream_encode_maps
+int decode_stream_encode_maps(void* out3x128, int fmt, const void* packed, const void* scales, uint32_t rows, uint32_t K);
+int launch_decode_stream_gate_up(const DecodeArgs& a, const void* maps, cudaStream_t s);
+int launch_decode_stream_down(const DecodeArgs& a, const void* maps, cudaStream_t s);
 void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_down(const DecodeArgs& a, cudaStream_t s);
 // prefill.cu : large-batch expert FFN (tcgen05 grouped GEMM path)
@@ -144,6 +152,10 @@ int launch_prefill_down(const PrefillArgs& a, const void* act16, const float* ac
 int prefill_encode_weight_map(void* out128, const void* packed, uint32_t rows, uint32_t K);
 int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
                         const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s);
+// Router projection on the tensor cores (approximate summation order; see router.cu for its use).
+// tile_table: scratch of prefill_scratch_bytes(1, T); offsets2: device {0, T}.
+int launch_router_tc(const void* x_bf16, uint32_t T, const void* wg_bf16, uint32_t E, uint32_t H, float* logits,
+                     uint32_t* tile_table, const uint32_t* offsets2, uint32_t* status, cudaStream_t s);
 // combine.cu
 void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
                     uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,
@@ -198,11 +210,11 @@ void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div
                           float* dst, cudaStream_t s);
 void launch_dsv4_gate_up(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& gate,
                          const WeightTable& up, const float* xq, const float* coef, float limit, float* act,
-                         uint32_t* status, cudaStream_t s);
+                         uint32_t* status, cudaStream_t s, bool fp8 = false);
 void launch_dsv4_join(const float* y, const uint32_t* inv, const float* shared, uint32_t T, uint32_t k, uint32_t H,
                       float* out, uint32_t* status, cudaStream_t s);
 void launch_dsv4_down(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& down,
-                      const float* actq, float* y, uint32_t* status, cudaStream_t s);
+                      const float* actq, float* y, uint32_t* status, cudaStream_t s, bool fp8 = false);
 
 // Launch counter (every wrapper above bumps it once per kernel launch; host threads of several
 // contexts share it).

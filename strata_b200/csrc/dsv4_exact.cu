@@ -5,6 +5,8 @@
 //   deepseek_fp4_gate_up_kernel       kernels/cuda/backend.cu:2308-2376
 //   deepseek_fp4_down_kernel          kernels/cuda/backend.cu:2378-2413
 //   CPU replay of all three           kernels/cpu/dsv4_fp4_expert.cpp:58-163, 774-884
+//   deepseek_fp8_gate_up_kernel / deepseek_fp8_down_kernel (the shared expert: FP8 E4M3 weights, one
+//   E8M0 scale per 128 x 128 block)   kernels/cuda/backend.cu:2781-2863
 //
 // The reference computes one output row with a 256-thread block: thread t accumulates the columns
 // t, t + 256, ... in increasing order with sum = fma(x * w, scale, sum), then the block adds the 256
@@ -71,6 +73,22 @@ __device__ __forceinline__ void e2m1x8_f32(uint32_t w, float v[8]) {
         const __half2 p = *reinterpret_cast<const __half2*>(&h[i]);
         v[2 * i] = __low2float(p);
         v[2 * i + 1] = __high2float(p);
+    }
+}
+
+// 8 E4M3 bytes (two 32-bit words, byte q = column q) -> 8 floats, exact; 0x7F / 0xFF -> NaN.
+__device__ __forceinline__ void e4m3x8_f32(uint2 w, float v[8]) {
+    const uint32_t words[2] = {w.x, w.y};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint32_t lo, hi;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(lo) : "h"((unsigned short)(words[i] & 0xFFFFu)));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(hi) : "h"((unsigned short)(words[i] >> 16)));
+        const __half2 a = *reinterpret_cast<const __half2*>(&lo), b = *reinterpret_cast<const __half2*>(&hi);
+        v[4 * i] = __low2float(a);
+        v[4 * i + 1] = __high2float(a);
+        v[4 * i + 2] = __low2float(b);
+        v[4 * i + 3] = __high2float(b);
     }
 }
 
@@ -141,7 +159,9 @@ struct Dsv4Args {
     uint32_t* status;
 };
 
-template <bool DUAL>
+// FP8 = false: E2M1 nibbles + one E8M0 scale per 32 columns of a row.
+// FP8 = true : E4M3 bytes + one E8M0 scale per 128 x 128 block (scales [ceil(R / 128), ceil(K / 128)]).
+template <bool DUAL, bool FP8>
 __global__ void __launch_bounds__(128) dsv4_rows_kernel(Dsv4Args a) {
     const uint32_t lane = threadIdx.x & 31u;
     const size_t total = (size_t)a.n_groups * a.R;
@@ -151,10 +171,12 @@ __global__ void __launch_bounds__(128) dsv4_rows_kernel(Dsv4Args a) {
         const uint32_t g = (uint32_t)(task / a.R), row = (uint32_t)(task % a.R);
         const uint32_t row0 = a.offsets[g], cnt = a.offsets[g + 1] - row0;
         if (cnt == 0u) continue;
-        const uint8_t* p0 = a.w0.packed[g] + (size_t)row * (K / 2u);
-        const uint8_t* s0 = a.w0.scales[g] + (size_t)row * (K / 32u);
-        const uint8_t* p1 = DUAL ? a.w1.packed[g] + (size_t)row * (K / 2u) : nullptr;
-        const uint8_t* s1 = DUAL ? a.w1.scales[g] + (size_t)row * (K / 32u) : nullptr;
+        const size_t prow = FP8 ? (size_t)row * K : (size_t)row * (K / 2u);
+        const size_t srow = FP8 ? (size_t)(row / 128u) * ((K + 127u) / 128u) : (size_t)row * (K / 32u);
+        const uint8_t* p0 = a.w0.packed[g] + prow;
+        const uint8_t* s0 = a.w0.scales[g] + srow;
+        const uint8_t* p1 = DUAL ? a.w1.packed[g] + prow : nullptr;
+        const uint8_t* s1 = DUAL ? a.w1.scales[g] + srow : nullptr;
         for (uint32_t tb = 0; tb < cnt; tb += kRT) {
             float acc0[kRT][8], acc1[DUAL ? kRT : 1][8];
 #pragma unroll
@@ -166,12 +188,21 @@ __global__ void __launch_bounds__(128) dsv4_rows_kernel(Dsv4Args a) {
                 }
             for (uint32_t c0 = lane * 8u; c0 < K; c0 += 256u) {
                 float w0v[8], w1v[8];
-                e2m1x8_f32(__ldg(reinterpret_cast<const uint32_t*>(p0 + c0 / 2u)), w0v);
-                const float sc0 = e8m0_dsv4(__ldg(s0 + c0 / 32u));
-                float sc1 = 0.0f;
-                if (DUAL) {
-                    e2m1x8_f32(__ldg(reinterpret_cast<const uint32_t*>(p1 + c0 / 2u)), w1v);
-                    sc1 = e8m0_dsv4(__ldg(s1 + c0 / 32u));
+                float sc0, sc1 = 0.0f;
+                if (FP8) {
+                    e4m3x8_f32(__ldg(reinterpret_cast<const uint2*>(p0 + c0)), w0v);
+                    sc0 = e8m0_dsv4(__ldg(s0 + c0 / 128u));
+                    if (DUAL) {
+                        e4m3x8_f32(__ldg(reinterpret_cast<const uint2*>(p1 + c0)), w1v);
+                        sc1 = e8m0_dsv4(__ldg(s1 + c0 / 128u));
+                    }
+                } else {
+                    e2m1x8_f32(__ldg(reinterpret_cast<const uint32_t*>(p0 + c0 / 2u)), w0v);
+                    sc0 = e8m0_dsv4(__ldg(s0 + c0 / 32u));
+                    if (DUAL) {
+                        e2m1x8_f32(__ldg(reinterpret_cast<const uint32_t*>(p1 + c0 / 2u)), w1v);
+                        sc1 = e8m0_dsv4(__ldg(s1 + c0 / 32u));
+                    }
                 }
 #pragma unroll
                 for (int r = 0; r < kRT; ++r) {
@@ -259,20 +290,22 @@ void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div
 
 void launch_dsv4_gate_up(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& gate,
                          const WeightTable& up, const float* xq, const float* coef, float limit, float* act,
-                         uint32_t* status, cudaStream_t s) {
+                         uint32_t* status, cudaStream_t s, bool fp8) {
     Dsv4Args a{n_groups, H, I, offsets, gate, up, xq, coef, limit, act, status};
     const size_t warps = (size_t)n_groups * I;
     const unsigned grid = (unsigned)((warps + 3) / 4 < (size_t)kNumSMs * 16u ? (warps + 3) / 4 : (size_t)kNumSMs * 16u);
-    dsv4_rows_kernel<true><<<grid, 128, 0, s>>>(a);
+    if (fp8) dsv4_rows_kernel<true, true><<<grid, 128, 0, s>>>(a);
+    else dsv4_rows_kernel<true, false><<<grid, 128, 0, s>>>(a);
     ++g_kernel_launches;
 }
 
 void launch_dsv4_down(uint32_t n_groups, const uint32_t* offsets, uint32_t H, uint32_t I, const WeightTable& down,
-                      const float* actq, float* y, uint32_t* status, cudaStream_t s) {
+                      const float* actq, float* y, uint32_t* status, cudaStream_t s, bool fp8) {
     Dsv4Args a{n_groups, I, H, offsets, down, down, actq, nullptr, 0.0f, y, status};
     const size_t warps = (size_t)n_groups * H;
     const unsigned grid = (unsigned)((warps + 3) / 4 < (size_t)kNumSMs * 16u ? (warps + 3) / 4 : (size_t)kNumSMs * 16u);
-    dsv4_rows_kernel<false><<<grid, 128, 0, s>>>(a);
+    if (fp8) dsv4_rows_kernel<false, true><<<grid, 128, 0, s>>>(a);
+    else dsv4_rows_kernel<false, false><<<grid, 128, 0, s>>>(a);
     ++g_kernel_launches;
 }
 

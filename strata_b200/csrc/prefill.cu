@@ -923,6 +923,48 @@ static int launch_bf16_nt(const PrefillArgs& a, const void* x, uint32_t rows, co
     return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Router projection on the tensor cores: logits[t, e] = sum_h x[t, h] * wg[e, h] for BF16 operands,
+// FP32 accumulation in tensor memory.  The expert rows play the 128-feature M tiles and the tokens the
+// N tiles of the single-GEMM modes (one group holding all T rows), so the output lands as [T, E] fp32.
+// The summation order differs from the canonical lane-strided order: these logits feed the fast
+// router, which re-derives everything that reaches the caller in the canonical order.
+// a.offsets must hold {0, T}.  Needs E % 128 == 0 and H % 64 == 0.
+template <int NT>
+static int launch_router_tc_nt(PrefillArgs a, const void* x, uint32_t T, const void* wg, uint32_t E, uint32_t H,
+                               cudaStream_t s) {
+    BMaps map_x;
+    CUtensorMap map_w;
+    if (!make_bmaps(&map_x, x, T, H) || !make_map(&map_w, wg, E, H, kMTile)) return -1;
+    const size_t smem = sizeof(PrefillSmem<NT>) + 1024;
+    if (set_smem_attr<kFmtBf16W, NT>(smem)) return -2;
+    a.fmt = kFmtBf16W;
+    a.H = E;     // features of the single-GEMM modes
+    a.I = H;     // their K
+    a.n_groups = 1;
+    a.pairs = T;
+    a.min_rows = 0;
+    prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, 1, a.tile_table, 0, NT);
+    if (E % 256u == 0u)
+        prefill_ffn_kernel<kFmtBf16W, 2, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, map_w, map_w, a, nullptr, nullptr, nullptr);
+    else
+        prefill_ffn_kernel<kFmtBf16W, 1, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, map_w, map_w, a, nullptr, nullptr, nullptr);
+    g_kernel_launches += 2;
+    return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+int launch_router_tc(const void* x, uint32_t T, const void* wg, uint32_t E, uint32_t H, float* logits,
+                     uint32_t* tile_table, const uint32_t* offsets2, uint32_t* status, cudaStream_t s) {
+    if (E % 128u || H % 64u || T == 0u) return -1;
+    PrefillArgs a{};
+    a.offsets = offsets2;
+    a.y = logits;
+    a.tile_table = tile_table;
+    a.status = status;
+    a.glu = GluParams{STRATA_MOE_ACT_SWIGLU, 1.0f, 1.0f};
+    // 128-token tiles: more tiles than the 192-token geometry gives, and a tile is short (E features x H)
+    return launch_router_tc_nt<128>(a, x, T, wg, E, H, s);
+}
+
 int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, const void* w_gate, const void* w_up,
                         const void* w_down, void* act, uint32_t rows_cap, cudaStream_t s) {
     return a.ntile != 128u ? launch_bf16_nt<192>(a, x, rows, w_gate, w_up, w_down, act, rows_cap, s)

@@ -31,10 +31,12 @@ __device__ __forceinline__ void router_stage8(float (*dst)[32][4], uint32_t c8, 
     }
 }
 
-template <int WARPS, int TT>
+// LIST = true: the tokens are list[0 .. *count) (indices into x and logits) and the blocks of a
+// column of the grid stride over the list, whose length is only known on the device.
+template <int WARPS, int TT, bool LIST>
 __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
-    uint32_t E, float* __restrict__ logits) {
+    uint32_t E, float* __restrict__ logits, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count) {
     // xs[tok][half][lane][4] : column = chunk + lane + 32 * (half * 4 + i)
     __shared__ __align__(16) float xs[TT][2][32][4];
     __shared__ __align__(16) float ws[WARPS][2][32][4];
@@ -42,9 +44,16 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
     constexpr int XV = (TT * (kRouterChunk / 8) + THREADS - 1) / THREADS;  // uint4 per thread
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t e = blockIdx.x * WARPS + warp;
-    const uint32_t t0 = blockIdx.y * TT;
-    const uint32_t nt = min((uint32_t)TT, T - t0);
     const bool e_ok = e < E;
+    if (LIST) T = *count;
+  for (uint32_t t0 = blockIdx.y * TT; t0 < T; t0 += gridDim.y * TT) {
+    const uint32_t nt = min((uint32_t)TT, T - t0);
+    __shared__ uint32_t tok_of[TT];
+    if (LIST) {
+        __syncthreads();
+        if (threadIdx.x < TT) tok_of[threadIdx.x] = threadIdx.x < nt ? list[t0 + threadIdx.x] : 0u;
+        __syncthreads();
+    }
     float sum[TT];
 #pragma unroll
     for (int i = 0; i < TT; ++i) sum[i] = 0.0f;
@@ -58,7 +67,7 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
             const uint32_t tok = i / (kRouterChunk / 8), c8 = (i % (kRouterChunk / 8)) * 8u;
             xr[q] = make_uint4(0, 0, 0, 0);
             if (i < TT * (kRouterChunk / 8) && tok < nt && c8 < cols)
-                xr[q] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(t0 + tok) * H + c0 + c8));
+                xr[q] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(LIST ? tok_of[tok] : t0 + tok) * H + c0 + c8));
         }
         wr = make_uint4(0, 0, 0, 0);
         if (e_ok && lane * 8u < cols)
@@ -98,14 +107,15 @@ __global__ void __launch_bounds__(WARPS * 32) router_logits_kernel(
             sum[tok] = s;
         }
     }
-    if (!e_ok) return;
 #pragma unroll
     for (int tok = 0; tok < TT; ++tok) {
         float v = sum[tok];
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) v = __fadd_rn(v, __shfl_down_sync(0xFFFFFFFFu, v, off));
-        if (lane == 0 && (uint32_t)tok < nt) logits[(size_t)(t0 + tok) * E + e] = v;
+        if (e_ok && lane == 0 && (uint32_t)tok < nt) logits[(size_t)(LIST ? tok_of[tok] : t0 + tok) * E + e] = v;
     }
+    if (!LIST) break;
+  }
 }
 
 // A single token (decode): the projection is a latency problem -- E rows of H BF16 values, a few bytes each
@@ -297,13 +307,13 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
         router_logits_tiny_kernel<2><<<(E + 1) / 2, 64, 0, s>>>(x, wg, T, H, E, logits);   // the 2-token build is the faster one even for one token (10 vs 31 us)
     } else if (T <= 8) {
         dim3 grid((E + 1) / 2, 1);
-        router_logits_kernel<2, 8><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+        router_logits_kernel<2, 8, false><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits, nullptr, nullptr);
     } else if (T <= 32) {
         dim3 grid((E + 1) / 2, (T + 15) / 16);
-        router_logits_kernel<2, 16><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits);
+        router_logits_kernel<2, 16, false><<<grid, 64, 0, s>>>(x, wg, T, H, E, logits, nullptr, nullptr);
     } else if (big_tiles < 96) {
         dim3 grid((E + 7) / 8, (T + 15) / 16);
-        router_logits_kernel<8, 16><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits);
+        router_logits_kernel<8, 16, false><<<grid, 256, 0, s>>>(x, wg, T, H, E, logits, nullptr, nullptr);
     } else {
         static bool attr[64] = {};   // the shared-memory opt-in is per device
         const size_t smem = (size_t)(kBigTT + kBigWarps * kBigRW) * kRouterChunk * sizeof(float);
@@ -325,14 +335,15 @@ constexpr int kRouteWarps = 4;
 __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
     uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
-    const uint32_t* __restrict__ forced_ids) {
+    const uint32_t* __restrict__ forced_ids, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count) {
     extern __shared__ float smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
     float* score = smem + (size_t)warp * 2u * E;
     float* choice = score + E;
-    const uint32_t tok = blockIdx.x * kRouteWarps + warp;
-    if (tok >= T) return;
+    if (list) T = *count;     // tokens list[0 .. *count), the grid strides over them
+  for (uint32_t slot = blockIdx.x * kRouteWarps + warp; slot < T; slot += gridDim.x * kRouteWarps) {
+    const uint32_t tok = list ? list[slot] : slot;
     const float* lg = logits + (size_t)tok * E;
     bool bad = false;
 
@@ -421,6 +432,237 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
         weights[(size_t)tok * k + lane] = w;
     }
     if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) atomicOr(status, kStatusNonFiniteLogit);
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Fast router for large token counts.
+//
+// The canonical projection above runs on the FP32 pipe (T * E * H multiply-adds); for thousands of
+// tokens it costs as much as a third of the expert GEMMs.  Here the projection runs on the tensor
+// cores first (launch_router_tc: same products, another summation order, so its logits differ from
+// the canonical ones in the last bits), and this kernel turns those APPROXIMATE logits into the
+// EXACT routing decision:
+//   1. scores and selection values from the approximate logits, and for every expert a bound eps
+//      on how far its selection value can be from the canonical one: |dlogit| <= delta (see below),
+//      times the local slope of the score function, plus rounding slack;
+//   2. top-k by (value desc, index asc) as usual.  The order of two experts is CERTAIN when their
+//      values differ by more than the sum of their bounds; the token is "safe" when every
+//      consecutive pair of the k selected is certain and the k-th is certain against the largest
+//      value + bound among all the others;
+//   3. the logits of the k selected experts are recomputed in the canonical lane-strided order
+//      (k * H multiply-adds), which gives bit-exact routing weights -- and checks delta: if any of
+//      them is further than delta / 2 from the approximate logit the token is not trusted;
+//   4. tokens that are not safe go on a list; the canonical kernels recompute them completely.
+// delta = 2^-13 * max(2, max_e |logit|): both summation orders round at most a few hundred partial
+// sums of magnitude <= that maximum (relative 2^-24 each; the tensor cores may truncate, 2^-23), so
+// the true distance is orders of magnitude below delta, and step 3 verifies that on every token.
+// The softmax rule normalises over all experts and is not served by this path.
+__device__ __forceinline__ float score_and_slope(const RouterParams& p, float l, float& slope) {
+    float cap = 1.0f;
+    if (p.softcap > 0.0f) {
+        const float th = tanhf(__fdiv_rn(l, p.softcap));
+        l = __fmul_rn(th, p.softcap);
+        cap = 1.0f;     // d/dl of the soft cap is 1 - th^2 <= 1
+    }
+    float sc;
+    if (p.score_kind == STRATA_MOE_SCORE_SIGMOID) {
+        sc = sigmoid_two_branch(l);
+        slope = sc * (1.0f - sc);
+    } else if (p.score_kind == STRATA_MOE_SCORE_SIGMOID_PLAIN) {
+        sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
+        slope = sc * (1.0f - sc);
+    } else {
+        sc = sqrtf(l > 20.0f ? l : log1pf(expf_libm(l)));
+        const float sg = 1.0f / (1.0f + __expf(-l));
+        slope = sc > 0.0f ? sg / (2.0f * sc) : 1.0f;
+    }
+    slope *= cap;
+    return sc;
+}
+
+constexpr int kFastWarps = 4;
+
+__global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
+    RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias,
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
+    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* __restrict__ list,
+    uint32_t* __restrict__ count, unsigned long long* __restrict__ recheck_total, uint32_t* status) {
+    extern __shared__ __align__(16) float fsm[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t E = p.experts, k = p.top_k;
+    const size_t per_warp = 3u * (size_t)E + H / 2u;     // floats: score, choice, eps, then the token's x row (bf16)
+    float* score = fsm + warp * per_warp;
+    float* choice = score + E;
+    float* eps = choice + E;
+    unsigned short* xs = reinterpret_cast<unsigned short*>(eps + E);
+    for (uint32_t tok = blockIdx.x * kFastWarps + warp; tok < T; tok += gridDim.x * kFastWarps) {
+        const float* lg = logits + (size_t)tok * E;
+        bool bad = false;
+        float mx = 0.0f;
+        for (uint32_t e = lane; e < E; e += 32u) {
+            const float l = lg[e];
+            bad |= !isfinite(l);
+            mx = fmaxf(mx, fabsf(l));
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+        const float delta = 1.220703125e-4f * fmaxf(2.0f, mx);
+        for (uint32_t e = lane; e < E; e += 32u) {
+            float slope;
+            const float sc = score_and_slope(p, lg[e], slope);
+            const float b = bias ? bias[e] : 0.0f;
+            bad |= !isfinite(b);
+            score[e] = sc;
+            choice[e] = __fadd_rn(sc, b);
+            eps[e] = 1.25f * slope * delta + 4.8e-7f * (fabsf(sc) + fabsf(b)) + 1e-30f;
+        }
+        // this token's activation row: 16-byte loads into shared memory
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
+            for (uint32_t i = lane; i < H / 8u; i += 32u) reinterpret_cast<uint4*>(xs)[i] = __ldg(src + i);
+        }
+        __syncwarp();
+        float my_c = 0.0f, my_e = 0.0f;
+        uint32_t my_id = 0;
+        for (uint32_t r = 0; r < k; ++r) {
+            float bv = -INFINITY;
+            uint32_t bi = 0xFFFFFFFFu;
+            for (uint32_t e = lane; e < E; e += 32u) {
+                const float v = choice[e];
+                if (v > bv || bi == 0xFFFFFFFFu) { bv = v; bi = e; }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+                const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (bi >= E) { bad = true; bi = 0; }
+            if (lane == r) { my_id = bi; my_c = bv; my_e = eps[bi]; }
+            if (lane == 0) choice[bi] = -INFINITY;
+            __syncwarp();
+        }
+        // the largest value any expert outside the selection could really have
+        float rest = -INFINITY;
+        for (uint32_t e = lane; e < E; e += 32u) rest = fmaxf(rest, choice[e] + eps[e]);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) rest = fmaxf(rest, __shfl_xor_sync(0xFFFFFFFFu, rest, off));
+        const float next_c = __shfl_down_sync(0xFFFFFFFFu, my_c, 1);
+        const float next_e = __shfl_down_sync(0xFFFFFFFFu, my_e, 1);
+        bool certain = true;
+        if (lane + 1u < k) certain = (my_c - my_e) > (next_c + next_e);
+        else if (lane + 1u == k) certain = (my_c - my_e) > rest;
+        bool safe = __all_sync(0xFFFFFFFFu, certain) && !__any_sync(0xFFFFFFFFu, bad);
+        // canonical-order logits of the selected experts
+        float my_logit = 0.0f;
+        // Two experts at a time: lane l owns columns l, l + 32, ... of both rows; sixteen 2-byte loads per row are
+        // issued before their multiply-adds, so 32 loads are in flight and the two sums form independent chains.
+        // Per (token, expert) the products are still added in increasing column order, then folded by the
+        // canonical five shuffle-down rounds.
+        const uint32_t per_lane = H / 32u;
+        for (uint32_t r = 0; r < k && safe; r += 2u) {
+            const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, my_id, r);
+            const bool two = r + 1u < k;
+            const uint32_t e1 = two ? __shfl_sync(0xFFFFFFFFu, my_id, r + 1u) : e0;
+            const unsigned short* w0 = reinterpret_cast<const unsigned short*>(wg) + (size_t)e0 * H + lane;
+            const unsigned short* w1 = reinterpret_cast<const unsigned short*>(wg) + (size_t)e1 * H + lane;
+            float a0 = 0.0f, a1 = 0.0f;
+            for (uint32_t j0 = 0; j0 < per_lane; j0 += 16u) {
+                unsigned short v0[16], v1[16];
+#pragma unroll
+                for (uint32_t q = 0; q < 16u; ++q) {
+                    const bool in = j0 + q < per_lane;
+                    v0[q] = in ? __ldg(w0 + (size_t)(j0 + q) * 32u) : (unsigned short)0;
+                    v1[q] = in && two ? __ldg(w1 + (size_t)(j0 + q) * 32u) : (unsigned short)0;
+                }
+#pragma unroll
+                for (uint32_t q = 0; q < 16u; ++q)
+                    if (j0 + q < per_lane) {
+                        const float xv = __uint_as_float((uint32_t)xs[lane + (j0 + q) * 32u] << 16);
+                        a0 = __fmaf_rn(xv, __uint_as_float((uint32_t)v0[q] << 16), a0);
+                        a1 = __fmaf_rn(xv, __uint_as_float((uint32_t)v1[q] << 16), a1);
+                    }
+            }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                a0 = __fadd_rn(a0, __shfl_down_sync(0xFFFFFFFFu, a0, off));
+                a1 = __fadd_rn(a1, __shfl_down_sync(0xFFFFFFFFu, a1, off));
+            }
+            a0 = __shfl_sync(0xFFFFFFFFu, a0, 0);
+            a1 = __shfl_sync(0xFFFFFFFFu, a1, 0);
+            // the bound itself is checked on every token
+            if (!(fabsf(a0 - lg[e0]) <= 0.5f * delta) || (two && !(fabsf(a1 - lg[e1]) <= 0.5f * delta))) safe = false;
+            if (lane == r) my_logit = a0;
+            if (two && lane == r + 1u) my_logit = a1;
+        }
+        safe = __all_sync(0xFFFFFFFFu, safe);
+        if (!safe) {
+            if (lane == 0) {
+                list[atomicAdd(count, 1u)] = tok;
+                atomicAdd(recheck_total, 1ull);
+            }
+            __syncwarp();
+            continue;
+        }
+        float slope_unused;
+        const float my_w = lane < k ? score_and_slope(p, my_logit, slope_unused) : 0.0f;
+        float sum = p.norm_init;
+        for (uint32_t r = 0; r < k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, my_w, r));
+        float w;
+        if (p.normalize) {
+            if (!(sum > 0.0f) || !isfinite(sum)) {
+                if (lane == 0) atomicOr(status, kStatusBadNormaliser);
+                w = 0.0f;
+            } else {
+                w = __fmul_rn(__fdiv_rn(my_w, sum), p.weight_scale);
+            }
+        } else {
+            w = __fmul_rn(my_w, p.weight_scale);
+        }
+        if (lane < k) {
+            ids[(size_t)tok * k + lane] = my_id;
+            weights[(size_t)tok * k + lane] = w;
+        }
+        __syncwarp();
+    }
+}
+
+bool route_fast_supported(const RouterParams& p, uint32_t H) {
+    if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) return false;
+    if (p.experts % 128u || H % 64u) return false;
+    return (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float)) <= 200u * 1024u;
+}
+
+// logits: approximate [T, E] (tensor-core projection); list [T], count, recheck_total: device scratch.
+// On return (stream order) ids / weights hold the canonical routing of every token and the canonical
+// logits of the rechecked tokens have replaced their approximate rows.
+void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
+                       const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,
+                       uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
+                       cudaStream_t s) {
+    if (T == 0) return;
+    const size_t smem = (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float));
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr[dev]) {
+        cudaFuncSetAttribute(route_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr[dev] = true;
+    }
+    cudaMemsetAsync(count, 0, sizeof(uint32_t), s);
+    uint32_t grid = (T + kFastWarps - 1) / kFastWarps;
+    if (grid > (uint32_t)kNumSMs * 4u) grid = (uint32_t)kNumSMs * 4u;
+    route_fast_kernel<<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
+                                                          recheck_total, status);
+    // the tokens on the list, completely in the canonical order (few: the grids stride over the list)
+    const uint32_t E = p.experts;
+    dim3 g2((E + 7) / 8, 32);
+    router_logits_kernel<8, 16, true><<<g2, 256, 0, s>>>(x, wg, T, H, E, logits, list, count);
+    const size_t smem_r = (size_t)kRouteWarps * 2u * E * sizeof(float);
+    route_kernel<<<64, kRouteWarps * 32, smem_r, s>>>(p, logits, bias, T, ids, weights, status, nullptr, list, count);
+    g_kernel_launches += 3;
 }
 
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
@@ -428,7 +670,7 @@ void launch_route(const RouterParams& p, const float* logits, const float* bias,
     if (T == 0) return;
     const size_t smem = (size_t)kRouteWarps * 2u * p.experts * sizeof(float);
     route_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, s>>>(
-        p, logits, bias, T, ids, weights, status, forced_ids);
+        p, logits, bias, T, ids, weights, status, forced_ids, nullptr, nullptr);
     ++g_kernel_launches;
 }
 

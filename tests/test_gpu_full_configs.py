@@ -64,6 +64,20 @@ def full_layer(ctx, cfg, T, sub, tight):
     sub = np.asarray(sub)
     ref = Hh.run_oracle(cfg, layer.x.cpu(), token_subset=sub)
     check_routing(aux, ref)
+    if T >= 512 and cfg.score_kind != synth.SCORE_SOFTMAX:
+        # without the logits in the aux outputs a batch this large takes the fast router (tensor-core projection,
+        # exact recheck): the routing and therefore the whole result must be bit-identical all the same
+        before = ctx.stats()
+        out3, aux3 = ml.forward(layer.x, want_aux=True, aux_logits=False)
+        ctx.synchronize()
+        after = ctx.stats()
+        assert after.router_fast_tokens - before.router_fast_tokens == T
+        assert after.router_rechecked_tokens - before.router_rechecked_tokens <= T // 4
+        assert np.array_equal(aux3["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
+        assert np.array_equal(aux3["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
+        assert np.array_equal(aux3["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
+        assert torch.equal(out3, out)
+        del out3, aux3
     rel, mx = Hh.error_metrics(out[torch.from_numpy(sub).cuda()].cpu().numpy(), ref["out"])
     counts = aux["counts"].cpu().numpy()
     release(ml)

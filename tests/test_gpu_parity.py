@@ -302,6 +302,36 @@ def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     assert rel <= TENSOR_REL_L2 and mx <= MAX_ABS, (rel, mx)
 
 
+@pytest.mark.parametrize("kind,zipf,dup", [(synth.SCORE_SIGMOID, 0.0, False), (synth.SCORE_SIGMOID_PLAIN, 1.1, False),
+                                           (synth.SCORE_SQRTSOFTPLUS, 0.0, False), (synth.SCORE_SIGMOID, 0.0, True)])
+def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
+    """Tensor-core projection + exact recheck against the canonical router: ids and weights bit for bit.
+    `dup` makes two experts identical, so that every token has an exact tie the fast path must not decide."""
+    monkeypatch.setenv("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", "1")
+    cfg = small(synth.FMT_MXFP4, T=700, E=128, k=8, H=512, I=256, score_kind=kind, zipf_s=zipf,
+                weight_scale=1.5, name=f"fast_router{kind}{int(dup)}")
+    layer = synth.build_layer(cfg, "cuda")
+    if dup:
+        layer.router_w[77] = layer.router_w[3]
+    ml = MoeLayer(ctx, cfg, max_tokens=cfg.T)
+    ml.load_synth(layer)
+    ids_x, w_x, _ = ml.route(layer.x, want_logits=True)      # canonical projection
+    before = ctx.stats()
+    ids_f, w_f = ml.route(layer.x)                            # fast path
+    ctx.synchronize()
+    after = ctx.stats()
+    assert after.router_fast_tokens - before.router_fast_tokens == cfg.T
+    rechecked = after.router_rechecked_tokens - before.router_rechecked_tokens
+    assert torch.equal(ids_f, ids_x)
+    assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
+    if dup:
+        # a token whose top-8 holds one of the twins has an exact tie and must have been rechecked
+        touched = int(((ids_x == 3) | (ids_x == 77)).any(dim=1).sum().item())
+        assert rechecked >= touched > 0
+    else:
+        assert rechecked <= cfg.T // 3
+
+
 @pytest.mark.parametrize("kind", [synth.SCORE_SIGMOID, synth.SCORE_SQRTSOFTPLUS])
 def test_hash_routing_weights(ctx, kind):
     """Experts given per token (hash routing): ids are passed through, weights equal the oracle's
