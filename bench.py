@@ -263,7 +263,8 @@ def measure_layer(ctx, cfg, T, steps, warmup, peaks, flush, cpu_seconds, want_pa
         flush.zero_()
         step()
     ctx.synchronize()
-    launches0 = ctx.stats().kernel_launches
+    st0 = ctx.stats()
+    launches0 = st0.kernel_launches
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     torch.cuda.synchronize()
     for a, b in evs:
@@ -272,7 +273,10 @@ def measure_layer(ctx, cfg, T, steps, warmup, peaks, flush, cpu_seconds, want_pa
         step()
         b.record()
     torch.cuda.synchronize()
-    launches = ctx.stats().kernel_launches - launches0
+    st1 = ctx.stats()
+    launches = st1.kernel_launches - launches0
+    router_stats = {"fast_tokens_per_step": (st1.router_fast_tokens - st0.router_fast_tokens) / steps,
+                    "rechecked_tokens_per_step": (st1.router_rechecked_tokens - st0.router_rechecked_tokens) / steps}
     ms_per_step = float(np.mean([a.elapsed_time(b) for a, b in evs]))
 
     # phase timing (separate iterations: the phase events serialise the host)
@@ -315,6 +319,7 @@ def measure_layer(ctx, cfg, T, steps, warmup, peaks, flush, cpu_seconds, want_pa
         "e2e": {"value": T / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": T * cfg.H * 2,
                 "d2h_bytes_per_step": T * cfg.H * 4},
         "gpu_launches": int(launches),
+        "router": router_stats,
     }
     layer_bytes = active * expert_weight_bytes(cfg) + cfg.E * cfg.H * 2 + 3 * cfg.I_shared * cfg.H * 2
     rec["layer_hbm_gbs"] = layer_bytes / (ms_per_step * 1e-3) / 1e9
@@ -404,7 +409,7 @@ def run_single(args, cfg, T):
         "config": dict(main["config"], parallelism="ep1"),
     }
     for k in ("layer_hbm_gbs", "layer_hbm_frac", "layer_tflops", "layer_tensor_frac", "phase_ms", "roofline",
-              "cpu_baseline", "e2e", "gpu_launches", "parity", "sweep"):
+              "cpu_baseline", "e2e", "gpu_launches", "router", "parity", "sweep"):
         if k in main:
             line[k] = main[k]
     line["clocks"] = clocks

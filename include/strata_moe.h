@@ -171,6 +171,13 @@ int strata_moe_set_shared(strata_moe_layer* layer, int role, const void* weights
  * Requires expert_count == experts (single-GPU layer). */
 int strata_moe_forward(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens, float* out,
                        const strata_moe_aux* aux);
+/* The same layer AFTER routing: the experts of every token and their routing weights are given
+ * (device, [T, k], selection-rank order), e.g. by a router that runs on other features than the
+ * experts (Kimi-K3 routes on the hidden state and runs the experts on a latent, see
+ * strata_moe_latent_*) or by a token-id table.  No shared expert term.
+ * ref: the part of sparse_mlp after the route call, src/models/glm52/glm_runtime.cpp:1521-1618. */
+int strata_moe_forward_routed(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens, const uint32_t* ids,
+                              const float* weights, float* out);
 /* Same call with HOST buffers (pageable or pinned): copies x in, runs, copies out back and
  * waits.  This is the call shape of the reference, whose commands take host spans
  * (ref: include/strata/cuda_backend.hpp:1147-1153). */
@@ -248,6 +255,32 @@ int strata_moe_enqueue_dense(strata_moe_layer* layer, const float* hidden_host, 
                              const uint32_t* experts, const float* coefficients, uint32_t n_experts,
                              int with_shared);
 int strata_moe_collect_dense(strata_moe_layer* layer, float* routed_output, float* shared_output);
+
+/* ---- LatentMoE wrapper (Kimi-K3) ------------------------------------------------------------
+ * ref: kimi_latent_moe_layer, include/strata/kimi_k3_layer.hpp:257-261,
+ * src/models/kimi_k3/kimi_k3_layer.cpp:781-1001.  Routing reads the raw hidden state [T, H]; the routed
+ * experts run on latent = x * down^T (BF16 [HL, H]); their routing-weighted mixture is RMS-normalised
+ * in the latent space (weight fp32 [HL], kimi_rms_norm) and projected back with up (BF16 [H, HL]); the
+ * BF16 shared experts (concatenated: gate / up [Is, H], down [H, Is]) run on the raw hidden state
+ * and add in.  desc describes the EXPERT side: desc->hidden = HL, desc->shared_intermediate = Is
+ * (0 = none), every expert resident; model_hidden = H.  Expert weights are registered on
+ * strata_moe_latent_experts() with strata_moe_set_expert (gate / up [I, HL], down [HL, I]).
+ * The mixture is summed in selection-rank order (the reference sums in ascending expert order per
+ * worker: a reassociation, inside the layer tolerance); the latent and the normalised mixture are
+ * rounded to BF16 before the expert and the output GEMMs. */
+typedef struct strata_moe_latent strata_moe_latent;
+int strata_moe_latent_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* desc, uint32_t model_hidden,
+                             float rms_epsilon, strata_moe_latent** out);
+void strata_moe_latent_destroy(strata_moe_latent* lat);
+strata_moe_layer* strata_moe_latent_experts(strata_moe_latent* lat);
+int strata_moe_latent_set_router(strata_moe_latent* lat, const void* gate_bf16 /* [E, H] */, const float* bias,
+                                 int source);
+int strata_moe_latent_set_projections(strata_moe_latent* lat, const void* down_bf16 /* [HL, H] */,
+                                      const void* up_bf16 /* [H, HL] */, const float* norm_f32 /* [HL] */, int source);
+int strata_moe_latent_set_shared(strata_moe_latent* lat, int role, const void* weights_bf16, int source);
+/* x_bf16 [T, H] and out [T, H] fp32 are device pointers; ids / weights (device, [T, k]) may be NULL. */
+int strata_moe_latent_forward(strata_moe_latent* lat, const void* x_bf16, uint32_t tokens, float* out,
+                              uint32_t* ids, float* weights);
 
 /* ---- weight handles and handle-based commands: the reference backend's own call shape -----
  * ref: CudaBackend::upload(device, CudaWeightDescriptor, weights, scales, CudaWeight&),

@@ -29,6 +29,7 @@ REF_SOURCES = [
     "src/platform/numa_topology.cpp",
     "src/platform/safetensors.cpp",
     "src/platform/json_cursor.cpp",
+    "src/platform/trace.cpp",
     "src/models/dsv4/deepseek_ops.cpp",
     "src/models/glm52/glm_ops.cpp",
     "src/models/laguna/laguna_ops.cpp",

@@ -77,6 +77,36 @@ def run_oracle(cfg, x_bf16, token_subset=None, accumulate_double=False):
     return res
 
 
+def run_oracle_latent(cfg, x_bf16, token_subset=None):
+    """LatentMoE (cfg.H_model > 0): routing for all tokens, outputs [len(subset), H_model] for the subset."""
+    import ctypes as C
+    T = x_bf16.shape[0]
+    w, b = synth.gen_router(cfg)
+    lat = synth.gen_latent(cfg)
+    desc = oracle_desc(cfg, T)
+    xs, ws = np_u16(x_bf16), np_u16(w)
+    ids = np.empty((T, cfg.k), np.uint32)
+    wts = np.empty((T, cfg.k), np.float32)
+    bias = np.ascontiguousarray(b.numpy()) if b is not None else None
+    down, up = np_u16(lat["down"]), np_u16(lat["up"])
+    norm = np.ascontiguousarray(lat["norm"].numpy())
+    lib = O.port()
+    def call(experts, shared, sub, out):
+        return lib.orc_latent_moe_layer(
+            C.byref(desc), cfg.H_model, float(cfg.rms_epsilon), xs.ctypes.data_as(O.u16p), ws.ctypes.data_as(O.u16p),
+            bias.ctypes.data_as(O.f32p) if bias is not None else None, down.ctypes.data_as(O.u16p),
+            up.ctypes.data_as(O.u16p), norm.ctypes.data_as(O.f32p), experts, C.byref(shared) if shared is not None else None,
+            sub.ctypes.data_as(O.u32p) if sub is not None else None, 0 if sub is None else len(sub),
+            ids.ctypes.data_as(O.u32p), wts.ctypes.data_as(O.f32p), out.ctypes.data_as(O.f32p) if out is not None else None)
+    assert call(None, None, None, None) == 0            # routing only: which experts does the subset need
+    sub = np.arange(T, dtype=np.uint32) if token_subset is None else np.asarray(token_subset, np.uint32)
+    experts, keep = oracle_experts(cfg, ids[sub].reshape(-1))
+    shared, keep2 = oracle_shared(cfg)
+    out = np.empty((len(sub), cfg.H_model), np.float32)
+    assert call(experts, shared, sub, out) == 0
+    return dict(ids=ids, weights=wts, out=out, subset=sub)
+
+
 def error_metrics(got, want):
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)

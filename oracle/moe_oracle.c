@@ -154,6 +154,67 @@ ORC_API float orc_expf_replica(float x, int use_fma) {
     return (float)y;
 }
 
+/* --------------------------------------------------------------------------
+ * log1pf restated as the single-precision algorithm glibc 2.39 ships for it (the classic
+ * fdlibm s_log1pf: argument reduction 1 + x = 2^k (1 + f), f / (2 + f) series with seven
+ * coefficients, ln2 split in two), every operation a separately rounded float operation
+ * (the host build does not contract them).  The CUDA router evaluates the same steps so that
+ * its sqrt(softplus) scores are bit-identical to the host's; tests/test_oracle_golden.py
+ * checks this restatement against the libm of the machine it runs on.  Inputs here are
+ * expf(logit) >= 0; the branches for x <= -1 are kept for completeness. */
+ORC_API float orc_log1pf_replica(float x) {
+    const float ln2_hi = 6.9313812256e-01f, ln2_lo = 9.0580006145e-06f;
+    const float Lp1 = 6.6666668653e-01f, Lp2 = 4.0000000596e-01f, Lp3 = 2.8571429849e-01f, Lp4 = 2.2222198546e-01f,
+                Lp5 = 1.8183572590e-01f, Lp6 = 1.5313838422e-01f, Lp7 = 1.4798198640e-01f;
+    float hfsq, f = 0.0f, c = 0.0f, s, z, R, u;
+    int32_t k = 1, hx = (int32_t)f32_bits(x), hu = 0, ax = hx & 0x7fffffff;
+    if (hx < 0x3ed413d7) {                       /* x < 0.41422 */
+        if (ax >= 0x3f800000) return x == -1.0f ? -INFINITY : NAN;
+        if (ax < 0x31000000) return ax < 0x24800000 ? x : x - x * x * 0.5f;
+        if (hx > 0 || hx <= (int32_t)0xbe95f61f) { k = 0; f = x; hu = 1; }
+    }
+    if (hx >= 0x7f800000) return x + x;
+    if (k != 0) {
+        if (hx < 0x5a000000) {
+            u = 1.0f + x;
+            hu = (int32_t)f32_bits(u);
+            k = (hu >> 23) - 127;
+            c = (k > 0) ? 1.0f - (u - x) : x - (u - 1.0f);
+            c /= u;
+        } else {
+            u = x;
+            hu = (int32_t)f32_bits(u);
+            k = (hu >> 23) - 127;
+            c = 0.0f;
+        }
+        hu &= 0x007fffff;
+        if (hu < 0x3504f7) {
+            u = bits_f32((uint32_t)hu | 0x3f800000u);
+        } else {
+            k += 1;
+            u = bits_f32((uint32_t)hu | 0x3f000000u);
+            hu = (0x00800000 - hu) >> 2;
+        }
+        f = u - 1.0f;
+    }
+    hfsq = 0.5f * f * f;
+    if (hu == 0) {
+        if (f == 0.0f) {
+            if (k == 0) return 0.0f;
+            c += (float)k * ln2_lo;
+            return (float)k * ln2_hi + c;
+        }
+        R = hfsq * (1.0f - 0.66666666666666666f * f);
+        if (k == 0) return f - R;
+        return (float)k * ln2_hi - ((R - ((float)k * ln2_lo + c)) - f);
+    }
+    s = f / (2.0f + f);
+    z = s * s;
+    R = z * (Lp1 + z * (Lp2 + z * (Lp3 + z * (Lp4 + z * (Lp5 + z * (Lp6 + z * Lp7))))));
+    if (k == 0) return f - (hfsq - s * (hfsq + R));
+    return (float)k * ln2_hi - ((hfsq - (s * (hfsq + R) + ((float)k * ln2_lo + c))) - f);
+}
+
 /* ------------------------------------------------------ weight matrices */
 typedef struct {
     int32_t fmt;
@@ -841,4 +902,84 @@ ORC_API int orc_dsv4_fp8_shared(float* out, const float* in, const uint8_t* w1, 
     orc_quantize_activation_e4m3(scratch, intermediate);
     for (uint64_t row = 0; row < hidden; ++row) out[row] = orc_bf16_round(dsv4_fp8_row(scratch, w2, s2, intermediate, row));
     return 0;
+}
+
+/* ======================================================================================
+ * LatentMoE (Kimi-K3), following kimi_latent_moe_layer, src/models/kimi_k3/kimi_k3_layer.cpp:781-1001:
+ *   route on the raw hidden state (router logits in this file's canonical order -- the reference's
+ *   kimi_bf16_matmul uses an 8-lane FMA order, see the note on orc_router_logits);
+ *   latent = x . down^T (BF16 weights, FP32 accumulation);  every selected expert runs on the FP32
+ *   latent (gate/up, SiTU-GLU, down) and weight * output is added to the token's mixture in
+ *   ASCENDING EXPERT order (one worker's order, :906-938);  the mixture is RMS-normalised
+ *   (kimi_rms_norm, src/models/kimi_k3/kimi_k3_ops.cpp:16-38) and projected back with up;
+ *   the shared experts (one concatenated BF16 expert) run on the raw hidden state and add in.
+ * Plain sequential FP32 sums for the BF16 projections (the reference's AVX2 order differs in the
+ * last bits; comparisons with it are tolerance-level).
+ * d->H is the latent width, H_model the layer's input width.  Expert FFNs only for token_subset.
+ * ====================================================================================== */
+static void orc_bf16_linear(const float* x, const uint16_t* w, uint32_t rows, uint32_t cols, float* y) {
+    for (uint32_t r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        const uint16_t* wr = w + (size_t)r * cols;
+        for (uint32_t c = 0; c < cols; ++c) sum += x[c] * orc_bf16_to_f32(wr[c]);
+        y[r] = sum;
+    }
+}
+
+ORC_API int orc_latent_moe_layer(const orc_layer_desc* d, uint32_t H_model, float rms_epsilon, const uint16_t* x_bf16,
+                                 const uint16_t* router_w, const float* bias, const uint16_t* latent_down,
+                                 const uint16_t* latent_up, const float* latent_norm, const orc_expert* experts,
+                                 const orc_expert* shared, const uint32_t* token_subset, uint32_t n_subset,
+                                 uint32_t* ids, float* weights, float* out) {
+    const uint32_t T = d->T, HL = d->H, I = d->I, E = d->E, k = d->k;
+    float* logits = (float*)malloc((size_t)T * E * sizeof(float));
+    orc_router_logits(x_bf16, router_w, T, H_model, E, logits);
+    int rc = orc_route(&d->router, logits, bias, T, ids, weights);
+    free(logits);
+    if (rc) return rc;
+    if (!out) return 0;
+    const uint32_t n = token_subset ? n_subset : T;
+    int fail = 0;
+#pragma omp parallel for schedule(dynamic, 1)
+    for (uint32_t s = 0; s < n; ++s) {
+        const uint32_t t = token_subset ? token_subset[s] : s;
+        float* xf = (float*)malloc((size_t)H_model * sizeof(float));
+        float* latent = (float*)malloc((size_t)HL * sizeof(float));
+        float* mix = (float*)calloc(HL, sizeof(float));
+        float* y = (float*)malloc((size_t)(HL > H_model ? HL : H_model) * sizeof(float));
+        const uint32_t Imax = (d->I_shared > I ? d->I_shared : I);
+        float* a = (float*)malloc((size_t)Imax * sizeof(float));
+        float* u = (float*)malloc((size_t)Imax * sizeof(float));
+        for (uint32_t h = 0; h < H_model; ++h) xf[h] = orc_bf16_to_f32(x_bf16[(size_t)t * H_model + h]);
+        orc_bf16_linear(xf, latent_down, HL, H_model, latent);
+        /* ascending expert order over the token's selection */
+        for (uint32_t e = 0; e < E; ++e) {
+            float w = 0.0f;
+            for (uint32_t r = 0; r < k; ++r)
+                if (ids[(size_t)t * k + r] == e) { w = weights[(size_t)t * k + r]; break; }
+            if (w == 0.0f) continue;
+            if (orc_expert_ffn(&experts[e], latent, 1.0f, 0, d->accumulate_double, a, u, y)) {
+#pragma omp critical
+                fail = 1;
+                break;
+            }
+            for (uint32_t h = 0; h < HL; ++h) mix[h] += w * y[h];
+        }
+        float ms = 0.0f;
+        for (uint32_t h = 0; h < HL; ++h) ms += mix[h] * mix[h];
+        const float scale = 1.0f / sqrtf(ms / (float)HL + rms_epsilon);
+        for (uint32_t h = 0; h < HL; ++h) mix[h] = latent_norm[h] * (mix[h] * scale);
+        float* o = out + (size_t)s * H_model;
+        orc_bf16_linear(mix, latent_up, H_model, HL, o);
+        if (shared) {
+            if (orc_expert_ffn(shared, xf, 1.0f, 0, d->accumulate_double, a, u, y)) {
+#pragma omp critical
+                fail = 1;
+            } else {
+                for (uint32_t h = 0; h < H_model; ++h) o[h] += y[h];
+            }
+        }
+        free(xf); free(latent); free(mix); free(y); free(a); free(u);
+    }
+    return fail;
 }

@@ -80,6 +80,8 @@ def port():
         lib.orc_silu.argtypes = [C.c_float]
         lib.orc_expf_replica.restype = C.c_float
         lib.orc_expf_replica.argtypes = [C.c_float, C.c_int]
+        lib.orc_log1pf_replica.restype = C.c_float
+        lib.orc_log1pf_replica.argtypes = [C.c_float]
         lib.orc_dequant_row.argtypes = [C.POINTER(Matrix), C.c_uint32, C.c_int, f32p]
         lib.orc_matvec.argtypes = [C.POINTER(Matrix), f32p, f32p, C.c_uint32, C.c_uint32, C.c_int]
         lib.orc_router_logits.restype = None
@@ -104,6 +106,8 @@ def port():
                                         C.c_float, C.c_float, f32p]
         lib.orc_dsv4_fp8_shared.argtypes = [f32p, f32p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint32, C.c_uint32,
                                             C.c_float, f32p]
+        lib.orc_latent_moe_layer.argtypes = [C.POINTER(LayerDesc), C.c_uint32, C.c_float, u16p, u16p, f32p, u16p, u16p, f32p,
+                                             C.POINTER(Expert), C.POINTER(Expert), u32p, C.c_uint32, u32p, f32p, f32p]
         lib.orc_experts_all.argtypes = [C.POINTER(LayerDesc), u16p, C.POINTER(Expert), u32p, f32p,
                                         u32p, u32p, f32p]
         _port = lib
@@ -143,6 +147,12 @@ def ref():
         lib.ref_dsv4_route_hash.argtypes = [f32p, u32p, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
         lib.ref_dsv4_quantize.argtypes = [f32p, C.c_uint32]
         lib.ref_kimi_situ_glu.argtypes = [f32p, f32p, f32p, C.c_uint32, C.c_float, C.c_float]
+        lib.ref_dsv4_tile_shard.restype = C.c_uint64
+        lib.ref_dsv4_tile_shard.argtypes = [u8p, u8p, u8p, u8p, u8p, u8p, u8p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]
+        lib.ref_parse_route_trace.restype = C.c_int64
+        lib.ref_parse_route_trace.argtypes = [C.c_char_p, C.POINTER(C.c_uint64), u32p, f32p, C.c_uint64, C.c_uint64]
+        lib.ref_kimi_latent_moe.argtypes = [f32p, f32p, C.c_uint32, u16p, f32p, u16p, u16p, f32p, u16p, u16p, u16p,
+                                            C.POINTER(C.c_void_p), u32p, f32p]
         lib.ref_cpu_experts.argtypes = [C.c_int, C.c_uint32, C.c_uint32, C.c_uint32,
                                         C.POINTER(RefExpertPtrs), f32p, u32p, u32p, f32p, C.c_uint32]
         _ref = lib

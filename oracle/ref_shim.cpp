@@ -26,6 +26,7 @@
 #include "strata/laguna_ops.hpp"
 #include "strata/model.hpp"
 #include "strata/numerics.hpp"
+#include "strata/trace.hpp"
 #include "strata/worker_pool.hpp"
 
 #define REF_API extern "C" __attribute__((visibility("default")))
@@ -34,6 +35,7 @@ namespace {
 std::span<const std::byte> bytes(const void* p, std::size_t n) {
     return {static_cast<const std::byte*>(p), n};
 }
+std::span<const std::byte> bytes_of(const void* p, std::size_t n) { return bytes(p, n); }
 }  // namespace
 
 // ---- scalar decoders (src/platform/numerics.cpp, compressed_tensors.cpp) ----
@@ -302,4 +304,111 @@ REF_API int64_t ref_cpu_experts(int fmt, uint32_t hidden, uint32_t intermediate,
                              .count();
     if (!status.ok() || failed.load() != 0) return -1;
     return static_cast<int64_t>(elapsed);
+}
+
+// ---- the whole LatentMoE block ------------------------------------------------------------
+// kimi_latent_moe_layer, src/models/kimi_k3/kimi_k3_layer.cpp:781-1001, at the shape its contract
+// fixes (hidden 7168, latent 3584, 896 experts of width 3072, top-16, two shared experts).
+// expert_ptrs[e * 6 + {0..5}] = gate packed, gate scales, up packed, up scales, down packed, down
+// scales of expert e (null for experts no token routes to).  selection receives the routed experts
+// and weights of every token ([tokens, 16]) as the reference computed them.
+namespace {
+struct PointerExpertSource final : strata::KimiExpertSource {
+    const uint8_t* const* ptrs{};
+    strata::ValidationResult prepare(std::uint32_t, std::span<const std::uint32_t>) override { return {}; }
+    strata::ValidationResult fetch(std::uint32_t, std::uint32_t expert, strata::KimiExpertWeights& w) override {
+        const auto& c = strata::kKimiK3ExecutionContract;
+        const uint8_t* const* e = ptrs + static_cast<std::size_t>(expert) * 6U;
+        strata::ValidationResult result;
+        if (e[0] == nullptr) {
+            result.errors.emplace_back("expert was not provided to the fixture");
+            return result;
+        }
+        const auto view = [](const uint8_t* p, const uint8_t* s, std::uint32_t rows, std::uint32_t cols) {
+            strata::KimiExpertModuleView v;
+            v.packed = {p, static_cast<std::size_t>(rows) * cols / 2U};
+            v.scales = {s, static_cast<std::size_t>(rows) * cols / 32U};
+            v.rows = rows;
+            v.columns = cols;
+            return v;
+        };
+        w.gate = view(e[0], e[1], c.expert_intermediate_size, c.routed_expert_hidden_size);
+        w.up = view(e[2], e[3], c.expert_intermediate_size, c.routed_expert_hidden_size);
+        w.down = view(e[4], e[5], c.routed_expert_hidden_size, c.expert_intermediate_size);
+        return result;
+    }
+};
+}  // namespace
+
+REF_API int ref_kimi_latent_moe(float* out, const float* in, uint32_t tokens, const uint16_t* router,
+                                const float* router_bias, const uint16_t* latent_down, const uint16_t* latent_up,
+                                const float* latent_norm, const uint16_t* shared_gate, const uint16_t* shared_up,
+                                const uint16_t* shared_down, const uint8_t* const* expert_ptrs, uint32_t* ids,
+                                float* weights) {
+    const auto& c = strata::kKimiK3ExecutionContract;
+    const std::size_t H = c.hidden_size, HL = c.routed_expert_hidden_size;
+    const std::size_t Is = static_cast<std::size_t>(c.expert_intermediate_size) * c.shared_experts;
+    strata::KimiMoeWeights w;
+    w.router = {{router, static_cast<std::size_t>(c.routed_experts) * H}, c.routed_experts, c.hidden_size};
+    w.router_bias = {router_bias, c.routed_experts};
+    w.latent_down = {{latent_down, HL * H}, c.routed_expert_hidden_size, c.hidden_size};
+    w.latent_up = {{latent_up, H * HL}, c.hidden_size, c.routed_expert_hidden_size};
+    w.latent_norm = {latent_norm, HL};
+    w.shared_gate = {{shared_gate, Is * H}, static_cast<std::uint32_t>(Is), c.hidden_size};
+    w.shared_up = {{shared_up, Is * H}, static_cast<std::uint32_t>(Is), c.hidden_size};
+    w.shared_down = {{shared_down, H * Is}, c.hidden_size, static_cast<std::uint32_t>(Is)};
+    PointerExpertSource source;
+    source.ptrs = expert_ptrs;
+    strata::KimiLayerScratch scratch;
+    const auto r = strata::kimi_latent_moe_layer({out, tokens * H}, {in, tokens * H}, w, source, 1U, tokens, scratch,
+                                                 nullptr);
+    if (ids != nullptr && weights != nullptr && scratch.selection.size() == static_cast<std::size_t>(tokens) * c.experts_per_token)
+        for (std::size_t i = 0; i < scratch.selection.size(); ++i) {
+            ids[i] = scratch.selection[i].expert;
+            weights[i] = scratch.selection[i].weight;
+        }
+    return r.ok() ? 0 : 1;
+}
+
+
+// ---- host decode layout and route traces (checkers of include/strata_moe_loader.hpp) --------
+// dsv4_transform_tiled_expert_shard, kernels/cpu/dsv4_fp4_expert.cpp:360-434.  Returns the shard's byte count
+// (0 on error); destination may be null to ask for the size only.
+REF_API uint64_t ref_dsv4_tile_shard(uint8_t* destination, const uint8_t* w1, const uint8_t* s1, const uint8_t* w3,
+                                     const uint8_t* s3, const uint8_t* w2, const uint8_t* s2, uint64_t hidden,
+                                     uint64_t intermediate, uint64_t shard, uint64_t shards) {
+    const auto bytes = strata::dsv4_tiled_expert_shard_bytes(hidden, intermediate, shards);
+    if (bytes == 0U || destination == nullptr) return bytes;
+    strata::Dsv4HostExpertWeights canonical;
+    canonical.w1_packed = bytes_of(w1, intermediate * (hidden / 2U));
+    canonical.w1_scales = bytes_of(s1, intermediate * (hidden / 32U));
+    canonical.w3_packed = bytes_of(w3, intermediate * (hidden / 2U));
+    canonical.w3_scales = bytes_of(s3, intermediate * (hidden / 32U));
+    canonical.w2_packed = bytes_of(w2, hidden * (intermediate / 2U));
+    canonical.w2_scales = bytes_of(s2, hidden * (intermediate / 32U));
+    const auto r = strata::dsv4_transform_tiled_expert_shard({reinterpret_cast<std::byte*>(destination), bytes}, canonical,
+                                                             hidden, intermediate, shard, shards);
+    return r.ok() ? bytes : 0U;
+}
+
+// parse_route_trace, src/platform/trace.cpp.  Fills up to `capacity` events (request, position, layer, phase,
+// expert count) and the flattened experts / coefficients; returns the event count or -1 on a parse error.
+REF_API int64_t ref_parse_route_trace(const char* path, uint64_t* header5, uint32_t* experts, float* coefficients,
+                                      uint64_t capacity_events, uint64_t capacity_values) {
+    const auto parsed = strata::parse_route_trace(path);
+    if (!parsed.ok()) return -1;
+    uint64_t values = 0;
+    for (std::size_t i = 0; i < parsed.events.size() && i < capacity_events; ++i) {
+        const auto& e = parsed.events[i];
+        header5[i * 5 + 0] = e.request;
+        header5[i * 5 + 1] = e.token_position;
+        header5[i * 5 + 2] = e.layer;
+        header5[i * 5 + 3] = static_cast<uint64_t>(e.phase);
+        header5[i * 5 + 4] = e.experts.size() | (static_cast<uint64_t>(e.coefficients.size()) << 32);
+        for (std::size_t j = 0; j < e.experts.size() && values < capacity_values; ++j, ++values) {
+            experts[values] = e.experts[j];
+            coefficients[values] = j < e.coefficients.size() ? e.coefficients[j] : 0.0F;
+        }
+    }
+    return static_cast<int64_t>(parsed.events.size());
 }

@@ -23,6 +23,9 @@ EXPORTS = [
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
     "strata_moe_route_hash",
+    "strata_moe_forward_routed", "strata_moe_latent_create", "strata_moe_latent_destroy", "strata_moe_latent_experts",
+    "strata_moe_latent_set_router", "strata_moe_latent_set_projections", "strata_moe_latent_set_shared",
+    "strata_moe_latent_forward",
     "strata_moe_device_count", "strata_moe_weight_upload", "strata_moe_weight_release", "strata_moe_command_enqueue",
     "strata_moe_command_collect", "strata_moe_command_enqueue_rows_dsv4", "strata_moe_command_collect_rows_dsv4",
 ]
@@ -119,6 +122,16 @@ def load_library():
     lib.strata_moe_experts_grouped_dsv4.argtypes = [vp, vp, u32, vp, vp, f32, vp]
     lib.strata_moe_quantize_e4m3.argtypes = [vp, vp, u32, u32]
     lib.strata_moe_combine_dsv4.argtypes = [vp, vp, vp, vp, u32, vp]
+    lib.strata_moe_forward_routed.argtypes = [vp, vp, u32, vp, vp, vp]
+    lib.strata_moe_latent_create.argtypes = [vp, C.POINTER(LayerDesc), u32, f32, C.POINTER(vp)]
+    lib.strata_moe_latent_destroy.argtypes = [vp]
+    lib.strata_moe_latent_destroy.restype = None
+    lib.strata_moe_latent_experts.argtypes = [vp]
+    lib.strata_moe_latent_experts.restype = C.c_void_p
+    lib.strata_moe_latent_set_router.argtypes = [vp, vp, vp, i32]
+    lib.strata_moe_latent_set_projections.argtypes = [vp, vp, vp, vp, i32]
+    lib.strata_moe_latent_set_shared.argtypes = [vp, i32, vp, i32]
+    lib.strata_moe_latent_forward.argtypes = [vp, vp, u32, vp, vp, vp]
     _LIB = lib
     return lib
 
@@ -415,6 +428,70 @@ class MoeLayer:
         if self.h:
             if self.ctx.h:               # a closed context has already closed this layer
                 self.lib.strata_moe_layer_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class LatentMoe:
+    """strata_moe_latent: the LatentMoE wrapper (router and shared experts on cfg.H_model wide rows, routed experts
+    on the cfg.H wide latent)."""
+
+    _close_order = 0
+
+    def __init__(self, ctx, cfg, max_tokens=None):
+        assert cfg.H_model, "configuration has no latent"
+        self.ctx, self.cfg, self.lib = ctx, cfg, ctx.lib
+        d = LayerDesc()
+        d.hidden, d.intermediate, d.experts, d.top_k = cfg.H, cfg.I, cfg.E, cfg.k
+        d.format, d.score_kind, d.normalize = cfg.fmt, cfg.score_kind, int(cfg.normalize)
+        d.norm_init, d.weight_scale, d.output_scale, d.softcap = cfg.norm_init, cfg.weight_scale, cfg.output_scale, 0.0
+        d.shared_intermediate = cfg.I_shared
+        d.expert_begin, d.expert_count = 0, cfg.E
+        d.max_tokens = cfg.T if max_tokens is None else max_tokens
+        d.max_pairs = 0
+        d.activation, d.gate_beta, d.linear_beta = cfg.activation, cfg.gate_beta, cfg.linear_beta
+        h = C.c_void_p()
+        ctx.check(self.lib.strata_moe_latent_create(ctx.h, C.byref(d), cfg.H_model, float(cfg.rms_epsilon), C.byref(h)))
+        self.h = h
+        self._keep = []
+        ctx._children.add(self)
+
+    def load_synth(self, layer):
+        self.ctx.enter()
+        src = lambda t: SRC_DEVICE_BORROW if t.is_cuda else SRC_HOST
+        self._keep += [layer.router_w, layer.bias, layer.latent, layer.shared, layer.packed, layer.scales]
+        self.ctx.check(self.lib.strata_moe_latent_set_router(self.h, _ptr(layer.router_w), _ptr(layer.bias), src(layer.router_w)))
+        lt = layer.latent
+        self.ctx.check(self.lib.strata_moe_latent_set_projections(self.h, _ptr(lt["down"]), _ptr(lt["up"]), _ptr(lt["norm"]),
+                                                                  src(lt["down"])))
+        experts = C.c_void_p(self.lib.strata_moe_latent_experts(self.h))
+        for r, role in enumerate(synth.ROLES):
+            p, s = layer.packed[role], layer.scales[role]
+            for e in range(self.cfg.E):
+                self.ctx.check(self.lib.strata_moe_set_expert(experts, e, r, _ptr(p[e]), _ptr(s[e]),
+                                                              float(layer.global_scale(role)), src(p)))
+            if layer.shared:
+                self.ctx.check(self.lib.strata_moe_latent_set_shared(self.h, r, _ptr(layer.shared[role]), src(layer.shared[role])))
+
+    def forward(self, x, want_routing=False):
+        T, dev = x.shape[0], x.device
+        out = torch.empty(T, self.cfg.H_model, dtype=torch.float32, device=dev)
+        ids = torch.empty(T, self.cfg.k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, self.cfg.k, dtype=torch.float32, device=dev)
+        self.ctx.enter()
+        self.ctx.check(self.lib.strata_moe_latent_forward(self.h, _ptr(x), T, _ptr(out), _ptr(ids), _ptr(w)))
+        self.ctx.leave()
+        return (out, ids, w) if want_routing else out
+
+    def close(self):
+        if self.h:
+            if self.ctx.h:
+                self.lib.strata_moe_latent_destroy(self.h)
             self.h = None
 
     def __del__(self):

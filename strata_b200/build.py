@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libstrata_moe.so")
-SOURCES = ["api.cu", "router.cu", "group.cu", "decode.cu", "decode_fp4.cu", "decode_stream.cu", "combine.cu", "prefill.cu", "ep.cu", "dsv4_exact.cu"]
+SOURCES = ["api.cu", "router.cu", "group.cu", "decode.cu", "decode_fp4.cu", "decode_stream.cu", "combine.cu", "prefill.cu", "ep.cu", "dsv4_exact.cu", "latent.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=default"]
 

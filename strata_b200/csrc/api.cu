@@ -61,6 +61,7 @@ struct LayerKnobs {
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
     int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
+    bool exact_router_weights = false;  // STRATA_MOE_EXACT_ROUTER_WEIGHTS: the fast router recomputes the selected logits
 };
 
 static LayerKnobs read_knobs() {
@@ -78,6 +79,7 @@ static LayerKnobs read_knobs() {
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
+    k.exact_router_weights = getenv("STRATA_MOE_EXACT_ROUTER_WEIGHTS") != nullptr;
     return k;
 }
 
@@ -353,7 +355,7 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
             return fail(ctx, STRATA_MOE_E_CUDA, "tensor-core router projection launch failed");
         mark(ctx, 1);
         launch_route_fast(rp, L->logits, L->bias, x, L->router, T, d.hidden, ids, w, L->recheck_list, L->recheck_count,
-                          ctx->d_router_rechecks, ctx->d_status, s);
+                          ctx->d_router_rechecks, ctx->d_status, s, L->knobs.exact_router_weights);
         ctx->router_fast_tokens += T;
         return 0;
     }
@@ -1098,6 +1100,37 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     return 0;
 }
 
+// The layer after routing: ids / weights given (device, [T, k], selection-rank order).
+int strata_moe_forward_routed(strata_moe_layer* L, const void* x, uint32_t T, const uint32_t* ids, const float* w,
+                              float* out) {
+    if (!L) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = L->ctx;
+    if (!x || !out || !ids || !w) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (L->d.expert_count != L->d.experts)
+        return fail(ctx, STRATA_MOE_E_INVALID, "forward needs every expert resident; use the stage calls for expert parallelism");
+    if (L->dense_in_flight) return fail(ctx, STRATA_MOE_E_BUSY, "a dense command is in flight");
+    if ((uint64_t)T * L->d.top_k > L->max_pairs)
+        return fail(ctx, STRATA_MOE_E_INVALID, "tokens * top_k exceed the layer's max_pairs");
+    for (int r = 0; r < 3; ++r)
+        for (uint32_t e = 0; e < L->d.expert_count; ++e)
+            if (!L->tab[r].packed[e] || !L->tab[r].scales[e]) return fail(ctx, STRATA_MOE_E_INVALID, "an expert has no weights");
+    if (T == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    int rc = sync_tables(L);
+    if (rc) return rc;
+    cudaStream_t s = ctx->stream;
+    const strata_moe_layer_desc& d = L->d;
+    const uint32_t P = T * d.top_k;
+    launch_group(ids, P, 0, d.experts, L->counts, L->offsets, L->perm, L->inv, L->active, L->n_active, L->group_scratch, s);
+    rc = run_experts(L, (const __nv_bfloat16*)x, L->perm, d.top_k, P, d.experts, L->offsets, L->active, L->n_active, T, L->y);
+    if (rc) return rc;
+    launch_combine(L->y, L->inv, w, nullptr, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s);
+    CK(cudaGetLastError());
+    ctx->stats.forward_calls++;
+    return 0;
+}
+
 int strata_moe_forward_host(strata_moe_layer* L, const void* x_host, uint32_t T, float* out_host) {
     if (!L) return STRATA_MOE_E_INVALID;
     strata_moe_ctx* ctx = L->ctx;
@@ -1339,6 +1372,164 @@ int strata_moe_combine_dsv4(strata_moe_layer* L, const float* y, const uint32_t*
     if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
     CK(cudaSetDevice(ctx->device));
     launch_dsv4_join(y, inv, shared_rows, T, L->d.top_k, L->d.hidden, out, ctx->d_status, ctx->stream);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------------- LatentMoE wrapper
+struct strata_moe_latent {
+    strata_moe_ctx* ctx = nullptr;
+    strata_moe_layer* route = nullptr;     // router + shared experts on the raw hidden state
+    strata_moe_layer* experts = nullptr;   // routed experts on the latent
+    uint32_t H = 0, HL = 0, max_tokens = 0;
+    float eps = 0.0f;
+    const __nv_bfloat16 *down = nullptr, *up = nullptr;
+    const float* norm = nullptr;
+    std::vector<void*> owned;
+    float *latent_f32 = nullptr, *mix = nullptr, *w = nullptr;
+    __nv_bfloat16 *latent_bf16 = nullptr, *mixn = nullptr;
+    uint32_t *tiles = nullptr, *off2 = nullptr, *ids = nullptr;
+};
+
+int strata_moe_latent_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* desc, uint32_t model_hidden,
+                             float rms_epsilon, strata_moe_latent** out) {
+    if (!ctx || !desc || !out) return STRATA_MOE_E_INVALID;
+    *out = nullptr;
+    if (model_hidden == 0 || model_hidden % 128u) return fail(ctx, STRATA_MOE_E_INVALID, "model hidden must be a positive multiple of 128");
+    if (desc->expert_count != desc->experts || desc->expert_begin != 0)
+        return fail(ctx, STRATA_MOE_E_INVALID, "the LatentMoE wrapper needs every expert resident");
+    if (!(rms_epsilon >= 0.0f) || !(rms_epsilon < 1.0f)) return fail(ctx, STRATA_MOE_E_INVALID, "RMS epsilon out of range");
+    if (desc->score_kind == STRATA_MOE_SCORE_SOFTMAX && false) return STRATA_MOE_E_INVALID;
+    CK(cudaSetDevice(ctx->device));
+    strata_moe_latent* lat = new (std::nothrow) strata_moe_latent();
+    if (!lat) return fail(ctx, STRATA_MOE_E_INVALID, "out of host memory");
+    lat->ctx = ctx;
+    lat->H = model_hidden;
+    lat->HL = desc->hidden;
+    lat->eps = rms_epsilon;
+    lat->max_tokens = desc->max_tokens;
+    strata_moe_layer_desc ed = *desc;
+    ed.shared_intermediate = 0;
+    strata_moe_layer_desc rd = *desc;      // router + shared experts: no routed weights, minimal pair workspaces
+    rd.hidden = model_hidden;
+    rd.intermediate = 128;
+    rd.format = STRATA_MOE_FMT_BF16;
+    rd.max_pairs = 1;
+    int rc = strata_moe_layer_create(ctx, &ed, &lat->experts);
+    if (rc == 0) rc = strata_moe_layer_create(ctx, &rd, &lat->route);
+    const size_t T = desc->max_tokens;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** p, size_t bytes) {
+        if (rc != 0 || e != cudaSuccess) return;
+        e = cudaMalloc(p, bytes ? bytes : 16);
+        if (e == cudaSuccess) lat->owned.push_back(*p);
+    };
+    alloc((void**)&lat->latent_f32, T * lat->HL * 4);
+    alloc((void**)&lat->mix, T * lat->HL * 4);
+    alloc((void**)&lat->latent_bf16, T * lat->HL * 2);
+    alloc((void**)&lat->mixn, T * lat->HL * 2);
+    alloc((void**)&lat->tiles, prefill_scratch_bytes(1, (uint32_t)T) + 16);
+    alloc((void**)&lat->off2, 16);
+    alloc((void**)&lat->ids, T * desc->top_k * 4);
+    alloc((void**)&lat->w, T * desc->top_k * 4);
+    if (rc != 0 || e != cudaSuccess) {
+        const std::string msg = rc != 0 ? ctx->err : std::string("LatentMoE allocation: ") + cudaGetErrorString(e);
+        strata_moe_latent_destroy(lat);
+        return fail(ctx, rc != 0 ? rc : STRATA_MOE_E_CUDA, msg);
+    }
+    *out = lat;
+    return 0;
+}
+
+void strata_moe_latent_destroy(strata_moe_latent* lat) {
+    if (!lat) return;
+    cudaSetDevice(lat->ctx->device);
+    cudaStreamSynchronize(lat->ctx->stream);
+    if (lat->experts) strata_moe_layer_destroy(lat->experts);
+    if (lat->route) strata_moe_layer_destroy(lat->route);
+    for (void* p : lat->owned) cudaFree(p);
+    delete lat;
+}
+
+strata_moe_layer* strata_moe_latent_experts(strata_moe_latent* lat) { return lat ? lat->experts : nullptr; }
+
+int strata_moe_latent_set_router(strata_moe_latent* lat, const void* gate_bf16, const float* bias, int source) {
+    if (!lat) return STRATA_MOE_E_INVALID;
+    return strata_moe_set_router(lat->route, gate_bf16, bias, source);
+}
+
+int strata_moe_latent_set_shared(strata_moe_latent* lat, int role, const void* w, int source) {
+    if (!lat) return STRATA_MOE_E_INVALID;
+    return strata_moe_set_shared(lat->route, role, w, source);
+}
+
+int strata_moe_latent_set_projections(strata_moe_latent* lat, const void* down, const void* up, const float* norm,
+                                      int source) {
+    if (!lat) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = lat->ctx;
+    if (!down || !up || !norm) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    CK(cudaSetDevice(ctx->device));
+    const void* p = nullptr;
+    int rc = put(lat->route, down, (size_t)lat->HL * lat->H * 2, source, &p);   // storage owned by the routing layer
+    if (rc) return rc;
+    lat->down = static_cast<const __nv_bfloat16*>(p);
+    rc = put(lat->route, up, (size_t)lat->H * lat->HL * 2, source, &p);
+    if (rc) return rc;
+    lat->up = static_cast<const __nv_bfloat16*>(p);
+    rc = put(lat->route, norm, (size_t)lat->HL * 4, source, &p);
+    if (rc) return rc;
+    lat->norm = static_cast<const float*>(p);
+    if ((((uintptr_t)lat->down | (uintptr_t)lat->up) & 15u) != 0)
+        return fail(ctx, STRATA_MOE_E_INVALID, "projection weights must be 16-byte aligned");
+    return 0;
+}
+
+int strata_moe_latent_forward(strata_moe_latent* lat, const void* x, uint32_t T, float* out, uint32_t* ids_out,
+                              float* weights_out) {
+    if (!lat) return STRATA_MOE_E_INVALID;
+    strata_moe_ctx* ctx = lat->ctx;
+    if (!x || !out) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (T > lat->max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
+    if (!lat->down || !lat->up || !lat->norm) return fail(ctx, STRATA_MOE_E_INVALID, "latent projections were never set");
+    if (((uintptr_t)x & 15u) != 0) return fail(ctx, STRATA_MOE_E_INVALID, "activations must be 16-byte aligned");
+    if (T == 0) return 0;
+    CK(cudaSetDevice(ctx->device));
+    cudaStream_t s = ctx->stream;
+    strata_moe_layer* R = lat->route;
+    const strata_moe_layer_desc& rd = R->d;
+    if (!tensor_path_ok(R, 3, 128)) return fail(ctx, STRATA_MOE_E_INVALID, "the LatentMoE projections need the tensor-core path");
+    uint32_t* ids = ids_out ? ids_out : lat->ids;
+    float* w = weights_out ? weights_out : lat->w;
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    const bool shared = rd.shared_intermediate != 0;
+    if (shared) {   // the shared experts need only x: side stream, joined before the final add
+        for (int r = 0; r < 3; ++r)
+            if (!R->shared_w[r]) return fail(ctx, STRATA_MOE_E_INVALID, "shared expert weights were never set");
+        uint32_t* off2 = R->offsets + rd.experts + 1 + 2;
+        set_pair_kernel<<<1, 1, 0, s>>>(off2, 0u, T);
+        ++g_kernel_launches;
+        CK(cudaEventRecord(ctx->ev_fork, s));
+        CK(cudaStreamWaitEvent(ctx->side, ctx->ev_fork, 0));
+        int rc = run_shared(R, xb, nullptr, T, off2, ctx->side);
+        if (rc) return rc;
+        CK(cudaEventRecord(ctx->ev_join, ctx->side));
+    }
+    int rc = strata_moe_route(R, x, T, nullptr, ids, w);      // routing reads the raw hidden state
+    if (rc) return rc;
+    set_pair_kernel<<<1, 1, 0, s>>>(lat->off2, 0u, T);
+    ++g_kernel_launches;
+    if (launch_router_tc(x, T, lat->down, lat->HL, lat->H, lat->latent_f32, lat->tiles, lat->off2, ctx->d_status, s) != 0)
+        return fail(ctx, STRATA_MOE_E_CUDA, "latent down projection launch failed");
+    launch_f32_to_bf16(lat->latent_f32, (size_t)T * lat->HL, lat->latent_bf16, s);
+    rc = strata_moe_forward_routed(lat->experts, lat->latent_bf16, T, ids, w, lat->mix);
+    if (rc) return rc;
+    launch_rmsnorm_bf16(lat->mix, lat->norm, T, lat->HL, lat->eps, lat->mixn, ctx->d_status, s);
+    if (launch_router_tc(lat->mixn, T, lat->up, lat->H, lat->HL, out, lat->tiles, lat->off2, ctx->d_status, s) != 0)
+        return fail(ctx, STRATA_MOE_E_CUDA, "latent up projection launch failed");
+    if (shared) {
+        CK(cudaStreamWaitEvent(s, ctx->ev_join, 0));
+        launch_add_rows(out, R->sh_y, (size_t)T * lat->H, s);
+    }
     CK(cudaGetLastError());
     return 0;
 }
@@ -1928,8 +2119,11 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
     if (expected_rows == 0) expected_rows = ep->T * L->d.top_k ? ep->T * L->d.top_k : 1u;
     int rc = run_experts(L, ep->w.rows(ep->w.rank, par), nullptr, 1, ep->w.cap, B, ep->loffsets, nullptr, nullptr,
-                         ep->w.cap, ep->w.y(ep->w.rank, par), expected_rows, ep->loffsets + B);
+                         ep->w.cap, L->y, expected_rows, ep->loffsets + B);
     if (rc) return rc;
+    // the outputs leave this GPU as f16 rows with an exact per-row power-of-two scale
+    launch_rows_to_f16_f32(L->y, 0, ep->w.cap, L->d.hidden, ep->w.y(ep->w.rank, par), nullptr,
+                           ep->w.yscale(ep->w.rank, par), s, ep->loffsets + B);
     launch_ep_signal(ep->w, 2, s);
     CK(cudaGetLastError());
     ep->stage = 3;

@@ -60,7 +60,7 @@ bool route_fast_supported(const RouterParams& p, uint32_t H);
 void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
                        const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
-                       cudaStream_t s);
+                       cudaStream_t s, bool exact_weights);
 // group.cu
 size_t group_scratch_bytes(uint32_t pairs, uint32_t n_experts);
 void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, uint32_t n_experts,
@@ -156,6 +156,11 @@ int launch_prefill_bf16(const PrefillArgs& a, const void* x, uint32_t rows, cons
 // tile_table: scratch of prefill_scratch_bytes(1, T); offsets2: device {0, T}.
 int launch_router_tc(const void* x_bf16, uint32_t T, const void* wg_bf16, uint32_t E, uint32_t H, float* logits,
                      uint32_t* tile_table, const uint32_t* offsets2, uint32_t* status, cudaStream_t s);
+// latent.cu : row kernels of the LatentMoE wrapper
+void launch_f32_to_bf16(const float* src, size_t n, __nv_bfloat16* dst, cudaStream_t s);
+void launch_rmsnorm_bf16(const float* x, const float* weight, uint32_t rows, uint32_t cols, float eps,
+                         __nv_bfloat16* y, uint32_t* status, cudaStream_t s);
+void launch_add_rows(float* out, const float* a, size_t n, cudaStream_t s);
 // combine.cu
 void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
                     uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,
@@ -167,7 +172,9 @@ void launch_dequant_export(int fmt, const uint8_t* packed, const uint8_t* scales
 constexpr uint32_t kEpMaxWorld = 16;
 // The windows of all ranks as mapped into this process, plus the step being executed.  Passed to
 // the kernels by value.  Layout of one window (byte offsets, every region 256-byte aligned):
-// flags | counts [2][world][E] u32 | rows [2][cap][H] bf16 | y [2][cap][H] f32.
+// flags | counts [2][world][E] u32 | rows [2][cap][H] bf16 | y [2][cap][H] f16 | yscale [2][cap] f32.
+// Expert outputs cross NVLink as f16 rows with an exact power-of-two scale per row (11 significant
+// bits, half the bytes of fp32); the home rank widens them back while it forms the weighted sum.
 struct EpWindows {
     uint8_t* win[kEpMaxWorld];
     uint32_t world, rank, E, H, cap, step;
@@ -176,8 +183,11 @@ struct EpWindows {
     __host__ __device__ size_t flags_bytes() const { return up256((size_t)3 * kEpMaxWorld * 4u); }
     __host__ __device__ size_t counts_bytes() const { return up256((size_t)2 * world * E * 4u); }
     __host__ __device__ size_t rows_bytes() const { return up256((size_t)2 * cap * H * 2u); }
-    __host__ __device__ size_t y_bytes() const { return up256((size_t)2 * cap * H * 4u); }
-    __host__ __device__ size_t total_bytes() const { return flags_bytes() + counts_bytes() + rows_bytes() + y_bytes(); }
+    __host__ __device__ size_t y_bytes() const { return up256((size_t)2 * cap * H * 2u); }
+    __host__ __device__ size_t yscale_bytes() const { return up256((size_t)2 * cap * 4u); }
+    __host__ __device__ size_t total_bytes() const {
+        return flags_bytes() + counts_bytes() + rows_bytes() + y_bytes() + yscale_bytes();
+    }
     __host__ __device__ uint32_t* flag(uint32_t r, uint32_t kind, uint32_t src) const {
         return reinterpret_cast<uint32_t*>(win[r]) + kind * kEpMaxWorld + src;
     }
@@ -187,9 +197,13 @@ struct EpWindows {
     __host__ __device__ __nv_bfloat16* rows(uint32_t r, uint32_t parity) const {
         return reinterpret_cast<__nv_bfloat16*>(win[r] + flags_bytes() + counts_bytes()) + (size_t)parity * cap * H;
     }
-    __host__ __device__ float* y(uint32_t r, uint32_t parity) const {
-        return reinterpret_cast<float*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes()) +
+    __host__ __device__ unsigned short* y(uint32_t r, uint32_t parity) const {   // f16 bit patterns
+        return reinterpret_cast<unsigned short*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes()) +
                (size_t)parity * cap * H;
+    }
+    __host__ __device__ float* yscale(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<float*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes() + y_bytes()) +
+               (size_t)parity * cap;
     }
 };
 size_t ep_window_bytes(uint32_t world, uint32_t E, uint32_t H, uint32_t cap);

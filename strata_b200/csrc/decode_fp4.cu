@@ -410,9 +410,10 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
             *reinterpret_cast<uint2*>(hi + (size_t)pos * C + i * 4u) =
                 make_uint2((uint32_t)__half_as_ushort(h[0]) | ((uint32_t)__half_as_ushort(h[1]) << 16),
                            (uint32_t)__half_as_ushort(h[2]) | ((uint32_t)__half_as_ushort(h[3]) << 16));
-            *reinterpret_cast<uint2*>(lo + (size_t)pos * C + i * 4u) =
-                make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
-                           (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
+            if (lo != nullptr)
+                *reinterpret_cast<uint2*>(lo + (size_t)pos * C + i * 4u) =
+                    make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
+                               (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
         }
     } else {
         const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C);

@@ -287,11 +287,7 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int q = 0; q < 4; ++q) acc0[nt][q] = acc1[nt][q] = 0.0f;
-        int32_t mx0 = 0, mx1 = 0;
-        if (FMT == STRATA_MOE_FMT_MXFP4) {
-            mx0 = kMxBiasS - (int32_t)(DUAL ? a.gate.emin[j.g] : a.down.emin[j.g]);
-            mx1 = kMxBiasS - (int32_t)(DUAL ? a.up.emin[j.g] : a.down.emin[j.g]);
-        }
+        const int32_t mx0 = 0, mx1 = 0;   // NVFP4 multipliers need no exponent base
         const bool my_unit = unit < j.nu;
         for (uint32_t c = 0; c < chunks; ++c, ++it) {
             const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -303,42 +299,84 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                 const uint32_t box1 = box0 + 2u * kBoxBytes;                      // tile 1
                 const uint32_t sc0 = st + G::kSOff + row_lo * ScaleGeo<FMT>::kPitch + ks * ScaleGeo<FMT>::kStepBytes;
                 const uint32_t sc1 = sc0 + kBoxRows * ScaleGeo<FMT>::kPitch;
-                uint32_t m0l[4], m0h[4], m1l[4], m1h[4];
-                step_mults<FMT>(sc0, mx0, t, m0l);
-                step_mults<FMT>(sc0 + 8u * ScaleGeo<FMT>::kPitch, mx0, t, m0h);
-                step_mults<FMT>(sc1, mx1, t, m1l);
-                step_mults<FMT>(sc1 + 8u * ScaleGeo<FMT>::kPitch, mx1, t, m1h);
                 const uint32_t xrow = st + G::kXOff + gid * kXP + ks * 256u + t * 16u;
+                if (FMT == STRATA_MOE_FMT_MXFP4) {
+                    // E8M0 block scales are powers of two and one 32-column block is exactly the two MMAs of
+                    // a (word index, tile): the raw E2M1 values go into the MMAs and the FP32 partial sum of
+                    // the block is scaled (exactly) on its way into the accumulator -- four multiply-adds in
+                    // place of sixteen packed multiplies on the weights.  Byte 0 decodes to 0, 0xFF to +inf.
+                    const uint32_t s0l = lds32(sc0), s0h = lds32(sc0 + 8u * ScaleGeo<FMT>::kPitch);
+                    const uint32_t s1l = lds32(sc1), s1h = lds32(sc1 + 8u * ScaleGeo<FMT>::kPitch);
 #pragma unroll
-                for (int wd = 0; wd < 4; ++wd) {
-                    uint4 bh[NT], bl[SPLIT ? NT : 1];
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
-                        if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
-                    }
-#pragma unroll
-                    for (int p = 0; p < 2; ++p) {
-                        const uint32_t box = p ? box1 : box0;
-                        const uint32_t wlo = lds32(box + woff[wd]);
-                        const uint32_t whi = lds32(box + woff[wd] + 8u * 128u);
-                        uint32_t al[4], ah[4];
-                        e2m1x8(wlo, al);
-                        e2m1x8(whi, ah);
-                        const uint32_t ml = p ? m1l[wd] : m0l[wd], mh = p ? m1h[wd] : m0h[wd];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            al[q] = mul2(al[q], ml);
-                            ah[q] = mul2(ah[q], mh);
-                        }
+                    for (int wd = 0; wd < 4; ++wd) {
+                        uint4 bh[NT], bl[SPLIT ? NT : 1];
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
-                            float* cacc = p ? acc1[nt] : acc0[nt];
-                            mma_f16(cacc, al[0], ah[0], al[1], ah[1], bh[nt].x, bh[nt].y);
-                            mma_f16(cacc, al[2], ah[2], al[3], ah[3], bh[nt].z, bh[nt].w);
-                            if (SPLIT) {
-                                mma_f16(cacc, al[0], ah[0], al[1], ah[1], bl[nt].x, bl[nt].y);
-                                mma_f16(cacc, al[2], ah[2], al[3], ah[3], bl[nt].z, bl[nt].w);
+                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
+                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
+                        }
+#pragma unroll
+                        for (int p = 0; p < 2; ++p) {
+                            const uint32_t box = p ? box1 : box0;
+                            uint32_t al[4], ah[4];
+                            e2m1x8(lds32(box + woff[wd]), al);
+                            e2m1x8(lds32(box + woff[wd] + 8u * 128u), ah);
+                            const float fl = __uint_as_float((((p ? s1l : s0l) >> (8 * wd)) & 0xFFu) << 23);
+                            const float fh = __uint_as_float((((p ? s1h : s0h) >> (8 * wd)) & 0xFFu) << 23);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                float tmp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                                mma_f16(tmp, al[0], ah[0], al[1], ah[1], bh[nt].x, bh[nt].y);
+                                mma_f16(tmp, al[2], ah[2], al[3], ah[3], bh[nt].z, bh[nt].w);
+                                if (SPLIT) {
+                                    mma_f16(tmp, al[0], ah[0], al[1], ah[1], bl[nt].x, bl[nt].y);
+                                    mma_f16(tmp, al[2], ah[2], al[3], ah[3], bl[nt].z, bl[nt].w);
+                                }
+                                float* cacc = p ? acc1[nt] : acc0[nt];
+                                cacc[0] = fmaf(tmp[0], fl, cacc[0]);
+                                cacc[1] = fmaf(tmp[1], fl, cacc[1]);
+                                cacc[2] = fmaf(tmp[2], fh, cacc[2]);
+                                cacc[3] = fmaf(tmp[3], fh, cacc[3]);
+                            }
+                        }
+                    }
+                } else {
+                    uint32_t m0l[4], m0h[4], m1l[4], m1h[4];
+                    step_mults<FMT>(sc0, mx0, t, m0l);
+                    step_mults<FMT>(sc0 + 8u * ScaleGeo<FMT>::kPitch, mx0, t, m0h);
+                    step_mults<FMT>(sc1, mx1, t, m1l);
+                    step_mults<FMT>(sc1 + 8u * ScaleGeo<FMT>::kPitch, mx1, t, m1h);
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        uint4 bh[NT], bl[SPLIT ? NT : 1];
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
+                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
+                        }
+#pragma unroll
+                        for (int p = 0; p < 2; ++p) {
+                            const uint32_t box = p ? box1 : box0;
+                            const uint32_t wlo = lds32(box + woff[wd]);
+                            const uint32_t whi = lds32(box + woff[wd] + 8u * 128u);
+                            uint32_t al[4], ah[4];
+                            e2m1x8(wlo, al);
+                            e2m1x8(whi, ah);
+                            const uint32_t ml = p ? m1l[wd] : m0l[wd], mh = p ? m1h[wd] : m0h[wd];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                al[q] = mul2(al[q], ml);
+                                ah[q] = mul2(ah[q], mh);
+                            }
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                float* cacc = p ? acc1[nt] : acc0[nt];
+                                mma_f16(cacc, al[0], ah[0], al[1], ah[1], bh[nt].x, bh[nt].y);
+                                mma_f16(cacc, al[2], ah[2], al[3], ah[3], bh[nt].z, bh[nt].w);
+                                if (SPLIT) {
+                                    mma_f16(cacc, al[0], ah[0], al[1], ah[1], bl[nt].x, bl[nt].y);
+                                    mma_f16(cacc, al[2], ah[2], al[3], ah[3], bl[nt].z, bl[nt].w);
+                                }
                             }
                         }
                     }
@@ -365,9 +403,11 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
         // warp (unit, ks) finishes the accumulator pairs q = ks, ks + 4, ... of its unit; the four partial
         // sums are added in k-step order
         if (my_unit) {
-            float s0, s1;
-            if (DUAL) { s0 = a.gate.post_scale[j.g]; s1 = a.up.post_scale[j.g]; }
-            else { s0 = s1 = a.down.post_scale[j.g]; }
+            float s0 = 1.0f, s1 = 1.0f;     // MXFP4: the block scales went into the accumulators whole
+            if (FMT != STRATA_MOE_FMT_MXFP4) {
+                if (DUAL) { s0 = a.gate.post_scale[j.g]; s1 = a.up.post_scale[j.g]; }
+                else { s0 = s1 = a.down.post_scale[j.g]; }
+            }
             for (uint32_t q = ks; q < 4u * NT; q += 4u) {
                 const uint32_t nt = q >> 2, jj = q & 3u;
                 float v0 = 0.0f, v1 = 0.0f;

@@ -15,7 +15,8 @@
 //   counts u32 [2][world][E]     counts[p][s][e] = rows rank s holds for global expert e
 //   rows   bf16 [2][cap][H]      grouped input rows of this rank's experts (local expert, source
 //                                rank, source scan order)
-//   y      f32 [2][cap][H]       expert outputs for those rows
+//   y      f16 [2][cap][H]       expert outputs for those rows, each row scaled by a power of two
+//   yscale f32 [2][cap]          the factor that undoes a row's scale
 //
 // [2] is the step parity: a buffer written in step n is next written in step n + 2, and a rank
 // can only reach step n + 2 after every peer finished step n (it waited for their step n + 1
@@ -25,6 +26,8 @@
 // a system fence, and are polled with acquire loads.  Every wait is bounded by wall time; a wait
 // that runs out sets the status word and an abort word, and the remaining kernels of the step
 // skip their peer accesses.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace smoe {
@@ -189,7 +192,8 @@ __global__ void ep_signal_kernel(EpWindows w, uint32_t kind) {
 // ------------------------------------------------------------------------------ combine
 // out[t] = output_scale * sum_r weight[t,r] * y_owner(t,r)[row(t,r)] + shared[t], the sum taken in
 // selection-rank order with separate multiply and add like the single-GPU combine.  The expert
-// rows are read from the owners' windows; each CTA first waits for flag 2 of every rank.
+// rows are read from the owners' windows as f16 (16-byte peer loads of eight values) and widened
+// with the row's power-of-two factor; each CTA first waits for flag 2 of every rank.
 __global__ void __launch_bounds__(256) ep_combine_kernel(EpWindows w, const uint32_t* __restrict__ ids,
                                                          const uint32_t* __restrict__ inv,
                                                          const uint32_t* __restrict__ offsets,
@@ -199,8 +203,8 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpWindows w, const uint
                                                          float output_scale, float* __restrict__ out,
                                                          uint32_t* __restrict__ abort_word,
                                                          uint32_t* __restrict__ status) {
-    __shared__ const float* src[32];
-    __shared__ float wgt[32];
+    __shared__ const unsigned short* src[32];
+    __shared__ float wgt[32], rscale[32];
     __shared__ uint32_t failed;
     const uint32_t tid = threadIdx.x;
     if (tid == 0) failed = *abort_word;
@@ -213,50 +217,57 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpWindows w, const uint
     __syncthreads();
     const bool skip = failed != 0;
     const uint32_t B = w.E / w.world;
-    const uint32_t per_row = w.H / 4u;
+    const uint32_t per_row = w.H / 8u;     // 16-byte vectors of eight f16 values
     bool bad = false;
     for (uint32_t t = blockIdx.x; t < T; t += gridDim.x) {
         __syncthreads();
         if (tid < k) {
             const uint32_t pair = t * k + tid;
             const uint32_t e = ids[pair], p = inv[pair];
-            const float* ptr = nullptr;
+            const unsigned short* ptr = nullptr;
+            float rs = 0.0f;
             if (!skip && e < w.E && p != 0xFFFFFFFFu) {
                 const uint32_t row = dst_row[e] + (p - offsets[e]);
-                if (row < w.cap) ptr = w.y(e / B, w.step & 1u) + (size_t)row * w.H;
+                if (row < w.cap) {
+                    ptr = w.y(e / B, w.step & 1u) + (size_t)row * w.H;
+                    rs = w.yscale(e / B, w.step & 1u)[row];
+                }
             }
             src[tid] = ptr;
+            rscale[tid] = rs;               // undoes the row's power-of-two scale: exact
             wgt[tid] = weights[pair];
         }
         __syncthreads();
         for (uint32_t c = tid; c < per_row; c += blockDim.x) {
-            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             for (uint32_t r = 0; r < k; ++r) {
-                const float* ptr = src[r];
+                const unsigned short* ptr = src[r];
                 if (!ptr) continue;
-                const float g = wgt[r];
-                const float4 v = *reinterpret_cast<const float4*>(ptr + c * 4u);
-                o.x = __fadd_rn(o.x, __fmul_rn(v.x, g));
-                o.y = __fadd_rn(o.y, __fmul_rn(v.y, g));
-                o.z = __fadd_rn(o.z, __fmul_rn(v.z, g));
-                o.w = __fadd_rn(o.w, __fmul_rn(v.w, g));
+                const float g = wgt[r], rs = rscale[r];
+                const uint4 v = *reinterpret_cast<const uint4*>(ptr + c * 8u);
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
+                    o[2 * q] = __fadd_rn(o[2 * q], __fmul_rn(__fmul_rn(f.x, rs), g));
+                    o[2 * q + 1] = __fadd_rn(o[2 * q + 1], __fmul_rn(__fmul_rn(f.y, rs), g));
+                }
             }
-            if (output_scale != 1.0f) {
-                o.x = __fmul_rn(o.x, output_scale);
-                o.y = __fmul_rn(o.y, output_scale);
-                o.z = __fmul_rn(o.z, output_scale);
-                o.w = __fmul_rn(o.w, output_scale);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                if (output_scale != 1.0f) o[q] = __fmul_rn(o[q], output_scale);
             }
             if (shared) {
-                const float4 s = __ldg(reinterpret_cast<const float4*>(shared + (size_t)t * w.H) + c);
-                o.x = __fadd_rn(o.x, s.x);
-                o.y = __fadd_rn(o.y, s.y);
-                o.z = __fadd_rn(o.z, s.z);
-                o.w = __fadd_rn(o.w, s.w);
+                const float4* sp = reinterpret_cast<const float4*>(shared + (size_t)t * w.H) + c * 2u;
+                const float4 s0 = __ldg(sp), s1 = __ldg(sp + 1);
+                o[0] = __fadd_rn(o[0], s0.x); o[1] = __fadd_rn(o[1], s0.y); o[2] = __fadd_rn(o[2], s0.z); o[3] = __fadd_rn(o[3], s0.w);
+                o[4] = __fadd_rn(o[4], s1.x); o[5] = __fadd_rn(o[5], s1.y); o[6] = __fadd_rn(o[6], s1.z); o[7] = __fadd_rn(o[7], s1.w);
             }
-            bad |= !(fabsf(o.x) <= 3.0e38f) | !(fabsf(o.y) <= 3.0e38f) | !(fabsf(o.z) <= 3.0e38f) |
-                   !(fabsf(o.w) <= 3.0e38f);
-            reinterpret_cast<float4*>(out + (size_t)t * w.H)[c] = o;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) bad |= !(fabsf(o[q]) <= 3.0e38f);
+            float4* op = reinterpret_cast<float4*>(out + (size_t)t * w.H) + c * 2u;
+            op[0] = make_float4(o[0], o[1], o[2], o[3]);
+            op[1] = make_float4(o[4], o[5], o[6], o[7]);
         }
     }
     if (bad) atomicOr(status, kStatusNonFiniteOutput);

@@ -44,6 +44,72 @@ static __device__ float expf_libm(float x) {
     return __double2float_rn(y);
 }
 
+// ---------------------------------------------------------------------------------------
+// log1pf as glibc 2.39 computes it (the fdlibm single-precision algorithm), with every operation
+// a separately rounded float operation like the host build.  The CPU restatement of the same
+// steps (oracle/moe_oracle.c) is checked bit for bit against the host libm; x >= 0 here
+// (the argument is expf of a logit), so the x <= -1 branches are left out.
+static __device__ float log1pf_libm(float x) {
+    const float ln2_hi = 6.9313812256e-01f, ln2_lo = 9.0580006145e-06f;
+    const float Lp1 = 6.6666668653e-01f, Lp2 = 4.0000000596e-01f, Lp3 = 2.8571429849e-01f, Lp4 = 2.2222198546e-01f,
+                Lp5 = 1.8183572590e-01f, Lp6 = 1.5313838422e-01f, Lp7 = 1.4798198640e-01f;
+    float f = 0.0f, c = 0.0f, u;
+    int k = 1, hx = __float_as_int(x), hu = 0;
+    const int ax = hx & 0x7fffffff;
+    if (hx < 0x3ed413d7) {
+        if (ax < 0x31000000) return ax < 0x24800000 ? x : __fsub_rn(x, __fmul_rn(__fmul_rn(x, x), 0.5f));
+        if (hx > 0) { k = 0; f = x; hu = 1; }
+    }
+    if (hx >= 0x7f800000) return __fadd_rn(x, x);
+    if (k != 0) {
+        if (hx < 0x5a000000) {
+            u = __fadd_rn(1.0f, x);
+            hu = __float_as_int(u);
+            k = (hu >> 23) - 127;
+            c = k > 0 ? __fsub_rn(1.0f, __fsub_rn(u, x)) : __fsub_rn(x, __fsub_rn(u, 1.0f));
+            c = __fdiv_rn(c, u);
+        } else {
+            u = x;
+            hu = __float_as_int(u);
+            k = (hu >> 23) - 127;
+            c = 0.0f;
+        }
+        hu &= 0x007fffff;
+        if (hu < 0x3504f7) {
+            u = __int_as_float(hu | 0x3f800000);
+        } else {
+            k += 1;
+            u = __int_as_float(hu | 0x3f000000);
+            hu = (0x00800000 - hu) >> 2;
+        }
+        f = __fsub_rn(u, 1.0f);
+    }
+    const float kf = (float)k;
+    const float hfsq = __fmul_rn(__fmul_rn(0.5f, f), f);
+    if (hu == 0) {
+        if (f == 0.0f) {
+            if (k == 0) return 0.0f;
+            c = __fadd_rn(c, __fmul_rn(kf, ln2_lo));
+            return __fadd_rn(__fmul_rn(kf, ln2_hi), c);
+        }
+        const float R = __fmul_rn(hfsq, __fsub_rn(1.0f, __fmul_rn(0.66666666666666666f, f)));
+        if (k == 0) return __fsub_rn(f, R);
+        return __fsub_rn(__fmul_rn(kf, ln2_hi), __fsub_rn(__fsub_rn(R, __fadd_rn(__fmul_rn(kf, ln2_lo), c)), f));
+    }
+    const float s = __fdiv_rn(f, __fadd_rn(2.0f, f));
+    const float z = __fmul_rn(s, s);
+    float R = __fadd_rn(Lp6, __fmul_rn(z, Lp7));
+    R = __fadd_rn(Lp5, __fmul_rn(z, R));
+    R = __fadd_rn(Lp4, __fmul_rn(z, R));
+    R = __fadd_rn(Lp3, __fmul_rn(z, R));
+    R = __fadd_rn(Lp2, __fmul_rn(z, R));
+    R = __fadd_rn(Lp1, __fmul_rn(z, R));
+    R = __fmul_rn(z, R);
+    if (k == 0) return __fsub_rn(f, __fsub_rn(hfsq, __fmul_rn(s, __fadd_rn(hfsq, R))));
+    return __fsub_rn(__fmul_rn(kf, ln2_hi),
+                     __fsub_rn(__fsub_rn(hfsq, __fadd_rn(__fmul_rn(s, __fadd_rn(hfsq, R)), __fadd_rn(__fmul_rn(kf, ln2_lo), c))), f));
+}
+
 static __device__ __forceinline__ float sigmoid_two_branch(float v) {
     // src/platform/numerics.cpp:44-48 of the reference
     if (v >= 0.0f) return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-v)));

@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
             if (p.score_kind == STRATA_MOE_SCORE_SIGMOID) sc = sigmoid_two_branch(l);
             else if (p.score_kind == STRATA_MOE_SCORE_SIGMOID_PLAIN)
                 sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
-            else sc = sqrtf(l > 20.0f ? l : log1pf(expf_libm(l)));
+            else sc = sqrtf(l > 20.0f ? l : log1pf_libm(expf_libm(l)));
             score[e] = sc;
         }
     }
@@ -451,9 +451,13 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
 //      values differ by more than the sum of their bounds; the token is "safe" when every
 //      consecutive pair of the k selected is certain and the k-th is certain against the largest
 //      value + bound among all the others;
-//   3. the logits of the k selected experts are recomputed in the canonical lane-strided order
-//      (k * H multiply-adds), which gives bit-exact routing weights -- and checks delta: if any of
-//      them is further than delta / 2 from the approximate logit the token is not trusted;
+//   3. routing weights: by default from the approximate logits of the selected experts (they differ
+//      from the canonical weights by a few units in the last place; expert ids, their rank order and
+//      therefore the permutation and the counts are exact).  With exact_weights the logits of the k
+//      selected experts are recomputed in the canonical lane-strided order (k * H multiply-adds per
+//      token) and the weights are bit-exact too.  Either way one token in 32 (every token with
+//      exact_weights) recomputes its selected logits canonically and checks delta on them: if any is
+//      further than delta / 2 from the approximate logit the token is not trusted;
 //   4. tokens that are not safe go on a list; the canonical kernels recompute them completely.
 // delta = 2^-13 * max(2, max_e |logit|): both summation orders round at most a few hundred partial
 // sums of magnitude <= that maximum (relative 2^-24 each; the tensor cores may truncate, 2^-23), so
@@ -474,7 +478,7 @@ __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l,
         sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
         slope = sc * (1.0f - sc);
     } else {
-        sc = sqrtf(l > 20.0f ? l : log1pf(expf_libm(l)));
+        sc = sqrtf(l > 20.0f ? l : log1pf_libm(expf_libm(l)));
         const float sg = 1.0f / (1.0f + __expf(-l));
         slope = sc > 0.0f ? sg / (2.0f * sc) : 1.0f;
     }
@@ -484,6 +488,7 @@ __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l,
 
 constexpr int kFastWarps = 4;
 
+template <bool EXACT_W>
 __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias,
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
@@ -518,8 +523,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             choice[e] = __fadd_rn(sc, b);
             eps[e] = 1.25f * slope * delta + 4.8e-7f * (fabsf(sc) + fabsf(b)) + 1e-30f;
         }
-        // this token's activation row: 16-byte loads into shared memory
-        {
+        const bool check = EXACT_W || (tok & 31u) == 0u;     // recompute the selected logits canonically?
+        if (check) {     // this token's activation row: 16-byte loads into shared memory
             const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
             for (uint32_t i = lane; i < H / 8u; i += 32u) reinterpret_cast<uint4*>(xs)[i] = __ldg(src + i);
         }
@@ -556,13 +561,13 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
         else if (lane + 1u == k) certain = (my_c - my_e) > rest;
         bool safe = __all_sync(0xFFFFFFFFu, certain) && !__any_sync(0xFFFFFFFFu, bad);
         // canonical-order logits of the selected experts
-        float my_logit = 0.0f;
+        float my_logit = lane < k ? lg[my_id] : 0.0f;        // approximate unless recomputed below
         // Two experts at a time: lane l owns columns l, l + 32, ... of both rows; sixteen 2-byte loads per row are
         // issued before their multiply-adds, so 32 loads are in flight and the two sums form independent chains.
         // Per (token, expert) the products are still added in increasing column order, then folded by the
         // canonical five shuffle-down rounds.
         const uint32_t per_lane = H / 32u;
-        for (uint32_t r = 0; r < k && safe; r += 2u) {
+        for (uint32_t r = 0; r < k && safe && check; r += 2u) {
             const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, my_id, r);
             const bool two = r + 1u < k;
             const uint32_t e1 = two ? __shfl_sync(0xFFFFFFFFu, my_id, r + 1u) : e0;
@@ -594,8 +599,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             a1 = __shfl_sync(0xFFFFFFFFu, a1, 0);
             // the bound itself is checked on every token
             if (!(fabsf(a0 - lg[e0]) <= 0.5f * delta) || (two && !(fabsf(a1 - lg[e1]) <= 0.5f * delta))) safe = false;
-            if (lane == r) my_logit = a0;
-            if (two && lane == r + 1u) my_logit = a1;
+            if (EXACT_W && lane == r) my_logit = a0;
+            if (EXACT_W && two && lane == r + 1u) my_logit = a1;
         }
         safe = __all_sync(0xFFFFFFFFu, safe);
         if (!safe) {
@@ -641,21 +646,26 @@ bool route_fast_supported(const RouterParams& p, uint32_t H) {
 void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
                        const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
-                       cudaStream_t s) {
+                       cudaStream_t s, bool exact_weights) {
     if (T == 0) return;
     const size_t smem = (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float));
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr[dev]) {
-        cudaFuncSetAttribute(route_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(route_fast_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(route_fast_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr[dev] = true;
     }
     cudaMemsetAsync(count, 0, sizeof(uint32_t), s);
     uint32_t grid = (T + kFastWarps - 1) / kFastWarps;
     if (grid > (uint32_t)kNumSMs * 4u) grid = (uint32_t)kNumSMs * 4u;
-    route_fast_kernel<<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
-                                                          recheck_total, status);
+    if (exact_weights)
+        route_fast_kernel<true><<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
+                                                                    recheck_total, status);
+    else
+        route_fast_kernel<false><<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list,
+                                                                     count, recheck_total, status);
     // the tokens on the list, completely in the canonical order (few: the grids stride over the list)
     const uint32_t E = p.experts;
     dim3 g2((E + 7) / 8, 32);

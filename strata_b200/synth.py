@@ -45,7 +45,14 @@ class MoeConfig:
     activation: int = 0           # 0 = SwiGLU, 1 = SiTU-GLU (Kimi-K3), routed and shared experts alike
     gate_beta: float = 1.0
     linear_beta: float = 1.0
+    H_model: int = 0              # > 0: LatentMoE (Kimi-K3): router and shared experts on H_model, experts on H
+    rms_epsilon: float = 1e-5
     description: str = ""
+
+    @property
+    def Hx(self):
+        """Width of the layer's input rows (the router's and the shared experts' K)."""
+        return self.H_model or self.H
 
     def with_(self, **kw):
         return replace(self, **kw)
@@ -77,6 +84,11 @@ CONFIGS = {
     "c4": MoeConfig("c4", H=7168, I=1024, E=896, k=16, fmt=FMT_MXFP4, T=256,
                     score_kind=SCORE_SIGMOID_PLAIN, seed=1, zipf_s=1.1,
                     description="Kimi-K3-style 896-expert MXFP4 decode, Zipf(1.1) bias"),
+    # Kimi-K3 LatentMoE at its real shape: route on 7168, 896 MXFP4 experts (top-16) on a 3584-wide latent,
+    # two BF16 shared experts (6144 wide together), SiTU-GLU.
+    "kimi": MoeConfig("kimi", H=3584, I=3072, E=896, k=16, fmt=FMT_MXFP4, T=4, score_kind=SCORE_SIGMOID_PLAIN,
+                      I_shared=6144, seed=2, activation=1, gate_beta=4.0, linear_beta=25.0, H_model=7168,
+                      description="Kimi-K3 LatentMoE, 896 experts on a 3584-wide latent"),
 }
 
 
@@ -189,6 +201,7 @@ class SynthLayer:
     packed: dict = field(default_factory=dict)   # role -> u8 [E_local, bytes]
     scales: dict = field(default_factory=dict)
     shared: dict = field(default_factory=dict)   # role -> bf16 [rows, cols]
+    latent: dict = field(default_factory=dict)   # LatentMoE: down / up (bf16), norm (fp32)
     expert_begin: int = 0
     expert_end: int = 0
 
@@ -200,13 +213,13 @@ def gen_inputs(cfg, T=None, seed=None):
     """Activations BF16 N(0,1) [T,H] (CPU tensor)."""
     T = cfg.T if T is None else T
     g = torch.Generator().manual_seed(1000 + (cfg.seed if seed is None else seed))
-    return torch.randn(T, cfg.H, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return torch.randn(T, cfg.Hx, generator=g, dtype=torch.float32).to(torch.bfloat16)
 
 
 def gen_router(cfg):
     """Router gate BF16 N(0, 0.02^2) [E,H] and selection bias (None or fp32 [E])."""
     g = torch.Generator().manual_seed(2000 + cfg.seed)
-    w = (torch.randn(cfg.E, cfg.H, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    w = (torch.randn(cfg.E, cfg.Hx, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
     bias = None
     if cfg.zipf_s > 0:
         # selection probability ~ rank^-s over a seeded permutation of expert ranks; the bias
@@ -223,9 +236,20 @@ def gen_shared(cfg):
     g = torch.Generator().manual_seed(3000 + cfg.seed)
     out = {}
     for role in ROLES:
-        rows, cols = (cfg.I_shared, cfg.H) if role != "down" else (cfg.H, cfg.I_shared)
+        rows, cols = (cfg.I_shared, cfg.Hx) if role != "down" else (cfg.Hx, cfg.I_shared)
         out[role] = (torch.randn(rows, cols, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
     return out
+
+
+def gen_latent(cfg):
+    """LatentMoE projections: down BF16 [H, H_model] (latent ~ N(0, 1)), up BF16 [H_model, H], norm fp32 [H]."""
+    if not cfg.H_model:
+        return {}
+    g = torch.Generator().manual_seed(4000 + cfg.seed)
+    down = (torch.randn(cfg.H, cfg.H_model, generator=g, dtype=torch.float32) * cfg.H_model ** -0.5).to(torch.bfloat16)
+    up = (torch.randn(cfg.H_model, cfg.H, generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+    norm = (1.0 + 0.1 * (torch.rand(cfg.H, generator=g, dtype=torch.float32) - 0.5)).contiguous()
+    return {"down": down, "up": up, "norm": norm}
 
 
 def build_layer(cfg, device, expert_begin=0, expert_end=None, T=None, with_weights=True):
@@ -238,6 +262,7 @@ def build_layer(cfg, device, expert_begin=0, expert_end=None, T=None, with_weigh
     layer.router_w = w.to(device)
     layer.bias = b.to(device) if b is not None else None
     layer.shared = {r: t.to(device) for r, t in gen_shared(cfg).items()}
+    layer.latent = {r: t.to(device) for r, t in gen_latent(cfg).items()}
     if with_weights:
         for role in ROLES:
             p, s = gen_expert_range(cfg, role, expert_begin, expert_end, device)

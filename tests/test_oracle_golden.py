@@ -151,3 +151,17 @@ def test_expf_replica_matches_host_libm(port):
     lib.expf.argtypes = [C.c_float]
     ref = np.array([lib.expf(float(x)) for x in xs[:100000]], np.float32)
     assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
+
+
+def test_log1pf_replica_matches_host_libm(port):
+    # sqrt(softplus) router scores: the CUDA router evaluates this restatement of log1pf; it must agree bit for
+    # bit with the libm the reference's DSV4 router calls.  Arguments are expf(logit), logit <= 20.
+    rng = np.random.default_rng(1)
+    logits = np.concatenate([rng.uniform(-40, 20, 150000), rng.normal(0, 3, 150000)]).astype(np.float32)
+    xs = np.exp(logits, dtype=np.float32)
+    lib = C.CDLL("libm.so.6")
+    lib.log1pf.restype = C.c_float
+    lib.log1pf.argtypes = [C.c_float]
+    got = np.array([port.orc_log1pf_replica(float(x)) for x in xs], np.float32)
+    ref = np.array([lib.log1pf(float(x)) for x in xs], np.float32)
+    assert np.array_equal(got.view(np.uint32), ref.view(np.uint32))
