@@ -37,7 +37,15 @@ struct strata_moe_ctx {
     bool cmd_shared = false;
     std::vector<void*> cmd_scratch;    // device buffers of the command in flight (row lists, gathered rows)
     uint64_t workspace_allocations = 0;
+    // Activation workspaces shared by every layer of the context (a model has tens of MoE layers that run one
+    // after the other on the context's stream; sizing them per layer would multiply gigabytes by the layer
+    // count).  Grown to the largest request; a layer picks the current pointers up at every call.
+    void* ws[16] = {};
+    size_t ws_bytes[16] = {};
 };
+
+enum WsSlot { kWsXg, kWsXgLo, kWsActHi, kWsActLo, kWsY, kWsActF32, kWsXRow, kWsActRow, kWsShActHi, kWsShActLo, kWsShY,
+              kWsXStage, kWsOutStage, kWsCount };
 
 struct DeviceTable {
     std::vector<const uint8_t*> packed, scales;
@@ -165,6 +173,41 @@ cudaError_t dalloc(strata_moe_layer* L, T** p, size_t n) {
     return e;
 }
 
+cudaError_t ws_reserve(strata_moe_ctx* ctx, int slot, size_t bytes) {
+    if (bytes <= ctx->ws_bytes[slot]) return cudaSuccess;
+    // nothing enqueued may still use the old buffer
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess && ctx->side) e = cudaStreamSynchronize(ctx->side);
+    if (e != cudaSuccess) return e;
+    if (ctx->ws[slot]) cudaFree(ctx->ws[slot]);
+    ctx->ws[slot] = nullptr;
+    ctx->ws_bytes[slot] = 0;
+    e = cudaMalloc(&ctx->ws[slot], bytes);
+    if (e != cudaSuccess) return e;
+    ctx->ws_bytes[slot] = bytes;
+    // rows the tensor-core path owns are still swept by the f32 -> f16 conversion pass: keep them finite
+    if (slot == kWsActF32) e = cudaMemset(ctx->ws[slot], 0, bytes);
+    return e;
+}
+
+// The context's current workspaces as this layer's pointers (they may have been regrown by another layer).
+void bind_ws(strata_moe_layer* L) {
+    strata_moe_ctx* c = L->ctx;
+    L->xg = static_cast<__nv_bfloat16*>(c->ws[kWsXg]);
+    L->xg_lo = static_cast<__nv_bfloat16*>(c->ws[kWsXgLo]);
+    L->act_hi = static_cast<__nv_bfloat16*>(c->ws[kWsActHi]);
+    L->act_lo = static_cast<__nv_bfloat16*>(c->ws[kWsActLo]);
+    L->y = static_cast<float*>(c->ws[kWsY]);
+    L->act_f32 = static_cast<float*>(c->ws[kWsActF32]);
+    L->x_rowscale = static_cast<float*>(c->ws[kWsXRow]);
+    L->act_rowscale = static_cast<float*>(c->ws[kWsActRow]);
+    L->sh_act_hi = static_cast<__nv_bfloat16*>(c->ws[kWsShActHi]);
+    L->sh_act_lo = static_cast<__nv_bfloat16*>(c->ws[kWsShActLo]);
+    L->sh_y = static_cast<float*>(c->ws[kWsShY]);
+    L->x_stage = static_cast<__nv_bfloat16*>(c->ws[kWsXStage]);
+    L->out_stage = static_cast<float*>(c->ws[kWsOutStage]);
+}
+
 size_t packed_bytes(int fmt, uint32_t rows, uint32_t cols) {
     return fmt == STRATA_MOE_FMT_BF16 ? (size_t)rows * cols * 2 : (size_t)rows * cols / 2;
 }
@@ -181,6 +224,7 @@ bool tensor_path_ok(const strata_moe_layer* L, int fmt, uint32_t I) {
 
 int sync_tables(strata_moe_layer* L) {
     strata_moe_ctx* ctx = L->ctx;
+    bind_ws(L);
     if (!L->tables_dirty) return 0;
     const uint32_t n = L->d.expert_count;
     for (int r = 0; r < 3; ++r) {
@@ -651,6 +695,10 @@ void strata_moe_destroy(strata_moe_ctx* ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->cmd_layer) strata_moe_layer_destroy(ctx->cmd_layer);
     for (void* p : ctx->cmd_scratch) cudaFree(p);
+    for (void*& p : ctx->ws) {
+        if (p) cudaFree(p);
+        p = nullptr;
+    }
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->d_router_rechecks) cudaFree(ctx->d_router_rechecks);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
@@ -779,11 +827,11 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         if (ps) L->owned.push_back(ps);
         L->prefill_scratch = ps;
     }
-    A(dalloc(L, &L->xg, (size_t)P * H));
-    A(dalloc(L, &L->xg_lo, 1));
-    A(dalloc(L, &L->act_hi, (size_t)P * I));
-    A(dalloc(L, &L->act_lo, (size_t)P * I));
-    A(dalloc(L, &L->y, (size_t)P * H));
+    A(ws_reserve(ctx, kWsXg, (size_t)P * H * 2));
+    A(ws_reserve(ctx, kWsXgLo, 16));
+    A(ws_reserve(ctx, kWsActHi, (size_t)P * I * 2));
+    A(ws_reserve(ctx, kWsActLo, (size_t)P * I * 2));
+    A(ws_reserve(ctx, kWsY, (size_t)P * H * 4));
     A(dalloc(L, &L->one_global, 1));
     A(dalloc(L, &L->d_not_ok, 1));
     {
@@ -796,27 +844,26 @@ int strata_moe_layer_create(strata_moe_ctx* ctx, const strata_moe_layer_desc* de
         if (sm) L->owned.push_back(sm);
         L->d_smaps = sm;
     }
-    A(dalloc(L, &L->act_f32, (size_t)P * I));
-    A(dalloc(L, &L->x_rowscale, (size_t)P));
-    A(dalloc(L, &L->act_rowscale, (size_t)P));
+    A(ws_reserve(ctx, kWsActF32, (size_t)P * I * 4));
+    A(ws_reserve(ctx, kWsXRow, (size_t)P * 4));
+    A(ws_reserve(ctx, kWsActRow, (size_t)P * 4));
     if (d.shared_intermediate) {
         A(dalloc(L, &L->shared_tiles, prefill_scratch_bytes(1, T) / sizeof(uint32_t) + 4));
-        A(dalloc(L, &L->sh_act_hi, (size_t)T * d.shared_intermediate));
-        A(dalloc(L, &L->sh_act_lo, (size_t)T * d.shared_intermediate));
-        A(dalloc(L, &L->sh_y, (size_t)T * H));
+        A(ws_reserve(ctx, kWsShActHi, (size_t)T * d.shared_intermediate * 2));
+        A(ws_reserve(ctx, kWsShActLo, (size_t)T * d.shared_intermediate * 2));
+        A(ws_reserve(ctx, kWsShY, (size_t)T * H * 4));
     }
     A(dalloc(L, &L->router_tiles, prefill_scratch_bytes(1, T) / sizeof(uint32_t) + 4));
     A(dalloc(L, &L->router_off2, 2));
     A(dalloc(L, &L->recheck_list, (size_t)T));
     A(dalloc(L, &L->recheck_count, 1));
-    A(dalloc(L, &L->x_stage, (size_t)T * H));
-    A(dalloc(L, &L->out_stage, (size_t)T * H));
+    A(ws_reserve(ctx, kWsXStage, (size_t)T * H * 2));
+    A(ws_reserve(ctx, kWsOutStage, (size_t)T * H * 4));
+    bind_ws(L);
     if (e == cudaSuccess) {
         const float one = 1.0f;
         e = cudaMemcpy(L->one_global, &one, sizeof(float), cudaMemcpyHostToDevice);
     }
-    // rows the tensor-core path owns are still swept by the f32 -> f16 conversion pass: keep them finite
-    if (e == cudaSuccess) e = cudaMemset(L->act_f32, 0, (size_t)P * I * sizeof(float));
     if (e != cudaSuccess) {
         strata_moe_layer_destroy(L);
         return fail(ctx, STRATA_MOE_E_CUDA, std::string("layer allocation: ") + cudaGetErrorString(e));
@@ -1009,6 +1056,7 @@ int strata_moe_combine(strata_moe_layer* L, const float* y, const uint32_t* inv,
     if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
     if (T == 0) return 0;
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     const float* shared = nullptr;
     if (x_shared && L->d.shared_intermediate) {
         for (int r = 0; r < 3; ++r)
@@ -1138,6 +1186,7 @@ int strata_moe_forward_host(strata_moe_layer* L, const void* x_host, uint32_t T,
     if (T > L->d.max_tokens) return fail(ctx, STRATA_MOE_E_INVALID, "tokens exceed max_tokens");
     if (T == 0) return 0;
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     const size_t in_bytes = (size_t)T * L->d.hidden * 2, out_bytes = (size_t)T * L->d.hidden * 4;
     CK(cudaMemcpyAsync(L->x_stage, x_host, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
     int rc = strata_moe_forward(L, L->x_stage, T, L->out_stage, nullptr);
@@ -1214,6 +1263,7 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
             return fail(ctx, STRATA_MOE_E_INVALID, "only INT4 experts fold a coefficient; pass 1.0");
     }
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     cudaStream_t s = ctx->stream;
     const uint32_t H = d.hidden;
     if (!L->dense_hidden) {
@@ -1221,7 +1271,8 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
         CK(dalloc(L, &L->dense_coef, (size_t)L->max_pairs));
         CK(dalloc(L, &L->dense_ptrs, (size_t)6 * d.expert_count));
         CK(dalloc(L, &L->dense_globals, (size_t)3 * d.expert_count));
-        CK(dalloc(L, &L->xg_lo, (size_t)L->max_pairs * H));
+        CK(ws_reserve(ctx, kWsXgLo, (size_t)L->max_pairs * H * 2));
+        bind_ws(L);
         CK(cudaMallocHost(&L->dense_pinned, (size_t)d.expert_count * (6 * sizeof(void*) + 3 * sizeof(float)) +
                                                 (size_t)L->max_pairs * sizeof(float)));
     }
@@ -1295,6 +1346,7 @@ int strata_moe_collect_dense(strata_moe_layer* L, float* routed_output, float* s
     strata_moe_ctx* ctx = L->ctx;
     if (!L->dense_in_flight) return fail(ctx, STRATA_MOE_E_INVALID, "no MoE command is in flight");
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     // results reach the caller only after completion and a clean status are confirmed
     int rc = strata_moe_synchronize(ctx);
     L->dense_in_flight = false;
@@ -1496,6 +1548,7 @@ int strata_moe_latent_forward(strata_moe_latent* lat, const void* x, uint32_t T,
     CK(cudaSetDevice(ctx->device));
     cudaStream_t s = ctx->stream;
     strata_moe_layer* R = lat->route;
+    bind_ws(R);
     const strata_moe_layer_desc& rd = R->d;
     if (!tensor_path_ok(R, 3, 128)) return fail(ctx, STRATA_MOE_E_INVALID, "the LatentMoE projections need the tensor-core path");
     uint32_t* ids = ids_out ? ids_out : lat->ids;
@@ -1528,6 +1581,7 @@ int strata_moe_latent_forward(strata_moe_latent* lat, const void* x, uint32_t T,
         return fail(ctx, STRATA_MOE_E_CUDA, "latent up projection launch failed");
     if (shared) {
         CK(cudaStreamWaitEvent(s, ctx->ev_join, 0));
+        bind_ws(R);
         launch_add_rows(out, R->sh_y, (size_t)T * lat->H, s);
     }
     CK(cudaGetLastError());
@@ -1723,6 +1777,7 @@ int strata_moe_command_collect(strata_moe_ctx* ctx, float* routed_out, size_t ro
     if (ctx->cmd_kind != 1) return fail(ctx, STRATA_MOE_E_INVALID, "no MoE command is in flight");
     strata_moe_layer* L = ctx->cmd_layer;
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     // every return consumes or drains the command; results reach the caller only after completion and a
     // clean status word are confirmed
     const int rc = strata_moe_synchronize(ctx);
@@ -2098,6 +2153,7 @@ int strata_moe_ep_dispatch(strata_moe_ep* ep) {
     strata_moe_ctx* ctx = L->ctx;
     if (ep->stage != 1) return fail(ctx, STRATA_MOE_E_INVALID, "ep_dispatch must follow ep_begin");
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     cudaStream_t s = ctx->stream;
     launch_ep_plan(ep->w, ep->dst_row, ep->loffsets, ep->abort_word, ctx->d_status, s);
     launch_ep_dispatch(ep->w, ep->x, L->ids, L->perm, L->offsets, ep->dst_row, ep->T * L->d.top_k, L->d.top_k,
@@ -2114,6 +2170,7 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     strata_moe_ctx* ctx = L->ctx;
     if (ep->stage != 2) return fail(ctx, STRATA_MOE_E_INVALID, "ep_experts must follow ep_dispatch");
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     cudaStream_t s = ctx->stream;
     const uint32_t par = ep->w.step & 1u, B = L->d.expert_count;
     launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
@@ -2138,6 +2195,7 @@ int strata_moe_ep_finish(strata_moe_ep* ep, float* out) {
     if (ep->stage != 3) return fail(ctx, STRATA_MOE_E_INVALID, "ep_finish must follow ep_experts");
     if (!out && ep->T) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
     CK(cudaSetDevice(ctx->device));
+    bind_ws(L);
     cudaStream_t s = ctx->stream;
     const float* shared = nullptr;
     if (ep->forked) {
