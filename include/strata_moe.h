@@ -121,6 +121,8 @@ typedef struct strata_moe_stats {
     uint64_t router_rechecked_tokens; /* of those, tokens recomputed completely by the canonical kernels */
     uint64_t command_calls;           /* handle-based commands collected */
     uint64_t workspace_allocations;   /* times a command had to (re)build its workspace */
+    float router_worst_error;         /* fast router: largest |canonical - tensor-core logit| seen on a selected expert,
+                                         as a fraction of the bound delta the selection assumes (trusted up to 0.5) */
 } strata_moe_stats;
 
 /* ---- context ------------------------------------------------------------------------

@@ -59,7 +59,7 @@ class Stats(C.Structure):
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64), ("weight_bytes", C.c_uint64),
                 ("last_forward_ms", C.c_float), ("router_fast_tokens", C.c_uint64),
                 ("router_rechecked_tokens", C.c_uint64), ("command_calls", C.c_uint64),
-                ("workspace_allocations", C.c_uint64)]
+                ("workspace_allocations", C.c_uint64), ("router_worst_error", C.c_float)]
 
 
 def library_path():

@@ -41,6 +41,7 @@ struct strata_moe_ctx {
     // after the other on the context's stream; sizing them per layer would multiply gigabytes by the layer
     // count).  Grown to the largest request; a layer picks the current pointers up at every call.
     void* ws[16] = {};
+    strata_moe_layer* ws_owner = nullptr;   // layer whose command holds results in the pool until collected
     size_t ws_bytes[16] = {};
 };
 
@@ -63,13 +64,14 @@ struct LayerKnobs {
     bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
     bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
     bool no_stream_ring = false;    // STRATA_MOE_NO_STREAM_RING: small batches use the register-streaming kernels
+    bool no_fp8_ring = false;       // STRATA_MOE_NO_FP8_RING: the MXFP4 ring kernels keep f16 MMAs
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
     int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
     int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
-    bool exact_router_weights = false;  // STRATA_MOE_EXACT_ROUTER_WEIGHTS: the fast router recomputes the selected logits
+    int stream_ring_max_rows = 8;   // STRATA_MOE_STREAM_RING_MAX_ROWS: largest token tile (8 or 16) given to the ring kernels
 };
 
 static LayerKnobs read_knobs() {
@@ -86,8 +88,9 @@ static LayerKnobs read_knobs() {
     k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
+    k.no_fp8_ring = getenv("STRATA_MOE_NO_FP8_RING") != nullptr;
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
-    k.exact_router_weights = getenv("STRATA_MOE_EXACT_ROUTER_WEIGHTS") != nullptr;
+    k.stream_ring_max_rows = num("STRATA_MOE_STREAM_RING_MAX_ROWS", 8);
     return k;
 }
 
@@ -224,6 +227,8 @@ bool tensor_path_ok(const strata_moe_layer* L, int fmt, uint32_t I) {
 
 int sync_tables(strata_moe_layer* L) {
     strata_moe_ctx* ctx = L->ctx;
+    if (ctx->ws_owner && ctx->ws_owner != L)
+        return fail(ctx, STRATA_MOE_E_BUSY, "a MoE command of another layer of this context is in flight");
     bind_ws(L);
     if (!L->tables_dirty) return 0;
     const uint32_t n = L->d.expert_count;
@@ -399,7 +404,7 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
             return fail(ctx, STRATA_MOE_E_CUDA, "tensor-core router projection launch failed");
         mark(ctx, 1);
         launch_route_fast(rp, L->logits, L->bias, x, L->router, T, d.hidden, ids, w, L->recheck_list, L->recheck_count,
-                          ctx->d_router_rechecks, ctx->d_status, s, L->knobs.exact_router_weights);
+                          ctx->d_router_rechecks, ctx->d_status, s);
         ctx->router_fast_tokens += T;
         return 0;
     }
@@ -499,15 +504,29 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         p.ntile = 128;   // hybrid down: few rows per expert
         a.skip_from = big;
-        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        // the ring kernels win while a group fits one 8-row token tile (measured: 8 tokens of c0 99 us against 114 us;
+        // 256 tokens of c1, 16-row tiles and several passes per group: 419 us against 339 us)
+        const bool ring = L->stream_ok && a.max_rows_per_group <= (uint32_t)L->knobs.stream_ring_max_rows;
+        // MXFP4 through the ring: FP8 MMAs on E4M3 terms of the activations, unless some groups of this step go to the
+        // tensor-core path (which reads the f16 rows) or the switch is off
+        const bool fp8 = ring && !big && !down_all_tensor && !L->knobs.no_fp8_ring && decode_stream_fp8_supported(L->d.format);
+        a.fp8_terms = fp8 ? 1u : 0u;
+        if (fp8)
+            launch_rows_to_e4m3_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        else
+            launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
-        if (L->stream_ok) {
+        if (ring) {
             if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
-        launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
-                               L->act_rowscale, s, pairs_dev);
+        if (fp8)
+            launch_rows_to_e4m3_f32(L->act_f32, bound, L->d.intermediate, L->act_hi, L->act_lo, L->act_rowscale, s,
+                                    pairs_dev);
+        else
+            launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
+                                   L->act_rowscale, s, pairs_dev);
         if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
             p.min_rows = big;
             p.ntile = 128;   // measured at the c4 shape: 407 us with 128-token tiles, 439 us with 192
@@ -525,7 +544,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
             if (launch_prefill_down(p, L->act_hi, L->act_rowscale, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill down launch failed");
         } else {
-            if (L->stream_ok) {
+            if (ring) {
                 if (launch_decode_stream_down(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
             } else {
                 launch_decode_fp4_down(a, s);
@@ -667,8 +686,8 @@ int strata_moe_create(int device, void* stream, strata_moe_ctx** out) {
         strata_moe_destroy(ctx);
         return STRATA_MOE_E_CUDA;
     }
-    if (cudaMalloc(&ctx->d_router_rechecks, sizeof(unsigned long long)) != cudaSuccess ||
-        cudaMemset(ctx->d_router_rechecks, 0, sizeof(unsigned long long)) != cudaSuccess) {
+    if (cudaMalloc(&ctx->d_router_rechecks, 2 * sizeof(unsigned long long)) != cudaSuccess ||
+        cudaMemset(ctx->d_router_rechecks, 0, 2 * sizeof(unsigned long long)) != cudaSuccess) {
         strata_moe_destroy(ctx);
         return STRATA_MOE_E_CUDA;
     }
@@ -740,10 +759,14 @@ int strata_moe_get_stats(const strata_moe_ctx* ctx, strata_moe_stats* out) {
     out->router_fast_tokens = ctx->router_fast_tokens;
     out->workspace_allocations = ctx->workspace_allocations;
     out->router_rechecked_tokens = 0;
+    out->router_worst_error = 0.0f;
     if (ctx->d_router_rechecks) {   // waits for the work enqueued so far
-        unsigned long long v = 0;
-        if (cudaMemcpy(&v, ctx->d_router_rechecks, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess)
-            out->router_rechecked_tokens = v;
+        unsigned long long v[2] = {0, 0};    // [0] rechecked tokens, [1] float bits of the worst error fraction
+        if (cudaMemcpy(v, ctx->d_router_rechecks, sizeof(v), cudaMemcpyDeviceToHost) == cudaSuccess) {
+            out->router_rechecked_tokens = v[0];
+            const uint32_t bits = (uint32_t)v[1];
+            memcpy(&out->router_worst_error, &bits, sizeof(bits));
+        }
     }
     return 0;
 }
@@ -876,6 +899,7 @@ void strata_moe_layer_destroy(strata_moe_layer* L) {
     if (!L) return;
     cudaSetDevice(L->ctx->device);
     cudaStreamSynchronize(L->ctx->stream);
+    if (L->ctx->ws_owner == L) L->ctx->ws_owner = nullptr;
     for (void* p : L->owned) cudaFree(p);
     if (L->dense_pinned) cudaFreeHost(L->dense_pinned);
     delete L;
@@ -1242,6 +1266,8 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
     const strata_moe_layer_desc& d = L->d;
     if (L->dense_in_flight)
         return fail(ctx, STRATA_MOE_E_BUSY, "a MoE command is already in flight on this layer");
+    if (ctx->ws_owner && ctx->ws_owner != L)
+        return fail(ctx, STRATA_MOE_E_BUSY, "a MoE command of another layer of this context is in flight");
     if (!hidden_host || rows == 0) return fail(ctx, STRATA_MOE_E_INVALID, "hidden rows are required");
     if (n == 0 && !with_shared) return fail(ctx, STRATA_MOE_E_INVALID, "command has no experts");
     if (n && (!experts || !coefficients)) return fail(ctx, STRATA_MOE_E_INVALID, "null expert list");
@@ -1335,6 +1361,7 @@ int strata_moe_enqueue_dense(strata_moe_layer* L, const float* hidden_host, uint
     }
     CK(cudaGetLastError());
     L->dense_in_flight = true;
+    ctx->ws_owner = L;
     L->dense_rows = rows;
     L->dense_n = n;
     L->dense_shared = with_shared != 0;
@@ -1350,6 +1377,7 @@ int strata_moe_collect_dense(strata_moe_layer* L, float* routed_output, float* s
     // results reach the caller only after completion and a clean status are confirmed
     int rc = strata_moe_synchronize(ctx);
     L->dense_in_flight = false;
+    ctx->ws_owner = nullptr;
     if (rc) return rc;
     const size_t H = L->d.hidden;
     if (L->dense_n) {
@@ -1783,6 +1811,7 @@ int strata_moe_command_collect(strata_moe_ctx* ctx, float* routed_out, size_t ro
     const int rc = strata_moe_synchronize(ctx);
     ctx->cmd_kind = 0;
     L->dense_in_flight = false;
+    ctx->ws_owner = nullptr;
     if (rc) return rc;
     const size_t H = L->d.hidden, row_floats = (size_t)ctx->cmd_rows * H;
     if (routed_floats != (size_t)ctx->cmd_n * row_floats || (ctx->cmd_n && !routed_out))

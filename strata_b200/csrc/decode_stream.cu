@@ -35,6 +35,8 @@
 // Replaces the reference's per-row NVFP4 / DeepSeek FP4 expert kernels for decode batches
 // (kernels/cuda/backend.cu:1978-2069, 2308-2413).
 #include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "stream_ring.cuh"
 
@@ -131,7 +133,13 @@ struct JobInfo {
 // DUAL = true : gate/up + SwiGLU, writes act fp32 [pairs, I].   K = H, a unit is 16 gate + 16 up rows.
 // DUAL = false: down, writes y fp32 [pairs, H].                 K = I, a unit is 2 x 16 rows.
 // maps: [3 roles][n_groups][3] tensor maps (64-row weight boxes, 16-row weight boxes, scale boxes).
-template <int FMT, int NT, bool SPLIT, bool DUAL>
+// F8 (MXFP4 only): the weights enter m16n8k32 E4M3 MMAs (an E2M1 code is an E4M3 code after two shifts and two masks:
+// the hardware E2M1 -> f16 conversion runs on the conversion unit at a quarter of the rate these kernels need, and that
+// unit, not memory, bounded the f16 variant).  The activations arrive as E4M3 TERMS of their row-scaled value, sixteen
+// bytes per eight columns: term 1 of columns 0 2 4 6, of 1 3 5 7, term 2 likewise (rows_to_e4m3_kernel); x_hi holds
+// terms 1 + 2, and for the down projection x_lo holds terms 3 + 4 scaled by 2^8.  Every term costs one MMA on the same
+// weight registers.  A BF16 activation is reproduced exactly by two terms unless it is below 2^-9 of its row maximum.
+template <int FMT, int NT, bool SPLIT, bool DUAL, bool F8>
 __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs a, const CUtensorMap* __restrict__ maps) {
     using G = StreamGeo<FMT, NT, SPLIT>;
     constexpr uint32_t S = G::kStages;
@@ -300,7 +308,49 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                 const uint32_t sc0 = st + G::kSOff + row_lo * ScaleGeo<FMT>::kPitch + ks * ScaleGeo<FMT>::kStepBytes;
                 const uint32_t sc1 = sc0 + kBoxRows * ScaleGeo<FMT>::kPitch;
                 const uint32_t xrow = st + G::kXOff + gid * kXP + ks * 256u + t * 16u;
-                if (FMT == STRATA_MOE_FMT_MXFP4) {
+                if (F8) {
+                    // as the MXFP4 branch below, with FP8 MMAs: 32 columns (one E8M0 block) per MMA and term
+                    const uint32_t s0l = lds32(sc0), s0h = lds32(sc0 + 8u * ScaleGeo<FMT>::kPitch);
+                    const uint32_t s1l = lds32(sc1), s1h = lds32(sc1 + 8u * ScaleGeo<FMT>::kPitch);
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        uint4 bh[NT], bl[SPLIT ? NT : 1];
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
+                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
+                        }
+#pragma unroll
+                        for (int p = 0; p < 2; ++p) {
+                            const uint32_t box = p ? box1 : box0;
+                            uint32_t a0, a1, a2, a3;
+                            e2m1x8_e4m3(lds32(box + woff[wd]), a0, a2);
+                            e2m1x8_e4m3(lds32(box + woff[wd] + 8u * 128u), a1, a3);
+                            const float fl = __uint_as_float((((p ? s1l : s0l) >> (8 * wd)) & 0xFFu) << 23);
+                            const float fh = __uint_as_float((((p ? s1h : s0h) >> (8 * wd)) & 0xFFu) << 23);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                float* cacc = p ? acc1[nt] : acc0[nt];
+                                float tmp[4];
+                                mma_e4m3_zero(tmp, a0, a1, a2, a3, bh[nt].x, bh[nt].y);
+                                mma_e4m3(tmp, a0, a1, a2, a3, bh[nt].z, bh[nt].w);
+                                cacc[0] = fmaf(tmp[0], fl, cacc[0]);
+                                cacc[1] = fmaf(tmp[1], fl, cacc[1]);
+                                cacc[2] = fmaf(tmp[2], fh, cacc[2]);
+                                cacc[3] = fmaf(tmp[3], fh, cacc[3]);
+                                if (SPLIT) {
+                                    const float fl2 = fl * 0.00390625f, fh2 = fh * 0.00390625f;   // terms 3, 4 carry 2^8
+                                    mma_e4m3_zero(tmp, a0, a1, a2, a3, bl[nt].x, bl[nt].y);
+                                    mma_e4m3(tmp, a0, a1, a2, a3, bl[nt].z, bl[nt].w);
+                                    cacc[0] = fmaf(tmp[0], fl2, cacc[0]);
+                                    cacc[1] = fmaf(tmp[1], fl2, cacc[1]);
+                                    cacc[2] = fmaf(tmp[2], fh2, cacc[2]);
+                                    cacc[3] = fmaf(tmp[3], fh2, cacc[3]);
+                                }
+                            }
+                        }
+                    }
+                } else if (FMT == STRATA_MOE_FMT_MXFP4) {
                     // E8M0 block scales are powers of two and one 32-column block is exactly the two MMAs of
                     // a (word index, tile): the raw E2M1 values go into the MMAs and the FP32 partial sum of
                     // the block is scaled (exactly) on its way into the accumulator -- four multiply-adds in
@@ -404,6 +454,7 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
         // sums are added in k-step order
         if (my_unit) {
             float s0 = 1.0f, s1 = 1.0f;     // MXFP4: the block scales went into the accumulators whole
+            if (F8) s0 = s1 = 64.0f;        // an E2M1 code read as E4M3 is 2^-6 of its value
             if (FMT != STRATA_MOE_FMT_MXFP4) {
                 if (DUAL) { s0 = a.gate.post_scale[j.g]; s1 = a.up.post_scale[j.g]; }
                 else { s0 = s1 = a.down.post_scale[j.g]; }
@@ -475,14 +526,14 @@ bool encode_u8_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int FMT, int NT, bool SPLIT, bool DUAL>
+template <int FMT, int NT, bool SPLIT, bool DUAL, bool F8>
 int launch_stream_one(const DecodeArgs& a, const void* maps, cudaStream_t s) {
     using G = StreamGeo<FMT, NT, SPLIT>;
     static bool attr[64] = {};   // the shared-memory opt-in is per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
     if (!attr[dev]) {
-        if (cudaFuncSetAttribute(decode_stream_kernel<FMT, NT, SPLIT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(decode_stream_kernel<FMT, NT, SPLIT, DUAL, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)G::kSmem) != cudaSuccess)
             return -1;
         attr[dev] = true;
@@ -491,15 +542,15 @@ int launch_stream_one(const DecodeArgs& a, const void* maps, cudaStream_t s) {
     const uint32_t jobs = a.n_groups * ((DUAL ? R / 16u : R / 32u) + kJobUnits - 1u) / kJobUnits;
     if (jobs == 0u) return 0;
     const uint32_t grid = jobs < (uint32_t)kNumSMs ? jobs : (uint32_t)kNumSMs;
-    decode_stream_kernel<FMT, NT, SPLIT, DUAL><<<grid, kSThreads, G::kSmem, s>>>(a, static_cast<const CUtensorMap*>(maps));
+    decode_stream_kernel<FMT, NT, SPLIT, DUAL, F8><<<grid, kSThreads, G::kSmem, s>>>(a, static_cast<const CUtensorMap*>(maps));
     ++g_kernel_launches;
     return 0;
 }
 
-template <int FMT, bool SPLIT, bool DUAL>
+template <int FMT, bool SPLIT, bool DUAL, bool F8 = false>
 int launch_stream_nt(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    return a.max_rows_per_group <= 8u ? launch_stream_one<FMT, 1, SPLIT, DUAL>(a, maps, s)
-                                      : launch_stream_one<FMT, 2, SPLIT, DUAL>(a, maps, s);
+    return a.max_rows_per_group <= 8u ? launch_stream_one<FMT, 1, SPLIT, DUAL, F8>(a, maps, s)
+                                      : launch_stream_one<FMT, 2, SPLIT, DUAL, F8>(a, maps, s);
 }
 
 }  // namespace
@@ -527,17 +578,125 @@ int decode_stream_encode_maps(void* out, int fmt, const void* packed, const void
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// Rows -> E4M3 terms for the FP8 variant (one warp per destination row).  The row is scaled by a power of two that
+// puts its maximum into [128, 256) (E4M3 holds up to 448); term 1 = the scaled value rounded to E4M3, term 2 = the
+// remainder rounded, and for an fp32 source terms 3 and 4 continue on the remainder times 2^8.  Layout per eight
+// columns, sixteen bytes: term 1 of columns 0 2 4 6, of 1 3 5 7, then term 2 likewise (hi); terms 3 and 4 the same
+// way (lo).  A value that is not finite becomes the E4M3 NaN so that it still poisons its row's results.
+namespace {
+
+__device__ __forceinline__ uint32_t q_e4m3(float v) {
+    if (!(fabsf(v) <= 3.0e38f)) return 0x7Fu;
+    return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ float dq_e4m3(uint32_t b) {
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
+}
+__device__ __forceinline__ uint32_t pack_even_odd(const uint32_t b[8], uint32_t& odd) {
+    odd = b[1] | (b[3] << 8) | (b[5] << 16) | (b[7] << 24);
+    return b[0] | (b[2] << 8) | (b[4] << 16) | (b[6] << 24);
+}
+
+template <bool SRC_F32>
+__global__ void __launch_bounds__(256) rows_to_e4m3_kernel(const void* __restrict__ src, const uint32_t* __restrict__ perm,
+                                                           uint32_t k_div, uint32_t rows, uint32_t C,
+                                                           uint4* __restrict__ hi, uint4* __restrict__ lo,
+                                                           float* __restrict__ rowscale,
+                                                           const uint32_t* __restrict__ rows_dev) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t pos = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (pos >= rows) return;
+    if (rows_dev && pos >= *rows_dev) return;   // `rows` is only an upper bound; the count lives on the device
+    const uint32_t srow = perm ? perm[pos] / k_div : pos;
+    auto load8 = [&](uint32_t i, float v[8]) {
+        if (SRC_F32) {
+            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)srow * C) + 2u * i;
+            const float4 x0 = __ldg(p), x1 = __ldg(p + 1);
+            v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
+        } else {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C) + i);
+            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                v[2 * q] = __uint_as_float(w[q] << 16);
+                v[2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
+            }
+        }
+    };
+    float mx = 0.0f;
+    for (uint32_t i = lane; i < C / 8u; i += 32u) {
+        float v[8];
+        load8(i, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mx = fmaxf(mx, fabsf(v[q]));     // fmaxf drops a NaN; the NaN itself is kept below
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    int ex = 0;
+    if (mx > 0.0f && mx < 3.0e38f) ex = 7 - (int)((__float_as_uint(mx) >> 23) & 0xFFu) + 127;
+    ex = max(-100, min(100, ex));
+    const float sc = __uint_as_float((uint32_t)(ex + 127) << 23);
+    if (lane == 0) rowscale[pos] = __uint_as_float((uint32_t)(127 - ex) << 23);
+    for (uint32_t i = lane; i < C / 8u; i += 32u) {
+        float v[8];
+        load8(i, v);
+        uint32_t t1[8], t2[8], t3[8], t4[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const float f = v[q] * sc;
+            t1[q] = q_e4m3(f);
+            const float r1 = f - dq_e4m3(t1[q]);
+            t2[q] = q_e4m3(r1);
+            if (SRC_F32) {
+                const float r2 = (r1 - dq_e4m3(t2[q])) * 256.0f;
+                t3[q] = q_e4m3(r2);
+                t4[q] = q_e4m3(r2 - dq_e4m3(t3[q]));
+            }
+        }
+        uint4 o;
+        o.x = pack_even_odd(t1, o.y);
+        o.z = pack_even_odd(t2, o.w);
+        hi[(size_t)pos * (C / 8u) + i] = o;
+        if (SRC_F32) {
+            o.x = pack_even_odd(t3, o.y);
+            o.z = pack_even_odd(t4, o.w);
+            lo[(size_t)pos * (C / 8u) + i] = o;
+        }
+    }
+}
+
+}  // namespace
+
+void launch_rows_to_e4m3_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t C,
+                              void* hi, float* rowscale, cudaStream_t s, const uint32_t* rows_dev) {
+    if (rows == 0) return;
+    rows_to_e4m3_kernel<false><<<(rows + 7) / 8, 256, 0, s>>>(x, perm, k_div, rows, C, static_cast<uint4*>(hi), nullptr,
+                                                             rowscale, rows_dev);
+    ++g_kernel_launches;
+}
+
+void launch_rows_to_e4m3_f32(const float* x, uint32_t rows, uint32_t C, void* hi, void* lo, float* rowscale,
+                             cudaStream_t s, const uint32_t* rows_dev) {
+    if (rows == 0) return;
+    rows_to_e4m3_kernel<true><<<(rows + 7) / 8, 256, 0, s>>>(x, nullptr, 1, rows, C, static_cast<uint4*>(hi),
+                                                            static_cast<uint4*>(lo), rowscale, rows_dev);
+    ++g_kernel_launches;
+}
+
+bool decode_stream_fp8_supported(int fmt) { return fmt == STRATA_MOE_FMT_MXFP4; }
+
 int launch_decode_stream_gate_up(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    const bool split = a.x_lo != nullptr;
     if (a.fmt == STRATA_MOE_FMT_MXFP4)
-        return split ? launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, true>(a, maps, s)
-                     : launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true>(a, maps, s);
-    return split ? launch_stream_nt<STRATA_MOE_FMT_NVFP4, true, true>(a, maps, s)
-                 : launch_stream_nt<STRATA_MOE_FMT_NVFP4, false, true>(a, maps, s);
+        return a.fp8_terms ? launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true, true>(a, maps, s)
+                           : launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true>(a, maps, s);
+    return launch_stream_nt<STRATA_MOE_FMT_NVFP4, false, true>(a, maps, s);
 }
 
 int launch_decode_stream_down(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    if (a.fmt == STRATA_MOE_FMT_MXFP4) return launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false>(a, maps, s);
+    if (a.fmt == STRATA_MOE_FMT_MXFP4)
+        return a.fp8_terms ? launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false, true>(a, maps, s)
+                           : launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false>(a, maps, s);
     return launch_stream_nt<STRATA_MOE_FMT_NVFP4, true, false>(a, maps, s);
 }
 

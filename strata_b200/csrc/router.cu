@@ -451,17 +451,17 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
 //      values differ by more than the sum of their bounds; the token is "safe" when every
 //      consecutive pair of the k selected is certain and the k-th is certain against the largest
 //      value + bound among all the others;
-//   3. routing weights: by default from the approximate logits of the selected experts (they differ
-//      from the canonical weights by a few units in the last place; expert ids, their rank order and
-//      therefore the permutation and the counts are exact).  With exact_weights the logits of the k
-//      selected experts are recomputed in the canonical lane-strided order (k * H multiply-adds per
-//      token) and the weights are bit-exact too.  Either way one token in 32 (every token with
-//      exact_weights) recomputes its selected logits canonically and checks delta on them: if any is
-//      further than delta / 2 from the approximate logit the token is not trusted;
+//   3. the logits of the k selected experts are recomputed in the canonical lane-strided order
+//      (k * H multiply-adds per token, router rows from L2), so the routing weights are bit-exact;
+//      the same values check delta: if any selected logit is further than delta / 2 from its
+//      approximate value the token is not trusted.  The largest distance seen, as a fraction of
+//      delta, is kept in recheck_total[1] (float bits) for the statistics;
 //   4. tokens that are not safe go on a list; the canonical kernels recompute them completely.
 // delta = 2^-13 * max(2, max_e |logit|): both summation orders round at most a few hundred partial
 // sums of magnitude <= that maximum (relative 2^-24 each; the tensor cores may truncate, 2^-23), so
-// the true distance is orders of magnitude below delta, and step 3 verifies that on every token.
+// the true distance is orders of magnitude below delta; step 3 verifies that on the selected logits of every
+// token.  For the experts that were NOT selected delta is an assumption, not a proof: a projection error
+// above delta on one of them alone could hide an expert that belongs in the selection.
 // The softmax rule normalises over all experts and is not served by this path.
 __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l, float& slope) {
     float cap = 1.0f;
@@ -488,7 +488,16 @@ __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l,
 
 constexpr int kFastWarps = 4;
 
-template <bool EXACT_W>
+// eight products of one 16-byte weight load with the matching activations, each added to its own chain
+__device__ __forceinline__ void chain_fma8(float (&c)[8], const uint4& xv, const uint4& wv) {
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        c[2 * i] = __fmaf_rn(__uint_as_float(xw[i] << 16), __uint_as_float(ww[i] << 16), c[2 * i]);
+        c[2 * i + 1] = __fmaf_rn(__uint_as_float(xw[i] & 0xFFFF0000u), __uint_as_float(ww[i] & 0xFFFF0000u), c[2 * i + 1]);
+    }
+}
+
 __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias,
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
@@ -502,8 +511,13 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     float* choice = score + E;
     float* eps = choice + E;
     unsigned short* xs = reinterpret_cast<unsigned short*>(eps + E);
+    float worst = 0.0f;        // largest |canonical - approximate| / delta this warp has seen
     for (uint32_t tok = blockIdx.x * kFastWarps + warp; tok < T; tok += gridDim.x * kFastWarps) {
         const float* lg = logits + (size_t)tok * E;
+        {     // this token's activation row, 16-byte loads into shared memory; consumed after the selection
+            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
+            for (uint32_t i = lane; i < H / 8u; i += 32u) reinterpret_cast<uint4*>(xs)[i] = __ldg(src + i);
+        }
         bool bad = false;
         float mx = 0.0f;
         for (uint32_t e = lane; e < E; e += 32u) {
@@ -522,11 +536,6 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             score[e] = sc;
             choice[e] = __fadd_rn(sc, b);
             eps[e] = 1.25f * slope * delta + 4.8e-7f * (fabsf(sc) + fabsf(b)) + 1e-30f;
-        }
-        const bool check = EXACT_W || (tok & 31u) == 0u;     // recompute the selected logits canonically?
-        if (check) {     // this token's activation row: 16-byte loads into shared memory
-            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
-            for (uint32_t i = lane; i < H / 8u; i += 32u) reinterpret_cast<uint4*>(xs)[i] = __ldg(src + i);
         }
         __syncwarp();
         float my_c = 0.0f, my_e = 0.0f;
@@ -560,47 +569,45 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
         if (lane + 1u < k) certain = (my_c - my_e) > (next_c + next_e);
         else if (lane + 1u == k) certain = (my_c - my_e) > rest;
         bool safe = __all_sync(0xFFFFFFFFu, certain) && !__any_sync(0xFFFFFFFFu, bad);
-        // canonical-order logits of the selected experts
-        float my_logit = lane < k ? lg[my_id] : 0.0f;        // approximate unless recomputed below
-        // Two experts at a time: lane l owns columns l, l + 32, ... of both rows; sixteen 2-byte loads per row are
-        // issued before their multiply-adds, so 32 loads are in flight and the two sums form independent chains.
-        // Per (token, expert) the products are still added in increasing column order, then folded by the
-        // canonical five shuffle-down rounds.
-        const uint32_t per_lane = H / 32u;
-        for (uint32_t r = 0; r < k && safe && check; r += 2u) {
-            const uint32_t e0 = __shfl_sync(0xFFFFFFFFu, my_id, r);
-            const bool two = r + 1u < k;
-            const uint32_t e1 = two ? __shfl_sync(0xFFFFFFFFu, my_id, r + 1u) : e0;
-            const unsigned short* w0 = reinterpret_cast<const unsigned short*>(wg) + (size_t)e0 * H + lane;
-            const unsigned short* w1 = reinterpret_cast<const unsigned short*>(wg) + (size_t)e1 * H + lane;
-            float a0 = 0.0f, a1 = 0.0f;
-            for (uint32_t j0 = 0; j0 < per_lane; j0 += 16u) {
-                unsigned short v0[16], v1[16];
+        // Canonical-order logits of the selected experts, eight experts per pass.  The canonical dot product gives
+        // lane v the columns v, v + 32, ... (one multiply-add chain per lane, increasing column order) and folds the 32
+        // chains by five shuffle-down rounds.  Here four lanes serve one expert and each owns EIGHT of those chains
+        // (columns 8*sub .. 8*sub+7 of every 32): one 16-byte load feeds eight chains, the chains keep their
+        // order, and the fold below pairs the same chains in the same rounds, so the sum is bit-identical.
+        float my_logit = 0.0f;
+        const uint32_t grp = lane >> 2, sub = lane & 3u, per_lane = H / 32u;
+        for (uint32_t r0 = 0; r0 < k && safe; r0 += 8u) {
+            const uint32_t r = r0 + grp;
+            const uint32_t e = __shfl_sync(0xFFFFFFFFu, my_id, r < k ? r : 0u);
+            const uint4* wrow = reinterpret_cast<const uint4*>(wg + (size_t)e * H) + sub;
+            const uint4* xrow = reinterpret_cast<const uint4*>(xs) + sub;
+            float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t j = 0;
+            for (; j + 4u <= per_lane; j += 4u) {
+                uint4 wv[4];
 #pragma unroll
-                for (uint32_t q = 0; q < 16u; ++q) {
-                    const bool in = j0 + q < per_lane;
-                    v0[q] = in ? __ldg(w0 + (size_t)(j0 + q) * 32u) : (unsigned short)0;
-                    v1[q] = in && two ? __ldg(w1 + (size_t)(j0 + q) * 32u) : (unsigned short)0;
-                }
+                for (uint32_t q = 0; q < 4u; ++q) wv[q] = __ldg(wrow + (size_t)(j + q) * 4u);
 #pragma unroll
-                for (uint32_t q = 0; q < 16u; ++q)
-                    if (j0 + q < per_lane) {
-                        const float xv = __uint_as_float((uint32_t)xs[lane + (j0 + q) * 32u] << 16);
-                        a0 = __fmaf_rn(xv, __uint_as_float((uint32_t)v0[q] << 16), a0);
-                        a1 = __fmaf_rn(xv, __uint_as_float((uint32_t)v1[q] << 16), a1);
-                    }
+                for (uint32_t q = 0; q < 4u; ++q) chain_fma8(c, xrow[(size_t)(j + q) * 4u], wv[q]);
             }
+            for (; j < per_lane; ++j) chain_fma8(c, xrow[(size_t)j * 4u], __ldg(wrow + (size_t)j * 4u));
+            // rounds 16 and 8 pair chains held by different lanes of the group, rounds 4, 2, 1 chains of one lane
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                a0 = __fadd_rn(a0, __shfl_down_sync(0xFFFFFFFFu, a0, off));
-                a1 = __fadd_rn(a1, __shfl_down_sync(0xFFFFFFFFu, a1, off));
-            }
-            a0 = __shfl_sync(0xFFFFFFFFu, a0, 0);
-            a1 = __shfl_sync(0xFFFFFFFFu, a1, 0);
-            // the bound itself is checked on every token
-            if (!(fabsf(a0 - lg[e0]) <= 0.5f * delta) || (two && !(fabsf(a1 - lg[e1]) <= 0.5f * delta))) safe = false;
-            if (EXACT_W && lane == r) my_logit = a0;
-            if (EXACT_W && two && lane == r + 1u) my_logit = a1;
+            for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 2));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 1));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[i] = __fadd_rn(c[i], c[i + 4]);
+            c[0] = __fadd_rn(c[0], c[2]);
+            c[1] = __fadd_rn(c[1], c[3]);
+            c[0] = __fadd_rn(c[0], c[1]);
+            const float canon = __shfl_sync(0xFFFFFFFFu, c[0], ((lane - r0) & 7u) * 4u);
+            if (lane >= r0 && lane < r0 + 8u && lane < k) my_logit = canon;
+        }
+        if (safe && lane < k) {     // the premise of the bounds, checked on every selected logit
+            const float d = fabsf(my_logit - lg[my_id]);
+            worst = fmaxf(worst, d / delta);
+            if (!(d <= 0.5f * delta)) safe = false;
         }
         safe = __all_sync(0xFFFFFFFFu, safe);
         if (!safe) {
@@ -632,6 +639,10 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
         }
         __syncwarp();
     }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) worst = fmaxf(worst, __shfl_xor_sync(0xFFFFFFFFu, worst, off));
+    // non-negative floats order like their bit patterns
+    if (lane == 0 && worst > 0.0f) atomicMax(reinterpret_cast<unsigned int*>(recheck_total + 1), __float_as_uint(worst));
 }
 
 bool route_fast_supported(const RouterParams& p, uint32_t H) {
@@ -646,26 +657,21 @@ bool route_fast_supported(const RouterParams& p, uint32_t H) {
 void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
                        const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
-                       cudaStream_t s, bool exact_weights) {
+                       cudaStream_t s) {
     if (T == 0) return;
     const size_t smem = (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float));
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr[dev]) {
-        cudaFuncSetAttribute(route_fast_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        cudaFuncSetAttribute(route_fast_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaFuncSetAttribute(route_fast_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr[dev] = true;
     }
     cudaMemsetAsync(count, 0, sizeof(uint32_t), s);
     uint32_t grid = (T + kFastWarps - 1) / kFastWarps;
     if (grid > (uint32_t)kNumSMs * 4u) grid = (uint32_t)kNumSMs * 4u;
-    if (exact_weights)
-        route_fast_kernel<true><<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
-                                                                    recheck_total, status);
-    else
-        route_fast_kernel<false><<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list,
-                                                                     count, recheck_total, status);
+    route_fast_kernel<<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
+                                                          recheck_total, status);
     // the tokens on the list, completely in the canonical order (few: the grids stride over the list)
     const uint32_t E = p.experts;
     dim3 g2((E + 7) / 8, 32);

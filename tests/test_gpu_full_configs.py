@@ -74,10 +74,11 @@ def full_layer(ctx, cfg, T, sub, tight):
         assert after.router_fast_tokens - before.router_fast_tokens == T
         assert after.router_rechecked_tokens - before.router_rechecked_tokens <= T // 4
         assert np.array_equal(aux3["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
-        assert np.allclose(aux3["weights"].cpu().numpy(), ref["weights"], rtol=2e-5, atol=0)   # exact with STRATA_MOE_EXACT_ROUTER_WEIGHTS
+        assert np.array_equal(aux3["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
+        assert after.router_worst_error <= 0.25, after.router_worst_error
         assert np.array_equal(aux3["counts"].cpu().numpy().astype(np.uint32), ref["counts"])
         assert np.array_equal(aux3["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
-        assert ((out3 - out).norm() / out.norm()).item() <= 1e-5
+        assert torch.equal(out3, out)
         del out3, aux3
     rel, mx = Hh.error_metrics(out[torch.from_numpy(sub).cuda()].cpu().numpy(), ref["out"])
     counts = aux["counts"].cpu().numpy()

@@ -266,6 +266,16 @@ def test_ring_and_register_streaming_kernels_agree(ctx, fmt, monkeypatch):
     assert rel <= 1e-5, rel        # same products, different FP32 summation order
 
 
+def test_ring_kernels_with_sixteen_row_token_tiles(ctx, monkeypatch):
+    # by default the ring kernels only take batches whose groups fit an 8-row tile; their 16-row variant on request
+    monkeypatch.setenv("STRATA_MOE_STREAM_RING_MAX_ROWS", "16")
+    cfg = small(synth.FMT_MXFP4, H=1024, I=512, T=23, E=4, k=2, name="ring_mx_sixteen")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
+    assert rel <= REL_L2 and mx <= MAX_ABS, (rel, mx)
+
+
 def test_shared_expert_on_tensor_core_path(ctx):
     # 200 tokens: the BF16 shared expert runs as a one-group grouped GEMM, the routed NVFP4
     # experts (50 rows each on average) take the tensor-core path as well
@@ -302,16 +312,13 @@ def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     assert rel <= TENSOR_REL_L2 and mx <= MAX_ABS, (rel, mx)
 
 
-@pytest.mark.parametrize("exact_w", [False, True])
 @pytest.mark.parametrize("kind,zipf,dup", [(synth.SCORE_SIGMOID, 0.0, False), (synth.SCORE_SIGMOID_PLAIN, 1.1, False),
                                            (synth.SCORE_SQRTSOFTPLUS, 0.0, False), (synth.SCORE_SIGMOID, 0.0, True)])
-def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, exact_w, monkeypatch):
-    """Tensor-core projection + exact recheck against the canonical router: expert ids in rank order bit for bit;
-    routing weights bit for bit when the layer asks for exact weights, else within a few units in the last place.
+def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
+    """Tensor-core projection + exact recheck against the canonical router: expert ids in rank order and routing
+    weights bit for bit (the selected logits are recomputed in the canonical summation order).
     `dup` makes two experts identical, so that every token has an exact tie the fast path must not decide."""
     monkeypatch.setenv("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", "1")
-    if exact_w:
-        monkeypatch.setenv("STRATA_MOE_EXACT_ROUTER_WEIGHTS", "1")
     cfg = small(synth.FMT_MXFP4, T=700, E=128, k=8, H=512, I=256, score_kind=kind, zipf_s=zipf,
                 weight_scale=1.5, name=f"fast_router{kind}{int(dup)}")
     layer = synth.build_layer(cfg, "cuda")
@@ -327,10 +334,8 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, exact_w, monkeypatch):
     assert after.router_fast_tokens - before.router_fast_tokens == cfg.T
     rechecked = after.router_rechecked_tokens - before.router_rechecked_tokens
     assert torch.equal(ids_f, ids_x)
-    if exact_w:
-        assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
-    else:
-        assert torch.allclose(w_f, w_x, rtol=2e-5, atol=0)
+    assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
+    assert 0.0 < after.router_worst_error <= 0.5      # the bound the selection assumes, with room to spare
     if dup:
         # a token whose top-8 holds one of the twins has an exact tie and must have been rechecked
         touched = int(((ids_x == 3) | (ids_x == 77)).any(dim=1).sum().item())
