@@ -64,7 +64,6 @@ struct LayerKnobs {
     bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
     bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
     bool no_stream_ring = false;    // STRATA_MOE_NO_STREAM_RING: small batches use the register-streaming kernels
-    bool no_fp8_ring = false;       // STRATA_MOE_NO_FP8_RING: the MXFP4 ring kernels keep f16 MMAs
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
     int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
@@ -88,7 +87,6 @@ static LayerKnobs read_knobs() {
     k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
-    k.no_fp8_ring = getenv("STRATA_MOE_NO_FP8_RING") != nullptr;
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
     k.stream_ring_max_rows = num("STRATA_MOE_STREAM_RING_MAX_ROWS", 8);
     return k;
@@ -483,6 +481,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         a.x_rowscale = L->x_rowscale;
         a.act_f32 = L->act_f32;
         a.act_rowscale = L->act_rowscale;
+        a.x_rows = (uint32_t)L->max_pairs;
         // Mixed dispatch for uneven loads: groups with many rows (a hot expert under a skewed router) go
         // to the tensor-core path, the rest stay on the weight-streaming kernels.  An expert receives at
         // most one row per token, so nothing qualifies while max_rows is below the threshold.
@@ -507,26 +506,15 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         // the ring kernels win while a group fits one 8-row token tile (measured: 8 tokens of c0 99 us against 114 us;
         // 256 tokens of c1, 16-row tiles and several passes per group: 419 us against 339 us)
         const bool ring = L->stream_ok && a.max_rows_per_group <= (uint32_t)L->knobs.stream_ring_max_rows;
-        // MXFP4 through the ring: FP8 MMAs on E4M3 terms of the activations, unless some groups of this step go to the
-        // tensor-core path (which reads the f16 rows) or the switch is off
-        const bool fp8 = ring && !big && !down_all_tensor && !L->knobs.no_fp8_ring && decode_stream_fp8_supported(L->d.format);
-        a.fp8_terms = fp8 ? 1u : 0u;
-        if (fp8)
-            launch_rows_to_e4m3_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
-        else
-            launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         if (ring) {
             if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
-        if (fp8)
-            launch_rows_to_e4m3_f32(L->act_f32, bound, L->d.intermediate, L->act_hi, L->act_lo, L->act_rowscale, s,
-                                    pairs_dev);
-        else
-            launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
-                                   L->act_rowscale, s, pairs_dev);
+        launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
+                               L->act_rowscale, s, pairs_dev);
         if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
             p.min_rows = big;
             p.ntile = 128;   // measured at the c4 shape: 407 us with 128-token tiles, 439 us with 192

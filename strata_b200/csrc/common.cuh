@@ -99,8 +99,7 @@ struct DecodeArgs {
     const float* x_rowscale;       // [pairs] factor that undoes the pre-scale of x
     float* act_f32;                // [pairs, I] SwiGLU output before its f16 split
     const float* act_rowscale;     // [pairs]
-    // decode_stream.cu, MXFP4: x_hi / x_lo (act_hi / act_lo) hold E4M3 terms (rows_to_e4m3) and the MMAs are FP8
-    uint32_t fp8_terms;
+    uint32_t x_rows;               // decode_stream.cu: rows allocated in x_hi / act_hi / act_lo (bounds of the row boxes)
 };
 void launch_decode_fp4_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_fp4_down(const DecodeArgs& a, cudaStream_t s);
@@ -117,11 +116,6 @@ void launch_dequant_export_f16(int fmt, const uint8_t* packed, const uint8_t* sc
 bool decode_stream_supported(int fmt, uint32_t H, uint32_t I);
 // maps: device array [3 roles][n_groups][3] of 128-byte tensor maps made by decode_stream_encode_maps
 int decode_stream_encode_maps(void* out3x128, int fmt, const void* packed, const void* scales, uint32_t rows, uint32_t K);
-bool decode_stream_fp8_supported(int fmt);
-void launch_rows_to_e4m3_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t C,
-                              void* hi, float* rowscale, cudaStream_t s, const uint32_t* rows_dev = nullptr);
-void launch_rows_to_e4m3_f32(const float* x, uint32_t rows, uint32_t C, void* hi, void* lo, float* rowscale,
-                             cudaStream_t s, const uint32_t* rows_dev = nullptr);
 int launch_decode_stream_gate_up(const DecodeArgs& a, const void* maps, cudaStream_t s);
 int launch_decode_stream_down(const DecodeArgs& a, const void* maps, cudaStream_t s);
 void launch_decode_gate_up(const DecodeArgs& a, cudaStream_t s);

@@ -35,8 +35,6 @@
 // Replaces the reference's per-row NVFP4 / DeepSeek FP4 expert kernels for decode batches
 // (kernels/cuda/backend.cu:1978-2069, 2308-2413).
 #include <cuda.h>
-#include <cuda_fp16.h>
-#include <cuda_fp8.h>
 
 #include "stream_ring.cuh"
 
@@ -52,7 +50,7 @@ constexpr uint32_t kStageSteps = 4;               // k-steps of 128 columns per 
 constexpr uint32_t kJobUnits = 4;                 // units of 16 (+16) rows per full job
 constexpr uint32_t kBoxRows = 16 * kJobUnits;     // 64
 constexpr uint32_t kBoxBytes = kBoxRows * 128;    // one weight box: 64 rows x 128 bytes
-constexpr uint32_t kXP = kStageSteps * 256 + 64;  // bytes between activation rows (1088)
+constexpr uint32_t kXSlabs = kStageSteps * 2;     // 128-byte slabs of one activation row per stage (64 f16 columns each)
 constexpr int kMxBiasS = 2;                       // f16 exponent field of an MXFP4 multiplier is e - emin + 2
 
 template <int FMT>
@@ -67,8 +65,9 @@ struct StreamGeo {
     // weights: [tile p][k half][64 rows][128 B], each box 1024-byte aligned (swizzle atom)
     static constexpr uint32_t kWOff = 0;
     static constexpr uint32_t kSOff = 4u * kBoxBytes;                               // scales: [tile p][64 rows][pitch]
-    static constexpr uint32_t kXOff = kSOff + 2u * kBoxRows * ScaleGeo<FMT>::kPitch;
-    static constexpr uint32_t kStageBytes = (kXOff + kXRows * kXP + 1023u) / 1024u * 1024u;
+    static constexpr uint32_t kXOff = (kSOff + 2u * kBoxRows * ScaleGeo<FMT>::kPitch + 1023u) / 1024u * 1024u;   // swizzle atom
+    static constexpr uint32_t kXBoxBytes = 8u * NT * kXSlabs * 128u;                // one activation box: [slab][8 NT rows][128 B]
+    static constexpr uint32_t kStageBytes = (kXOff + (SPLIT ? 2u : 1u) * kXBoxBytes + 1023u) / 1024u * 1024u;
     static constexpr uint32_t kRedBytes = kCWarps * 32u * 8u * NT * 4u;
     static constexpr uint32_t kBudget = 225u * 1024u;
     static constexpr uint32_t kStagesRaw = (kBudget - kRedBytes - 1024u) / kStageBytes;
@@ -87,6 +86,13 @@ __device__ __forceinline__ void tma_box(void* dst, const CUtensorMap* map, uint3
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_addr(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_box3(void* dst, const CUtensorMap* map, uint32_t x, uint32_t y, uint32_t z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(smem_addr(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(smem_addr(bar))
         : "memory");
 }
 
@@ -133,14 +139,10 @@ struct JobInfo {
 // DUAL = true : gate/up + SwiGLU, writes act fp32 [pairs, I].   K = H, a unit is 16 gate + 16 up rows.
 // DUAL = false: down, writes y fp32 [pairs, H].                 K = I, a unit is 2 x 16 rows.
 // maps: [3 roles][n_groups][3] tensor maps (64-row weight boxes, 16-row weight boxes, scale boxes).
-// F8 (MXFP4 only): the weights enter m16n8k32 E4M3 MMAs (an E2M1 code is an E4M3 code after two shifts and two masks:
-// the hardware E2M1 -> f16 conversion runs on the conversion unit at a quarter of the rate these kernels need, and that
-// unit, not memory, bounded the f16 variant).  The activations arrive as E4M3 TERMS of their row-scaled value, sixteen
-// bytes per eight columns: term 1 of columns 0 2 4 6, of 1 3 5 7, term 2 likewise (rows_to_e4m3_kernel); x_hi holds
-// terms 1 + 2, and for the down projection x_lo holds terms 3 + 4 scaled by 2^8.  Every term costs one MMA on the same
-// weight registers.  A BF16 activation is reproduced exactly by two terms unless it is below 2^-9 of its row maximum.
-template <int FMT, int NT, bool SPLIT, bool DUAL, bool F8>
-__global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs a, const CUtensorMap* __restrict__ maps) {
+template <int FMT, int NT, bool SPLIT, bool DUAL>
+__global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs a, const CUtensorMap* __restrict__ maps,
+                                                                     const __grid_constant__ CUtensorMap xmap_hi,
+                                                                     const __grid_constant__ CUtensorMap xmap_lo) {
     using G = StreamGeo<FMT, NT, SPLIT>;
     constexpr uint32_t S = G::kStages;
     extern __shared__ uint8_t smem_raw_s[];
@@ -198,9 +200,6 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
         return false;
     };
 
-    const __half* xh_base = reinterpret_cast<const __half*>(DUAL ? a.x_hi : a.act_hi);
-    const __half* xl_base = reinterpret_cast<const __half*>(DUAL ? a.x_lo : a.act_lo);
-
     if (warp == kCWarps) {
         // ------------------------------------------------------------------ producer
         uint32_t it = 0, u = u_begin;
@@ -212,7 +211,6 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
             const CUtensorMap* m1 = maps + ((size_t)(DUAL ? 1u : 2u) * a.n_groups + j.g) * 3u;
             const uint32_t rowp0 = DUAL ? j.us * 16u : j.us * 32u;
             const uint32_t rowp1 = DUAL ? j.us * 16u : j.us * 32u + j.nu * 16u;
-            const uint32_t nvalid = min(8u * NT, j.cnt - j.tb);
             const bool full_job = j.nu == kJobUnits;
             for (uint32_t c = 0; c < chunks; ++c, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -222,39 +220,42 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                 if (!got) { ok = false; break; }
                 const uint32_t nks = min(kStageSteps, steps - c * kStageSteps);
                 const uint32_t khalves = (nks + 1u) / 2u;                // 128-byte K slices in this stage (1 or 2)
-                const uint32_t xbytes = nks * 256u;
                 uint8_t* st = stages + (size_t)s * G::kStageBytes;
+                // Few, large requests: one elected lane issues a request in some tens of nanoseconds, and a stage of a
+                // dozen requests (one per box, row and scale slice) was bounded by that, not by memory.  A full job is
+                // two weight boxes of 16 KB (3-D: 128 bytes x 64 rows x 2 K slices; a slice past the end of K arrives
+                // as zeros and still counts), two scale boxes and one box of activation rows per operand half.
                 if (lane == 0) {
-                    const uint32_t wtx = 2u * khalves * (full_job ? kBoxBytes : j.nu * 16u * 128u);
+                    const uint32_t wtx = full_job ? 2u * 2u * kBoxBytes : 2u * khalves * j.nu * 16u * 128u;
                     const uint32_t stx = 2u * kBoxRows * ScaleGeo<FMT>::kPitch;
-                    mbar_arrive_expect_tx(&C.full[s], wtx + stx + nvalid * (SPLIT ? 2u : 1u) * xbytes);
+                    mbar_arrive_expect_tx(&C.full[s], wtx + stx + (SPLIT ? 2u : 1u) * G::kXBoxBytes);
                 }
                 __syncwarp();
-                if (lane < 4u) {
-                    // weights: lane = tile p * 2 + k half
-                    const uint32_t p = lane >> 1, kh = lane & 1u;
-                    if (kh < khalves) {
-                        const CUtensorMap* m = p ? m1 : m0;
-                        uint8_t* dst = st + G::kWOff + (p * 2u + kh) * kBoxBytes;
-                        const uint32_t xb = c * (kStageSteps * 64u) + kh * 128u, y0 = p ? rowp1 : rowp0;
-                        if (full_job) {
-                            tma_box(dst, m + 0, xb, y0, &C.full[s]);
-                        } else {
-                            for (uint32_t q = 0; q < j.nu; ++q) tma_box(dst + q * 2048u, m + 1, xb, y0 + q * 16u, &C.full[s]);
-                        }
+                if (lane < 2u) {
+                    // weights of tile p
+                    const uint32_t p = lane;
+                    const CUtensorMap* m = p ? m1 : m0;
+                    uint8_t* dst = st + G::kWOff + p * 2u * kBoxBytes;
+                    const uint32_t y0 = p ? rowp1 : rowp0;
+                    if (full_job) {
+                        tma_box3(dst, m + 0, 0u, y0, c * 2u, &C.full[s]);
+                    } else {
+                        for (uint32_t kh = 0; kh < khalves; ++kh)
+                            for (uint32_t q = 0; q < j.nu; ++q)
+                                tma_box(dst + kh * kBoxBytes + q * 2048u, m + 1, c * (kStageSteps * 64u) + kh * 128u,
+                                        y0 + q * 16u, &C.full[s]);
                     }
-                } else if (lane < 6u) {
+                } else if (lane < 4u) {
                     // block scales of the 64 rows from the tile's first row on (rows past the job are not read)
-                    const uint32_t p = lane - 4u;
+                    const uint32_t p = lane - 2u;
                     tma_box(st + G::kSOff + p * kBoxRows * ScaleGeo<FMT>::kPitch, (p ? m1 : m0) + 2,
                             c * ScaleGeo<FMT>::kPitch, p ? rowp1 : rowp0, &C.full[s]);
-                }
-                for (uint32_t i = lane; i < nvalid * (SPLIT ? 2u : 1u); i += 32u) {
-                    const uint32_t tok = i < nvalid ? i : i - nvalid;
-                    const __half* src = (i < nvalid ? xh_base : xl_base) + (size_t)(j.row0 + j.tb + tok) * K +
-                                        (size_t)c * (kStageSteps * 128u);
-                    const uint32_t slot = i < nvalid ? tok : 8u * NT + tok;
-                    bulk_g2s(st + G::kXOff + slot * kXP, src, xbytes, &C.full[s]);
+                } else if (lane < (SPLIT ? 6u : 5u)) {
+                    // 8 NT activation rows from the job's first token row on, 512 columns: rows past the group belong
+                    // to the next group (their results are dropped), rows or columns past the buffer arrive as zeros
+                    const bool lo = lane == 5u;
+                    tma_box3(st + G::kXOff + (lo ? G::kXBoxBytes : 0u), lo ? &xmap_lo : &xmap_hi, 0u, j.row0 + j.tb,
+                             c * kXSlabs, &C.full[s]);
                 }
             }
         }
@@ -307,50 +308,14 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                 const uint32_t box1 = box0 + 2u * kBoxBytes;                      // tile 1
                 const uint32_t sc0 = st + G::kSOff + row_lo * ScaleGeo<FMT>::kPitch + ks * ScaleGeo<FMT>::kStepBytes;
                 const uint32_t sc1 = sc0 + kBoxRows * ScaleGeo<FMT>::kPitch;
-                const uint32_t xrow = st + G::kXOff + gid * kXP + ks * 256u + t * 16u;
-                if (F8) {
-                    // as the MXFP4 branch below, with FP8 MMAs: 32 columns (one E8M0 block) per MMA and term
-                    const uint32_t s0l = lds32(sc0), s0h = lds32(sc0 + 8u * ScaleGeo<FMT>::kPitch);
-                    const uint32_t s1l = lds32(sc1), s1h = lds32(sc1 + 8u * ScaleGeo<FMT>::kPitch);
+                // activation box: [slab][8 NT rows][128 B], 16-byte chunk c of row r at chunk position c ^ (r & 7); this
+                // lane's word wd of the k-step lies in slab 2 ks + (wd >> 1), chunk 4 (wd & 1) + t, of row gid (+ 8 nt)
+                uint32_t xoff[4];
 #pragma unroll
-                    for (int wd = 0; wd < 4; ++wd) {
-                        uint4 bh[NT], bl[SPLIT ? NT : 1];
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
-                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
-                        }
-#pragma unroll
-                        for (int p = 0; p < 2; ++p) {
-                            const uint32_t box = p ? box1 : box0;
-                            uint32_t a0, a1, a2, a3;
-                            e2m1x8_e4m3(lds32(box + woff[wd]), a0, a2);
-                            e2m1x8_e4m3(lds32(box + woff[wd] + 8u * 128u), a1, a3);
-                            const float fl = __uint_as_float((((p ? s1l : s0l) >> (8 * wd)) & 0xFFu) << 23);
-                            const float fh = __uint_as_float((((p ? s1h : s0h) >> (8 * wd)) & 0xFFu) << 23);
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                float* cacc = p ? acc1[nt] : acc0[nt];
-                                float tmp[4];
-                                mma_e4m3_zero(tmp, a0, a1, a2, a3, bh[nt].x, bh[nt].y);
-                                mma_e4m3(tmp, a0, a1, a2, a3, bh[nt].z, bh[nt].w);
-                                cacc[0] = fmaf(tmp[0], fl, cacc[0]);
-                                cacc[1] = fmaf(tmp[1], fl, cacc[1]);
-                                cacc[2] = fmaf(tmp[2], fh, cacc[2]);
-                                cacc[3] = fmaf(tmp[3], fh, cacc[3]);
-                                if (SPLIT) {
-                                    const float fl2 = fl * 0.00390625f, fh2 = fh * 0.00390625f;   // terms 3, 4 carry 2^8
-                                    mma_e4m3_zero(tmp, a0, a1, a2, a3, bl[nt].x, bl[nt].y);
-                                    mma_e4m3(tmp, a0, a1, a2, a3, bl[nt].z, bl[nt].w);
-                                    cacc[0] = fmaf(tmp[0], fl2, cacc[0]);
-                                    cacc[1] = fmaf(tmp[1], fl2, cacc[1]);
-                                    cacc[2] = fmaf(tmp[2], fh2, cacc[2]);
-                                    cacc[3] = fmaf(tmp[3], fh2, cacc[3]);
-                                }
-                            }
-                        }
-                    }
-                } else if (FMT == STRATA_MOE_FMT_MXFP4) {
+                for (int wd = 0; wd < 4; ++wd)
+                    xoff[wd] = st + G::kXOff + ((ks * 2u + ((uint32_t)wd >> 1)) * (8u * NT) + gid) * 128u +
+                               ((((uint32_t)(wd & 1) * 4u + t) ^ gid) << 4);
+                if (FMT == STRATA_MOE_FMT_MXFP4) {
                     // E8M0 block scales are powers of two and one 32-column block is exactly the two MMAs of
                     // a (word index, tile): the raw E2M1 values go into the MMAs and the FP32 partial sum of
                     // the block is scaled (exactly) on its way into the accumulator -- four multiply-adds in
@@ -362,8 +327,8 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                         uint4 bh[NT], bl[SPLIT ? NT : 1];
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
-                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
-                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
+                            bh[nt] = lds128(xoff[wd] + (uint32_t)nt * 1024u);
+                            if (SPLIT) bl[nt] = lds128(xoff[wd] + G::kXBoxBytes + (uint32_t)nt * 1024u);
                         }
 #pragma unroll
                         for (int p = 0; p < 2; ++p) {
@@ -401,8 +366,8 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                         uint4 bh[NT], bl[SPLIT ? NT : 1];
 #pragma unroll
                         for (int nt = 0; nt < NT; ++nt) {
-                            bh[nt] = lds128(xrow + (uint32_t)nt * 8u * kXP + (uint32_t)wd * 64u);
-                            if (SPLIT) bl[nt] = lds128(xrow + (uint32_t)(NT + nt) * 8u * kXP + (uint32_t)wd * 64u);
+                            bh[nt] = lds128(xoff[wd] + (uint32_t)nt * 1024u);
+                            if (SPLIT) bl[nt] = lds128(xoff[wd] + G::kXBoxBytes + (uint32_t)nt * 1024u);
                         }
 #pragma unroll
                         for (int p = 0; p < 2; ++p) {
@@ -454,7 +419,6 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
         // sums are added in k-step order
         if (my_unit) {
             float s0 = 1.0f, s1 = 1.0f;     // MXFP4: the block scales went into the accumulators whole
-            if (F8) s0 = s1 = 64.0f;        // an E2M1 code read as E4M3 is 2^-6 of its value
             if (FMT != STRATA_MOE_FMT_MXFP4) {
                 if (DUAL) { s0 = a.gate.post_scale[j.g]; s1 = a.up.post_scale[j.g]; }
                 else { s0 = s1 = a.down.post_scale[j.g]; }
@@ -526,14 +490,29 @@ bool encode_u8_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_
               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int FMT, int NT, bool SPLIT, bool DUAL, bool F8>
+// [rows, row_bytes] bytes seen as {128 B, rows, row_bytes / 128 slabs}: one box = box_rows rows x box_slabs slabs,
+// laid out [slab][row][128 B] with the 128-byte swizzle (what the consumers' addressing expects)
+bool encode_slab_map(CUtensorMap* m, const void* base, uint64_t row_bytes, uint64_t rows, uint32_t box_rows,
+                     uint32_t box_slabs) {
+    EncodeTiledFnS fn = encode_fn_s();
+    if (!fn || row_bytes % 128u) return false;
+    const cuuint64_t dims[3] = {128, rows, row_bytes / 128u};
+    const cuuint64_t strides[2] = {row_bytes, 128};
+    const cuuint32_t box[3] = {128, box_rows, box_slabs};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int FMT, int NT, bool SPLIT, bool DUAL>
 int launch_stream_one(const DecodeArgs& a, const void* maps, cudaStream_t s) {
     using G = StreamGeo<FMT, NT, SPLIT>;
     static bool attr[64] = {};   // the shared-memory opt-in is per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
     if (!attr[dev]) {
-        if (cudaFuncSetAttribute(decode_stream_kernel<FMT, NT, SPLIT, DUAL, F8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(decode_stream_kernel<FMT, NT, SPLIT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)G::kSmem) != cudaSuccess)
             return -1;
         attr[dev] = true;
@@ -542,15 +521,27 @@ int launch_stream_one(const DecodeArgs& a, const void* maps, cudaStream_t s) {
     const uint32_t jobs = a.n_groups * ((DUAL ? R / 16u : R / 32u) + kJobUnits - 1u) / kJobUnits;
     if (jobs == 0u) return 0;
     const uint32_t grid = jobs < (uint32_t)kNumSMs ? jobs : (uint32_t)kNumSMs;
-    decode_stream_kernel<FMT, NT, SPLIT, DUAL, F8><<<grid, kSThreads, G::kSmem, s>>>(a, static_cast<const CUtensorMap*>(maps));
+    // the activation rows of this launch: f16 [x_rows, K], hi (and lo) halves
+    const uint32_t K = DUAL ? a.H : a.I;
+    const void* xh = DUAL ? static_cast<const void*>(a.x_hi) : static_cast<const void*>(a.act_hi);
+    const void* xl = DUAL ? static_cast<const void*>(a.x_lo) : static_cast<const void*>(a.act_lo);
+    CUtensorMap xmap_hi, xmap_lo;
+    if (a.x_rows == 0u || !encode_slab_map(&xmap_hi, xh, (uint64_t)K * 2u, a.x_rows, 8u * NT, kXSlabs)) return -1;
+    if (SPLIT) {
+        if (!encode_slab_map(&xmap_lo, xl, (uint64_t)K * 2u, a.x_rows, 8u * NT, kXSlabs)) return -1;
+    } else {
+        xmap_lo = xmap_hi;
+    }
+    decode_stream_kernel<FMT, NT, SPLIT, DUAL><<<grid, kSThreads, G::kSmem, s>>>(a, static_cast<const CUtensorMap*>(maps),
+                                                                                 xmap_hi, xmap_lo);
     ++g_kernel_launches;
     return 0;
 }
 
-template <int FMT, bool SPLIT, bool DUAL, bool F8 = false>
+template <int FMT, bool SPLIT, bool DUAL>
 int launch_stream_nt(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    return a.max_rows_per_group <= 8u ? launch_stream_one<FMT, 1, SPLIT, DUAL, F8>(a, maps, s)
-                                      : launch_stream_one<FMT, 2, SPLIT, DUAL, F8>(a, maps, s);
+    return a.max_rows_per_group <= 8u ? launch_stream_one<FMT, 1, SPLIT, DUAL>(a, maps, s)
+                                      : launch_stream_one<FMT, 2, SPLIT, DUAL>(a, maps, s);
 }
 
 }  // namespace
@@ -565,138 +556,27 @@ bool decode_stream_supported(int fmt, uint32_t H, uint32_t I) {
 }
 
 // The three tensor maps of one projection ([rows, K] weights of format fmt) into out (3 x 128 bytes, host memory):
-// 64-row and 16-row boxes of 128 packed bytes (128-byte swizzle), and 64-row boxes of one stage's scale bytes.
+// 64-row x two-slice boxes (3-D, one request per tile and stage) and 16-row boxes of 128 packed bytes (both with the
+// 128-byte swizzle), and 64-row boxes of one stage's scale bytes.
 int decode_stream_encode_maps(void* out, int fmt, const void* packed, const void* scales, uint32_t rows, uint32_t K) {
     static_assert(sizeof(CUtensorMap) == 128, "descriptor size");
     CUtensorMap* m = static_cast<CUtensorMap*>(out);
     const uint32_t spitch = fmt == STRATA_MOE_FMT_MXFP4 ? ScaleGeo<STRATA_MOE_FMT_MXFP4>::kPitch
                                                         : ScaleGeo<STRATA_MOE_FMT_NVFP4>::kPitch;
     const uint64_t srow = fmt == STRATA_MOE_FMT_MXFP4 ? K / 32u : K / 16u;
-    if (!encode_u8_map(m + 0, packed, K / 2u, rows, 128, kBoxRows, true)) return -1;
+    if (!encode_slab_map(m + 0, packed, K / 2u, rows, kBoxRows, 2)) return -1;
     if (!encode_u8_map(m + 1, packed, K / 2u, rows, 128, 16, true)) return -1;
     if (!encode_u8_map(m + 2, scales, srow, rows, spitch, kBoxRows, false)) return -1;
     return 0;
 }
 
-// ---------------------------------------------------------------------------------------
-// Rows -> E4M3 terms for the FP8 variant (one warp per destination row).  The row is scaled by a power of two that
-// puts its maximum into [128, 256) (E4M3 holds up to 448); term 1 = the scaled value rounded to E4M3, term 2 = the
-// remainder rounded, and for an fp32 source terms 3 and 4 continue on the remainder times 2^8.  Layout per eight
-// columns, sixteen bytes: term 1 of columns 0 2 4 6, of 1 3 5 7, then term 2 likewise (hi); terms 3 and 4 the same
-// way (lo).  A value that is not finite becomes the E4M3 NaN so that it still poisons its row's results.
-namespace {
-
-__device__ __forceinline__ uint32_t q_e4m3(float v) {
-    if (!(fabsf(v) <= 3.0e38f)) return 0x7Fu;
-    return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-}
-__device__ __forceinline__ float dq_e4m3(uint32_t b) {
-    return __half2float(__half(__nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3)));
-}
-__device__ __forceinline__ uint32_t pack_even_odd(const uint32_t b[8], uint32_t& odd) {
-    odd = b[1] | (b[3] << 8) | (b[5] << 16) | (b[7] << 24);
-    return b[0] | (b[2] << 8) | (b[4] << 16) | (b[6] << 24);
-}
-
-template <bool SRC_F32>
-__global__ void __launch_bounds__(256) rows_to_e4m3_kernel(const void* __restrict__ src, const uint32_t* __restrict__ perm,
-                                                           uint32_t k_div, uint32_t rows, uint32_t C,
-                                                           uint4* __restrict__ hi, uint4* __restrict__ lo,
-                                                           float* __restrict__ rowscale,
-                                                           const uint32_t* __restrict__ rows_dev) {
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t pos = blockIdx.x * 8u + (threadIdx.x >> 5);
-    if (pos >= rows) return;
-    if (rows_dev && pos >= *rows_dev) return;   // `rows` is only an upper bound; the count lives on the device
-    const uint32_t srow = perm ? perm[pos] / k_div : pos;
-    auto load8 = [&](uint32_t i, float v[8]) {
-        if (SRC_F32) {
-            const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)srow * C) + 2u * i;
-            const float4 x0 = __ldg(p), x1 = __ldg(p + 1);
-            v[0] = x0.x; v[1] = x0.y; v[2] = x0.z; v[3] = x0.w; v[4] = x1.x; v[5] = x1.y; v[6] = x1.z; v[7] = x1.w;
-        } else {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C) + i);
-            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                v[2 * q] = __uint_as_float(w[q] << 16);
-                v[2 * q + 1] = __uint_as_float(w[q] & 0xFFFF0000u);
-            }
-        }
-    };
-    float mx = 0.0f;
-    for (uint32_t i = lane; i < C / 8u; i += 32u) {
-        float v[8];
-        load8(i, v);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) mx = fmaxf(mx, fabsf(v[q]));     // fmaxf drops a NaN; the NaN itself is kept below
-    }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
-    int ex = 0;
-    if (mx > 0.0f && mx < 3.0e38f) ex = 7 - (int)((__float_as_uint(mx) >> 23) & 0xFFu) + 127;
-    ex = max(-100, min(100, ex));
-    const float sc = __uint_as_float((uint32_t)(ex + 127) << 23);
-    if (lane == 0) rowscale[pos] = __uint_as_float((uint32_t)(127 - ex) << 23);
-    for (uint32_t i = lane; i < C / 8u; i += 32u) {
-        float v[8];
-        load8(i, v);
-        uint32_t t1[8], t2[8], t3[8], t4[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const float f = v[q] * sc;
-            t1[q] = q_e4m3(f);
-            const float r1 = f - dq_e4m3(t1[q]);
-            t2[q] = q_e4m3(r1);
-            if (SRC_F32) {
-                const float r2 = (r1 - dq_e4m3(t2[q])) * 256.0f;
-                t3[q] = q_e4m3(r2);
-                t4[q] = q_e4m3(r2 - dq_e4m3(t3[q]));
-            }
-        }
-        uint4 o;
-        o.x = pack_even_odd(t1, o.y);
-        o.z = pack_even_odd(t2, o.w);
-        hi[(size_t)pos * (C / 8u) + i] = o;
-        if (SRC_F32) {
-            o.x = pack_even_odd(t3, o.y);
-            o.z = pack_even_odd(t4, o.w);
-            lo[(size_t)pos * (C / 8u) + i] = o;
-        }
-    }
-}
-
-}  // namespace
-
-void launch_rows_to_e4m3_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t C,
-                              void* hi, float* rowscale, cudaStream_t s, const uint32_t* rows_dev) {
-    if (rows == 0) return;
-    rows_to_e4m3_kernel<false><<<(rows + 7) / 8, 256, 0, s>>>(x, perm, k_div, rows, C, static_cast<uint4*>(hi), nullptr,
-                                                             rowscale, rows_dev);
-    ++g_kernel_launches;
-}
-
-void launch_rows_to_e4m3_f32(const float* x, uint32_t rows, uint32_t C, void* hi, void* lo, float* rowscale,
-                             cudaStream_t s, const uint32_t* rows_dev) {
-    if (rows == 0) return;
-    rows_to_e4m3_kernel<true><<<(rows + 7) / 8, 256, 0, s>>>(x, nullptr, 1, rows, C, static_cast<uint4*>(hi),
-                                                            static_cast<uint4*>(lo), rowscale, rows_dev);
-    ++g_kernel_launches;
-}
-
-bool decode_stream_fp8_supported(int fmt) { return fmt == STRATA_MOE_FMT_MXFP4; }
-
 int launch_decode_stream_gate_up(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    if (a.fmt == STRATA_MOE_FMT_MXFP4)
-        return a.fp8_terms ? launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true, true>(a, maps, s)
-                           : launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true>(a, maps, s);
+    if (a.fmt == STRATA_MOE_FMT_MXFP4) return launch_stream_nt<STRATA_MOE_FMT_MXFP4, false, true>(a, maps, s);
     return launch_stream_nt<STRATA_MOE_FMT_NVFP4, false, true>(a, maps, s);
 }
 
 int launch_decode_stream_down(const DecodeArgs& a, const void* maps, cudaStream_t s) {
-    if (a.fmt == STRATA_MOE_FMT_MXFP4)
-        return a.fp8_terms ? launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false, true>(a, maps, s)
-                           : launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false>(a, maps, s);
+    if (a.fmt == STRATA_MOE_FMT_MXFP4) return launch_stream_nt<STRATA_MOE_FMT_MXFP4, true, false>(a, maps, s);
     return launch_stream_nt<STRATA_MOE_FMT_NVFP4, true, false>(a, maps, s);
 }
 

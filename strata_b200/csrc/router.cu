@@ -444,19 +444,23 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
 // cores first (launch_router_tc: same products, another summation order, so its logits differ from
 // the canonical ones in the last bits), and this kernel turns those APPROXIMATE logits into the
 // EXACT routing decision:
-//   1. scores and selection values from the approximate logits, and for every expert a bound eps
-//      on how far its selection value can be from the canonical one: |dlogit| <= delta (see below),
-//      times the local slope of the score function, plus rounding slack;
-//   2. top-k by (value desc, index asc) as usual.  The order of two experts is CERTAIN when their
-//      values differ by more than the sum of their bounds; the token is "safe" when every
-//      consecutive pair of the k selected is certain and the k-th is certain against the largest
-//      value + bound among all the others;
-//   3. the logits of the k selected experts are recomputed in the canonical lane-strided order
-//      (k * H multiply-adds per token, router rows from L2), so the routing weights are bit-exact;
-//      the same values check delta: if any selected logit is further than delta / 2 from its
-//      approximate value the token is not trusted.  The largest distance seen, as a fraction of
+//   1. selection values from the approximate logits, and for every expert a bound eps on how far its
+//      value can be from the canonical one: |dlogit| <= delta (see below) times the local slope of the
+//      score function, plus rounding slack;
+//   2. the k largest approximate values; L = the smallest of their lower bounds (value - eps).  At least
+//      k experts truly reach L, so an expert whose upper bound (value + eps) is below L cannot be selected;
+//   3. CANDIDATES = those k plus every expert whose upper bound reaches L (usually none, sometimes one
+//      or two);
+//   4. the logits of the candidates are recomputed in the canonical lane-strided order (a few * H
+//      multiply-adds per token, router rows from L2);
+//   5. their exact scores and selection values follow, and the canonical rule -- (value desc, index
+//      asc) -- picks and orders the k among them; routing weights come from the same exact scores.
+//      Ids, rank order and weights are therefore bit-identical to the canonical router's, exact ties
+//      included.  The same canonical logits check delta: a candidate further than delta / 2 from its
+//      approximate logit sends the token to the list.  The largest distance seen, as a fraction of
 //      delta, is kept in recheck_total[1] (float bits) for the statistics;
-//   4. tokens that are not safe go on a list; the canonical kernels recompute them completely.
+//   6. a token with non-finite logits, more than 32 candidates or a failed check goes on a list; the
+//      canonical kernels recompute those completely.
 // delta = 2^-13 * max(2, max_e |logit|): both summation orders round at most a few hundred partial
 // sums of magnitude <= that maximum (relative 2^-24 each; the tensor cores may truncate, 2^-23), so
 // the true distance is orders of magnitude below delta; step 3 verifies that on the selected logits of every
@@ -498,6 +502,8 @@ __device__ __forceinline__ void chain_fma8(float (&c)[8], const uint4& xv, const
     }
 }
 
+constexpr uint32_t kMaxCand = 32;     // candidates per token: one lane each
+
 __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias,
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H,
@@ -506,11 +512,16 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     extern __shared__ __align__(16) float fsm[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
-    const size_t per_warp = 3u * (size_t)E + H / 2u;     // floats: score, choice, eps, then the token's x row (bf16)
-    float* score = fsm + warp * per_warp;
-    float* choice = score + E;
+    // per warp: choice, eps [E]; candidate ids, their canonical logits, selected ids and scores [32 each]; the token's
+    // x row (bf16)
+    const size_t per_warp = 2u * (size_t)E + 4u * kMaxCand + H / 2u;
+    float* choice = fsm + warp * per_warp;
     float* eps = choice + E;
-    unsigned short* xs = reinterpret_cast<unsigned short*>(eps + E);
+    uint32_t* cand = reinterpret_cast<uint32_t*>(eps + E);
+    float* canon = reinterpret_cast<float*>(cand + kMaxCand);
+    uint32_t* sel_id = reinterpret_cast<uint32_t*>(canon + kMaxCand);
+    float* sel_sc = reinterpret_cast<float*>(sel_id + kMaxCand);
+    unsigned short* xs = reinterpret_cast<unsigned short*>(sel_sc + kMaxCand);
     float worst = 0.0f;        // largest |canonical - approximate| / delta this warp has seen
     for (uint32_t tok = blockIdx.x * kFastWarps + warp; tok < T; tok += gridDim.x * kFastWarps) {
         const float* lg = logits + (size_t)tok * E;
@@ -533,13 +544,12 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             const float sc = score_and_slope(p, lg[e], slope);
             const float b = bias ? bias[e] : 0.0f;
             bad |= !isfinite(b);
-            score[e] = sc;
             choice[e] = __fadd_rn(sc, b);
             eps[e] = 1.25f * slope * delta + 4.8e-7f * (fabsf(sc) + fabsf(b)) + 1e-30f;
         }
         __syncwarp();
-        float my_c = 0.0f, my_e = 0.0f;
-        uint32_t my_id = 0;
+        // step 2: the k largest approximate values; lane r keeps the lower bound of the r-th
+        float my_low = INFINITY;
         for (uint32_t r = 0; r < k; ++r) {
             float bv = -INFINITY;
             uint32_t bi = 0xFFFFFFFFu;
@@ -554,31 +564,35 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
             if (bi >= E) { bad = true; bi = 0; }
-            if (lane == r) { my_id = bi; my_c = bv; my_e = eps[bi]; }
+            if (lane == r) { cand[r] = bi; my_low = bv - eps[bi]; }
             if (lane == 0) choice[bi] = -INFINITY;
             __syncwarp();
         }
-        // the largest value any expert outside the selection could really have
-        float rest = -INFINITY;
-        for (uint32_t e = lane; e < E; e += 32u) rest = fmaxf(rest, choice[e] + eps[e]);
 #pragma unroll
-        for (int off = 16; off > 0; off >>= 1) rest = fmaxf(rest, __shfl_xor_sync(0xFFFFFFFFu, rest, off));
-        const float next_c = __shfl_down_sync(0xFFFFFFFFu, my_c, 1);
-        const float next_e = __shfl_down_sync(0xFFFFFFFFu, my_e, 1);
-        bool certain = true;
-        if (lane + 1u < k) certain = (my_c - my_e) > (next_c + next_e);
-        else if (lane + 1u == k) certain = (my_c - my_e) > rest;
-        bool safe = __all_sync(0xFFFFFFFFu, certain) && !__any_sync(0xFFFFFFFFu, bad);
-        // Canonical-order logits of the selected experts, eight experts per pass.  The canonical dot product gives
-        // lane v the columns v, v + 32, ... (one multiply-add chain per lane, increasing column order) and folds the 32
-        // chains by five shuffle-down rounds.  Here four lanes serve one expert and each owns EIGHT of those chains
-        // (columns 8*sub .. 8*sub+7 of every 32): one 16-byte load feeds eight chains, the chains keep their
-        // order, and the fold below pairs the same chains in the same rounds, so the sum is bit-identical.
-        float my_logit = 0.0f;
+        for (int off = 16; off > 0; off >>= 1) my_low = fminf(my_low, __shfl_xor_sync(0xFFFFFFFFu, my_low, off));
+        // step 3: every other expert whose value could reach the weakest of those lower bounds joins the candidates
+        uint32_t n = k;
+        for (uint32_t base = 0; base < E; base += 32u) {
+            const uint32_t e = base + lane;
+            const bool in = e < E && (choice[e] + eps[e] >= my_low);      // the k found above hold -inf
+            const uint32_t m = __ballot_sync(0xFFFFFFFFu, in);
+            if (in) {
+                const uint32_t pos = n + __popc(m & ((1u << lane) - 1u));
+                if (pos < kMaxCand) cand[pos] = e;
+            }
+            n += __popc(m);
+        }
+        bool safe = !__any_sync(0xFFFFFFFFu, bad) && n <= kMaxCand;
+        __syncwarp();
+        // step 4: canonical-order logits of the candidates, eight per pass.  The canonical dot product gives lane v the
+        // columns v, v + 32, ... (one multiply-add chain per lane, increasing column order) and folds the 32 chains by
+        // five shuffle-down rounds.  Here four lanes serve one expert and each owns EIGHT of those chains (columns
+        // 8*sub .. 8*sub+7 of every 32): one 16-byte load feeds eight chains, the chains keep their order, and the
+        // fold below pairs the same chains in the same rounds, so the sum is bit-identical.
         const uint32_t grp = lane >> 2, sub = lane & 3u, per_lane = H / 32u;
-        for (uint32_t r0 = 0; r0 < k && safe; r0 += 8u) {
+        for (uint32_t r0 = 0; r0 < n && safe; r0 += 8u) {
             const uint32_t r = r0 + grp;
-            const uint32_t e = __shfl_sync(0xFFFFFFFFu, my_id, r < k ? r : 0u);
+            const uint32_t e = cand[r < n ? r : n - 1u];
             const uint4* wrow = reinterpret_cast<const uint4*>(wg + (size_t)e * H) + sub;
             const uint4* xrow = reinterpret_cast<const uint4*>(xs) + sub;
             float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
@@ -601,13 +615,22 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             c[0] = __fadd_rn(c[0], c[2]);
             c[1] = __fadd_rn(c[1], c[3]);
             c[0] = __fadd_rn(c[0], c[1]);
-            const float canon = __shfl_sync(0xFFFFFFFFu, c[0], ((lane - r0) & 7u) * 4u);
-            if (lane >= r0 && lane < r0 + 8u && lane < k) my_logit = canon;
+            if (sub == 0u && r < n) canon[r] = c[0];
         }
-        if (safe && lane < k) {     // the premise of the bounds, checked on every selected logit
-            const float d = fabsf(my_logit - lg[my_id]);
+        __syncwarp();
+        // step 5: exact values of the candidates; the premise of the bounds is checked on each of them
+        const bool mine = safe && lane < n;
+        uint32_t my_e = 0xFFFFFFFFu;
+        float my_sc = 0.0f, my_val = -INFINITY;
+        if (mine) {
+            my_e = cand[lane];
+            const float cl = canon[lane];
+            const float d = fabsf(cl - lg[my_e]);
             worst = fmaxf(worst, d / delta);
             if (!(d <= 0.5f * delta)) safe = false;
+            float slope_unused;
+            my_sc = score_and_slope(p, cl, slope_unused);
+            my_val = __fadd_rn(my_sc, bias ? bias[my_e] : 0.0f);
         }
         safe = __all_sync(0xFFFFFFFFu, safe);
         if (!safe) {
@@ -618,10 +641,18 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             __syncwarp();
             continue;
         }
-        float slope_unused;
-        const float my_w = lane < k ? score_and_slope(p, my_logit, slope_unused) : 0.0f;
+        // step 6: rank by (value desc, index asc) among the candidates -- the canonical selection rule on canonical values
+        uint32_t rank = 0;
+        for (uint32_t jn = 0; jn < n; ++jn) {
+            const float vj = __shfl_sync(0xFFFFFFFFu, my_val, jn);
+            const uint32_t ej = __shfl_sync(0xFFFFFFFFu, my_e, jn);
+            rank += (vj > my_val || (vj == my_val && ej < my_e)) ? 1u : 0u;
+        }
+        if (mine && rank < k) { sel_id[rank] = my_e; sel_sc[rank] = my_sc; }
+        __syncwarp();
+        const float my_w = lane < k ? sel_sc[lane] : 0.0f;
         float sum = p.norm_init;
-        for (uint32_t r = 0; r < k; ++r) sum = __fadd_rn(sum, __shfl_sync(0xFFFFFFFFu, my_w, r));
+        for (uint32_t r = 0; r < k; ++r) sum = __fadd_rn(sum, sel_sc[r]);
         float w;
         if (p.normalize) {
             if (!(sum > 0.0f) || !isfinite(sum)) {
@@ -634,7 +665,7 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             w = __fmul_rn(my_w, p.weight_scale);
         }
         if (lane < k) {
-            ids[(size_t)tok * k + lane] = my_id;
+            ids[(size_t)tok * k + lane] = sel_id[lane];
             weights[(size_t)tok * k + lane] = w;
         }
         __syncwarp();
@@ -648,7 +679,8 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
 bool route_fast_supported(const RouterParams& p, uint32_t H) {
     if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) return false;
     if (p.experts % 128u || H % 64u) return false;
-    return (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float)) <= 200u * 1024u;
+    return p.top_k <= kMaxCand &&
+           (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand + H / 2u) * sizeof(float)) <= 200u * 1024u;
 }
 
 // logits: approximate [T, E] (tensor-core projection); list [T], count, recheck_total: device scratch.
@@ -659,7 +691,7 @@ void launch_route_fast(const RouterParams& p, float* logits, const float* bias, 
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
                        cudaStream_t s) {
     if (T == 0) return;
-    const size_t smem = (size_t)kFastWarps * ((3u * (size_t)p.experts + H / 2u) * sizeof(float));
+    const size_t smem = (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand + H / 2u) * sizeof(float));
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);

@@ -93,32 +93,6 @@ __device__ __forceinline__ void e2m1x8(uint32_t w, uint32_t r[4]) {
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
         : "r"(w));
 }
-// m16n8k32 FP8 (E4M3 x E4M3) MMA with FP32 accumulation.  Lane (g, t): a0 / a1 = rows g / g + 8, k slots 4t .. 4t+3;
-// a2 / a3 = the same rows, k slots 16 + 4t .. ; b0 / b1 = column g, the same k slots.
-__device__ __forceinline__ void mma_e4m3(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// the same with a zero addend (a fresh partial sum)
-__device__ __forceinline__ void mma_e4m3_zero(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                              uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%10,%10,%10,%10};"
-        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
-}
-// 8 E2M1 nibbles (nibble q = column q of the word) -> two registers of four E4M3 bytes: even = columns 0, 2, 4, 6,
-// odd = columns 1, 3, 5, 7.  The nibble s.ee.m becomes the byte s.00ee.m00: 2^-6 times the E2M1 value for normal and
-// subnormal codes alike (exact), by integer shifts and masks only -- no conversion-unit instruction.
-__device__ __forceinline__ void e2m1x8_e4m3(uint32_t w, uint32_t& even, uint32_t& odd) {
-    even = ((w << 4) & 0x80808080u) | ((w << 2) & 0x1C1C1C1Cu);
-    odd = (w & 0x80808080u) | ((w >> 2) & 0x1C1C1C1Cu);
-}
 __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
     uint32_t d;
     asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));

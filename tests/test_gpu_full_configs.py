@@ -72,7 +72,7 @@ def full_layer(ctx, cfg, T, sub, tight):
         ctx.synchronize()
         after = ctx.stats()
         assert after.router_fast_tokens - before.router_fast_tokens == T
-        assert after.router_rechecked_tokens - before.router_rechecked_tokens <= T // 4
+        assert after.router_rechecked_tokens - before.router_rechecked_tokens <= T // 100
         assert np.array_equal(aux3["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
         assert np.array_equal(aux3["weights"].cpu().numpy().view(np.uint32), ref["weights"].view(np.uint32))
         assert after.router_worst_error <= 0.25, after.router_worst_error

@@ -317,7 +317,7 @@ def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
 def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
     """Tensor-core projection + exact recheck against the canonical router: expert ids in rank order and routing
     weights bit for bit (the selected logits are recomputed in the canonical summation order).
-    `dup` makes two experts identical, so that every token has an exact tie the fast path must not decide."""
+    `dup` makes two experts identical, so that every token has an exact tie."""
     monkeypatch.setenv("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", "1")
     cfg = small(synth.FMT_MXFP4, T=700, E=128, k=8, H=512, I=256, score_kind=kind, zipf_s=zipf,
                 weight_scale=1.5, name=f"fast_router{kind}{int(dup)}")
@@ -337,11 +337,11 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
     assert torch.equal(w_f.view(torch.int32), w_x.view(torch.int32))
     assert 0.0 < after.router_worst_error <= 0.5      # the bound the selection assumes, with room to spare
     if dup:
-        # a token whose top-8 holds one of the twins has an exact tie and must have been rechecked
+        # tokens whose selection holds a twin have an exact tie; the canonical rule (lower index first) decides it on the
+        # recomputed logits, inside the fast path
         touched = int(((ids_x == 3) | (ids_x == 77)).any(dim=1).sum().item())
-        assert rechecked >= touched > 0
-    else:
-        assert rechecked <= cfg.T // 3
+        assert touched > 0
+    assert rechecked <= cfg.T // 50
 
 
 @pytest.mark.parametrize("kind", [synth.SCORE_SIGMOID, synth.SCORE_SQRTSOFTPLUS])
