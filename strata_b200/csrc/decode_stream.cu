@@ -340,8 +340,8 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                             const float fh = __uint_as_float((((p ? s1h : s0h) >> (8 * wd)) & 0xFFu) << 23);
 #pragma unroll
                             for (int nt = 0; nt < NT; ++nt) {
-                                float tmp[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                                mma_f16(tmp, al[0], ah[0], al[1], ah[1], bh[nt].x, bh[nt].y);
+                                float tmp[4];
+                                mma_f16_zero(tmp, al[0], ah[0], al[1], ah[1], bh[nt].x, bh[nt].y);
                                 mma_f16(tmp, al[2], ah[2], al[3], ah[3], bh[nt].z, bh[nt].w);
                                 if (SPLIT) {
                                     mma_f16(tmp, al[0], ah[0], al[1], ah[1], bl[nt].x, bl[nt].y);

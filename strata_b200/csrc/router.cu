@@ -492,6 +492,14 @@ __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l,
 
 constexpr int kFastWarps = 4;
 
+// a read-only 16-byte load the compiler keeps in program order with its neighbours: a run of them is issued
+// back to back, before the arithmetic that consumes the first
+__device__ __forceinline__ uint4 ldg128_ordered(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 // eight products of one 16-byte weight load with the matching activations, each added to its own chain
 __device__ __forceinline__ void chain_fma8(float (&c)[8], const uint4& xv, const uint4& wv) {
     const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w}, ww[4] = {wv.x, wv.y, wv.z, wv.w};
@@ -512,23 +520,17 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     extern __shared__ __align__(16) float fsm[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
-    // per warp: choice, eps [E]; candidate ids, their canonical logits, selected ids and scores [32 each]; the token's
-    // x row (bf16)
-    const size_t per_warp = 2u * (size_t)E + 4u * kMaxCand + H / 2u;
+    // per warp: choice, eps [E]; candidate ids, their canonical logits, selected ids and scores [32 each]
+    const size_t per_warp = 2u * (size_t)E + 4u * kMaxCand;
     float* choice = fsm + warp * per_warp;
     float* eps = choice + E;
     uint32_t* cand = reinterpret_cast<uint32_t*>(eps + E);
     float* canon = reinterpret_cast<float*>(cand + kMaxCand);
     uint32_t* sel_id = reinterpret_cast<uint32_t*>(canon + kMaxCand);
     float* sel_sc = reinterpret_cast<float*>(sel_id + kMaxCand);
-    unsigned short* xs = reinterpret_cast<unsigned short*>(sel_sc + kMaxCand);
     float worst = 0.0f;        // largest |canonical - approximate| / delta this warp has seen
     for (uint32_t tok = blockIdx.x * kFastWarps + warp; tok < T; tok += gridDim.x * kFastWarps) {
         const float* lg = logits + (size_t)tok * E;
-        {     // this token's activation row, 16-byte loads into shared memory; consumed after the selection
-            const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)tok * H);
-            for (uint32_t i = lane; i < H / 8u; i += 32u) reinterpret_cast<uint4*>(xs)[i] = __ldg(src + i);
-        }
         bool bad = false;
         float mx = 0.0f;
         for (uint32_t e = lane; e < E; e += 32u) {
@@ -594,17 +596,20 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             const uint32_t r = r0 + grp;
             const uint32_t e = cand[r < n ? r : n - 1u];
             const uint4* wrow = reinterpret_cast<const uint4*>(wg + (size_t)e * H) + sub;
-            const uint4* xrow = reinterpret_cast<const uint4*>(xs) + sub;
+            // the token's row comes through L1: the four lanes of a group read 64 contiguous bytes, all groups the same
+            const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)tok * H) + sub;
             float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t j = 0;
-            for (; j + 4u <= per_lane; j += 4u) {
-                uint4 wv[4];
+            for (; j + 8u <= per_lane; j += 8u) {     // eight 16-byte router loads in flight per lane
+                uint4 wv[8], xv[8];
 #pragma unroll
-                for (uint32_t q = 0; q < 4u; ++q) wv[q] = __ldg(wrow + (size_t)(j + q) * 4u);
+                for (uint32_t q = 0; q < 8u; ++q) wv[q] = ldg128_ordered(wrow + (size_t)(j + q) * 4u);
 #pragma unroll
-                for (uint32_t q = 0; q < 4u; ++q) chain_fma8(c, xrow[(size_t)(j + q) * 4u], wv[q]);
+                for (uint32_t q = 0; q < 8u; ++q) xv[q] = ldg128_ordered(xrow + (size_t)(j + q) * 4u);
+#pragma unroll
+                for (uint32_t q = 0; q < 8u; ++q) chain_fma8(c, xv[q], wv[q]);
             }
-            for (; j < per_lane; ++j) chain_fma8(c, xrow[(size_t)j * 4u], __ldg(wrow + (size_t)j * 4u));
+            for (; j < per_lane; ++j) chain_fma8(c, __ldg(xrow + (size_t)j * 4u), __ldg(wrow + (size_t)j * 4u));
             // rounds 16 and 8 pair chains held by different lanes of the group, rounds 4, 2, 1 chains of one lane
 #pragma unroll
             for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 2));
@@ -680,7 +685,7 @@ bool route_fast_supported(const RouterParams& p, uint32_t H) {
     if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) return false;
     if (p.experts % 128u || H % 64u) return false;
     return p.top_k <= kMaxCand &&
-           (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand + H / 2u) * sizeof(float)) <= 200u * 1024u;
+           (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float)) <= 200u * 1024u;
 }
 
 // logits: approximate [T, E] (tensor-core projection); list [T], count, recheck_total: device scratch.
@@ -691,7 +696,7 @@ void launch_route_fast(const RouterParams& p, float* logits, const float* bias, 
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
                        cudaStream_t s) {
     if (T == 0) return;
-    const size_t smem = (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand + H / 2u) * sizeof(float));
+    const size_t smem = (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float));
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -701,7 +706,7 @@ void launch_route_fast(const RouterParams& p, float* logits, const float* bias, 
     }
     cudaMemsetAsync(count, 0, sizeof(uint32_t), s);
     uint32_t grid = (T + kFastWarps - 1) / kFastWarps;
-    if (grid > (uint32_t)kNumSMs * 4u) grid = (uint32_t)kNumSMs * 4u;
+    if (grid > (uint32_t)kNumSMs * 8u) grid = (uint32_t)kNumSMs * 8u;
     route_fast_kernel<<<grid, kFastWarps * 32, smem, s>>>(p, logits, bias, x, wg, T, H, ids, weights, list, count,
                                                           recheck_total, status);
     // the tokens on the list, completely in the canonical order (few: the grids stride over the list)

@@ -85,6 +85,15 @@ __device__ __forceinline__ void mma_f16(float c[4], uint32_t a0, uint32_t a1, ui
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the same MMA with a zero addend: starts a fresh partial sum without four register moves
+__device__ __forceinline__ void mma_f16_zero(float d[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
 // 8 E2M1 nibbles (one 32-bit word, nibble q = column q) -> r[b] = f16x2 {column 2b, column 2b+1}, exact
 __device__ __forceinline__ void e2m1x8(uint32_t w, uint32_t r[4]) {
     asm("{\n .reg .b8 b0, b1, b2, b3;\n mov.b32 {b0, b1, b2, b3}, %4;\n"
