@@ -656,6 +656,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None)
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--experts", type=int, default=None,
+                    help="override the expert count of the workload (profiler captures of a full-shape tile on a small device footprint)")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-sub", dest="sub", action="store_false", help="skip the sub-records of the other configurations")
     ap.add_argument("--no-parity", dest="parity", action="store_false", help="skip the oracle check of the timed layer")
@@ -669,6 +671,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     name = args.workload or "c3"
     cfg = synth.CONFIGS[name]
+    if args.experts:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, E=args.experts, name=f"{cfg.name}_e{args.experts}",
+                                  description=f"{cfg.description} ({args.experts} experts)")
     T = args.tokens or cfg.T
     if args.scaling is None:
         args.scaling = "strong"

@@ -199,6 +199,21 @@ int strata_moe_route(strata_moe_layer* layer, const void* x_bf16, uint32_t token
  * ref: dsv4_route_hash_sqrtsoftplus_f32(_into), src/models/dsv4/deepseek_ops.cpp:390-461. */
 int strata_moe_route_hash(strata_moe_layer* layer, const void* x_bf16, uint32_t tokens,
                           const uint32_t* token_experts, float* logits, uint32_t* ids, float* weights);
+/* Inkling's router with shared "sink" experts.  Two stage calls, all pointers device memory:
+ *   strata_moe_project_rows   logits[t, r] = x[t, :] . w[r, :] in the router's canonical summation order, for any
+ *                             BF16 matrix w [rows, hidden] (here the gate over routed_experts + sinks rows);
+ *   strata_moe_route_sink     logits [tokens, routed_experts + sinks] -> ids [tokens, top_k] (top-k of
+ *                             sigmoid(logit) + bias over the routed range), their weights [tokens, top_k] and the
+ *                             sinks' weights [tokens, sinks]: softmax over the log-sigmoid of the raw logits of the
+ *                             selected experts and every sink, times scale (= routed_scale * global_scale).
+ * top_k + sinks <= 32.  The routed part then runs through strata_moe_forward_routed, the sinks as a dense command.
+ * ref: inkling_route_sigmoid_sink, src/models/inkling/inkling_ops.cpp:184-275; call site
+ * src/models/inkling/inkling_runtime.cpp:524-560. */
+int strata_moe_project_rows(strata_moe_ctx* ctx, const void* x_bf16, uint32_t tokens, uint32_t hidden,
+                            const void* w_bf16, uint32_t rows, float* logits);
+int strata_moe_route_sink(strata_moe_ctx* ctx, const float* logits, const float* bias, uint32_t tokens,
+                          uint32_t routed_experts, uint32_t sinks, uint32_t top_k, float scale, uint32_t* ids,
+                          float* weights, float* sink_weights);
 /* ref: job building in sparse_mlp (src/models/glm52/glm_runtime.cpp:1521-1541) and the page
  * group table (src/models/dsv4/deepseek_runtime.cpp:6216-6321).  Groups pairs whose expert lies
  * in [expert_begin, expert_begin + n_experts); counts/offsets are indexed from expert_begin.

@@ -33,6 +33,7 @@ REF_SOURCES = [
     "src/models/dsv4/deepseek_ops.cpp",
     "src/models/glm52/glm_ops.cpp",
     "src/models/laguna/laguna_ops.cpp",
+    "src/models/inkling/inkling_ops.cpp",
     "src/models/kimi_k3/kimi_k3_ops.cpp",
     "src/models/kimi_k3/kimi_k3_layer.cpp",
     "src/models/kimi_k3/kimi_k3_kv_cache.cpp",

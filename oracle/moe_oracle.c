@@ -457,6 +457,47 @@ ORC_API int orc_route_row(const orc_router_spec* s, const float* logits, const f
     return 0;
 }
 
+/* Inkling's sink router, inkling_route_sigmoid_sink (src/models/inkling/inkling_ops.cpp:184-275).
+ * logits holds the E routed experts followed by S shared "sink" experts.  Selection: top-k of
+ * sigmoid(logit) + bias over the ROUTED range (lower index wins ties).  Weights: the RAW logits of the k
+ * selected experts and of every sink go through log-sigmoid (min(x,0) - log1p(exp(-|x|)),
+ * src/platform/numerics.cpp:54-59), then a softmax over that joint set (maximum subtracted, sum in index
+ * order), times scale = routed_scale * global_scale.  ids / weights: k selected then S sinks (ids E..E+S-1).
+ * Returns 0, -1 on a non-finite logit or bias, -2 when the softmax sum is not positive and finite. */
+ORC_API int orc_route_sigmoid_sink(const float* logits, const float* bias, uint32_t E, uint32_t S, uint32_t k,
+                                   float scale, float* scratch /* E */, uint32_t* ids, float* weights) {
+    if (k == 0 || k > E) return -3;
+    for (uint32_t e = 0; e < E + S; ++e)
+        if (!isfinite(logits[e])) return -1;
+    for (uint32_t e = 0; e < E; ++e) {
+        if (!isfinite(bias[e])) return -1;
+        scratch[e] = orc_sigmoid(logits[e]) + bias[e];
+    }
+    for (uint32_t r = 0; r < k; ++r) {
+        uint32_t best = 0;
+        float best_v = -INFINITY;
+        for (uint32_t e = 0; e < E; ++e)
+            if (scratch[e] > best_v) { best_v = scratch[e]; best = e; }
+        ids[r] = best;
+        scratch[best] = -INFINITY;
+    }
+    for (uint32_t i = 0; i < S; ++i) ids[k + i] = E + i;
+    float mx = -INFINITY;
+    for (uint32_t i = 0; i < k + S; ++i) {
+        const float v = logits[ids[i]];
+        weights[i] = fminf(v, 0.0f) - log1pf(expf(-fabsf(v)));
+        if (weights[i] > mx) mx = weights[i];
+    }
+    float total = 0.0f;
+    for (uint32_t i = 0; i < k + S; ++i) {
+        weights[i] = expf(weights[i] - mx);
+        total += weights[i];
+    }
+    if (!(total > 0.0f) || !isfinite(total)) return -2;
+    for (uint32_t i = 0; i < k + S; ++i) weights[i] = weights[i] / total * scale;
+    return 0;
+}
+
 /* Hash routing, dsv4_route_hash_sqrtsoftplus_f32_into (src/models/dsv4/deepseek_ops.cpp:414-461): the
  * experts are given, the weights are their scores summed in rank order, normalised and scaled.  Stated
  * for every score kind; softmax is not covered (it has no reference).  Returns -3 for an id >= E. */

@@ -134,6 +134,8 @@ def ref():
             getattr(lib, name).argtypes = [f32p, f32p, C.c_uint32, C.c_uint32, C.c_float, u32p, f32p]
         lib.ref_laguna_route.argtypes = [f32p, f32p, C.c_uint32, C.c_uint32, C.c_int, C.c_float,
                                          u32p, f32p]
+        lib.ref_inkling_route_sink.argtypes = [f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float,
+                                               u32p, f32p]
         lib.ref_kimi_mxfp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_uint32, C.c_uint32]
         lib.ref_dsv4_fp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_uint32, C.c_uint32]
         lib.ref_laguna_nvfp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_float, C.c_uint32,
@@ -223,6 +225,24 @@ def route(spec, logits, bias=None):
     rc = port().orc_route(C.byref(spec), _p(logits, f32p), _p(b, f32p) if b is not None else None,
                           T, _p(ids, u32p), _p(w, f32p))
     return rc, ids, w
+
+
+def route_sigmoid_sink(logits, bias, experts, sinks, top_k, scale):
+    """Inkling's sink router over logits [T, experts + sinks]: ids / weights [T, top_k + sinks]."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    T = logits.shape[0]
+    ids = np.empty((T, top_k + sinks), np.uint32)
+    w = np.empty((T, top_k + sinks), np.float32)
+    scratch = np.empty(experts, np.float32)
+    lib = port()
+    lib.orc_route_sigmoid_sink.argtypes = [f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, f32p, u32p, f32p]
+    for t in range(T):
+        rc = lib.orc_route_sigmoid_sink(_p(logits[t], f32p), _p(bias, f32p), experts, sinks, top_k, scale,
+                                        _p(scratch, f32p), _p(ids[t], u32p), _p(w[t], f32p))
+        if rc:
+            return rc, ids, w
+    return 0, ids, w
 
 
 def group(ids, experts):

@@ -21,6 +21,7 @@
 #include "strata/deepseek_ops.hpp"
 #include "strata/glm_int4.hpp"
 #include "strata/glm_ops.hpp"
+#include "strata/inkling_ops.hpp"
 #include "strata/kimi_k3_layer.hpp"
 #include "strata/kimi_k3_ops.hpp"
 #include "strata/laguna_ops.hpp"
@@ -92,6 +93,24 @@ REF_API int ref_kimi_route(const float* logits, const float* bias, uint32_t expe
         ids[i] = sel[i].expert;
         weights[i] = sel[i].weight;
     }
+    return 0;
+}
+
+// inkling_route_sigmoid_sink, src/models/inkling/inkling_ops.cpp:184-275
+REF_API int ref_inkling_route_sink(const float* logits, const float* bias, uint32_t experts, uint32_t sinks, uint32_t k,
+                                   float routed_scale, float global_scale, uint32_t* ids, float* weights) {
+    strata::RouterSpec spec;
+    spec.selection = strata::RouterSelectionKind::TopK;
+    spec.scoring = strata::RouterScoreKind::Sigmoid;
+    spec.routed_experts = experts;
+    spec.experts_per_token = k;
+    spec.normalize_topk = true;
+    spec.selection_bias = true;
+    spec.routed_scale = routed_scale;
+    auto r = strata::inkling_route_sigmoid_sink({logits, (size_t)experts + sinks}, {bias, experts}, spec, sinks, global_scale);
+    if (!r.ok()) return 1;
+    std::copy(r.value.experts.begin(), r.value.experts.end(), ids);
+    std::copy(r.value.weights.begin(), r.value.weights.end(), weights);
     return 0;
 }
 

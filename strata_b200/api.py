@@ -22,7 +22,7 @@ EXPORTS = [
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
-    "strata_moe_route_hash",
+    "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink",
     "strata_moe_forward_routed", "strata_moe_latent_create", "strata_moe_latent_destroy", "strata_moe_latent_experts",
     "strata_moe_latent_set_router", "strata_moe_latent_set_projections", "strata_moe_latent_set_shared",
     "strata_moe_latent_forward",
@@ -96,6 +96,8 @@ def load_library():
     lib.strata_moe_forward_host.argtypes = [vp, vp, u32, vp]
     lib.strata_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
     lib.strata_moe_route_hash.argtypes = [vp, vp, u32, vp, vp, vp, vp]
+    lib.strata_moe_project_rows.argtypes = [vp, vp, u32, u32, vp, u32, vp]
+    lib.strata_moe_route_sink.argtypes = [vp, vp, vp, u32, u32, u32, u32, C.c_float, vp, vp, vp]
     lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp]
     lib.strata_moe_gather_rows.argtypes = [vp, vp, u32, vp, u32, u32, vp]
     lib.strata_moe_combine.argtypes = [vp, vp, vp, vp, vp, u32, vp]
@@ -203,6 +205,27 @@ class MoeContext:
         s = Stats()
         self.check(self.lib.strata_moe_get_stats(self.h, C.byref(s)))
         return s
+
+    def project_rows(self, x, w):
+        """logits [T, rows] of BF16 x [T, H] against BF16 w [rows, H] in the router's canonical summation order."""
+        T, H = x.shape
+        out = torch.empty(T, w.shape[0], dtype=torch.float32, device=x.device)
+        self.enter()
+        self.check(self.lib.strata_moe_project_rows(self.h, _ptr(x), T, H, _ptr(w), w.shape[0], _ptr(out)))
+        self.leave()
+        return out
+
+    def route_sink(self, logits, bias, routed_experts, sinks, top_k, scale):
+        """Inkling's sink router: (ids [T, k], weights [T, k], sink weights [T, sinks])."""
+        T, dev = logits.shape[0], logits.device
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=dev)
+        w = torch.empty(T, top_k, dtype=torch.float32, device=dev)
+        ws = torch.empty(T, max(sinks, 1), dtype=torch.float32, device=dev)
+        self.enter()
+        self.check(self.lib.strata_moe_route_sink(self.h, _ptr(logits), _ptr(bias), T, routed_experts, sinks, top_k,
+                                                  scale, _ptr(ids), _ptr(w), _ptr(ws)))
+        self.leave()
+        return ids, w, ws[:, :sinks]
 
     def quantize_e4m3(self, values):
         """In-place E4M3 activation quantisation of fp32 [rows, cols] (one power-of-two scale per 128 columns)."""

@@ -64,6 +64,7 @@ struct LayerKnobs {
     bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
     bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
     bool no_stream_ring = false;    // STRATA_MOE_NO_STREAM_RING: small batches use the register-streaming kernels
+    bool no_small_front = false;    // STRATA_MOE_NO_SMALL_FRONT: decode batches keep the separate route / group / convert kernels
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
     int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
@@ -87,6 +88,7 @@ static LayerKnobs read_knobs() {
     k.prefill_ntile = num("STRATA_MOE_PREFILL_NTILE", 0);
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
+    k.no_small_front = getenv("STRATA_MOE_NO_SMALL_FRONT") != nullptr;
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
     k.stream_ring_max_rows = num("STRATA_MOE_STREAM_RING_MAX_ROWS", 8);
     return k;
@@ -407,7 +409,7 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
         return 0;
     }
     float* lg = logits_out ? logits_out : L->logits;
-    launch_router_logits(x, L->router, T, d.hidden, d.experts, lg, s);
+    launch_router_logits(x, L->router, T, d.hidden, d.experts, lg, s, L->knobs.no_small_front ? nullptr : ctx->d_status);
     mark(ctx, 1);
     launch_route(rp, lg, L->bias, T, ids, w, ctx->d_status, s);
     return 0;
@@ -418,7 +420,7 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
                 uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
                 const uint32_t* n_active, uint32_t max_rows, float* y, uint32_t expected_pairs = 0,
-                const uint32_t* pairs_dev = nullptr) {
+                const uint32_t* pairs_dev = nullptr, bool x_ready = false) {
     // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
     // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
     strata_moe_ctx* ctx = L->ctx;
@@ -426,8 +428,9 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     if (pairs == 0) return 0;
     const uint32_t bound = pairs;
     if (pairs_dev && expected_pairs) pairs = expected_pairs < bound ? expected_pairs : bound;
+    // x_ready: the caller's front-end kernel already left the f16 rows and their factors in the workspace
     if (use_prefill(L, pairs, n_groups)) {
-        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        if (!x_ready) launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
         PrefillArgs p{};
         p.fmt = L->d.format;
@@ -1003,11 +1006,37 @@ int strata_moe_route_hash(strata_moe_layer* L, const void* x, uint32_t T, const 
     if (!L->router) return fail(ctx, STRATA_MOE_E_INVALID, "router weights were never set");
     CK(cudaSetDevice(ctx->device));
     float* lg = logits ? logits : L->logits;
-    launch_router_logits((const __nv_bfloat16*)x, L->router, T, L->d.hidden, L->d.experts, lg, ctx->stream);
+    launch_router_logits((const __nv_bfloat16*)x, L->router, T, L->d.hidden, L->d.experts, lg, ctx->stream, ctx->d_status);
     RouterParams p{L->d.experts, L->d.top_k, L->d.score_kind, L->d.normalize, L->d.norm_init,
                    L->d.weight_scale, L->d.softcap};
     // an expert id outside the layer raises the status word (kStatusNonFiniteLogit's neighbour: bad route)
     launch_route(p, lg, nullptr, T, ids, weights, ctx->d_status, ctx->stream, token_experts);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_project_rows(strata_moe_ctx* ctx, const void* x, uint32_t T, uint32_t H, const void* w, uint32_t rows,
+                            float* logits) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (!x || !w || !logits) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (H == 0 || H % 32u || rows == 0) return fail(ctx, STRATA_MOE_E_INVALID, "hidden must be a positive multiple of 32 and rows positive");
+    if ((((uintptr_t)x | (uintptr_t)w) & 15u) != 0) return fail(ctx, STRATA_MOE_E_INVALID, "x and w must be 16-byte aligned");
+    CK(cudaSetDevice(ctx->device));
+    launch_router_logits((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, T, H, rows, logits, ctx->stream, ctx->d_status);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_route_sink(strata_moe_ctx* ctx, const float* logits, const float* bias, uint32_t T, uint32_t E, uint32_t S,
+                          uint32_t k, float scale, uint32_t* ids, float* weights, float* sink_weights) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (!logits || !bias || !ids || !weights || (S && !sink_weights)) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    if (k == 0 || k > E) return fail(ctx, STRATA_MOE_E_INVALID, "Inkling router selection is out of range");
+    if (k + S > 32u) return fail(ctx, STRATA_MOE_E_INVALID, "top_k + sinks exceed 32");
+    if ((size_t)E * 4u * sizeof(float) > 48u * 1024u) return fail(ctx, STRATA_MOE_E_INVALID, "too many routed experts");
+    if (!std::isfinite(scale)) return fail(ctx, STRATA_MOE_E_INVALID, "Inkling router global scale must be finite");
+    CK(cudaSetDevice(ctx->device));
+    launch_route_sink(logits, bias, T, E, S, k, scale, ids, weights, sink_weights, ctx->d_status, ctx->stream);
     CK(cudaGetLastError());
     return 0;
 }
@@ -1126,13 +1155,35 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
         if (rc) return rc;
         CK(cudaEventRecord(ctx->ev_join, ctx->side));
     }
-    rc = run_router(L, xb, T, (aux && aux->logits) ? aux->logits : nullptr, ids, w);
-    if (rc) return rc;
-    mark(ctx, 2);
-    launch_group(ids, P, 0, d.experts, counts, offsets, perm, L->inv, L->active, L->n_active,
-                 L->group_scratch, s);
-    mark(ctx, 3);
-    rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y);
+    // Decode batches (<= 16 tokens): canonical logits, then ONE kernel for scores / top-k / weights, grouping and the
+    // gather + f16 conversion of the routed rows (when the expert kernels read f16 rows at all).
+    bool x_ready = false, front_done = false;
+    if (T <= 16 && !L->knobs.no_small_front) {
+        float* lg = (aux && aux->logits) ? aux->logits : L->logits;
+        const bool convert = use_prefill(L, P, d.experts) || L->f16_ok;
+        RouterParams rp{d.experts, d.top_k, d.score_kind, d.normalize, d.norm_init, d.weight_scale, d.softcap};
+        launch_router_logits(xb, L->router, T, d.hidden, d.experts, lg, s, ctx->d_status);
+        mark(ctx, 1);
+        front_done = launch_front_small(rp, lg, L->bias, T, ids, w, counts, offsets, perm, L->inv, L->active, L->n_active,
+                                        xb, d.hidden, convert ? L->xg : nullptr, L->x_rowscale, ctx->d_status, s);
+        if (front_done) {
+            x_ready = convert;
+            mark(ctx, 2);
+            mark(ctx, 3);
+        } else {
+            launch_route(rp, lg, L->bias, T, ids, w, ctx->d_status, s);
+        }
+    } else {
+        rc = run_router(L, xb, T, (aux && aux->logits) ? aux->logits : nullptr, ids, w);
+        if (rc) return rc;
+    }
+    if (!front_done) {
+        mark(ctx, 2);
+        launch_group(ids, P, 0, d.experts, counts, offsets, perm, L->inv, L->active, L->n_active,
+                     L->group_scratch, s);
+        mark(ctx, 3);
+    }
+    rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y, 0, nullptr, x_ready);
     if (rc) return rc;
     const float* shared = nullptr;
     if (fork_shared) {

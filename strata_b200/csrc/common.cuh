@@ -51,11 +51,17 @@ struct WeightTable {
 // ---- launch wrappers (definitions in the .cu files) ---------------------------------
 // router.cu
 void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
-                          uint32_t E, float* logits, cudaStream_t s);
+                          uint32_t E, float* logits, cudaStream_t s, uint32_t* status = nullptr);
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,
                   uint32_t* ids, float* weights, uint32_t* status, cudaStream_t s,
                   const uint32_t* forced_ids = nullptr);
 // Fast router (tensor-core projection + exact recheck), see router.cu.
+bool launch_front_small(const RouterParams& p, const float* logits, const float* bias, uint32_t T, uint32_t* ids,
+                        float* weights, uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* inv,
+                        uint32_t* active_list, uint32_t* n_active, const __nv_bfloat16* x, uint32_t H, void* xg,
+                        float* x_rowscale, uint32_t* status, cudaStream_t s);
+void launch_route_sink(const float* logits, const float* bias, uint32_t T, uint32_t E, uint32_t S, uint32_t k, float scale,
+                       uint32_t* ids, float* w_routed, float* w_sinks, uint32_t* status, cudaStream_t s);
 bool route_fast_supported(const RouterParams& p, uint32_t H);
 void launch_route_fast(const RouterParams& p, float* logits, const float* bias, const __nv_bfloat16* x,
                        const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t* ids, float* weights,

@@ -26,6 +26,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "rows_f16.cuh"
 
 namespace smoe {
 
@@ -368,23 +369,17 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
     if (pos >= rows) return;
     if (rows_dev && pos >= *rows_dev) return;   // `rows` is only an upper bound; the count lives on the device
     const uint32_t srow = perm ? perm[pos] / k_div : (src_rows ? pos % src_rows : pos);
+    if (!SRC_F32) {
+        warp_row_to_f16_bf16(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C, C, hi + (size_t)pos * C,
+                             rowscale + pos);
+        return;
+    }
     float mx = 0.0f;
-    if (SRC_F32) {
+    {
         const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)srow * C);
         for (uint32_t i = lane; i < C / 4u; i += 32u) {
             const float4 v = __ldg(p + i);
             mx = fmaxf(mx, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-        }
-    } else {
-        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C);
-        for (uint32_t i = lane; i < C / 8u; i += 32u) {
-            const uint4 v = __ldg(p + i);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                mx = fmaxf(mx, fabsf(__uint_as_float(w[q] << 16)));
-                mx = fmaxf(mx, fabsf(__uint_as_float(w[q] & 0xFFFF0000u)));
-            }
         }
     }
 #pragma unroll
@@ -396,7 +391,7 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
     ex = max(-100, min(100, ex));
     const float sc = __uint_as_float((uint32_t)(ex + 127) << 23);
     if (lane == 0) rowscale[pos] = __uint_as_float((uint32_t)(127 - ex) << 23);
-    if (SRC_F32) {
+    {
         const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(src) + (size_t)srow * C);
         for (uint32_t i = lane; i < C / 4u; i += 32u) {
             const float4 v = __ldg(p + i);
@@ -414,20 +409,6 @@ __global__ void __launch_bounds__(256) rows_to_f16_kernel(const void* __restrict
                 *reinterpret_cast<uint2*>(lo + (size_t)pos * C + i * 4u) =
                     make_uint2((uint32_t)__half_as_ushort(l[0]) | ((uint32_t)__half_as_ushort(l[1]) << 16),
                                (uint32_t)__half_as_ushort(l[2]) | ((uint32_t)__half_as_ushort(l[3]) << 16));
-        }
-    } else {
-        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + (size_t)srow * C);
-        for (uint32_t i = lane; i < C / 8u; i += 32u) {
-            const uint4 v = __ldg(p + i);
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const __half a = __float2half_rn(__uint_as_float(w[q] << 16) * sc);
-                const __half b = __float2half_rn(__uint_as_float(w[q] & 0xFFFF0000u) * sc);
-                o[q] = (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
-            }
-            *reinterpret_cast<uint4*>(hi + (size_t)pos * C + i * 8u) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     }
 }

@@ -11,8 +11,13 @@
 
 #include "common.cuh"
 #include "libm_exact.cuh"
+#include "rows_f16.cuh"
+#include "stream_ring.cuh"
 
 namespace smoe {
+
+bool launch_router_logits_small(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t E,
+                                float* logits, uint32_t* status, cudaStream_t s);
 
 // ---------------------------------------------------------------------------------------
 // logits[t, e] for a tile of TT tokens and WARPS expert rows per CTA.  The activation tile and
@@ -296,8 +301,10 @@ __global__ void __launch_bounds__(kBigWarps * 32, 1) router_logits_big_kernel(
 }
 
 void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H,
-                          uint32_t E, float* logits, cudaStream_t s) {
+                          uint32_t E, float* logits, cudaStream_t s, uint32_t* status) {
     if (T == 0) return;
+    // decode batches: whole rows by bulk copy, one warp per token (25 -> about 6 us for 8 tokens at E = 256, H = 4096)
+    if (status != nullptr && launch_router_logits_small(x, wg, T, H, E, logits, status, s)) return;
     // few tokens: one expert row per warp, two warps per CTA, so the rows spread over many SMs;
     // many tokens: register-blocked kernel (4 rows per warp, 32 rows per CTA)
     const size_t big_tiles = (size_t)((T + 15) / 16) * ((E + 31) / 32);
@@ -329,21 +336,13 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
     ++g_kernel_launches;
 }
 
-// One warp per token.  Shared memory: score[E] and choice[E] per warp.
-constexpr int kRouteWarps = 4;
-
-__global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
-    RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
-    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
-    const uint32_t* __restrict__ forced_ids, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count) {
-    extern __shared__ float smem[];
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+// Scores, top-k and routing weights of ONE token by one warp.  score / choice: [E] floats of shared memory each.
+__device__ __forceinline__ void route_token(const RouterParams& p, const float* __restrict__ logits,
+                                            const float* __restrict__ bias, uint32_t tok, float* score, float* choice,
+                                            uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
+                                            const uint32_t* __restrict__ forced_ids) {
+    const uint32_t lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
-    float* score = smem + (size_t)warp * 2u * E;
-    float* choice = score + E;
-    if (list) T = *count;     // tokens list[0 .. *count), the grid strides over them
-  for (uint32_t slot = blockIdx.x * kRouteWarps + warp; slot < T; slot += gridDim.x * kRouteWarps) {
-    const uint32_t tok = list ? list[slot] : slot;
     const float* lg = logits + (size_t)tok * E;
     bool bad = false;
 
@@ -433,7 +432,23 @@ __global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
     }
     if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) atomicOr(status, kStatusNonFiniteLogit);
     __syncwarp();
-  }
+}
+
+// One warp per token.  Shared memory: score[E] and choice[E] per warp.
+constexpr int kRouteWarps = 4;
+
+__global__ void __launch_bounds__(kRouteWarps * 32) route_kernel(
+    RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
+    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
+    const uint32_t* __restrict__ forced_ids, const uint32_t* __restrict__ list, const uint32_t* __restrict__ count) {
+    extern __shared__ float smem[];
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t E = p.experts;
+    float* score = smem + (size_t)warp * 2u * E;
+    float* choice = score + E;
+    if (list) T = *count;     // tokens list[0 .. *count), the grid strides over them
+    for (uint32_t slot = blockIdx.x * kRouteWarps + warp; slot < T; slot += gridDim.x * kRouteWarps)
+        route_token(p, logits, bias, list ? list[slot] : slot, score, choice, ids, weights, status, forced_ids);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -681,6 +696,123 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     if (lane == 0 && worst > 0.0f) atomicMax(reinterpret_cast<unsigned int*>(recheck_total + 1), __float_as_uint(worst));
 }
 
+// ---------------------------------------------------------------------------------------
+// Canonical logits for a handful of tokens (decode batches), latency-oriented.
+//
+// The staged kernel above walks a row in 256-column chunks with two block barriers per chunk; for eight tokens that
+// chain of load -> barrier -> arithmetic -> barrier takes 25 us at H = 4096 although the router is only 2 MB.  Here a
+// CTA owns eight expert rows and fetches them WHOLE into shared memory with bulk copies (four column quarters per row,
+// each quarter completing on its own mbarrier, all issued up front), and warp w computes token w against the eight
+// rows with the four-lanes-per-expert chain mapping of route_fast_kernel: bit-identical sums, no block barrier, and
+// the arithmetic on a quarter starts as soon as that quarter has landed.
+constexpr uint32_t kSmallRows = 8;        // expert rows per CTA
+constexpr uint32_t kSmallMaxTokens = 16;  // one warp per token
+constexpr uint32_t kSmallPad = 64;        // bytes added to the row pitch: two neighbouring rows fill one 128-byte wavefront
+
+__global__ void __launch_bounds__(kSmallMaxTokens * 32) router_logits_small_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H, uint32_t E,
+    float* __restrict__ logits, uint32_t* status) {
+    extern __shared__ __align__(128) uint8_t small_smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(small_smem);     // [4]
+    uint8_t* rows = small_smem + 128;
+    const uint32_t pitch = H * 2u + kSmallPad;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t e0 = blockIdx.x * kSmallRows;
+    const uint32_t nrows = min(kSmallRows, E - e0);
+    const uint32_t per_lane = H / 32u;                            // 64-byte steps of a row
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        for (int q = 0; q < 4; ++q) ring::mbar_init(&bars[q], 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (warp == 0) {
+        if (lane == 0)
+            for (uint32_t q = 0; q < 4u; ++q) {
+                const uint32_t j0 = per_lane * q / 4u, j1 = per_lane * (q + 1u) / 4u;
+                ring::mbar_arrive_expect_tx(&bars[q], nrows * (j1 - j0) * 64u);
+            }
+        __syncwarp();
+        if (lane < nrows)
+            for (uint32_t q = 0; q < 4u; ++q) {
+                const uint32_t j0 = per_lane * q / 4u, j1 = per_lane * (q + 1u) / 4u;
+                if (j1 > j0)
+                    ring::bulk_g2s(rows + (size_t)lane * pitch + j0 * 64u,
+                                   reinterpret_cast<const uint8_t*>(wg + (size_t)(e0 + lane) * H) + j0 * 64u,
+                                   (j1 - j0) * 64u, &bars[q]);
+            }
+    }
+    bool ok = true;
+    if (warp < T) {
+        const uint32_t grp = lane >> 2, sub = lane & 3u;
+        const uint32_t row = grp < nrows ? grp : nrows - 1u;
+        const uint32_t wrow = ring::smem_addr(rows + (size_t)row * pitch) + sub * 16u;
+        const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)warp * H) + sub;
+        float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t q = 0; q < 4u && ok; ++q) {
+            const uint32_t j0 = per_lane * q / 4u, j1 = per_lane * (q + 1u) / 4u;
+            uint32_t j = j0;
+            uint4 xv[8];
+            const uint32_t first = min(8u, j1 - j0);
+            for (uint32_t i = 0; i < 8u; ++i)      // the token's columns of this quarter start before the wait
+                if (i < first) xv[i] = ldg128_ordered(xrow + (size_t)(j0 + i) * 4u);
+            ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait(&bars[q], 0u, &abort_flag));
+            if (!ok) break;
+            for (; j + 8u <= j1; j += 8u) {
+#pragma unroll
+                for (uint32_t i = 0; i < 8u; ++i) chain_fma8(c, xv[i], ring::lds128(wrow + (j + i) * 64u));
+                const uint32_t nxt = j + 8u;
+#pragma unroll
+                for (uint32_t i = 0; i < 8u; ++i)
+                    if (nxt + i < j1) xv[i] = ldg128_ordered(xrow + (size_t)(nxt + i) * 4u);
+            }
+            for (uint32_t i = 0; j < j1; ++j, ++i) chain_fma8(c, xv[i], ring::lds128(wrow + j * 64u));
+        }
+        if (ok) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 2));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 1));
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[i] = __fadd_rn(c[i], c[i + 4]);
+            c[0] = __fadd_rn(c[0], c[2]);
+            c[1] = __fadd_rn(c[1], c[3]);
+            c[0] = __fadd_rn(c[0], c[1]);
+            if (sub == 0u && grp < nrows) logits[(size_t)warp * E + e0 + grp] = c[0];
+        }
+    }
+    if (!ok && lane == 0) { abort_flag = 1; atomicOr(status, kStatusWaitTimeout); }
+    // the copies target this CTA's shared memory: none may be in flight when the CTA retires
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (uint32_t q = 0; q < 4u; ++q)
+            for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+                if (ring::mbar_test(&bars[q], 0u)) break;
+}
+
+bool launch_router_logits_small(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint32_t T, uint32_t H, uint32_t E,
+                                float* logits, uint32_t* status, cudaStream_t s) {
+    if (T == 0 || T > kSmallMaxTokens || H % 128u || status == nullptr) return false;
+    if ((((uintptr_t)x | (uintptr_t)wg) & 15u) != 0) return false;
+    const size_t smem = 128u + (size_t)kSmallRows * (H * 2u + kSmallPad);
+    if (smem > 200u * 1024u) return false;
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return false;
+    if (!attr[dev]) {
+        if (cudaFuncSetAttribute(router_logits_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+            cudaSuccess)
+            return false;
+        attr[dev] = true;
+    }
+    const uint32_t warps = T < 4u ? 4u : T;      // warp 0 also issues the copies
+    router_logits_small_kernel<<<(E + kSmallRows - 1) / kSmallRows, warps * 32u, smem, s>>>(x, wg, T, H, E, logits, status);
+    ++g_kernel_launches;
+    return true;
+}
+
 bool route_fast_supported(const RouterParams& p, uint32_t H) {
     if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) return false;
     if (p.experts % 128u || H % 64u) return false;
@@ -716,6 +848,191 @@ void launch_route_fast(const RouterParams& p, float* logits, const float* bias, 
     const size_t smem_r = (size_t)kRouteWarps * 2u * E * sizeof(float);
     route_kernel<<<64, kRouteWarps * 32, smem_r, s>>>(p, logits, bias, T, ids, weights, status, nullptr, list, count);
     g_kernel_launches += 3;
+}
+
+// ---------------------------------------------------------------------------------------
+// Decode front end in ONE launch: scores / top-k / weights, grouping and the gather + f16 conversion of the routed
+// rows, for at most 16 tokens.  As separate kernels (route, group, convert) these cost 14 + 12 + 8 us for 8 tokens,
+// mostly launch latency and single-CTA barrier chains.  One CTA of 16 warps: warp w routes token w; the pairs
+// (<= 512) are counted per expert in shared memory, offsets come from a two-level warp scan (two experts per thread,
+// so up to 1024 experts), every pair finds its stable position by counting the earlier pairs of its expert; then the
+// warps convert the routed rows.  Outputs are those of route_kernel, the grouping kernels and rows_to_f16_kernel.
+constexpr uint32_t kFrontWarps = 16, kFrontMaxPairs = 512, kFrontMaxExperts = 1024;
+
+__global__ void __launch_bounds__(kFrontWarps * 32) front_small_kernel(
+    RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T,
+    uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* __restrict__ counts,
+    uint32_t* __restrict__ offsets, uint32_t* __restrict__ perm, uint32_t* __restrict__ inv,
+    uint32_t* __restrict__ active_list, uint32_t* __restrict__ n_active, const __nv_bfloat16* __restrict__ x, uint32_t H,
+    __half* __restrict__ xg, float* __restrict__ x_rowscale, uint32_t* status) {
+    extern __shared__ float fsm2[];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t E = p.experts, k = p.top_k, P = T * k;
+    float* score = fsm2 + (size_t)warp * 2u * E;
+    float* choice = score + E;
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(fsm2 + (size_t)kFrontWarps * 2u * E);   // [E]
+    uint32_t* off = cnt + E;                                                            // [E]
+    uint32_t* ids_s = off + E;                                                          // [P]
+    uint32_t* perm_s = ids_s + kFrontMaxPairs;                                          // [P]
+    __shared__ uint32_t wtot[kFrontWarps], wact[kFrontWarps];
+    for (uint32_t e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+    if (warp < T) {
+        route_token(p, logits, bias, warp, score, choice, ids, weights, status, nullptr);
+        if (lane < k) ids_s[warp * k + lane] = ids[(size_t)warp * k + lane];    // this lane's own store
+    }
+    __syncthreads();
+    if (tid < P) atomicAdd(&cnt[ids_s[tid]], 1u);
+    __syncthreads();
+    // exclusive scans over the experts of (count) and of (count != 0): thread t owns experts 2t and 2t + 1
+    const uint32_t ea = 2u * tid, eb = ea + 1u;
+    const uint32_t ca = ea < E ? cnt[ea] : 0u, cb = eb < E ? cnt[eb] : 0u;
+    uint32_t run = ca + cb, act = (ca != 0u) + (cb != 0u);
+    uint32_t inc = run, inca = act;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xFFFFFFFFu, inc, o), va = __shfl_up_sync(0xFFFFFFFFu, inca, o);
+        if (lane >= (uint32_t)o) { inc += v; inca += va; }
+    }
+    if (lane == 31u) { wtot[warp] = inc; wact[warp] = inca; }
+    __syncthreads();
+    uint32_t base = 0, basea = 0;
+    for (uint32_t w = 0; w < warp; ++w) { base += wtot[w]; basea += wact[w]; }
+    const uint32_t oa = base + inc - run, ra = basea + inca - act;      // exclusive prefixes at expert 2t
+    if (ea < E) {
+        counts[ea] = ca;
+        offsets[ea] = oa;
+        off[ea] = oa;
+        if (ca) active_list[ra] = ea;
+    }
+    if (eb < E) {
+        counts[eb] = cb;
+        offsets[eb] = oa + ca;
+        off[eb] = oa + ca;
+        if (cb) active_list[ra + (ca != 0u)] = eb;
+    }
+    if (tid == blockDim.x - 1u) {
+        offsets[E] = base + inc;
+        *n_active = basea + inca;
+    }
+    __syncthreads();
+    if (tid < P) {
+        const uint32_t e = ids_s[tid];
+        uint32_t r = 0;
+        for (uint32_t j = 0; j < tid; ++j) r += ids_s[j] == e ? 1u : 0u;
+        const uint32_t pos = off[e] + r;
+        perm[pos] = tid;
+        inv[tid] = pos;
+        perm_s[pos] = tid;
+    }
+    __syncthreads();
+    if (xg != nullptr)
+        for (uint32_t pos = warp; pos < P; pos += kFrontWarps)
+            warp_row_to_f16_bf16(x + (size_t)(perm_s[pos] / k) * H, H, xg + (size_t)pos * H, x_rowscale + pos);
+}
+
+// false: the shape is outside the kernel's limits and nothing was launched
+bool launch_front_small(const RouterParams& p, const float* logits, const float* bias, uint32_t T, uint32_t* ids,
+                        float* weights, uint32_t* counts, uint32_t* offsets, uint32_t* perm, uint32_t* inv,
+                        uint32_t* active_list, uint32_t* n_active, const __nv_bfloat16* x, uint32_t H, void* xg,
+                        float* x_rowscale, uint32_t* status, cudaStream_t s) {
+    if (T == 0 || T > kFrontWarps || T * p.top_k > kFrontMaxPairs || p.experts > kFrontMaxExperts || p.top_k > 32u)
+        return false;
+    if (xg != nullptr && (H % 8u || (((uintptr_t)x | (uintptr_t)xg) & 15u))) return false;
+    const size_t smem = ((size_t)kFrontWarps * 2u * p.experts + 2u * p.experts + 2u * kFrontMaxPairs) * sizeof(float);
+    if (smem > 200u * 1024u) return false;
+    static bool attr[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return false;
+    if (!attr[dev]) {
+        if (cudaFuncSetAttribute(front_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+            return false;
+        attr[dev] = true;
+    }
+    front_small_kernel<<<1, kFrontWarps * 32, smem, s>>>(p, logits, bias, T, ids, weights, counts, offsets, perm, inv,
+                                                         active_list, n_active, x, H, static_cast<__half*>(xg),
+                                                         x_rowscale, status);
+    ++g_kernel_launches;
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------
+// Inkling's sink router (src/models/inkling/inkling_ops.cpp:184-275), one warp per token.  logits [T, E + S]:
+// the routed experts followed by S shared "sink" experts.  Selection: top-k of sigmoid(logit) + bias over the routed
+// range, lower index on ties.  Weights: log-sigmoid (min(x, 0) - log1p(exp(-|x|)), src/platform/numerics.cpp:54-59)
+// of the RAW logits of the k selected experts and of every sink, softmax over that joint set (maximum subtracted,
+// sum in index order), times scale.  expf / log1pf follow the host libm step by step, so the weights are bit-exact.
+__global__ void __launch_bounds__(kRouteWarps * 32) route_sink_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, uint32_t T, uint32_t E, uint32_t S, uint32_t k,
+    float scale, uint32_t* __restrict__ ids, float* __restrict__ w_routed, float* __restrict__ w_sinks,
+    uint32_t* status) {
+    extern __shared__ float smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    float* choice = smem + (size_t)warp * E;
+    const uint32_t tok = blockIdx.x * kRouteWarps + warp;
+    if (tok >= T) return;
+    const float* lg = logits + (size_t)tok * (E + S);
+    bool bad = false;
+    for (uint32_t e = lane; e < E + S; e += 32u) bad |= !isfinite(lg[e]);
+    for (uint32_t e = lane; e < E; e += 32u) {
+        const float b = bias[e];
+        bad |= !isfinite(b);
+        choice[e] = __fadd_rn(sigmoid_two_branch(lg[e]), b);
+    }
+    __syncwarp();
+    uint32_t my_id = 0;
+    for (uint32_t r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        uint32_t bi = 0xFFFFFFFFu;
+        for (uint32_t e = lane; e < E; e += 32u) {
+            const float v = choice[e];
+            if (v > bv || bi == 0xFFFFFFFFu) { bv = v; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xFFFFFFFFu, bv, off);
+            const uint32_t oi = __shfl_xor_sync(0xFFFFFFFFu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (bi >= E) { bad = true; bi = 0; }
+        if (lane == r) my_id = bi;
+        if (lane == 0) choice[bi] = -INFINITY;
+        __syncwarp();
+    }
+    if (lane >= k && lane < k + S) my_id = E + (lane - k);
+    const bool mine = lane < k + S;
+    float lp = -INFINITY;
+    if (mine) {
+        const float v = lg[my_id];
+        lp = __fsub_rn(fminf(v, 0.0f), log1pf_libm(expf_libm(-fabsf(v))));
+    }
+    float mx = lp;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    const float ex = mine ? expf_libm(__fsub_rn(lp, mx)) : 0.0f;
+    float total = 0.0f;
+    for (uint32_t i = 0; i < k + S; ++i) total = __fadd_rn(total, __shfl_sync(0xFFFFFFFFu, ex, i));
+    float w = 0.0f;
+    if (!(total > 0.0f) || !isfinite(total)) {
+        if (lane == 0) atomicOr(status, kStatusBadNormaliser);
+    } else {
+        w = __fmul_rn(__fdiv_rn(ex, total), scale);
+    }
+    if (lane < k) {
+        ids[(size_t)tok * k + lane] = my_id;
+        w_routed[(size_t)tok * k + lane] = w;
+    } else if (mine) {
+        w_sinks[(size_t)tok * S + (lane - k)] = w;
+    }
+    if (__any_sync(0xFFFFFFFFu, bad) && lane == 0) atomicOr(status, kStatusNonFiniteLogit);
+}
+
+void launch_route_sink(const float* logits, const float* bias, uint32_t T, uint32_t E, uint32_t S, uint32_t k, float scale,
+                       uint32_t* ids, float* w_routed, float* w_sinks, uint32_t* status, cudaStream_t s) {
+    if (T == 0) return;
+    route_sink_kernel<<<(T + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, (size_t)kRouteWarps * E * sizeof(float), s>>>(
+        logits, bias, T, E, S, k, scale, ids, w_routed, w_sinks, status);
+    ++g_kernel_launches;
 }
 
 void launch_route(const RouterParams& p, const float* logits, const float* bias, uint32_t T,

@@ -266,6 +266,28 @@ def test_ring_and_register_streaming_kernels_agree(ctx, fmt, monkeypatch):
     assert rel <= 1e-5, rel        # same products, different FP32 summation order
 
 
+@pytest.mark.parametrize("T,E,k,kind", [(1, 128, 4, synth.SCORE_SIGMOID), (8, 256, 6, synth.SCORE_SQRTSOFTPLUS),
+                                        (16, 64, 8, synth.SCORE_SIGMOID), (13, 896, 16, synth.SCORE_SIGMOID_PLAIN)])
+def test_decode_front_end_matches_separate_kernels(ctx, T, E, k, kind, monkeypatch):
+    """At most 16 tokens: the whole-row logits kernel and the fused route + group + convert kernel against the staged
+    logits kernel and the separate route / group / convert kernels: every routing and grouping output and the layer
+    output bit for bit (the arithmetic is the same, only the launches differ)."""
+    cfg = small(synth.FMT_MXFP4, T=T, E=E, k=k, H=512, I=512, score_kind=kind, zipf_s=0.7, name=f"front{T}_{E}_{k}")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    monkeypatch.setenv("STRATA_MOE_NO_SMALL_FRONT", "1")
+    ml2 = MoeLayer(ctx, cfg, max_tokens=T)
+    ml2.load_synth(layer)
+    out2, aux2 = ml2.forward(layer.x, want_aux=True)
+    ctx.synchronize()
+    for key in ("logits", "ids", "weights", "counts", "offsets", "perm"):
+        a, b = aux[key].cpu().numpy(), aux2[key].cpu().numpy()
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32)), key
+    assert torch.equal(out, out2)
+    ref = Hh.run_oracle(cfg, layer.x.cpu())
+    assert np.array_equal(aux["logits"].cpu().numpy().view(np.uint32), ref["logits"].view(np.uint32))
+    assert np.array_equal(aux["perm"].cpu().numpy().astype(np.uint32), ref["perm"])
+
+
 def test_ring_kernels_with_sixteen_row_token_tiles(ctx, monkeypatch):
     # by default the ring kernels only take batches whose groups fit an 8-row tile; their 16-row variant on request
     monkeypatch.setenv("STRATA_MOE_STREAM_RING_MAX_ROWS", "16")
@@ -342,6 +364,32 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
         touched = int(((ids_x == 3) | (ids_x == 77)).any(dim=1).sum().item())
         assert touched > 0
     assert rechecked <= cfg.T // 50
+
+
+@pytest.mark.parametrize("T,E,S,k", [(5, 256, 2, 6), (300, 128, 1, 8), (33, 64, 0, 4)])
+def test_inkling_sink_router(ctx, T, E, S, k):
+    """Gate projection over routed + sink rows and the sink router against the oracle (which is pinned bit for bit to
+    the compiled inkling_route_sigmoid_sink): logits, ids and every weight bit-exact; one forced exact tie."""
+    H = 512
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E + S, H, generator=g) * 0.08).to(torch.bfloat16)
+    w[11] = w[2]                                            # twins: identical logits for every token
+    bias = (torch.randn(E, generator=g) * 0.05).float()
+    bias[11] = bias[2]
+    scale = float(np.float32(2.5) * np.float32(0.75))
+    logits = ctx.project_rows(x.cuda(), w.cuda())
+    ids, wr, ws = ctx.route_sink(logits, bias.cuda(), E, S, k, scale)
+    ctx.synchronize()
+    ref_logits = O.router_logits(Hh.np_u16(x), Hh.np_u16(w))
+    assert np.array_equal(logits.cpu().numpy().view(np.uint32), ref_logits.view(np.uint32))
+    rc, rids, rw = O.route_sigmoid_sink(ref_logits, bias.numpy(), E, S, k, np.float32(scale))
+    assert rc == 0
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32), rids[:, :k])
+    assert np.array_equal(wr.cpu().numpy().view(np.uint32), rw[:, :k].view(np.uint32))
+    if S:
+        assert np.array_equal(ws.cpu().numpy().view(np.uint32), np.ascontiguousarray(rw[:, k:]).view(np.uint32))
+    assert ((rids[:, :k] == 2).any(axis=1) >= (rids[:, :k] == 11).any(axis=1)).all()   # the lower twin goes first
 
 
 @pytest.mark.parametrize("kind", [synth.SCORE_SIGMOID, synth.SCORE_SQRTSOFTPLUS])

@@ -200,3 +200,29 @@ def test_hash_route_matches_reference_bitwise():
     bad = np.array([0, 1, 2, 3, 4, E], np.uint32)
     assert port.orc_route_given_row(C.byref(spec), logits.ctypes.data_as(f32p), bad.ctypes.data_as(u32p),
                                     ids_a.ctypes.data_as(u32p), w_a.ctypes.data_as(f32p)) == -3
+
+
+def test_inkling_sink_router_matches_reference():
+    """orc_route_sigmoid_sink against the compiled inkling_route_sigmoid_sink (src/models/inkling/inkling_ops.cpp:184-275):
+    ids and weights bit for bit, with ties and strongly negative logits (the log-sigmoid branch that must not underflow)."""
+    ref = O.ref()
+    rng = np.random.default_rng(7)
+    E, S, k = 256, 2, 6
+    for trial in range(200):
+        logits = (rng.standard_normal(E + S) * rng.choice([0.5, 3.0, 30.0])).astype(np.float32)
+        if trial % 5 == 0:
+            logits[17] = logits[3]                      # an exact tie: the lower index must win
+        bias = (rng.standard_normal(E) * 0.1).astype(np.float32)
+        if trial % 5 == 0:
+            bias[17] = bias[3]
+        rc, ids, w = O.route_sigmoid_sink(logits[None, :], bias, E, S, k, np.float32(2.5 * 0.75))
+        assert rc == 0
+        rids = np.empty(k + S, np.uint32)
+        rw = np.empty(k + S, np.float32)
+        f32p, u32p = C.POINTER(C.c_float), C.POINTER(C.c_uint32)
+        rrc = ref.ref_inkling_route_sink(logits.ctypes.data_as(f32p), bias.ctypes.data_as(f32p), E, S, k,
+                                         C.c_float(2.5), C.c_float(0.75), rids.ctypes.data_as(u32p),
+                                         rw.ctypes.data_as(f32p))
+        assert rrc == 0
+        assert np.array_equal(ids[0], rids)
+        assert np.array_equal(w[0].view(np.uint32), rw.view(np.uint32)), (trial, w[0], rw)
