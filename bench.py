@@ -455,7 +455,18 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
     x_local = layer.x[rank * Tl:(rank + 1) * Tl].contiguous()
     ml = MoeLayer(ctx, cfg, max_tokens=Tl, expert_begin=rank * B, expert_count=B, max_pairs=max_pairs)
     ml.load_synth(layer)
-    if args.exchange == "peer":
+    parts = max(1, int(getattr(args, "microbatches", 1)))
+    if args.exchange == "peer" and parts > 1 and Tl >= 2 * parts:
+        from strata_b200.ep import EpMoePeerPipelined
+
+        def make_layer(c, n, cap):
+            m = MoeLayer(c, cfg, max_tokens=n, expert_begin=rank * B, expert_count=B, max_pairs=cap)
+            m.load_synth(layer)
+            return m
+        ep = EpMoePeerPipelined(make_layer, cfg, rank, world, Tl, max_pairs, parts=parts)
+        exchange_text = (f"library kernels over peer memory (NVLink stores / loads, no collective on the data path), "
+                         f"{parts} token micro-batches in flight")
+    elif args.exchange == "peer":
         try:
             ep = EpMoePeer(ml, cfg, rank, world, max_pairs)
             exchange_text = "library kernels over peer memory (NVLink stores / loads, no collective on the data path)"
@@ -491,6 +502,8 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
     per_rank_ms = [torch.zeros(1, device=device, dtype=torch.float64) for _ in range(world)]
     dist.all_gather(per_rank_ms, ms_local.mean().reshape(1))
     ctx.synchronize()    # raises if any step tripped the device status word (overflow, timeout, non-finite)
+    if hasattr(ep, "synchronize"):
+        ep.synchronize()
     ids_loc, _ = ml.route(x_local)
     per_rank = torch.bincount((ids_loc.reshape(-1) // B).long(), minlength=world).double()
     dist.all_reduce(per_rank)     # rows every rank receives in one step
@@ -593,7 +606,7 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
     }
     if parity is not None:
         rec["parity"] = parity
-    if isinstance(ep, EpMoePeer):
+    if hasattr(ep, "close"):
         ep.close()
     ml.close()
     del layer, ml, ep
@@ -661,6 +674,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-sub", dest="sub", action="store_false", help="skip the sub-records of the other configurations")
     ap.add_argument("--no-parity", dest="parity", action="store_false", help="skip the oracle check of the timed layer")
+    ap.add_argument("--microbatches", type=int, default=1,
+                    help="multi-GPU, peer exchange: token micro-batches in flight per step (each on its own stream)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="multi-GPU row exchange: the library's peer-memory kernels or NCCL all-to-allv")
     ap.add_argument("--scaling", default=None, choices=["weak", "strong"],

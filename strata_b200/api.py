@@ -594,12 +594,15 @@ class EpState:
         self.ctx.leave()
         return out
 
-    def forward(self, x, out=None, expected_rows=0):
+    def forward(self, x, out=None, expected_rows=0, join=True):
+        """join=False leaves the caller's stream un-ordered against this step (the caller joins later with
+        ctx.leave()): several steps on different contexts can then be in flight together."""
         if out is None:
             out = torch.empty(x.shape[0], self.layer.cfg.H, dtype=torch.float32, device=x.device)
         self.ctx.enter()
         self.ctx.check(self.lib.strata_moe_ep_forward(self.h, _ptr(x), x.shape[0], _ptr(out), expected_rows))
-        self.ctx.leave()
+        if join:
+            self.ctx.leave()
         return out
 
     def abandon(self):

@@ -509,23 +509,30 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         // the ring kernels win while a group fits one 8-row token tile (measured: 8 tokens of c0 99 us against 114 us;
         // 256 tokens of c1, 16-row tiles and several passes per group: 419 us against 339 us)
         const bool ring = L->stream_ok && a.max_rows_per_group <= (uint32_t)L->knobs.stream_ring_max_rows;
-        launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        if (!x_ready) launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
         mark(ctx, 4);
+        // ring kernels, no group handed to the tensor-core path: the gate/up epilogue writes the down kernel's f16
+        // operand itself and the separate conversion pass is skipped
+        const bool act_direct = ring && !big && !down_all_tensor;
+        a.act_direct = act_direct ? 1u : 0u;
+        a.act_rowscale_out = L->act_rowscale;
         if (ring) {
             if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
-        launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
-                               L->act_rowscale, s, pairs_dev);
+        if (!big) mark(ctx, 5);     // the gate/up phase is the kernel alone; the f16 split below belongs to the down phase
+        if (!act_direct)
+            launch_rows_to_f16_f32(L->act_f32, 0, bound, L->d.intermediate, L->act_hi, L->act_lo,
+                                   L->act_rowscale, s, pairs_dev);
         if (big) {   // after the conversion above: these rows' f16 activations and unit row factors overwrite it
             p.min_rows = big;
             p.ntile = 128;   // measured at the c4 shape: 407 us with 128-token tiles, 439 us with 192
             p.act_rowscale_out = L->act_rowscale;
             if (launch_prefill_gate_up(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s) != 0)
                 return fail(ctx, STRATA_MOE_E_CUDA, "prefill gate/up launch failed");
+            mark(ctx, 5);
         }
-        mark(ctx, 5);
         // Medium batches: the down projection (short K, many output tiles) is faster on the tensor-core
         // path from about 8 rows per expert, the gate/up projection only from about 12.
         p.act_rowscale_out = nullptr;
@@ -2270,6 +2277,9 @@ int strata_moe_ep_finish(strata_moe_ep* ep, float* out) {
         CK(cudaStreamWaitEvent(s, ctx->ev_join, 0));
         shared = L->sh_y;
     }
+    // one CTA waits for the peers' results; the combine kernel's own check then passes at once, so its CTAs never sit
+    // on SMs spinning (a second step in flight on another stream may need them for its GEMMs)
+    launch_ep_wait(ep->w, 2, ep->abort_word, ctx->d_status, s);
     launch_ep_combine(ep->w, L->ids, L->inv, L->offsets, ep->dst_row, L->weights, shared, ep->T, L->d.top_k,
                       L->d.output_scale, out, ep->abort_word, ctx->d_status, s);
     CK(cudaGetLastError());

@@ -106,6 +106,8 @@ struct DecodeArgs {
     float* act_f32;                // [pairs, I] SwiGLU output before its f16 split
     const float* act_rowscale;     // [pairs]
     uint32_t x_rows;               // decode_stream.cu: rows allocated in x_hi / act_hi / act_lo (bounds of the row boxes)
+    uint32_t act_direct;           // decode_stream.cu gate/up: write act_hi / act_lo (f16 hi + lo) and unit row factors, not act_f32
+    float* act_rowscale_out;       // [pairs], written when act_direct
 };
 void launch_decode_fp4_gate_up(const DecodeArgs& a, cudaStream_t s);
 void launch_decode_fp4_down(const DecodeArgs& a, cudaStream_t s);

@@ -35,6 +35,7 @@
 // Replaces the reference's per-row NVFP4 / DeepSeek FP4 expert kernels for decode batches
 // (kernels/cuda/backend.cu:1978-2069, 2308-2413).
 #include <cuda.h>
+#include <cuda_fp16.h>
 
 #include "stream_ring.cuh"
 
@@ -442,8 +443,18 @@ __global__ void __launch_bounds__(kSThreads, 1) decode_stream_kernel(DecodeArgs 
                         const float gv = v0 * s0 * rs, uv = v1 * s1 * rs;
                         float v = a.glu.kind == STRATA_MOE_ACT_SWIGLU ? silu_mul_s(gv, uv) : glu_other(gv, uv, a.glu);
                         if (a.coef) v *= a.coef[pos];
-                        if (!(fabsf(v) <= 3.0e38f)) bad = true;
-                        a.act_f32[pos * R + orow] = v;
+                        if (a.act_direct) {
+                            // f16 hi + lo straight from the epilogue (unit row factor): the down kernel's operand
+                            // without a conversion pass; a value beyond the f16 range is reported, not clipped
+                            if (!(fabsf(v) <= 65504.0f)) bad = true;
+                            const __half h = __float2half_rn(v);
+                            reinterpret_cast<__half*>(a.act_hi)[pos * R + orow] = h;
+                            reinterpret_cast<__half*>(a.act_lo)[pos * R + orow] = __float2half_rn(v - __half2float(h));
+                            if (orow == 0u) a.act_rowscale_out[pos] = 1.0f;
+                        } else {
+                            if (!(fabsf(v) <= 3.0e38f)) bad = true;
+                            a.act_f32[pos * R + orow] = v;
+                        }
                     } else {
                         const uint32_t orow = j.us * 32u + r16;
                         const float y0 = v0 * s0 * rs, y1 = v1 * s1 * rs;

@@ -337,16 +337,42 @@ void launch_router_logits(const __nv_bfloat16* x, const __nv_bfloat16* wg, uint3
 }
 
 // Scores, top-k and routing weights of ONE token by one warp.  score / choice: [E] floats of shared memory each.
+// Scores and selection values of the experts first, first + step, ... of one token (every rule but softmax, whose
+// normaliser needs the whole row).  Returns true when a logit or bias is not finite.
+__device__ __forceinline__ bool route_scores_part(const RouterParams& p, const float* __restrict__ lg,
+                                                  const float* __restrict__ bias, float* score, float* choice,
+                                                  uint32_t first, uint32_t step) {
+    bool bad = false;
+    for (uint32_t e = first; e < p.experts; e += step) {
+        float l = lg[e];
+        bad |= !isfinite(l);
+        if (p.softcap > 0.0f) l = __fmul_rn(tanhf(__fdiv_rn(l, p.softcap)), p.softcap);
+        float sc;
+        if (p.score_kind == STRATA_MOE_SCORE_SIGMOID) sc = sigmoid_two_branch(l);
+        else if (p.score_kind == STRATA_MOE_SCORE_SIGMOID_PLAIN)
+            sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
+        else sc = sqrtf(l > 20.0f ? l : log1pf_libm(expf_libm(l)));
+        const float b = bias ? bias[e] : 0.0f;
+        bad |= !isfinite(b);
+        score[e] = sc;
+        choice[e] = __fadd_rn(sc, b);
+    }
+    return bad;
+}
+
+// scores_ready: score / choice were filled by route_scores_part (bad_in = its verdict); else they are computed here.
 __device__ __forceinline__ void route_token(const RouterParams& p, const float* __restrict__ logits,
                                             const float* __restrict__ bias, uint32_t tok, float* score, float* choice,
                                             uint32_t* __restrict__ ids, float* __restrict__ weights, uint32_t* status,
-                                            const uint32_t* __restrict__ forced_ids) {
+                                            const uint32_t* __restrict__ forced_ids, bool scores_ready = false,
+                                            bool bad_in = false) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
     const float* lg = logits + (size_t)tok * E;
-    bool bad = false;
+    bool bad = bad_in;
 
-    if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) {
+    if (scores_ready) {
+    } else if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) {
         float mx = -INFINITY;
         for (uint32_t e = lane; e < E; e += 32u) {
             const float l = lg[e];
@@ -363,23 +389,14 @@ __device__ __forceinline__ void route_token(const RouterParams& p, const float* 
         sum = __shfl_sync(0xFFFFFFFFu, sum, 0);
         for (uint32_t e = lane; e < E; e += 32u) score[e] = __fdiv_rn(score[e], sum);
     } else {
+        bad |= route_scores_part(p, lg, bias, score, choice, lane, 32u);
+    }
+    if (!scores_ready && p.score_kind == STRATA_MOE_SCORE_SOFTMAX)
         for (uint32_t e = lane; e < E; e += 32u) {
-            float l = lg[e];
-            bad |= !isfinite(l);
-            if (p.softcap > 0.0f) l = __fmul_rn(tanhf(__fdiv_rn(l, p.softcap)), p.softcap);
-            float sc;
-            if (p.score_kind == STRATA_MOE_SCORE_SIGMOID) sc = sigmoid_two_branch(l);
-            else if (p.score_kind == STRATA_MOE_SCORE_SIGMOID_PLAIN)
-                sc = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf_libm(-l)));
-            else sc = sqrtf(l > 20.0f ? l : log1pf_libm(expf_libm(l)));
-            score[e] = sc;
+            const float b = bias ? bias[e] : 0.0f;
+            bad |= !isfinite(b);
+            choice[e] = __fadd_rn(score[e], b);
         }
-    }
-    for (uint32_t e = lane; e < E; e += 32u) {
-        const float b = bias ? bias[e] : 0.0f;
-        bad |= !isfinite(b);
-        choice[e] = __fadd_rn(score[e], b);
-    }
     __syncwarp();
 
     // k rounds of arg-max over (value desc, index asc); taken entries drop to -inf.
@@ -711,7 +728,7 @@ constexpr uint32_t kSmallPad = 64;        // bytes added to the row pitch: two n
 
 __global__ void __launch_bounds__(kSmallMaxTokens * 32) router_logits_small_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wg, uint32_t T, uint32_t H, uint32_t E,
-    float* __restrict__ logits, uint32_t* status) {
+    float* __restrict__ logits, uint32_t* status, uint32_t tokens_per_cta) {
     extern __shared__ __align__(128) uint8_t small_smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(small_smem);     // [4]
     uint8_t* rows = small_smem + 128;
@@ -744,30 +761,54 @@ __global__ void __launch_bounds__(kSmallMaxTokens * 32) router_logits_small_kern
             }
     }
     bool ok = true;
-    if (warp < T) {
+    const uint32_t tok = blockIdx.y * tokens_per_cta + warp;
+    if (warp < tokens_per_cta && tok < T) {
+        // the whole token row is requested into L2 now: the register batches below then never wait on HBM (every CTA
+        // reads the same T rows; without this each batch of four lines was a fresh miss for all CTAs at once)
+        if (lane == 0)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(x + (size_t)tok * H), "r"(H * 2u) : "memory");
         const uint32_t grp = lane >> 2, sub = lane & 3u;
         const uint32_t row = grp < nrows ? grp : nrows - 1u;
         const uint32_t wrow = ring::smem_addr(rows + (size_t)row * pitch) + sub * 16u;
-        const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)warp * H) + sub;
+        const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)tok * H) + sub;
         float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        for (uint32_t q = 0; q < 4u && ok; ++q) {
-            const uint32_t j0 = per_lane * q / 4u, j1 = per_lane * (q + 1u) / 4u;
-            uint32_t j = j0;
-            uint4 xv[8];
-            const uint32_t first = min(8u, j1 - j0);
-            for (uint32_t i = 0; i < 8u; ++i)      // the token's columns of this quarter start before the wait
-                if (i < first) xv[i] = ldg128_ordered(xrow + (size_t)(j0 + i) * 4u);
-            ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait(&bars[q], 0u, &abort_flag));
-            if (!ok) break;
-            for (; j + 8u <= j1; j += 8u) {
+        // the token's row comes from global memory in batches of eight 16-byte loads, two batches in flight: the next
+        // batch is requested before the arithmetic on the current one
+        uint4 xa[8], xb[8];
+        auto fetch = [&](uint4 (&buf)[8], uint32_t j) {
 #pragma unroll
-                for (uint32_t i = 0; i < 8u; ++i) chain_fma8(c, xv[i], ring::lds128(wrow + (j + i) * 64u));
-                const uint32_t nxt = j + 8u;
+            for (uint32_t i = 0; i < 8u; ++i)
+                if (j + i < per_lane) buf[i] = ldg128_ordered(xrow + (size_t)(j + i) * 4u);
+        };
+        auto consume = [&](const uint4 (&buf)[8], uint32_t j, uint32_t jend) {
 #pragma unroll
-                for (uint32_t i = 0; i < 8u; ++i)
-                    if (nxt + i < j1) xv[i] = ldg128_ordered(xrow + (size_t)(nxt + i) * 4u);
+            for (uint32_t i = 0; i < 8u; ++i)
+                if (j + i < jend) chain_fma8(c, buf[i], ring::lds128(wrow + (j + i) * 64u));
+        };
+        fetch(xa, 0u);
+        fetch(xb, 8u);
+        uint32_t q = 0, jq = per_lane / 4u;          // quarter being consumed and its end step
+        ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait_poll(&bars[0], 0u, &abort_flag));
+        for (uint32_t j = 0; j < per_lane && ok; j += 16u) {
+            // steps [j, j + 8) from xa, [j + 8, j + 16) from xb; a batch may straddle a quarter boundary
+            for (uint32_t half = 0; half < 2u && ok; ++half) {
+                const uint32_t jb = j + half * 8u;
+                if (jb >= per_lane) break;
+                const uint32_t je = min(jb + 8u, per_lane);
+                while (ok && q < 3u && je > jq) {      // the batch reaches into the next quarter: wait for it too
+                    ++q;
+                    jq = per_lane * (q + 1u) / 4u;
+                    ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait_poll(&bars[q], 0u, &abort_flag));
+                }
+                if (!ok) break;
+                if (half == 0u) {
+                    consume(xa, jb, je);
+                    fetch(xa, jb + 16u);
+                } else {
+                    consume(xb, jb, je);
+                    fetch(xb, jb + 16u);
+                }
             }
-            for (uint32_t i = 0; j < j1; ++j, ++i) chain_fma8(c, xv[i], ring::lds128(wrow + j * 64u));
         }
         if (ok) {
 #pragma unroll
@@ -779,7 +820,7 @@ __global__ void __launch_bounds__(kSmallMaxTokens * 32) router_logits_small_kern
             c[0] = __fadd_rn(c[0], c[2]);
             c[1] = __fadd_rn(c[1], c[3]);
             c[0] = __fadd_rn(c[0], c[1]);
-            if (sub == 0u && grp < nrows) logits[(size_t)warp * E + e0 + grp] = c[0];
+            if (sub == 0u && grp < nrows) logits[(size_t)tok * E + e0 + grp] = c[0];
         }
     }
     if (!ok && lane == 0) { abort_flag = 1; atomicOr(status, kStatusWaitTimeout); }
@@ -807,8 +848,15 @@ bool launch_router_logits_small(const __nv_bfloat16* x, const __nv_bfloat16* wg,
             return false;
         attr[dev] = true;
     }
-    const uint32_t warps = T < 4u ? 4u : T;      // warp 0 also issues the copies
-    router_logits_small_kernel<<<(E + kSmallRows - 1) / kSmallRows, warps * 32u, smem, s>>>(x, wg, T, H, E, logits, status);
+    // two tokens per CTA while that keeps the grid within two CTAs per SM: more SMs stream and decode (a CTA whose
+    // rows another CTA already fetched reads them from L2)
+    const uint32_t row_groups = (E + kSmallRows - 1) / kSmallRows;
+    uint32_t tpc = 2u;
+    while (tpc < T && row_groups * ((T + tpc - 1u) / tpc) > 2u * (uint32_t)kNumSMs) tpc *= 2u;
+    if (tpc > T) tpc = T;
+    const uint32_t warps = tpc < 4u ? 4u : tpc;      // warp 0 also issues the copies
+    dim3 grid(row_groups, (T + tpc - 1u) / tpc);
+    router_logits_small_kernel<<<grid, warps * 32u, smem, s>>>(x, wg, T, H, E, logits, status, tpc);
     ++g_kernel_launches;
     return true;
 }
@@ -868,16 +916,28 @@ __global__ void __launch_bounds__(kFrontWarps * 32) front_small_kernel(
     extern __shared__ float fsm2[];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t E = p.experts, k = p.top_k, P = T * k;
-    float* score = fsm2 + (size_t)warp * 2u * E;
-    float* choice = score + E;
     uint32_t* cnt = reinterpret_cast<uint32_t*>(fsm2 + (size_t)kFrontWarps * 2u * E);   // [E]
     uint32_t* off = cnt + E;                                                            // [E]
     uint32_t* ids_s = off + E;                                                          // [P]
     uint32_t* perm_s = ids_s + kFrontMaxPairs;                                          // [P]
-    __shared__ uint32_t wtot[kFrontWarps], wact[kFrontWarps];
+    __shared__ uint32_t wtot[kFrontWarps], wact[kFrontWarps], bad_s[kFrontWarps];
     for (uint32_t e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+    if (tid < kFrontWarps) bad_s[tid] = 0;
+    // scores: the exact exp / log1p replicas are the long part of routing a token, so all 16 warps share them
+    // (16 / T warps per token, each a strided subset of the experts); the softmax rule keeps one warp per token
+    const bool coop = p.score_kind != STRATA_MOE_SCORE_SOFTMAX;
+    const uint32_t nsub = kFrontWarps / T;
+    __syncthreads();
+    if (coop && warp < T * nsub) {
+        const uint32_t tok = warp % T, part = warp / T;
+        float* sc = fsm2 + (size_t)tok * 2u * E;
+        if (route_scores_part(p, logits + (size_t)tok * E, bias, sc, sc + E, part * 32u + lane, 32u * nsub))
+            bad_s[tok] = 1u;
+    }
+    __syncthreads();
     if (warp < T) {
-        route_token(p, logits, bias, warp, score, choice, ids, weights, status, nullptr);
+        float* score = fsm2 + (size_t)warp * 2u * E;
+        route_token(p, logits, bias, warp, score, score + E, ids, weights, status, nullptr, coop, bad_s[warp] != 0u);
         if (lane < k) ids_s[warp * k + lane] = ids[(size_t)warp * k + lane];    // this lane's own store
     }
     __syncthreads();

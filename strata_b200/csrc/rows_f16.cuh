@@ -8,18 +8,58 @@
 
 namespace smoe {
 
+__device__ __forceinline__ float absmax8_bf16(const uint4& v, float mx) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        mx = fmaxf(mx, fabsf(__uint_as_float(w[q] << 16)));
+        mx = fmaxf(mx, fabsf(__uint_as_float(w[q] & 0xFFFF0000u)));
+    }
+    return mx;
+}
+
+__device__ __forceinline__ uint4 scale8_bf16_to_f16(const uint4& v, float sc) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const __half a = __float2half_rn(__uint_as_float(w[q] << 16) * sc);
+        const __half b = __float2half_rn(__uint_as_float(w[q] & 0xFFFF0000u) * sc);
+        o[q] = (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Rows of up to 4096 columns are read ONCE: the lane keeps its sixteen 16-byte pieces in registers between the
+// maximum and the conversion, and all sixteen loads are in flight together (a warp that converts several rows in
+// turn is otherwise bound by one memory round trip per piece).  Longer rows take two passes in batches of eight loads.
 __device__ __forceinline__ void warp_row_to_f16_bf16(const __nv_bfloat16* __restrict__ src, uint32_t C,
                                                      __half* __restrict__ hi, float* __restrict__ rowscale) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint4* p = reinterpret_cast<const uint4*>(src);
+    uint4* out = reinterpret_cast<uint4*>(hi);
+    const uint32_t n = C / 8u;
+    const bool once = n <= 16u * 32u;
+    uint4 keep[16];
     float mx = 0.0f;
-    for (uint32_t i = lane; i < C / 8u; i += 32u) {
-        const uint4 v = __ldg(p + i);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    if (once) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            mx = fmaxf(mx, fabsf(__uint_as_float(w[q] << 16)));
-            mx = fmaxf(mx, fabsf(__uint_as_float(w[q] & 0xFFFF0000u)));
+        for (uint32_t q = 0; q < 16u; ++q) {
+            const uint32_t i = lane + 32u * q;
+            keep[q] = i < n ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 16u; ++q) mx = absmax8_bf16(keep[q], mx);
+    } else {
+        for (uint32_t base = 0; base < n; base += 256u) {
+            uint4 v[8];
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) {
+                const uint32_t i = base + lane + 32u * q;
+                v[q] = i < n ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) mx = absmax8_bf16(v[q], mx);
         }
     }
 #pragma unroll
@@ -29,17 +69,26 @@ __device__ __forceinline__ void warp_row_to_f16_bf16(const __nv_bfloat16* __rest
     ex = max(-100, min(100, ex));
     const float sc = __uint_as_float((uint32_t)(ex + 127) << 23);
     if (lane == 0) *rowscale = __uint_as_float((uint32_t)(127 - ex) << 23);
-    for (uint32_t i = lane; i < C / 8u; i += 32u) {
-        const uint4 v = __ldg(p + i);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-        uint32_t o[4];
+    if (once) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const __half a = __float2half_rn(__uint_as_float(w[q] << 16) * sc);
-            const __half b = __float2half_rn(__uint_as_float(w[q] & 0xFFFF0000u) * sc);
-            o[q] = (uint32_t)__half_as_ushort(a) | ((uint32_t)__half_as_ushort(b) << 16);
+        for (uint32_t q = 0; q < 16u; ++q) {
+            const uint32_t i = lane + 32u * q;
+            if (i < n) out[i] = scale8_bf16_to_f16(keep[q], sc);
         }
-        *reinterpret_cast<uint4*>(hi + i * 8u) = make_uint4(o[0], o[1], o[2], o[3]);
+    } else {
+        for (uint32_t base = 0; base < n; base += 256u) {
+            uint4 v[8];
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) {
+                const uint32_t i = base + lane + 32u * q;
+                v[q] = i < n ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) {
+                const uint32_t i = base + lane + 32u * q;
+                if (i < n) out[i] = scale8_bf16_to_f16(v[q], sc);
+            }
+        }
     }
 }
 

@@ -41,6 +41,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     }
     return false;
 }
+// The same wait by plain polling (no suspend hint): for latency-critical kernels whose whole run is a few
+// microseconds -- a parked thread was seen to resume microseconds after its barrier completed.
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity, const volatile uint32_t* abort_flag) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t spin = 0; spin < (1u << 24); ++spin) {
+        uint32_t done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(done)
+                     : "r"(addr), "r"(parity)
+                     : "memory");
+        if (done) return true;
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    return false;
+}
 // One poll, no suspend: used to drain copies still in flight when a CTA gives up.
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t done;

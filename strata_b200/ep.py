@@ -124,8 +124,8 @@ class EpMoePeer:
         if int(ok.item()) == 0:
             raise RuntimeError(f"peer-memory exchange unavailable: {err or 'a peer failed to map the windows'}")
 
-    def forward(self, x, out=None, expected_rows=0):
-        return self.state.forward(x, out, expected_rows)
+    def forward(self, x, out=None, expected_rows=0, join=True):
+        return self.state.forward(x, out, expected_rows, join)
 
     def close(self):
         self.state.close()
@@ -134,3 +134,44 @@ class EpMoePeer:
                 w.close()
         dist.barrier()
         self.own.close()
+
+
+class EpMoePeerPipelined:
+    """A step cut into token micro-batches that are in flight together: each part has its own context (stream and
+    workspaces), its own layer object over the SAME weights (borrowed in place) and its own windows, so the dispatch
+    and combine kernels of one part (NVLink copies, a few CTAs' worth of work) run while the expert GEMMs of the other
+    occupy the tensor cores.  Results are identical to the one-part step: tokens are independent.
+
+    make_layer(ctx, max_tokens, max_pairs) -> MoeLayer with the rank's weights registered."""
+
+    def __init__(self, make_layer, cfg, rank, world, tokens, row_capacity, parts=2, group=None, wait_ms=0):
+        from .api import MoeContext
+        self.cfg, self.parts = cfg, []
+        dev = torch.cuda.current_device()
+        bounds = [tokens * i // parts for i in range(parts + 1)]
+        for i in range(parts):
+            n = bounds[i + 1] - bounds[i]
+            cap = max(1, (row_capacity * n + tokens - 1) // tokens + 1024)
+            ctx = MoeContext(dev)
+            layer = make_layer(ctx, n, cap)
+            self.parts.append((bounds[i], bounds[i + 1], ctx, layer, EpMoePeer(layer, cfg, rank, world, cap, group, wait_ms)))
+
+    def forward(self, x, out=None):
+        if out is None:
+            out = torch.empty(x.shape[0], self.cfg.H, dtype=torch.float32, device=x.device)
+        for a, b, ctx, layer, ep in self.parts:
+            ep.forward(x[a:b], out[a:b], join=False)
+        for a, b, ctx, layer, ep in self.parts:
+            ctx.leave()
+        return out
+
+    def synchronize(self):
+        for a, b, ctx, layer, ep in self.parts:
+            ctx.synchronize()
+
+    def kernel_launches(self):
+        return sum(ctx.stats().kernel_launches for a, b, ctx, layer, ep in self.parts)
+
+    def close(self):
+        for a, b, ctx, layer, ep in self.parts:
+            ep.close()
