@@ -186,6 +186,12 @@ int strata_moe_forward_routed(strata_moe_layer* layer, const void* x_bf16, uint3
 int strata_moe_forward_host(strata_moe_layer* layer, const void* x_bf16_host, uint32_t tokens,
                             float* out_host);
 
+/* Diagnostics: FNV-1a hash of n fp32 values (device memory) after round-to-nearest-even to BF16, the reference's
+ * per-layer state hash ("[state]" lines, src/models/glm52/glm_runtime.cpp:1592-1598).  Waits for the context's
+ * stream, copies the values to the host and hashes them there.
+ * ref: stable_bf16_hash, include/strata/diagnostics.hpp:38-41, src/platform/diagnostics.cpp:84-88. */
+int strata_moe_stable_bf16_hash(strata_moe_ctx* ctx, const float* values, size_t n, uint64_t* hash);
+
 /* ---- stages (used by the expert-parallel driver and by the parity tests) ---------------- */
 /* ref: linear(gate) + glm_route_logits_noaux_tc / laguna_route_sigmoid_topk / kimi_route_topk /
  * dsv4_route_sqrtsoftplus_f32 (src/models/glm52/glm_ops.cpp:176-233, src/models/laguna/

@@ -24,6 +24,7 @@ REF_SOURCES = [
     "kernels/cpu/dsv4_fp4_expert.cpp",
     "kernels/cpu/glm_int4.cpp",
     "src/platform/numerics.cpp",
+    "src/platform/diagnostics.cpp",
     "src/platform/compressed_tensors.cpp",
     "src/platform/worker_pool.cpp",
     "src/platform/numa_topology.cpp",

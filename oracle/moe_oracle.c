@@ -53,6 +53,21 @@ ORC_API uint16_t orc_f32_to_bf16(float f) {
     return (uint16_t)(b >> 16);
 }
 
+/* stable_bf16_hash (src/platform/diagnostics.cpp:14-27, 84-88): FNV-1a over the little-endian bytes of every
+ * value after round-to-nearest-even to BF16; values whose exponent field is all ones (infinities, NaNs) are
+ * truncated, not rounded. */
+ORC_API uint64_t orc_stable_bf16_hash(const float* values, size_t n) {
+    uint64_t h = 14695981039346656037ull;
+    for (size_t i = 0; i < n; ++i) {
+        uint32_t b = f32_bits(values[i]);
+        if ((b & 0x7F800000u) != 0x7F800000u) b += 0x7FFFu + ((b >> 16) & 1u);
+        const uint32_t v = b >> 16;
+        h = (h ^ (v & 0xFFu)) * 1099511628211ull;
+        h = (h ^ (v >> 8)) * 1099511628211ull;
+    }
+    return h;
+}
+
 /* E2M1 value table.  CPU tables in the reference give -0.0 for nibble 0x8
  * (src/platform/numerics.cpp:75-83, include/strata/compressed_tensors.hpp:52-54);
  * the device decoder gives +0.0 (kernels/cuda/backend.cu:194-210, pinned by

@@ -227,6 +227,14 @@ def route(spec, logits, bias=None):
     return rc, ids, w
 
 
+def stable_bf16_hash(values):
+    values = np.ascontiguousarray(values, np.float32)
+    lib = port()
+    lib.orc_stable_bf16_hash.restype = C.c_uint64
+    lib.orc_stable_bf16_hash.argtypes = [f32p, C.c_size_t]
+    return int(lib.orc_stable_bf16_hash(_p(values, f32p), values.size))
+
+
 def route_sigmoid_sink(logits, bias, experts, sinks, top_k, scale):
     """Inkling's sink router over logits [T, experts + sinks]: ids / weights [T, top_k + sinks]."""
     logits = np.ascontiguousarray(logits, np.float32)

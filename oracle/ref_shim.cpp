@@ -19,6 +19,7 @@
 #include "strata/compressed_tensors.hpp"
 #include "strata/deepseek_host_expert.hpp"
 #include "strata/deepseek_ops.hpp"
+#include "strata/diagnostics.hpp"
 #include "strata/glm_int4.hpp"
 #include "strata/glm_ops.hpp"
 #include "strata/inkling_ops.hpp"
@@ -95,6 +96,9 @@ REF_API int ref_kimi_route(const float* logits, const float* bias, uint32_t expe
     }
     return 0;
 }
+
+// stable_bf16_hash, src/platform/diagnostics.cpp:84-88
+REF_API uint64_t ref_stable_bf16_hash(const float* values, size_t n) { return strata::stable_bf16_hash({values, n}); }
 
 // inkling_route_sigmoid_sink, src/models/inkling/inkling_ops.cpp:184-275
 REF_API int ref_inkling_route_sink(const float* logits, const float* bias, uint32_t experts, uint32_t sinks, uint32_t k,

@@ -22,7 +22,7 @@ EXPORTS = [
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
-    "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink",
+    "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink", "strata_moe_stable_bf16_hash",
     "strata_moe_forward_routed", "strata_moe_latent_create", "strata_moe_latent_destroy", "strata_moe_latent_experts",
     "strata_moe_latent_set_router", "strata_moe_latent_set_projections", "strata_moe_latent_set_shared",
     "strata_moe_latent_forward",
@@ -97,6 +97,7 @@ def load_library():
     lib.strata_moe_route.argtypes = [vp, vp, u32, vp, vp, vp]
     lib.strata_moe_route_hash.argtypes = [vp, vp, u32, vp, vp, vp, vp]
     lib.strata_moe_project_rows.argtypes = [vp, vp, u32, u32, vp, u32, vp]
+    lib.strata_moe_stable_bf16_hash.argtypes = [vp, vp, C.c_size_t, C.POINTER(C.c_uint64)]
     lib.strata_moe_route_sink.argtypes = [vp, vp, vp, u32, u32, u32, u32, C.c_float, vp, vp, vp]
     lib.strata_moe_group.argtypes = [vp, vp, u32, u32, u32, vp, vp, vp, vp]
     lib.strata_moe_gather_rows.argtypes = [vp, vp, u32, vp, u32, u32, vp]
@@ -205,6 +206,14 @@ class MoeContext:
         s = Stats()
         self.check(self.lib.strata_moe_get_stats(self.h, C.byref(s)))
         return s
+
+    def stable_bf16_hash(self, values):
+        """The reference's per-layer state hash of an fp32 device tensor (FNV-1a over its BF16 rounding)."""
+        h = C.c_uint64()
+        self.enter()
+        self.check(self.lib.strata_moe_stable_bf16_hash(self.h, _ptr(values), values.numel(), C.byref(h)))
+        self.leave()
+        return int(h.value)
 
     def project_rows(self, x, w):
         """logits [T, rows] of BF16 x [T, H] against BF16 w [rows, H] in the router's canonical summation order."""

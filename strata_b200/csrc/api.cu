@@ -131,6 +131,8 @@ struct strata_moe_layer {
     // f16 decode path for the FP4 formats
     bool f16_ok = false;
     bool stream_ok = false;   // shapes and alignments allow the TMA ring kernels
+    uint8_t* arena_cur = nullptr;   // weight arena: next free byte of the newest chunk (chunks are in `owned`)
+    size_t arena_left = 0, arena_next = 4u << 20;
     void* d_smaps = nullptr;  // [3][n_local][3] tensor maps of the ring kernels
     uint32_t* d_not_ok = nullptr;
     float *act_f32 = nullptr, *x_rowscale = nullptr, *act_rowscale = nullptr;
@@ -903,6 +905,8 @@ void strata_moe_layer_destroy(strata_moe_layer* L) {
     delete L;
 }
 
+constexpr size_t kArenaChunk = 256u << 20;
+
 static int put(strata_moe_layer* L, const void* src, size_t bytes, int source, const void** dev) {
     strata_moe_ctx* ctx = L->ctx;
     if (!src) return fail(ctx, STRATA_MOE_E_INVALID, "null weight pointer");
@@ -912,10 +916,22 @@ static int put(strata_moe_layer* L, const void* src, size_t bytes, int source, c
     }
     if (source != STRATA_MOE_SRC_HOST && source != STRATA_MOE_SRC_DEVICE_COPY)
         return fail(ctx, STRATA_MOE_E_INVALID, "unknown source kind");
-    void* p = nullptr;
-    // 256-byte granularity like the reference's weight arena (kernels/cuda/backend.cu:4889-4890)
-    CK(cudaMalloc(&p, (bytes + 255) / 256 * 256));
-    L->owned.push_back(p);
+    // Layer-owned copies are carved out of large chunks at 256-byte granularity, like the reference's weight arena
+    // (kernels/cuda/backend.cu:4889-4890): a few allocations per layer instead of six per expert.  Space is only
+    // returned when the layer is destroyed (a tensor registered twice keeps both copies until then).
+    const size_t need = (bytes + 255) / 256 * 256;
+    if (need > L->arena_left) {
+        const size_t chunk = need > L->arena_next ? need : L->arena_next;     // 4 MB, doubling up to 256 MB
+        if (L->arena_next < kArenaChunk) L->arena_next *= 2;
+        void* c = nullptr;
+        CK(cudaMalloc(&c, chunk));
+        L->owned.push_back(c);
+        L->arena_cur = static_cast<uint8_t*>(c);
+        L->arena_left = chunk;
+    }
+    void* p = L->arena_cur;
+    L->arena_cur += need;
+    L->arena_left -= need;
     CK(cudaMemcpyAsync(p, src, bytes,
                        source == STRATA_MOE_SRC_HOST ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToDevice,
                        ctx->stream));
@@ -1019,6 +1035,27 @@ int strata_moe_route_hash(strata_moe_layer* L, const void* x, uint32_t T, const 
     // an expert id outside the layer raises the status word (kStatusNonFiniteLogit's neighbour: bad route)
     launch_route(p, lg, nullptr, T, ids, weights, ctx->d_status, ctx->stream, token_experts);
     CK(cudaGetLastError());
+    return 0;
+}
+
+int strata_moe_stable_bf16_hash(strata_moe_ctx* ctx, const float* values, size_t n, uint64_t* hash) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    if (!hash || (!values && n)) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
+    CK(cudaSetDevice(ctx->device));
+    std::vector<float> host(n);
+    if (n) CK(cudaMemcpyAsync(host.data(), values, n * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    CK(cudaStreamSynchronize(ctx->stream));
+    ctx->stats.d2h_bytes += n * sizeof(float);
+    uint64_t h = 14695981039346656037ull;
+    for (size_t i = 0; i < n; ++i) {
+        uint32_t b;
+        memcpy(&b, &host[i], 4);
+        if ((b & 0x7F800000u) != 0x7F800000u) b += 0x7FFFu + ((b >> 16) & 1u);   // infinities and NaNs are truncated
+        const uint32_t v = b >> 16;
+        h = (h ^ (v & 0xFFu)) * 1099511628211ull;
+        h = (h ^ (v >> 8)) * 1099511628211ull;
+    }
+    *hash = h;
     return 0;
 }
 

@@ -366,6 +366,16 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
     assert rechecked <= cfg.T // 50
 
 
+def test_state_hash_of_the_output(ctx):
+    """strata_moe_stable_bf16_hash of a layer's output equals the oracle's hash of the same values (the reference's
+    "[state]" diagnostic), and two runs of the layer hash alike."""
+    cfg = small(synth.FMT_MXFP4, T=9, name="hash")
+    layer, ml, out, aux = run_layer(ctx, cfg)
+    h = ctx.stable_bf16_hash(out)
+    assert h == O.stable_bf16_hash(out.cpu().numpy())
+    assert ctx.stable_bf16_hash(ml.forward(layer.x)) == h
+
+
 @pytest.mark.parametrize("T,E,S,k", [(5, 256, 2, 6), (300, 128, 1, 8), (33, 64, 0, 4)])
 def test_inkling_sink_router(ctx, T, E, S, k):
     """Gate projection over routed + sink rows and the sink router against the oracle (which is pinned bit for bit to

@@ -226,3 +226,19 @@ def test_inkling_sink_router_matches_reference():
         assert rrc == 0
         assert np.array_equal(ids[0], rids)
         assert np.array_equal(w[0].view(np.uint32), rw.view(np.uint32)), (trial, w[0], rw)
+
+
+def test_stable_bf16_hash_matches_reference():
+    """orc_stable_bf16_hash against the compiled stable_bf16_hash (src/platform/diagnostics.cpp:84-88), ties, subnormals,
+    infinities and NaNs (which the reference truncates instead of rounding) included."""
+    ref = O.ref()
+    ref.ref_stable_bf16_hash.restype = C.c_uint64
+    ref.ref_stable_bf16_hash.argtypes = [C.POINTER(C.c_float), C.c_size_t]
+    rng = np.random.default_rng(3)
+    v = rng.standard_normal(5000).astype(np.float32)
+    special = np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1.00390625, 1.01171875, 1e-40, -3e38], np.float32)
+    bits = np.array([0x7F800001, 0x7FC00000, 0x3F808000, 0x3F818000], np.uint32).view(np.float32)
+    v = np.concatenate([v, special, bits])
+    want = int(ref.ref_stable_bf16_hash(v.ctypes.data_as(C.POINTER(C.c_float)), v.size))
+    assert O.stable_bf16_hash(v) == want
+    assert O.stable_bf16_hash(v[:0]) == 14695981039346656037
