@@ -186,6 +186,12 @@ int strata_moe_forward_routed(strata_moe_layer* layer, const void* x_bf16, uint3
 int strata_moe_forward_host(strata_moe_layer* layer, const void* x_bf16_host, uint32_t tokens,
                             float* out_host);
 
+/* Diagnostics: every activation workspace of the context lies between two guard zones filled with a canary byte;
+ * this waits for the context's streams and compares them.  0, or STRATA_MOE_E_CUDA with the workspace named in the
+ * error text when a kernel wrote outside its buffer.  (The reference relies on host-side shape validation and a
+ * device error flag, kernels/cuda/backend.cu:1922-1924, 16045-16142; a memory checker is not available to the tests.) */
+int strata_moe_check_canaries(strata_moe_ctx* ctx);
+
 /* Diagnostics: FNV-1a hash of n fp32 values (device memory) after round-to-nearest-even to BF16, the reference's
  * per-layer state hash ("[state]" lines, src/models/glm52/glm_runtime.cpp:1592-1598).  Waits for the context's
  * stream, copies the values to the host and hashes them there.

@@ -22,7 +22,7 @@ EXPORTS = [
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
     "strata_moe_ep_forward", "strata_moe_ep_abandon",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
-    "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink", "strata_moe_stable_bf16_hash",
+    "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink", "strata_moe_stable_bf16_hash", "strata_moe_check_canaries",
     "strata_moe_forward_routed", "strata_moe_latent_create", "strata_moe_latent_destroy", "strata_moe_latent_experts",
     "strata_moe_latent_set_router", "strata_moe_latent_set_projections", "strata_moe_latent_set_shared",
     "strata_moe_latent_forward",
@@ -206,6 +206,10 @@ class MoeContext:
         s = Stats()
         self.check(self.lib.strata_moe_get_stats(self.h, C.byref(s)))
         return s
+
+    def check_canaries(self):
+        """Raises when a kernel wrote outside one of the context's workspaces."""
+        self.check(self.lib.strata_moe_check_canaries(self.h))
 
     def stable_bf16_hash(self, values):
         """The reference's per-layer state hash of an fp32 device tensor (FNV-1a over its BF16 rounding)."""

@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+
+#include <nvtx3/nvToolsExt.h>
 #include <new>
 #include <string>
 #include <vector>
@@ -41,6 +43,7 @@ struct strata_moe_ctx {
     // after the other on the context's stream; sizing them per layer would multiply gigabytes by the layer
     // count).  Grown to the largest request; a layer picks the current pointers up at every call.
     void* ws[16] = {};
+    void* ws_raw[16] = {};    // the allocations behind ws[]: guard zone, body, guard zone
     strata_moe_layer* ws_owner = nullptr;   // layer whose command holds results in the pool until collected
     size_t ws_bytes[16] = {};
 };
@@ -155,6 +158,15 @@ int fail(strata_moe_ctx* c, int code, const std::string& msg) {
 }
 
 // phase boundary i of a timed forward (no-op unless timing is on)
+// NVTX range over a host-side scope (the launches of one phase): shows up in a timeline profiler, costs a few
+// nanoseconds when none is attached.
+struct Range {
+    explicit Range(const char* name) { nvtxRangePushA(name); }
+    ~Range() { nvtxRangePop(); }
+    Range(const Range&) = delete;
+    Range& operator=(const Range&) = delete;
+};
+
 void mark(strata_moe_ctx* c, int i) {
     if (c->timing) cudaEventRecord(c->pev[i], c->stream);
 }
@@ -178,20 +190,31 @@ cudaError_t dalloc(strata_moe_layer* L, T** p, size_t n) {
     return e;
 }
 
+// Every workspace sits between two 256-byte guard zones filled with a canary byte; strata_moe_check_canaries compares
+// them (the device-side check that stands in for a memory checker: a kernel that writes past its buffer is found by the
+// tests that call it, without a trap).
+constexpr size_t kGuard = 256;
+constexpr int kCanary = 0xA5;
+
 cudaError_t ws_reserve(strata_moe_ctx* ctx, int slot, size_t bytes) {
     if (bytes <= ctx->ws_bytes[slot]) return cudaSuccess;
     // nothing enqueued may still use the old buffer
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess && ctx->side) e = cudaStreamSynchronize(ctx->side);
     if (e != cudaSuccess) return e;
-    if (ctx->ws[slot]) cudaFree(ctx->ws[slot]);
-    ctx->ws[slot] = nullptr;
+    if (ctx->ws_raw[slot]) cudaFree(ctx->ws_raw[slot]);
+    ctx->ws[slot] = ctx->ws_raw[slot] = nullptr;
     ctx->ws_bytes[slot] = 0;
-    e = cudaMalloc(&ctx->ws[slot], bytes);
+    const size_t body = (bytes + kGuard - 1) / kGuard * kGuard;
+    e = cudaMalloc(&ctx->ws_raw[slot], body + 2 * kGuard);
     if (e != cudaSuccess) return e;
+    uint8_t* raw = static_cast<uint8_t*>(ctx->ws_raw[slot]);
+    ctx->ws[slot] = raw + kGuard;
     ctx->ws_bytes[slot] = bytes;
+    e = cudaMemset(raw, kCanary, kGuard);
+    if (e == cudaSuccess) e = cudaMemset(raw + kGuard + body, kCanary, kGuard);
     // rows the tensor-core path owns are still swept by the f32 -> f16 conversion pass: keep them finite
-    if (slot == kWsActF32) e = cudaMemset(ctx->ws[slot], 0, bytes);
+    if (e == cudaSuccess && slot == kWsActF32) e = cudaMemset(ctx->ws[slot], 0, bytes);
     return e;
 }
 
@@ -391,6 +414,7 @@ __global__ void set_pair_kernel(uint32_t* p, uint32_t a, uint32_t b) {
 // Otherwise large batches take the fast path: tensor-core projection into the layer's workspace, exact
 // selection and weights by route_fast_kernel, canonical recomputation of the tokens it does not trust.
 int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* logits_out, uint32_t* ids, float* w) {
+    Range range("strata_moe.router");
     strata_moe_ctx* ctx = L->ctx;
     cudaStream_t s = ctx->stream;
     const strata_moe_layer_desc& d = L->d;
@@ -425,6 +449,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
                 const uint32_t* pairs_dev = nullptr, bool x_ready = false) {
     // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
     // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
+    Range range("strata_moe.experts");
     strata_moe_ctx* ctx = L->ctx;
     cudaStream_t s = ctx->stream;
     if (pairs == 0) return 0;
@@ -714,7 +739,7 @@ void strata_moe_destroy(strata_moe_ctx* ctx) {
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->cmd_layer) strata_moe_layer_destroy(ctx->cmd_layer);
     for (void* p : ctx->cmd_scratch) cudaFree(p);
-    for (void*& p : ctx->ws) {
+    for (void*& p : ctx->ws_raw) {
         if (p) cudaFree(p);
         p = nullptr;
     }
@@ -1038,6 +1063,26 @@ int strata_moe_route_hash(strata_moe_layer* L, const void* x, uint32_t T, const 
     return 0;
 }
 
+int strata_moe_check_canaries(strata_moe_ctx* ctx) {
+    if (!ctx) return STRATA_MOE_E_INVALID;
+    CK(cudaSetDevice(ctx->device));
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (ctx->side) CK(cudaStreamSynchronize(ctx->side));
+    uint8_t guard[2 * kGuard];
+    for (int slot = 0; slot < 16; ++slot) {
+        if (!ctx->ws_raw[slot]) continue;
+        const uint8_t* raw = static_cast<const uint8_t*>(ctx->ws_raw[slot]);
+        const size_t body = (ctx->ws_bytes[slot] + kGuard - 1) / kGuard * kGuard;
+        CK(cudaMemcpy(guard, raw, kGuard, cudaMemcpyDeviceToHost));
+        CK(cudaMemcpy(guard + kGuard, raw + kGuard + body, kGuard, cudaMemcpyDeviceToHost));
+        for (size_t i = 0; i < 2 * kGuard; ++i)
+            if (guard[i] != (uint8_t)kCanary)
+                return fail(ctx, STRATA_MOE_E_CUDA, "workspace " + std::to_string(slot) + ": guard zone " +
+                                                        (i < kGuard ? "before" : "after") + " the buffer was overwritten");
+    }
+    return 0;
+}
+
 int strata_moe_stable_bf16_hash(strata_moe_ctx* ctx, const float* values, size_t n, uint64_t* hash) {
     if (!ctx) return STRATA_MOE_E_INVALID;
     if (!hash || (!values && n)) return fail(ctx, STRATA_MOE_E_INVALID, "null pointer");
@@ -1222,6 +1267,7 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
         if (rc) return rc;
     }
     if (!front_done) {
+        Range range("strata_moe.group");
         mark(ctx, 2);
         launch_group(ids, P, 0, d.experts, counts, offsets, perm, L->inv, L->active, L->n_active,
                      L->group_scratch, s);
@@ -1242,7 +1288,10 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
         shared = L->sh_y;
     }
     mark(ctx, 7);
-    launch_combine(L->y, L->inv, w, shared, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s);
+    {
+        Range range("strata_moe.combine");
+        launch_combine(L->y, L->inv, w, shared, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s);
+    }
     mark(ctx, 8);
     CK(cudaGetLastError());
     if (ctx->timing) {
@@ -2261,6 +2310,7 @@ int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
 // Stage 2: wait for every rank's counts, lay out the owners' buffers, store the rows there.
 int strata_moe_ep_dispatch(strata_moe_ep* ep) {
     if (!ep) return STRATA_MOE_E_INVALID;
+    Range range("strata_moe.ep.dispatch");
     strata_moe_layer* L = ep->L;
     strata_moe_ctx* ctx = L->ctx;
     if (ep->stage != 1) return fail(ctx, STRATA_MOE_E_INVALID, "ep_dispatch must follow ep_begin");
@@ -2302,6 +2352,7 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
 // Stage 4: wait for every owner's outputs and form this rank's tokens from them.
 int strata_moe_ep_finish(strata_moe_ep* ep, float* out) {
     if (!ep) return STRATA_MOE_E_INVALID;
+    Range range("strata_moe.ep.combine");
     strata_moe_layer* L = ep->L;
     strata_moe_ctx* ctx = L->ctx;
     if (ep->stage != 3) return fail(ctx, STRATA_MOE_E_INVALID, "ep_finish must follow ep_experts");

@@ -366,6 +366,24 @@ def test_fast_router_is_bit_exact(ctx, kind, zipf, dup, monkeypatch):
     assert rechecked <= cfg.T // 50
 
 
+def test_workspace_guard_zones_stay_intact():
+    """Ragged shapes through every expert path on a fresh context (small workspaces, so an overrun lands in a guard
+    zone and not in slack): the canary bytes around all workspaces are intact afterwards."""
+    c = MoeContext(0)
+    for cfg in (small(synth.FMT_MXFP4, T=13, E=8, k=3, H=1024, I=512, name="guard_ring"),
+                small(synth.FMT_NVFP4, T=37, E=8, k=2, H=768, I=256, name="guard_stream"),
+                small(synth.FMT_INT4, T=333, E=8, k=2, H=512, I=256, norm_init=1e-20, name="guard_prefill"),
+                small(synth.FMT_MXFP4, T=64, E=64, k=6, zipf_s=1.3, name="guard_mixed"),
+                small(synth.FMT_NVFP4, T=200, I_shared=256, name="guard_shared")):
+        layer = synth.build_layer(cfg, "cuda")
+        ml = MoeLayer(c, cfg, max_tokens=layer.x.shape[0])
+        ml.load_synth(layer)
+        ml.forward(layer.x)
+        c.synchronize()
+        c.check_canaries()
+        ml.close()
+
+
 def test_state_hash_of_the_output(ctx):
     """strata_moe_stable_bf16_hash of a layer's output equals the oracle's hash of the same values (the reference's
     "[state]" diagnostic), and two runs of the layer hash alike."""
