@@ -70,6 +70,7 @@ struct LayerKnobs {
     bool no_f16_path = false;       // STRATA_MOE_NO_F16_PATH: FP4 formats use the general BF16 decoders
     bool no_prefill_path = false;   // STRATA_MOE_NO_PREFILL_PATH: never use the tensor-core tile path
     bool no_stream_ring = false;    // STRATA_MOE_NO_STREAM_RING: small batches use the register-streaming kernels
+    bool no_half_y = false;         // STRATA_MOE_NO_HALF_Y: the tensor-core down kernel always stores fp32 expert rows
     bool no_small_front = false;    // STRATA_MOE_NO_SMALL_FRONT: decode batches keep the separate route / group / convert kernels
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
@@ -96,6 +97,7 @@ static LayerKnobs read_knobs() {
     k.mixed_min_rows = num("STRATA_MOE_MIXED_MIN_ROWS", -1);
     k.mixed_min_tokens = num("STRATA_MOE_MIXED_MIN_TOKENS", -1);
     k.no_small_front = getenv("STRATA_MOE_NO_SMALL_FRONT") != nullptr;
+    k.no_half_y = getenv("STRATA_MOE_NO_HALF_Y") != nullptr;
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
     k.stream_ring_max_rows = num("STRATA_MOE_STREAM_RING_MAX_ROWS", 8);
     k.host_chunks = num("STRATA_MOE_HOST_CHUNKS", 0);
@@ -451,7 +453,7 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
                 uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
                 const uint32_t* n_active, uint32_t max_rows, float* y, uint32_t expected_pairs = 0,
-                const uint32_t* pairs_dev = nullptr, bool x_ready = false) {
+                const uint32_t* pairs_dev = nullptr, bool x_ready = false, bool* y_half = nullptr) {
     // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
     // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
     Range range("strata_moe.experts");
@@ -479,6 +481,10 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.status = ctx->d_status;
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         p.ntile = prefill_ntile(L, pairs, n_groups);
+        // the caller combines right away and can take the expert rows as f16: half the bytes written here and read
+        // by the combine pass, which is bound by exactly those bytes
+        p.y_half = (y_half && *y_half && !L->knobs.no_half_y) ? 1u : 0u;
+        if (y_half) *y_half = p.y_half != 0u;
         if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s,
                            ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
@@ -486,6 +492,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         CK(cudaGetLastError());
         return 0;
     }
+    if (y_half) *y_half = false;      // only the all-tensor-core path above stores f16 rows
     DecodeArgs a{};
     a.fmt = L->d.format;
     a.H = L->d.hidden;
@@ -1284,7 +1291,9 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
                      L->group_scratch, s);
         mark(ctx, 3);
     }
-    rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y, 0, nullptr, x_ready);
+    bool y_half = true;
+    rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y, 0, nullptr, x_ready,
+                     &y_half);
     if (rc) return rc;
     const float* shared = nullptr;
     if (fork_shared) {
@@ -1301,7 +1310,7 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
     mark(ctx, 7);
     {
         Range range("strata_moe.combine");
-        launch_combine(L->y, L->inv, w, shared, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s);
+        launch_combine(L->y, L->inv, w, shared, T, d.top_k, d.hidden, d.output_scale, out, ctx->d_status, s, y_half);
     }
     mark(ctx, 8);
     CK(cudaGetLastError());

@@ -135,6 +135,7 @@ struct PrefillArgs {
     const uint32_t* offsets;       // [n_groups + 1]
     WeightTable gate, up, down;
     float* y;                      // [pairs, H] fp32
+    uint32_t y_half;               // down: store y as f16 [pairs, H] into the same buffer (values beyond the f16 range are reported)
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
     GluParams glu;                 // activation of the gate/up epilogue
@@ -171,9 +172,9 @@ void launch_rmsnorm_bf16(const float* x, const float* weight, uint32_t rows, uin
                          __nv_bfloat16* y, uint32_t* status, cudaStream_t s);
 void launch_add_rows(float* out, const float* a, size_t n, cudaStream_t s);
 // combine.cu
-void launch_combine(const float* y, const uint32_t* inv, const float* weights, const float* shared,
+void launch_combine(const void* y, const uint32_t* inv, const float* weights, const float* shared,
                     uint32_t T, uint32_t k, uint32_t H, float output_scale, float* out,
-                    uint32_t* status, cudaStream_t s);
+                    uint32_t* status, cudaStream_t s, bool y_half = false);
 void launch_dequant_export(int fmt, const uint8_t* packed, const uint8_t* scales, float global_scale,
                            uint32_t rows, uint32_t cols, float* out, cudaStream_t s);
 

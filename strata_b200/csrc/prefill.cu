@@ -660,12 +660,15 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     } else {
                         const float rs = rowscale ? rowscale[pos] : 1.0f;   // pre-scaled activation rows
                         const float v = __uint_as_float(g[j]) * s0 * rs;
-                        if (!(fabsf(v) <= 3.0e38f)) bad = true;
-                        a.y[pos * R + feat] = v;
+                        const float lim = a.y_half ? 65504.0f : 3.0e38f;
+                        if (!(fabsf(v) <= lim)) bad = true;
+                        if (a.y_half) reinterpret_cast<__half*>(a.y)[pos * R + feat] = __float2half_rn(v);
+                        else a.y[pos * R + feat] = v;
                         if (MODE == 2) {
                             const float v2 = __uint_as_float(u[j]) * s1 * rs;
-                            if (!(fabsf(v2) <= 3.0e38f)) bad = true;
-                            a.y[pos * R + feat + kMTile] = v2;
+                            if (!(fabsf(v2) <= lim)) bad = true;
+                            if (a.y_half) reinterpret_cast<__half*>(a.y)[pos * R + feat + kMTile] = __float2half_rn(v2);
+                            else a.y[pos * R + feat + kMTile] = v2;
                         }
                     }
                 }
