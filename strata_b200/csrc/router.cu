@@ -524,13 +524,16 @@ __device__ __forceinline__ float score_and_slope(const RouterParams& p, float l,
 
 constexpr int kFastWarps = 4;
 
-// a read-only 16-byte load the compiler keeps in program order with its neighbours: a run of them is issued
-// back to back, before the arithmetic that consumes the first
-__device__ __forceinline__ uint4 ldg128_ordered(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
+// 16-byte asynchronous copies global -> shared (cp.async): the data of a whole batch is in flight without occupying
+// registers, and the wait is an instruction of its own, so the instruction scheduler cannot shorten the batch to save
+// registers (with plain loads it placed each multiply-add right behind its own load and the in-order warp then
+// waited out one memory round trip per vector instead of one per batch).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src)
+                 : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // eight products of one 16-byte weight load with the matching activations, each added to its own chain
 __device__ __forceinline__ void chain_fma8(float (&c)[8], const uint4& xv, const uint4& wv) {
@@ -543,6 +546,7 @@ __device__ __forceinline__ void chain_fma8(float (&c)[8], const uint4& xv, const
 }
 
 constexpr uint32_t kMaxCand = 32;     // candidates per token: one lane each
+constexpr uint32_t kFastStageFloats = (512u + 64u) * 4u;   // per warp: two weight buffers of 256 vectors, two activation buffers of 32
 
 __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     RouterParams p, const float* __restrict__ logits, const float* __restrict__ bias,
@@ -552,9 +556,12 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
     extern __shared__ __align__(16) float fsm[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t E = p.experts, k = p.top_k;
-    // per warp: choice, eps [E]; candidate ids, their canonical logits, selected ids and scores [32 each]
-    const size_t per_warp = 2u * (size_t)E + 4u * kMaxCand;
-    float* choice = fsm + warp * per_warp;
+    // per warp: staging buffers for the canonical dot products (2 x 256 + 2 x 32 vectors of 16 bytes, first so that they
+    // stay 16-byte aligned), then choice, eps [E]; candidate ids, their canonical logits, selected ids and scores [32 each]
+    const size_t per_warp = kFastStageFloats + 2u * (size_t)E + 4u * kMaxCand;
+    uint4* wbuf = reinterpret_cast<uint4*>(fsm + warp * per_warp);
+    uint4* xbuf = wbuf + 512;
+    float* choice = fsm + warp * per_warp + kFastStageFloats;
     float* eps = choice + E;
     uint32_t* cand = reinterpret_cast<uint32_t*>(eps + E);
     float* canon = reinterpret_cast<float*>(cand + kMaxCand);
@@ -631,17 +638,33 @@ __global__ void __launch_bounds__(kFastWarps * 32) route_fast_kernel(
             // the token's row comes through L1: the four lanes of a group read 64 contiguous bytes, all groups the same
             const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)tok * H) + sub;
             float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t j = 0;
-            for (; j + 8u <= per_lane; j += 8u) {     // eight 16-byte router loads in flight per lane
-                uint4 wv[8], xv[8];
+            // batches of eight steps through two shared-memory buffers per warp: batch b + 1 is requested before batch
+            // b is consumed.  The router rows differ per group (32 x 16 bytes per step); the token row is the same for
+            // all groups, so group 0 fetches it (4 x 16 bytes per step).
+            auto issue = [&](uint32_t b, uint32_t j) {
+                uint4* wb = wbuf + (b & 1u) * 256u;
+                uint4* xb = xbuf + (b & 1u) * 32u;
 #pragma unroll
-                for (uint32_t q = 0; q < 8u; ++q) wv[q] = ldg128_ordered(wrow + (size_t)(j + q) * 4u);
+                for (uint32_t q = 0; q < 8u; ++q)
+                    if (j + q < per_lane) {
+                        cp_async16(wb + q * 32u + lane, wrow + (size_t)(j + q) * 4u);
+                        if (grp == 0u) cp_async16(xb + q * 4u + sub, xrow + (size_t)(j + q) * 4u);
+                    }
+                cp_async_commit();
+            };
+            issue(0u, 0u);
+            for (uint32_t b = 0, j = 0; j < per_lane; ++b, j += 8u) {
+                if (j + 8u < per_lane) issue(b + 1u, j + 8u);
+                else cp_async_commit();             // an empty group keeps the count the wait relies on
+                cp_async_wait_all_but_one();
+                __syncwarp();
+                const uint4* wb = wbuf + (b & 1u) * 256u;
+                const uint4* xb = xbuf + (b & 1u) * 32u;
 #pragma unroll
-                for (uint32_t q = 0; q < 8u; ++q) xv[q] = ldg128_ordered(xrow + (size_t)(j + q) * 4u);
-#pragma unroll
-                for (uint32_t q = 0; q < 8u; ++q) chain_fma8(c, xv[q], wv[q]);
+                for (uint32_t q = 0; q < 8u; ++q)
+                    if (j + q < per_lane) chain_fma8(c, xb[q * 4u + sub], wb[q * 32u + lane]);
+                __syncwarp();                       // the buffer is refilled by the issue after next
             }
-            for (; j < per_lane; ++j) chain_fma8(c, __ldg(xrow + (size_t)j * 4u), __ldg(wrow + (size_t)j * 4u));
             // rounds 16 and 8 pair chains held by different lanes of the group, rounds 4, 2, 1 chains of one lane
 #pragma unroll
             for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 2));
@@ -772,44 +795,39 @@ __global__ void __launch_bounds__(kSmallMaxTokens * 32) router_logits_small_kern
         const uint32_t wrow = ring::smem_addr(rows + (size_t)row * pitch) + sub * 16u;
         const uint4* xrow = reinterpret_cast<const uint4*>(x + (size_t)tok * H) + sub;
         float c[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        // the token's row comes from global memory in batches of eight 16-byte loads, two batches in flight: the next
-        // batch is requested before the arithmetic on the current one
-        uint4 xa[8], xb[8];
-        auto fetch = [&](uint4 (&buf)[8], uint32_t j) {
+        // the token's row comes from global memory in batches of eight steps through two small shared-memory buffers
+        // (cp.async; group 0 fetches, the row is the same for all groups): batch b + 1 is in flight while b is consumed
+        uint4* xbuf = reinterpret_cast<uint4*>(rows + (size_t)kSmallRows * pitch) + warp * 64u;
+        auto issue = [&](uint32_t b, uint32_t j) {
+            if (grp == 0u) {
 #pragma unroll
-            for (uint32_t i = 0; i < 8u; ++i)
-                if (j + i < per_lane) buf[i] = ldg128_ordered(xrow + (size_t)(j + i) * 4u);
+                for (uint32_t i = 0; i < 8u; ++i)
+                    if (j + i < per_lane) cp_async16(xbuf + (b & 1u) * 32u + i * 4u + sub, xrow + (size_t)(j + i) * 4u);
+            }
+            cp_async_commit();
         };
-        auto consume = [&](const uint4 (&buf)[8], uint32_t j, uint32_t jend) {
-#pragma unroll
-            for (uint32_t i = 0; i < 8u; ++i)
-                if (j + i < jend) chain_fma8(c, buf[i], ring::lds128(wrow + (j + i) * 64u));
-        };
-        fetch(xa, 0u);
-        fetch(xb, 8u);
+        issue(0u, 0u);
         uint32_t q = 0, jq = per_lane / 4u;          // quarter being consumed and its end step
         ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait_poll(&bars[0], 0u, &abort_flag));
-        for (uint32_t j = 0; j < per_lane && ok; j += 16u) {
-            // steps [j, j + 8) from xa, [j + 8, j + 16) from xb; a batch may straddle a quarter boundary
-            for (uint32_t half = 0; half < 2u && ok; ++half) {
-                const uint32_t jb = j + half * 8u;
-                if (jb >= per_lane) break;
-                const uint32_t je = min(jb + 8u, per_lane);
-                while (ok && q < 3u && je > jq) {      // the batch reaches into the next quarter: wait for it too
-                    ++q;
-                    jq = per_lane * (q + 1u) / 4u;
-                    ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait_poll(&bars[q], 0u, &abort_flag));
-                }
-                if (!ok) break;
-                if (half == 0u) {
-                    consume(xa, jb, je);
-                    fetch(xa, jb + 16u);
-                } else {
-                    consume(xb, jb, je);
-                    fetch(xb, jb + 16u);
-                }
+        for (uint32_t b = 0, j = 0; j < per_lane && ok; ++b, j += 8u) {
+            if (j + 8u < per_lane) issue(b + 1u, j + 8u);
+            else cp_async_commit();
+            const uint32_t je = min(j + 8u, per_lane);
+            while (ok && q < 3u && je > jq) {      // the batch reaches into the next quarter of the router rows
+                ++q;
+                jq = per_lane * (q + 1u) / 4u;
+                ok = __all_sync(0xFFFFFFFFu, ring::mbar_wait_poll(&bars[q], 0u, &abort_flag));
             }
+            if (!ok) break;
+            cp_async_wait_all_but_one();
+            __syncwarp();
+            const uint4* xb = xbuf + (b & 1u) * 32u;
+#pragma unroll
+            for (uint32_t i = 0; i < 8u; ++i)
+                if (j + i < je) chain_fma8(c, xb[i * 4u + sub], ring::lds128(wrow + (j + i) * 64u));
+            __syncwarp();
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
         if (ok) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) c[i] = __fadd_rn(c[i], __shfl_down_sync(0xFFFFFFFFu, c[i], 2));
@@ -836,7 +854,7 @@ bool launch_router_logits_small(const __nv_bfloat16* x, const __nv_bfloat16* wg,
                                 float* logits, uint32_t* status, cudaStream_t s) {
     if (T == 0 || T > kSmallMaxTokens || H % 128u || status == nullptr) return false;
     if ((((uintptr_t)x | (uintptr_t)wg) & 15u) != 0) return false;
-    const size_t smem = 128u + (size_t)kSmallRows * (H * 2u + kSmallPad);
+    const size_t smem = 128u + (size_t)kSmallRows * (H * 2u + kSmallPad) + (size_t)kSmallMaxTokens * 64u * 16u;
     if (smem > 200u * 1024u) return false;
     static bool attr[64] = {};
     int dev = 0;
@@ -865,7 +883,7 @@ bool route_fast_supported(const RouterParams& p, uint32_t H) {
     if (p.score_kind == STRATA_MOE_SCORE_SOFTMAX) return false;
     if (p.experts % 128u || H % 64u) return false;
     return p.top_k <= kMaxCand &&
-           (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float)) <= 200u * 1024u;
+           (size_t)kFastWarps * ((kFastStageFloats + 2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float)) <= 200u * 1024u;
 }
 
 // logits: approximate [T, E] (tensor-core projection); list [T], count, recheck_total: device scratch.
@@ -876,7 +894,7 @@ void launch_route_fast(const RouterParams& p, float* logits, const float* bias, 
                        uint32_t* list, uint32_t* count, unsigned long long* recheck_total, uint32_t* status,
                        cudaStream_t s) {
     if (T == 0) return;
-    const size_t smem = (size_t)kFastWarps * ((2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float));
+    const size_t smem = (size_t)kFastWarps * ((kFastStageFloats + 2u * (size_t)p.experts + 4u * kMaxCand) * sizeof(float));
     static bool attr[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
