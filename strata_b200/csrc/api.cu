@@ -453,7 +453,8 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
                 uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
                 const uint32_t* n_active, uint32_t max_rows, float* y, uint32_t expected_pairs = 0,
-                const uint32_t* pairs_dev = nullptr, bool x_ready = false, bool* y_half = nullptr) {
+                const uint32_t* pairs_dev = nullptr, bool x_ready = false, bool* y_half = nullptr,
+                float* y_rowscale_out = nullptr) {
     // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
     // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
     Range range("strata_moe.experts");
@@ -485,6 +486,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         // by the combine pass, which is bound by exactly those bytes
         p.y_half = (y_half && *y_half && !L->knobs.no_half_y) ? 1u : 0u;
         if (y_half) *y_half = p.y_half != 0u;
+        p.y_rowscale_out = p.y_half ? y_rowscale_out : nullptr;
         if (launch_prefill(p, L->xg, L->x_rowscale, L->act_hi, L->max_pairs, L->d_wmaps, s,
                            ctx->timing ? ctx->pev[5] : nullptr) != 0)
             return fail(ctx, STRATA_MOE_E_CUDA, "prefill launch failed");
@@ -492,7 +494,10 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         CK(cudaGetLastError());
         return 0;
     }
-    if (y_half) *y_half = false;      // only the all-tensor-core path above stores f16 rows
+    // only the all-tensor-core path above stores f16 rows; a caller that pointed y at an f16-sized buffer must have
+    // predicted that path with the same test
+    if (y_half && *y_half && y != L->y) return fail(ctx, STRATA_MOE_E_INVALID, "f16 output buffer offered to a path that writes fp32");
+    if (y_half) *y_half = false;
     DecodeArgs a{};
     a.fmt = L->d.format;
     a.H = L->d.hidden;
@@ -545,18 +550,35 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         p.glu = GluParams{L->d.activation, L->d.gate_beta, L->d.linear_beta};
         p.ntile = 128;   // hybrid down: few rows per expert
         a.skip_from = big;
+        if (!x_ready) launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        mark(ctx, 4);
         // the ring kernels win while a group fits one 8-row token tile (measured: 8 tokens of c0 99 us against 114 us;
         // 256 tokens of c1, 16-row tiles and several passes per group: 419 us against 339 us)
         const bool ring = L->stream_ok && a.max_rows_per_group <= (uint32_t)L->knobs.stream_ring_max_rows;
-        if (!x_ready) launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
-        mark(ctx, 4);
-        // ring kernels, no group handed to the tensor-core path: the gate/up epilogue writes the down kernel's f16
-        // operand itself and the separate conversion pass is skipped
-        const bool act_direct = ring && !big && !down_all_tensor;
+        // An expert gets at most one row per token: with more tokens than a ring tile holds, a group CAN be larger than
+        // the typical one the tile was sized for (a skewed router).  The ring kernels would re-stream such a group's
+        // weights once per 8 rows, so they keep the groups that fit one tile and the register-streaming kernels (16-row
+        // tiles) take the ones between that and the tensor-core threshold.  Measured on 8 GPUs at the c4 shape (896
+        // experts, Zipf): 1.24 ms per step with the ring kernels alone against 0.78 ms before they existed.
+        const uint32_t ring_rows = (uint32_t)L->knobs.stream_ring_max_rows;
+        // (from 4 tiles' worth of tokens on: below that the worst case is a few extra passes over one group, cheaper than
+        // two more launches and the activation conversion pass)
+        const bool split = ring && max_rows > 4u * ring_rows;
+        // ring kernels for every group, no group on the tensor-core path: the gate/up epilogue writes the down kernel's
+        // f16 operand itself and the separate conversion pass is skipped
+        const bool act_direct = ring && !split && !big && !down_all_tensor;
         a.act_direct = act_direct ? 1u : 0u;
         a.act_rowscale_out = L->act_rowscale;
+        DecodeArgs mid = a;        // the register-streaming launch beside the ring one
+        if (split) {
+            a.skip_from = ring_rows + 1u;
+            mid.skip_below = ring_rows + 1u;
+            const uint32_t cap = big ? big - 1u : max_rows;
+            mid.max_rows_per_group = cap < 16u ? cap : 16u;
+        }
         if (ring) {
             if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
+            if (split) launch_decode_fp4_gate_up(mid, s);
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
@@ -583,6 +605,7 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         } else {
             if (ring) {
                 if (launch_decode_stream_down(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
+                if (split) launch_decode_fp4_down(mid, s);
             } else {
                 launch_decode_fp4_down(a, s);
             }
@@ -2411,12 +2434,18 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     const uint32_t par = ep->w.step & 1u, B = L->d.expert_count;
     launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
     if (expected_rows == 0) expected_rows = ep->T * L->d.top_k ? ep->T * L->d.top_k : 1u;
+    // When the whole step runs on the tensor-core path its down kernel stores the f16 rows the peers will read (unit
+    // row factors) straight into the window; otherwise the fp32 outputs leave through a conversion pass as f16 rows
+    // with an exact per-row power-of-two scale.
+    const uint32_t est = expected_rows < ep->w.cap ? expected_rows : ep->w.cap;
+    bool direct = use_prefill(L, est, B) && !L->knobs.no_half_y;
+    float* y = direct ? reinterpret_cast<float*>(ep->w.y(ep->w.rank, par)) : L->y;
     int rc = run_experts(L, ep->w.rows(ep->w.rank, par), nullptr, 1, ep->w.cap, B, ep->loffsets, nullptr, nullptr,
-                         ep->w.cap, L->y, expected_rows, ep->loffsets + B);
+                         ep->w.cap, y, expected_rows, ep->loffsets + B, false, &direct, ep->w.yscale(ep->w.rank, par));
     if (rc) return rc;
-    // the outputs leave this GPU as f16 rows with an exact per-row power-of-two scale
-    launch_rows_to_f16_f32(L->y, 0, ep->w.cap, L->d.hidden, ep->w.y(ep->w.rank, par), nullptr,
-                           ep->w.yscale(ep->w.rank, par), s, ep->loffsets + B);
+    if (!direct)
+        launch_rows_to_f16_f32(L->y, 0, ep->w.cap, L->d.hidden, ep->w.y(ep->w.rank, par), nullptr,
+                               ep->w.yscale(ep->w.rank, par), s, ep->loffsets + B);
     launch_ep_signal(ep->w, 2, s);
     CK(cudaGetLastError());
     ep->stage = 3;

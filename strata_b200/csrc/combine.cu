@@ -29,26 +29,47 @@ __global__ void __launch_bounds__(256) combine_kernel(const void* __restrict__ y
         float o[V];
 #pragma unroll
         for (uint32_t q = 0; q < V; ++q) o[q] = 0.0f;
-        for (uint32_t r = 0; r < k; ++r) {
-            const uint32_t pos = inv[(size_t)t * k + r];
-            if (pos == 0xFFFFFFFFu) continue;
-            const float w = weights[(size_t)t * k + r];
-            float v[V];
-            if (Y_HALF) {
-                const uint4 h = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(y_v) + (size_t)pos * H + c));
-                const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+        // four expert rows are requested together (their loads do not depend on one another); the products are still
+        // added in selection-rank order
+        for (uint32_t r0 = 0; r0 < k; r0 += 4u) {
+            uint32_t pos[4];
+            float w[4];
+            uint4 raw[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[q]));
-                    v[2 * q] = f.x;
-                    v[2 * q + 1] = f.y;
-                }
-            } else {
-                const float4 f = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(y_v) + (size_t)pos * H + c));
-                v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+            for (uint32_t q = 0; q < 4u; ++q) {
+                const bool in = r0 + q < k;
+                pos[q] = in ? inv[(size_t)t * k + r0 + q] : 0xFFFFFFFFu;
+                w[q] = in ? weights[(size_t)t * k + r0 + q] : 0.0f;
             }
 #pragma unroll
-            for (uint32_t q = 0; q < V; ++q) o[q] = __fadd_rn(o[q], __fmul_rn(v[q], w));
+            for (uint32_t q = 0; q < 4u; ++q) {
+                raw[q] = make_uint4(0, 0, 0, 0);
+                if (pos[q] != 0xFFFFFFFFu) {
+                    if (Y_HALF)
+                        raw[q] = __ldg(reinterpret_cast<const uint4*>(static_cast<const __half*>(y_v) + (size_t)pos[q] * H + c));
+                    else
+                        raw[q] = __ldg(reinterpret_cast<const uint4*>(static_cast<const float*>(y_v) + (size_t)pos[q] * H + c));
+                }
+            }
+#pragma unroll
+            for (uint32_t q = 0; q < 4u; ++q) {
+                if (pos[q] == 0xFFFFFFFFu) continue;
+                float v[V];
+                const uint32_t hw[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
+                if (Y_HALF) {
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[h]));
+                        v[2 * h] = f.x;
+                        v[2 * h + 1] = f.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) v[h] = __uint_as_float(hw[h]);
+                }
+#pragma unroll
+                for (uint32_t e = 0; e < V; ++e) o[e] = __fadd_rn(o[e], __fmul_rn(v[e], w[q]));
+            }
         }
         if (output_scale != 1.0f) {
 #pragma unroll

@@ -92,7 +92,8 @@ struct DecodeArgs {
     uint32_t max_rows_per_group;   // upper bound used to pick the token tile
     uint32_t ksplit;               // decode.cu: 1 = the four warps of a CTA split K of one tile (few tiles)
     GluParams glu;                 // activation between gate/up and down
-    uint32_t skip_from;            // decode_fp4.cu: groups with at least this many rows are left to the tensor-core path (0 = none)
+    uint32_t skip_from;            // groups with at least this many rows are left to another kernel (0 = none)
+    uint32_t skip_below;           // decode_fp4.cu: groups with fewer rows than this are left to the ring kernels (0 = none)
     WeightTable gate, up, down;
     const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
     const __nv_bfloat16* x_lo;     // optional low part (fp32 inputs), nullptr otherwise
@@ -136,6 +137,7 @@ struct PrefillArgs {
     WeightTable gate, up, down;
     float* y;                      // [pairs, H] fp32
     uint32_t y_half;               // down: store y as f16 [pairs, H] into the same buffer (values beyond the f16 range are reported)
+    float* y_rowscale_out;         // down with y_half: receives 1.0 for every row written (rows are not scaled), or nullptr
     uint32_t* tile_table;          // scratch of prefill_scratch_bytes()
     uint32_t* status;
     GluParams glu;                 // activation of the gate/up epilogue

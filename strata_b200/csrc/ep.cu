@@ -240,17 +240,26 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(EpWindows w, const uint
         __syncthreads();
         for (uint32_t c = tid; c < per_row; c += blockDim.x) {
             float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (uint32_t r = 0; r < k; ++r) {
-                const unsigned short* ptr = src[r];
-                if (!ptr) continue;
-                const float g = wgt[r], rs = rscale[r];
-                const uint4 v = *reinterpret_cast<const uint4*>(ptr + c * 8u);
-                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+            // four peer rows are requested together: a load over NVLink takes microseconds, and one after the other
+            // (the loop count is a run-time value) they would add up per thread; the sums keep the rank order
+            for (uint32_t r0 = 0; r0 < k; r0 += 4u) {
+                uint4 v[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[q]));
-                    o[2 * q] = __fadd_rn(o[2 * q], __fmul_rn(__fmul_rn(f.x, rs), g));
-                    o[2 * q + 1] = __fadd_rn(o[2 * q + 1], __fmul_rn(__fmul_rn(f.y, rs), g));
+                for (uint32_t q = 0; q < 4u; ++q) {
+                    const unsigned short* ptr = r0 + q < k ? src[r0 + q] : nullptr;
+                    v[q] = ptr ? *reinterpret_cast<const uint4*>(ptr + c * 8u) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (uint32_t q = 0; q < 4u; ++q) {
+                    if (r0 + q >= k || !src[r0 + q]) continue;
+                    const float g = wgt[r0 + q], rs = rscale[r0 + q];
+                    const uint32_t wv[4] = {v[q].x, v[q].y, v[q].z, v[q].w};
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[h]));
+                        o[2 * h] = __fadd_rn(o[2 * h], __fmul_rn(__fmul_rn(f.x, rs), g));
+                        o[2 * h + 1] = __fadd_rn(o[2 * h + 1], __fmul_rn(__fmul_rn(f.y, rs), g));
+                    }
                 }
             }
 #pragma unroll

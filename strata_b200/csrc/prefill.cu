@@ -661,6 +661,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         const float rs = rowscale ? rowscale[pos] : 1.0f;   // pre-scaled activation rows
                         const float v = __uint_as_float(g[j]) * s0 * rs;
                         const float lim = a.y_half ? 65504.0f : 3.0e38f;
+                        if (a.y_rowscale_out != nullptr && feat == 0u) a.y_rowscale_out[pos] = 1.0f;
                         if (!(fabsf(v) <= lim)) bad = true;
                         if (a.y_half) reinterpret_cast<__half*>(a.y)[pos * R + feat] = __float2half_rn(v);
                         else a.y[pos * R + feat] = v;
