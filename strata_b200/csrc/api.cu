@@ -554,31 +554,20 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         mark(ctx, 4);
         // the ring kernels win while a group fits one 8-row token tile (measured: 8 tokens of c0 99 us against 114 us;
         // 256 tokens of c1, 16-row tiles and several passes per group: 419 us against 339 us)
-        const bool ring = L->stream_ok && a.max_rows_per_group <= (uint32_t)L->knobs.stream_ring_max_rows;
-        // An expert gets at most one row per token: with more tokens than a ring tile holds, a group CAN be larger than
-        // the typical one the tile was sized for (a skewed router).  The ring kernels would re-stream such a group's
-        // weights once per 8 rows, so they keep the groups that fit one tile and the register-streaming kernels (16-row
-        // tiles) take the ones between that and the tensor-core threshold.  Measured on 8 GPUs at the c4 shape (896
-        // experts, Zipf): 1.24 ms per step with the ring kernels alone against 0.78 ms before they existed.
+        // ... and only for decode-sized calls (at most 32 rows per call can reach one expert: an expert gets at most one
+        // row per token).  With more tokens a skewed router makes groups of many rows, whose weights the 8-row ring tile
+        // would stream again for every 8 rows: measured at the c4 shape (896 experts, Zipf, 256 tokens) 1.13 ms per step
+        // with the ring kernels for the small groups against 0.96 ms with the register-streaming kernels for all; at 64
+        // uniformly routed tokens of c1 the two are equal (0.405 / 0.408 ms).
         const uint32_t ring_rows = (uint32_t)L->knobs.stream_ring_max_rows;
-        // (from 4 tiles' worth of tokens on: below that the worst case is a few extra passes over one group, cheaper than
-        // two more launches and the activation conversion pass)
-        const bool split = ring && max_rows > 4u * ring_rows;
-        // ring kernels for every group, no group on the tensor-core path: the gate/up epilogue writes the down kernel's
-        // f16 operand itself and the separate conversion pass is skipped
-        const bool act_direct = ring && !split && !big && !down_all_tensor;
+        const bool ring = L->stream_ok && a.max_rows_per_group <= ring_rows && max_rows <= 4u * ring_rows;
+        // ring kernels, no group on the tensor-core path: the gate/up epilogue writes the down kernel's f16 operand itself
+        // and the separate conversion pass is skipped
+        const bool act_direct = ring && !big && !down_all_tensor;
         a.act_direct = act_direct ? 1u : 0u;
         a.act_rowscale_out = L->act_rowscale;
-        DecodeArgs mid = a;        // the register-streaming launch beside the ring one
-        if (split) {
-            a.skip_from = ring_rows + 1u;
-            mid.skip_below = ring_rows + 1u;
-            const uint32_t cap = big ? big - 1u : max_rows;
-            mid.max_rows_per_group = cap < 16u ? cap : 16u;
-        }
         if (ring) {
             if (launch_decode_stream_gate_up(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream gate/up launch failed");
-            if (split) launch_decode_fp4_gate_up(mid, s);
         } else {
             launch_decode_fp4_gate_up(a, s);
         }
@@ -605,7 +594,6 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
         } else {
             if (ring) {
                 if (launch_decode_stream_down(a, L->d_smaps, s) != 0) return fail(ctx, STRATA_MOE_E_CUDA, "stream down launch failed");
-                if (split) launch_decode_fp4_down(mid, s);
             } else {
                 launch_decode_fp4_down(a, s);
             }

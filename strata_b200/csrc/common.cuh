@@ -93,7 +93,6 @@ struct DecodeArgs {
     uint32_t ksplit;               // decode.cu: 1 = the four warps of a CTA split K of one tile (few tiles)
     GluParams glu;                 // activation between gate/up and down
     uint32_t skip_from;            // groups with at least this many rows are left to another kernel (0 = none)
-    uint32_t skip_below;           // decode_fp4.cu: groups with fewer rows than this are left to the ring kernels (0 = none)
     WeightTable gate, up, down;
     const __nv_bfloat16* x_hi;     // [pairs, H] K-permuted (or natural for BF16 weights)
     const __nv_bfloat16* x_lo;     // optional low part (fp32 inputs), nullptr otherwise

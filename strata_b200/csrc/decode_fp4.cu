@@ -216,8 +216,7 @@ __global__ void __launch_bounds__(128, NT == 1 ? 4 : (NT == 2 ? 3 : 2)) decode_f
         const uint32_t g = a.active_list ? a.active_list[slot] : slot;
         const uint32_t rt = tile - slot * tiles_per_group;
         const uint32_t row0 = a.offsets[g], cnt = a.offsets[g + 1] - row0;
-        // big groups: tensor-core path; small ones: the ring kernels, when those run beside this one
-        if (cnt == 0u || (a.skip_from != 0u && cnt >= a.skip_from) || cnt < a.skip_below) continue;
+        if (cnt == 0u || (a.skip_from != 0u && cnt >= a.skip_from)) continue;   // big groups: tensor-core path
         const uint32_t row = (DUAL ? rt * 16u : rt * 32u) + gid;
 
         Fp4Stream p0, p1;

@@ -336,20 +336,6 @@ def test_prefill_path_odd_hidden_size(ctx):
     assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
 
 
-def test_three_way_dispatch_under_a_skewed_router(ctx, monkeypatch):
-    """Ring-capable shape, 64 tokens, Zipf router: inside one step the groups of up to 8 rows run on the ring kernels,
-    those of 9 .. 23 rows on the register-streaming kernels and the hot ones on the tensor-core path."""
-    monkeypatch.setenv("STRATA_MOE_MIXED_MIN_TOKENS", "1")
-    cfg = small(synth.FMT_MXFP4, H=512, I=512, T=64, E=64, k=6, zipf_s=1.3, name="three_way")
-    layer, ml, out, aux = run_layer(ctx, cfg)
-    counts = aux["counts"].cpu().numpy()
-    assert (counts >= 24).any() and ((counts > 8) & (counts < 24)).any() and ((counts > 0) & (counts <= 8)).any(), counts
-    ref = Hh.run_oracle(cfg, layer.x.cpu())
-    assert np.array_equal(aux["ids"].cpu().numpy().astype(np.uint32), ref["ids"])
-    rel, mx = Hh.error_metrics(out.cpu().numpy(), ref["out"])
-    assert rel <= PREFILL_TIGHT and mx <= MAX_ABS, (rel, mx)
-
-
 def test_mixed_dispatch_under_a_skewed_router(ctx, monkeypatch):
     """A Zipf-biased router gives a few experts many rows and most experts few: inside one step the
     hot experts run on the tensor-core path and the rest on the weight-streaming kernels."""
