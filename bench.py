@@ -420,7 +420,8 @@ def run_single(args, cfg, T):
         for name, Ts, sweep in plan:
             if name == cfg.name and Ts == T:
                 continue
-            rec = measure_layer(ctx, synth.CONFIGS[name], Ts, sub_steps, 3, peaks, flush, sub_cpu, batch_sweep=sweep)
+            rec = measure_layer(ctx, synth.CONFIGS[name], Ts, sub_steps, 3, peaks, flush, sub_cpu,
+                                want_parity=args.parity, batch_sweep=sweep)
             rec["name"], rec["steps"] = name, sub_steps
             sub.append(rec)
     line = {

@@ -107,10 +107,16 @@ struct CudaDeepSeekMoeExpert {
     float coefficient{1.0F};
 };
 
+inline constexpr std::size_t kCudaDsv4TiledShards = 2U;
+
 struct CudaDeepSeekMoeRowGroup {
     const CudaWeight* w1{};
     const CudaWeight* w3{};
     const CudaWeight* w2{};
+    // The reference's transformed alternative to w1/w3/w2 (include/strata/cuda_backend.hpp:728-733).  This backend
+    // keeps the canonical layout only (include/strata_moe_loader.hpp converts tiled shards back): a group that sets
+    // a shard is rejected.
+    std::array<const CudaWeight*, kCudaDsv4TiledShards> tiled_shards{};
     std::span<const std::uint32_t> rows;
     std::span<const float> coefficients;
 };
@@ -252,7 +258,7 @@ public:
         std::vector<float> coefficients(routed.size());
         for (std::size_t i = 0; i < routed.size(); ++i) {
             coefficients[i] = routed[i].coefficient;
-            groups.push_back({routed[i].w1, routed[i].w3, routed[i].w2, std::span<const std::uint32_t>(&kRowZero, 1),
+            groups.push_back({routed[i].w1, routed[i].w3, routed[i].w2, {}, std::span<const std::uint32_t>(&kRowZero, 1),
                               std::span<const float>(&coefficients[i], 1)});
         }
         return enqueue_rows(device, hidden, 1U, groups, shared,
@@ -333,6 +339,8 @@ private:
         if (state->in_flight != 0) return error("MoE workspace already has an in-flight command");
         std::vector<strata_moe_row_group> raw;
         for (const auto& g : groups) {
+            if (g.tiled_shards[0] != nullptr || g.tiled_shards[1] != nullptr)
+                return error("transformed expert shards are not supported: upload the canonical w1 / w3 / w2");
             if (!usable(g.w1, device) || !usable(g.w3, device) || !usable(g.w2, device))
                 return error("DeepSeek MoE command contains an incompatible CUDA weight");
             if (g.rows.size() != g.coefficients.size()) return error("row group rows and coefficients differ in size");

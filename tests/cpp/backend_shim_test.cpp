@@ -12,6 +12,7 @@
 #include <algorithm>
 #include <array>
 #include <bit>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -19,9 +20,17 @@
 #include <limits>
 #include <vector>
 
+// STRATA_TEST_REFERENCE_BACKEND: the same cases against the reference's own CUDA backend (compiled unmodified by
+// oracle/build.py), which makes this file a two-way check: both implementations have to meet the CPU checker's values.
+#ifdef STRATA_TEST_REFERENCE_BACKEND
+#include "strata/cuda_backend.hpp"
+#define BACKEND_NAME "reference backend"
+#else
 #include "strata_moe_backend.hpp"
 
 namespace strata = strata_b200;   // the one line a reference call site changes
+#define BACKEND_NAME "backend shim"
+#endif
 
 extern "C" {
 // CPU checker (test infrastructure): oracle/moe_oracle.c
@@ -317,8 +326,8 @@ void deepseek_exact_commands() {
     const std::array<std::uint32_t, 1> rows1{1U};
     const std::array<float, 1> coefs1{coefficient1};
     const std::array<strata::CudaDeepSeekMoeRowGroup, 2> groups{{
-        {&routed0_w1, &routed0_w3, &routed0_w2, rows0, coefs0},
-        {&routed1_w1, &routed1_w3, &routed1_w2, rows1, coefs1},
+        {&routed0_w1, &routed0_w3, &routed0_w2, {}, rows0, coefs0},
+        {&routed1_w1, &routed1_w3, &routed1_w2, {}, rows1, coefs1},
     }};
     const std::array<std::uint32_t, 2> shared_rows{0U, 1U};
     std::array<float, 3U * hidden_columns> grouped_output{};
@@ -369,14 +378,57 @@ void deepseek_exact_commands() {
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// Timing of one command shape through whichever backend this file was compiled against: the GLM INT4 command at the
+// target shape (hidden 6144, intermediate 2048) with `experts` routed experts over `rows` rows, host buffers in and
+// out (the reference command's contract), wall clock around enqueue + collect, best of `repeats` after two warm-ups.
+void time_glm_command(std::uint32_t rows, std::uint32_t experts, int repeats) {
+    const auto devices = strata::CudaBackend::available_devices();
+    if (!strata::CudaBackend::compiled() || devices.empty()) return;
+    constexpr std::uint64_t hidden_columns = 6144U, intermediate_columns = 2048U;
+    const int device = devices.front();
+    strata::CudaBackend backend;
+    const std::array<int, 1> selected{device};
+    REQUIRE(backend.initialize(selected, false).ok());
+    std::vector<HostWeight> keep(3U * experts);
+    std::vector<strata::CudaWeight> w(3U * experts);
+    for (std::uint32_t e = 0; e < experts; ++e) {
+        w[3U * e] = upload_int4(backend, device, intermediate_columns, hidden_columns, (std::uint8_t)(1U + e), keep[3U * e]);
+        w[3U * e + 1U] = upload_int4(backend, device, intermediate_columns, hidden_columns, (std::uint8_t)(3U + e), keep[3U * e + 1U]);
+        w[3U * e + 2U] = upload_int4(backend, device, hidden_columns, intermediate_columns, (std::uint8_t)(5U + e), keep[3U * e + 2U]);
+    }
+    std::vector<strata::CudaMoeExpert> routed;
+    for (std::uint32_t e = 0; e < experts; ++e) routed.push_back({&w[3U * e], &w[3U * e + 1U], &w[3U * e + 2U], 1.0F});
+    std::vector<float> hidden(static_cast<std::size_t>(rows) * hidden_columns);
+    for (std::size_t index = 0U; index < hidden.size(); ++index)
+        hidden[index] = static_cast<float>(static_cast<int>(index % 13U) - 6) / 16.0F;
+    std::vector<float> routed_output(static_cast<std::size_t>(experts) * rows * hidden_columns), none;
+    double best = 1.0e30;
+    for (int it = 0; it < repeats + 2; ++it) {
+        const auto t0 = std::chrono::steady_clock::now();
+        REQUIRE(backend.enqueue_moe(device, hidden, rows, routed, nullptr).ok());
+        REQUIRE(backend.collect_moe(device, routed_output, none).ok());
+        const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+        if (it >= 2) best = std::min(best, ms);
+    }
+    double checksum = 0.0;
+    for (float v : routed_output) checksum += v;
+    std::printf("%s: glm int4 command, %u experts x %u rows: %.3f ms per command (checksum %.6e)\n", BACKEND_NAME, experts, rows,
+                best, checksum);
+}
+
 int main(int argc, char** argv) {
     if (argc > 1 && std::strcmp(argv[1], "--compile-check") == 0) return 0;
+    if (argc > 1 && std::strcmp(argv[1], "--time") == 0) {
+        for (std::uint32_t rows : {1U, 2U, 16U, 128U, 512U}) time_glm_command(rows, 8U, 5);
+        return g_failures == 0 ? 0 : 1;
+    }
     glm_int4_target_shape_command();
     deepseek_exact_commands();
     if (g_failures != 0) {
         std::fprintf(stderr, "%d case(s) failed\n", g_failures);
         return 1;
     }
-    std::printf("backend shim cases passed\n");
+    std::printf(BACKEND_NAME " cases passed\n");
     return 0;
 }

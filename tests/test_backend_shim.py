@@ -38,3 +38,20 @@ def test_reference_command_cases_through_the_shim(tmp_path):
     sys.stdout.write(r.stdout)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "backend shim cases passed" in r.stdout
+
+
+REF_EXE = os.path.join(ROOT, "oracle", "_ref", "backend_shim_test_ref")
+
+
+@pytest.mark.gpu
+def test_the_same_cases_pass_on_the_reference_cuda_backend():
+    """The reference's own CUDA backend (kernels/cuda/backend.cu compiled unmodified for sm_100a by oracle/build.py,
+    together with this very test program built against the reference's headers) has to pass the same cases with the
+    same expected values from the CPU checker: the checker is thereby pinned to the reference's GPU path too, and the
+    shim's signatures are proven source-compatible.  Skipped where the prebuilt executable did not travel."""
+    if not os.path.exists(REF_EXE):
+        pytest.skip("oracle/_ref/backend_shim_test_ref was not built (no reference checkout at build time)")
+    r = subprocess.run([REF_EXE], capture_output=True, text=True, timeout=600)
+    sys.stdout.write(r.stdout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "reference backend cases passed" in r.stdout
