@@ -886,8 +886,8 @@ ORC_API int orc_dsv4_expert(float* out, const float* in, const uint8_t* w1, cons
  * src/models/dsv4/deepseek_ops.cpp:523-560, accumulates in double and is only tolerance-close), so this
  * function is PINNED THROUGH THE REFERENCE'S GPU KERNELS instead: the ported command cases
  * (tests/cpp/backend_shim_test.cpp, built against the reference's own backend by oracle/build.py) compare
- * the reference backend's shared-expert output with this function bit for bit at hidden = intermediate = 128;
- * the full DeepSeek shape is not pinned.  This restates the DEVICE kernels
+ * the reference backend's shared-expert output with this function bit for bit at hidden = intermediate = 128
+ * and at the DeepSeek-V4 shape 4096 / 2048.  This restates the DEVICE kernels
  * deepseek_fp8_gate_up_kernel / deepseek_fp8_down_kernel (kernels/cuda/backend.cu:2781-2863):
  * thread t of a 256-thread block sums columns t, t + 256, ... with sum = fma(x * w, scale, sum),
  * then the same block tree as the FP4 kernels; decode fp8_e4m3_value (:159-173).

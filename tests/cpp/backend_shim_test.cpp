@@ -6,7 +6,7 @@
 //   * expected values come from the CPU checker (oracle/libmoe_oracle.so) instead of a second pass
 //     through the device matmul;
 //   * the DeepSeek case runs at hidden = intermediate = 128 (this library's shapes are multiples of
-//     128; the reference case uses 32);
+//     128; the reference case uses 32) and at the DeepSeek-V4 shape 4096 / 2048;
 //   * statistics that count the reference's own launches and transfers are not asserted.
 // Exit code 0 = all cases passed (or no usable device).
 #include <algorithm>
@@ -257,11 +257,13 @@ void glm_int4_target_shape_command() {
 
 // ---------------------------------------------------------------------------------------------
 // ref: TEST_CASE("native CUDA backend enqueues exact grouped DeepSeek MoE when available")
+// Run at hidden = intermediate = 128 (the reference case uses 32; this library's shapes are multiples of 128) and at the
+// DeepSeek-V4 shape 4096 / 2048, the shape of the reference's host-versus-device exactness test
+// (tests/test_deepseek_host_expert.cpp:456-496).
+template <std::uint64_t hidden_columns, std::uint64_t intermediate_columns>
 void deepseek_exact_commands() {
     const auto devices = strata::CudaBackend::available_devices();
     if (!strata::CudaBackend::compiled() || devices.empty()) return;
-    constexpr std::uint64_t hidden_columns = 128U;        // the reference case uses 32
-    constexpr std::uint64_t intermediate_columns = 128U;
     const int device = devices.front();
     strata::CudaBackend backend;
     const std::array<int, 1> selected{device};
@@ -424,7 +426,8 @@ int main(int argc, char** argv) {
         return g_failures == 0 ? 0 : 1;
     }
     glm_int4_target_shape_command();
-    deepseek_exact_commands();
+    deepseek_exact_commands<128U, 128U>();
+    deepseek_exact_commands<4096U, 2048U>();
     if (g_failures != 0) {
         std::fprintf(stderr, "%d case(s) failed\n", g_failures);
         return 1;
