@@ -51,6 +51,7 @@ int orc_expert_ffn(const orc_expert* ex, const float* x, float coef, int coef_be
 int orc_dsv4_expert(float* out, const float* in, const uint8_t* w1, const uint8_t* s1, const uint8_t* w3,
                     const uint8_t* s3, const uint8_t* w2, const uint8_t* s2, uint32_t hidden, uint32_t intermediate,
                     float coefficient, float swiglu_limit, float* scratch);
+void orc_router_logits(const uint16_t* x_bf16, const uint16_t* wg_bf16, uint32_t T, uint32_t H, uint32_t E, float* logits);
 int orc_dsv4_fp8_shared(float* out, const float* in, const uint8_t* w1, const uint8_t* s1, const uint8_t* w3,
                         const uint8_t* s3, const uint8_t* w2, const uint8_t* s2, uint32_t hidden, uint32_t intermediate,
                         float swiglu_limit, float* scratch);
@@ -380,6 +381,56 @@ void deepseek_exact_commands() {
 
 }  // namespace
 
+#ifdef STRATA_TEST_REFERENCE_BACKEND
+// ---------------------------------------------------------------------------------------------
+// The router projection's summation order: the reference runs the gate through CudaBackend::matmul on a plain BF16
+// weight (bf16_matvec_kernel / bf16_matvec_rows_kernel, kernels/cuda/backend.cu:651-728).  The CPU checker's
+// orc_router_logits restates that order; here the reference's own kernels have to reproduce it bit for bit, for one row
+// (the matvec kernel), a few rows and more rows than one tile of the rows kernel (16).  This library's logits are
+// compared with the same checker function in the GPU parity tests.
+void reference_router_projection_order() {
+    const auto devices = strata::CudaBackend::available_devices();
+    if (!strata::CudaBackend::compiled() || devices.empty()) return;
+    constexpr std::uint32_t experts = 256U, hidden_columns = 4096U;
+    const int device = devices.front();
+    strata::CudaBackend backend;
+    const std::array<int, 1> selected{device};
+    REQUIRE(backend.initialize(selected, false).ok());
+    std::vector<std::uint16_t> w(static_cast<std::size_t>(experts) * hidden_columns);
+    std::uint32_t state = 12345U;
+    auto next_bf16 = [&](float scale) {
+        state = state * 1664525U + 1013904223U;
+        const float v = (static_cast<float>((state >> 8) & 0xFFFFU) / 65535.0F - 0.5F) * scale;
+        const auto b = bf16(v);
+        return static_cast<std::uint16_t>(static_cast<unsigned>(b[0]) | (static_cast<unsigned>(b[1]) << 8));
+    };
+    for (auto& v : w) v = next_bf16(0.08F);
+    strata::CudaWeightDescriptor descriptor;
+    descriptor.encoding = strata::CudaWeightEncoding::Plain;
+    descriptor.dtype = strata::SafetensorsDtype::Bf16;
+    descriptor.rows = experts;
+    descriptor.columns = hidden_columns;
+    strata::CudaWeight gate;
+    const std::span<const std::byte> bytes(reinterpret_cast<const std::byte*>(w.data()), w.size() * 2U);
+    REQUIRE(backend.upload(device, descriptor, bytes, {}, gate).ok());
+    for (std::uint32_t rows : {1U, 3U, 20U}) {
+        std::vector<std::uint16_t> x(static_cast<std::size_t>(rows) * hidden_columns);
+        for (auto& v : x) v = next_bf16(6.0F);
+        std::vector<float> xf(x.size());
+        for (std::size_t i = 0; i < x.size(); ++i) xf[i] = std::bit_cast<float>(static_cast<std::uint32_t>(x[i]) << 16);
+        std::vector<float> got(static_cast<std::size_t>(rows) * experts), want(got.size());
+        REQUIRE(backend.matmul(gate, xf, rows, got).ok());
+        orc_router_logits(x.data(), w.data(), rows, hidden_columns, experts, want.data());
+        std::size_t differ = 0;
+        for (std::size_t i = 0; i < got.size(); ++i)
+            differ += std::bit_cast<std::uint32_t>(got[i]) != std::bit_cast<std::uint32_t>(want[i]);
+        std::printf("reference router projection, %u row(s): %zu of %zu logits differ from the checker\n", rows, differ,
+                    got.size());
+        REQUIRE(differ == 0U);
+    }
+}
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // Timing of one command shape through whichever backend this file was compiled against: the GLM INT4 command at the
 // target shape (hidden 6144, intermediate 2048) with `experts` routed experts over `rows` rows, host buffers in and
@@ -428,6 +479,9 @@ int main(int argc, char** argv) {
     glm_int4_target_shape_command();
     deepseek_exact_commands<128U, 128U>();
     deepseek_exact_commands<4096U, 2048U>();
+#ifdef STRATA_TEST_REFERENCE_BACKEND
+    reference_router_projection_order();
+#endif
     if (g_failures != 0) {
         std::fprintf(stderr, "%d case(s) failed\n", g_failures);
         return 1;
