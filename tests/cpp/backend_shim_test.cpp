@@ -162,6 +162,35 @@ strata::CudaWeight upload_fp8(strata::CudaBackend& backend, int device, std::uin
     return result;
 }
 
+// compressed-tensors "nvfp4-pack-quantized" (Laguna routed experts): E2M1 nibble pairs, one E4M3 scale per 16 columns,
+// one FP32 per-tensor divisor.  Scale bytes stay in the normal range of E4M3 (0x30 .. 0x3F: 0.5 .. 1.875).
+strata::CudaWeight upload_nvfp4(strata::CudaBackend& backend, int device, std::uint64_t rows, std::uint64_t columns,
+                                std::uint8_t seed, float global_scale, HostWeight& keep) {
+    strata::CudaWeightDescriptor descriptor;
+    descriptor.encoding = strata::CudaWeightEncoding::Nvfp4Group16;
+    descriptor.dtype = strata::SafetensorsDtype::U8;
+    descriptor.rows = rows;
+    descriptor.columns = columns;
+    descriptor.packed_columns = columns / 2U;
+    descriptor.scale_columns = columns / 16U;
+    descriptor.group_size = 16U;
+    descriptor.global_scale = global_scale;
+    keep.weights.resize(static_cast<std::size_t>(rows * descriptor.packed_columns));
+    for (std::uint64_t row = 0U; row < rows; ++row)
+        for (std::uint64_t packed = 0U; packed < descriptor.packed_columns; ++packed) {
+            const auto low = static_cast<std::uint8_t>((seed + row * 5U + packed * 3U) & 0x0FU);
+            const auto high = static_cast<std::uint8_t>((seed + row * 11U + packed * 7U + 2U) & 0x0FU);
+            keep.weights[row * descriptor.packed_columns + packed] =
+                static_cast<std::byte>(low | static_cast<std::uint8_t>(high << 4U));
+        }
+    keep.scales.resize(static_cast<std::size_t>(rows * descriptor.scale_columns));
+    for (std::size_t index = 0U; index < keep.scales.size(); ++index)
+        keep.scales[index] = static_cast<std::byte>(0x30U + static_cast<std::uint8_t>((index * 7U + seed) % 16U));
+    strata::CudaWeight result;
+    if (!backend.upload(device, descriptor, keep.weights, keep.scales, result).ok()) ++g_failures;
+    return result;
+}
+
 const uint8_t* u8(const std::vector<std::byte>& v) { return reinterpret_cast<const uint8_t*>(v.data()); }
 
 std::vector<float> oracle_int4_expert(const HostWeight& gate, const HostWeight& up, const HostWeight& down,
@@ -254,6 +283,61 @@ void glm_int4_target_shape_command() {
     nan_hidden[5] = std::numeric_limits<float>::quiet_NaN();
     REQUIRE(!backend.enqueue_moe(device, nan_hidden, rows, routed, &shared).ok());      // non-finite hidden rejected
     REQUIRE(backend.synchronize(device).ok());
+}
+
+// ---------------------------------------------------------------------------------------------
+// The Laguna command: NVFP4 routed experts (hidden 2048, intermediate 1024 here), three rows.  The reference has no
+// test of its own for this encoding on the MoE command; the case is this repository's, run on both backends against
+// the CPU checker (decode, scale direction = divide by the per-tensor value, FP32 accumulation in another order).
+void laguna_nvfp4_command() {
+    const auto devices = strata::CudaBackend::available_devices();
+    if (!strata::CudaBackend::compiled() || devices.empty()) return;
+    constexpr std::uint32_t rows = 3U;
+    constexpr std::uint64_t hidden_columns = 2048U, intermediate_columns = 1024U;
+    const int device = devices.front();
+    strata::CudaBackend backend;
+    const std::array<int, 1> selected{device};
+    REQUIRE(backend.initialize(selected, false).ok());
+    HostWeight h[6];
+    const float gs[6] = {384.0F, 448.0F, 512.0F, 320.0F, 640.0F, 416.0F};
+    auto gate0 = upload_nvfp4(backend, device, intermediate_columns, hidden_columns, 1U, gs[0], h[0]);
+    auto up0 = upload_nvfp4(backend, device, intermediate_columns, hidden_columns, 4U, gs[1], h[1]);
+    auto down0 = upload_nvfp4(backend, device, hidden_columns, intermediate_columns, 7U, gs[2], h[2]);
+    auto gate1 = upload_nvfp4(backend, device, intermediate_columns, hidden_columns, 10U, gs[3], h[3]);
+    auto up1 = upload_nvfp4(backend, device, intermediate_columns, hidden_columns, 13U, gs[4], h[4]);
+    auto down1 = upload_nvfp4(backend, device, hidden_columns, intermediate_columns, 2U, gs[5], h[5]);
+    std::vector<float> hidden(rows * hidden_columns);
+    for (std::size_t index = 0U; index < hidden.size(); ++index)
+        hidden[index] = static_cast<float>(static_cast<int>(index % 11U) - 5) / 8.0F;
+    std::vector<float> expected[2];
+    for (int e = 0; e < 2; ++e) {
+        orc_expert ex{};
+        ex.gate = {1, (uint32_t)intermediate_columns, (uint32_t)hidden_columns, h[3 * e].weights.data(), h[3 * e].scales.data(), gs[3 * e]};
+        ex.up = {1, (uint32_t)intermediate_columns, (uint32_t)hidden_columns, h[3 * e + 1].weights.data(), h[3 * e + 1].scales.data(), gs[3 * e + 1]};
+        ex.down = {1, (uint32_t)hidden_columns, (uint32_t)intermediate_columns, h[3 * e + 2].weights.data(), h[3 * e + 2].scales.data(), gs[3 * e + 2]};
+        expected[e].resize(static_cast<std::size_t>(rows) * hidden_columns);
+        std::vector<float> a(intermediate_columns), u(intermediate_columns);
+        for (std::uint32_t r = 0; r < rows; ++r)
+            REQUIRE(orc_expert_ffn(&ex, hidden.data() + static_cast<std::size_t>(r) * hidden_columns, 1.0F, 0, 0, a.data(), u.data(),
+                                   expected[e].data() + static_cast<std::size_t>(r) * hidden_columns) == 0);
+    }
+    const std::array<strata::CudaMoeExpert, 2> routed{{
+        {&gate0, &up0, &down0, 1.0F},
+        {&gate1, &up1, &down1, 1.0F},
+    }};
+    std::vector<float> routed_output(2U * rows * hidden_columns), none;
+    REQUIRE(backend.enqueue_moe(device, hidden, rows, routed, nullptr).ok());
+    REQUIRE(backend.collect_moe(device, routed_output, none).ok());
+    double num = 0.0, den = 0.0;
+    for (int e = 0; e < 2; ++e)
+        for (std::size_t index = 0U; index < expected[e].size(); ++index) {
+            const double d = static_cast<double>(routed_output[e * expected[e].size() + index]) - expected[e][index];
+            num += d * d;
+            den += static_cast<double>(expected[e][index]) * expected[e][index];
+        }
+    const double rel = std::sqrt(num / den);
+    std::printf("laguna nvfp4 command: relative L2 difference to the checker %.3e\n", rel);
+    REQUIRE(den > 0.0 && rel <= 2.0e-5);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -477,6 +561,7 @@ int main(int argc, char** argv) {
         return g_failures == 0 ? 0 : 1;
     }
     glm_int4_target_shape_command();
+    laguna_nvfp4_command();
     deepseek_exact_commands<128U, 128U>();
     deepseek_exact_commands<4096U, 2048U>();
 #ifdef STRATA_TEST_REFERENCE_BACKEND
