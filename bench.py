@@ -132,6 +132,45 @@ def measured_traffic(workload, tokens, kernel):
     return table.get(f"{workload}/T{tokens}/{kernel}")
 
 
+def reference_gpu_commands():
+    """The reference's own CUDA backend (compiled unmodified for sm_100a by oracle/build.py, a checker like the CPU arm)
+    and this library, each timing the same GLM INT4 MoE command -- 8 routed experts applied to R rows at hidden 6144 /
+    intermediate 2048, host fp32 rows in and out, wall clock around enqueue + collect -- through the same C++ program
+    (tests/cpp/backend_shim_test.cpp --time).  None when the prebuilt reference executable did not travel."""
+    import re
+    import tempfile
+    ref_exe = os.path.join(ROOT, "oracle", "_ref", "backend_shim_test_ref")
+    if not os.path.exists(ref_exe):
+        return None
+    pat = re.compile(r"(\d+) experts x (\d+) rows: ([0-9.]+) ms per command")
+
+    def run(exe):
+        r = subprocess.run([exe, "--time"], capture_output=True, text=True, timeout=300)
+        if r.returncode != 0:
+            return None
+        return {int(m.group(2)): float(m.group(3)) for m in pat.finditer(r.stdout)}
+    try:
+        ref = run(ref_exe)
+        with tempfile.TemporaryDirectory() as tmp:
+            ours_exe = os.path.join(tmp, "shim_time")
+            lib_dir, orc_dir = os.path.join(ROOT, "strata_b200"), os.path.join(ROOT, "oracle")
+            c = subprocess.run(["g++", "-std=c++20", "-O1", "-I", os.path.join(ROOT, "include"),
+                                os.path.join(ROOT, "tests", "cpp", "backend_shim_test.cpp"), "-o", ours_exe,
+                                "-L", lib_dir, "-lstrata_moe", "-L", orc_dir, "-lmoe_oracle",
+                                f"-Wl,-rpath,{lib_dir}", f"-Wl,-rpath,{orc_dir}"], capture_output=True, text=True)
+            ours = run(ours_exe) if c.returncode == 0 else None
+    except (OSError, subprocess.SubprocessError):
+        return None
+    if not ref or not ours:
+        return None
+    return {"what": "GLM INT4 MoE command, 8 routed experts x R rows, hidden 6144 / intermediate 2048, host fp32 rows in and out, "
+                    "wall clock around enqueue + collect, best of 5; the reference's CUDA backend compiled unmodified for sm_100a "
+                    "against this library through the C++ shim, same program",
+            "rows": sorted(ref), "reference_ms": [ref[r] for r in sorted(ref)],
+            "this_library_ms": [ours.get(r) for r in sorted(ref)],
+            "speedup": [round(ref[r] / ours[r], 2) if ours.get(r) else None for r in sorted(ref)]}
+
+
 def expert_weight_bytes(cfg):
     from strata_b200 import synth
     return sum(sum(synth.expert_bytes(cfg, r)) for r in synth.ROLES)
@@ -437,6 +476,10 @@ def run_single(args, cfg, T):
     line["clocks"] = clocks
     if sub:
         line["sub"] = sub
+    if args.sub:
+        ref_gpu = reference_gpu_commands()
+        if ref_gpu:
+            line["reference_gpu"] = ref_gpu
     return line
 
 
