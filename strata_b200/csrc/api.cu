@@ -2421,7 +2421,7 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     cudaStream_t s = ctx->stream;
     const uint32_t par = ep->w.step & 1u, B = L->d.expert_count;
     launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
-    if (expected_rows == 0) expected_rows = ep->T * L->d.top_k ? ep->T * L->d.top_k : 1u;
+    if (expected_rows == 0) expected_rows = ep->T != 0u ? ep->T * L->d.top_k : 1u;
     // When the whole step runs on the tensor-core path its down kernel stores the f16 rows the peers will read (unit
     // row factors) straight into the window; otherwise the fp32 outputs leave through a conversion pass as f16 rows
     // with an exact per-row power-of-two scale.

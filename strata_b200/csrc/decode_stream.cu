@@ -62,7 +62,6 @@ struct ScaleGeo {
 
 template <int FMT, int NT, bool SPLIT>
 struct StreamGeo {
-    static constexpr uint32_t kXRows = 8u * NT * (SPLIT ? 2u : 1u);
     // weights: [tile p][k half][64 rows][128 B], each box 1024-byte aligned (swizzle atom)
     static constexpr uint32_t kWOff = 0;
     static constexpr uint32_t kSOff = 4u * kBoxBytes;                               // scales: [tile p][64 rows][pitch]
