@@ -2227,10 +2227,7 @@ int strata_moe_command_collect_rows_dsv4(strata_moe_ctx* ctx, float* routed_out,
 struct strata_moe_ep {
     strata_moe_layer* L = nullptr;
     EpWindows w{};
-    uint32_t* dst_row = nullptr;    // [E]
-    uint32_t* loffsets = nullptr;   // [B + 1]
-    uint32_t* abort_word = nullptr;
-    uint32_t* done = nullptr;
+    EpPlan pl{};                    // device tables of the step (layer scratch)
     const __nv_bfloat16* x = nullptr;   // inputs of the step in progress
     uint32_t T = 0;
     int stage = 0;                  // 0 idle, 1 counts published, 2 rows sent, 3 experts done
@@ -2239,7 +2236,8 @@ struct strata_moe_ep {
 
 size_t strata_moe_ep_window_bytes(const strata_moe_layer_desc* desc, uint32_t world, uint32_t row_capacity) {
     if (!desc || world == 0 || world > kEpMaxWorld || row_capacity == 0) return 0;
-    return ep_window_bytes(world, desc->experts, desc->hidden, row_capacity);
+    if (desc->top_k == 0 || desc->top_k > 32u) return 0;
+    return ep_window_bytes(world, desc->experts, desc->hidden, row_capacity, desc->top_k);
 }
 
 int strata_moe_ep_window_alloc(strata_moe_ctx* ctx, size_t bytes, void** window, void* handle64) {
@@ -2299,6 +2297,8 @@ int strata_moe_ep_create(strata_moe_layer* L, uint32_t rank, uint32_t world, uin
     if (world == 0 || world > kEpMaxWorld || rank >= world)
         return fail(ctx, STRATA_MOE_E_INVALID, "world must be 1..16 and rank below it");
     if (d.experts % world) return fail(ctx, STRATA_MOE_E_INVALID, "experts must divide evenly over the ranks");
+    if (d.experts > 1024u) return fail(ctx, STRATA_MOE_E_INVALID, "expert parallelism supports at most 1024 experts");
+    if (d.top_k > 32u) return fail(ctx, STRATA_MOE_E_INVALID, "expert parallelism supports top_k up to 32");
     const uint32_t B = d.experts / world;
     if (d.expert_count != B || d.expert_begin != rank * B)
         return fail(ctx, STRATA_MOE_E_INVALID, "layer must hold exactly this rank's block of experts");
@@ -2320,13 +2320,22 @@ int strata_moe_ep_create(strata_moe_layer* L, uint32_t rank, uint32_t world, uin
     ep->w.H = d.hidden;
     ep->w.cap = row_capacity;
     ep->w.step = 0;
+    ep->w.k = d.top_k;
     ep->w.wait_ns = (unsigned long long)(wait_ms ? wait_ms : 10000u) * 1000000ull;
-    cudaError_t e = dalloc(L, &ep->dst_row, (size_t)d.experts);
-    if (e == cudaSuccess) e = dalloc(L, &ep->loffsets, (size_t)B + 1);
-    if (e == cudaSuccess) e = dalloc(L, &ep->abort_word, 1);
-    if (e == cudaSuccess) e = dalloc(L, &ep->done, 1);
-    if (e == cudaSuccess) e = cudaMemset(ep->done, 0, sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemset(ep->abort_word, 0, sizeof(uint32_t));
+    EpPlan& pl = ep->pl;
+    pl.stride = d.max_tokens;
+    cudaError_t e = dalloc(L, &pl.dst_row, (size_t)d.experts);
+    if (e == cudaSuccess) e = dalloc(L, &pl.loffsets, (size_t)B + 1);
+    if (e == cudaSuccess) e = dalloc(L, &pl.vis_idx, (size_t)world * d.max_tokens);
+    if (e == cudaSuccess) e = dalloc(L, &pl.nvis, (size_t)kEpMaxWorld);
+    if (e == cudaSuccess) e = dalloc(L, &pl.tok_base, (size_t)kEpMaxWorld);
+    if (e == cudaSuccess) e = dalloc(L, &pl.vis_total, 1);
+    if (e == cudaSuccess) e = dalloc(L, &pl.abort_word, 1);
+    if (e == cudaSuccess) e = dalloc(L, &pl.done, 1);
+    if (e == cudaSuccess) e = cudaMemset(pl.done, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(pl.abort_word, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(pl.nvis, 0, kEpMaxWorld * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(pl.vis_total, 0, sizeof(uint32_t));
     if (e != cudaSuccess) {
         delete ep;
         return fail(ctx, STRATA_MOE_E_CUDA, std::string("ep allocation: ") + cudaGetErrorString(e));
@@ -2382,8 +2391,9 @@ int strata_moe_ep_begin(strata_moe_ep* ep, const void* x, uint32_t T) {
     }
     // The step number advances only once nothing on the host can fail any more: a begin that
     // returned an error must leave this rank in step with its peers.
+    launch_ep_visits(ep->w, ep->pl, L->ids, T, s);
     ep->w.step += 1;
-    launch_ep_publish(ep->w, L->counts, s);
+    launch_ep_publish(ep->w, ep->pl, L->counts, s);
     if (cudaError_t e = cudaGetLastError(); e != cudaSuccess) {
         ep->w.step -= 1;
         return fail(ctx, STRATA_MOE_E_CUDA, std::string("ep publish launch: ") + cudaGetErrorString(e));
@@ -2402,9 +2412,8 @@ int strata_moe_ep_dispatch(strata_moe_ep* ep) {
     CK(cudaSetDevice(ctx->device));
     bind_ws(L);
     cudaStream_t s = ctx->stream;
-    launch_ep_plan(ep->w, ep->dst_row, ep->loffsets, ep->abort_word, ctx->d_status, s);
-    launch_ep_dispatch(ep->w, ep->x, L->ids, L->perm, L->offsets, ep->dst_row, ep->T * L->d.top_k, L->d.top_k,
-                       ep->abort_word, ep->done, s);
+    launch_ep_plan(ep->w, ep->pl, ctx->d_status, s);
+    launch_ep_dispatch(ep->w, ep->pl, ep->x, L->ids, L->inv, L->offsets, L->weights, ep->T, s);
     CK(cudaGetLastError());
     ep->stage = 2;
     return 0;
@@ -2420,20 +2429,18 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     bind_ws(L);
     cudaStream_t s = ctx->stream;
     const uint32_t par = ep->w.step & 1u, B = L->d.expert_count;
-    launch_ep_wait(ep->w, 1, ep->abort_word, ctx->d_status, s);
+    launch_ep_wait(ep->w, 1, ep->pl.abort_word, ctx->d_status, s);
     if (expected_rows == 0) expected_rows = ep->T != 0u ? ep->T * L->d.top_k : 1u;
-    // When the whole step runs on the tensor-core path its down kernel stores the f16 rows the peers will read (unit
-    // row factors) straight into the window; otherwise the fp32 outputs leave through a conversion pass as f16 rows
-    // with an exact per-row power-of-two scale.
-    const uint32_t est = expected_rows < ep->w.cap ? expected_rows : ep->w.cap;
-    bool direct = use_prefill(L, est, B) && !L->knobs.no_half_y;
-    float* y = direct ? reinterpret_cast<float*>(ep->w.y(ep->w.rank, par)) : L->y;
-    int rc = run_experts(L, ep->w.rows(ep->w.rank, par), nullptr, 1, ep->w.cap, B, ep->loffsets, nullptr, nullptr,
-                         ep->w.cap, y, expected_rows, ep->loffsets + B, false, &direct, ep->w.yscale(ep->w.rank, par));
+    // The experts read their grouped rows out of the received token rows through the slot table the
+    // sources filled (one token row serves all of the token's experts here); the tensor-core path
+    // leaves its outputs as f16 rows, the others as fp32, and the partial-sum pass takes either.
+    const uint32_t* total = ep->pl.loffsets + B;
+    bool half = true;
+    int rc = run_experts(L, ep->w.rows(ep->w.rank, par), ep->w.src_of(ep->w.rank, par), 1, ep->w.cap, B,
+                         ep->pl.loffsets, nullptr, nullptr, ep->w.cap, L->y, expected_rows, total, false, &half,
+                         nullptr);
     if (rc) return rc;
-    if (!direct)
-        launch_rows_to_f16_f32(L->y, 0, ep->w.cap, L->d.hidden, ep->w.y(ep->w.rank, par), nullptr,
-                               ep->w.yscale(ep->w.rank, par), s, ep->loffsets + B);
+    launch_ep_partial(ep->w, ep->pl, L->y, half, ctx->d_status, s);
     launch_ep_signal(ep->w, 2, s);
     CK(cudaGetLastError());
     ep->stage = 3;
@@ -2458,9 +2465,8 @@ int strata_moe_ep_finish(strata_moe_ep* ep, float* out) {
     }
     // one CTA waits for the peers' results; the combine kernel's own check then passes at once, so its CTAs never sit
     // on SMs spinning (a second step in flight on another stream may need them for its GEMMs)
-    launch_ep_wait(ep->w, 2, ep->abort_word, ctx->d_status, s);
-    launch_ep_combine(ep->w, L->ids, L->inv, L->offsets, ep->dst_row, L->weights, shared, ep->T, L->d.top_k,
-                      L->d.output_scale, out, ep->abort_word, ctx->d_status, s);
+    launch_ep_wait(ep->w, 2, ep->pl.abort_word, ctx->d_status, s);
+    launch_ep_combine(ep->w, ep->pl, shared, ep->T, L->d.output_scale, out, ctx->d_status, s);
     CK(cudaGetLastError());
     ep->stage = 0;
     ctx->stats.forward_calls++;

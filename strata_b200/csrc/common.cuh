@@ -188,16 +188,20 @@ constexpr uint32_t kEpMaxWorld = 16;
 // bits, half the bytes of fp32); the home rank widens them back while it forms the weighted sum.
 struct EpWindows {
     uint8_t* win[kEpMaxWorld];
-    uint32_t world, rank, E, H, cap, step;
+    uint32_t world, rank, E, H, cap, step, k;
     unsigned long long wait_ns;
     __host__ __device__ static size_t up256(size_t v) { return (v + 255u) / 256u * 256u; }
     __host__ __device__ size_t flags_bytes() const { return up256((size_t)3 * kEpMaxWorld * 4u); }
     __host__ __device__ size_t counts_bytes() const { return up256((size_t)2 * world * E * 4u); }
+    __host__ __device__ size_t visits_bytes() const { return up256((size_t)2 * kEpMaxWorld * kEpMaxWorld * 4u); }
     __host__ __device__ size_t rows_bytes() const { return up256((size_t)2 * cap * H * 2u); }
     __host__ __device__ size_t y_bytes() const { return up256((size_t)2 * cap * H * 2u); }
     __host__ __device__ size_t yscale_bytes() const { return up256((size_t)2 * cap * 4u); }
+    __host__ __device__ size_t src_of_bytes() const { return up256((size_t)2 * cap * 4u); }
+    __host__ __device__ size_t vis_bytes() const { return up256((size_t)2 * cap * k * 4u); }
     __host__ __device__ size_t total_bytes() const {
-        return flags_bytes() + counts_bytes() + rows_bytes() + y_bytes() + yscale_bytes();
+        return flags_bytes() + counts_bytes() + visits_bytes() + rows_bytes() + y_bytes() + yscale_bytes() +
+               src_of_bytes() + 2u * vis_bytes();
     }
     __host__ __device__ uint32_t* flag(uint32_t r, uint32_t kind, uint32_t src) const {
         return reinterpret_cast<uint32_t*>(win[r]) + kind * kEpMaxWorld + src;
@@ -205,30 +209,59 @@ struct EpWindows {
     __host__ __device__ uint32_t* counts(uint32_t r, uint32_t parity, uint32_t src) const {
         return reinterpret_cast<uint32_t*>(win[r] + flags_bytes()) + ((size_t)parity * world + src) * E;
     }
+    // visits(r, p, s)[o] = token rows rank s sends to owner o in a step of parity p (every rank holds the full matrix)
+    __host__ __device__ uint32_t* visits(uint32_t r, uint32_t parity, uint32_t src) const {
+        return reinterpret_cast<uint32_t*>(win[r] + flags_bytes() + counts_bytes()) +
+               ((size_t)parity * kEpMaxWorld + src) * kEpMaxWorld;
+    }
+    __host__ __device__ size_t rows_at() const { return flags_bytes() + counts_bytes() + visits_bytes(); }
     __host__ __device__ __nv_bfloat16* rows(uint32_t r, uint32_t parity) const {
-        return reinterpret_cast<__nv_bfloat16*>(win[r] + flags_bytes() + counts_bytes()) + (size_t)parity * cap * H;
+        return reinterpret_cast<__nv_bfloat16*>(win[r] + rows_at()) + (size_t)parity * cap * H;
     }
     __host__ __device__ unsigned short* y(uint32_t r, uint32_t parity) const {   // f16 bit patterns
-        return reinterpret_cast<unsigned short*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes()) +
-               (size_t)parity * cap * H;
+        return reinterpret_cast<unsigned short*>(win[r] + rows_at() + rows_bytes()) + (size_t)parity * cap * H;
     }
     __host__ __device__ float* yscale(uint32_t r, uint32_t parity) const {
-        return reinterpret_cast<float*>(win[r] + flags_bytes() + counts_bytes() + rows_bytes() + y_bytes()) +
+        return reinterpret_cast<float*>(win[r] + rows_at() + rows_bytes() + y_bytes()) + (size_t)parity * cap;
+    }
+    __host__ __device__ uint32_t* src_of(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<uint32_t*>(win[r] + rows_at() + rows_bytes() + y_bytes() + yscale_bytes()) +
                (size_t)parity * cap;
     }
+    __host__ __device__ uint32_t* vis_pos(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<uint32_t*>(win[r] + rows_at() + rows_bytes() + y_bytes() + yscale_bytes() +
+                                           src_of_bytes()) + (size_t)parity * cap * k;
+    }
+    __host__ __device__ float* vis_w(uint32_t r, uint32_t parity) const {
+        return reinterpret_cast<float*>(win[r] + rows_at() + rows_bytes() + y_bytes() + yscale_bytes() +
+                                        src_of_bytes() + vis_bytes()) + (size_t)parity * cap * k;
+    }
 };
-size_t ep_window_bytes(uint32_t world, uint32_t E, uint32_t H, uint32_t cap);
-void launch_ep_publish(const EpWindows& w, const uint32_t* counts, cudaStream_t s);
-void launch_ep_plan(const EpWindows& w, uint32_t* dst_row, uint32_t* loffsets, uint32_t* abort_word,
-                    uint32_t* status, cudaStream_t s);
-void launch_ep_dispatch(const EpWindows& w, const __nv_bfloat16* x, const uint32_t* ids, const uint32_t* perm,
-                        const uint32_t* offsets, const uint32_t* dst_row, uint32_t pairs, uint32_t k,
-                        const uint32_t* abort_word, uint32_t* done, cudaStream_t s);
+// Device-side tables of one rank's step (all in the layer's scratch).
+struct EpPlan {
+    uint32_t* dst_row;     // [E]      first row, in the owner's grouped order, of this rank's pairs for expert e
+    uint32_t* loffsets;    // [B + 1]  row ranges of this rank's local experts over all sources
+    uint32_t* vis_idx;     // [world][stride]  index of token t among the rows this rank sends to owner o, or ~0
+    uint32_t* nvis;        // [world]  rows this rank sends to owner o
+    uint32_t* tok_base;    // [world]  first slot, in owner o's window, of this rank's token rows
+    uint32_t* vis_total;   // [1]      token rows this rank received as an owner
+    uint32_t* abort_word;
+    uint32_t* done;
+    uint32_t stride;       // tokens per row of vis_idx
+};
+size_t ep_window_bytes(uint32_t world, uint32_t E, uint32_t H, uint32_t cap, uint32_t k);
+void launch_ep_visits(const EpWindows& w, const EpPlan& pl, const uint32_t* ids, uint32_t T, cudaStream_t s);
+void launch_ep_publish(const EpWindows& w, const EpPlan& pl, const uint32_t* counts, cudaStream_t s);
+void launch_ep_plan(const EpWindows& w, const EpPlan& pl, uint32_t* status, cudaStream_t s);
+void launch_ep_dispatch(const EpWindows& w, const EpPlan& pl, const __nv_bfloat16* x, const uint32_t* ids,
+                        const uint32_t* inv, const uint32_t* offsets, const float* weights, uint32_t T,
+                        cudaStream_t s);
 void launch_ep_wait(const EpWindows& w, uint32_t kind, uint32_t* abort_word, uint32_t* status, cudaStream_t s);
 void launch_ep_signal(const EpWindows& w, uint32_t kind, cudaStream_t s);
-void launch_ep_combine(const EpWindows& w, const uint32_t* ids, const uint32_t* inv, const uint32_t* offsets,
-                       const uint32_t* dst_row, const float* weights, const float* shared, uint32_t T, uint32_t k,
-                       float output_scale, float* out, uint32_t* abort_word, uint32_t* status, cudaStream_t s);
+void launch_ep_partial(const EpWindows& w, const EpPlan& pl, const void* y, bool y_half, uint32_t* status,
+                       cudaStream_t s);
+void launch_ep_combine(const EpWindows& w, const EpPlan& pl, const float* shared, uint32_t T, float output_scale,
+                       float* out, uint32_t* status, cudaStream_t s);
 
 // dsv4_exact.cu : bit-exact DeepSeek-V4 numerical mode (CUDA-core kernels, reference summation order)
 void launch_dsv4_quantize(const float* src, const uint32_t* perm, uint32_t k_div, uint32_t rows, uint32_t cols,

@@ -113,18 +113,34 @@ __global__ void __launch_bounds__(256) group_hist_kernel(const uint32_t* __restr
         for (uint32_t e = lane; e < nexp; e += 32u) hist[(size_t)seg * nexp + e] = h[e];
 }
 
-// B: per expert, exclusive scan over segments (in place) and total count
-__global__ void group_segscan_kernel(uint32_t* __restrict__ hist, uint32_t nseg, uint32_t nexp,
-                                     uint32_t* __restrict__ counts) {
-    const uint32_t e = blockIdx.x * blockDim.x + threadIdx.x;
+// B: per expert, exclusive scan over segments (in place) and total count.  One warp per expert,
+// 128 segments per round: the four loads of a round are issued together, a shuffle scan orders them.
+__global__ void __launch_bounds__(256) group_segscan_kernel(uint32_t* __restrict__ hist, uint32_t nseg,
+                                                            uint32_t nexp, uint32_t* __restrict__ counts) {
+    const uint32_t e = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
     if (e >= nexp) return;
     uint32_t run = 0;
-    for (uint32_t s = 0; s < nseg; ++s) {
-        const uint32_t v = hist[(size_t)s * nexp + e];
-        hist[(size_t)s * nexp + e] = run;
-        run += v;
+    for (uint32_t b = 0; b < nseg; b += 128u) {
+        uint32_t v[4];
+#pragma unroll
+        for (uint32_t q = 0; q < 4u; ++q) {
+            const uint32_t sidx = b + q * 32u + lane;
+            v[q] = sidx < nseg ? hist[(size_t)sidx * nexp + e] : 0u;
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 4u; ++q) {
+            uint32_t incl = v[q];
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+                if ((int)lane >= off) incl += t;
+            }
+            const uint32_t sidx = b + q * 32u + lane;
+            if (sidx < nseg) hist[(size_t)sidx * nexp + e] = run + incl - v[q];
+            run += __shfl_sync(0xFFFFFFFFu, incl, 31);
+        }
     }
-    counts[e] = run;
+    if (lane == 0) counts[e] = run;
 }
 
 // C: offsets = exclusive scan of counts; active list
@@ -206,7 +222,7 @@ void launch_group(const uint32_t* ids, uint32_t pairs, uint32_t expert_begin, ui
     const uint32_t blocks = (nseg + 7) / 8;
     const size_t smem = 8u * (size_t)n_experts * sizeof(uint32_t);
     group_hist_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, hist);
-    group_segscan_kernel<<<(n_experts + 127) / 128, 128, 0, s>>>(hist, nseg, n_experts, counts);
+    group_segscan_kernel<<<(n_experts + 7) / 8, 256, 0, s>>>(hist, nseg, n_experts, counts);
     group_offsets_kernel<<<1, 1024, 0, s>>>(counts, n_experts, offsets, active_list, n_active);
     group_scatter_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, hist, offsets,
                                                    perm, inv);
@@ -286,7 +302,7 @@ extern "C" int strata_moe_group_static(void* stream, const uint32_t* ids, uint32
     const uint32_t blocks = (nseg + 7) / 8;
     const size_t smem = 8u * (size_t)n_experts * sizeof(uint32_t);
     if (nseg) group_hist_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, scratch);
-    group_segscan_kernel<<<(n_experts + 127) / 128, 128, 0, s>>>(scratch, nseg, n_experts, counts);
+    group_segscan_kernel<<<(n_experts + 7) / 8, 256, 0, s>>>(scratch, nseg, n_experts, counts);
     group_offsets_kernel<<<1, 1024, 0, s>>>(counts, n_experts, offsets, nullptr, nullptr);
     if (nseg)
         group_scatter_kernel<<<blocks, 256, smem, s>>>(ids, pairs, expert_begin, n_experts, scratch, offsets, perm,
