@@ -402,15 +402,20 @@ int strata_moe_quantize_e4m3(strata_moe_ctx* ctx, float* values, uint32_t rows, 
  * enqueue/collect); these calls replace that transport for one rank per GPU.  Rank r holds the
  * experts [r * E / world, (r + 1) * E / world) (a layer created with that expert_begin /
  * expert_count) and its own tokens.  Each rank owns a "window" of device memory that all peers
- * map; the dispatch kernel stores token rows straight into the owners' windows and the combine
- * kernel loads expert outputs straight from them (NVLink peer loads and stores, flags with
- * release/acquire at system scope, every wait bounded by wait_ms).
+ * map; the dispatch kernel stores a token's row straight into the window of every rank that owns
+ * one of its selected experts (once per owner, however many of that owner's experts were selected),
+ * the owner forms the routing-weighted sum of its experts' outputs for the token, and the combine
+ * kernel loads those partial sums straight from the owners' windows and adds them in rank order
+ * (NVLink peer loads and stores, flags with release/acquire at system scope, every wait bounded by
+ * wait_ms).  The partial sums travel as f16 rows with an exact power-of-two factor per row, so a
+ * step agrees with the single-GPU forward to f16 rounding of the partial sums, not bit for bit.
+ * Limits: experts <= 1024, top_k <= 32.
  *
  * Set-up: every rank calls ep_window_bytes (same arguments everywhere), ep_window_alloc, sends
  * the 64-byte handle to its peers by any host channel, opens the peers' handles with
  * ep_window_open, passes the `world` window pointers (its own at index rank) to ep_create, and
- * the ranks synchronise on the host once before the first step.  row_capacity bounds the rows a
- * rank can receive in one step; a step that would exceed it on any rank stores nothing, computes
+ * the ranks synchronise on the host once before the first step.  row_capacity bounds the (token,
+ * expert) pairs a rank can receive in one step; a step that would exceed it on any rank stores nothing, computes
  * nothing and reports STRATA_MOE_E_NUMERIC ("inconsistent group table") at the next synchronize
  * on every rank.  A rank that stops taking part makes its peers' waits run out after wait_ms
  * (0 = 10 s): "bounded wait timed out" from synchronize, context still usable. */

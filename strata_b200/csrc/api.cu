@@ -78,7 +78,7 @@ struct LayerKnobs {
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
     int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
-    int host_chunks = 0;            // STRATA_MOE_HOST_CHUNKS: token chunks of a host-buffer call (0 = 2 from 4096 tokens, else 1)
+    int host_chunks = 0;            // STRATA_MOE_HOST_CHUNKS: token chunks of a host-buffer call (0 = chosen from the rows per expert)
     int stream_ring_max_rows = 8;   // STRATA_MOE_STREAM_RING_MAX_ROWS: largest token tile (8 or 16) given to the ring kernels
 };
 
@@ -1382,11 +1382,20 @@ int strata_moe_forward_host(strata_moe_layer* L, const void* x_host, uint32_t T,
     // back to the host run on their own streams while chunk i computes.  Tokens are independent, so the result is
     // bit-identical to the one-piece call; the expert GEMMs see fewer rows per expert per chunk, which costs less than
     // the copies it hides (16384 tokens of c3: 235 MB in, 470 MB out, about 14 ms of PCIe time beside 12 ms of compute).
-    // by default two chunks, and only while a chunk still brings every expert a full 192-token tile on average: with
-    // fewer rows per expert the GEMMs lose more than the copies hide (4096 tokens of c2 in two chunks: 606 k tokens/s
-    // end to end against 685 k in one piece; 16384 tokens of c3: 821 k against 680 k)
-    const bool chunk_pays = T >= 4096u && (uint64_t)(T / 2u) * L->d.top_k >= 192ull * L->d.experts;
-    uint32_t parts = L->knobs.host_chunks > 0 ? (uint32_t)L->knobs.host_chunks : (chunk_pays ? 2u : 1u);
+    // by default up to three chunks, and only while a chunk still brings every expert most of a 192-token tile on
+    // average: with fewer rows per expert the GEMMs lose more than the copies hide (4096 tokens of c2 in two chunks:
+    // 606 k tokens/s end to end against 685 k in one piece; 16384 tokens of c3: 680 k in one piece, 851 k in two
+    // chunks, 981 k in three -- 171 rows per expert, still one tile each -- and 935 k in four)
+    uint32_t parts = 1u;
+    if (L->knobs.host_chunks > 0) {
+        parts = (uint32_t)L->knobs.host_chunks;
+    } else if (T >= 4096u) {
+        for (uint32_t p = 3u; p >= 2u; --p)
+            if ((uint64_t)(T / p) * L->d.top_k >= 160ull * L->d.experts) {
+                parts = p;
+                break;
+            }
+    }
     if (parts > 4u) parts = 4u;
     if (parts > T) parts = T;
     // only while every chunk stays on the expert path the whole batch would take (the tensor-core path): the paths

@@ -102,6 +102,32 @@ def test_peer_steps_match_single_gpu(world, fmt, T_local):
         ranks.close()
 
 
+def test_peer_full_shape_c3_two_ranks():
+    """The bench's workload (c3: 16384 tokens, 256 MXFP4 experts, top-8, hidden 7168) over two ranks stepped by one
+    process: every owner runs the tensor-core path on 65536 grouped rows read through the slot table from 8192 + 8192
+    token rows, and returns one partial sum per token.  Both window parities must give the same bits."""
+    cfg = synth.CONFIGS["c3"]
+    world, T = 2, cfg.T
+    T_local = T // world
+    ranks = Ranks(cfg, world, T_local, cap=T_local * cfg.k * 3 // 2)
+    try:
+        x = synth.gen_inputs(cfg, T, seed=5).cuda()
+        xs = [x[r * T_local:(r + 1) * T_local].contiguous() for r in range(world)]
+        first, _ = ranks.step(xs)
+        first = torch.cat([first[r] for r in range(world)], 0).clone()
+        second, _ = ranks.step(xs)
+        second = torch.cat([second[r] for r in range(world)], 0)
+        assert torch.equal(first, second)
+    finally:
+        ranks.close()
+    ref, _ = reference(cfg, x)
+    rel = ((second - ref).norm() / ref.norm()).item()
+    assert rel <= 2e-3, rel
+    # per token too: no row may be off by more than f16 rounding of a few partial sums allows
+    worst = ((second - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-6)).max().item()
+    assert worst <= 1e-2, worst
+
+
 def test_peer_overflow_is_reported_by_every_rank_and_next_step_works():
     cfg = synth.MoeConfig("ep_over", H=256, I=128, E=8, k=2, fmt=0, T=64, seed=3, zipf_s=1.4)
     world, T_local = 2, 32
