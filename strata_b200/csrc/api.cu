@@ -78,6 +78,7 @@ struct LayerKnobs {
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
     int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
+    int no_spread = 0;              // STRATA_MOE_NO_SPREAD=1: operand conversion per grouped row instead of per source row
     int host_chunks = 0;            // STRATA_MOE_HOST_CHUNKS: token chunks of a host-buffer call (0 = chosen from the rows per expert)
     int stream_ring_max_rows = 8;   // STRATA_MOE_STREAM_RING_MAX_ROWS: largest token tile (8 or 16) given to the ring kernels
 };
@@ -101,6 +102,7 @@ static LayerKnobs read_knobs() {
     k.fast_router_min_tokens = num("STRATA_MOE_FAST_ROUTER_MIN_TOKENS", 0);
     k.stream_ring_max_rows = num("STRATA_MOE_STREAM_RING_MAX_ROWS", 8);
     k.host_chunks = num("STRATA_MOE_HOST_CHUNKS", 0);
+    k.no_spread = num("STRATA_MOE_NO_SPREAD", 0);
     return k;
 }
 
@@ -448,13 +450,21 @@ int run_router(strata_moe_layer* L, const __nv_bfloat16* x, uint32_t T, float* l
     return 0;
 }
 
+// Source rows that each feed k grouped rows: dest[t * k + j] is the grouped row of source row t's j-th use
+// (0xFFFFFFFF = none).  Lets the operand conversion of the tensor-core path read and convert a row once.
+struct SpreadRows {
+    const uint32_t* dest;
+    uint32_t rows, k;
+    const uint32_t* rows_dev;   // device-side count of source rows, or null
+};
+
 // Expert FFN over grouped rows.  x_nat: rows in natural column order (group order).
 // If x_kperm is non-null it already holds the K-permuted copy.
 int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t* perm, uint32_t k_div,
                 uint32_t pairs, uint32_t n_groups, const uint32_t* offsets, const uint32_t* active,
                 const uint32_t* n_active, uint32_t max_rows, float* y, uint32_t expected_pairs = 0,
                 const uint32_t* pairs_dev = nullptr, bool x_ready = false, bool* y_half = nullptr,
-                float* y_rowscale_out = nullptr) {
+                float* y_rowscale_out = nullptr, const SpreadRows* spread = nullptr) {
     // `pairs` bounds the row count.  When the exact count exists only on the device (rows received
     // from other ranks) pairs_dev points at it and expected_pairs steers the host-side heuristics.
     Range range("strata_moe.experts");
@@ -465,7 +475,13 @@ int run_experts(strata_moe_layer* L, const __nv_bfloat16* x_src, const uint32_t*
     if (pairs_dev && expected_pairs) pairs = expected_pairs < bound ? expected_pairs : bound;
     // x_ready: the caller's front-end kernel already left the f16 rows and their factors in the workspace
     if (use_prefill(L, pairs, n_groups)) {
-        if (!x_ready) launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        if (!x_ready) {
+            if (spread && !L->knobs.no_spread)
+                launch_rows_to_f16_spread(x_src, spread->dest, spread->k, spread->rows, spread->rows_dev, bound,
+                                          L->d.hidden, L->xg, L->x_rowscale, s);
+            else
+                launch_rows_to_f16_bf16(x_src, perm, k_div, bound, L->d.hidden, L->xg, L->x_rowscale, s, pairs_dev);
+        }
         mark(ctx, 4);
         PrefillArgs p{};
         p.fmt = L->d.format;
@@ -1303,8 +1319,9 @@ int strata_moe_forward(strata_moe_layer* L, const void* x, uint32_t T, float* ou
         mark(ctx, 3);
     }
     bool y_half = true;
+    const SpreadRows spread{L->inv, T, d.top_k, nullptr};
     rc = run_experts(L, xb, perm, d.top_k, P, d.experts, offsets, L->active, L->n_active, T, L->y, 0, nullptr, x_ready,
-                     &y_half);
+                     &y_half, nullptr, d.top_k <= 32u ? &spread : nullptr);
     if (rc) return rc;
     const float* shared = nullptr;
     if (fork_shared) {
@@ -2444,10 +2461,11 @@ int strata_moe_ep_experts(strata_moe_ep* ep, uint32_t expected_rows) {
     // sources filled (one token row serves all of the token's experts here); the tensor-core path
     // leaves its outputs as f16 rows, the others as fp32, and the partial-sum pass takes either.
     const uint32_t* total = ep->pl.loffsets + B;
+    const SpreadRows spread{ep->w.vis_pos(ep->w.rank, par), ep->w.cap, L->d.top_k, ep->pl.vis_total};
     bool half = true;
     int rc = run_experts(L, ep->w.rows(ep->w.rank, par), ep->w.src_of(ep->w.rank, par), 1, ep->w.cap, B,
                          ep->pl.loffsets, nullptr, nullptr, ep->w.cap, L->y, expected_rows, total, false, &half,
-                         nullptr);
+                         nullptr, &spread);
     if (rc) return rc;
     launch_ep_partial(ep->w, ep->pl, L->y, half, ctx->d_status, s);
     launch_ep_signal(ep->w, 2, s);

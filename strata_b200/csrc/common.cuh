@@ -114,6 +114,9 @@ void launch_decode_fp4_down(const DecodeArgs& a, cudaStream_t s);
 void launch_rows_to_f16_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint32_t k_div, uint32_t rows,
                              uint32_t C, void* hi, float* rowscale, cudaStream_t s,
                              const uint32_t* rows_dev = nullptr);
+void launch_rows_to_f16_spread(const __nv_bfloat16* x, const uint32_t* dest, uint32_t k, uint32_t rows,
+                               const uint32_t* rows_dev, uint32_t dst_bound, uint32_t C, void* hi, float* rowscale,
+                               cudaStream_t s);
 void launch_rows_to_f16_f32(const float* x, uint32_t src_rows, uint32_t rows, uint32_t C, void* hi, void* lo,
                             float* rowscale, cudaStream_t s, const uint32_t* rows_dev = nullptr);
 void launch_mx_scale_range(const uint8_t* const* scales, uint32_t n, size_t bytes, uint32_t* emin,

@@ -421,6 +421,33 @@ void launch_rows_to_f16_bf16(const __nv_bfloat16* x, const uint32_t* perm, uint3
     ++g_kernel_launches;
 }
 
+// One warp per SOURCE row, stored to each of its k destination rows dest[t * k + j] (0xFFFFFFFF or a value of
+// dst_bound and above = none).  rows_dev, when given, holds the number of source rows.
+__global__ void __launch_bounds__(256) rows_to_f16_spread_kernel(const __nv_bfloat16* __restrict__ src,
+                                                                 const uint32_t* __restrict__ dest, uint32_t k,
+                                                                 uint32_t rows, const uint32_t* __restrict__ rows_dev,
+                                                                 uint32_t dst_bound, uint32_t C,
+                                                                 __half* __restrict__ hi,
+                                                                 float* __restrict__ rowscale) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t t = blockIdx.x * 8u + (threadIdx.x >> 5);
+    if (t >= rows) return;
+    if (rows_dev && t >= *rows_dev) return;
+    uint32_t mydst = lane < k ? dest[(size_t)t * k + lane] : 0xFFFFFFFFu;
+    if (mydst >= dst_bound) mydst = 0xFFFFFFFFu;
+    if (__ballot_sync(0xFFFFFFFFu, mydst != 0xFFFFFFFFu) == 0u) return;
+    warp_row_to_f16_bf16_spread(src + (size_t)t * C, C, hi, rowscale, mydst, k);
+}
+
+void launch_rows_to_f16_spread(const __nv_bfloat16* x, const uint32_t* dest, uint32_t k, uint32_t rows,
+                               const uint32_t* rows_dev, uint32_t dst_bound, uint32_t C, void* hi, float* rowscale,
+                               cudaStream_t s) {
+    if (rows == 0) return;
+    rows_to_f16_spread_kernel<<<(rows + 7) / 8, 256, 0, s>>>(x, dest, k, rows, rows_dev, dst_bound, C,
+                                                            static_cast<__half*>(hi), rowscale);
+    ++g_kernel_launches;
+}
+
 void launch_rows_to_f16_f32(const float* x, uint32_t src_rows, uint32_t rows, uint32_t C, void* hi, void* lo,
                             float* rowscale, cudaStream_t s, const uint32_t* rows_dev) {
     if (rows == 0) return;

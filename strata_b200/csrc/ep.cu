@@ -22,7 +22,8 @@
 //                                scaled by a power of two
 //   yscale  f32 [2][cap]         the factor that undoes a slot's scale
 //   src_of  u32 [2][cap]         per grouped row (local expert, source rank, source scan order): its slot
-//   vis_pos u32 [2][cap][k]      per slot: the grouped rows of the token's experts here, selection order, ~0 = none
+//   vis_pos u32 [2][cap][k]      per slot: the grouped rows of the token's experts here, selection order, packed
+//                                to the front, ~0 = none
 //   vis_w   f32 [2][cap][k]      per slot: their routing weights
 //
 // [2] is the step parity: a buffer written in step n is next written in step n + 2, and a rank
@@ -217,10 +218,14 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpWindows w, EpPlan pl
             if (vi == 0xFFFFFFFFu) continue;
             const uint32_t slot = pl.tok_base[o] + vi;
             if (slot >= w.cap) continue;   // cannot happen after a clean plan; never store outside the window
+            // the token's experts on this owner, selection order kept, listed first: the owner's loops stop at the
+            // first empty entry
+            uint32_t pos = 0xFFFFFFFFu;
+            float wt = 0.0f;
             if (lane < w.k) {
                 const uint32_t pair = t * w.k + lane;
                 const uint32_t e = ids[pair], p = inv[pair];
-                uint32_t pos = 0xFFFFFFFFu;
+                wt = weights[pair];
                 if (e < w.E && e / B == o && p != 0xFFFFFFFFu) {
                     const uint32_t row = pl.dst_row[e] + (p - offsets[e]);
                     if (row < w.cap) {
@@ -228,8 +233,14 @@ __global__ void __launch_bounds__(256) ep_dispatch_kernel(EpWindows w, EpPlan pl
                         w.src_of(o, par)[row] = slot;
                     }
                 }
-                w.vis_pos(o, par)[(size_t)slot * w.k + lane] = pos;
-                w.vis_w(o, par)[(size_t)slot * w.k + lane] = weights[pair];
+            }
+            const uint32_t valid = __ballot_sync(0xFFFFFFFFu, pos != 0xFFFFFFFFu);
+            if (lane < w.k) {
+                const uint32_t below = (1u << lane) - 1u;
+                const uint32_t idx = pos != 0xFFFFFFFFu ? __popc(valid & below)
+                                                        : __popc(valid) + __popc(~valid & below);
+                w.vis_pos(o, par)[(size_t)slot * w.k + idx] = pos;
+                w.vis_w(o, par)[(size_t)slot * w.k + idx] = wt;
             }
             const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)t * w.H);
             uint4* dst = reinterpret_cast<uint4*>(w.rows(o, par) + (size_t)slot * w.H);
@@ -399,19 +410,27 @@ __global__ void __launch_bounds__(256) ep_partial_half_kernel(EpWindows w, EpPla
     const uint32_t par = w.step & 1u, k = w.k;
     const uint32_t n = min(*pl.vis_total, w.cap);
     const uint32_t per_row = w.H / 8u;
+    // a thread forms two stretches of a slot's row (c and c + half) from the same table entries: over many GPUs a
+    // slot has only one or two experts here, and one 16-byte load per table look-up would leave the thread waiting
+    const uint32_t half = (per_row + 1u) / 2u;
     const uint32_t* __restrict__ vpos = w.vis_pos(w.rank, par);
     const float* __restrict__ vw = w.vis_w(w.rank, par);
     uint4* __restrict__ dst = reinterpret_cast<uint4*>(w.y(w.rank, par));
     bool bad = false;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n * per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < (size_t)n * half;
          i += (size_t)gridDim.x * blockDim.x) {
-        const uint32_t slot = (uint32_t)(i / per_row), c = (uint32_t)(i % per_row);
-        if (c == 0) w.yscale(w.rank, par)[slot] = 1.0f;
-        float o[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const uint32_t slot = (uint32_t)(i / half), c0 = (uint32_t)(i % half), c1 = c0 + half;
+        const bool two = c1 < per_row;
+        if (c0 == 0) w.yscale(w.rank, par)[slot] = 1.0f;
+        float o[2][8];
+#pragma unroll
+        for (int v = 0; v < 2; ++v)
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[v][q] = 0.0f;
         for (uint32_t r0 = 0; r0 < k; r0 += 4u) {
             uint32_t pos[4];
             float g[4];
-            uint4 raw[4];
+            uint4 raw[4][2];
 #pragma unroll
             for (uint32_t q = 0; q < 4u; ++q) {
                 const bool in = r0 + q < k;
@@ -419,32 +438,44 @@ __global__ void __launch_bounds__(256) ep_partial_half_kernel(EpWindows w, EpPla
                 pos[q] = p < w.cap ? p : 0xFFFFFFFFu;
                 g[q] = in ? vw[(size_t)slot * k + r0 + q] : 0.0f;
             }
+            if (pos[0] == 0xFFFFFFFFu) break;   // the list is packed: nothing follows an empty entry
 #pragma unroll
             for (uint32_t q = 0; q < 4u; ++q) {
-                raw[q] = make_uint4(0, 0, 0, 0);
-                if (pos[q] != 0xFFFFFFFFu) raw[q] = __ldg(reinterpret_cast<const uint4*>(y + (size_t)pos[q] * w.H) + c);
+                raw[q][0] = raw[q][1] = make_uint4(0, 0, 0, 0);
+                if (pos[q] != 0xFFFFFFFFu) {
+                    const uint4* row = reinterpret_cast<const uint4*>(y + (size_t)pos[q] * w.H);
+                    raw[q][0] = __ldg(row + c0);
+                    if (two) raw[q][1] = __ldg(row + c1);
+                }
             }
 #pragma unroll
             for (uint32_t q = 0; q < 4u; ++q) {
                 if (pos[q] == 0xFFFFFFFFu) continue;
-                const uint32_t hw[4] = {raw[q].x, raw[q].y, raw[q].z, raw[q].w};
 #pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[h]));
-                    o[2 * h] = __fadd_rn(o[2 * h], __fmul_rn(f.x, g[q]));
-                    o[2 * h + 1] = __fadd_rn(o[2 * h + 1], __fmul_rn(f.y, g[q]));
+                for (int v = 0; v < 2; ++v) {
+                    const uint32_t hw[4] = {raw[q][v].x, raw[q][v].y, raw[q][v].z, raw[q][v].w};
+#pragma unroll
+                    for (int h = 0; h < 4; ++h) {
+                        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[h]));
+                        o[v][2 * h] = __fadd_rn(o[v][2 * h], __fmul_rn(f.x, g[q]));
+                        o[v][2 * h + 1] = __fadd_rn(o[v][2 * h + 1], __fmul_rn(f.y, g[q]));
+                    }
                 }
             }
         }
-        uint32_t pk[4];
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-            bad |= !(fabsf(o[2 * h]) <= 3.0e38f) || !(fabsf(o[2 * h + 1]) <= 3.0e38f);
-            const __half2 v = __floats2half2_rn(fminf(fmaxf(o[2 * h], -65504.0f), 65504.0f),
-                                                fminf(fmaxf(o[2 * h + 1], -65504.0f), 65504.0f));
-            pk[h] = *reinterpret_cast<const uint32_t*>(&v);
+        for (int v = 0; v < 2; ++v) {
+            if (v == 1 && !two) break;
+            uint32_t pk[4];
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+                bad |= !(fabsf(o[v][2 * h]) <= 3.0e38f) || !(fabsf(o[v][2 * h + 1]) <= 3.0e38f);
+                const __half2 r = __floats2half2_rn(fminf(fmaxf(o[v][2 * h], -65504.0f), 65504.0f),
+                                                    fminf(fmaxf(o[v][2 * h + 1], -65504.0f), 65504.0f));
+                pk[h] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+            dst[(size_t)slot * per_row + (v ? c1 : c0)] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
         }
-        dst[(size_t)slot * per_row + c] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
     if (bad) atomicOr(status, kStatusNonFiniteOutput);
 }
@@ -584,7 +615,7 @@ void launch_ep_partial(const EpWindows& w, const EpPlan& pl, const void* y, bool
     // the row count lives on the device; the grid covers the machine and strides over the slots
     const uint32_t grid = w.cap < (uint32_t)kNumSMs * 8u ? w.cap : (uint32_t)kNumSMs * 8u;
     if (y_half) {
-        const uint64_t work = ((uint64_t)w.cap * (w.H / 8u) + 255u) / 256u;
+        const uint64_t work = ((uint64_t)w.cap * ((w.H / 8u + 1u) / 2u) + 255u) / 256u;
         const uint32_t g = work < (uint64_t)kNumSMs * 8u ? (uint32_t)work : (uint32_t)kNumSMs * 8u;
         ep_partial_half_kernel<<<g, 256, 0, s>>>(w, pl, static_cast<const __half*>(y), status);
     } else {

@@ -92,4 +92,51 @@ __device__ __forceinline__ void warp_row_to_f16_bf16(const __nv_bfloat16* __rest
     }
 }
 
+// The same conversion when one source row feeds several destination rows (a token's row in front of each of its k
+// experts): the row is read and converted once and stored k times.  Lane j < k holds destination row j in `mydst`
+// (0xFFFFFFFF = none); hi / rowscale are the bases of the destination arrays.
+__device__ __forceinline__ void warp_row_to_f16_bf16_spread(const __nv_bfloat16* __restrict__ src, uint32_t C,
+                                                            __half* __restrict__ hi, float* __restrict__ rowscale,
+                                                            uint32_t mydst, uint32_t k) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint4* p = reinterpret_cast<const uint4*>(src);
+    const uint32_t n = C / 8u;
+    float mx = 0.0f;
+    for (uint32_t base = 0; base < n; base += 256u) {
+        uint4 v[8];
+#pragma unroll
+        for (uint32_t q = 0; q < 8u; ++q) {
+            const uint32_t i = base + lane + 32u * q;
+            v[q] = i < n ? __ldg(p + i) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (uint32_t q = 0; q < 8u; ++q) mx = absmax8_bf16(v[q], mx);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+    int ex = 0;
+    if (mx > 0.0f && mx < 3.0e38f) ex = 14 - (int)((__float_as_uint(mx) >> 23) & 0xFFu) + 127;
+    ex = max(-100, min(100, ex));
+    const float sc = __uint_as_float((uint32_t)(ex + 127) << 23);
+    if (lane < k && mydst != 0xFFFFFFFFu) rowscale[mydst] = __uint_as_float((uint32_t)(127 - ex) << 23);
+    for (uint32_t base = 0; base < n; base += 256u) {
+        uint4 v[8];
+#pragma unroll
+        for (uint32_t q = 0; q < 8u; ++q) {
+            const uint32_t i = base + lane + 32u * q;
+            v[q] = i < n ? scale8_bf16_to_f16(__ldg(p + i), sc) : make_uint4(0, 0, 0, 0);
+        }
+        for (uint32_t j = 0; j < k; ++j) {
+            const uint32_t d = __shfl_sync(0xFFFFFFFFu, mydst, j);
+            if (d == 0xFFFFFFFFu) continue;
+            uint4* out = reinterpret_cast<uint4*>(hi + (size_t)d * C);
+#pragma unroll
+            for (uint32_t q = 0; q < 8u; ++q) {
+                const uint32_t i = base + lane + 32u * q;
+                if (i < n) out[i] = v[q];
+            }
+        }
+    }
+}
+
 }  // namespace smoe

@@ -83,7 +83,7 @@ def reference(cfg, x):
     return out, aux
 
 
-@pytest.mark.parametrize("world,fmt,T_local", [(1, 0, 24), (2, 1, 32), (4, 2, 16), (4, 0, 256), (2, 1, 1)])
+@pytest.mark.parametrize("world,fmt,T_local", [(1, 0, 24), (2, 1, 32), (4, 2, 16), (4, 0, 256), (2, 1, 1), (8, 0, 160), (8, 2, 3)])
 def test_peer_steps_match_single_gpu(world, fmt, T_local):
     cfg = synth.MoeConfig("ep_peer", H=512, I=256, E=16, k=4, fmt=fmt, T=T_local * world, seed=21 + fmt,
                           I_shared=128 if fmt == synth.FMT_NVFP4 else 0, zipf_s=1.1)
