@@ -948,7 +948,10 @@ static int launch_router_tc_nt(PrefillArgs a, const void* x, uint32_t T, const v
     a.pairs = T;
     a.min_rows = 0;
     prefill_tiles_kernel<<<1, 1024, 0, s>>>(a.offsets, 1, a.tile_table, 0, NT);
-    if (E % 256u == 0u)
+    // 256 experts per job while that still gives every other SM a job; with few tokens (a rank's share of an
+    // expert-parallel step) 128 per job: twice the jobs, each half as long (2048 tokens: 16 jobs otherwise)
+    const uint64_t jobs256 = (uint64_t)((T + NT - 1) / NT) * (E / 256u);
+    if (E % 256u == 0u && jobs256 * 2u >= (uint64_t)kNumSMs)
         prefill_ffn_kernel<kFmtBf16W, 2, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, map_w, map_w, a, nullptr, nullptr, nullptr);
     else
         prefill_ffn_kernel<kFmtBf16W, 1, NT><<<kNumSMs, kThreads, smem, s>>>(map_x, map_w, map_w, a, nullptr, nullptr, nullptr);
