@@ -102,12 +102,14 @@ def test_peer_steps_match_single_gpu(world, fmt, T_local):
         ranks.close()
 
 
-def test_peer_full_shape_c3_two_ranks():
-    """The bench's workload (c3: 16384 tokens, 256 MXFP4 experts, top-8, hidden 7168) over two ranks stepped by one
-    process: every owner runs the tensor-core path on 65536 grouped rows read through the slot table from 8192 + 8192
-    token rows, and returns one partial sum per token.  Both window parities must give the same bits."""
+@pytest.mark.parametrize("world", [2, 8])
+def test_peer_full_shape_c3(world):
+    """The bench's workload (c3: 16384 tokens, 256 MXFP4 experts, top-8, hidden 7168) over 2 and over 8 ranks stepped
+    by one process: every owner runs the tensor-core path on its 131072 / world grouped rows, read through the slot
+    table from the token rows it received, and returns one partial sum per received token row.  Both window parities
+    must give the same bits."""
     cfg = synth.CONFIGS["c3"]
-    world, T = 2, cfg.T
+    T = cfg.T
     T_local = T // world
     ranks = Ranks(cfg, world, T_local, cap=T_local * cfg.k * 3 // 2)
     try:
