@@ -56,7 +56,6 @@ constexpr uint32_t kMTile = 128;    // output features per tile
 constexpr uint32_t kBK = 64;        // K per pipeline stage (128 bytes of f16 per row)
 // Two rings: decoded weight tiles only have to bridge decode -> MMA (on-chip, short), while
 // the activation tiles arrive by TMA and need enough stages in flight to cover its latency.
-constexpr uint32_t kASmemStages = 2;
 constexpr uint32_t kPkBufs = 2;      // packed-weight staging blocks (256 columns each) in flight
 constexpr uint32_t kAStageCols = 64;                    // tensor-memory columns per A stage: 2 tiles x (kBK / 2)
 constexpr uint32_t kATile = kMTile * kBK * 2;  // 16 KiB
@@ -262,8 +261,9 @@ struct TileInfo {
 
 template <int NT>
 struct __align__(1024) PrefillSmem {
-    // 4-bit formats: packed staging [buffer][gate/down, up][kPkTile].
-    // BF16 weights: A tiles [stage][gate/down, up][kATile] (kPkTile == kATile).
+    // 4-bit formats: packed staging [buffer][gate/down, up][kPkTile], then the activation ring.
+    // BF16 weights: w and b together are one arena that the kernel cuts into four stages of A tiles
+    // [stage][gate/down, up][kATile] followed by the activation stages that still fit.
     uint8_t w[kPkBufs][2][kPkTile];
     uint8_t b[Geo<NT>::kBStages][Geo<NT>::kBTile];   // activation tile
     uint64_t full_a[kMaxAStages], empty_a[kMaxAStages], full_b[Geo<NT>::kBStages], empty_b[Geo<NT>::kBStages];
@@ -298,8 +298,20 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     extern __shared__ uint8_t smem_raw[];
     PrefillSmem<NT>& S =
         *reinterpret_cast<PrefillSmem<NT>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    constexpr uint32_t kNTile = Geo<NT>::kNTile, kAccCols = Geo<NT>::kAccCols, kAStages = Geo<NT>::kAStages,
-                       kBStages = Geo<NT>::kBStages;
+    constexpr uint32_t kNTile = Geo<NT>::kNTile, kAccCols = Geo<NT>::kAccCols, kAStages = Geo<NT>::kAStages;
+    // BF16 weights arrive as ready A tiles by TMA: the staging blocks and the activation ring are re-cut into four
+    // stages of weight tiles (two stages left a K-step waiting for a whole memory round trip: 112 K-steps of a
+    // router projection took 0.6 us each) and as many activation stages as the rest holds (4 at 128 tokens, 3 at 192)
+    constexpr bool BF = FMT == kFmtBf16W;
+    constexpr uint32_t kBfAStages = 4;
+    constexpr uint32_t kArena = kPkBufs * 2u * kPkTile + Geo<NT>::kBStages * Geo<NT>::kBTile;
+    constexpr uint32_t kBStages = BF ? (kArena - kBfAStages * 2u * kATile) / Geo<NT>::kBTile : Geo<NT>::kBStages;
+    static_assert(kBfAStages <= kMaxAStages && kBStages >= 2u && kBStages <= Geo<NT>::kBStages, "ring geometry");
+    uint8_t* const arena = &S.w[0][0][0];
+    auto a_tile = [&](uint32_t stage, uint32_t which) -> uint8_t* { return arena + (stage * 2u + which) * kATile; };
+    auto b_tile = [&](uint32_t stage) -> uint8_t* {
+        return BF ? arena + kBfAStages * 2u * kATile + stage * Geo<NT>::kBTile : S.b[stage];
+    };
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     constexpr bool DUAL = MODE != 1;
     constexpr bool GU = MODE == 0;
@@ -313,12 +325,12 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     if (a.tile_table[0] == 0u) return;   // nothing listed (mixed dispatch with no large group): leave before any set-up
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kAStages; ++s) {
+        for (uint32_t s = 0; s < kMaxAStages; ++s) {
             // one arrival per producer warp, or one TMA transaction group for BF16 weights
             mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps : kDecodeWarps / 2u));
             mbar_init(&S.empty_a[s], DUAL ? 2u : 1u);   // one commit per MMA issuer
         }
-        for (uint32_t s = 0; s < kBStages; ++s) {
+        for (uint32_t s = 0; s < Geo<NT>::kBStages; ++s) {
             mbar_init(&S.full_b[s], 1);
             mbar_init(&S.empty_b[s], DUAL ? 2u : 1u);
         }
@@ -356,14 +368,14 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
                     const bool tail = t.n > 128u;   // rows 128..191 arrive as a second, 64-row box
                     mbar_arrive_expect_tx(&S.full_b[s], ((16u << bsel) + (tail ? 64u : 0u)) * kBK * 2u);
-                    tma_load_2d(S.b[s], &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
-                    if (tail) tma_load_2d(S.b[s] + 128u * kBK * 2u, &maps_b.m[2], ks * kBK, t.row0 + 128u, &S.full_b[s]);
+                    tma_load_2d(b_tile(s), &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
+                    if (tail) tma_load_2d(b_tile(s) + 128u * kBK * 2u, &maps_b.m[2], ks * kBK, t.row0 + 128u, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
-                        const uint32_t sa = it % kASmemStages, pa = (it / kASmemStages) & 1u;
+                        const uint32_t sa = it % kBfAStages, pa = (it / kBfAStages) & 1u;
                         if (!mbar_wait(&S.empty_a[sa], pa ^ 1u, abort_flag)) { ok = false; break; }
                         mbar_arrive_expect_tx(&S.full_a[sa], DUAL ? 2u * kATile : kATile);
-                        tma_load_2d(S.w[sa][0], &map_a0, ks * kBK, t.m0, &S.full_a[sa]);
-                        if (DUAL) tma_load_2d(S.w[sa][1], &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[sa]);
+                        tma_load_2d(a_tile(sa, 0), &map_a0, ks * kBK, t.m0, &S.full_a[sa]);
+                        if (DUAL) tma_load_2d(a_tile(sa, 1), &map_a1, ks * kBK, t.m0 + kSecond, &S.full_a[sa]);
                     }
                 }
             }
@@ -402,7 +414,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                 const uint32_t n = (t.n + 15u) & ~15u;
                 const uint32_t idesc = umma_idesc_f16(n, FMT == kFmtBf16W ? 1u : 0u);
                 const uint32_t d = tmem_base + mi * kNTile;
-                constexpr uint32_t kRing = FMT == kFmtBf16W ? kASmemStages : kAStages;
+                constexpr uint32_t kRing = BF ? kBfAStages : kAStages;
                 for (uint32_t ks = 0; ks < k_stages; ++ks, ++it) {
                     const uint32_t sa = it % kRing, pa = (it / kRing) & 1u;
                     const uint32_t sb = it % kBStages, pb = (it / kBStages) & 1u;
@@ -411,9 +423,9 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t b = smem_u32(S.b[sb]);
+                    const uint32_t b = smem_u32(b_tile(sb));
                     if (FMT == kFmtBf16W) {
-                        const uint32_t a0 = smem_u32(S.w[sa][mi]);
+                        const uint32_t a0 = smem_u32(a_tile(sa, mi));
 #pragma unroll
                         for (uint32_t kk = 0; kk < kBK / 16u; ++kk) {
                             umma_f16(d, umma_desc_sw128(a0 + kk * 32u), umma_desc_sw128(b + kk * 32u), idesc,
