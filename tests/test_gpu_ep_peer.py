@@ -102,6 +102,28 @@ def test_peer_steps_match_single_gpu(world, fmt, T_local):
         ranks.close()
 
 
+@pytest.mark.parametrize("T_local", [4, 0])
+def test_peer_wide_rows_and_a_rank_without_tokens(T_local):
+    """Rows wider than the owner-side partial-sum kernel keeps in registers (hidden 9216 > 8192: its recompute
+    tail runs), and a step in which rank 1 has no tokens of its own but still serves its experts."""
+    cfg = synth.MoeConfig("ep_wide", H=9216, I=128, E=8, k=2, fmt=0, T=8, seed=33)
+    world = 2
+    T0 = 4
+    ranks = Ranks(cfg, world, T0, cap=32)
+    try:
+        x = synth.gen_inputs(cfg, T0 + T_local, seed=7).cuda()
+        xs = [x[:T0].contiguous(), x[T0:].contiguous()]
+        for it in range(2):
+            outs, _ = ranks.step(xs)
+        got = torch.cat([outs[0], outs[1]], 0)
+        ref, _ = reference(cfg, x)
+        assert got.shape == ref.shape
+        rel = ((got - ref).norm() / ref.norm()).item()
+        assert rel <= 2e-3, rel
+    finally:
+        ranks.close()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_peer_full_shape_c3(world):
     """The bench's workload (c3: 16384 tokens, 256 MXFP4 experts, top-8, hidden 7168) over 2 and over 8 ranks stepped
