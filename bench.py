@@ -669,6 +669,10 @@ def run_multi(args, cfg, T, rank, world):
     from strata_b200 import MoeContext, synth
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(device)
+    # before any pinned buffer exists: staging memory on the GPU's own NUMA node (eight ranks copying through the
+    # inter-socket link at once were measured at 14 GB/s each against 40 - 57 GB/s with two or four ranks)
+    from strata_b200 import hostmem
+    placement = hostmem.bind_near_gpu(device.index) if not args.no_numa else {"bound": False, "why": "--no-numa"}
     peaks = load_peaks()
     dist.init_process_group("nccl", device_id=device)
     ctx = MoeContext(device.index)
@@ -704,6 +708,10 @@ def run_multi(args, cfg, T, rank, world):
         line["clocks"] = clocks
         if sub:
             line["sub"] = sub
+    placements = [None] * world
+    dist.all_gather_object(placements, placement)
+    if rank == 0:
+        line["host_placement"] = placements
     dist.barrier()
     dist.destroy_process_group()
     return line
@@ -722,6 +730,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-sub", dest="sub", action="store_false", help="skip the sub-records of the other configurations")
     ap.add_argument("--no-parity", dest="parity", action="store_false", help="skip the oracle check of the timed layer")
+    ap.add_argument("--no-numa", action="store_true",
+                    help="N > 1: leave the ranks' CPU affinity alone (default: confine each rank to its GPU's NUMA node)")
     ap.add_argument("--microbatches", type=int, default=1,
                     help="multi-GPU, peer exchange: token micro-batches in flight per step (each on its own stream)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
