@@ -669,8 +669,9 @@ def run_multi(args, cfg, T, rank, world):
     from strata_b200 import MoeContext, synth
     device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0)))
     torch.cuda.set_device(device)
-    # before any pinned buffer exists: staging memory on the GPU's own NUMA node (eight ranks copying through the
-    # inter-socket link at once were measured at 14 GB/s each against 40 - 57 GB/s with two or four ranks)
+    # before any pinned buffer exists: staging memory on the GPU's own NUMA node.  Best effort: a virtual machine that
+    # reports one node and no node for its GPUs is left alone, and the record in the JSON line says so.  (Eight ranks
+    # copying at once were measured at 14 GB/s each against 40 - 57 GB/s with two or four ranks on such a machine.)
     from strata_b200 import hostmem
     placement = hostmem.bind_near_gpu(device.index) if not args.no_numa else {"bound": False, "why": "--no-numa"}
     peaks = load_peaks()
