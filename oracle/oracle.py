@@ -140,6 +140,7 @@ def ref():
         lib.ref_dsv4_fp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_uint32, C.c_uint32]
         lib.ref_laguna_nvfp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_float, C.c_uint32,
                                                 C.c_uint32, C.c_uint32, C.c_uint32]
+        lib.ref_inkling_nvfp4_matvec.argtypes = [f32p, f32p, u8p, u8p, C.c_float, C.c_uint32, C.c_uint32]
         lib.ref_glm_int4_matvec_scalar.argtypes = [f32p, f32p, u8p, u8p, C.c_uint32, C.c_uint32]
         lib.ref_glm_int4_matvec_rows.argtypes = [f32p, f32p, u8p, u8p, C.c_uint32, C.c_uint32,
                                                  C.c_uint32, C.c_uint32]

@@ -194,6 +194,22 @@ REF_API int ref_laguna_nvfp4_matvec(float* out, const float* in, const uint8_t* 
                                                                                                  : 1;
 }
 
+// inkling_nvfp4_matvec_rows, src/models/inkling/inkling_ops.cpp:16-69 (block scale = e4m3 * global: the
+// multiply convention of ModelOpt checkpoints, where Laguna's compressed-tensors form divides)
+REF_API int ref_inkling_nvfp4_matvec(float* out, const float* in, const uint8_t* packed,
+                                     const uint8_t* scales, float global_scale, uint32_t rows, uint32_t cols) {
+    strata::InklingNvfp4MatrixView m;
+    m.packed = bytes(packed, static_cast<std::size_t>(rows) * (cols / 2U));
+    m.scales = bytes(scales, static_cast<std::size_t>(rows) * (cols / 16U));
+    m.global_scale = global_scale;
+    m.rows = rows;
+    m.columns = cols;
+    m.packed_columns = cols / 2U;
+    m.scale_columns = cols / 16U;
+    m.group_size = 16U;
+    return strata::inkling_nvfp4_matvec_rows(m, {in, cols}, {out, rows}, 0U, rows).ok() ? 0 : 1;
+}
+
 namespace {
 strata::GlmInt4MatrixView int4_view(const uint8_t* packed, const uint8_t* scales, uint32_t rows,
                                     uint32_t cols) {

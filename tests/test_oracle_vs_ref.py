@@ -100,6 +100,29 @@ def test_nvfp4_matvec_bit_exact(port, ref):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+def test_inkling_multiply_convention_through_the_reciprocal(port, ref):
+    """Inkling (ModelOpt) NVFP4 multiplies the block scale by the tensor scale where the layer's format divides
+    (src/models/inkling/inkling_ops.cpp:50-56 against src/models/laguna/laguna_ops.cpp:77-91).  The loader header passes
+    1 / scale (`invert_global`): bit-identical when the scale is a power of two, otherwise one rounding of the block
+    scale apart -- far inside the layer tolerance."""
+    rng = np.random.default_rng(12)
+    rows, cols = 40, 768
+    packed = _rand_fp4(rng, rows, cols, 16)
+    scales = rng.integers(0, 0x7F, rows * cols // 16, dtype=np.uint8)
+    x = rng.normal(0, 1, cols).astype(np.float32)
+    for g, exact in ((0.03125, True), (2.0, True), (0.0123, False), (7.3e-3, False)):
+        want = np.empty(rows, np.float32)
+        assert ref.ref_inkling_nvfp4_matvec(P(want, f32p), P(x, f32p), P(packed, u8p), P(scales, u8p),
+                                            g, rows, cols) == 0
+        m = O.make_matrix(O.FMT_NVFP4, rows, cols, packed, scales, float(np.float32(1.0) / np.float32(g)))
+        got = O.matvec(m, x)
+        if exact:
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        else:
+            scale = np.abs(want).max()
+            assert np.abs(got - want).max() <= 4e-7 * scale * np.sqrt(cols)
+
+
 def test_int4_matvec_bit_exact_and_avx2_close(port, ref):
     rng = np.random.default_rng(3)
     rows, cols = 40, 1024
