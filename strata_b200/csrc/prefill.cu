@@ -41,14 +41,15 @@
 namespace smoe {
 
 // Tokens per tile: 192 (an expert with up to 192 rows is decoded once; two tensor-memory weight stages) when
-// groups are large, 128 (four weight stages: shorter handshakes for small tiles) otherwise.
+// groups are large, 128 (four weight stages: shorter handshakes for small tiles) when they are small, and 160
+// (three weight stages) for groups of about 128 rows, which a 128-token tile would split in two half the time.
 template <int NT>
 struct Geo {
-    static_assert(NT == 128 || NT == 192, "tile sizes");
+    static_assert(NT == 128 || NT == 160 || NT == 192, "tile sizes");
     static constexpr uint32_t kNTile = NT;
     static constexpr uint32_t kAccCols = 2u * NT;                    // accumulator columns (2 tiles x NT)
     static constexpr uint32_t kAStages = (512u - 2u * NT) / 64u;     // tensor-memory ring of decoded weight slices
-    static constexpr uint32_t kBStages = NT == 192 ? 6u : 8u;        // activation tiles in flight
+    static constexpr uint32_t kBStages = NT == 128 ? 8u : 6u;        // activation tiles in flight
     static constexpr uint32_t kBTile = NT * 64u * 2u;                // bytes of one activation tile stage
 };
 constexpr uint32_t kMaxAStages = 4;
@@ -327,7 +328,8 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kMaxAStages; ++s) {
             // one arrival per producer warp, or one TMA transaction group for BF16 weights
-            mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps : kDecodeWarps / 2u));
+            // (a stage is decoded by half of the decode warps: the other half works on the next one)
+            mbar_init(&S.full_a[s], FMT == kFmtBf16W ? 1u : (DUAL ? kDecodeWarps / 2u : kDecodeWarps / 4u));
             mbar_init(&S.empty_a[s], DUAL ? 2u : 1u);   // one commit per MMA issuer
         }
         for (uint32_t s = 0; s < Geo<NT>::kBStages; ++s) {
@@ -366,10 +368,11 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     const uint32_t s = it % kBStages, ph = (it / kBStages) & 1u;
                     if (!mbar_wait(&S.empty_b[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t bsel = t.n <= 16u ? 0u : (t.n <= 32u ? 1u : (t.n <= 64u ? 2u : 3u));
-                    const bool tail = t.n > 128u;   // rows 128..191 arrive as a second, 64-row box
-                    mbar_arrive_expect_tx(&S.full_b[s], ((16u << bsel) + (tail ? 64u : 0u)) * kBK * 2u);
+                    const bool tail = t.n > 128u;   // rows from 128 on arrive as a second box: 64 rows (192-token tile) or 32
+                    constexpr uint32_t kTailSel = NT == 192 ? 2u : 1u, kTailRows = 16u << kTailSel;
+                    mbar_arrive_expect_tx(&S.full_b[s], ((16u << bsel) + (tail ? kTailRows : 0u)) * kBK * 2u);
                     tma_load_2d(b_tile(s), &maps_b.m[bsel], ks * kBK, t.row0, &S.full_b[s]);
-                    if (tail) tma_load_2d(b_tile(s) + 128u * kBK * 2u, &maps_b.m[2], ks * kBK, t.row0 + 128u, &S.full_b[s]);
+                    if (tail) tma_load_2d(b_tile(s) + 128u * kBK * 2u, &maps_b.m[kTailSel], ks * kBK, t.row0 + 128u, &S.full_b[s]);
                     if (FMT == kFmtBf16W) {
                         const uint32_t sa = it % kBfAStages, pa = (it / kBfAStages) & 1u;
                         if (!mbar_wait(&S.empty_a[sa], pa ^ 1u, abort_flag)) { ok = false; break; }
@@ -490,18 +493,20 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
         // ---------------------------------------------------------------- weight producers
         // A warp can only write the tensor-memory lanes 32 * (warp % 4) .. + 31, and a lane holds one
         // weight row: lane i of a decode warp owns row 32 * (warp % 4) + i of one weight tile and
-        // decodes 32 of its columns per stage.  The four decode warps that share a lane quarter
-        // split into tile 0 / tile 1 and first / second 32 columns of the stage.  (32 consecutive
-        // rows reading the same swizzled 16-byte chunk index are free of bank conflicts.)  With one
-        // weight tile per stage (MODE 1) only the tile-0 warps work.
+        // decodes all 64 of its columns in EVERY OTHER stage.  The four decode warps that share a lane
+        // quarter split into tile 0 / tile 1 and even / odd stages: a warp's chain for one stage (wait for
+        // the stage's columns, store, wait for the store, arrive) takes longer than the MMAs of a stage, and
+        // with every warp in every stage that chain set the pace of the whole pipeline; now two stages'
+        // chains overlap.  (32 consecutive rows reading the same swizzled 16-byte chunk index are free of
+        // bank conflicts.)  With one weight tile per stage (MODE 1) only the tile-0 warps work.
         const uint32_t wd = warp - kFirstDecodeWarp;
         const uint32_t which = DUAL ? (wd >> 3) : 0u;
-        const uint32_t half = (wd >> 2) & 1u;
+        const uint32_t parity = (wd >> 2) & 1u;
         const uint32_t arow = (warp & 3u) * 32u + lane;
-        constexpr uint32_t CH = 1u;  // 16-byte packed chunks per thread per stage
+        constexpr uint32_t CH = 2u;  // 16-byte packed chunks per thread per stage
         const bool active = DUAL || wd < kDecodeWarps / 2u;
-        // this thread's first column in an A stage: tile, then 16 columns (32 K values) per half
-        const uint32_t a_col = kAccCols + which * (kBK / 2u) + half * 16u;
+        // this thread's first column in an A stage: tile, then 16 columns (32 K values) per chunk
+        const uint32_t a_col = kAccCols + which * (kBK / 2u);
         const uint32_t a_lane_addr = tmem_base + (((warp & 3u) * 32u) << 16) + a_col;
         uint32_t it = 0, bi = 0;
         bool ok = true;
@@ -573,19 +578,21 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     const uint32_t ks = q * (kPkCols / kBK) + j;
                     if (ks >= k_stages) break;
                     const uint32_t s = it % kAStages, ph = (it / kAStages) & 1u;
+                    const bool mine = (it & 1u) == parity;
                     ++it;
-                    // this thread's packed bytes of the stage: 16-byte chunks 2j (+1), swizzled by row
+                    if (!mine) continue;   // the other warp of this lane quarter and tile decodes this stage
+                    // this thread's packed bytes of the stage: 16-byte chunks 2j and 2j + 1, swizzled by row
                     uint4 pkv[CH];
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
-                        const uint32_t chunk = 2u * j + half + c;
+                        const uint32_t chunk = 2u * j + c;
                         pkv[c] = *reinterpret_cast<const uint4*>(pk_row + ((chunk ^ (arow & 7u)) << 4));
                     }
                     // block multipliers of this thread's 32-column chunks
                     uint32_t m[CH][4];
 #pragma unroll
                     for (uint32_t c = 0; c < CH; ++c) {
-                        const uint32_t c32 = 2u * j + half + c;  // 32-column chunk inside the block
+                        const uint32_t c32 = 2u * j + c;  // 32-column chunk inside the block
                         if (FMT == STRATA_MOE_FMT_MXFP4) {
                             const uint32_t e = (scw[c32 >> 2] >> (8u * (c32 & 3u))) & 0xFFu;
                             const uint32_t h = (uint32_t)((int32_t)e + mx_off) << 10;
@@ -604,14 +611,15 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
                     }
                     if (!mbar_wait(&S.empty_a[s], ph ^ 1u, abort_flag)) { ok = false; break; }
                     tc_fence_after();   // the MMAs that read this stage have completed
-                    {
+#pragma unroll
+                    for (uint32_t c = 0; c < CH; ++c) {
                         uint4 o[4];
-                        decode16<FMT>(pkv[0], m[0], o);
+                        decode16<FMT>(pkv[c], m[c], o);
                         const uint32_t v[16] = {o[0].x, o[0].y, o[0].z, o[0].w, o[1].x, o[1].y, o[1].z, o[1].w,
                                                 o[2].x, o[2].y, o[2].z, o[2].w, o[3].x, o[3].y, o[3].z, o[3].w};
-                        tmem_st16(a_lane_addr + s * kAStageCols, v);
-                        tmem_st_wait();
+                        tmem_st16(a_lane_addr + s * kAStageCols + c * 16u, v);
                     }
+                    tmem_st_wait();
                     tc_fence_before();   // order the tensor-memory stores before the MMA issuer's reads
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&S.full_a[s]);
@@ -902,6 +910,7 @@ int launch_prefill(const PrefillArgs& a, const void* x16, const float* x_rowscal
     const bool wide = a.ntile != 128u;
 #define STRATA_PREFILL_CASE(F)                                                                              \
     case F:                                                                                                 \
+        if (a.ntile == 160u) return launch_fmt<F, 160>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid); \
         return wide ? launch_fmt<F, 192>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid)               \
                     : launch_fmt<F, 128>(a, x16, x_rowscale, act16, pairs_cap, wmaps, s, mid);
     switch (a.fmt) {
