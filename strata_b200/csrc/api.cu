@@ -74,7 +74,7 @@ struct LayerKnobs {
     bool no_small_front = false;    // STRATA_MOE_NO_SMALL_FRONT: decode batches keep the separate route / group / convert kernels
     int prefill_min_rows = -1;      // STRATA_MOE_PREFILL_MIN_ROWS: average rows per expert for the tensor-core path
     int prefill_down_min_rows = -1; // STRATA_MOE_PREFILL_DOWN_MIN_ROWS
-    int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128 or 192
+    int prefill_ntile = 0;          // STRATA_MOE_PREFILL_NTILE: 128, 160 or 192
     int mixed_min_rows = -1;        // STRATA_MOE_MIXED_MIN_ROWS
     int mixed_min_tokens = -1;      // STRATA_MOE_MIXED_MIN_TOKENS
     int fast_router_min_tokens = 0; // STRATA_MOE_FAST_ROUTER_MIN_TOKENS: 0 = default (512), negative = never
