@@ -150,6 +150,13 @@ def test_peer_full_shape_c3(world):
     # per token too: no row may be off by more than f16 rounding of a few partial sums allows
     worst = ((second - ref).norm(dim=1) / ref.norm(dim=1).clamp_min(1e-6)).max().item()
     assert worst <= 1e-2, worst
+    # and against the CPU oracle itself on a few tokens of different ranks (the bars of the single-GPU full-shape tests)
+    import numpy as np
+    from tests import helpers as Hh
+    sub = np.asarray([0, T_local - 1, T_local, T - 1])
+    want = Hh.run_oracle(cfg, x.cpu(), token_subset=sub)
+    rel_o, mx_o = Hh.error_metrics(second[torch.from_numpy(sub).cuda()].cpu().numpy(), want["out"])
+    assert rel_o <= 2e-3 and mx_o <= 2.0 ** -6, (rel_o, mx_o)
 
 
 def test_peer_overflow_is_reported_by_every_rank_and_next_step_works():
