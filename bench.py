@@ -21,6 +21,9 @@ the 1-GPU line, the scaling curve and the prefill target are one workload.
              cpu_baseline: c0 at 8 tokens (decode, HBM target), the c1_sigmoid batch sweep
              1/4/16/64/256 (the reference's Laguna routing rule; the softmax variant is a second
              arm), c2 at 4096 tokens (prefill, tensor target); (N = 8) c4 with per-rank max latency
+  stage_ms_rank0  (N > 1) rank 0's four stages of an expert-parallel step (CUDA events)
+  host_placement  (N > 1) per rank: the NUMA node of its GPU and whether the rank confined itself to that node's
+             CPUs before allocating its pinned staging buffers (strata_b200/hostmem.py; --no-numa leaves it alone)
 
   python bench.py --impl reference ...   times only the CPU arm on the main workload.
 """
