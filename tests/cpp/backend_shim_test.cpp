@@ -341,6 +341,82 @@ void laguna_nvfp4_command() {
 }
 
 // ---------------------------------------------------------------------------------------------
+// The Inkling sink command: both always-on sink experts are plain BF16 and run on every row as one dense enqueue_moe
+// command beside the routed NVFP4 command (ref: src/models/inkling/inkling_runtime.cpp:870-900).  The reference has no
+// command test of its own for plain BF16 experts; the case is this repository's, run on both backends against the CPU
+// checker.
+strata::CudaWeight upload_bf16(strata::CudaBackend& backend, int device, std::uint64_t rows, std::uint64_t columns,
+                               std::uint32_t seed, HostWeight& keep) {
+    strata::CudaWeightDescriptor descriptor;
+    descriptor.encoding = strata::CudaWeightEncoding::Plain;
+    descriptor.dtype = strata::SafetensorsDtype::Bf16;
+    descriptor.rows = rows;
+    descriptor.columns = columns;
+    keep.weights.resize(static_cast<std::size_t>(rows * columns * 2U));
+    for (std::uint64_t index = 0U; index < rows * columns; ++index) {
+        // small exactly representable values: multiples of 1/64 in [-15/64, 15/64]
+        const int q = static_cast<int>((index * 7U + seed * 13U + (index >> 9U)) % 31U) - 15;
+        const auto b = bf16(static_cast<float>(q) / 64.0F);
+        keep.weights[2U * index] = b[0];
+        keep.weights[2U * index + 1U] = b[1];
+    }
+    keep.scales.clear();
+    strata::CudaWeight result;
+    if (!backend.upload(device, descriptor, keep.weights, keep.scales, result).ok()) ++g_failures;
+    return result;
+}
+
+void inkling_bf16_sink_command() {
+    const auto devices = strata::CudaBackend::available_devices();
+    if (!strata::CudaBackend::compiled() || devices.empty()) return;
+    constexpr std::uint32_t rows = 5U;
+    constexpr std::uint64_t hidden_columns = 1024U, intermediate_columns = 512U;
+    const int device = devices.front();
+    strata::CudaBackend backend;
+    const std::array<int, 1> selected{device};
+    REQUIRE(backend.initialize(selected, false).ok());
+    HostWeight h[6];
+    auto gate0 = upload_bf16(backend, device, intermediate_columns, hidden_columns, 1U, h[0]);
+    auto up0 = upload_bf16(backend, device, intermediate_columns, hidden_columns, 2U, h[1]);
+    auto down0 = upload_bf16(backend, device, hidden_columns, intermediate_columns, 3U, h[2]);
+    auto gate1 = upload_bf16(backend, device, intermediate_columns, hidden_columns, 4U, h[3]);
+    auto up1 = upload_bf16(backend, device, intermediate_columns, hidden_columns, 5U, h[4]);
+    auto down1 = upload_bf16(backend, device, hidden_columns, intermediate_columns, 6U, h[5]);
+    std::vector<float> hidden(rows * hidden_columns);
+    for (std::size_t index = 0U; index < hidden.size(); ++index)
+        hidden[index] = static_cast<float>(static_cast<int>(index % 17U) - 8) / 32.0F;
+    std::vector<float> expected[2];
+    for (int e = 0; e < 2; ++e) {
+        orc_expert ex{};
+        ex.gate = {3, (uint32_t)intermediate_columns, (uint32_t)hidden_columns, h[3 * e].weights.data(), nullptr, 1.0F};
+        ex.up = {3, (uint32_t)intermediate_columns, (uint32_t)hidden_columns, h[3 * e + 1].weights.data(), nullptr, 1.0F};
+        ex.down = {3, (uint32_t)hidden_columns, (uint32_t)intermediate_columns, h[3 * e + 2].weights.data(), nullptr, 1.0F};
+        expected[e].resize(static_cast<std::size_t>(rows) * hidden_columns);
+        std::vector<float> a(intermediate_columns), u(intermediate_columns);
+        for (std::uint32_t r = 0; r < rows; ++r)
+            REQUIRE(orc_expert_ffn(&ex, hidden.data() + static_cast<std::size_t>(r) * hidden_columns, 1.0F, 0, 0, a.data(), u.data(),
+                                   expected[e].data() + static_cast<std::size_t>(r) * hidden_columns) == 0);
+    }
+    const std::array<strata::CudaMoeExpert, 2> sinks{{
+        {&gate0, &up0, &down0, 1.0F},
+        {&gate1, &up1, &down1, 1.0F},
+    }};
+    std::vector<float> output(2U * rows * hidden_columns), none;
+    REQUIRE(backend.enqueue_moe(device, hidden, rows, sinks, nullptr).ok());
+    REQUIRE(backend.collect_moe(device, output, none).ok());
+    double num = 0.0, den = 0.0;
+    for (int e = 0; e < 2; ++e)
+        for (std::size_t index = 0U; index < expected[e].size(); ++index) {
+            const double d = static_cast<double>(output[e * expected[e].size() + index]) - expected[e][index];
+            num += d * d;
+            den += static_cast<double>(expected[e][index]) * expected[e][index];
+        }
+    const double rel = std::sqrt(num / den);
+    std::printf("inkling bf16 sink command: relative L2 difference to the checker %.3e\n", rel);
+    REQUIRE(den > 0.0 && rel <= 2.0e-5);
+}
+
+// ---------------------------------------------------------------------------------------------
 // ref: TEST_CASE("native CUDA backend enqueues exact grouped DeepSeek MoE when available")
 // Run at hidden = intermediate = 128 (the reference case uses 32; this library's shapes are multiples of 128) and at the
 // DeepSeek-V4 shape 4096 / 2048, the shape of the reference's host-versus-device exactness test
@@ -562,6 +638,7 @@ int main(int argc, char** argv) {
     }
     glm_int4_target_shape_command();
     laguna_nvfp4_command();
+    inkling_bf16_sink_command();
     deepseek_exact_commands<128U, 128U>();
     deepseek_exact_commands<4096U, 2048U>();
 #ifdef STRATA_TEST_REFERENCE_BACKEND
