@@ -34,6 +34,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstddef>
 #include <cstdlib>
 
 #include "common.cuh"
@@ -308,6 +309,7 @@ prefill_ffn_kernel(const __grid_constant__ BMaps maps_b, const __grid_constant__
     constexpr uint32_t kArena = kPkBufs * 2u * kPkTile + Geo<NT>::kBStages * Geo<NT>::kBTile;
     constexpr uint32_t kBStages = BF ? (kArena - kBfAStages * 2u * kATile) / Geo<NT>::kBTile : Geo<NT>::kBStages;
     static_assert(kBfAStages <= kMaxAStages && kBStages >= 2u && kBStages <= Geo<NT>::kBStages, "ring geometry");
+    static_assert(offsetof(PrefillSmem<NT>, b) == kPkBufs * 2u * kPkTile, "staging blocks and activation ring form one arena");
     uint8_t* const arena = &S.w[0][0][0];
     auto a_tile = [&](uint32_t stage, uint32_t which) -> uint8_t* { return arena + (stage * 2u + which) * kATile; };
     auto b_tile = [&](uint32_t stage) -> uint8_t* {
