@@ -442,6 +442,14 @@ int strata_moe_ep_forward(strata_moe_ep* ep, const void* x_bf16, uint32_t tokens
                           uint32_t expected_rows);
 /* Drops a step that failed between stages so that the next ep_begin is accepted. */
 int strata_moe_ep_abandon(strata_moe_ep* ep);
+/* Row counts of the last completed step, read back from the device (waits for the context's stream):
+ * sent_rows [world] = token rows this rank stored into each owner's window (its own included),
+ * received_rows = token rows it received as an owner, received_pairs = (token, expert) rows its experts
+ * computed.  A token counts once per owner, so sum(sent_rows) <= tokens * min(top_k, world).
+ * Any pointer may be NULL.  Diagnostics; ref: the per-command counters of CudaBackendStats,
+ * include/strata/cuda_backend.hpp:71-262. */
+int strata_moe_ep_last_counts(strata_moe_ep* ep, uint32_t* sent_rows, uint32_t* received_rows,
+                              uint32_t* received_pairs);
 
 #ifdef __cplusplus
 }

@@ -20,7 +20,7 @@ EXPORTS = [
     "strata_moe_ep_window_bytes", "strata_moe_ep_window_alloc", "strata_moe_ep_window_open",
     "strata_moe_ep_window_close", "strata_moe_ep_window_free", "strata_moe_ep_create", "strata_moe_ep_destroy",
     "strata_moe_ep_begin", "strata_moe_ep_dispatch", "strata_moe_ep_experts", "strata_moe_ep_finish",
-    "strata_moe_ep_forward", "strata_moe_ep_abandon",
+    "strata_moe_ep_forward", "strata_moe_ep_abandon", "strata_moe_ep_last_counts",
     "strata_moe_experts_grouped_dsv4", "strata_moe_quantize_e4m3", "strata_moe_combine_dsv4",
     "strata_moe_route_hash", "strata_moe_project_rows", "strata_moe_route_sink", "strata_moe_stable_bf16_hash", "strata_moe_check_canaries",
     "strata_moe_forward_routed", "strata_moe_latent_create", "strata_moe_latent_destroy", "strata_moe_latent_experts",
@@ -122,6 +122,7 @@ def load_library():
     lib.strata_moe_ep_finish.argtypes = [vp, vp]
     lib.strata_moe_ep_forward.argtypes = [vp, vp, u32, vp, u32]
     lib.strata_moe_ep_abandon.argtypes = [vp]
+    lib.strata_moe_ep_last_counts.argtypes = [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u32)]
     lib.strata_moe_experts_grouped_dsv4.argtypes = [vp, vp, u32, vp, vp, f32, vp]
     lib.strata_moe_quantize_e4m3.argtypes = [vp, vp, u32, u32]
     lib.strata_moe_combine_dsv4.argtypes = [vp, vp, vp, vp, u32, vp]
@@ -582,6 +583,7 @@ class EpState:
     def __init__(self, layer, rank, world, row_capacity, window_ptrs, wait_ms=0):
         self.layer, self.ctx, self.lib = layer, layer.ctx, layer.lib
         self.h = None
+        self.world = world
         self.ctx._children.add(self)
         arr = (C.c_void_p * world)(*[C.c_void_p(p) for p in window_ptrs])
         h = C.c_void_p()
@@ -620,6 +622,13 @@ class EpState:
 
     def abandon(self):
         self.ctx.check(self.lib.strata_moe_ep_abandon(self.h))
+
+    def last_counts(self):
+        """(token rows sent to each owner, token rows received, (token, expert) rows computed) of the last step."""
+        sent = (C.c_uint32 * self.world)()
+        recv, pairs = C.c_uint32(0), C.c_uint32(0)
+        self.ctx.check(self.lib.strata_moe_ep_last_counts(self.h, sent, C.byref(recv), C.byref(pairs)))
+        return list(sent), recv.value, pairs.value
 
     def close(self):
         if self.h:

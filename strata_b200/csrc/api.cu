@@ -2513,6 +2513,22 @@ int strata_moe_ep_abandon(strata_moe_ep* ep) {
     return 0;
 }
 
+int strata_moe_ep_last_counts(strata_moe_ep* ep, uint32_t* sent_rows, uint32_t* received_rows,
+                              uint32_t* received_pairs) {
+    if (!ep) return STRATA_MOE_E_INVALID;
+    strata_moe_layer* L = ep->L;
+    strata_moe_ctx* ctx = L->ctx;
+    if (ep->stage != 0) return fail(ctx, STRATA_MOE_E_BUSY, "an expert-parallel step is in progress");
+    CK(cudaSetDevice(ctx->device));
+    CK(cudaStreamSynchronize(ctx->stream));
+    if (sent_rows)
+        CK(cudaMemcpy(sent_rows, ep->pl.nvis, ep->w.world * sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (received_rows) CK(cudaMemcpy(received_rows, ep->pl.vis_total, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (received_pairs)
+        CK(cudaMemcpy(received_pairs, ep->pl.loffsets + L->d.expert_count, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
 int strata_moe_ep_forward(strata_moe_ep* ep, const void* x, uint32_t T, float* out, uint32_t expected_rows) {
     int rc = strata_moe_ep_begin(ep, x, T);
     if (rc == 0) rc = strata_moe_ep_dispatch(ep);

@@ -142,9 +142,21 @@ def test_peer_full_shape_c3(world):
         second, _ = ranks.step(xs)
         second = torch.cat([second[r] for r in range(world)], 0)
         assert torch.equal(first, second)
+        counts = [st.last_counts() for st in ranks.states]
     finally:
         ranks.close()
-    ref, _ = reference(cfg, x)
+    ref, aux = reference(cfg, x)
+    # a token's row crosses once per owning rank, however many of that rank's experts it selected
+    owners = (aux["ids"].long() // (cfg.E // world)).cpu()                       # [T, k]
+    visits = torch.zeros(T, world, dtype=torch.bool)
+    visits.scatter_(1, owners, True)
+    for r in range(world):
+        sent, received, pairs = counts[r]
+        mine = visits[r * T_local:(r + 1) * T_local]
+        assert sent == [int(v) for v in mine.sum(0)]
+        assert received == int(visits[:, r].sum())
+        assert pairs == int((owners == r).sum())
+    assert sum(c[1] for c in counts) < T * min(cfg.k, world)                     # fewer rows than (token, expert) pairs
     rel = ((second - ref).norm() / ref.norm()).item()
     assert rel <= 2e-3, rel
     # per token too: no row may be off by more than f16 rounding of a few partial sums allows
