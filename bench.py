@@ -22,6 +22,7 @@ the 1-GPU line, the scaling curve and the prefill target are one workload.
              1/4/16/64/256 (the reference's Laguna routing rule; the softmax variant is a second
              arm), c2 at 4096 tokens (prefill, tensor target); (N = 8) c4 with per-rank max latency
   stage_ms_rank0  (N > 1) rank 0's four stages of an expert-parallel step (CUDA events)
+  exchange   (N > 1) token rows per token that cross NVLink each way, read back from the library's counters
   host_placement  (N > 1) per rank: the NUMA node of its GPU and whether the rank confined itself to that node's
              CPUs before allocating its pinned staging buffers (strata_b200/hostmem.py; --no-numa leaves it alone)
 
@@ -593,6 +594,7 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
     # where a step's time goes: the four stages of the peer exchange, timed on this rank's stream
     # (each stage's time includes waiting for the slowest peer)
     stage_ms = None
+    exchange = None
     if isinstance(ep, EpMoePeer):
         st = ep.state
         acc = torch.zeros(4, dtype=torch.float64)
@@ -615,6 +617,15 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
         ctx.synchronize()
         stage_ms = dict(zip(("route_group_publish", "plan_dispatch", "wait_experts_signal", "wait_combine"),
                             [round(float(v), 4) for v in acc / reps]))
+        # what crossed: token rows per token each way (a token counts once per owning rank), beside k rows per token
+        # that an exchange per (token, expert) pair would move
+        sent, _, _ = st.last_counts()
+        remote = torch.tensor([float(sum(v for r, v in enumerate(sent) if r != rank)), float(sum(sent))],
+                              device=device, dtype=torch.float64)
+        dist.all_reduce(remote)
+        exchange = {"rows_per_token_over_nvlink": round(float(remote[0].item()) / T, 3),
+                    "rows_per_token_with_local": round(float(remote[1].item()) / T, 3),
+                    "pairs_per_token": cfg.k, "bytes_per_row_each_way": cfg.H * 2}
 
     parity = None
     if want_parity:
@@ -655,6 +666,8 @@ def measure_ep(args, cfg, T, rank, world, device, ctx, peaks, flush, strong, wan
                 "h2d_bytes_per_step": Tl * cfg.H * 2, "d2h_bytes_per_step": Tl * cfg.H * 4},
         "gpu_launches": int(launches), "stage_ms_rank0": stage_ms,
     }
+    if exchange is not None:
+        rec["exchange"] = exchange
     if parity is not None:
         rec["parity"] = parity
     if hasattr(ep, "close"):
@@ -706,7 +719,7 @@ def run_multi(args, cfg, T, rank, world):
             "dtype": "bf16", "data": DATA,
         }
         for k in ("config", "roofline", "per_rank_ms", "per_rank_max_ms", "max_rank_pairs", "mean_rank_pairs", "e2e",
-                  "gpu_launches", "stage_ms_rank0", "parity"):
+                  "gpu_launches", "stage_ms_rank0", "exchange", "parity"):
             if k in main:
                 line[k] = main[k]
         line["clocks"] = clocks

@@ -95,8 +95,9 @@ class EpMoe:
 
 class EpMoePeer:
     """The same layer with the exchange done by the library's own kernels over peer memory
-    (strata_moe_ep_*): rows are stored straight into the owners' windows by the dispatch kernel and
-    expert outputs are loaded straight from them by the combine kernel.  Nothing on the data path
+    (strata_moe_ep_*): a token's row is stored straight into the window of every rank that owns one of
+    its experts (once per owner) by the dispatch kernel, and each owner's routing-weighted partial sum
+    for the token is loaded straight from its window by the combine kernel.  Nothing on the data path
     goes through NCCL or the host; torch.distributed only carries the 64-byte window handles once."""
 
     def __init__(self, layer, cfg, rank, world, row_capacity, group=None, wait_ms=0):
