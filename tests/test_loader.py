@@ -28,6 +28,28 @@ def exe(tmp_path_factory):
     return out
 
 
+@pytest.fixture(scope="module")
+def exe_sanitized(tmp_path_factory):
+    """The same program under AddressSanitizer and UndefinedBehaviorSanitizer (the reference builds its host layer
+    that way in its sanitizer configuration, CMakeLists.txt:17, 194-200): the header-only loader parses untrusted
+    file contents, which is where such a build earns its keep.  Only the CPU sub-commands run under it."""
+    out = str(tmp_path_factory.mktemp("loader_san") / "loader_test_san")
+    lib_dir = os.path.join(ROOT, "strata_b200")
+    r = subprocess.run(["g++", "-std=c++20", "-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=all",
+                        "-fno-omit-frame-pointer", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+                        os.path.join(ROOT, "tests", "cpp", "loader_test.cpp"), "-o", out, "-L", lib_dir,
+                        "-lstrata_moe", f"-Wl,-rpath,{lib_dir}"], capture_output=True, text=True)
+    if r.returncode != 0 and "sanitize" in r.stderr and ("cannot find" in r.stderr or "unrecognized" in r.stderr):
+        pytest.skip("this toolchain has no sanitizer runtime")
+    assert r.returncode == 0, r.stderr[-3000:]
+    return out
+
+
+@pytest.fixture(params=["plain", "sanitized"])
+def cpu_exe(request):
+    return request.getfixturevalue("exe" if request.param == "plain" else "exe_sanitized")
+
+
 def fnv1a64(b):
     h = 1469598103934665603
     for v in b:
@@ -66,12 +88,12 @@ def laguna_checkpoint(cfg, layer_index):
     return layer, t
 
 
-def test_safetensors_index(exe, tmp_path):
+def test_safetensors_index(cpu_exe, tmp_path):
     cfg = synth.MoeConfig("ckpt", H=256, I=128, E=4, k=2, fmt=synth.FMT_NVFP4, T=6, seed=11, I_shared=128)
     _, tensors = laguna_checkpoint(cfg, 7)
     path = str(tmp_path / "model-00001.safetensors")
     write_safetensors(path, tensors)
-    r = subprocess.run([exe, "list", path], capture_output=True, text=True)
+    r = subprocess.run([cpu_exe, "list", path], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     seen = {}
     for line in r.stdout.splitlines():
@@ -82,7 +104,7 @@ def test_safetensors_index(exe, tmp_path):
         assert seen[name] == (dtype, tuple(shape), len(data), fnv1a64(data)), name
 
 
-def test_tiled32_layout_round_trip_against_reference_transform(exe, ref, tmp_path):
+def test_tiled32_layout_round_trip_against_reference_transform(cpu_exe, ref, tmp_path):
     H, I, shards = 256, 128, 2
     rng = np.random.default_rng(3)
     t = {k: rng.integers(0, 256, n, dtype=np.uint8) for k, n in
@@ -98,15 +120,15 @@ def test_tiled32_layout_round_trip_against_reference_transform(exe, ref, tmp_pat
         files.append(str(tmp_path / f"shard{s}.bin"))
         buf.tofile(files[-1])
     out = str(tmp_path / "canon")
-    r = subprocess.run([exe, "untile", str(H), str(I), out] + files, capture_output=True, text=True)
+    r = subprocess.run([cpu_exe, "untile", str(H), str(I), out] + files, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     for k, want in t.items():
         assert np.array_equal(np.fromfile(f"{out}.{k}", np.uint8), want), k
 
 
-def test_route_trace_is_read_by_the_reference_parser(exe, ref, tmp_path):
+def test_route_trace_is_read_by_the_reference_parser(cpu_exe, ref, tmp_path):
     path = str(tmp_path / "routes.jsonl")
-    assert subprocess.run([exe, "trace", path]).returncode == 0
+    assert subprocess.run([cpu_exe, "trace", path]).returncode == 0
     head = (C.c_uint64 * 50)()
     experts = np.zeros(64, np.uint32)
     coefs = np.zeros(64, np.float32)
