@@ -104,6 +104,46 @@ def test_safetensors_index(cpu_exe, tmp_path):
         assert seen[name] == (dtype, tuple(shape), len(data), fnv1a64(data)), name
 
 
+def test_damaged_safetensors_files_are_rejected_cleanly(exe_sanitized, tmp_path):
+    """Checkpoint files are untrusted input.  A valid file is damaged in seeded ways (bytes of the JSON header
+    overwritten, the header length changed, the file cut short, offsets moved past the end) and read by the sanitizer
+    build: every case must end with a parsed listing or a reported error, never with a sanitizer finding or a crash."""
+    cfg = synth.MoeConfig("ckpt_fuzz", H=256, I=128, E=2, k=1, fmt=synth.FMT_NVFP4, T=2, seed=5, I_shared=128)
+    _, tensors = laguna_checkpoint(cfg, 0)
+    good = str(tmp_path / "good.safetensors")
+    write_safetensors(good, tensors)
+    blob = bytearray(open(good, "rb").read())
+    hlen = struct.unpack("<Q", bytes(blob[:8]))[0]
+    rng = np.random.default_rng(2024)
+    cases = []
+    for _ in range(60):                                   # header bytes overwritten
+        b = bytearray(blob)
+        for _ in range(int(rng.integers(1, 6))):
+            b[8 + int(rng.integers(0, hlen))] = int(rng.integers(0, 256))
+        cases.append(bytes(b))
+    for v in (0, 1, 7, hlen - 1, hlen + 1, len(blob), len(blob) * 4, 2 ** 40, 2 ** 63, 2 ** 64 - 1):   # header length
+        cases.append(struct.pack("<Q", v) + bytes(blob[8:]))
+    for cut in (0, 4, 8, 9, 8 + hlen // 2, 8 + hlen, 8 + hlen + 1, len(blob) - 1):                        # truncation
+        cases.append(bytes(blob[:cut]))
+    text = bytes(blob[8:8 + hlen]).decode()
+    for old, new in (('"data_offsets": [0,', '"data_offsets": [18446744073709551615,'), ('"shape": [', '"shape": [-1, '),
+                     ('"dtype": "U8"', '"dtype": 7'), ('{', '[', ), ('"data_offsets"', '"data_offset"')):
+        t = text.replace(old, new, 1).encode()
+        t += b" " * ((8 - len(t) % 8) % 8)
+        cases.append(struct.pack("<Q", len(t)) + t + bytes(blob[8 + hlen:]))
+    verdicts = {0: 0, 1: 0}
+    for i, data in enumerate(cases):
+        path = str(tmp_path / f"case{i}.safetensors")
+        with open(path, "wb") as f:
+            f.write(data)
+        r = subprocess.run([exe_sanitized, "list", path], capture_output=True, timeout=60)
+        err = r.stderr.decode(errors="replace")     # a damaged tensor name need not be UTF-8 any more
+        assert r.returncode in (0, 1), (i, r.returncode, err[-1500:])
+        assert "Sanitizer" not in err and "runtime error" not in err, (i, err[-1500:])
+        verdicts[r.returncode] += 1
+    assert verdicts[1] >= 20, verdicts      # most damage must be noticed, not silently accepted
+
+
 def test_tiled32_layout_round_trip_against_reference_transform(cpu_exe, ref, tmp_path):
     H, I, shards = 256, 128, 2
     rng = np.random.default_rng(3)
