@@ -19,7 +19,7 @@ static std::vector<std::byte> slurp(const std::string& path) {
     std::ifstream f(path, std::ios::binary);
     std::vector<char> c((std::istreambuf_iterator<char>(f)), std::istreambuf_iterator<char>());
     std::vector<std::byte> b(c.size());
-    std::memcpy(b.data(), c.data(), c.size());
+    if (!c.empty()) std::memcpy(b.data(), c.data(), c.size());   // an empty file has no storage to copy from
     return b;
 }
 static void dump(const std::string& path, const void* p, std::size_t n) {

@@ -166,6 +166,42 @@ def test_tiled32_layout_round_trip_against_reference_transform(cpu_exe, ref, tmp
         assert np.array_equal(np.fromfile(f"{out}.{k}", np.uint8), want), k
 
 
+def test_damaged_tiled_shards_are_rejected_cleanly(exe_sanitized, ref, tmp_path):
+    """The 32-row tiled host layout read with wrong sizes: truncated, empty, over-long shards and shapes that do not
+    match the files must give a reported error under the sanitizer build, not a finding."""
+    H, I, shards = 256, 128, 2
+    rng = np.random.default_rng(9)
+    t = {k: rng.integers(0, 256, n, dtype=np.uint8) for k, n in
+         dict(w1=I * H // 2, s1=I * H // 32, w3=I * H // 2, s3=I * H // 32, w2=H * I // 2, s2=H * I // 32).items()}
+    p = lambda a: a.ctypes.data_as(O.u8p)
+    size = ref.ref_dsv4_tile_shard(None, p(t["w1"]), p(t["s1"]), p(t["w3"]), p(t["s3"]), p(t["w2"]), p(t["s2"]), H, I, 0, shards)
+    good = []
+    for sidx in range(shards):
+        buf = np.zeros(size, np.uint8)
+        ref.ref_dsv4_tile_shard(p(buf), p(t["w1"]), p(t["s1"]), p(t["w3"]), p(t["s3"]), p(t["w2"]), p(t["s2"]), H, I, sidx, shards)
+        good.append(buf)
+
+    def run(files, h=H, i=I):
+        paths = []
+        for n, data in enumerate(files):
+            paths.append(str(tmp_path / f"d{len(os.listdir(tmp_path))}_{n}.bin"))
+            np.asarray(data, np.uint8).tofile(paths[-1])
+        r = subprocess.run([exe_sanitized, "untile", str(h), str(i), str(tmp_path / "out")] + paths, capture_output=True)
+        err = r.stderr.decode(errors="replace")
+        assert "Sanitizer" not in err and "runtime error" not in err, err[-1500:]
+        return r.returncode
+
+    assert run(good) == 0
+    assert run([good[0][:-1], good[1]]) == 1                   # one byte short
+    assert run([good[0], good[1][:size // 2]]) == 1            # half a shard
+    assert run([good[0], np.zeros(0, np.uint8)]) == 1          # empty shard
+    assert run([good[0], np.concatenate([good[1], good[1][:64]])]) == 1   # over-long
+    assert run([good[0]]) in (0, 1)                            # a lone shard is a different, smaller split: either way no finding
+    assert run(good, h=H * 2) == 1 and run(good, i=I * 2) == 1  # shapes that the files do not hold
+    assert run(good, h=0) == 1 and run(good, i=0) == 1
+    assert run(good, h=100) == 1                               # not a multiple of the tile
+
+
 def test_route_trace_is_read_by_the_reference_parser(cpu_exe, ref, tmp_path):
     path = str(tmp_path / "routes.jsonl")
     assert subprocess.run([cpu_exe, "trace", path]).returncode == 0
